@@ -1,0 +1,158 @@
+"""In-tree native build for the sm_100a kernels and the libtorch C++ core.
+
+Two shared objects are produced next to this file:
+
+* ``libtitb200_kernels.so`` -- every ``csrc/kernels/*.cu`` file, compiled with
+  ``nvcc -gencode arch=compute_100a,code=sm_100a``.  It depends on the CUDA
+  runtime only and exports a plain C API (``csrc/kernels/api.h``).
+* ``_C.so`` -- the libtorch side: op bindings (``csrc/binding``) and the C++
+  framework core (``csrc/core``), linked against the kernel library.
+
+Objects are cached under ``build/`` keyed by source + header mtimes and flags,
+so a second call is a no-op.  ``nvcc`` cross-compiles without a GPU.
+"""
+from __future__ import annotations
+
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import sysconfig
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+CSRC = PKG / "csrc"
+BUILD = PKG.parent / "build" / "titb200"
+
+KERNEL_LIB = PKG / "libtitb200_kernels.so"
+CORE_LIB = PKG / "_C.so"
+
+NVCC = os.environ.get("NVCC", shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc")
+CXX = os.environ.get("CXX", "g++")
+CUDA_HOME = Path(NVCC).resolve().parent.parent
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "--expt-relaxed-constexpr", "--expt-extended-lambda", "-Xcompiler", "-fPIC",
+    "-Xcompiler", "-fvisibility=hidden", "-DNDEBUG",
+]
+
+
+def _torch_paths():
+    import torch  # noqa: F401
+    from torch.utils import cpp_extension as ce
+
+    inc = ce.include_paths()
+    lib = ce.library_paths()
+    return inc, lib
+
+
+def _hdr_stamp(dirs) -> str:
+    h = hashlib.sha1()
+    for d in dirs:
+        for p in sorted(Path(d).rglob("*")):
+            if p.suffix in (".h", ".cuh", ".hpp"):
+                h.update(str(p).encode())
+                h.update(str(p.stat().st_mtime_ns).encode())
+    return h.hexdigest()
+
+
+def _obj_key(src: Path, flags, stamp: str) -> str:
+    h = hashlib.sha1()
+    h.update(str(src).encode())
+    h.update(str(src.stat().st_mtime_ns).encode())
+    h.update(" ".join(flags).encode())
+    h.update(stamp.encode())
+    return h.hexdigest()[:16]
+
+
+def _run(cmd, verbose):
+    if verbose:
+        print(" ".join(map(str, cmd)), flush=True)
+    r = subprocess.run(list(map(str, cmd)), capture_output=True, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(r.stdout)
+        sys.stderr.write(r.stderr)
+        raise RuntimeError(f"build step failed: {' '.join(map(str, cmd[:6]))} ...")
+    if verbose and (r.stdout or r.stderr):
+        sys.stderr.write(r.stdout + r.stderr)
+
+
+def _compile_all(jobs, verbose):
+    """jobs: list of (cmd, obj_path). Skips those whose obj exists."""
+    todo = [(c, o) for c, o in jobs if not o.exists()]
+    if not todo:
+        return False
+    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 4)) as ex:
+        list(ex.map(lambda co: _run(co[0], verbose), todo))
+    return True
+
+
+def build(verbose: bool = False, force: bool = False) -> None:
+    BUILD.mkdir(parents=True, exist_ok=True)
+    stamp = _hdr_stamp([CSRC])
+
+    # ---- 1. kernel library (pure CUDA) -------------------------------------
+    cu_srcs = sorted((CSRC / "kernels").glob("*.cu"))
+    kflags = NVCC_FLAGS + ["-I", str(CSRC / "kernels")]
+    if os.environ.get("TITB200_PTXAS_V"):
+        kflags = kflags + ["-Xptxas", "-v"]
+    kjobs, kobjs = [], []
+    for s in cu_srcs:
+        o = BUILD / f"{s.stem}.{_obj_key(s, kflags, stamp)}.o"
+        if force and o.exists():
+            o.unlink()
+        kobjs.append(o)
+        kjobs.append(([NVCC, *kflags, "-c", s, "-o", o], o))
+    changed = _compile_all(kjobs, verbose)
+    if changed or not KERNEL_LIB.exists():
+        _run([NVCC, "-shared", "-o", KERNEL_LIB, *kobjs, "-cudart", "shared",
+              "-Xlinker", f"-rpath={CUDA_HOME}/lib64"], verbose)
+
+    # ---- 2. libtorch core + bindings ---------------------------------------
+    inc, lib = _torch_paths()
+    py_inc = sysconfig.get_paths()["include"]
+    cc_srcs = sorted((CSRC / "binding").glob("*.cpp")) + sorted((CSRC / "core").rglob("*.cc"))
+    cflags = [
+        "-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-DNDEBUG",
+        "-DTORCH_EXTENSION_NAME=_C", "-DTORCH_API_INCLUDE_EXTENSION_H",
+        "-D_GLIBCXX_USE_CXX11_ABI=1", "-Wno-deprecated-declarations",
+        "-I", str(CSRC), "-I", str(CSRC / "kernels"), "-I", str(CUDA_HOME / "include"),
+        "-I", py_inc,
+    ]
+    for i in inc:
+        cflags += ["-isystem", i]
+    cjobs, cobjs = [], []
+    for s in cc_srcs:
+        tag = hashlib.sha1(str(s.relative_to(CSRC)).encode()).hexdigest()[:6]
+        o = BUILD / f"{s.stem}.{tag}.{_obj_key(s, cflags, stamp)}.o"
+        if force and o.exists():
+            o.unlink()
+        cobjs.append(o)
+        cjobs.append(([CXX, *cflags, "-c", s, "-o", o], o))
+    changed2 = _compile_all(cjobs, verbose)
+    if changed or changed2 or not CORE_LIB.exists():
+        link = [CXX, "-shared", "-o", CORE_LIB, *cobjs,
+                f"-L{PKG}", "-ltitb200_kernels", "-Wl,-rpath,$ORIGIN"]
+        for l in lib:
+            link += [f"-L{l}", f"-Wl,-rpath,{l}"]
+        link += ["-lc10", "-ltorch_cpu", "-ltorch", "-ltorch_python",
+                 f"-L{CUDA_HOME}/lib64", "-lcudart", "-lc10_cuda", "-ltorch_cuda"]
+        _run(link, verbose)
+
+    # stale objects from earlier source versions
+    live = {o.name for o in kobjs + cobjs}
+    for p in BUILD.glob("*.o"):
+        if p.name not in live:
+            p.unlink()
+
+
+def is_built() -> bool:
+    return KERNEL_LIB.exists() and CORE_LIB.exists()
+
+
+if __name__ == "__main__":
+    build(verbose="-v" in sys.argv, force="-f" in sys.argv)
+    print("built:", KERNEL_LIB.name, CORE_LIB.name)

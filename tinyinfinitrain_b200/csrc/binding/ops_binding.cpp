@@ -1,0 +1,492 @@
+// Python bindings of the sm_100a kernel library: at::Tensor in, at::Tensor out.
+// Outputs are allocated with the torch caching allocator and every launch goes
+// to the current CUDA stream, so the ops can be captured in CUDA graphs.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "kernels/api.h"
+
+namespace {
+
+using at::Tensor;
+using c10::optional;
+
+inline cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+inline int dt_code(const Tensor& t) {
+  if (t.scalar_type() == at::kFloat) return 0;
+  if (t.scalar_type() == at::kBFloat16) return 1;
+  TORCH_CHECK(false, "titb200: only float32 and bfloat16 tensors are supported, got ", t.scalar_type());
+}
+inline void check_cuda(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), "titb200: ", name, " must be a CUDA tensor");
+  TORCH_CHECK(t.is_contiguous(), "titb200: ", name, " must be contiguous");
+}
+int64_t g_launches = 0;  // kernels launched through this module (host-side count)
+inline void check_rc(int rc, const char* what, int nkernels = 1) {
+  g_launches += nkernels;
+  if (rc >= 20000) {
+    const char* msg = rc == TITB_ERR_ALIGNMENT ? "operand base or row stride not 16-byte aligned"
+                      : rc == TITB_ERR_TENSOR_MAP ? "TMA tensor map could not be encoded"
+                                                  : "unsupported shape";
+    TORCH_CHECK(false, "titb200: ", what, " failed: ", msg);
+  }
+  TORCH_CHECK(rc == 0, "titb200: ", what, " failed: ", cudaGetErrorString(static_cast<cudaError_t>(rc)));
+}
+// Clears any error left on this thread by an unrelated earlier CUDA call, then launches.
+#define CHECK_RC(...)          \
+  do {                         \
+    (void)cudaGetLastError();  \
+    check_rc(__VA_ARGS__);     \
+  } while (0)
+inline const void* opt_ptr(const optional<Tensor>& t) { return t.has_value() && t->defined() ? t->data_ptr() : nullptr; }
+
+// ----------------------------------------------------------------------- GEMM
+// out[M,N] = A . B^T.  a: [M,K] (a_mn=0) or [K,M] (a_mn=1); b: [N,K] (b_mn=0) or [K,N] (b_mn=1).
+// Row strides may exceed the logical width (2-D views with stride(1) == 1).
+std::vector<Tensor> gemm(const Tensor& a, const Tensor& b, bool a_mn, bool b_mn, int64_t epilogue,
+                         const optional<Tensor>& bias, const optional<Tensor>& aux_in, bool want_aux_out,
+                         const optional<Tensor>& out_, bool accumulate, bool out_fp32, int64_t tile_n,
+                         int64_t splits, const optional<Tensor>& alpha) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda(), "titb200 gemm: CUDA tensors required");
+  TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "titb200 gemm: bf16 operands");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1, "titb200 gemm: 2-D row-major");
+  c10::cuda::CUDAGuard guard(a.device());
+  const int64_t M = a_mn ? a.size(1) : a.size(0);
+  const int64_t K = a_mn ? a.size(0) : a.size(1);
+  const int64_t N = b_mn ? b.size(1) : b.size(0);
+  const int64_t Kb = b_mn ? b.size(0) : b.size(1);
+  TORCH_CHECK(K == Kb, "titb200 gemm: reduction sizes differ: ", K, " vs ", Kb);
+  Tensor out;
+  if (out_.has_value() && out_->defined()) {
+    out = *out_;
+    TORCH_CHECK(out.dim() == 2 && out.size(0) == M && out.size(1) == N && out.stride(1) == 1, "titb200 gemm: bad out");
+    out_fp32 = out.scalar_type() == at::kFloat;
+    TORCH_CHECK(out_fp32 || out.scalar_type() == at::kBFloat16, "titb200 gemm: out must be fp32 or bf16");
+  } else {
+    out = at::empty({M, N}, a.options().dtype(out_fp32 ? at::kFloat : at::kBFloat16));
+    accumulate = false;
+  }
+  Tensor aux_out;
+  if (want_aux_out) aux_out = at::empty({M, N}, a.options());
+
+  TitbGemmDesc d{};
+  d.a = a.data_ptr(); d.b = b.data_ptr(); d.out = out.data_ptr();
+  d.M = (int)M; d.N = (int)N; d.K = (int)K;
+  d.a_mn_major = a_mn; d.b_mn_major = b_mn;
+  d.lda = a.stride(0); d.ldb = b.stride(0); d.ldo = out.stride(0);
+  d.out_fp32 = out_fp32; d.accumulate = accumulate; d.epilogue = (int)epilogue;
+  d.bias = opt_ptr(bias);
+  if (bias.has_value() && bias->defined())
+    TORCH_CHECK(bias->scalar_type() == at::kBFloat16 && bias->numel() == N, "titb200 gemm: bias must be bf16 [N]");
+  if (aux_in.has_value() && aux_in->defined()) {
+    TORCH_CHECK(aux_in->scalar_type() == at::kBFloat16 && aux_in->dim() == 2 && aux_in->size(0) == M &&
+                    aux_in->size(1) == N && aux_in->stride(1) == 1, "titb200 gemm: aux_in must be bf16 [M,N]");
+    d.aux_in = aux_in->data_ptr(); d.ld_aux_in = aux_in->stride(0);
+  }
+  if (want_aux_out) { d.aux_out = aux_out.data_ptr(); d.ld_aux_out = N; }
+  d.tile_n = (int)tile_n;
+  if (alpha.has_value() && alpha->defined()) {
+    TORCH_CHECK(alpha->is_cuda() && alpha->scalar_type() == at::kFloat && alpha->numel() == 1, "titb200 gemm: alpha must be a CUDA fp32 scalar");
+    d.alpha = alpha->data_ptr();
+  }
+  int s = splits > 0 ? (int)splits : titb_gemm_pick_splits((int)M, (int)N, (int)K);
+  if (epilogue != TITB_EPI_NONE || (N & 3)) s = 1;
+  Tensor ws;
+  if (s > 1) {
+    ws = at::empty({s, M, N}, a.options().dtype(at::kFloat));
+    d.workspace = ws.data_ptr();
+  }
+  d.splits = s;
+  CHECK_RC(titb_gemm_bf16(&d, cur_stream()), "gemm_bf16", s > 1 ? 2 : 1);
+  if (want_aux_out) return {out, aux_out};
+  return {out};
+}
+
+Tensor sgemm(const Tensor& a, const Tensor& b, bool ta, bool tb, const optional<Tensor>& out_, bool accumulate) {
+  check_cuda(a, "a"); check_cuda(b, "b");
+  TORCH_CHECK(a.scalar_type() == at::kFloat && b.scalar_type() == at::kFloat && a.dim() == 2 && b.dim() == 2);
+  c10::cuda::CUDAGuard guard(a.device());
+  const int64_t M = ta ? a.size(1) : a.size(0), K = ta ? a.size(0) : a.size(1);
+  const int64_t N = tb ? b.size(0) : b.size(1);
+  TORCH_CHECK((tb ? b.size(1) : b.size(0)) == K, "titb200 sgemm: reduction sizes differ");
+  Tensor out = (out_.has_value() && out_->defined()) ? *out_ : at::empty({M, N}, a.options());
+  if (!(out_.has_value() && out_->defined())) accumulate = false;
+  CHECK_RC(titb_sgemm(a.data_ptr<float>(), b.data_ptr<float>(), out.data_ptr<float>(), (int)M, (int)N, (int)K, ta, tb,
+                      accumulate, cur_stream()), "sgemm");
+  return out;
+}
+
+// ---------------------------------------------------------------------- norms
+std::vector<Tensor> layernorm_fwd(const Tensor& x, const Tensor& w, const Tensor& b, double eps) {
+  check_cuda(x, "x"); check_cuda(w, "weight"); check_cuda(b, "bias");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t C = x.size(-1), rows = x.numel() / C;
+  Tensor y = at::empty_like(x);
+  Tensor mean = at::empty({rows}, x.options().dtype(at::kFloat)), rstd = at::empty_like(mean);
+  CHECK_RC(titb_layernorm_fwd(x.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(), mean.data_ptr<float>(),
+                              rstd.data_ptr<float>(), rows, (int)C, (float)eps, dt_code(x), cur_stream()),
+           "layernorm_fwd");
+  return {y, mean, rstd};
+}
+// dw/db are written (or accumulated) into fp32 tensors supplied by the caller, or fresh ones.
+std::vector<Tensor> layernorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& mean,
+                                  const Tensor& rstd, const optional<Tensor>& dw_, const optional<Tensor>& db_,
+                                  bool accumulate) {
+  check_cuda(dy, "dy"); check_cuda(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t C = x.size(-1), rows = x.numel() / C;
+  Tensor dx = at::empty_like(x);
+  auto fopt = x.options().dtype(at::kFloat);
+  const bool have = dw_.has_value() && dw_->defined();
+  Tensor dw = have ? *dw_ : at::empty({C}, fopt);
+  Tensor db = (db_.has_value() && db_->defined()) ? *db_ : at::empty({C}, fopt);
+  TORCH_CHECK(dw.scalar_type() == at::kFloat && db.scalar_type() == at::kFloat, "titb200: fp32 weight grads");
+  Tensor scratch = at::empty({2, titb_layernorm_bwd_blocks(rows), C}, fopt);
+  CHECK_RC(titb_layernorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), mean.data_ptr<float>(),
+                              rstd.data_ptr<float>(), dx.data_ptr(), dw.data_ptr<float>(), db.data_ptr<float>(),
+                              scratch.data_ptr<float>(), rows, (int)C, dt_code(x), have && accumulate, cur_stream()),
+           "layernorm_bwd", 3);
+  return {dx, dw, db};
+}
+std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const Tensor& w, double eps) {
+  check_cuda(x, "x"); check_cuda(w, "weight");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t C = x.size(-1), rows = x.numel() / C;
+  Tensor y = at::empty_like(x);
+  Tensor rstd = at::empty({rows}, x.options().dtype(at::kFloat));
+  CHECK_RC(titb_rmsnorm_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr<float>(), rows, (int)C,
+                            (float)eps, dt_code(x), cur_stream()), "rmsnorm_fwd");
+  return {y, rstd};
+}
+std::vector<Tensor> rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& rstd,
+                                const optional<Tensor>& dw_, bool accumulate) {
+  check_cuda(dy, "dy"); check_cuda(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t C = x.size(-1), rows = x.numel() / C;
+  Tensor dx = at::empty_like(x);
+  auto fopt = x.options().dtype(at::kFloat);
+  const bool have = dw_.has_value() && dw_->defined();
+  Tensor dw = have ? *dw_ : at::empty({C}, fopt);
+  Tensor scratch = at::empty({2, titb_layernorm_bwd_blocks(rows), C}, fopt);
+  CHECK_RC(titb_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(),
+                            dw.data_ptr<float>(), scratch.data_ptr<float>(), rows, (int)C, dt_code(x),
+                            have && accumulate, cur_stream()), "rmsnorm_bwd", 2);
+  return {dx, dw};
+}
+
+// ---------------------------------------------------------------- activations
+Tensor gelu_fwd(const Tensor& x) {
+  check_cuda(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = at::empty_like(x);
+  CHECK_RC(titb_gelu_fwd(x.data_ptr(), y.data_ptr(), x.numel(), dt_code(x), cur_stream()), "gelu_fwd");
+  return y;
+}
+Tensor gelu_bwd(const Tensor& dy, const Tensor& x) {
+  check_cuda(x, "x"); check_cuda(dy, "dy");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor dx = at::empty_like(x);
+  CHECK_RC(titb_gelu_bwd(dy.data_ptr(), x.data_ptr(), dx.data_ptr(), x.numel(), dt_code(x), cur_stream()), "gelu_bwd");
+  return dx;
+}
+Tensor swiglu_fwd(const Tensor& x) {
+  check_cuda(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t F = x.size(-1) / 2, rows = x.numel() / (2 * F);
+  auto sizes = x.sizes().vec();
+  sizes.back() = F;
+  Tensor y = at::empty(sizes, x.options());
+  CHECK_RC(titb_swiglu_fwd(x.data_ptr(), y.data_ptr(), rows, (int)F, dt_code(x), cur_stream()), "swiglu_fwd");
+  return y;
+}
+Tensor swiglu_bwd(const Tensor& dy, const Tensor& x) {
+  check_cuda(x, "x"); check_cuda(dy, "dy");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t F = x.size(-1) / 2, rows = x.numel() / (2 * F);
+  Tensor dx = at::empty_like(x);
+  CHECK_RC(titb_swiglu_bwd(dy.data_ptr(), x.data_ptr(), dx.data_ptr(), rows, (int)F, dt_code(x), cur_stream()),
+           "swiglu_bwd");
+  return dx;
+}
+// x: [B, T, H, hd] contiguous.
+Tensor rope(const Tensor& x, int64_t pos_offset, double theta, bool inverse, bool inplace) {
+  check_cuda(x, "x");
+  TORCH_CHECK(x.dim() == 4, "titb200 rope: expects [B, T, H, hd]");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = inplace ? x : at::empty_like(x);
+  CHECK_RC(titb_rope(x.data_ptr(), y.data_ptr(), (int)x.size(0), (int)x.size(1), (int)x.size(2), (int)x.size(3),
+                     (int)pos_offset, (float)theta, inverse, dt_code(x), cur_stream()), "rope");
+  return y;
+}
+
+// ------------------------------------------------------------------ embedding
+Tensor embedding_fwd(const Tensor& idx, const Tensor& wte, const optional<Tensor>& wpe, int64_t pos_offset) {
+  check_cuda(idx, "idx"); check_cuda(wte, "wte");
+  TORCH_CHECK(idx.scalar_type() == at::kLong, "titb200 embedding: indices must be int64");
+  c10::cuda::CUDAGuard guard(wte.device());
+  const int64_t C = wte.size(1), BT = idx.numel(), T = idx.dim() >= 1 ? idx.size(-1) : 1;
+  auto sizes = idx.sizes().vec();
+  sizes.push_back(C);
+  Tensor out = at::empty(sizes, wte.options());
+  CHECK_RC(titb_embedding_fwd(idx.data_ptr<int64_t>() ? (const long long*)idx.data_ptr<int64_t>() : nullptr,
+                              wte.data_ptr(), opt_ptr(wpe), out.data_ptr(), BT, (int)T, (int)C, (int)pos_offset,
+                              dt_code(wte), cur_stream()), "embedding_fwd");
+  return out;
+}
+void embedding_bwd(const Tensor& idx, const Tensor& dout, const optional<Tensor>& dwte, const optional<Tensor>& dwpe,
+                   int64_t vocab_lo, int64_t vocab_hi) {
+  check_cuda(idx, "idx"); check_cuda(dout, "dout");
+  c10::cuda::CUDAGuard guard(dout.device());
+  const int64_t C = dout.size(-1), BT = idx.numel(), T = idx.size(-1);
+  float* pw = dwte.has_value() && dwte->defined() ? dwte->data_ptr<float>() : nullptr;
+  float* pp = dwpe.has_value() && dwpe->defined() ? dwpe->data_ptr<float>() : nullptr;
+  CHECK_RC(titb_embedding_bwd((const long long*)idx.data_ptr<int64_t>(), dout.data_ptr(), pw, pp, BT, (int)T, (int)C,
+                              (int)vocab_lo, (int)vocab_hi, dt_code(dout), cur_stream()), "embedding_bwd");
+}
+
+// ------------------------------------------------------- softmax / cross entropy
+Tensor softmax_fwd(const Tensor& x, int64_t dim) {
+  check_cuda(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  dim = at::maybe_wrap_dim(dim, x.dim());
+  int64_t outer = 1, inner = 1;
+  for (int64_t i = 0; i < dim; ++i) outer *= x.size(i);
+  for (int64_t i = dim + 1; i < x.dim(); ++i) inner *= x.size(i);
+  Tensor y = at::empty_like(x);
+  CHECK_RC(titb_softmax_fwd(x.data_ptr(), y.data_ptr(), outer, (int)x.size(dim), inner, dt_code(x), cur_stream()),
+           "softmax_fwd");
+  return y;
+}
+Tensor softmax_bwd(const Tensor& dy, const Tensor& y, int64_t dim) {
+  check_cuda(dy, "dy"); check_cuda(y, "y");
+  c10::cuda::CUDAGuard guard(y.device());
+  dim = at::maybe_wrap_dim(dim, y.dim());
+  int64_t outer = 1, inner = 1;
+  for (int64_t i = 0; i < dim; ++i) outer *= y.size(i);
+  for (int64_t i = dim + 1; i < y.dim(); ++i) inner *= y.size(i);
+  Tensor dx = at::empty_like(y);
+  CHECK_RC(titb_softmax_bwd(dy.data_ptr(), y.data_ptr(), dx.data_ptr(), outer, (int)y.size(dim), inner, dt_code(y),
+                            cur_stream()), "softmax_bwd");
+  return dx;
+}
+// logits: [rows, ld] (last dim may be padded beyond V).  Returns the mean loss (0-d fp32);
+// when write_grad the gradient scaled by grad_scale overwrites `logits`.
+Tensor xent_fused(const Tensor& logits, const Tensor& targets, int64_t V, double grad_scale, bool write_grad,
+                  double mean_scale) {
+  check_cuda(logits, "logits"); check_cuda(targets, "targets");
+  TORCH_CHECK(targets.scalar_type() == at::kLong, "titb200 cross entropy: targets must be int64");
+  c10::cuda::CUDAGuard guard(logits.device());
+  const int64_t ld = logits.size(-1), rows = logits.numel() / ld;
+  TORCH_CHECK(targets.numel() == rows, "titb200 cross entropy: one target per row");
+  Tensor losses = at::empty({rows}, logits.options().dtype(at::kFloat));
+  CHECK_RC(titb_xent_fwd_bwd(logits.data_ptr(), (const long long*)targets.data_ptr<int64_t>(),
+                             losses.data_ptr<float>(), write_grad ? logits.data_ptr() : nullptr, rows, (int)V, ld,
+                             (float)grad_scale, dt_code(logits), cur_stream()), "xent_fwd_bwd");
+  Tensor loss = at::empty({}, losses.options());
+  CHECK_RC(titb_mean(losses.data_ptr<float>(), loss.data_ptr<float>(), rows, (float)mean_scale, cur_stream()), "mean");
+  return loss;
+}
+Tensor xent_bwd(const Tensor& logits, const Tensor& targets, const Tensor& upstream, int64_t V, double grad_scale,
+                bool inplace) {
+  check_cuda(logits, "logits");
+  c10::cuda::CUDAGuard guard(logits.device());
+  const int64_t ld = logits.size(-1), rows = logits.numel() / ld;
+  Tensor up = upstream.to(at::kFloat).contiguous();
+  Tensor d = inplace ? logits : at::empty_like(logits);
+  CHECK_RC(titb_xent_bwd(logits.data_ptr(), (const long long*)targets.data_ptr<int64_t>(), d.data_ptr(),
+                         up.data_ptr<float>(), rows, (int)V, ld, (float)grad_scale, dt_code(logits), cur_stream()),
+           "xent_bwd");
+  return d;
+}
+
+// ------------------------------------------------------------------ optimizers
+void adam_flat(const Tensor& master, const optional<Tensor>& lp, const Tensor& grad, const Tensor& m, const Tensor& v,
+               double lr, double b1, double b2, double eps, double wd, int64_t step, double grad_scale,
+               const optional<Tensor>& dev_state) {
+  check_cuda(master, "master"); check_cuda(grad, "grad");
+  TORCH_CHECK(master.scalar_type() == at::kFloat && grad.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat &&
+              v.scalar_type() == at::kFloat, "titb200 adam: fp32 state");
+  c10::cuda::CUDAGuard guard(master.device());
+  const int64_t n = master.numel();
+  TORCH_CHECK(grad.numel() == n && m.numel() == n && v.numel() == n, "titb200 adam: size mismatch");
+  const double bc1 = 1.0 - std::pow(b1, (double)step), bc2 = 1.0 - std::pow(b2, (double)step);
+  void* lpp = nullptr; int lpd = 0;
+  if (lp.has_value() && lp->defined()) { TORCH_CHECK(lp->numel() == n); lpp = lp->data_ptr(); lpd = dt_code(*lp); }
+  CHECK_RC(titb_adam_flat(master.data_ptr<float>(), lpp, grad.data_ptr<float>(), m.data_ptr<float>(),
+                          v.data_ptr<float>(), n, (float)lr, (float)b1, (float)b2, (float)eps, (float)wd, (float)bc1,
+                          (float)bc2, (float)grad_scale, lpd,
+                          dev_state.has_value() && dev_state->defined() ? dev_state->data_ptr<float>() : nullptr,
+                          cur_stream()), "adam_flat");
+}
+void adam_tick(const Tensor& state, double b1, double b2) {
+  TORCH_CHECK(state.is_cuda() && state.scalar_type() == at::kFloat && state.numel() >= 4);
+  c10::cuda::CUDAGuard guard(state.device());
+  CHECK_RC(titb_adam_tick(state.data_ptr<float>(), (float)b1, (float)b2, cur_stream()), "adam_tick");
+}
+void sgd_flat(const Tensor& master, const optional<Tensor>& lp, const Tensor& grad, double lr) {
+  check_cuda(master, "master"); check_cuda(grad, "grad");
+  c10::cuda::CUDAGuard guard(master.device());
+  void* lpp = nullptr; int lpd = 0;
+  if (lp.has_value() && lp->defined()) { lpp = lp->data_ptr(); lpd = dt_code(*lp); }
+  CHECK_RC(titb_sgd_flat(master.data_ptr<float>(), lpp, grad.data_ptr<float>(), master.numel(), (float)lr, lpd,
+                         cur_stream()), "sgd_flat");
+}
+void axpy(const Tensor& y, const Tensor& x, double a) {
+  check_cuda(y, "y"); check_cuda(x, "x");
+  TORCH_CHECK(y.scalar_type() == at::kFloat && y.numel() == x.numel());
+  c10::cuda::CUDAGuard guard(y.device());
+  CHECK_RC(titb_axpy(y.data_ptr<float>(), x.data_ptr(), (float)a, y.numel(), dt_code(x), cur_stream()), "axpy");
+}
+
+// ----------------------------------------------------------- elementwise family
+Tensor unary_fwd(int64_t op, const Tensor& x, double s) {
+  check_cuda(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = at::empty_like(x);
+  CHECK_RC(titb_unary_fwd((int)op, x.data_ptr(), y.data_ptr(), x.numel(), (float)s, dt_code(x), cur_stream()), "unary");
+  return y;
+}
+Tensor unary_bwd(int64_t op, const Tensor& dy, const Tensor& saved, double s) {
+  check_cuda(dy, "dy"); check_cuda(saved, "saved");
+  c10::cuda::CUDAGuard guard(dy.device());
+  Tensor dx = at::empty_like(dy);
+  CHECK_RC(titb_unary_bwd((int)op, dy.data_ptr(), saved.data_ptr(), dx.data_ptr(), dy.numel(), (float)s, dt_code(dy),
+                          cur_stream()), "unary_bwd");
+  return dx;
+}
+// y = a (op) b with b broadcast to a's shape (right-aligned, one-way).
+Tensor binary_fwd(int64_t op, const Tensor& a, const Tensor& b) {
+  check_cuda(a, "a"); check_cuda(b, "b");
+  TORCH_CHECK(a.scalar_type() == b.scalar_type(), "titb200 binary: dtype mismatch");
+  TORCH_CHECK(a.dim() <= 8 && b.dim() <= a.dim(), "titb200 binary: b must broadcast to a (<= 8 dims)");
+  c10::cuda::CUDAGuard guard(a.device());
+  TitbBroadcast bc{};
+  bc.ndim = (int)a.dim();
+  const int64_t off = a.dim() - b.dim();
+  int64_t bstride = 1;
+  std::vector<int64_t> bs(a.dim(), 0);
+  for (int64_t d = a.dim() - 1; d >= 0; --d) {
+    bc.a_dims[d] = a.size(d);
+    if (d >= off) {
+      const int64_t bd = b.size(d - off);
+      TORCH_CHECK(bd == a.size(d) || bd == 1, "titb200 binary: cannot broadcast dim ", d);
+      bc.b_strides[d] = (bd == 1) ? 0 : bstride;
+      bstride *= bd;
+    } else {
+      bc.b_strides[d] = 0;
+    }
+  }
+  Tensor y = at::empty_like(a);
+  CHECK_RC(titb_binary_fwd((int)op, a.data_ptr(), b.data_ptr(), y.data_ptr(), a.numel(), bc, dt_code(a), cur_stream()),
+           "binary");
+  return y;
+}
+Tensor cast(const Tensor& x, bool to_bf16) {
+  check_cuda(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = at::empty(x.sizes(), x.options().dtype(to_bf16 ? at::kBFloat16 : at::kFloat));
+  CHECK_RC(titb_cast(x.data_ptr(), y.data_ptr(), x.numel(), dt_code(x), to_bf16 ? 1 : 0, cur_stream()), "cast");
+  return y;
+}
+void fill_(const Tensor& y, double value) {
+  check_cuda(y, "y");
+  c10::cuda::CUDAGuard guard(y.device());
+  CHECK_RC(titb_fill(y.data_ptr(), y.numel(), (float)value, dt_code(y), cur_stream()), "fill");
+}
+Tensor transpose_last2(const Tensor& x) {
+  check_cuda(x, "x");
+  TORCH_CHECK(x.dim() >= 2);
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t R = x.size(-2), C = x.size(-1), batch = x.numel() / (R * C);
+  auto sizes = x.sizes().vec();
+  std::swap(sizes[sizes.size() - 1], sizes[sizes.size() - 2]);
+  Tensor y = at::empty(sizes, x.options());
+  CHECK_RC(titb_transpose(x.data_ptr(), y.data_ptr(), batch, (int)R, (int)C, dt_code(x), cur_stream()), "transpose");
+  return y;
+}
+Tensor tri(const Tensor& x, int64_t diagonal, bool upper) {
+  check_cuda(x, "x");
+  TORCH_CHECK(x.dim() == 2, "titb200 tril/triu: 2-D only");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = at::empty_like(x);
+  CHECK_RC(titb_tri(x.data_ptr(), y.data_ptr(), (int)x.size(0), (int)x.size(1), (int)diagonal, upper, dt_code(x),
+                    cur_stream()), "tri");
+  return y;
+}
+// Column sums of a [rows, C] view into an fp32 [C] tensor (bias gradients).
+Tensor colsum(const Tensor& x, const optional<Tensor>& out_, bool accumulate) {
+  check_cuda(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t C = x.size(-1), rows = x.numel() / C;
+  auto fopt = x.options().dtype(at::kFloat);
+  const bool have = out_.has_value() && out_->defined();
+  Tensor out = have ? *out_ : at::empty({C}, fopt);
+  Tensor scratch = at::empty({titb_colsum_blocks(rows), C}, fopt);
+  CHECK_RC(titb_colsum(x.data_ptr(), out.data_ptr<float>(), rows, (int)C, dt_code(x), have && accumulate,
+                       scratch.data_ptr<float>(), cur_stream()), "colsum", 2);
+  return out;
+}
+
+int64_t status_read(bool clear) { return titb_status_read(clear, cur_stream()); }
+void gemm_debug_override(int64_t lbo, int64_t sbo, int64_t kstep) {
+  titb_gemm_debug_override((unsigned)lbo, (unsigned)sbo, (unsigned)kstep);
+}
+
+}  // namespace
+
+void bind_attention(pybind11::module_& m);
+void bind_comm(pybind11::module_& m);
+void bind_core(pybind11::module_& m);
+
+PYBIND11_MODULE(_C, m) {
+  m.doc() = "tinyinfinitrain_b200 native ops (sm_100a)";
+  m.def("gemm", &gemm, py::arg("a"), py::arg("b"), py::arg("a_mn") = false, py::arg("b_mn") = false,
+        py::arg("epilogue") = 0, py::arg("bias") = py::none(), py::arg("aux_in") = py::none(),
+        py::arg("want_aux_out") = false, py::arg("out") = py::none(), py::arg("accumulate") = false,
+        py::arg("out_fp32") = false, py::arg("tile_n") = 0, py::arg("splits") = 0, py::arg("alpha") = py::none());
+  m.def("sgemm", &sgemm, py::arg("a"), py::arg("b"), py::arg("ta") = false, py::arg("tb") = false,
+        py::arg("out") = py::none(), py::arg("accumulate") = false);
+  m.def("layernorm_fwd", &layernorm_fwd);
+  m.def("layernorm_bwd", &layernorm_bwd, py::arg("dy"), py::arg("x"), py::arg("w"), py::arg("mean"), py::arg("rstd"),
+        py::arg("dw") = py::none(), py::arg("db") = py::none(), py::arg("accumulate") = false);
+  m.def("rmsnorm_fwd", &rmsnorm_fwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd, py::arg("dy"), py::arg("x"), py::arg("w"), py::arg("rstd"),
+        py::arg("dw") = py::none(), py::arg("accumulate") = false);
+  m.def("gelu_fwd", &gelu_fwd);
+  m.def("gelu_bwd", &gelu_bwd);
+  m.def("swiglu_fwd", &swiglu_fwd);
+  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("rope", &rope, py::arg("x"), py::arg("pos_offset") = 0, py::arg("theta") = 10000.0, py::arg("inverse") = false,
+        py::arg("inplace") = false);
+  m.def("embedding_fwd", &embedding_fwd, py::arg("idx"), py::arg("wte"), py::arg("wpe") = py::none(),
+        py::arg("pos_offset") = 0);
+  m.def("embedding_bwd", &embedding_bwd, py::arg("idx"), py::arg("dout"), py::arg("dwte") = py::none(),
+        py::arg("dwpe") = py::none(), py::arg("vocab_lo") = 0, py::arg("vocab_hi") = (int64_t)1 << 40);
+  m.def("softmax_fwd", &softmax_fwd);
+  m.def("softmax_bwd", &softmax_bwd);
+  m.def("xent_fused", &xent_fused, py::arg("logits"), py::arg("targets"), py::arg("V"), py::arg("grad_scale"),
+        py::arg("write_grad"), py::arg("mean_scale"));
+  m.def("xent_bwd", &xent_bwd);
+  m.def("adam_flat", &adam_flat, py::arg("master"), py::arg("lp"), py::arg("grad"), py::arg("m"), py::arg("v"),
+        py::arg("lr"), py::arg("b1"), py::arg("b2"), py::arg("eps"), py::arg("wd"), py::arg("step"),
+        py::arg("grad_scale"), py::arg("dev_state") = py::none());
+  m.def("adam_tick", &adam_tick);
+  m.def("launch_count", [] { return g_launches; });
+  m.def("sgd_flat", &sgd_flat);
+  m.def("axpy", &axpy);
+  m.def("unary_fwd", &unary_fwd);
+  m.def("unary_bwd", &unary_bwd);
+  m.def("binary_fwd", &binary_fwd);
+  m.def("cast", &cast);
+  m.def("fill_", &fill_);
+  m.def("transpose_last2", &transpose_last2);
+  m.def("tri", &tri);
+  m.def("colsum", &colsum, py::arg("x"), py::arg("out") = py::none(), py::arg("accumulate") = false);
+  m.def("status_read", &status_read, py::arg("clear") = true);
+  m.def("gemm_debug_override", &gemm_debug_override);
+  bind_attention(m);
+  bind_comm(m);
+  bind_core(m);
+}

@@ -1,0 +1,186 @@
+// C API of the sm_100a kernel library (libtitb200_kernels.so).
+//
+// Every function enqueues work on `stream` and returns a cudaError_t-compatible
+// int (0 = success) from the launch; none of them synchronises.  Pointers are
+// device pointers unless a comment says otherwise.  "bf16" buffers hold
+// __nv_bfloat16, row-major, with the row stride given in elements.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define TITB_API extern "C" __attribute__((visibility("default")))
+#else
+#define TITB_API extern "C"
+#endif
+
+// Error codes of this library (outside the cudaError_t range).
+enum TitbError {
+  TITB_ERR_ALIGNMENT = 20001,   // a base pointer or row stride is not 16-byte aligned
+  TITB_ERR_TENSOR_MAP = 20002,  // cuTensorMapEncodeTiled rejected the operand description
+  TITB_ERR_SHAPE = 20003,       // unsupported shape for this kernel
+};
+
+// ---- library status ---------------------------------------------------------
+// One int per device, in device memory, written by kernels whose bounded waits
+// ran out (see common.cuh StatusCode).  titb_status_ptr returns the device
+// pointer (allocating it on first use); titb_status_read copies it to the host
+// after synchronising `stream` and optionally clears it.
+TITB_API int* titb_status_ptr(void);
+TITB_API int titb_status_read(int clear, cudaStream_t stream);
+
+// ---- tcgen05 GEMM -----------------------------------------------------------
+// D[M,N] = A . B^T over a reduction of length K, bf16 inputs, fp32 accumulation in
+// tensor memory.  Each operand is either K-major (stored [rows, K], ld >= K) or
+// MN-major (stored [K, rows], ld >= rows): this covers forward (X W^T), dgrad
+// (dY W) and wgrad (dY^T X) without a transpose pass.
+enum TitbEpilogue {
+  TITB_EPI_NONE = 0,
+  TITB_EPI_BIAS = 1,           // out = acc + bias[col]
+  TITB_EPI_BIAS_GELU = 2,      // aux_out = acc + bias ; out = gelu_tanh(aux_out)
+  TITB_EPI_DGELU = 3,          // out = acc * gelu_tanh'(aux_in)
+  TITB_EPI_BIAS_RESIDUAL = 4,  // out = acc + bias + aux_in   (bias may be null)
+  TITB_EPI_SWIGLU = 5,         // reserved
+};
+
+struct TitbGemmDesc {
+  const void* a;        // bf16
+  const void* b;        // bf16
+  void* out;            // bf16 or fp32, [M, ldo]
+  int M, N, K;
+  int a_mn_major, b_mn_major;
+  long long lda, ldb, ldo;
+  int out_fp32;         // 1: out is float
+  int accumulate;       // 1: out += result (read-modify-write)
+  int epilogue;         // TitbEpilogue
+  const void* bias;     // bf16 [N] or null
+  const void* aux_in;   // bf16 [M, ld_aux_in] or null
+  long long ld_aux_in;
+  void* aux_out;        // bf16 [M, ld_aux_out] or null
+  long long ld_aux_out;
+  int splits;           // split-K factor (>=1); >1 needs `workspace`
+  void* workspace;      // fp32 [splits, M, N] scratch when splits > 1
+  int tile_n;           // 0 = heuristic, else 128 or 256
+  const void* alpha;    // optional device fp32 scalar: result = alpha * (A . B^T) before the epilogue
+};
+TITB_API int titb_gemm_bf16(const TitbGemmDesc* d, cudaStream_t stream);
+// Picks the split-K factor the heuristic would use (so callers can size the workspace).
+TITB_API int titb_gemm_pick_splits(int M, int N, int K);
+// Debug hook: override descriptor strides for MN-major operands (0 = default).
+TITB_API void titb_gemm_debug_override(unsigned lbo, unsigned sbo, unsigned kstep);
+// fp32 SIMT GEMM for API parity with fp32 tensors: C[M,N] (+)= op(A) op(B), row-major.
+TITB_API int titb_sgemm(const float* A, const float* B, float* C, int M, int N, int K, int trans_a, int trans_b,
+                        int accumulate, cudaStream_t stream);
+
+// ---- normalisation ------------------------------------------------------------
+// dtype: 0 = fp32, 1 = bf16 for x/y/w/b; statistics are always fp32.
+TITB_API int titb_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
+                                long long rows, int C, float eps, int dtype, cudaStream_t stream);
+// dw/db partial sums use `scratch` (fp32 [2, nblocks, C]); nblocks = titb_layernorm_bwd_blocks(rows).
+TITB_API int titb_layernorm_bwd_blocks(long long rows);
+TITB_API int titb_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
+                                void* dx, float* dw, float* db, float* scratch, long long rows, int C, int dtype,
+                                int accumulate_wgrad, cudaStream_t stream);
+TITB_API int titb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long long rows, int C, float eps,
+                              int dtype, cudaStream_t stream);
+TITB_API int titb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw,
+                              float* scratch, long long rows, int C, int dtype, int accumulate_wgrad,
+                              cudaStream_t stream);
+
+// ---- activations ----------------------------------------------------------------
+TITB_API int titb_gelu_fwd(const void* x, void* y, long long n, int dtype, cudaStream_t stream);
+TITB_API int titb_gelu_bwd(const void* dy, const void* x, void* dx, long long n, int dtype, cudaStream_t stream);
+// SwiGLU on a fused [rows, 2*F] projection: y[r, f] = silu(x[r, f]) * x[r, F + f].
+TITB_API int titb_swiglu_fwd(const void* x, void* y, long long rows, int F, int dtype, cudaStream_t stream);
+TITB_API int titb_swiglu_bwd(const void* dy, const void* x, void* dx, long long rows, int F, int dtype,
+                             cudaStream_t stream);
+
+// ---- rotary embedding --------------------------------------------------------------
+// x: [B, T, H, hd] (contiguous), rotates pairs (i, i + hd/2) with angle pos * theta^(-2i/hd).
+// inverse = 1 applies the transpose rotation (the backward pass).  In place when y == x.
+TITB_API int titb_rope(const void* x, void* y, int B, int T, int H, int hd, int pos_offset, float theta,
+                       int inverse, int dtype, cudaStream_t stream);
+
+// ---- embedding ------------------------------------------------------------------------
+// out[b,t,:] = wte[idx[b,t],:] (+ wpe[t + pos_offset,:] when wpe != null).
+TITB_API int titb_embedding_fwd(const long long* idx, const void* wte, const void* wpe, void* out, long long BT,
+                                int T, int C, int pos_offset, int dtype, cudaStream_t stream);
+// dwte[idx[b,t],:] += dout[b,t,:] ; dwpe[t,:] += sum_b dout[b,t,:].  fp32 gradient buffers.
+TITB_API int titb_embedding_bwd(const long long* idx, const void* dout, float* dwte, float* dwpe, long long BT,
+                                int T, int C, int vocab_lo, int vocab_hi, int dtype, cudaStream_t stream);
+
+// ---- softmax / cross entropy -------------------------------------------------------------
+TITB_API int titb_softmax_fwd(const void* x, void* y, long long outer, int axis, long long inner, int dtype,
+                              cudaStream_t stream);
+TITB_API int titb_softmax_bwd(const void* dy, const void* y, void* dx, long long outer, int axis, long long inner,
+                              int dtype, cudaStream_t stream);
+// Fused loss + gradient.  logits: [rows, ld] with V valid columns (columns >= V are
+// padding: ignored for the loss, gradient written as 0).  losses: fp32 [rows].  When
+// dlogits != null it receives grad_scale * (softmax - onehot); it may alias logits.
+TITB_API int titb_xent_fwd_bwd(const void* logits, const long long* targets, float* losses, void* dlogits,
+                               long long rows, int V, long long ld, float grad_scale, int dtype,
+                               cudaStream_t stream);
+TITB_API int titb_xent_bwd(const void* logits, const long long* targets, void* dlogits, const float* upstream,
+                           long long rows, int V, long long ld, float grad_scale, int dtype, cudaStream_t stream);
+TITB_API int titb_mean(const float* x, float* out, long long n, float scale, cudaStream_t stream);
+
+// ---- optimizers ----------------------------------------------------------------------------
+// One launch over a flat range.  master/m/v fp32; grad fp32; param_bf16 (optional) gets the
+// rounded copy of the updated master weights.
+TITB_API int titb_adam_flat(float* master, void* param_lp, const float* grad, float* m, float* v, long long n,
+                            float lr, float beta1, float beta2, float eps, float weight_decay, float bc1,
+                            float bc2, float grad_scale, int lp_dtype, const float* dev_state,
+                            cudaStream_t stream);
+// dev_state: optional device float[4] = {t, 1-beta1^t, 1-beta2^t, lr} overriding bc1/bc2/lr;
+// titb_adam_tick advances it by one step on the device (graph-capturable step counter).
+TITB_API int titb_adam_tick(float* state, float beta1, float beta2, cudaStream_t stream);
+TITB_API int titb_axpy(float* y, const void* x, float a, long long n, int x_dtype, cudaStream_t stream);
+TITB_API int titb_sgd_flat(float* master, void* param_lp, const float* grad, long long n, float lr, int lp_dtype,
+                           cudaStream_t stream);
+
+// ---- elementwise family ------------------------------------------------------------------------
+enum TitbUnary {
+  TITB_NEG = 0, TITB_RECIPROCAL, TITB_SIN, TITB_COS, TITB_TANH, TITB_POW_SCALAR_EXP, TITB_POW_SCALAR_BASE,
+  TITB_RSQRT, TITB_EQUALS_SCALAR, TITB_ADD_SCALAR, TITB_MUL_SCALAR, TITB_SIGMOID, TITB_COPY,
+};
+TITB_API int titb_unary_fwd(int op, const void* x, void* y, long long n, float s, int dtype, cudaStream_t stream);
+// dx = dy * f'(.) where the saved tensor is the input (or the output for tanh/sigmoid).
+TITB_API int titb_unary_bwd(int op, const void* dy, const void* saved, void* dx, long long n, float s, int dtype,
+                            cudaStream_t stream);
+enum TitbBinary { TITB_ADD = 0, TITB_SUB, TITB_MUL, TITB_DIV };
+// y = a (op) broadcast(b); b is right-aligned against a, b_numel divides a_numel and the
+// broadcast is described by up to 8 (a_dim, b_stride) pairs passed by value.
+struct TitbBroadcast {
+  int ndim;
+  long long a_dims[8];
+  long long b_strides[8];  // 0 where b is broadcast
+};
+TITB_API int titb_binary_fwd(int op, const void* a, const void* b, void* y, long long n, TitbBroadcast bc,
+                             int dtype, cudaStream_t stream);
+TITB_API int titb_cast(const void* x, void* y, long long n, int src_dtype, int dst_dtype, cudaStream_t stream);
+TITB_API int titb_fill(void* y, long long n, float value, int dtype, cudaStream_t stream);
+// 2-D batched transpose: in [batch, R, C] -> out [batch, C, R].
+TITB_API int titb_transpose(const void* x, void* y, long long batch, int R, int C, int dtype, cudaStream_t stream);
+TITB_API int titb_tri(const void* x, void* y, int R, int C, int diagonal, int upper, int dtype,
+                      cudaStream_t stream);
+TITB_API int titb_colsum(const void* x, float* out, long long rows, int C, int dtype, int accumulate,
+                         float* scratch, cudaStream_t stream);
+TITB_API int titb_colsum_blocks(long long rows);
+
+// ---- attention --------------------------------------------------------------------------------------
+// Causal self-attention over packed projections.  q: [B, T, Hq, hd], k/v: [B, T, Hkv, hd] with
+// arbitrary (16-byte aligned) token strides so a fused QKV buffer can be addressed in place.
+struct TitbAttnDesc {
+  const void* q; const void* k; const void* v;   // bf16
+  void* o;                                        // bf16 [B, T, Hq, hd]
+  float* lse;                                     // fp32 [B, Hq, T]
+  const void* d_o; void* dq; void* dk; void* dv;   // backward only
+  float* delta;                                   // fp32 [B, Hq, T] scratch (backward)
+  float* dq_accum;                                // fp32 [B, T, Hq, hd] scratch (backward)
+  int B, T, Hq, Hkv, hd;
+  long long q_stride_t, k_stride_t, v_stride_t, o_stride_t;   // elements between tokens
+  long long dq_stride_t, dk_stride_t, dv_stride_t, do_stride_t;
+  float scale;
+};
+TITB_API int titb_attn_fwd(const TitbAttnDesc* d, cudaStream_t stream);
+TITB_API int titb_attn_bwd(const TitbAttnDesc* d, cudaStream_t stream);

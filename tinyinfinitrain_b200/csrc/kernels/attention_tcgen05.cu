@@ -1,0 +1,687 @@
+// Fused causal self-attention (flash-attention style) on tcgen05 tensor cores.
+//
+// Replaces the reference's attention chain -- QKV split, four transposes, a batched
+// matmul that materialises the [B,H,T,T] scores, scale, mask, softmax, a second
+// batched matmul and a transpose back (example/gpt2/net.cc:77-108; kernels
+// split.cu, transform.cu, softmax.cu, linear.cu) -- with one forward and one
+// backward kernel that keep the score tile in tensor memory:
+//
+//   forward, one CTA per (128 query rows, head, batch), loop over key blocks j <= i:
+//     S = Q K_j^T          tcgen05.mma, A/B from TMA-loaded swizzled smem, D in TMEM
+//     online softmax       128 threads, one score row each, read with tcgen05.ld
+//     P -> smem (bf16)     written in the 128-byte-swizzle layout the MMA expects
+//     O_blk = P V_j        tcgen05.mma with V as an MN-major operand (no transpose)
+//     O = O * alpha + O_blk in registers; finally O / l and the log-sum-exp row.
+//
+//   backward, one CTA per (128 key rows, kv head, batch), loop over query blocks i >= j
+//   and over the query heads that share the kv head (GQA):
+//     S = Q_i K_j^T, dP = dO_i V_j^T            -> TMEM
+//     P = exp(S - lse), dS = P (dP - delta)     -> smem (bf16), both stored once and read
+//                                                  as K-major and as MN-major operands
+//     dV += P^T dO_i, dK += dS^T Q_i            accumulate in TMEM over the whole loop
+//     dQ_i += dS K_j                            TMEM -> fp32 vector reductions in HBM
+//
+// q/k/v are addressed in place inside a fused projection buffer through TMA tensor
+// maps (row stride = token stride), so no split/transpose kernel runs.  All waits
+// are bounded (ptx_sm100.cuh).
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "api.h"
+#include "ptx_sm100.cuh"
+
+namespace titb {
+
+bool make_tmap_bf16_2d(CUtensorMap* m, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
+                       uint32_t box_inner, uint32_t box_outer);
+
+constexpr int kAttnThreads = 192;
+constexpr int kBlk = 128;             // query rows per CTA tile and keys per step
+constexpr int kChunkBytes = kBlk * 128;  // one [128 rows x 64 bf16] swizzled sub-tile
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Byte offset of 8 consecutive bf16 (one 16-byte unit) in a [128 x 128] tile stored as two
+// [128 rows x 128 B] sub-tiles with the 128-byte swizzle: unit index u = col / 8 in 0..15.
+__device__ __forceinline__ uint32_t swz_off(int row, int u) {
+  return static_cast<uint32_t>((u >> 3) * kChunkBytes + row * 128 + (((u & 7) ^ (row & 7)) << 4));
+}
+
+struct AttnArgs {
+  int B, T, Hq, Hkv, hd;
+  float scale;
+  bf16* o;
+  float* lse;
+  long long o_stride_t;
+  // backward
+  const float* delta;
+  float* dq_accum;  // fp32 [B, T, Hq, hd]
+  bf16* dk;
+  bf16* dv;
+  long long dk_stride_t, dv_stride_t;
+  int* status;
+};
+
+// ------------------------------------------------------------------------- forward
+template <int HD>
+struct FwdCfg {
+  static constexpr int kTileBytes = kBlk * HD * 2;  // Q, K or V tile
+  static constexpr int kStages = 2;
+  static constexpr int kQ = 0;
+  static constexpr int kK = kQ + kTileBytes;
+  static constexpr int kV = kK + kStages * kTileBytes;
+  static constexpr int kP = kV + kStages * kTileBytes;
+  static constexpr int kBar = kP + kBlk * kBlk * 2;
+  static constexpr int kSmem = kBar + 128;
+  static constexpr int kTmemCols = 256;  // S: [0,128)  O_blk: [128, 128+HD)
+};
+
+template <int HD>
+__global__ void __launch_bounds__(kAttnThreads, (HD == 64) ? 2 : 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                const __grid_constant__ CUtensorMap tv, const AttnArgs p) {
+  using Cfg = FwdCfg<HD>;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kBar);
+  uint64_t* q_full = bars;          // 1
+  uint64_t* kv_full = bars + 1;     // [2]
+  uint64_t* kv_empty = bars + 3;    // [2]
+  uint64_t* s_full = bars + 5;
+  uint64_t* p_full = bars + 6;
+  uint64_t* o_full = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nqb = (p.T + kBlk - 1) / kBlk;
+  const int qb = nqb - 1 - blockIdx.x;  // heaviest tiles first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.Hq / p.Hkv);
+  const int q0 = qb * kBlk;
+  const int nblk = qb + 1;
+
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) { ptx::mbar_init(&kv_full[s], 1); ptx::mbar_init(&kv_empty[s], 1); }
+    ptx::mbar_init(s_full, 1);
+    ptx::mbar_init(p_full, 4);
+    ptx::mbar_init(o_full, 1);
+    *abort_flag = (ptx::smem_u32(smem) & 1023u) ? 1u : 0u;  // swizzled tiles need a 1024-byte aligned base
+    ptx::mbar_fence_init();
+    ptx::tma_prefetch_desc(&tq);
+    ptx::tma_prefetch_desc(&tk);
+    ptx::tma_prefetch_desc(&tv);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tO = tmem_base + 128;
+  const bool bad_align = (*abort_flag != 0);
+
+  if (bad_align) {
+    // fall through to the common exit
+  } else if (warp == 0) {
+    if (lane == 0) {
+      ptx::mbar_expect_tx(q_full, Cfg::kTileBytes);
+#pragma unroll
+      for (int c = 0; c < HD / 64; ++c)
+        ptx::tma_load_2d(smem + Cfg::kQ + c * kChunkBytes, &tq, q_full, h * HD + c * 64, b * p.T + q0);
+      for (int j = 0; j < nblk; ++j) {
+        const int st = j & 1;
+        if (!ptx::mbar_wait(&kv_empty[st], ((j >> 1) & 1) ^ 1u, abort_flag)) break;
+        ptx::mbar_expect_tx(&kv_full[st], 2 * Cfg::kTileBytes);
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c) {
+          ptx::tma_load_2d(smem + Cfg::kK + st * Cfg::kTileBytes + c * kChunkBytes, &tk, &kv_full[st],
+                           hk * HD + c * 64, b * p.T + j * kBlk);
+          ptx::tma_load_2d(smem + Cfg::kV + st * Cfg::kTileBytes + c * kChunkBytes, &tv, &kv_full[st],
+                           hk * HD + c * 64, b * p.T + j * kBlk);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = ptx::make_idesc_bf16(128, 128, 0, 0);
+      const uint32_t idesc_o = ptx::make_idesc_bf16(128, HD, 0, 1);
+      const uint32_t q_base = ptx::smem_u32(smem + Cfg::kQ);
+      const uint32_t p_base = ptx::smem_u32(smem + Cfg::kP);
+      auto issue_s = [&](int j) {
+        const uint32_t k_base = ptx::smem_u32(smem + Cfg::kK + (j & 1) * Cfg::kTileBytes);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t off = (k >> 2) * kChunkBytes + (k & 3) * 32;
+          ptx::mma_f16_ss(tS, ptx::make_smem_desc(q_base + off, 16, 1024), ptx::make_smem_desc(k_base + off, 16, 1024),
+                          idesc_s, k > 0);
+        }
+        ptx::tc_commit(s_full);
+      };
+      bool ok = ptx::mbar_wait(q_full, 0, abort_flag) && ptx::mbar_wait(&kv_full[0], 0, abort_flag);
+      if (ok) {
+        ptx::tc_fence_after_sync();
+        issue_s(0);
+      }
+      for (int j = 0; j < nblk && ok; ++j) {
+        if (!ptx::mbar_wait(p_full, j & 1, abort_flag)) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t v_base = ptx::smem_u32(smem + Cfg::kV + (j & 1) * Cfg::kTileBytes);
+#pragma unroll
+        for (int k = 0; k < kBlk / 16; ++k) {
+          const uint32_t a_off = (k >> 2) * kChunkBytes + (k & 3) * 32;
+          ptx::mma_f16_ss(tO, ptx::make_smem_desc(p_base + a_off, 16, 1024),
+                          ptx::make_smem_desc(v_base + k * 2048, kChunkBytes, 1024), idesc_o, k > 0);
+        }
+        ptx::tc_commit(o_full);
+        ptx::tc_commit(&kv_empty[j & 1]);
+        if (j + 1 < nblk) {
+          if (!ptx::mbar_wait(&kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag)) break;
+          ptx::tc_fence_after_sync();
+          issue_s(j + 1);
+        }
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const int q_idx = q0 + row;
+    const uint32_t lane_sel = static_cast<uint32_t>(quad * 32) << 16;
+    const float sc = p.scale * kLog2e;
+    float m = -INFINITY, l = 0.f;
+    float o[HD];
+#pragma unroll
+    for (int d = 0; d < HD; ++d) o[d] = 0.f;
+    uint8_t* p_smem = smem + Cfg::kP;
+    bool ok = true;
+    for (int j = 0; j < nblk; ++j) {
+      if (!ptx::mbar_wait(s_full, j & 1, abort_flag)) { ok = false; break; }
+      ptx::tc_fence_after_sync();
+      const bool diag = (j == qb);
+      const int kv0 = j * kBlk;
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        ptx::tmem_ld32(tS + lane_sel + c * 32, r);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          float x = __uint_as_float(r[e]) * sc;
+          if (diag && (kv0 + c * 32 + e > q_idx)) x = -INFINITY;
+          mx = fmaxf(mx, x);
+        }
+      }
+      const float m_new = fmaxf(m, mx);
+      const float alpha = ex2(m - m_new);
+      float rs = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        ptx::tmem_ld32(tS + lane_sel + c * 32, r);
+        ptx::tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float x0 = __uint_as_float(r[e]) * sc, x1 = __uint_as_float(r[e + 1]) * sc;
+          if (diag) {
+            if (kv0 + c * 32 + e > q_idx) x0 = -INFINITY;
+            if (kv0 + c * 32 + e + 1 > q_idx) x1 = -INFINITY;
+          }
+          const float p0 = ex2(x0 - m_new), p1 = ex2(x1 - m_new);
+          rs += p0 + p1;
+          pk[e >> 1] = pack_bf16x2(p0, p1);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          *reinterpret_cast<uint4*>(p_smem + swz_off(row, c * 4 + u)) =
+              make_uint4(pk[u * 4], pk[u * 4 + 1], pk[u * 4 + 2], pk[u * 4 + 3]);
+      }
+      l = l * alpha + rs;
+      m = m_new;
+      ptx::fence_proxy_async_smem();
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(p_full);
+      if (!ptx::mbar_wait(o_full, j & 1, abort_flag)) { ok = false; break; }
+      ptx::tc_fence_after_sync();
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t r[32];
+        ptx::tmem_ld32(tO + lane_sel + c * 32, r);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) o[c * 32 + e] = o[c * 32 + e] * alpha + __uint_as_float(r[e]);
+      }
+    }
+    if (ok && q_idx < p.T) {
+      const float inv = 1.f / l;
+      bf16* dst = p.o + (static_cast<long long>(b) * p.T + q_idx) * p.o_stride_t + h * HD;
+#pragma unroll
+      for (int d = 0; d < HD; d += 8) {
+        uint4 u;
+        u.x = pack_bf16x2(o[d] * inv, o[d + 1] * inv);
+        u.y = pack_bf16x2(o[d + 2] * inv, o[d + 3] * inv);
+        u.z = pack_bf16x2(o[d + 4] * inv, o[d + 5] * inv);
+        u.w = pack_bf16x2(o[d + 6] * inv, o[d + 7] * inv);
+        *reinterpret_cast<uint4*>(dst + d) = u;
+      }
+      p.lse[(static_cast<long long>(b) * p.Hq + h) * p.T + q_idx] = (m + log2f(l)) * 0.6931471805599453f;
+    }
+  }
+
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, kStatusMbarTimeout);
+}
+
+// ------------------------------------------------------------------------ backward
+template <int HD>
+struct BwdCfg {
+  static constexpr int kTileBytes = kBlk * HD * 2;
+  static constexpr int kStages = (HD == 64) ? 2 : 1;
+  static constexpr bool kAliasDq = (HD > 64);  // dQ partial reuses the S columns when TMEM is full
+  static constexpr int kK = 0;
+  static constexpr int kV = kK + kTileBytes;
+  static constexpr int kQ = kV + kTileBytes;
+  static constexpr int kDO = kQ + kStages * kTileBytes;
+  static constexpr int kP = kDO + kStages * kTileBytes;
+  static constexpr int kDS = kP + kBlk * kBlk * 2;
+  static constexpr int kBar = kDS + kBlk * kBlk * 2;
+  static constexpr int kSmem = kBar + 128;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kColS = 0, kColDP = 128, kColDV = 256, kColDK = 256 + HD;
+  static constexpr int kColDQ = kAliasDq ? 0 : 256 + 2 * HD;
+};
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo, const AttnArgs p) {
+  using Cfg = BwdCfg<HD>;
+  constexpr int S = Cfg::kStages;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kBar);
+  uint64_t* kv_full = bars;            // 1
+  uint64_t* qdo_full = bars + 1;       // [2]
+  uint64_t* qdo_empty = bars + 3;      // [2]
+  uint64_t* sdp_full = bars + 5;
+  uint64_t* pds_full = bars + 6;
+  uint64_t* dq_full = bars + 7;
+  uint64_t* dq_free = bars + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nqb = (p.T + kBlk - 1) / kBlk;
+  const int jb = blockIdx.x;  // key block
+  const int hk = blockIdx.y, b = blockIdx.z;
+  const int G = p.Hq / p.Hkv;
+  const int nq = nqb - jb;     // query blocks jb .. nqb-1
+  const int niter = G * nq;
+
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) { ptx::mbar_init(&qdo_full[s], 1); ptx::mbar_init(&qdo_empty[s], 1); }
+    ptx::mbar_init(sdp_full, 1);
+    ptx::mbar_init(pds_full, 4);
+    ptx::mbar_init(dq_full, 1);
+    ptx::mbar_init(dq_free, 4);
+    *abort_flag = (ptx::smem_u32(smem) & 1023u) ? 1u : 0u;
+    ptx::mbar_fence_init();
+    ptx::tma_prefetch_desc(&tq);
+    ptx::tma_prefetch_desc(&tk);
+    ptx::tma_prefetch_desc(&tv);
+    ptx::tma_prefetch_desc(&tdo);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const bool bad_align = (*abort_flag != 0);
+
+  if (bad_align) {
+  } else if (warp == 0) {
+    if (lane == 0) {
+      ptx::mbar_expect_tx(kv_full, 2 * Cfg::kTileBytes);
+#pragma unroll
+      for (int c = 0; c < HD / 64; ++c) {
+        ptx::tma_load_2d(smem + Cfg::kK + c * kChunkBytes, &tk, kv_full, hk * HD + c * 64, b * p.T + jb * kBlk);
+        ptx::tma_load_2d(smem + Cfg::kV + c * kChunkBytes, &tv, kv_full, hk * HD + c * 64, b * p.T + jb * kBlk);
+      }
+      for (int it = 0; it < niter; ++it) {
+        const int g = it / nq, i = jb + (it - g * nq);
+        const int h = hk * G + g;
+        const int st = it % S;
+        if (!ptx::mbar_wait(&qdo_empty[st], ((it / S) & 1) ^ 1u, abort_flag)) break;
+        ptx::mbar_expect_tx(&qdo_full[st], 2 * Cfg::kTileBytes);
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c) {
+          ptx::tma_load_2d(smem + Cfg::kQ + st * Cfg::kTileBytes + c * kChunkBytes, &tq, &qdo_full[st],
+                           h * HD + c * 64, b * p.T + i * kBlk);
+          ptx::tma_load_2d(smem + Cfg::kDO + st * Cfg::kTileBytes + c * kChunkBytes, &tdo, &qdo_full[st],
+                           h * HD + c * 64, b * p.T + i * kBlk);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = ptx::make_idesc_bf16(128, 128, 0, 0);   // S, dP : K-major x K-major
+      const uint32_t idesc_t = ptx::make_idesc_bf16(128, HD, 1, 1);    // dV, dK: MN-major x MN-major
+      const uint32_t idesc_q = ptx::make_idesc_bf16(128, HD, 0, 1);    // dQ    : K-major x MN-major
+      const uint32_t k_base = ptx::smem_u32(smem + Cfg::kK), v_base = ptx::smem_u32(smem + Cfg::kV);
+      const uint32_t p_base = ptx::smem_u32(smem + Cfg::kP), ds_base = ptx::smem_u32(smem + Cfg::kDS);
+      bool ok = ptx::mbar_wait(kv_full, 0, abort_flag);
+      for (int it = 0; it < niter && ok; ++it) {
+        const int st = it % S;
+        const uint32_t q_base = ptx::smem_u32(smem + Cfg::kQ + st * Cfg::kTileBytes);
+        const uint32_t do_base = ptx::smem_u32(smem + Cfg::kDO + st * Cfg::kTileBytes);
+        if (!ptx::mbar_wait(&qdo_full[st], (it / S) & 1, abort_flag)) break;
+        if (Cfg::kAliasDq && it > 0) {
+          if (!ptx::mbar_wait(dq_free, (it - 1) & 1, abort_flag)) break;
+        }
+        ptx::tc_fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t off = (k >> 2) * kChunkBytes + (k & 3) * 32;
+          ptx::mma_f16_ss(tmem_base + Cfg::kColS, ptx::make_smem_desc(q_base + off, 16, 1024),
+                          ptx::make_smem_desc(k_base + off, 16, 1024), idesc_s, k > 0);
+        }
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t off = (k >> 2) * kChunkBytes + (k & 3) * 32;
+          ptx::mma_f16_ss(tmem_base + Cfg::kColDP, ptx::make_smem_desc(do_base + off, 16, 1024),
+                          ptx::make_smem_desc(v_base + off, 16, 1024), idesc_s, k > 0);
+        }
+        ptx::tc_commit(sdp_full);
+        if (!ptx::mbar_wait(pds_full, it & 1, abort_flag)) break;
+        ptx::tc_fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < kBlk / 16; ++k) {  // reduction over the 128 query rows
+          ptx::mma_f16_ss(tmem_base + Cfg::kColDV, ptx::make_smem_desc(p_base + k * 2048, kChunkBytes, 1024),
+                          ptx::make_smem_desc(do_base + k * 2048, kChunkBytes, 1024), idesc_t, (it > 0 || k > 0));
+        }
+#pragma unroll
+        for (int k = 0; k < kBlk / 16; ++k) {
+          ptx::mma_f16_ss(tmem_base + Cfg::kColDK, ptx::make_smem_desc(ds_base + k * 2048, kChunkBytes, 1024),
+                          ptx::make_smem_desc(q_base + k * 2048, kChunkBytes, 1024), idesc_t, (it > 0 || k > 0));
+        }
+#pragma unroll
+        for (int k = 0; k < kBlk / 16; ++k) {  // reduction over the 128 keys
+          const uint32_t a_off = (k >> 2) * kChunkBytes + (k & 3) * 32;
+          ptx::mma_f16_ss(tmem_base + Cfg::kColDQ, ptx::make_smem_desc(ds_base + a_off, 16, 1024),
+                          ptx::make_smem_desc(k_base + k * 2048, kChunkBytes, 1024), idesc_q, k > 0);
+        }
+        ptx::tc_commit(dq_full);
+        ptx::tc_commit(&qdo_empty[st]);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_sel = static_cast<uint32_t>(quad * 32) << 16;
+    const float sc = p.scale * kLog2e;
+    uint8_t* p_smem = smem + Cfg::kP;
+    uint8_t* ds_smem = smem + Cfg::kDS;
+    bool ok = true;
+    for (int it = 0; it < niter; ++it) {
+      const int g = it / nq, i = jb + (it - g * nq);
+      const int h = hk * G + g;
+      const int q_idx = i * kBlk + row;
+      const bool q_valid = q_idx < p.T;
+      const long long stat = (static_cast<long long>(b) * p.Hq + h) * p.T + q_idx;
+      const float lse2 = q_valid ? p.lse[stat] * kLog2e : 0.f;
+      const float dlt = q_valid ? p.delta[stat] : 0.f;
+      if (!ptx::mbar_wait(sdp_full, it & 1, abort_flag)) { ok = false; break; }
+      ptx::tc_fence_after_sync();
+      const bool diag = (i == jb);
+      const int kv0 = jb * kBlk;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t rs[32], rd[32];
+        ptx::tmem_ld32(tmem_base + Cfg::kColS + lane_sel + c * 32, rs);
+        ptx::tmem_ld32(tmem_base + Cfg::kColDP + lane_sel + c * 32, rd);
+        ptx::tmem_ld_wait();
+        uint32_t pk[16], dk_[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float pv[2], dv_[2];
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            const bool keep = q_valid && !(diag && (kv0 + c * 32 + e + t > q_idx));
+            const float pr = keep ? ex2(__uint_as_float(rs[e + t]) * sc - lse2) : 0.f;
+            pv[t] = pr;
+            dv_[t] = pr * (__uint_as_float(rd[e + t]) - dlt) * p.scale;
+          }
+          pk[e >> 1] = pack_bf16x2(pv[0], pv[1]);
+          dk_[e >> 1] = pack_bf16x2(dv_[0], dv_[1]);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const uint32_t off = swz_off(row, c * 4 + u);
+          *reinterpret_cast<uint4*>(p_smem + off) = make_uint4(pk[u * 4], pk[u * 4 + 1], pk[u * 4 + 2], pk[u * 4 + 3]);
+          *reinterpret_cast<uint4*>(ds_smem + off) = make_uint4(dk_[u * 4], dk_[u * 4 + 1], dk_[u * 4 + 2], dk_[u * 4 + 3]);
+        }
+      }
+      ptx::fence_proxy_async_smem();
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(pds_full);
+      if (!ptx::mbar_wait(dq_full, it & 1, abort_flag)) { ok = false; break; }
+      ptx::tc_fence_after_sync();
+      float* dq_row = p.dq_accum + ((static_cast<long long>(b) * p.T + q_idx) * p.Hq + h) * HD;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t r[32];
+        ptx::tmem_ld32(tmem_base + Cfg::kColDQ + lane_sel + c * 32, r);
+        ptx::tmem_ld_wait();
+        if (q_valid) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 4)
+            red_add_v4(dq_row + c * 32 + e, __uint_as_float(r[e]), __uint_as_float(r[e + 1]), __uint_as_float(r[e + 2]),
+                       __uint_as_float(r[e + 3]));
+        }
+      }
+      if (Cfg::kAliasDq) {
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(dq_free);
+      }
+    }
+    // The last dq_full arrival also covers every dV/dK accumulation issued before it.
+    const int kv_idx = jb * kBlk + row;
+    if (ok && niter > 0) {
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        bf16* base = which == 0 ? p.dv : p.dk;
+        const long long stride = which == 0 ? p.dv_stride_t : p.dk_stride_t;
+        const uint32_t col = which == 0 ? Cfg::kColDV : Cfg::kColDK;
+        bf16* dst = base + (static_cast<long long>(b) * p.T + kv_idx) * stride + hk * HD;
+#pragma unroll 1
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t r[32];
+          ptx::tmem_ld32(tmem_base + col + lane_sel + c * 32, r);
+          ptx::tmem_ld_wait();
+          if (kv_idx < p.T) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 8) {
+              uint4 u;
+              u.x = pack_bf16x2(__uint_as_float(r[e]), __uint_as_float(r[e + 1]));
+              u.y = pack_bf16x2(__uint_as_float(r[e + 2]), __uint_as_float(r[e + 3]));
+              u.z = pack_bf16x2(__uint_as_float(r[e + 4]), __uint_as_float(r[e + 5]));
+              u.w = pack_bf16x2(__uint_as_float(r[e + 6]), __uint_as_float(r[e + 7]));
+              *reinterpret_cast<uint4*>(dst + c * 32 + e) = u;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, kStatusMbarTimeout);
+}
+
+// delta[b,h,t] = sum_d dO[b,t,h,d] * O[b,t,h,d]; one thread per (b,t,h) row.
+__global__ void attn_delta_kernel(const bf16* __restrict__ d_o, const bf16* __restrict__ o, float* __restrict__ delta,
+                                  int B, int T, int H, int hd, long long do_stride_t, long long o_stride_t) {
+  const long long n = static_cast<long long>(B) * T * H;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const int h = static_cast<int>(i % H);
+    const long long bt = i / H;
+    const bf16* a = d_o + bt * do_stride_t + h * hd;
+    const bf16* c = o + bt * o_stride_t + h * hd;
+    float s = 0.f;
+    for (int d = 0; d < hd; d += 8) {
+      uint4 ua = *reinterpret_cast<const uint4*>(a + d), uc = *reinterpret_cast<const uint4*>(c + d);
+      float2 a0 = unpack_bf16x2(ua.x), a1 = unpack_bf16x2(ua.y), a2 = unpack_bf16x2(ua.z), a3 = unpack_bf16x2(ua.w);
+      float2 c0 = unpack_bf16x2(uc.x), c1 = unpack_bf16x2(uc.y), c2 = unpack_bf16x2(uc.z), c3 = unpack_bf16x2(uc.w);
+      s += a0.x * c0.x + a0.y * c0.y + a1.x * c1.x + a1.y * c1.y + a2.x * c2.x + a2.y * c2.y + a3.x * c3.x + a3.y * c3.y;
+    }
+    const long long b = bt / T, t = bt - b * T;
+    delta[(b * H + h) * T + t] = s;
+  }
+}
+
+// dq (bf16, token stride dq_stride_t) = dq_accum (fp32 [B*T, H*hd])
+__global__ void attn_dq_convert_kernel(const float* __restrict__ acc, bf16* __restrict__ dq, long long BT, int width,
+                                       long long dq_stride_t) {
+  const int wv = width / 8;
+  const long long n = BT * wv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long bt = i / wv;
+    const int c = static_cast<int>(i - bt * wv) * 8;
+    const float4 f0 = *reinterpret_cast<const float4*>(acc + bt * width + c);
+    const float4 f1 = *reinterpret_cast<const float4*>(acc + bt * width + c + 4);
+    uint4 u;
+    u.x = pack_bf16x2(f0.x, f0.y); u.y = pack_bf16x2(f0.z, f0.w);
+    u.z = pack_bf16x2(f1.x, f1.y); u.w = pack_bf16x2(f1.z, f1.w);
+    *reinterpret_cast<uint4*>(dq + bt * dq_stride_t + c) = u;
+  }
+}
+
+static bool attn_check(const TitbAttnDesc* d) {
+  if (d->hd != 64 && d->hd != 128) return false;
+  if (d->Hq % d->Hkv) return false;
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (!al(d->q) || !al(d->k) || !al(d->v) || !al(d->o)) return false;
+  if ((d->q_stride_t & 7) || (d->k_stride_t & 7) || (d->v_stride_t & 7) || (d->o_stride_t & 7)) return false;
+  return true;
+}
+
+template <int HD>
+static int attn_fwd_launch(const TitbAttnDesc* d, cudaStream_t st) {
+  using Cfg = FwdCfg<HD>;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (!attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set[dev] = true;
+  }
+  const uint64_t rows = static_cast<uint64_t>(d->B) * d->T;
+  CUtensorMap tq, tk, tv;
+  if (!make_tmap_bf16_2d(&tq, d->q, static_cast<uint64_t>(d->Hq) * HD, rows, d->q_stride_t, 64, kBlk) ||
+      !make_tmap_bf16_2d(&tk, d->k, static_cast<uint64_t>(d->Hkv) * HD, rows, d->k_stride_t, 64, kBlk) ||
+      !make_tmap_bf16_2d(&tv, d->v, static_cast<uint64_t>(d->Hkv) * HD, rows, d->v_stride_t, 64, kBlk))
+    return TITB_ERR_TENSOR_MAP;
+  AttnArgs a{};
+  a.B = d->B; a.T = d->T; a.Hq = d->Hq; a.Hkv = d->Hkv; a.hd = HD;
+  a.scale = d->scale;
+  a.o = static_cast<bf16*>(d->o); a.lse = d->lse; a.o_stride_t = d->o_stride_t;
+  a.status = titb_status_ptr();
+  dim3 grid((d->T + kBlk - 1) / kBlk, d->Hq, d->B);
+  attn_fwd_kernel<HD><<<grid, kAttnThreads, Cfg::kSmem, st>>>(tq, tk, tv, a);
+  return static_cast<int>(cudaGetLastError());
+}
+
+template <int HD>
+static int attn_bwd_launch(const TitbAttnDesc* d, cudaStream_t st) {
+  using Cfg = BwdCfg<HD>;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (!attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set[dev] = true;
+  }
+  const uint64_t rows = static_cast<uint64_t>(d->B) * d->T;
+  CUtensorMap tq, tk, tv, tdo;
+  if (!make_tmap_bf16_2d(&tq, d->q, static_cast<uint64_t>(d->Hq) * HD, rows, d->q_stride_t, 64, kBlk) ||
+      !make_tmap_bf16_2d(&tk, d->k, static_cast<uint64_t>(d->Hkv) * HD, rows, d->k_stride_t, 64, kBlk) ||
+      !make_tmap_bf16_2d(&tv, d->v, static_cast<uint64_t>(d->Hkv) * HD, rows, d->v_stride_t, 64, kBlk) ||
+      !make_tmap_bf16_2d(&tdo, d->d_o, static_cast<uint64_t>(d->Hq) * HD, rows, d->do_stride_t, 64, kBlk))
+    return TITB_ERR_TENSOR_MAP;
+  const long long nrows = static_cast<long long>(d->B) * d->T * d->Hq;
+  int blocks = static_cast<int>((nrows + 255) / 256);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  attn_delta_kernel<<<blocks, 256, 0, st>>>(static_cast<const bf16*>(d->d_o), static_cast<const bf16*>(d->o), d->delta,
+                                            d->B, d->T, d->Hq, HD, d->do_stride_t, d->o_stride_t);
+  cudaError_t e = cudaMemsetAsync(d->dq_accum, 0, sizeof(float) * nrows * HD, st);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  AttnArgs a{};
+  a.B = d->B; a.T = d->T; a.Hq = d->Hq; a.Hkv = d->Hkv; a.hd = HD;
+  a.scale = d->scale;
+  a.lse = d->lse; a.delta = d->delta; a.dq_accum = d->dq_accum;
+  a.dk = static_cast<bf16*>(d->dk); a.dv = static_cast<bf16*>(d->dv);
+  a.dk_stride_t = d->dk_stride_t; a.dv_stride_t = d->dv_stride_t;
+  a.status = titb_status_ptr();
+  dim3 grid((d->T + kBlk - 1) / kBlk, d->Hkv, d->B);
+  attn_bwd_kernel<HD><<<grid, kAttnThreads, Cfg::kSmem, st>>>(tq, tk, tv, tdo, a);
+  const long long bt = static_cast<long long>(d->B) * d->T;
+  const int width = d->Hq * HD;
+  int cb = static_cast<int>((bt * (width / 8) + 255) / 256);
+  if (cb > 148 * 8) cb = 148 * 8;
+  attn_dq_convert_kernel<<<cb, 256, 0, st>>>(d->dq_accum, static_cast<bf16*>(d->dq), bt, width, d->dq_stride_t);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace titb
+
+using namespace titb;
+
+TITB_API int titb_attn_fwd(const TitbAttnDesc* d, cudaStream_t stream) {
+  (void)cudaGetLastError();
+  if (d->B <= 0 || d->T <= 0) return 0;
+  if (!attn_check(d)) return TITB_ERR_SHAPE;
+  return d->hd == 64 ? attn_fwd_launch<64>(d, stream) : attn_fwd_launch<128>(d, stream);
+}
+
+TITB_API int titb_attn_bwd(const TitbAttnDesc* d, cudaStream_t stream) {
+  (void)cudaGetLastError();
+  if (d->B <= 0 || d->T <= 0) return 0;
+  if (!attn_check(d)) return TITB_ERR_SHAPE;
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (!al(d->d_o) || !al(d->dq) || !al(d->dk) || !al(d->dv) || (d->do_stride_t & 7) || (d->dq_stride_t & 7) ||
+      (d->dk_stride_t & 7) || (d->dv_stride_t & 7))
+    return TITB_ERR_ALIGNMENT;
+  return d->hd == 64 ? attn_bwd_launch<64>(d, stream) : attn_bwd_launch<128>(d, stream);
+}

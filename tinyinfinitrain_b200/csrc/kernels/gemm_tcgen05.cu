@@ -1,0 +1,638 @@
+// bf16 GEMM on the 5th-generation tensor cores: TMA -> shared-memory ring ->
+// tcgen05.mma (accumulators in tensor memory) -> tcgen05.ld -> fused epilogue.
+//
+// Replaces the reference's cuBLAS SGEMM call sites (infini_train/src/kernels/cuda/linear.cu:58-128
+// LinearForward, :148-232 LinearBackward, :26-47 Matmul) with one persistent,
+// warp-specialised kernel:
+//   warp 0 (one lane)  TMA producer, fills a STAGES-deep ring of A/B tiles
+//   warp 1 (one lane)  issues tcgen05.mma, 128 x BN x 16 per instruction
+//   warps 2..5         epilogue: read the fp32 accumulator from TMEM, apply
+//                      bias / GELU / dGELU / residual, store bf16 or fp32
+// The accumulator is double buffered in TMEM (2 x BN columns), so the epilogue
+// of tile i overlaps the main loop of tile i+1.  Operands may be K-major or
+// MN-major, which covers forward, dgrad and wgrad without transposing in HBM.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdio.h>
+
+#include "api.h"
+#include "ptx_sm100.cuh"
+
+namespace titb {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+constexpr int kABytes = kBM * kBK * 2;
+constexpr int kGemmThreads = 192;
+
+struct GemmArgs {
+  int M, N, K;
+  int a_mn, b_mn;
+  void* out;
+  long long ldo;
+  int out_fp32, accumulate, epi;
+  const bf16* bias;
+  const bf16* aux_in;
+  long long ld_aux_in;
+  bf16* aux_out;
+  long long ld_aux_out;
+  int splits;       // split-K factor; partial tiles go to `out` = workspace [splits, M, N] fp32
+  int kb_per_split;
+  int vec_ok;       // all row strides / base pointers allow 16-byte accesses
+  const float* alpha;  // optional device scalar multiplied into the accumulator
+  uint32_t a_lbo, a_sbo, a_kstep, b_lbo, b_sbo, b_kstep;
+  int* status;
+};
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kTmemCols = 2 * BN;
+  static constexpr int kRing = kStages * (kABytes + kBBytes);
+  static constexpr int kSmem = kRing + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float gelu_fast(float x) {
+  const float k = 0.7978845608028654f;
+  return 0.5f * x * (1.f + tanh_fast(k * (x + 0.044715f * x * x * x)));
+}
+__device__ __forceinline__ float gelu_grad_fast(float x) {
+  const float k = 0.7978845608028654f;
+  float x2 = x * x;
+  float t = tanh_fast(k * (x + 0.044715f * x * x2));
+  return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * k * (1.f + 0.134145f * x2);
+}
+
+// Epilogue for one thread: 32 consecutive columns [col0, col0+32) of one output row.
+__device__ __forceinline__ void epilogue_row32(const GemmArgs& p, float (&v)[32], long long row, int col0,
+                                                int split) {
+  const int ncols = min(32, p.N - col0);
+  const bool full = (ncols == 32) && p.vec_ok;
+
+  if (p.alpha != nullptr && p.splits == 1) {
+    const float al = *p.alpha;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] *= al;
+  }
+  if (p.splits > 1) {  // raw fp32 partials, reduced by splitk_reduce_kernel
+    float* dst = reinterpret_cast<float*>(p.out) + (static_cast<long long>(split) * p.M + row) * p.N + col0;
+    if (ncols == 32 && (p.N & 3) == 0) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    } else {
+      for (int j = 0; j < ncols; ++j) dst[j] = v[j];
+    }
+    return;
+  }
+
+  if (p.epi == TITB_EPI_BIAS || p.epi == TITB_EPI_BIAS_GELU || p.epi == TITB_EPI_BIAS_RESIDUAL) {
+    if (p.bias != nullptr) {
+      if (full) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          uint4 u = *reinterpret_cast<const uint4*>(p.bias + col0 + j);
+          float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
+          v[j] += f0.x; v[j + 1] += f0.y; v[j + 2] += f1.x; v[j + 3] += f1.y;
+          v[j + 4] += f2.x; v[j + 5] += f2.y; v[j + 6] += f3.x; v[j + 7] += f3.y;
+        }
+      } else {
+        for (int j = 0; j < ncols; ++j) v[j] += __bfloat162float(p.bias[col0 + j]);
+      }
+    }
+  }
+  if (p.epi == TITB_EPI_BIAS_GELU) {
+    if (p.aux_out != nullptr) {
+      bf16* ao = p.aux_out + row * p.ld_aux_out + col0;
+      if (full) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          uint4 u;
+          u.x = pack_bf16x2(v[j], v[j + 1]); u.y = pack_bf16x2(v[j + 2], v[j + 3]);
+          u.z = pack_bf16x2(v[j + 4], v[j + 5]); u.w = pack_bf16x2(v[j + 6], v[j + 7]);
+          *reinterpret_cast<uint4*>(ao + j) = u;
+        }
+      } else {
+        for (int j = 0; j < ncols; ++j) ao[j] = __float2bfloat16_rn(v[j]);
+      }
+    }
+    // The activation is evaluated on the bf16-rounded pre-activation so that the
+    // backward pass, which only has the stored bf16 copy, differentiates the same point.
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = gelu_fast(__bfloat162float(__float2bfloat16_rn(v[j])));
+  } else if (p.epi == TITB_EPI_DGELU || p.epi == TITB_EPI_BIAS_RESIDUAL) {
+    if (p.aux_in != nullptr) {
+      const bf16* ai = p.aux_in + row * p.ld_aux_in + col0;
+      float a[32];
+      if (full) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          uint4 u = *reinterpret_cast<const uint4*>(ai + j);
+          float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
+          a[j] = f0.x; a[j + 1] = f0.y; a[j + 2] = f1.x; a[j + 3] = f1.y;
+          a[j + 4] = f2.x; a[j + 5] = f2.y; a[j + 6] = f3.x; a[j + 7] = f3.y;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) a[j] = (j < ncols) ? __bfloat162float(ai[j]) : 0.f;
+      }
+      if (p.epi == TITB_EPI_DGELU) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] *= gelu_grad_fast(a[j]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] += a[j];
+      }
+    }
+  }
+
+  if (p.out_fp32) {
+    float* dst = reinterpret_cast<float*>(p.out) + row * p.ldo + col0;
+    if (full) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        if (p.accumulate) {
+          float4 c = *reinterpret_cast<const float4*>(dst + j);
+          o.x += c.x; o.y += c.y; o.z += c.z; o.w += c.w;
+        }
+        *reinterpret_cast<float4*>(dst + j) = o;
+      }
+    } else {
+      for (int j = 0; j < ncols; ++j) dst[j] = p.accumulate ? dst[j] + v[j] : v[j];
+    }
+  } else {
+    bf16* dst = reinterpret_cast<bf16*>(p.out) + row * p.ldo + col0;
+    if (full) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        if (p.accumulate) {
+          uint4 c = *reinterpret_cast<const uint4*>(dst + j);
+          float2 f0 = unpack_bf16x2(c.x), f1 = unpack_bf16x2(c.y), f2 = unpack_bf16x2(c.z), f3 = unpack_bf16x2(c.w);
+          v[j] += f0.x; v[j + 1] += f0.y; v[j + 2] += f1.x; v[j + 3] += f1.y;
+          v[j + 4] += f2.x; v[j + 5] += f2.y; v[j + 6] += f3.x; v[j + 7] += f3.y;
+        }
+        uint4 u;
+        u.x = pack_bf16x2(v[j], v[j + 1]); u.y = pack_bf16x2(v[j + 2], v[j + 3]);
+        u.z = pack_bf16x2(v[j + 4], v[j + 5]); u.w = pack_bf16x2(v[j + 6], v[j + 7]);
+        *reinterpret_cast<uint4*>(dst + j) = u;
+      }
+    } else {
+      for (int j = 0; j < ncols; ++j) {
+        float o = v[j];
+        if (p.accumulate) o += __bfloat162float(dst[j]);
+        dst[j] = __float2bfloat16_rn(o);
+      }
+    }
+  }
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                         const GemmArgs p) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int kStages = Cfg::kStages;
+  constexpr int kBBytes = Cfg::kBBytes;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sa = smem;
+  uint8_t* sb = smem + kStages * kABytes;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + Cfg::kRing);
+  uint64_t* empty = full + kStages;
+  uint64_t* acc_full = empty + kStages;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(&full[s], 1);
+      ptx::mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(&acc_full[b], 1);
+      ptx::mbar_init(&acc_empty[b], 4);
+    }
+    *abort_flag = 0;
+    ptx::mbar_fence_init();
+    ptx::tma_prefetch_desc(&tma_a);
+    ptx::tma_prefetch_desc(&tma_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_m = (p.M + kBM - 1) / kBM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int tiles_mn = tiles_m * tiles_n;
+  const int num_tiles = tiles_mn * p.splits;
+  const int num_kb_total = (p.K + kBK - 1) / kBK;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int split = tile / tiles_mn;
+        const int mn = tile - split * tiles_mn;
+        const int m0 = (mn % tiles_m) * kBM;
+        const int n0 = (mn / tiles_m) * BN;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(num_kb_total, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!ptx::mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+          ptx::mbar_expect_tx(&full[stage], kABytes + kBBytes);
+          uint8_t* a_dst = sa + stage * kABytes;
+          uint8_t* b_dst = sb + stage * kBBytes;
+          if (!p.a_mn) {
+            ptx::tma_load_2d(a_dst, &tma_a, &full[stage], kb * kBK, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < kBM / 64; ++j)
+              ptx::tma_load_2d(a_dst + j * (64 * kBK * 2), &tma_a, &full[stage], m0 + j * 64, kb * kBK);
+          }
+          if (!p.b_mn) {
+            ptx::tma_load_2d(b_dst, &tma_b, &full[stage], kb * kBK, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              ptx::tma_load_2d(b_dst + j * (64 * kBK * 2), &tma_b, &full[stage], n0 + j * 64, kb * kBK);
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // Give copies already issued a bounded chance to land before the CTA exits.
+        for (int s = 0; s < kStages; ++s) {
+          const long long t0 = clock64();
+          while (!ptx::mbar_try_wait(&full[s], 0) && !ptx::mbar_try_wait(&full[s], 1) &&
+                 clock64() - t0 < 2000000LL) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = ptx::make_idesc_bf16(kBM, BN, p.a_mn, p.b_mn);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+        const int split = tile / tiles_mn;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(num_kb_total, kb0 + p.kb_per_split);
+        const int buf = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!ptx::mbar_wait(&acc_empty[buf], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+        ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!ptx::mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
+          ptx::tc_fence_after_sync();
+          const uint32_t a_base = ptx::smem_u32(sa + stage * kABytes);
+          const uint32_t b_base = ptx::smem_u32(sb + stage * kBBytes);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            const uint64_t adesc = ptx::make_smem_desc(a_base + k * p.a_kstep, p.a_lbo, p.a_sbo);
+            const uint64_t bdesc = ptx::make_smem_desc(b_base + k * p.b_kstep, p.b_lbo, p.b_sbo);
+            ptx::mma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          ptx::tc_commit(&empty[stage]);  // frees the smem stage once these MMAs retire
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) ptx::tc_commit(&acc_full[buf]);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int quad = warp & 3;  // TMEM lane quarter this warp may read
+    int it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+      const int split = tile / tiles_mn;
+      const int mn = tile - split * tiles_mn;
+      const int m0 = (mn % tiles_m) * kBM;
+      const int n0 = (mn / tiles_m) * BN;
+      const int buf = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!ptx::mbar_wait(&acc_full[buf], acc_phase, abort_flag)) break;
+      ptx::tc_fence_after_sync();
+      const long long row = m0 + quad * 32 + lane;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        ptx::tmem_ld32(t_row + c * 32, r);
+        ptx::tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (row < p.M && col0 < p.N) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          epilogue_row32(p, v, row, col0, split);
+        }
+      }
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
+    }
+  }
+
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, kStatusMbarTimeout);
+}
+
+// out (+)= sum_s ws[s] ; ws is fp32 [splits, M*N] with N contiguous, out has row stride ldo.
+template <typename OutT>
+__global__ void splitk_reduce_kernel(const float* __restrict__ ws, OutT* __restrict__ out, long long M, int N,
+                                     long long ldo, int splits, int accumulate, const float* __restrict__ alpha) {
+  const long long total = M * N;
+  const float al = alpha ? *alpha : 1.f;
+  for (long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 4; i < total;
+       i += (long long)gridDim.x * blockDim.x * 4) {
+    // N % 4 == 0 is enforced by the host, so a group of 4 never straddles a row.
+    float4 acc = *reinterpret_cast<const float4*>(ws + i);
+    for (int s = 1; s < splits; ++s) {
+      float4 t = *reinterpret_cast<const float4*>(ws + s * total + i);
+      acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+    }
+    acc.x *= al; acc.y *= al; acc.z *= al; acc.w *= al;
+    const long long r = i / N;
+    const int c = static_cast<int>(i - r * N);
+    OutT* o = out + r * ldo + c;
+    if (accumulate) {
+      acc.x += to_f32(o[0]); acc.y += to_f32(o[1]); acc.z += to_f32(o[2]); acc.w += to_f32(o[3]);
+    }
+    o[0] = from_f32<OutT>(acc.x); o[1] = from_f32<OutT>(acc.y);
+    o[2] = from_f32<OutT>(acc.z); o[3] = from_f32<OutT>(acc.w);
+  }
+}
+
+// ------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      f = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(f);
+  }();
+  return fn;
+}
+
+// bf16 matrix stored [outer, inner] with `ld` elements between rows; box = box_inner x box_outer.
+bool make_tmap_bf16_2d(CUtensorMap* m, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
+                       uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+int device_sm_count() {
+  static int sms[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (sms[dev] == 0) cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
+  return sms[dev] > 0 ? sms[dev] : 148;
+}
+
+static unsigned g_dbg_lbo = 0, g_dbg_sbo = 0, g_dbg_kstep = 0;
+
+static int pick_tile_n(int M, int N, int splits) {
+  const int sms = device_sm_count();
+  const long long tm = (M + kBM - 1) / kBM;
+  long long best_cost = -1;
+  int best = 256;
+  for (int bn : {256, 128}) {
+    long long tiles = tm * ((N + bn - 1) / bn) * splits;
+    long long waves = (tiles + sms - 1) / sms;
+    long long cost = waves * bn;
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
+  }
+  return best;
+}
+
+}  // namespace titb
+
+using namespace titb;
+
+static int* g_status_dev[64] = {nullptr};
+
+TITB_API int* titb_status_ptr(void) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (!g_status_dev[dev]) {
+    if (cudaMalloc(&g_status_dev[dev], sizeof(int)) != cudaSuccess) return nullptr;
+    cudaMemset(g_status_dev[dev], 0, sizeof(int));
+  }
+  return g_status_dev[dev];
+}
+
+TITB_API int titb_status_read(int clear, cudaStream_t stream) {
+  int* p = titb_status_ptr();
+  if (!p) return -1;
+  int h = 0;
+  if (cudaMemcpyAsync(&h, p, sizeof(int), cudaMemcpyDeviceToHost, stream) != cudaSuccess) return -1;
+  if (cudaStreamSynchronize(stream) != cudaSuccess) return -1;
+  if (clear && h != 0) cudaMemsetAsync(p, 0, sizeof(int), stream);
+  return h;
+}
+
+TITB_API void titb_gemm_debug_override(unsigned lbo, unsigned sbo, unsigned kstep) {
+  g_dbg_lbo = lbo; g_dbg_sbo = sbo; g_dbg_kstep = kstep;
+}
+
+TITB_API int titb_gemm_pick_splits(int M, int N, int K) {
+  // Split the reduction only when the output has too few tiles to fill the GPU and the
+  // reduction is long enough that each split still runs a deep pipeline.
+  const int sms = device_sm_count();
+  const long long tm = (M + kBM - 1) / kBM;
+  const long long tiles = tm * ((N + 127) / 128);
+  const int kb = (K + kBK - 1) / kBK;
+  if (tiles * 2 > sms || kb < 32) return 1;
+  int s = static_cast<int>(sms / tiles);
+  while (s > 1 && kb / s < 8) --s;
+  return s < 1 ? 1 : (s > 16 ? 16 : s);
+}
+
+template <int BN>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (!attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::kSmem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set[dev] = true;
+  }
+  const int tiles = ((args.M + kBM - 1) / kBM) * ((args.N + BN - 1) / BN) * args.splits;
+  const int grid = tiles < device_sm_count() ? tiles : device_sm_count();
+  gemm_bf16_tcgen05_kernel<BN><<<grid, kGemmThreads, Cfg::kSmem, stream>>>(ta, tb, args);
+  return static_cast<int>(cudaGetLastError());
+}
+
+TITB_API int titb_gemm_bf16(const TitbGemmDesc* d, cudaStream_t stream) {
+  if (d->M <= 0 || d->N <= 0 || d->K <= 0) return 0;
+  (void)cudaGetLastError();  // do not report an error left behind by an earlier, unrelated call
+  // TMA needs 16-byte aligned bases and row strides.
+  if ((reinterpret_cast<uintptr_t>(d->a) & 15) || (reinterpret_cast<uintptr_t>(d->b) & 15) || (d->lda & 7) ||
+      (d->ldb & 7))
+    return TITB_ERR_ALIGNMENT;
+  int splits = d->splits < 1 ? 1 : d->splits;
+  const int num_kb = (d->K + kBK - 1) / kBK;
+  if (splits > num_kb) splits = num_kb;
+  if (splits > 1 && (d->workspace == nullptr || (d->N & 3))) splits = 1;
+  const int bn = d->tile_n ? d->tile_n : pick_tile_n(d->M, d->N, splits);
+
+  CUtensorMap ta, tb;
+  bool ok;
+  if (!d->a_mn_major) ok = make_tmap_bf16_2d(&ta, d->a, d->K, d->M, d->lda, kBK, kBM);
+  else ok = make_tmap_bf16_2d(&ta, d->a, d->M, d->K, d->lda, 64, kBK);
+  if (!d->b_mn_major) ok = ok && make_tmap_bf16_2d(&tb, d->b, d->K, d->N, d->ldb, kBK, bn);
+  else ok = ok && make_tmap_bf16_2d(&tb, d->b, d->N, d->K, d->ldb, 64, kBK);
+  if (!ok) return TITB_ERR_TENSOR_MAP;
+
+  GemmArgs a;
+  a.M = d->M; a.N = d->N; a.K = d->K;
+  a.a_mn = d->a_mn_major ? 1 : 0;
+  a.b_mn = d->b_mn_major ? 1 : 0;
+  a.out = splits > 1 ? d->workspace : d->out;
+  a.ldo = d->ldo;
+  a.out_fp32 = d->out_fp32; a.accumulate = d->accumulate; a.epi = d->epilogue;
+  a.bias = static_cast<const bf16*>(d->bias);
+  a.aux_in = static_cast<const bf16*>(d->aux_in); a.ld_aux_in = d->ld_aux_in;
+  a.aux_out = static_cast<bf16*>(d->aux_out); a.ld_aux_out = d->ld_aux_out;
+  a.kb_per_split = (num_kb + splits - 1) / splits;
+  splits = (num_kb + a.kb_per_split - 1) / a.kb_per_split;  // no empty trailing split
+  a.splits = splits;
+  const int out_vec = d->out_fp32 ? 3 : 7;
+  a.vec_ok = !((d->ldo & out_vec) || (reinterpret_cast<uintptr_t>(d->out) & 15) ||
+               (d->bias && (reinterpret_cast<uintptr_t>(d->bias) & 15)) ||
+               (d->aux_in && ((reinterpret_cast<uintptr_t>(d->aux_in) & 15) || (d->ld_aux_in & 7))) ||
+               (d->aux_out && ((reinterpret_cast<uintptr_t>(d->aux_out) & 15) || (d->ld_aux_out & 7))));
+  // K-major: 32 bytes per 16-wide k step inside the 128-byte row, 8-row groups 1024 bytes apart.
+  // MN-major: 16 k-rows of 128 bytes per step, 64-wide chunks one TMA box (64 x kBK) apart.
+  const uint32_t mn_lbo = g_dbg_lbo ? g_dbg_lbo : 64 * kBK * 2;
+  const uint32_t mn_sbo = g_dbg_sbo ? g_dbg_sbo : 1024;
+  const uint32_t mn_kstep = g_dbg_kstep ? g_dbg_kstep : 16 * 128;
+  a.a_lbo = a.a_mn ? mn_lbo : 16; a.a_sbo = a.a_mn ? mn_sbo : 1024; a.a_kstep = a.a_mn ? mn_kstep : 32;
+  a.b_lbo = a.b_mn ? mn_lbo : 16; a.b_sbo = a.b_mn ? mn_sbo : 1024; a.b_kstep = a.b_mn ? mn_kstep : 32;
+  a.alpha = static_cast<const float*>(d->alpha);
+  a.status = titb_status_ptr();
+  if (!a.status) return static_cast<int>(cudaErrorMemoryAllocation);
+
+  int rc = (bn == 256) ? launch_gemm<256>(ta, tb, a, stream) : launch_gemm<128>(ta, tb, a, stream);
+  if (rc != 0) return rc;
+  if (splits > 1) {
+    const long long total = static_cast<long long>(d->M) * d->N;
+    int blocks = static_cast<int>((total / 4 + 255) / 256);
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (d->out_fp32)
+      splitk_reduce_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<const float*>(d->workspace),
+                                                               static_cast<float*>(d->out), d->M, d->N, d->ldo,
+                                                               splits, d->accumulate, static_cast<const float*>(d->alpha));
+    else
+      splitk_reduce_kernel<bf16><<<blocks, 256, 0, stream>>>(static_cast<const float*>(d->workspace),
+                                                              static_cast<bf16*>(d->out), d->M, d->N, d->ldo, splits,
+                                                              d->accumulate, static_cast<const float*>(d->alpha));
+    rc = static_cast<int>(cudaGetLastError());
+  }
+  return rc;
+}
+
+// ------------------------------------------------------------- fp32 SIMT GEMM
+// Kept for fp32 tensors on the GPU (API parity with the reference's fp32-only
+// Matmul/Linear); not a hot path.  64x64 tile, 16-deep k slab, 4x4 per thread.
+namespace titb {
+__global__ void __launch_bounds__(256) sgemm_kernel(const float* __restrict__ A, const float* __restrict__ B,
+                                                    float* __restrict__ C, int M, int N, int K, int ta, int tb,
+                                                    int accumulate) {
+  __shared__ float As[16][64 + 1];
+  __shared__ float Bs[16][64 + 1];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < K; k0 += 16) {
+    for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+      int kk = i & 15, mm = i >> 4;
+      int gm = m0 + mm, gk = k0 + kk;
+      float va = 0.f, vb = 0.f;
+      if (gm < M && gk < K) va = ta ? A[(long long)gk * M + gm] : A[(long long)gm * K + gk];
+      int gn = n0 + mm;
+      if (gn < N && gk < K) vb = tb ? B[(long long)gn * K + gk] : B[(long long)gk * N + gn];
+      As[kk][mm] = va;
+      Bs[kk][mm] = vb;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = Bs[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+  for (int i = 0; i < 4; ++i)
+    for (int j = 0; j < 4; ++j) {
+      int gm = m0 + ty * 4 + i, gn = n0 + tx * 4 + j;
+      if (gm < M && gn < N) {
+        float* c = C + (long long)gm * N + gn;
+        *c = accumulate ? *c + acc[i][j] : acc[i][j];
+      }
+    }
+}
+}  // namespace titb
+
+TITB_API int titb_sgemm(const float* A, const float* B, float* C, int M, int N, int K, int trans_a, int trans_b,
+                        int accumulate, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  dim3 grid((N + 63) / 64, (M + 63) / 64);
+  titb::sgemm_kernel<<<grid, 256, 0, stream>>>(A, B, C, M, N, K, trans_a, trans_b, accumulate);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -1,0 +1,390 @@
+// LayerNorm and RMSNorm, forward and backward, for bf16 and fp32 rows.
+//
+// Counterpart of infini_train/src/kernels/cuda/layernorm.cu:9-55 (forward) and
+// :87-138 (backward).  Differences that matter on B200:
+//  * a row is read once with 128-bit loads and kept in registers (the reference
+//    makes two passes and uses E[x^2]-mean^2; here the variance is the two-pass
+//    form computed from registers),
+//  * one warp owns a row when it fits (no block barrier); wide rows use a CTA,
+//  * dweight/dbias are reduced deterministically in two stages through a scratch
+//    buffer instead of one atomicAdd per element per token (reference :135-136).
+#include "api.h"
+#include "common.cuh"
+
+namespace titb {
+
+// Sum two values over the G threads that share a row.
+template <int G>
+__device__ __forceinline__ void group_sum2(float& a, float& b, float* red) {
+  a = warp_sum(a);
+  b = warp_sum(b);
+  if constexpr (G > 32) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    constexpr int NW = G / 32;
+    __syncthreads();
+    if (lane == 0) { red[w] = a; red[NW + w] = b; }
+    __syncthreads();
+    float ra = (lane < NW) ? red[lane] : 0.f;
+    float rb = (lane < NW) ? red[NW + lane] : 0.f;
+    a = warp_sum(ra);
+    b = warp_sum(rb);
+  }
+}
+
+// G = 32: one warp per row, several rows per CTA.  G > 32: the CTA (G threads) owns a row.
+template <typename T, int MAXV, int G, bool RMS>
+__global__ void norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ b,
+                                T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                                long long rows, int C, float eps) {
+  constexpr int VN = VecN<T>::n;
+  __shared__ float red[2 * (G > 32 ? G / 32 : 1)];
+  const int tig = (G == 32) ? (threadIdx.x & 31) : threadIdx.x;  // thread in group
+  const long long row = (G == 32) ? (blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5)) : blockIdx.x;
+  if (G == 32 && row >= rows) return;
+  const int nvec = C / VN;
+  const T* xr = x + row * C;
+  Pack<T, VN> xv[MAXV];
+  float s = 0.f, s2 = 0.f;
+#pragma unroll
+  for (int k = 0; k < MAXV; ++k) {
+    const int i = tig + k * G;
+    if (i < nvec) {
+      xv[k] = ld128(xr + i * VN);
+#pragma unroll
+      for (int e = 0; e < VN; ++e) s += to_f32(xv[k].v[e]);
+    }
+  }
+  float dummy = 0.f;
+  group_sum2<G>(s, dummy, red);
+  const float mean = RMS ? 0.f : s / C;
+#pragma unroll
+  for (int k = 0; k < MAXV; ++k) {
+    const int i = tig + k * G;
+    if (i < nvec) {
+#pragma unroll
+      for (int e = 0; e < VN; ++e) {
+        float d = to_f32(xv[k].v[e]) - mean;
+        s2 += d * d;
+      }
+    }
+  }
+  dummy = 0.f;
+  group_sum2<G>(s2, dummy, red);
+  const float rstd = rsqrtf(s2 / C + eps);
+  if (tig == 0) {
+    if (!RMS && mean_out) mean_out[row] = mean;
+    if (rstd_out) rstd_out[row] = rstd;
+  }
+  T* yr = y + row * C;
+#pragma unroll
+  for (int k = 0; k < MAXV; ++k) {
+    const int i = tig + k * G;
+    if (i < nvec) {
+      Pack<T, VN> wv = ld128(w + i * VN), ov;
+      Pack<T, VN> bv;
+      if (!RMS) bv = ld128(b + i * VN);
+#pragma unroll
+      for (int e = 0; e < VN; ++e) {
+        float n = (to_f32(xv[k].v[e]) - mean) * rstd;
+        float o = n * to_f32(wv.v[e]);
+        if (!RMS) o += to_f32(bv.v[e]);
+        ov.v[e] = from_f32<T>(o);
+      }
+      st128(yr + i * VN, ov);
+    }
+  }
+}
+
+// Backward.  Every group walks rows with a grid stride and keeps dw/db partial sums
+// for the columns it owns in registers; the partials go to scratch[2][nparts][C].
+template <typename T, int MAXV, int G, bool RMS>
+__global__ void norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
+                                const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
+                                T* __restrict__ dx, float* __restrict__ scratch, long long rows, int C,
+                                int nparts) {
+  constexpr int VN = VecN<T>::n;
+  __shared__ float red[2 * (G > 32 ? G / 32 : 1)];
+  const int tig = (G == 32) ? (threadIdx.x & 31) : threadIdx.x;
+  const int groups_per_block = (G == 32) ? (blockDim.x >> 5) : 1;
+  const int gib = (G == 32) ? (threadIdx.x >> 5) : 0;  // group in block
+  const long long group = blockIdx.x * (long long)groups_per_block + gib;
+  const long long ngroups = gridDim.x * (long long)groups_per_block;
+  const int nvec = C / VN;
+
+  float dwacc[MAXV][VN], dbacc[MAXV][VN];
+  Pack<T, VN> wv[MAXV];
+#pragma unroll
+  for (int k = 0; k < MAXV; ++k) {
+    const int i = tig + k * G;
+#pragma unroll
+    for (int e = 0; e < VN; ++e) { dwacc[k][e] = 0.f; dbacc[k][e] = 0.f; }
+    if (i < nvec) wv[k] = ld128(w + i * VN);
+  }
+
+  for (long long row = group; row < rows; row += ngroups) {
+    const float mean = RMS ? 0.f : mean_in[row];
+    const float rstd = rstd_in[row];
+    const T* xr = x + row * C;
+    const T* dyr = dy + row * C;
+    Pack<T, VN> xv[MAXV], dv[MAXV];
+    float s1 = 0.f, s2 = 0.f;  // sum(dnorm), sum(dnorm * norm)
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int i = tig + k * G;
+      if (i < nvec) {
+        xv[k] = ld128(xr + i * VN);
+        dv[k] = ld128(dyr + i * VN);
+#pragma unroll
+        for (int e = 0; e < VN; ++e) {
+          float n = (to_f32(xv[k].v[e]) - mean) * rstd;
+          float g = to_f32(dv[k].v[e]);
+          float dn = g * to_f32(wv[k].v[e]);
+          s1 += dn;
+          s2 += dn * n;
+          dwacc[k][e] += g * n;
+          dbacc[k][e] += g;
+        }
+      }
+    }
+    group_sum2<G>(s1, s2, red);
+    const float m1 = RMS ? 0.f : s1 / C, m2 = s2 / C;
+    T* dxr = dx + row * C;
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int i = tig + k * G;
+      if (i < nvec) {
+        Pack<T, VN> ov;
+#pragma unroll
+        for (int e = 0; e < VN; ++e) {
+          float n = (to_f32(xv[k].v[e]) - mean) * rstd;
+          float dn = to_f32(dv[k].v[e]) * to_f32(wv[k].v[e]);
+          ov.v[e] = from_f32<T>((dn - m1 - n * m2) * rstd);
+        }
+        st128(dxr + i * VN, ov);
+      }
+    }
+  }
+
+  // Stage 1 of the dw/db reduction: the groups of a CTA fold their sums in a fixed
+  // order through shared memory, then the CTA writes one partial row.
+  extern __shared__ float acc_smem[];  // [2][C] when G == 32
+  float* dwp = scratch + (long long)blockIdx.x * C;
+  float* dbp = scratch + ((long long)nparts + blockIdx.x) * C;
+  if constexpr (G == 32) {
+    for (int g = 0; g < groups_per_block; ++g) {
+      if (gib == g) {
+#pragma unroll
+        for (int k = 0; k < MAXV; ++k) {
+          const int i = tig + k * G;
+          if (i < nvec) {
+#pragma unroll
+            for (int e = 0; e < VN; ++e) {
+              const int c = i * VN + e;
+              acc_smem[c] = (g == 0 ? 0.f : acc_smem[c]) + dwacc[k][e];
+              if (!RMS) acc_smem[C + c] = (g == 0 ? 0.f : acc_smem[C + c]) + dbacc[k][e];
+            }
+          }
+        }
+      }
+      __syncthreads();
+    }
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+      dwp[c] = acc_smem[c];
+      if (!RMS) dbp[c] = acc_smem[C + c];
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int i = tig + k * G;
+      if (i < nvec) {
+#pragma unroll
+        for (int e = 0; e < VN; ++e) {
+          dwp[i * VN + e] = dwacc[k][e];
+          if (!RMS) dbp[i * VN + e] = dbacc[k][e];
+        }
+      }
+    }
+  }
+}
+
+// Stage 2: out[c] (+)= sum_p scratch[p][c], in a fixed order.  32 columns per CTA,
+// 8 threads per column each summing every 8th partial row.
+__global__ void partial_colsum_kernel(const float* __restrict__ scratch, float* __restrict__ out, int nparts, int C,
+                                      int accumulate) {
+  __shared__ float sm[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + tx;
+  float s = 0.f;
+  if (c < C)
+    for (int p = ty; p < nparts; p += 8) s += scratch[(long long)p * C + c];
+  sm[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && c < C) {
+    float t = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) t += sm[j][tx];
+    out[c] = accumulate ? out[c] + t : t;
+  }
+}
+
+// Scalar fallbacks (any C): CTA per row, re-reading the row from L1/L2.
+template <typename T, bool RMS>
+__global__ void norm_fwd_generic(const T* x, const T* w, const T* b, T* y, float* mean_out, float* rstd_out,
+                                 long long rows, int C, float eps) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const T* xr = x + row * C;
+  float s = 0.f;
+  if (!RMS) for (int i = threadIdx.x; i < C; i += blockDim.x) s += to_f32(xr[i]);
+  const float mean = RMS ? 0.f : block_sum(s, red) / C;
+  float s2 = 0.f;
+  for (int i = threadIdx.x; i < C; i += blockDim.x) { float d = to_f32(xr[i]) - mean; s2 += d * d; }
+  const float rstd = rsqrtf(block_sum(s2, red) / C + eps);
+  if (threadIdx.x == 0) {
+    if (!RMS && mean_out) mean_out[row] = mean;
+    if (rstd_out) rstd_out[row] = rstd;
+  }
+  for (int i = threadIdx.x; i < C; i += blockDim.x) {
+    float o = (to_f32(xr[i]) - mean) * rstd * to_f32(w[i]);
+    if (!RMS) o += to_f32(b[i]);
+    y[row * C + i] = from_f32<T>(o);
+  }
+}
+template <typename T, bool RMS>
+__global__ void norm_bwd_dx_generic(const T* dy, const T* x, const T* w, const float* mean_in, const float* rstd_in,
+                                    T* dx, long long rows, int C) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const float mean = RMS ? 0.f : mean_in[row], rstd = rstd_in[row];
+  float s1 = 0.f, s2 = 0.f;
+  for (int i = threadIdx.x; i < C; i += blockDim.x) {
+    float n = (to_f32(x[row * C + i]) - mean) * rstd;
+    float dn = to_f32(dy[row * C + i]) * to_f32(w[i]);
+    s1 += dn; s2 += dn * n;
+  }
+  s1 = block_sum(s1, red);
+  s2 = block_sum(s2, red);
+  const float m1 = RMS ? 0.f : s1 / C, m2 = s2 / C;
+  for (int i = threadIdx.x; i < C; i += blockDim.x) {
+    float n = (to_f32(x[row * C + i]) - mean) * rstd;
+    float dn = to_f32(dy[row * C + i]) * to_f32(w[i]);
+    dx[row * C + i] = from_f32<T>((dn - m1 - n * m2) * rstd);
+  }
+}
+template <typename T, bool RMS>
+__global__ void norm_bwd_dw_generic(const T* dy, const T* x, const float* mean_in, const float* rstd_in, float* dw,
+                                    float* db, long long rows, int C, int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float sw = 0.f, sb = 0.f;
+  for (long long r = 0; r < rows; ++r) {
+    float g = to_f32(dy[r * C + c]);
+    float n = (to_f32(x[r * C + c]) - (RMS ? 0.f : mean_in[r])) * rstd_in[r];
+    sw += g * n; sb += g;
+  }
+  dw[c] = accumulate ? dw[c] + sw : sw;
+  if (!RMS && db) db[c] = accumulate ? db[c] + sb : sb;
+}
+
+constexpr int kNormBwdBlocks = 148 * 2;  // CTAs of the warp-per-row backward kernel
+constexpr int kNormBwdParts = 148 * 4;   // partial rows per gradient in the scratch buffer (upper bound)
+
+struct NormPlan {
+  int G;      // 32 or 256; 0 = generic fallback
+  int maxv;   // register vectors per thread
+};
+template <typename T>
+static NormPlan plan_norm(int C) {
+  constexpr int VN = VecN<T>::n;
+  NormPlan p{0, 0};
+  if (C % VN != 0) return p;
+  const int nvec = C / VN;
+  if (nvec <= 32 * 4) { p.G = 32; p.maxv = 4; }
+  else if (nvec <= 32 * 8) { p.G = 32; p.maxv = 8; }
+  else if (nvec <= 256 * 2) { p.G = 256; p.maxv = 2; }
+  else if (nvec <= 256 * 8) { p.G = 256; p.maxv = 8; }
+  return p;
+}
+
+template <typename T, bool RMS>
+static int norm_fwd_launch(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
+                           long long rows, int C, float eps, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  const T* X = static_cast<const T*>(x); const T* W = static_cast<const T*>(w); const T* Bv = static_cast<const T*>(b);
+  T* Y = static_cast<T*>(y);
+  NormPlan p = plan_norm<T>(C);
+  const bool aligned = !((uintptr_t)x & 15) && !((uintptr_t)y & 15) && !((uintptr_t)w & 15) && !((uintptr_t)b & 15);
+  if (p.G == 32 && aligned) {
+    const int blocks = (int)((rows + 3) / 4);
+    if (p.maxv == 4) norm_fwd_kernel<T, 4, 32, RMS><<<blocks, 128, 0, st>>>(X, W, Bv, Y, mean, rstd, rows, C, eps);
+    else norm_fwd_kernel<T, 8, 32, RMS><<<blocks, 128, 0, st>>>(X, W, Bv, Y, mean, rstd, rows, C, eps);
+  } else if (p.G == 256 && aligned) {
+    if (p.maxv == 2) norm_fwd_kernel<T, 2, 256, RMS><<<(unsigned)rows, 256, 0, st>>>(X, W, Bv, Y, mean, rstd, rows, C, eps);
+    else norm_fwd_kernel<T, 8, 256, RMS><<<(unsigned)rows, 256, 0, st>>>(X, W, Bv, Y, mean, rstd, rows, C, eps);
+  } else {
+    norm_fwd_generic<T, RMS><<<(unsigned)rows, 256, 0, st>>>(X, W, Bv, Y, mean, rstd, rows, C, eps);
+  }
+  return (int)cudaGetLastError();
+}
+
+template <typename T, bool RMS>
+static int norm_bwd_launch(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
+                           void* dx, float* dw, float* db, float* scratch, long long rows, int C, int accumulate,
+                           cudaStream_t st) {
+  if (rows <= 0) return 0;
+  const T* DY = static_cast<const T*>(dy); const T* X = static_cast<const T*>(x); const T* W = static_cast<const T*>(w);
+  T* DX = static_cast<T*>(dx);
+  NormPlan p = plan_norm<T>(C);
+  const bool aligned = !((uintptr_t)x & 15) && !((uintptr_t)dy & 15) && !((uintptr_t)w & 15) && !((uintptr_t)dx & 15);
+  if (p.G != 0 && aligned && scratch != nullptr) {
+    const int nparts = kNormBwdParts;  // scratch is [2][kNormBwdParts][C]; the first `used` rows are written
+    int used;
+    if (p.G == 32) {
+      used = kNormBwdBlocks;
+      const size_t sm = 2 * (size_t)C * sizeof(float);
+      if (p.maxv == 4) norm_bwd_kernel<T, 4, 32, RMS><<<used, 128, sm, st>>>(DY, X, W, mean, rstd, DX, scratch, rows, C, nparts);
+      else norm_bwd_kernel<T, 8, 32, RMS><<<used, 128, sm, st>>>(DY, X, W, mean, rstd, DX, scratch, rows, C, nparts);
+    } else {
+      used = kNormBwdParts;
+      if (p.maxv == 2) norm_bwd_kernel<T, 2, 256, RMS><<<used, 256, 0, st>>>(DY, X, W, mean, rstd, DX, scratch, rows, C, nparts);
+      else norm_bwd_kernel<T, 8, 256, RMS><<<used, 256, 0, st>>>(DY, X, W, mean, rstd, DX, scratch, rows, C, nparts);
+    }
+    partial_colsum_kernel<<<(C + 31) / 32, 256, 0, st>>>(scratch, dw, used, C, accumulate);
+    if (!RMS && db)
+      partial_colsum_kernel<<<(C + 31) / 32, 256, 0, st>>>(scratch + (long long)nparts * C, db, used, C, accumulate);
+  } else {
+    norm_bwd_dx_generic<T, RMS><<<(unsigned)rows, 256, 0, st>>>(DY, X, W, mean, rstd, DX, rows, C);
+    norm_bwd_dw_generic<T, RMS><<<(C + 127) / 128, 128, 0, st>>>(DY, X, mean, rstd, dw, db, rows, C, accumulate);
+  }
+  return (int)cudaGetLastError();
+}
+
+}  // namespace titb
+
+using namespace titb;
+
+TITB_API int titb_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
+                                long long rows, int C, float eps, int dtype, cudaStream_t stream) {
+  return dtype == 1 ? norm_fwd_launch<bf16, false>(x, w, b, y, mean, rstd, rows, C, eps, stream)
+                    : norm_fwd_launch<float, false>(x, w, b, y, mean, rstd, rows, C, eps, stream);
+}
+TITB_API int titb_layernorm_bwd_blocks(long long) { return kNormBwdParts; }
+TITB_API int titb_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
+                                void* dx, float* dw, float* db, float* scratch, long long rows, int C, int dtype,
+                                int accumulate_wgrad, cudaStream_t stream) {
+  return dtype == 1
+             ? norm_bwd_launch<bf16, false>(dy, x, w, mean, rstd, dx, dw, db, scratch, rows, C, accumulate_wgrad, stream)
+             : norm_bwd_launch<float, false>(dy, x, w, mean, rstd, dx, dw, db, scratch, rows, C, accumulate_wgrad, stream);
+}
+TITB_API int titb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long long rows, int C, float eps,
+                              int dtype, cudaStream_t stream) {
+  return dtype == 1 ? norm_fwd_launch<bf16, true>(x, w, w, y, nullptr, rstd, rows, C, eps, stream)
+                    : norm_fwd_launch<float, true>(x, w, w, y, nullptr, rstd, rows, C, eps, stream);
+}
+TITB_API int titb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw,
+                              float* scratch, long long rows, int C, int dtype, int accumulate_wgrad,
+                              cudaStream_t stream) {
+  return dtype == 1
+             ? norm_bwd_launch<bf16, true>(dy, x, w, nullptr, rstd, dx, dw, nullptr, scratch, rows, C, accumulate_wgrad, stream)
+             : norm_bwd_launch<float, true>(dy, x, w, nullptr, rstd, dx, dw, nullptr, scratch, rows, C, accumulate_wgrad, stream);
+}

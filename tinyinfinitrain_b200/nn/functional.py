@@ -1,0 +1,78 @@
+"""The reference's ``nn::function`` namespace (infini_train/include/nn/functional.h:23-168)."""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+
+
+def Tril(x, diagonal: int = 0):
+    return ops.tril(x, diagonal)
+
+
+def Triu(x, diagonal: int = 0):
+    return ops.triu(x, diagonal)
+
+
+def Ones(dims, dtype=torch.float32, device=None):
+    return torch.ones(*dims, dtype=dtype, device=device)
+
+
+def Reciprocal(x):
+    return ops.unary("reciprocal", x)
+
+
+def Sin(x):
+    return ops.unary("sin", x)
+
+
+def Cos(x):
+    return ops.unary("cos", x)
+
+
+def Tanh(x):
+    return ops.unary("tanh", x)
+
+
+def Pow(a, b):
+    """Pow(tensor, exponent) or Pow(base, tensor)."""
+    if isinstance(a, torch.Tensor):
+        return ops.unary("pow_exp", a, float(b))
+    return ops.unary("pow_base", b, float(a))
+
+
+def Rsqrt(x):
+    return ops.unary("rsqrt", x)
+
+
+def Mean(x, dim: int, keep_dim: bool = False):
+    return x.mean(dim, keepdim=keep_dim)
+
+
+def Sum(x, dim: int, keep_dim: bool = False):
+    return x.sum(dim, keepdim=keep_dim)
+
+
+def Max(x, dim: int, keep_dim: bool = False):
+    return x.amax(dim, keepdim=keep_dim)
+
+
+def Min(x, dim: int, keep_dim: bool = False):
+    return x.amin(dim, keepdim=keep_dim)
+
+
+def Sigmoid(x):
+    return ops.unary("sigmoid", x)
+
+
+def Softmax(x, dim: int = -1):
+    return ops.softmax(x, dim)
+
+
+def Slice(x, starts, ends, steps):
+    idx = tuple(slice(s, e, st) for s, e, st in zip(starts, ends, steps))
+    return x[idx].contiguous()
+
+
+def Stack(tensors, dim: int = 0):
+    return torch.stack(list(tensors), dim)
