@@ -184,3 +184,28 @@ struct TitbAttnDesc {
 };
 TITB_API int titb_attn_fwd(const TitbAttnDesc* d, cudaStream_t stream);
 TITB_API int titb_attn_bwd(const TitbAttnDesc* d, cudaStream_t stream);
+
+// ---- NVLink communication (peer-mapped symmetric memory) -------------------------------------------
+// Pointer tables are host arrays of device addresses, one per rank, valid on the calling GPU.
+// Cross-GPU barrier on signal pads: pad of rank r = uint32[8 channels][16]; `epoch` is a device
+// counter advanced by the kernel (graph-replayable).  The wait gives up after timeout_s seconds and
+// records kStatusPeerTimeout in the library status word.
+TITB_API int titb_comm_barrier(const unsigned long long* pad_ptrs, int rank, int world, int channel,
+                               unsigned int* epoch, double timeout_s, cudaStream_t stream);
+// ZeRO-1 step in one kernel: reduce this rank's gradient shard over all ranks, Adam on the fp32
+// shard state, write the bf16 parameters of the shard into every rank's parameter buffer.
+struct TitbRsAdamDesc {
+  const unsigned long long* grad_ptrs;   // fp32 flat gradient buffer per rank
+  const unsigned long long* param_ptrs;  // bf16 flat parameter buffer per rank
+  const void* grad_mc;                   // NVLS multicast address of the gradient buffer, or null
+  void* param_mc;                        // NVLS multicast address of the parameter buffer, or null
+  float* master; float* m; float* v;     // local shard state (length shard_n)
+  long long shard_off, shard_n;          // shard position in the flat space (elements; n % 8 == 0)
+  int world, rank;
+  float lr, beta1, beta2, eps, weight_decay, bc1, bc2, grad_scale;
+  const float* dev_state;                // optional device {t, bc1, bc2, lr}
+  int max_blocks;                        // 0 = default
+};
+TITB_API int titb_rs_adam_ag(const TitbRsAdamDesc* d, cudaStream_t stream);
+TITB_API int titb_allreduce_small(const unsigned long long* buf_ptrs, float* out, int n, int world, int op,
+                                  cudaStream_t stream);
