@@ -221,6 +221,16 @@ Tensor rope(const Tensor& x, int64_t pos_offset, double theta, bool inverse, boo
   return y;
 }
 
+// In-place rotary embedding on the first `n_heads` heads of a fused [B, T, W] projection buffer.
+void rope_qkv_(const Tensor& qkv, int64_t n_heads, int64_t hd, int64_t pos_offset, double theta, bool inverse) {
+  check_cuda(qkv, "qkv");
+  TORCH_CHECK(qkv.dim() == 3 && n_heads * hd <= qkv.size(2), "titb200 rope_qkv_: expects [B, T, W] with W >= heads*hd");
+  c10::cuda::CUDAGuard guard(qkv.device());
+  CHECK_RC(titb_rope_strided(qkv.data_ptr(), qkv.data_ptr(), (int)qkv.size(0), (int)qkv.size(1), (int)n_heads, (int)hd,
+                             qkv.size(2), (int)pos_offset, (float)theta, inverse, dt_code(qkv), cur_stream()),
+           "rope_strided");
+}
+
 // ------------------------------------------------------------------ embedding
 Tensor embedding_fwd(const Tensor& idx, const Tensor& wte, const optional<Tensor>& wpe, int64_t pos_offset) {
   check_cuda(idx, "idx"); check_cuda(wte, "wte");
@@ -460,6 +470,7 @@ PYBIND11_MODULE(_C, m) {
   m.def("swiglu_bwd", &swiglu_bwd);
   m.def("rope", &rope, py::arg("x"), py::arg("pos_offset") = 0, py::arg("theta") = 10000.0, py::arg("inverse") = false,
         py::arg("inplace") = false);
+  m.def("rope_qkv_", &rope_qkv_);
   m.def("embedding_fwd", &embedding_fwd, py::arg("idx"), py::arg("wte"), py::arg("wpe") = py::none(),
         py::arg("pos_offset") = 0);
   m.def("embedding_bwd", &embedding_bwd, py::arg("idx"), py::arg("dout"), py::arg("dwte") = py::none(),

@@ -101,6 +101,11 @@ TITB_API int titb_swiglu_bwd(const void* dy, const void* x, void* dx, long long 
 TITB_API int titb_rope(const void* x, void* y, int B, int T, int H, int hd, int pos_offset, float theta,
                        int inverse, int dtype, cudaStream_t stream);
 
+// Same on the first H heads of rows that are stride_t elements apart (e.g. the q and k heads of a
+// fused QKV buffer); x and y use the same stride.
+TITB_API int titb_rope_strided(const void* x, void* y, int B, int T, int H, int hd, long long stride_t,
+                               int pos_offset, float theta, int inverse, int dtype, cudaStream_t stream);
+
 // ---- embedding ------------------------------------------------------------------------
 // out[b,t,:] = wte[idx[b,t],:] (+ wpe[t + pos_offset,:] when wpe != null).
 TITB_API int titb_embedding_fwd(const long long* idx, const void* wte, const void* wpe, void* out, long long BT,

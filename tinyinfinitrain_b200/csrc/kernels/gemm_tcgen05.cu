@@ -435,17 +435,17 @@ int device_sm_count() {
 static unsigned g_dbg_lbo = 0, g_dbg_sbo = 0, g_dbg_kstep = 0;
 
 static int pick_tile_n(int M, int N, int splits) {
+  // 128 x 256 tiles move fewer operand bytes per FLOP; 128 x 128 only wins when it removes
+  // a clearly larger share of the last, partially filled wave.
   const int sms = device_sm_count();
   const long long tm = (M + kBM - 1) / kBM;
-  long long best_cost = -1;
-  int best = 256;
-  for (int bn : {256, 128}) {
-    long long tiles = tm * ((N + bn - 1) / bn) * splits;
-    long long waves = (tiles + sms - 1) / sms;
-    long long cost = waves * bn;
-    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
-  }
-  return best;
+  auto cost = [&](int bn) {
+    const long long tiles = tm * ((N + bn - 1) / bn) * splits;
+    const long long waves = (tiles + sms - 1) / sms;
+    return waves * bn;
+  };
+  if (N <= 128) return 128;
+  return (cost(128) * 5 < cost(256) * 4) ? 128 : 256;
 }
 
 }  // namespace titb

@@ -113,7 +113,7 @@ __global__ void swiglu_bwd_kernel(const T* __restrict__ dy, const T* __restrict_
 
 // Rotary embedding on [B, T, H, hd]: pairs (i, i + hd/2), angle (t + offset) * theta^(-2i/hd).
 template <typename T>
-__global__ void rope_kernel(const T* __restrict__ x, T* __restrict__ y, long long BT, int T_, int H, int hd,
+__global__ void rope_kernel(const T* x, T* y, long long BT, int T_, int H, int hd, long long stride_t,
                             int pos_offset, float log2_theta, int inverse) {
   constexpr int VN = VecN<T>::n;
   const int half = hd / 2;
@@ -124,8 +124,9 @@ __global__ void rope_kernel(const T* __restrict__ x, T* __restrict__ y, long lon
     const long long bth = i / hv;
     const long long bt = bth / H;
     const int t = (int)(bt % T_) + pos_offset;
-    const T* xp = x + bth * hd + v * VN;
-    T* yp = y + bth * hd + v * VN;
+    const int hh = (int)(bth - bt * H);
+    const T* xp = x + bt * stride_t + hh * hd + v * VN;
+    T* yp = y + bt * stride_t + hh * hd + v * VN;
     Pack<T, VN> a = ld128(xp), b = ld128(xp + half), oa, ob;
 #pragma unroll
     for (int e = 0; e < VN; ++e) {
@@ -248,11 +249,21 @@ __global__ void colsum_stage1(const T* __restrict__ x, float* __restrict__ scrat
 }
 __global__ void colsum_stage2(const float* __restrict__ scratch, float* __restrict__ out, int nparts, int C,
                               int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
+  // 32 columns per CTA, 8 threads per column each folding every 8th partial row, fixed order.
+  __shared__ float sm[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + tx;
   float s = 0.f;
-  for (int p = 0; p < nparts; ++p) s += scratch[(long long)p * C + c];
-  out[c] = accumulate ? out[c] + s : s;
+  if (c < C)
+    for (int p = ty; p < nparts; p += 8) s += scratch[(long long)p * C + c];
+  sm[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && c < C) {
+    float t = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) t += sm[j][tx];
+    out[c] = accumulate ? out[c] + t : t;
+  }
 }
 template <typename T>
 __global__ void colsum_generic(const T* __restrict__ x, float* __restrict__ out, long long rows, int C, int accumulate) {
@@ -298,14 +309,19 @@ TITB_API int titb_swiglu_bwd(const void* dy, const void* x, void* dx, long long 
 
 TITB_API int titb_rope(const void* x, void* y, int B, int T, int H, int hd, int pos_offset, float theta, int inverse,
                        int dtype, cudaStream_t st) {
+  return titb_rope_strided(x, y, B, T, H, hd, (long long)H * hd, pos_offset, theta, inverse, dtype, st);
+}
+
+TITB_API int titb_rope_strided(const void* x, void* y, int B, int T, int H, int hd, long long stride_t, int pos_offset,
+                               float theta, int inverse, int dtype, cudaStream_t st) {
   const long long BT = (long long)B * T;
   if (BT <= 0) return 0;
   const int vn = dtype == 1 ? 8 : 4;
   if ((hd / 2) % vn) return (int)cudaErrorInvalidValue;
   const int blocks = ew_blocks(BT * H * (hd / 2 / vn));
   const float l2 = log2f(theta);
-  if (dtype == 1) rope_kernel<bf16><<<blocks, kEwThreads, 0, st>>>((const bf16*)x, (bf16*)y, BT, T, H, hd, pos_offset, l2, inverse);
-  else rope_kernel<float><<<blocks, kEwThreads, 0, st>>>((const float*)x, (float*)y, BT, T, H, hd, pos_offset, l2, inverse);
+  if (dtype == 1) rope_kernel<bf16><<<blocks, kEwThreads, 0, st>>>((const bf16*)x, (bf16*)y, BT, T, H, hd, stride_t, pos_offset, l2, inverse);
+  else rope_kernel<float><<<blocks, kEwThreads, 0, st>>>((const float*)x, (float*)y, BT, T, H, hd, stride_t, pos_offset, l2, inverse);
   return (int)cudaGetLastError();
 }
 
@@ -406,12 +422,12 @@ TITB_API int titb_colsum(const void* x, float* out, long long rows, int C, int d
   if (C <= 0) return 0;
   const int vn = dtype == 1 ? 8 : 4;
   if (scratch && (C % vn) == 0 && !((uintptr_t)x & 15) && rows > 0) {
-    int parts = (int)((rows + 63) / 64);
+    int parts = (int)((rows + 127) / 128);
     if (parts > kColsumParts) parts = kColsumParts;
     dim3 grid((C / vn + 31) / 32, parts);
     if (dtype == 1) colsum_stage1<bf16><<<grid, 256, 0, st>>>((const bf16*)x, scratch, rows, C);
     else colsum_stage1<float><<<grid, 256, 0, st>>>((const float*)x, scratch, rows, C);
-    colsum_stage2<<<(C + 127) / 128, 128, 0, st>>>(scratch, out, parts, C, accumulate);
+    colsum_stage2<<<(C + 31) / 32, 256, 0, st>>>(scratch, out, parts, C, accumulate);
   } else {
     if (dtype == 1) colsum_generic<bf16><<<(C + 127) / 128, 128, 0, st>>>((const bf16*)x, out, rows, C, accumulate);
     else colsum_generic<float><<<(C + 127) / 128, 128, 0, st>>>((const float*)x, out, rows, C, accumulate);

@@ -2,6 +2,6 @@
 from .functional import (  # noqa: F401
     EPI_BIAS, EPI_BIAS_GELU, EPI_BIAS_RESIDUAL, EPI_DGELU, EPI_NONE,
     attention_ref, binary, cast, causal_attention, causal_attention_qkv, cross_entropy, embedding, gelu, gelu_ref, layernorm, linear,
-    lm_head_loss, matmul, mlp_gelu, rmsnorm, rmsnorm_ref, rope, rope_ref, set_attention_impl, softmax, swiglu,
+    lm_head_loss, matmul, mlp_gelu, rmsnorm, rmsnorm_ref, rope, rope_qkv, rope_ref, set_attention_impl, softmax, swiglu,
     transpose, tril, triu, unary,
 )

@@ -370,6 +370,34 @@ def rope(x, pos_offset: int = 0, theta: float = 500000.0):
     return _RopeFn.apply(x, pos_offset, theta)
 
 
+class _RopeQKVFn(torch.autograd.Function):
+    """Rotates the first ``n_heads`` heads (q and k) of a fused [B, T, W] projection in place."""
+
+    @staticmethod
+    def forward(ctx, qkv, n_heads, hd, pos_offset, theta):
+        ctx.args = (n_heads, hd, pos_offset, theta)
+        C.rope_qkv_(qkv, n_heads, hd, pos_offset, theta, False)
+        ctx.mark_dirty(qkv)
+        return qkv
+
+    @staticmethod
+    def backward(ctx, d):
+        n_heads, hd, pos_offset, theta = ctx.args
+        d = d.contiguous()
+        C.rope_qkv_(d, n_heads, hd, pos_offset, theta, True)
+        return d, None, None, None, None
+
+
+def rope_qkv(qkv, n_rot_heads: int, head_dim: int, pos_offset: int = 0, theta: float = 500000.0):
+    """RoPE on the q and k heads of a fused QKV projection [B, T, (Hq + 2 Hkv) * hd]."""
+    if qkv.is_cuda and qkv.dtype in (torch.float32, _bf16) and qkv.is_contiguous():
+        return _RopeQKVFn.apply(qkv, n_rot_heads, head_dim, pos_offset, theta)
+    B, T, W = qkv.shape
+    n = n_rot_heads * head_dim
+    rot = rope(qkv[..., :n].reshape(B, T, n_rot_heads, head_dim), pos_offset, theta).reshape(B, T, n)
+    return torch.cat([rot, qkv[..., n:]], dim=-1)
+
+
 # -------------------------------------------------------------------------- embedding
 class _EmbeddingFn(torch.autograd.Function):
     @staticmethod

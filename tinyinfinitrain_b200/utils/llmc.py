@@ -37,3 +37,27 @@ def save_gpt2(model, path: str, bf16: bool = False) -> None:
            "padded_vocab_size": cfg.padded_vocab_size}
     sd = {k: v.detach().float().cpu() for k, v in model.StateDict().items() if k != "lm_head.weight"}
     C.llmc_write_gpt2(path, hdr, sd)
+
+
+def load_llama3(path: str, device=None, dtype=torch.float32):
+    from ..models.llama3 import LLaMA3, LLaMA3Config
+
+    hdr, sd = C.llmc_read_llama3(path)
+    cfg = LLaMA3Config(block_size=hdr["max_seq_len"], vocab_size=hdr["vocab_size"], n_layer=hdr["n_layer"],
+                       n_head=hdr["n_head"], n_kv_head=hdr["n_kv_head"], n_embd=hdr["n_embd"], ffn_dim=hdr["ffn_dim"],
+                       norm_eps=hdr["norm_eps"], rope_theta=hdr["rope_theta"])
+    model = LLaMA3(cfg, device=device, dtype=dtype, seed=None)
+    own = model.StateDict()
+    with torch.no_grad():
+        for name, t in sd.items():
+            own[name].copy_(t.to(own[name].dtype))
+    return model
+
+
+def save_llama3(model, path: str, bf16: bool = False) -> None:
+    cfg = model.config
+    hdr = {"version": 5 if bf16 else 3, "max_seq_len": cfg.block_size, "vocab_size": cfg.vocab_size,
+           "n_layer": cfg.n_layer, "n_head": cfg.n_head, "n_kv_head": cfg.n_kv_head, "n_embd": cfg.n_embd,
+           "ffn_dim": cfg.ffn_dim, "rope_theta": cfg.rope_theta, "norm_eps": cfg.norm_eps}
+    sd = {k: v.detach().float().cpu() for k, v in model.StateDict().items()}
+    C.llmc_write_llama3(path, hdr, sd)
