@@ -1,0 +1,65 @@
+"""Tensor + sequence parallel models on 2 CPU ranks (gloo) against the single-process model."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, q, which):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from tinyinfinitrain_b200.models import GPT2, GPT2Config, LLaMA3, LLaMA3Config
+        from tinyinfinitrain_b200.models.tp_models import TPTransformer, shard_state_dict
+        from tinyinfinitrain_b200.parallel import mesh as pm
+        from tinyinfinitrain_b200.parallel.tp import TPComm, sync_sequence_parallel_grads
+
+        m = pm.init_mesh(tp=world, pp=1)
+        comm = TPComm(m.tp_group)
+        if which == "gpt2":
+            cfg, cls = GPT2Config(block_size=32, vocab_size=250, n_layer=2, n_head=4, n_embd=32), GPT2
+        else:
+            cfg, cls = LLaMA3Config(block_size=32, vocab_size=256, n_layer=2, n_head=4, n_kv_head=2, n_embd=64,
+                                    ffn_dim=96), LLaMA3
+        full = cls(cfg)
+        tp = TPTransformer(cfg, comm)
+        tp.load_full_state_dict(full.StateDict())
+        g = torch.Generator().manual_seed(7)
+        idx = torch.randint(0, cfg.vocab_size, (2, 16), generator=g)
+        tgt = torch.roll(idx, -1, 1)
+        _, l0 = full(idx, tgt)
+        l1 = tp(idx, tgt)
+        l0.backward()
+        l1.backward()
+        sync_sequence_parallel_grads(tp.parameters(), comm)
+        ok = abs(l0.item() - l1.item()) < 1e-4
+        ref = shard_state_dict({k: v.grad for k, v in full.StateDict().items() if v.grad is not None}, cfg, world, rank)
+        worst = 0.0
+        for name, p in tp.named_parameters():
+            if name in ref and p.grad is not None:
+                r = ref[name]
+                worst = max(worst, (p.grad[:r.shape[0]] - r).abs().max().item())
+        q.put((rank, ok and worst < 1e-4, l0.item(), l1.item(), worst))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("which", ["gpt2", "llama3"])
+def test_tp2_matches_single_process(which):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29900 + (os.getpid() + hash(which)) % 90
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, which)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=180) for _ in procs]
+    for p in procs:
+        p.join(timeout=30)
+    assert all(r[1] for r in res), res

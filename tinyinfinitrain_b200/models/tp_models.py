@@ -1,0 +1,226 @@
+"""Tensor + sequence parallel GPT-2 and LLaMA-3.
+
+Same layer names as the single-GPU models; every rank holds its slice of each weight:
+``c_attn`` (heads), ``c_fc`` (hidden units) and ``wte`` / ``lm_head`` (vocabulary rows) are
+split by output rows, the two ``c_proj`` by input columns; norm weights, biases of the row
+parallel layers and ``wpe`` are replicated.  Activations between blocks are token shards
+``[B*T/tp, C]``.  ``shard_state_dict`` cuts a full model's tensors into one rank's slices.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional
+
+import torch
+
+from .. import nn, ops
+from ..nn import init
+from ..parallel import tp as tpl
+from .gpt2 import GPT2Config
+from .llama3 import LLaMA3Config
+
+
+def _qkv_rows(n_head: int, n_kv_head: int, hd: int, tp: int, rank: int):
+    """Row indices of a fused [q | k | v] projection that belong to one tensor-parallel rank."""
+    hq, hk = n_head // tp, n_kv_head // tp
+    q = torch.arange(rank * hq * hd, (rank + 1) * hq * hd)
+    k = n_head * hd + torch.arange(rank * hk * hd, (rank + 1) * hk * hd)
+    v = (n_head + n_kv_head) * hd + torch.arange(rank * hk * hd, (rank + 1) * hk * hd)
+    return torch.cat([q, k, v])
+
+
+def shard_state_dict(sd: Dict[str, torch.Tensor], cfg, tp: int, rank: int) -> Dict[str, torch.Tensor]:
+    """Slices a full GPT-2 / LLaMA-3 state dict for tensor-parallel rank ``rank`` of ``tp``."""
+    is_llama = isinstance(cfg, LLaMA3Config)
+    n_kv = cfg.n_kv_head if is_llama else cfg.n_head
+    hd = cfg.n_embd // cfg.n_head
+    out = {}
+    for name, t in sd.items():
+        if name.endswith("attn.c_attn.weight") or name.endswith("attn.c_attn.bias"):
+            out[name] = t[_qkv_rows(cfg.n_head, n_kv, hd, tp, rank)]
+        elif name.endswith("mlp.c_fc.weight") or name.endswith("mlp.c_fc.bias"):
+            if is_llama:  # rows are [gate | up]
+                F = t.shape[0] // 2
+                f = F // tp
+                out[name] = torch.cat([t[rank * f:(rank + 1) * f], t[F + rank * f:F + (rank + 1) * f]])
+            else:
+                n = t.shape[0] // tp
+                out[name] = t[rank * n:(rank + 1) * n]
+        elif name.endswith("c_proj.weight"):
+            n = t.shape[1] // tp
+            out[name] = t[:, rank * n:(rank + 1) * n]
+        elif name in ("transformer.wte.weight", "lm_head.weight"):
+            n = t.shape[0] // tp
+            out[name] = t[rank * n:(rank + 1) * n]
+        else:
+            out[name] = t
+    return {k: v.contiguous() for k, v in out.items()}
+
+
+class TPAttention(nn.Module):
+    kType = "CausalSelfAttention"
+
+    def __init__(self, n_embd, n_head, n_kv_head, comm, bias, rope_theta=None, device=None, dtype=torch.float32):
+        super().__init__()
+        assert n_head % comm.world == 0 and n_kv_head % comm.world == 0
+        self.hd = n_embd // n_head
+        self.hq, self.hk = n_head // comm.world, n_kv_head // comm.world
+        self.rope_theta = rope_theta
+        self.c_attn = tpl.ColumnParallelLinear(n_embd, (n_head + 2 * n_kv_head) * self.hd, comm, bias, device, dtype)
+        self.c_proj = tpl.RowParallelLinear(n_embd, n_embd, comm, bias, device, dtype)
+
+    def forward(self, x_s, B: int, T: int, residual_s=None):
+        qkv = self.c_attn(x_s).view(B, T, -1)
+        if self.rope_theta is not None:
+            qkv = ops.rope_qkv(qkv, self.hq + self.hk, self.hd, 0, self.rope_theta)
+        y = ops.causal_attention_qkv(qkv, self.hq, self.hk)
+        return self.c_proj(y.reshape(B * T, self.hq * self.hd), residual_s)
+
+
+class TPGPT2MLP(nn.Module):
+    kType = "MLP"
+
+    def __init__(self, n_embd, comm, device=None, dtype=torch.float32):
+        super().__init__()
+        self.comm = comm
+        self.c_fc = tpl.ColumnParallelLinear(n_embd, 4 * n_embd, comm, True, device, dtype)
+        self.c_proj = tpl.RowParallelLinear(4 * n_embd, n_embd, comm, True, device, dtype)
+
+    def forward(self, x_s, residual_s=None):
+        return tpl._TPMLPGeluFn.apply(x_s, self.c_fc.weight, self.c_fc.bias, self.c_proj.weight, self.c_proj.bias,
+                                      residual_s, self.comm)
+
+
+class TPLLaMAMLP(nn.Module):
+    kType = "MLP"
+
+    def __init__(self, n_embd, ffn_dim, comm, device=None, dtype=torch.float32):
+        super().__init__()
+        self.c_fc = tpl.ColumnParallelLinear(n_embd, 2 * ffn_dim, comm, False, device, dtype)  # local [gate | up]
+        self.c_proj = tpl.RowParallelLinear(ffn_dim, n_embd, comm, False, device, dtype)
+
+    def forward(self, x_s, residual_s=None):
+        return self.c_proj(ops.swiglu(self.c_fc(x_s)), residual_s)
+
+
+class TPBlock(nn.Module):
+    kType = "Block"
+
+    def __init__(self, cfg, comm, device=None, dtype=torch.float32):
+        super().__init__()
+        llama = isinstance(cfg, LLaMA3Config)
+        if llama:
+            self.ln_1 = nn.RMSNorm(cfg.n_embd, cfg.norm_eps, device=device, dtype=dtype)
+            self.ln_2 = nn.RMSNorm(cfg.n_embd, cfg.norm_eps, device=device, dtype=dtype)
+            self.attn = TPAttention(cfg.n_embd, cfg.n_head, cfg.n_kv_head, comm, False, cfg.rope_theta, device, dtype)
+            self.mlp = TPLLaMAMLP(cfg.n_embd, cfg.ffn_dim, comm, device, dtype)
+        else:
+            self.ln_1 = nn.LayerNorm(cfg.n_embd, device=device, dtype=dtype)
+            self.ln_2 = nn.LayerNorm(cfg.n_embd, device=device, dtype=dtype)
+            self.attn = TPAttention(cfg.n_embd, cfg.n_head, cfg.n_head, comm, True, None, device, dtype)
+            self.mlp = TPGPT2MLP(cfg.n_embd, comm, device, dtype)
+        for ln in (self.ln_1, self.ln_2):
+            for p in ln.parameters():
+                tpl._mark_sp(p)
+
+    def forward(self, x_s, B: int, T: int):
+        x_s = self.attn(self.ln_1(x_s), B, T, residual_s=x_s)
+        x_s = self.mlp(self.ln_2(x_s), residual_s=x_s)
+        return x_s
+
+
+class TPTransformer(nn.Module):
+    """GPT-2 or LLaMA-3 (chosen by the config type) on one tensor-parallel group.
+
+    ``layers`` restricts the module to a contiguous range of blocks (a pipeline stage);
+    ``first``/``last`` say whether the stage owns the embedding / the final norm + lm_head.
+    """
+
+    kType = "TPTransformer"
+
+    def __init__(self, cfg, comm: tpl.TPComm, device=None, dtype=torch.float32, seed: Optional[int] = 42,
+                 layers: Optional[range] = None, first: bool = True, last: bool = True):
+        super().__init__()
+        self.config, self.comm = cfg, comm
+        self.is_llama = isinstance(cfg, LLaMA3Config)
+        self.first, self.last = first, last
+        self.layer_ids = list(layers) if layers is not None else list(range(cfg.n_layer))
+        Cdim = cfg.n_embd
+        vp = cfg.vocab_size if self.is_llama else cfg.padded_vocab_size
+        gran = 128 * comm.world
+        self.vocab_padded = (vp + gran - 1) // gran * gran
+        mods = {}
+        if first:
+            mods["wte"] = tpl.VocabParallelEmbedding(self.vocab_padded, Cdim, comm, device, dtype)
+            if not self.is_llama:
+                mods["wpe"] = nn.Embedding(cfg.block_size, Cdim, device=device, dtype=dtype)
+                tpl._mark_sp(mods["wpe"].weight)
+        mods["h"] = nn.ModuleDict({str(i): TPBlock(cfg, comm, device, dtype) for i in self.layer_ids})
+        if last:
+            mods["ln_f"] = (nn.RMSNorm(Cdim, cfg.norm_eps, device=device, dtype=dtype) if self.is_llama
+                            else nn.LayerNorm(Cdim, device=device, dtype=dtype))
+            for p in mods["ln_f"].parameters():
+                tpl._mark_sp(p)
+        self.transformer = nn.ModuleDict(mods)
+        if last:
+            if self.is_llama or not first:
+                self.lm_head = nn.Module()
+                self.lm_head.weight = torch.nn.Parameter(
+                    torch.empty(self.vocab_padded // comm.world, Cdim, device=device, dtype=dtype))
+            else:
+                self.lm_head = nn.Module()
+                self.lm_head.weight = self.transformer["wte"].weight  # tied (GPT-2, single stage)
+        self.reset_parameters(seed)
+
+    def reset_parameters(self, seed: Optional[int]) -> None:
+        cfg = self.config
+        resid_std = 0.02 / math.sqrt(2 * cfg.n_layer)
+        for name, p in self.named_parameters():
+            if "ln_" in name and name.endswith("weight"):
+                init.Ones(p)
+            elif name.endswith(".bias"):
+                init.Zeros(p)
+            elif name.endswith("c_proj.weight"):
+                init.Normal(p, 0.0, resid_std, generator=seed)
+            else:
+                init.Normal(p, 0.0, 0.02, generator=seed)
+
+    def load_full_state_dict(self, sd: Dict[str, torch.Tensor]) -> None:
+        """Loads this rank's slices from a full (unsharded) state dict of the single-GPU model."""
+        sd = dict(sd)
+        for k in ("transformer.wte.weight", "lm_head.weight"):
+            if k in sd and sd[k].shape[0] < self.vocab_padded:
+                pad = torch.zeros(self.vocab_padded - sd[k].shape[0], sd[k].shape[1], dtype=sd[k].dtype)
+                sd[k] = torch.cat([sd[k].cpu(), pad])
+        mine = shard_state_dict(sd, self.config, self.comm.world, self.comm.rank)
+        own = dict(self.named_parameters(remove_duplicate=False))
+        with torch.no_grad():
+            for name, p in own.items():
+                if name in mine:
+                    p.copy_(mine[name].to(device=p.device, dtype=p.dtype))
+
+    def embed(self, idx):
+        B, T = idx.shape
+        x_s = self.transformer["wte"](idx)
+        if not self.is_llama:
+            Ms = x_s.shape[0]
+            rows = torch.arange(self.comm.rank * Ms, (self.comm.rank + 1) * Ms, device=idx.device)
+            x_s = x_s + ops.embedding(rows % T, self.transformer["wpe"].weight)
+        return x_s
+
+    def forward(self, idx_or_x, targets=None, B: Optional[int] = None, T: Optional[int] = None):
+        """First stage: ``idx`` int64 [B, T]; later stages: the previous stage's token shard plus B, T.
+        Last stage with ``targets`` returns the loss, otherwise the token shard is returned."""
+        if self.first:
+            B, T = idx_or_x.shape
+            x_s = self.embed(idx_or_x)
+        else:
+            x_s = idx_or_x
+        for i in self.layer_ids:
+            x_s = self.transformer["h"][str(i)](x_s, B, T)
+        if not self.last:
+            return x_s
+        x_s = self.transformer["ln_f"](x_s)
+        if targets is None:
+            return x_s
+        return tpl.vocab_parallel_lm_head_loss(x_s, self.lm_head.weight, targets, self.config.vocab_size, self.comm)

@@ -83,17 +83,20 @@ class _LinearFn(torch.autograd.Function):
         K = x.shape[-1]
         x2 = x.reshape(-1, K)
         N = w.shape[0]
+        # the output is allocated in its final shape so that it is not a view (callers may modify it in place)
+        y = torch.empty(*x.shape[:-1], N, device=x.device, dtype=x.dtype)
+        y2 = y.view(-1, N)
         if residual is not None:
-            y = C.gemm(x2, w, epilogue=EPI_BIAS_RESIDUAL, bias=b, aux_in=residual.reshape(-1, N))[0]
+            C.gemm(x2, w, epilogue=EPI_BIAS_RESIDUAL, bias=b, aux_in=residual.reshape(-1, N), out=y2)
         elif b is not None:
-            y = C.gemm(x2, w, epilogue=EPI_BIAS, bias=b)[0]
+            C.gemm(x2, w, epilogue=EPI_BIAS, bias=b, out=y2)
         else:
-            y = C.gemm(x2, w)[0]
+            C.gemm(x2, w, out=y2)
         ctx.save_for_backward(x2, w)
         ctx.b = b
         ctx.has_res = residual is not None
         ctx.xshape = x.shape
-        return y.view(*x.shape[:-1], N)
+        return y
 
     @staticmethod
     def backward(ctx, dy):
