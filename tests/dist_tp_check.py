@@ -1,0 +1,92 @@
+"""Worker for the multi-GPU tensor-parallel test (torchrun, one rank per GPU).
+
+1. all-gather -> GEMM and GEMM -> reduce-scatter fused kernels against NCCL + tcgen05 GEMM and
+   against fp32 PyTorch math, several shapes, repeated calls (buffer reuse).
+2. A sequence-parallel LLaMA-3 and GPT-2 block stack: fused vs NCCL path, loss and gradients.
+"""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    import tinyinfinitrain_b200 as tit
+    from tinyinfinitrain_b200.models import GPT2Config, LLaMA3Config
+    from tinyinfinitrain_b200.models.tp_models import TPTransformer
+    from tinyinfinitrain_b200.parallel.tp import TPComm, sync_sequence_parallel_grads
+
+    nccl = TPComm(dist.group.WORLD, "nccl")
+    fused = TPComm(dist.group.WORLD, "fused")
+    ok = True
+    msgs = []
+    for rep in range(2):
+        for (Ms, K, N) in [(128, 256, 512), (256, 2048, 384), (1024, 512, 1024)]:
+            g = torch.Generator(device=dev).manual_seed(100 + rank + rep)
+            x_s = (torch.randn(Ms, K, device=dev, generator=g) * 0.5).bfloat16()
+            gw = torch.Generator(device=dev).manual_seed(7 + rank)
+            w = (torch.randn(N, K, device=dev, generator=gw) * 0.1).bfloat16()
+            b = (torch.randn(N, device=dev, generator=gw) * 0.1).bfloat16()
+            y0, X0 = nccl.ag_gemm(x_s, w, b)
+            y1, X1 = fused.ag_gemm(x_s, w, b)
+            e_ag = (y0.float() - y1.float()).abs().max().item()
+            e_x = (X0.float() - X1.float()).abs().max().item()
+            ref = X0.float() @ w.float().t() + b.float()
+            e_ref = (y1.float() - ref).abs().max().item()
+            # row parallel: y [M, K] local features, weight [N, K]
+            M = Ms * world
+            yin = (torch.randn(M, K, device=dev, generator=g) * 0.5).bfloat16()
+            res = torch.randn(Ms, N, device=dev, generator=g).bfloat16()
+            z0 = nccl.gemm_rs(yin, w, False, b, res)
+            z1 = fused.gemm_rs(yin, w, False, b, res)
+            e_rs = (z0.float() - z1.float()).abs().max().item()
+            wt = w.t().contiguous()  # MN-major weight path (dgrad form)
+            z2 = fused.gemm_rs(yin, wt, True)
+            z3 = nccl.gemm_rs(yin, wt, True)
+            e_rs2 = (z2.float() - z3.float()).abs().max().item()
+            torch.cuda.synchronize()
+            good = e_ag < 5e-2 and e_x == 0.0 and e_ref < 0.15 and e_rs < 0.2 and e_rs2 < 0.2
+            ok = ok and good
+            msgs.append(f"[{Ms},{K},{N}] ag {e_ag:.3g} X {e_x:.3g} ref {e_ref:.3g} rs {e_rs:.3g} rs_mn {e_rs2:.3g}")
+    status = tit._lib.C.status_read(True)
+    ok = ok and status == 0
+
+    # model level
+    for cfg in (LLaMA3Config(block_size=256, vocab_size=1000, n_layer=2, n_head=4, n_kv_head=2, n_embd=256, ffn_dim=512),
+                GPT2Config(block_size=256, vocab_size=1000, n_layer=2, n_head=4, n_embd=256)):
+        gi = torch.Generator().manual_seed(5)
+        idx = torch.randint(0, 1000, (2, 256), generator=gi).to(dev)
+        tgt = torch.roll(idx, -1, 1)
+        res = {}
+        for name, comm in (("nccl", nccl), ("fused", fused)):
+            model = TPTransformer(cfg, comm, device=dev, dtype=torch.bfloat16, seed=42)
+            loss = model(idx, tgt)
+            loss.backward()
+            sync_sequence_parallel_grads(model.parameters(), comm)
+            res[name] = (loss.item(), {n: p.grad.float().clone() for n, p in model.named_parameters() if p.grad is not None})
+        dl = abs(res["nccl"][0] - res["fused"][0])
+        worst = 0.0
+        for n, gn in res["nccl"][1].items():
+            gf = res["fused"][1][n]
+            worst = max(worst, ((gn - gf).abs().max() / (gn.abs().max() + 1e-6)).item())
+        good = dl < 2e-2 and worst < 8e-2
+        ok = ok and good
+        msgs.append(f"{type(cfg).__name__}: loss nccl {res['nccl'][0]:.4f} fused {res['fused'][0]:.4f} worst rel grad diff {worst:.3g}")
+    status = tit._lib.C.status_read(True)
+    ok = ok and status == 0
+    print(f"rank {rank}: ok={ok} status={status}\n  " + "\n  ".join(msgs), flush=True)
+    t = torch.tensor([1.0 if ok else 0.0], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    dist.destroy_process_group()
+    sys.exit(0 if t.item() == 1.0 else 1)
+
+
+if __name__ == "__main__":
+    main()

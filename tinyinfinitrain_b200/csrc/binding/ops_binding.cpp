@@ -104,6 +104,67 @@ std::vector<Tensor> gemm(const Tensor& a, const Tensor& b, bool a_mn, bool b_mn,
   return {out};
 }
 
+// all-gather -> GEMM.  `peer_ptrs`: every rank's [Ms, K] bf16 shard (symmetric memory, already
+// separated from its writers by a cross-GPU barrier).  Returns {Y [M, N] (, pre-activation), X [M, K]}.
+std::vector<Tensor> gemm_ag(const std::vector<int64_t>& peer_ptrs, int64_t rank, int64_t rows_per_rank, int64_t K,
+                            const Tensor& b, bool b_mn, int64_t epilogue, const optional<Tensor>& bias,
+                            bool want_aux_out, int64_t helper_ctas) {
+  TORCH_CHECK(b.is_cuda() && b.scalar_type() == at::kBFloat16 && b.dim() == 2 && b.stride(1) == 1);
+  c10::cuda::CUDAGuard guard(b.device());
+  const int64_t world = (int64_t)peer_ptrs.size(), M = rows_per_rank * world;
+  const int64_t N = b_mn ? b.size(1) : b.size(0);
+  TORCH_CHECK((b_mn ? b.size(0) : b.size(1)) == K, "titb200 gemm_ag: reduction sizes differ");
+  Tensor X = at::empty({M, K}, b.options());
+  Tensor flags = at::empty({M / 128 + 1}, b.options().dtype(at::kInt));
+  Tensor out = at::empty({M, N}, b.options());
+  Tensor aux_out;
+  if (want_aux_out) aux_out = at::empty({M, N}, b.options());
+  std::vector<unsigned long long> pp(peer_ptrs.begin(), peer_ptrs.end());
+  TitbGemmColl c{};
+  c.mode = 1; c.world = (int)world; c.rank = (int)rank; c.helper_ctas = (int)helper_ctas;
+  c.rows_per_rank = (int)rows_per_rank; c.peer_ptrs = pp.data(); c.gathered = X.data_ptr(); c.flags = flags.data_ptr();
+  TitbGemmDesc d{};
+  d.a = X.data_ptr(); d.b = b.data_ptr(); d.out = out.data_ptr();
+  d.M = (int)M; d.N = (int)N; d.K = (int)K; d.a_mn_major = 0; d.b_mn_major = b_mn;
+  d.lda = K; d.ldb = b.stride(0); d.ldo = N; d.epilogue = (int)epilogue; d.bias = opt_ptr(bias);
+  if (want_aux_out) { d.aux_out = aux_out.data_ptr(); d.ld_aux_out = N; }
+  d.splits = 1; d.coll = &c;
+  CHECK_RC(titb_gemm_bf16(&d, cur_stream()), "gemm_ag");
+  if (want_aux_out) return {out, aux_out, X};
+  return {out, X};
+}
+
+// GEMM -> reduce-scatter.  `recv_ptrs`: every rank's receive buffer bf16 [world][Ms][N]; `cnt_ptrs`:
+// every rank's uint32 [Ms/128] counters.  Returns this rank's [Ms, N] rows of sum_r (a_r . b_r^T).
+Tensor gemm_rs(const Tensor& a, const Tensor& b, bool b_mn, const std::vector<int64_t>& recv_ptrs,
+               const std::vector<int64_t>& cnt_ptrs, int64_t rank, const optional<Tensor>& bias,
+               const optional<Tensor>& residual, int64_t helper_ctas) {
+  TORCH_CHECK(a.is_cuda() && a.scalar_type() == at::kBFloat16 && a.dim() == 2 && a.stride(1) == 1);
+  TORCH_CHECK(b.is_cuda() && b.scalar_type() == at::kBFloat16 && b.dim() == 2 && b.stride(1) == 1);
+  c10::cuda::CUDAGuard guard(a.device());
+  const int64_t world = (int64_t)recv_ptrs.size(), M = a.size(0), K = a.size(1);
+  const int64_t N = b_mn ? b.size(1) : b.size(0);
+  TORCH_CHECK((b_mn ? b.size(0) : b.size(1)) == K, "titb200 gemm_rs: reduction sizes differ");
+  TORCH_CHECK(M % world == 0, "titb200 gemm_rs: rows not divisible by the group size");
+  const int64_t Ms = M / world;
+  Tensor out = at::empty({Ms, N}, a.options());
+  std::vector<unsigned long long> rp(recv_ptrs.begin(), recv_ptrs.end()), cp(cnt_ptrs.begin(), cnt_ptrs.end());
+  TitbGemmColl c{};
+  c.mode = 2; c.world = (int)world; c.rank = (int)rank; c.helper_ctas = (int)helper_ctas; c.rows_per_rank = (int)Ms;
+  c.peer_ptrs = rp.data(); c.cnt_ptrs = cp.data(); c.flags = reinterpret_cast<void*>(cp[rank]);
+  c.rs_out = out.data_ptr(); c.rs_bias = opt_ptr(bias);
+  if (residual.has_value() && residual->defined()) {
+    TORCH_CHECK(residual->is_contiguous() && residual->numel() == Ms * N, "titb200 gemm_rs: residual must be [Ms, N]");
+    c.rs_residual = residual->data_ptr();
+  }
+  TitbGemmDesc d{};
+  d.a = a.data_ptr(); d.b = b.data_ptr(); d.out = out.data_ptr();
+  d.M = (int)M; d.N = (int)N; d.K = (int)K; d.a_mn_major = 0; d.b_mn_major = b_mn;
+  d.lda = a.stride(0); d.ldb = b.stride(0); d.ldo = N; d.splits = 1; d.coll = &c;
+  CHECK_RC(titb_gemm_bf16(&d, cur_stream()), "gemm_rs");
+  return out;
+}
+
 Tensor sgemm(const Tensor& a, const Tensor& b, bool ta, bool tb, const optional<Tensor>& out_, bool accumulate) {
   check_cuda(a, "a"); check_cuda(b, "b");
   TORCH_CHECK(a.scalar_type() == at::kFloat && b.scalar_type() == at::kFloat && a.dim() == 2 && b.dim() == 2);
@@ -456,6 +517,11 @@ PYBIND11_MODULE(_C, m) {
         py::arg("epilogue") = 0, py::arg("bias") = py::none(), py::arg("aux_in") = py::none(),
         py::arg("want_aux_out") = false, py::arg("out") = py::none(), py::arg("accumulate") = false,
         py::arg("out_fp32") = false, py::arg("tile_n") = 0, py::arg("splits") = 0, py::arg("alpha") = py::none());
+  m.def("gemm_ag", &gemm_ag, py::arg("peer_ptrs"), py::arg("rank"), py::arg("rows_per_rank"), py::arg("K"),
+        py::arg("b"), py::arg("b_mn") = false, py::arg("epilogue") = 0, py::arg("bias") = py::none(),
+        py::arg("want_aux_out") = false, py::arg("helper_ctas") = 16);
+  m.def("gemm_rs", &gemm_rs, py::arg("a"), py::arg("b"), py::arg("b_mn"), py::arg("recv_ptrs"), py::arg("cnt_ptrs"),
+        py::arg("rank"), py::arg("bias") = py::none(), py::arg("residual") = py::none(), py::arg("helper_ctas") = 8);
   m.def("sgemm", &sgemm, py::arg("a"), py::arg("b"), py::arg("ta") = false, py::arg("tb") = false,
         py::arg("out") = py::none(), py::arg("accumulate") = false);
   m.def("layernorm_fwd", &layernorm_fwd);

@@ -43,6 +43,27 @@ enum TitbEpilogue {
   TITB_EPI_SWIGLU = 5,         // reserved
 };
 
+// Optional collective fused into the GEMM (see gemm_tcgen05.cu, CollArgs).  All pointer tables are
+// host arrays of `world` device addresses as mapped on the calling GPU (symmetric memory).
+//  mode 1 (all-gather -> GEMM): A = all ranks' [rows_per_rank, K] shards; `peer_ptrs` are the shard
+//    bases, `gathered` a local [M, K] buffer that receives the gathered rows (and must be passed as
+//    TitbGemmDesc::a), `flags` a local uint32 [M / 128] array.
+//  mode 2 (GEMM -> reduce-scatter): `peer_ptrs` are the receive buffers bf16 [world][rows_per_rank][N],
+//    `cnt_ptrs` the per-rank counter arrays uint32 [rows_per_rank / 128] (zero before first use),
+//    `flags` this rank's own counter array, `rs_out` the [rows_per_rank, N] result (+bias +residual).
+//    TitbGemmDesc::out is unused.
+// A cross-GPU barrier (titb_comm_barrier) must separate the writes of the peers' inputs from this call.
+struct TitbGemmColl {
+  int mode, world, rank, helper_ctas, rows_per_rank;
+  const unsigned long long* peer_ptrs;
+  const unsigned long long* cnt_ptrs;
+  void* gathered;
+  void* flags;
+  void* rs_out;
+  const void* rs_bias;
+  const void* rs_residual;
+};
+
 struct TitbGemmDesc {
   const void* a;        // bf16
   const void* b;        // bf16
@@ -62,6 +83,7 @@ struct TitbGemmDesc {
   void* workspace;      // fp32 [splits, M, N] scratch when splits > 1
   int tile_n;           // 0 = heuristic, else 128 or 256
   const void* alpha;    // optional device fp32 scalar: result = alpha * (A . B^T) before the epilogue
+  const TitbGemmColl* coll;  // optional fused collective, or null
 };
 TITB_API int titb_gemm_bf16(const TitbGemmDesc* d, cudaStream_t stream);
 // Picks the split-K factor the heuristic would use (so callers can size the workspace).

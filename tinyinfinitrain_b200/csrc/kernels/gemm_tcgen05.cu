@@ -25,7 +25,28 @@ constexpr int kBK = 64;
 constexpr int kABytes = kBM * kBK * 2;
 constexpr int kGemmThreads = 192;
 
+// Collective fused into the GEMM (tensor parallelism with sequence-sharded activations).
+//  mode 1, all-gather -> GEMM: the first `helper_ctas` CTAs copy 128-row chunks of every rank's
+//    activation shard from peer memory (plain loads over NVLink) into the local `gathered`
+//    buffer and raise a per-chunk flag; the GEMM CTAs visit m-blocks in the same order (local
+//    shard first) and their TMA producer waits on the flag of the chunk it is about to load.
+//  mode 2, GEMM -> reduce-scatter: the epilogue stores each bf16 partial tile straight into the
+//    receive buffer of the rank that owns those rows (peer stores over NVLink) and bumps a
+//    counter there; the first `helper_ctas` CTAs of the owner wait per 128-row chunk for all
+//    partial tiles, sum the `world` slots (+bias +residual) and write the output shard.
+struct CollArgs {
+  int mode, world, rank, helper_ctas, rows_per_rank;
+  void* peers[16];      // mode 1: shard bases bf16 [Ms, K]; mode 2: receive buffers bf16 [world][Ms][N]
+  void* cnt_peers[16];  // mode 2: counter arrays uint32 [Ms / 128] of every rank
+  bf16* gathered;       // mode 1: local [M, K] staging buffer (the GEMM's A operand)
+  uint32_t* flags;      // mode 1: local chunk flags [M / 128]; mode 2: this rank's counters
+  bf16* rs_out;         // mode 2: output shard [Ms, N]
+  const bf16* rs_bias;
+  const bf16* rs_residual;
+};
+
 struct GemmArgs {
+  CollArgs coll;
   int M, N, K;
   int a_mn, b_mn;
   void* out;
@@ -192,6 +213,134 @@ __device__ __forceinline__ void epilogue_row32(const GemmArgs& p, float (&v)[32]
   }
 }
 
+struct TileCoord { int m0, n0, split, mblk; };
+
+__device__ __forceinline__ TileCoord tile_coord(const GemmArgs& p, int tile, int tiles_m, int tiles_n, int bn) {
+  const int tiles_mn = tiles_m * tiles_n;
+  TileCoord t;
+  t.split = tile / tiles_mn;
+  const int mn = tile - t.split * tiles_mn;
+  int nblk;
+  if (p.coll.mode == 0) {
+    t.mblk = mn % tiles_m;
+    nblk = mn / tiles_m;
+  } else {
+    // m-blocks are visited shard by shard: all-gather starts with the local shard (already here),
+    // reduce-scatter with the next rank's rows so that remote partials leave early.
+    const int cpr = p.coll.rows_per_rank / kBM;
+    const int start = (p.coll.mode == 1 ? p.coll.rank : p.coll.rank + 1) * cpr;
+    t.mblk = (mn / tiles_n + start) % tiles_m;
+    nblk = mn % tiles_n;
+  }
+  t.m0 = t.mblk * kBM;
+  t.n0 = nblk * bn;
+  return t;
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* a) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(a) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* a) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(a) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu_u32(uint32_t* a, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(a), "r"(v) : "memory");
+}
+__device__ __forceinline__ void red_release_sys_add_u32(uint32_t* a, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(a), "r"(v) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+// Bounded spin until *flag >= want (acquire at `sys` or `gpu` scope); false on timeout.
+template <bool SYS>
+__device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t want) {
+  const long long t0 = clock64();
+  while (true) {
+    const uint32_t v = SYS ? ld_acquire_sys_u32(flag) : ld_acquire_gpu_u32(flag);
+    if (v >= want) return true;
+    __nanosleep(32);
+    if (clock64() - t0 > ptx::kWaitBudgetCycles) return false;
+  }
+}
+
+// mode 1 helper CTA: pull 128-row chunks of every rank's shard into the local gathered buffer.
+__device__ void ag_copy_role(const GemmArgs& p) {
+  const CollArgs& c = p.coll;
+  const int nchunks = p.M / kBM, cpr = c.rows_per_rank / kBM;
+  const long long vec_per_chunk = static_cast<long long>(kBM) * p.K / 8;  // 16-byte units
+  for (int pos = blockIdx.x; pos < nchunks; pos += c.helper_ctas) {
+    const int mblk = (pos + c.rank * cpr) % nchunks;
+    const int src_rank = mblk / cpr;
+    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const bf16*>(c.peers[src_rank]) +
+                                                      static_cast<long long>(mblk - src_rank * cpr) * kBM * p.K);
+    uint4* dst = reinterpret_cast<uint4*>(c.gathered + static_cast<long long>(mblk) * kBM * p.K);
+    long long i = threadIdx.x;
+    for (; i + 3 * kGemmThreads < vec_per_chunk; i += 4 * kGemmThreads) {
+      const uint4 v0 = src[i], v1 = src[i + kGemmThreads], v2 = src[i + 2 * kGemmThreads], v3 = src[i + 3 * kGemmThreads];
+      dst[i] = v0; dst[i + kGemmThreads] = v1; dst[i + 2 * kGemmThreads] = v2; dst[i + 3 * kGemmThreads] = v3;
+    }
+    for (; i < vec_per_chunk; i += kGemmThreads) dst[i] = src[i];
+    fence_proxy_async_all();  // these generic-proxy writes are read by TMA (async proxy) below
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) st_release_gpu_u32(c.flags + mblk, 1u);
+  }
+}
+
+// mode 2 helper CTA: sum the `world` partial slots of this rank's row chunks as they complete.
+__device__ void rs_reduce_role(const GemmArgs& p, int tiles_n) {
+  const CollArgs& c = p.coll;
+  __shared__ int ok_sh;
+  const int cpr = c.rows_per_rank / kBM;
+  const uint32_t expected = static_cast<uint32_t>(c.world * tiles_n * 4);  // 4 epilogue warps per tile
+  const bf16* recv = static_cast<const bf16*>(c.peers[c.rank]);
+  const long long slot = static_cast<long long>(c.rows_per_rank) * p.N;
+  const int nv = p.N / 8;
+  for (int ch = blockIdx.x; ch < cpr; ch += c.helper_ctas) {
+    if (threadIdx.x == 0) {
+      ok_sh = wait_flag_ge<true>(c.flags + ch, expected) ? 1 : 0;
+      if (!ok_sh) atomicExch(p.status, kStatusPeerTimeout);
+    }
+    __syncthreads();
+    if (ok_sh) {
+      for (int i = threadIdx.x; i < kBM * nv; i += kGemmThreads) {
+        const int r = ch * kBM + i / nv, col = (i % nv) * 8;
+        const long long off = static_cast<long long>(r) * p.N + col;
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int s = 0; s < c.world; ++s) {
+          const uint4 u = *reinterpret_cast<const uint4*>(recv + s * slot + off);
+          const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
+          acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
+          acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+        }
+        if (c.rs_bias != nullptr) {
+          const uint4 u = *reinterpret_cast<const uint4*>(c.rs_bias + col);
+          const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
+          acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
+          acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+        }
+        if (c.rs_residual != nullptr) {
+          const uint4 u = *reinterpret_cast<const uint4*>(c.rs_residual + off);
+          const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
+          acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
+          acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+        }
+        *reinterpret_cast<uint4*>(c.rs_out + off) =
+            make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
+                       pack_bf16x2(acc[6], acc[7]));
+      }
+    }
+    __syncthreads();
+    // Every partial of this chunk has arrived, so the counter can be cleared for the next call:
+    // peers only start the next call's stores after a cross-GPU barrier that follows this kernel.
+    if (threadIdx.x == 0) { c.flags[ch] = 0u; __threadfence_system(); }
+  }
+}
+
 template <int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
@@ -199,6 +348,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   using Cfg = GemmCfg<BN>;
   constexpr int kStages = Cfg::kStages;
   constexpr int kBBytes = Cfg::kBBytes;
+
+  // Leading CTAs of a fused-collective launch do the copy / reduction instead of GEMM tiles.
+  const int helpers = p.coll.mode ? p.coll.helper_ctas : 0;
+  if (static_cast<int>(blockIdx.x) < helpers) {
+    if (p.coll.mode == 1) ag_copy_role(p);
+    else rs_reduce_role(p, (p.N + BN - 1) / BN);
+    return;
+  }
+  const int cta = static_cast<int>(blockIdx.x) - helpers;
+  const int ncta = static_cast<int>(gridDim.x) - helpers;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -249,13 +408,23 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int split = tile / tiles_mn;
-        const int mn = tile - split * tiles_mn;
-        const int m0 = (mn % tiles_m) * kBM;
-        const int n0 = (mn / tiles_m) * BN;
+      int ready_mblk = -1;
+      for (int tile = cta; tile < num_tiles && ok; tile += ncta) {
+        const TileCoord tc = tile_coord(p, tile, tiles_m, tiles_n, BN);
+        const int split = tc.split, m0 = tc.m0, n0 = tc.n0;
         const int kb0 = split * p.kb_per_split;
         const int kb1 = min(num_kb_total, kb0 + p.kb_per_split);
+        if (p.coll.mode == 1 && tc.mblk != ready_mblk) {
+          // the rows of this m-block must have landed in the gathered buffer
+          if (!wait_flag_ge<false>(p.coll.flags + tc.mblk, 1u)) {
+            *abort_flag = 1u;
+            atomicExch(p.status, kStatusPeerTimeout);
+            ok = false;
+            break;
+          }
+          fence_proxy_async_all();
+          ready_mblk = tc.mblk;
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!ptx::mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
           ptx::mbar_expect_tx(&full[stage], kABytes + kBBytes);
@@ -296,7 +465,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      for (int tile = cta; tile < num_tiles && ok; tile += ncta, ++it) {
         const int split = tile / tiles_mn;
         const int kb0 = split * p.kb_per_split;
         const int kb1 = min(num_kb_total, kb0 + p.kb_per_split);
@@ -326,11 +495,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     // ---------------------------------------------------------------- epilogue
     const int quad = warp & 3;  // TMEM lane quarter this warp may read
     int it = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
-      const int split = tile / tiles_mn;
-      const int mn = tile - split * tiles_mn;
-      const int m0 = (mn % tiles_m) * kBM;
-      const int n0 = (mn / tiles_m) * BN;
+    for (int tile = cta; tile < num_tiles; tile += ncta, ++it) {
+      const TileCoord tc = tile_coord(p, tile, tiles_m, tiles_n, BN);
+      const int split = tc.split, m0 = tc.m0, n0 = tc.n0;
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       if (!ptx::mbar_wait(&acc_full[buf], acc_phase, abort_flag)) break;
@@ -347,12 +514,39 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
           float v[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-          epilogue_row32(p, v, row, col0, split);
+          if (p.coll.mode == 2) {
+            // partial tile -> slot [this rank] of the owning rank's receive buffer (peer store)
+            const int owner = static_cast<int>(row / p.coll.rows_per_rank);
+            const long long lrow = row - static_cast<long long>(owner) * p.coll.rows_per_rank;
+            bf16* dst = static_cast<bf16*>(p.coll.peers[owner]) +
+                        (static_cast<long long>(p.coll.rank) * p.coll.rows_per_rank + lrow) * p.N + col0;
+            const int ncols = min(32, p.N - col0);
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (j < ncols)
+                *reinterpret_cast<uint4*>(dst + j) =
+                    make_uint4(pack_bf16x2(v[j], v[j + 1]), pack_bf16x2(v[j + 2], v[j + 3]),
+                               pack_bf16x2(v[j + 4], v[j + 5]), pack_bf16x2(v[j + 6], v[j + 7]));
+            }
+          } else {
+            epilogue_row32(p, v, row, col0, split);
+          }
         }
       }
       ptx::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
+      if (p.coll.mode == 2) {
+        // this warp's 32 rows of the tile are on their way: publish them to the owner (the owner
+        // expects four such arrivals per tile, one per epilogue warp)
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+          const int owner = m0 / p.coll.rows_per_rank;
+          const int chunk = (m0 - owner * p.coll.rows_per_rank) / kBM;
+          red_release_sys_add_u32(static_cast<uint32_t*>(p.coll.cnt_peers[owner]) + chunk, 1u);
+        }
+      }
     }
   }
 
@@ -506,7 +700,9 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmA
     attr_set[dev] = true;
   }
   const int tiles = ((args.M + kBM - 1) / kBM) * ((args.N + BN - 1) / BN) * args.splits;
-  const int grid = tiles < device_sm_count() ? tiles : device_sm_count();
+  const int helpers = args.coll.mode ? args.coll.helper_ctas : 0;
+  int grid = tiles + helpers < device_sm_count() ? tiles + helpers : device_sm_count();
+  if (grid <= helpers) return TITB_ERR_SHAPE;
   gemm_bf16_tcgen05_kernel<BN><<<grid, kGemmThreads, Cfg::kSmem, stream>>>(ta, tb, args);
   return static_cast<int>(cudaGetLastError());
 }
@@ -532,7 +728,7 @@ TITB_API int titb_gemm_bf16(const TitbGemmDesc* d, cudaStream_t stream) {
   else ok = ok && make_tmap_bf16_2d(&tb, d->b, d->N, d->K, d->ldb, 64, kBK);
   if (!ok) return TITB_ERR_TENSOR_MAP;
 
-  GemmArgs a;
+  GemmArgs a{};
   a.M = d->M; a.N = d->N; a.K = d->K;
   a.a_mn = d->a_mn_major ? 1 : 0;
   a.b_mn = d->b_mn_major ? 1 : 0;
@@ -560,6 +756,29 @@ TITB_API int titb_gemm_bf16(const TitbGemmDesc* d, cudaStream_t stream) {
   a.alpha = static_cast<const float*>(d->alpha);
   a.status = titb_status_ptr();
   if (!a.status) return static_cast<int>(cudaErrorMemoryAllocation);
+  if (d->coll != nullptr && d->coll->mode != 0) {
+    const TitbGemmColl* c = d->coll;
+    if (c->world < 1 || c->world > 16 || c->rows_per_rank % kBM || d->M != c->rows_per_rank * c->world || splits != 1 ||
+        (d->N & 7) || (d->K & 7) || c->helper_ctas < 1)
+      return TITB_ERR_SHAPE;
+    if (c->mode == 2 && (d->epilogue != TITB_EPI_NONE || d->accumulate || d->alpha)) return TITB_ERR_SHAPE;
+    a.coll.mode = c->mode; a.coll.world = c->world; a.coll.rank = c->rank;
+    a.coll.helper_ctas = c->helper_ctas; a.coll.rows_per_rank = c->rows_per_rank;
+    for (int i = 0; i < c->world; ++i) {
+      a.coll.peers[i] = reinterpret_cast<void*>(c->peer_ptrs[i]);
+      a.coll.cnt_peers[i] = c->cnt_ptrs ? reinterpret_cast<void*>(c->cnt_ptrs[i]) : nullptr;
+    }
+    a.coll.gathered = static_cast<bf16*>(c->gathered);
+    a.coll.flags = static_cast<uint32_t*>(c->flags);
+    a.coll.rs_out = static_cast<bf16*>(c->rs_out);
+    a.coll.rs_bias = static_cast<const bf16*>(c->rs_bias);
+    a.coll.rs_residual = static_cast<const bf16*>(c->rs_residual);
+    if (c->mode == 1) {
+      // chunk flags start at 0 for every launch (stream-ordered, capturable)
+      cudaError_t e = cudaMemsetAsync(c->flags, 0, sizeof(uint32_t) * (d->M / kBM), stream);
+      if (e != cudaSuccess) return static_cast<int>(e);
+    }
+  }
 
   int rc = (bn == 256) ? launch_gemm<256>(ta, tb, a, stream) : launch_gemm<128>(ta, tb, a, stream);
   if (rc != 0) return rc;

@@ -211,6 +211,7 @@ class TPTransformer(nn.Module):
     def forward(self, idx_or_x, targets=None, B: Optional[int] = None, T: Optional[int] = None):
         """First stage: ``idx`` int64 [B, T]; later stages: the previous stage's token shard plus B, T.
         Last stage with ``targets`` returns the loss, otherwise the token shard is returned."""
+        self.comm.new_step()
         if self.first:
             B, T = idx_or_x.shape
             x_s = self.embed(idx_or_x)

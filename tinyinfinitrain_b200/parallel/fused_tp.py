@@ -1,0 +1,101 @@
+"""Fused tensor-parallel collectives: all-gather -> GEMM and GEMM -> reduce-scatter in one kernel.
+
+Buffers live in symmetric (peer-mapped) memory, allocated once per shape and reused.  Each fused
+call is preceded by one device-side barrier, which both publishes the peers' inputs and proves
+that every rank has finished reading what the previous call left in the shared buffers; a second
+barrier is inserted only when a buffer would otherwise be rewritten with no barrier since it
+was last read (first use in a step, or two consecutive calls on the same buffer).
+"""
+from __future__ import annotations
+
+from typing import Dict, Tuple
+
+import torch
+
+from .._lib import C
+from ..ops import functional as F_
+from .symm import DeviceBarrier, SymmetricBuffer
+
+
+class FusedTP:
+    AG_HELPERS = 16   # CTAs that pull peer shards over NVLink while the rest run GEMM tiles
+    RS_HELPERS = 8    # CTAs that reduce arriving partial tiles
+
+    def __init__(self, comm):
+        self.comm = comm
+        self.world, self.rank, self.group = comm.world, comm.rank, comm.group
+        self._ag: Dict[int, SymmetricBuffer] = {}
+        self._rs: Dict[Tuple[int, int], Tuple[SymmetricBuffer, SymmetricBuffer]] = {}
+        self._barrier = None
+        self._nbar = 0
+        self._last_read: Dict[object, int] = {}
+
+    # ---- bookkeeping -----------------------------------------------------------------------
+    def new_step(self) -> None:
+        """Forget what is known about barriers since each buffer was last read (call at the start of
+        a step: a captured graph replays from here, so the first use must assume nothing)."""
+        self._last_read.clear()
+
+    def _bar(self, dev) -> None:
+        if self._barrier is None:
+            anchor = SymmetricBuffer(1024, torch.float32, dev, self.group)
+            self._barrier = DeviceBarrier(anchor, channel=1)
+        self._barrier()
+        self._nbar += 1
+
+    def _ag_buf(self, numel: int, dev) -> SymmetricBuffer:
+        b = self._ag.get(numel)
+        if b is None:
+            b = self._ag[numel] = SymmetricBuffer(numel, torch.bfloat16, dev, self.group)
+        return b
+
+    def _rs_buf(self, Ms: int, N: int, dev):
+        key = (Ms, N)
+        b = self._rs.get(key)
+        if b is None:
+            recv = SymmetricBuffer(self.world * Ms * N, torch.bfloat16, dev, self.group)
+            cnt = SymmetricBuffer(max(128, Ms // 128 + 1), torch.int32, dev, self.group)
+            cnt.tensor.zero_()
+            torch.cuda.synchronize(dev)
+            b = self._rs[key] = (recv, cnt)
+        return b
+
+    # ---- all-gather -> GEMM ---------------------------------------------------------------------
+    def ag_gemm(self, x_s, w, bias=None, gelu=False, b_mn=False):
+        Ms, K = x_s.shape
+        N = w.shape[1] if b_mn else w.shape[0]
+        if Ms % 128 or K % 8 or N % 8:
+            X = self.comm.all_gather_rows(x_s)
+            from .tp import _local_gemm
+
+            return _local_gemm(X, w, bias, gelu, b_mn) + (X,)
+        dev = x_s.device
+        buf = self._ag_buf(Ms * K, dev)
+        key = ("ag", Ms * K)
+        if self._last_read.get(key, 1 << 60) >= self._nbar:
+            self._bar(dev)                       # peers may still be reading this buffer
+        buf.tensor.view(Ms, K).copy_(x_s)
+        self._bar(dev)                           # every shard is written
+        epi = F_.EPI_BIAS_GELU if gelu else (F_.EPI_BIAS if bias is not None else F_.EPI_NONE)
+        out = C.gemm_ag(buf.ptrs, self.rank, Ms, K, w, b_mn, epi, bias, gelu, self.AG_HELPERS)
+        self._last_read[key] = self._nbar
+        return tuple(out)
+
+    # ---- GEMM -> reduce-scatter ------------------------------------------------------------------
+    def gemm_rs(self, y, w, b_mn=False, bias=None, residual_s=None):
+        M, K = y.shape
+        N = w.shape[1] if b_mn else w.shape[0]
+        Ms = M // self.world
+        if M % self.world or Ms % 128 or K % 8 or N % 8 or not y.is_contiguous():
+            Z = C.gemm(y.contiguous(), w, False, b_mn)[0]
+            z_s = self.comm.reduce_scatter_rows(Z)
+            if bias is not None:
+                z_s = z_s + bias
+            if residual_s is not None:
+                z_s = z_s + residual_s
+            return z_s
+        dev = y.device
+        recv, cnt = self._rs_buf(Ms, N, dev)
+        self._bar(dev)                           # every rank has consumed the previous contents of its receive buffer
+        res = residual_s.contiguous() if residual_s is not None else None
+        return C.gemm_rs(y, w, b_mn, recv.ptrs, cnt.ptrs, self.rank, bias, res, min(self.RS_HELPERS, Ms // 128))

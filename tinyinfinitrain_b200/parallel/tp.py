@@ -47,6 +47,10 @@ class TPComm:
 
             self._fused = FusedTP(self)
 
+    def new_step(self) -> None:
+        if self._fused is not None:
+            self._fused.new_step()
+
     # ---- unfused collectives on row-sharded 2-D tensors --------------------------------------
     def all_gather_rows(self, x_s: torch.Tensor) -> torch.Tensor:
         if self.world == 1:
