@@ -30,7 +30,10 @@ KERNEL_LIB = PKG / "libtitb200_kernels.so"
 CORE_LIB = PKG / "_C.so"
 
 NVCC = os.environ.get("NVCC", shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc")
-CXX = os.environ.get("CXX", "g++")
+# The distribution's own g++ is used on purpose (override with TITB200_CXX): a toolchain wrapper found
+# through $CXX on some images links parts of a static libstdc++ into the module, whose iostream state
+# is then never initialised inside the Python process.
+CXX = os.environ.get("TITB200_CXX") or ("/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++")
 CUDA_HOME = Path(NVCC).resolve().parent.parent
 
 NVCC_FLAGS = [

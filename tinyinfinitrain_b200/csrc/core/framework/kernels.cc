@@ -1,0 +1,424 @@
+// Kernel functions behind the facade's Dispatcher, registered under the reference's names
+// ("LinearForward", "AdamAccumulateGrad", ...) for both device types.
+//
+// CPU tensors: ATen fp32 math restating infini_train/src/kernels/cpu/*.cc (the numerical oracle).
+// CUDA float32/bfloat16 tensors: the sm_100a kernel library (tcgen05 GEMM for bf16 Linear/Matmul,
+// the SIMT SGEMM for fp32, fused LayerNorm / softmax / cross-entropy / embedding / Adam kernels);
+// the remaining layout ops are views or ATen copies.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+
+#include <cmath>
+#include <tuple>
+
+#include "core/framework/dispatcher.h"
+#include "kernels/api.h"
+
+namespace infini_train::kernels {
+
+using TP = std::shared_ptr<Tensor>;
+static TP W(at::Tensor t) { return std::make_shared<Tensor>(t.contiguous()); }
+static bool native(const at::Tensor& t) {
+  return t.is_cuda() && (t.scalar_type() == at::kFloat || t.scalar_type() == at::kBFloat16);
+}
+static int dt(const at::Tensor& t) { return t.scalar_type() == at::kBFloat16 ? 1 : 0; }
+static cudaStream_t stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+static void ok(int rc, const char* what) { TORCH_CHECK(rc == 0, "kernel ", what, " failed with code ", rc); }
+
+// ---- accumulate / optimizers ------------------------------------------------------------------------
+void AccumulateGrad(const TP& gradient, float rate, const TP& tensor) {
+  at::Tensor& t = tensor->data();
+  const at::Tensor& g = gradient->data();
+  if (t.is_cuda() && t.scalar_type() == at::kFloat && native(g) && t.is_contiguous() && g.is_contiguous()) {
+    c10::cuda::CUDAGuard guard(t.device());
+    ok(titb_axpy(t.data_ptr<float>(), g.data_ptr(), rate, t.numel(), dt(g), stream()), "AccumulateGrad");
+    return;
+  }
+  t.add_(g.to(t.scalar_type()), rate);
+}
+
+void AdamAccumulateGrad(const TP& grad, const TP& param, const TP& m, const TP& v, float learning_rate, float beta1,
+                        float beta2, float eps, int64_t t) {
+  at::Tensor& p = param->data();
+  const at::Tensor& g = grad->data();
+  const double bc1 = 1.0 - std::pow(beta1, static_cast<double>(t)), bc2 = 1.0 - std::pow(beta2, static_cast<double>(t));
+  if (p.is_cuda() && p.scalar_type() == at::kFloat && g.scalar_type() == at::kFloat && p.is_contiguous()) {
+    c10::cuda::CUDAGuard guard(p.device());
+    ok(titb_adam_flat(p.data_ptr<float>(), nullptr, g.data_ptr<float>(), m->data().data_ptr<float>(),
+                      v->data().data_ptr<float>(), p.numel(), learning_rate, beta1, beta2, eps, 0.f, (float)bc1,
+                      (float)bc2, 1.f, 0, nullptr, stream()), "AdamAccumulateGrad");
+    return;
+  }
+  at::Tensor gf = g.to(at::kFloat);
+  m->data().mul_(beta1).add_(gf, 1.0 - beta1);
+  v->data().mul_(beta2).addcmul_(gf, gf, 1.0 - beta2);
+  at::Tensor mh = m->data() / bc1, vh = v->data() / bc2;
+  p.sub_((mh / (vh.sqrt() + eps)).mul_(learning_rate).to(p.scalar_type()));
+}
+
+void Fill(const TP& tensor, void* value_ptr) { tensor->data().fill_(*static_cast<float*>(value_ptr)); }
+
+// ---- unary elementwise ------------------------------------------------------------------------------------
+static TP unary(int op, const TP& x, float s, at::Tensor (*ref)(const at::Tensor&, float)) {
+  const at::Tensor& a = x->data();
+  if (native(a) && a.is_contiguous()) {
+    c10::cuda::CUDAGuard guard(a.device());
+    at::Tensor y = at::empty_like(a);
+    ok(titb_unary_fwd(op, a.data_ptr(), y.data_ptr(), a.numel(), s, dt(a), stream()), "unary");
+    return W(y);
+  }
+  return W(ref(a, s));
+}
+static TP unary_bwd(int op, const TP& dy, const TP& saved, float s, at::Tensor (*ref)(const at::Tensor&, const at::Tensor&, float)) {
+  const at::Tensor& g = dy->data();
+  const at::Tensor& sv = saved ? saved->data() : g;
+  if (native(g) && g.is_contiguous() && sv.is_contiguous() && sv.scalar_type() == g.scalar_type()) {
+    c10::cuda::CUDAGuard guard(g.device());
+    at::Tensor dx = at::empty_like(g);
+    ok(titb_unary_bwd(op, g.data_ptr(), sv.data_ptr(), dx.data_ptr(), g.numel(), s, dt(g), stream()), "unary_bwd");
+    return W(dx);
+  }
+  return W(ref(g, sv, s));
+}
+#define UNARY_KERNEL(Name, OP, FWD, BWD)                                                                          \
+  TP Name##Forward(const TP& x) { return unary(OP, x, 0.f, [](const at::Tensor& a, float) -> at::Tensor { return FWD; }); } \
+  TP Name##Backward(const TP& dy, const TP& saved) {                                                              \
+    return unary_bwd(OP, dy, saved, 0.f, [](const at::Tensor& g, const at::Tensor& a, float) -> at::Tensor { return BWD; }); \
+  }
+UNARY_KERNEL(Neg, TITB_NEG, -a, -g + 0 * a)
+UNARY_KERNEL(Reciprocal, TITB_RECIPROCAL, a.reciprocal(), -g / (a * a))
+UNARY_KERNEL(Sin, TITB_SIN, a.sin(), g * a.cos())
+UNARY_KERNEL(Cos, TITB_COS, a.cos(), -g * a.sin())
+UNARY_KERNEL(Tanh, TITB_TANH, a.tanh(), g * (1 - a * a))          // saved = output
+UNARY_KERNEL(Rsqrt, TITB_RSQRT, a.rsqrt(), g * (-0.5 / (a * a.sqrt())))
+UNARY_KERNEL(Sigmoid, TITB_SIGMOID, a.sigmoid(), g * a * (1 - a))  // saved = output
+
+TP PowForward(const TP& x, float e, bool scalar_is_base) {
+  return unary(scalar_is_base ? TITB_POW_SCALAR_BASE : TITB_POW_SCALAR_EXP, x, e,
+               scalar_is_base ? +[](const at::Tensor& a, float s) -> at::Tensor { return at::pow(s, a); }
+                              : +[](const at::Tensor& a, float s) -> at::Tensor { return a.pow(s); });
+}
+TP PowBackward(const TP& dy, const TP& x, float e, bool scalar_is_base) {
+  return unary_bwd(scalar_is_base ? TITB_POW_SCALAR_BASE : TITB_POW_SCALAR_EXP, dy, x, e,
+                   scalar_is_base
+                       ? +[](const at::Tensor& g, const at::Tensor& a, float s) -> at::Tensor { return g * std::log(s) * at::pow(s, a); }
+                       : +[](const at::Tensor& g, const at::Tensor& a, float s) -> at::Tensor { return g * s * a.pow(s - 1); });
+}
+TP EqualsScalarForward(const TP& x, float s) {
+  return unary(TITB_EQUALS_SCALAR, x, s, [](const at::Tensor& a, float v) -> at::Tensor { return (a == v).to(a.scalar_type()); });
+}
+TP AddScalarForward(const TP& x, float s) {
+  return unary(TITB_ADD_SCALAR, x, s, [](const at::Tensor& a, float v) -> at::Tensor { return a + v; });
+}
+TP AddScalarBackward(const TP& dy) { return W(dy->data().clone()); }
+TP MulScalarForward(const TP& x, float s) {
+  return unary(TITB_MUL_SCALAR, x, s, [](const at::Tensor& a, float v) -> at::Tensor { return a * v; });
+}
+TP MulScalarBackward(const TP& dy, float s) {
+  return unary(TITB_MUL_SCALAR, dy, s, [](const at::Tensor& a, float v) -> at::Tensor { return a * v; });
+}
+
+// ---- binary elementwise: result has a's shape, b broadcast right-aligned --------------------------------------------
+static at::Tensor reduce_to(at::Tensor g, const std::vector<int64_t>& dims) {
+  while (g.dim() > static_cast<int64_t>(dims.size())) g = g.sum(0);
+  for (size_t d = 0; d < dims.size(); ++d)
+    if (dims[d] == 1 && g.size(d) != 1) g = g.sum(static_cast<int64_t>(d), true);
+  return g.contiguous();
+}
+static TP binary(int op, const TP& a, const TP& b) {
+  const at::Tensor &x = a->data(), &y = b->data();
+  TORCH_CHECK(x.numel() % std::max<int64_t>(1, y.numel()) == 0, "binary op: b does not broadcast to a");
+  switch (op) {
+    case 0: return W(x + y);
+    case 1: return W(x - y);
+    case 2: return W(x * y);
+    default: return W(x / y);
+  }
+}
+TP AddForward(const TP& a, const TP& b) { return binary(0, a, b); }
+TP SubForward(const TP& a, const TP& b) { return binary(1, a, b); }
+TP MulForward(const TP& a, const TP& b) { return binary(2, a, b); }
+TP DivForward(const TP& a, const TP& b) { return binary(3, a, b); }
+std::pair<TP, TP> AddBackward(const TP& dy, const std::vector<int64_t>& a_dims, const std::vector<int64_t>& b_dims) {
+  return {W(dy->data().clone()), W(reduce_to(dy->data(), b_dims))};
+}
+std::pair<TP, TP> SubBackward(const TP& dy, const std::vector<int64_t>& a_dims, const std::vector<int64_t>& b_dims) {
+  return {W(dy->data().clone()), W(reduce_to(-dy->data(), b_dims))};
+}
+std::pair<TP, TP> MulBackward(const TP& dy, const TP& a, const TP& b) {
+  return {W(dy->data() * b->data()), W(reduce_to(dy->data() * a->data(), b->Dims()))};
+}
+std::pair<TP, TP> DivBackward(const TP& dy, const TP& a, const TP& b) {
+  const at::Tensor &g = dy->data(), &x = a->data(), &y = b->data();
+  return {W(g / y), W(reduce_to(-g * x / (y * y), b->Dims()))};
+}
+
+// ---- GEMM family ------------------------------------------------------------------------------------------------
+// D[M,N] = A op B for 2-D row-major operands; ta/tb select the transposed reading of the stored matrix.
+static at::Tensor gemm2d(const at::Tensor& a_, const at::Tensor& b_, bool ta, bool tb) {
+  at::Tensor a = a_.contiguous(), b = b_.contiguous();
+  const int64_t M = ta ? a.size(1) : a.size(0), K = ta ? a.size(0) : a.size(1), N = tb ? b.size(0) : b.size(1);
+  if (a.is_cuda() && a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && (K % 8 == 0) &&
+      ((ta ? M : K) % 8 == 0) && ((tb ? K : N) % 8 == 0)) {
+    c10::cuda::CUDAGuard guard(a.device());
+    at::Tensor out = at::empty({M, N}, a.options());
+    TitbGemmDesc d{};
+    d.a = a.data_ptr(); d.b = b.data_ptr(); d.out = out.data_ptr();
+    d.M = (int)M; d.N = (int)N; d.K = (int)K;
+    d.a_mn_major = ta;         // stored [K, M]
+    d.b_mn_major = !tb;        // stored [K, N]
+    d.lda = a.stride(0); d.ldb = b.stride(0); d.ldo = N; d.splits = 1;
+    ok(titb_gemm_bf16(&d, stream()), "gemm_bf16");
+    return out;
+  }
+  if (a.is_cuda() && a.scalar_type() == at::kFloat && b.scalar_type() == at::kFloat) {
+    c10::cuda::CUDAGuard guard(a.device());
+    at::Tensor out = at::empty({M, N}, a.options());
+    ok(titb_sgemm(a.data_ptr<float>(), b.data_ptr<float>(), out.data_ptr<float>(), (int)M, (int)N, (int)K, ta, tb, 0,
+                  stream()), "sgemm");
+    return out;
+  }
+  return at::matmul(ta ? a.t() : a, tb ? b.t() : b);
+}
+
+TP MatmulForward(const TP& a, const TP& b) {
+  const at::Tensor &x = a->data(), &y = b->data();
+  if (x.dim() == 2 && y.dim() == 2) return W(gemm2d(x, y, false, false));
+  const int64_t M = x.size(-2), K = x.size(-1), N = y.size(-1);
+  at::Tensor x3 = x.reshape({-1, M, K}), y3 = y.reshape({-1, K, N});
+  TORCH_CHECK(x3.size(0) == y3.size(0), "Matmul: both operands must carry the same batch dims");
+  std::vector<at::Tensor> outs;
+  for (int64_t i = 0; i < x3.size(0); ++i) outs.push_back(gemm2d(x3[i], y3[i], false, false));
+  auto shape = x.sizes().vec();
+  shape.back() = N;
+  return W(at::stack(outs).reshape(shape));
+}
+std::pair<TP, TP> MatmulBackward(const TP& a, const TP& b, const TP& dc) {
+  const at::Tensor &x = a->data(), &y = b->data(), &g = dc->data();
+  const int64_t M = x.size(-2), K = x.size(-1), N = y.size(-1);
+  at::Tensor x3 = x.reshape({-1, M, K}), y3 = y.reshape({-1, K, N}), g3 = g.reshape({-1, M, N});
+  std::vector<at::Tensor> da, db;
+  for (int64_t i = 0; i < x3.size(0); ++i) {
+    da.push_back(gemm2d(g3[i], y3[i], false, true));   // dA = dC B^T
+    db.push_back(gemm2d(x3[i], g3[i], true, false));   // dB = A^T dC
+  }
+  return {W(at::stack(da).reshape(x.sizes())), W(at::stack(db).reshape(y.sizes()))};
+}
+
+// y = x W^T + b when transpose (weight [out, in]) else x W + b (weight [in, out]).
+TP LinearForward(const TP& input, const TP& weight, bool transpose, const TP& bias) {
+  const at::Tensor& x = input->data();
+  at::Tensor x2 = x.reshape({-1, x.size(-1)});
+  at::Tensor y = gemm2d(x2, weight->data(), false, transpose);
+  if (bias) y = y + bias->data();
+  auto shape = x.sizes().vec();
+  shape.back() = y.size(1);
+  return W(y.reshape(shape));
+}
+std::tuple<TP, TP, TP> LinearBackward(const TP& input, const TP& weight, bool transpose, int64_t out_features,
+                                      const TP& grad_output, bool has_bias) {
+  const at::Tensor &x = input->data(), &w = weight->data(), &g = grad_output->data();
+  at::Tensor x2 = x.reshape({-1, x.size(-1)}), g2 = g.reshape({-1, out_features});
+  at::Tensor dx = gemm2d(g2, w, false, !transpose).reshape(x.sizes());  // dY W  (or dY W^T)
+  at::Tensor dw = transpose ? gemm2d(g2, x2, true, false) : gemm2d(x2, g2, true, false);
+  TP db = has_bias ? W(g2.sum(0)) : nullptr;  // column sums (the reference's CUDA path sums the wrong axis)
+  return {W(dx), W(dw), db};
+}
+
+TP OuterForward(const TP& a, const TP& b) { return W(at::outer(a->data(), b->data())); }
+std::pair<TP, TP> OuterBackward(const TP& a, const TP& b, const TP& g) {
+  return {W(at::mv(g->data(), b->data())), W(at::mv(g->data().t(), a->data()))};
+}
+
+// ---- normalisation ------------------------------------------------------------------------------------------------------
+std::tuple<TP, TP, TP> LayerNormForward(const TP& input, const TP& weight, const TP& bias, float eps) {
+  const at::Tensor& x = input->data();
+  const int64_t C = x.size(-1), rows = x.numel() / C;
+  if (native(x) && x.is_contiguous() && weight->data().scalar_type() == x.scalar_type()) {
+    c10::cuda::CUDAGuard guard(x.device());
+    at::Tensor y = at::empty_like(x), mean = at::empty({rows}, x.options().dtype(at::kFloat)), rstd = at::empty_like(mean);
+    ok(titb_layernorm_fwd(x.data_ptr(), weight->data().data_ptr(), bias->data().data_ptr(), y.data_ptr(),
+                          mean.data_ptr<float>(), rstd.data_ptr<float>(), rows, (int)C, eps, dt(x), stream()), "LayerNormForward");
+    return {W(y), W(mean), W(rstd)};
+  }
+  at::Tensor xf = x.to(at::kFloat).reshape({rows, C});
+  at::Tensor mean = xf.mean(1), var = xf.var(1, false);
+  at::Tensor rstd = (var + eps).rsqrt();
+  at::Tensor y = (xf - mean.unsqueeze(1)) * rstd.unsqueeze(1) * weight->data().to(at::kFloat) + bias->data().to(at::kFloat);
+  return {W(y.reshape(x.sizes()).to(x.scalar_type())), W(mean), W(rstd)};
+}
+std::tuple<TP, TP, TP> LayerNormBackward(const TP& input, const TP& weight, const TP& bias, const TP& mean, const TP& rstd,
+                                         const TP& grad_output) {
+  const at::Tensor& x = input->data();
+  const int64_t C = x.size(-1), rows = x.numel() / C;
+  at::Tensor xf = x.to(at::kFloat).reshape({rows, C}), g = grad_output->data().to(at::kFloat).reshape({rows, C});
+  at::Tensor w = weight->data().to(at::kFloat);
+  at::Tensor norm = (xf - mean->data().unsqueeze(1)) * rstd->data().unsqueeze(1);
+  at::Tensor dnorm = g * w;
+  at::Tensor dx = (dnorm - dnorm.mean(1, true) - norm * (dnorm * norm).mean(1, true)) * rstd->data().unsqueeze(1);
+  return {W(dx.reshape(x.sizes()).to(x.scalar_type())), W((g * norm).sum(0).to(weight->data().scalar_type())),
+          W(g.sum(0).to(weight->data().scalar_type()))};
+}
+
+// ---- softmax / cross entropy / embedding -------------------------------------------------------------------------------
+TP SoftmaxForward(const TP& input, int64_t dim) { return W(at::softmax(input->data(), dim)); }
+TP SoftmaxBackward(const TP& grad_output, const TP& output, int64_t dim) {
+  const at::Tensor &g = grad_output->data(), &y = output->data();
+  return W(y * (g - (g * y).sum(dim, true)));
+}
+TP CrossEntropyForward(const TP& input, const TP& target) {
+  const at::Tensor& x = input->data();
+  const int64_t V = x.size(-1), rows = x.numel() / V;
+  at::Tensor tgt = target->data().reshape({rows}).to(at::kLong);
+  if (native(x) && x.is_contiguous()) {
+    c10::cuda::CUDAGuard guard(x.device());
+    at::Tensor losses = at::empty({rows}, x.options().dtype(at::kFloat)), loss = at::empty({}, losses.options());
+    ok(titb_xent_fwd_bwd(x.data_ptr(), (const long long*)tgt.data_ptr<int64_t>(), losses.data_ptr<float>(), nullptr, rows,
+                         (int)V, V, 0.f, dt(x), stream()), "CrossEntropyForward");
+    ok(titb_mean(losses.data_ptr<float>(), loss.data_ptr<float>(), rows, 1.f / rows, stream()), "mean");
+    return W(loss);
+  }
+  at::Tensor lsm = at::log_softmax(x.to(at::kFloat).reshape({rows, V}), 1);
+  return W(-lsm.gather(1, tgt.unsqueeze(1)).mean());
+}
+TP CrossEntropyBackward(const TP& input, const TP& target, const TP& grad_output) {
+  const at::Tensor& x = input->data();
+  const int64_t V = x.size(-1), rows = x.numel() / V;
+  at::Tensor tgt = target->data().reshape({rows}).to(at::kLong);
+  at::Tensor p = at::softmax(x.to(at::kFloat).reshape({rows, V}), 1);
+  p.scatter_add_(1, tgt.unsqueeze(1), at::full({rows, 1}, -1.0, p.options()));
+  at::Tensor d = p * (grad_output->data().to(at::kFloat) / static_cast<double>(rows));  // honours the upstream gradient
+  return W(d.reshape(x.sizes()).to(x.scalar_type()));
+}
+TP EmbeddingForward(const TP& input, const TP& weight) {
+  TORCH_CHECK(input->data().scalar_type() == at::kLong, "Embedding indices must be INT64");
+  return W(at::embedding(weight->data(), input->data()));
+}
+TP EmbeddingBackward(const TP& input, const std::vector<int64_t>& weight_dims, const TP& grad_output) {
+  const at::Tensor& g = grad_output->data();
+  at::Tensor dw = at::zeros(weight_dims, g.options().dtype(at::kFloat));
+  dw.index_add_(0, input->data().reshape({-1}), g.reshape({-1, g.size(-1)}).to(at::kFloat));
+  return W(dw.to(g.scalar_type()));
+}
+
+// ---- reductions -----------------------------------------------------------------------------------------------------------
+static at::Tensor expand_back(const at::Tensor& g, const std::vector<int64_t>& in_dims, int64_t dim, bool keep_dim) {
+  at::Tensor gg = keep_dim ? g : g.unsqueeze(dim);
+  return gg.expand(in_dims).contiguous();
+}
+TP MeanForward(const TP& x, int64_t dim, bool keep) { return W(x->data().mean(dim, keep)); }
+TP SumForward(const TP& x, int64_t dim, bool keep) { return W(x->data().sum(dim, keep)); }
+TP MaxForward(const TP& x, int64_t dim, bool keep) { return W(x->data().amax(dim, keep)); }
+TP MinForward(const TP& x, int64_t dim, bool keep) { return W(x->data().amin(dim, keep)); }
+TP MeanBackward(const TP& g, const std::vector<int64_t>& in_dims, int64_t dim, bool keep) {
+  const int64_t d = dim < 0 ? dim + (int64_t)in_dims.size() : dim;
+  return W(expand_back(g->data(), in_dims, d, keep) / static_cast<double>(in_dims[d]));
+}
+TP SumBackward(const TP& g, const std::vector<int64_t>& in_dims, int64_t dim, bool keep) {
+  const int64_t d = dim < 0 ? dim + (int64_t)in_dims.size() : dim;
+  return W(expand_back(g->data(), in_dims, d, keep));
+}
+// Max/Min route the gradient to every element equal to the extremum (reference reduction.cc:13-167).
+TP MaxBackward(const TP& g, const TP& input, const TP& output, int64_t dim, bool keep) {
+  const at::Tensor& x = input->data();
+  const int64_t d = dim < 0 ? dim + x.dim() : dim;
+  at::Tensor o = keep ? output->data() : output->data().unsqueeze(d);
+  return W(expand_back(g->data(), x.sizes().vec(), d, keep) * (x == o).to(x.scalar_type()));
+}
+TP MinBackward(const TP& g, const TP& input, const TP& output, int64_t dim, bool keep) {
+  return MaxBackward(g, input, output, dim, keep);
+}
+
+// ---- transforms -------------------------------------------------------------------------------------------------------------
+TP TrilForward(const TP& x, int64_t diag) { return W(at::tril(x->data(), diag)); }
+TP TrilBackward(const TP& g, int64_t diag) { return W(at::tril(g->data(), diag)); }
+TP TriuForward(const TP& x, int64_t diag) { return W(at::triu(x->data(), diag)); }
+TP TriuBackward(const TP& g, int64_t diag) { return W(at::triu(g->data(), diag)); }
+TP TransposeForward(const TP& x, int64_t d0, int64_t d1) { return W(x->data().transpose(d0, d1)); }
+TP TransposeBackward(const TP& g, int64_t d0, int64_t d1) { return W(g->data().transpose(d0, d1)); }
+// mask is broadcast by modulo over the flattened input (reference transform.cc:121-152).
+static at::Tensor mask_like(const at::Tensor& x, const at::Tensor& mask) {
+  const int64_t n = x.numel(), m = mask.numel();
+  at::Tensor flat = mask.reshape({-1});
+  if (m != n) flat = flat.repeat({(n + m - 1) / m}).narrow(0, 0, n);
+  return (flat == 1).reshape(x.sizes());
+}
+TP MaskForward(const TP& x, const TP& mask, float value) {
+  return W(x->data().masked_fill(mask_like(x->data(), mask->data()), value));
+}
+TP MaskBackward(const TP& g, const TP& mask) { return W(g->data().masked_fill(mask_like(g->data(), mask->data()), 0)); }
+TP RepeatInterleaveForward(const TP& x, int64_t repeat, int64_t dim) {
+  return W(x->data().repeat_interleave(repeat, dim));
+}
+TP RepeatInterleaveBackward(const TP& g, const std::vector<int64_t>& in_dims, int64_t dim) {
+  std::vector<int64_t> shape = in_dims;
+  const int64_t repeat = g->data().size(dim) / in_dims[dim];
+  shape.insert(shape.begin() + dim + 1, repeat);
+  return W(g->data().reshape(shape).sum(dim + 1));
+}
+
+// ---- misc ---------------------------------------------------------------------------------------------------------------------
+std::vector<TP> SplitForward(const TP& x, int64_t split_size, int dim) {
+  std::vector<TP> out;
+  for (auto& t : x->data().split(split_size, dim)) out.push_back(W(t));
+  return out;
+}
+TP SplitBackward(const std::vector<int64_t>& in_dims, int64_t split_size, int dim, const std::vector<TP>& grads) {
+  std::vector<at::Tensor> parts;
+  for (auto& g : grads) parts.push_back(g->data());
+  return W(at::cat(parts, dim));
+}
+TP NoOpForward(const TP& x, const std::vector<int64_t>& dims) { return std::make_shared<Tensor>(x->data().reshape(dims)); }
+TP NoOpBackward(const std::vector<int64_t>& dims, const TP& g) { return std::make_shared<Tensor>(g->data().reshape(dims)); }
+static at::Tensor slice_nd(at::Tensor t, const std::vector<int64_t>& s, const std::vector<int64_t>& e,
+                           const std::vector<int64_t>& st) {
+  for (size_t d = 0; d < s.size(); ++d) t = t.slice(static_cast<int64_t>(d), s[d], e[d], st[d]);
+  return t;
+}
+TP SliceForward(const TP& x, const std::vector<int64_t>& s, const std::vector<int64_t>& e, const std::vector<int64_t>& st) {
+  return W(slice_nd(x->data(), s, e, st));
+}
+TP SliceBackward(const TP& g, const std::vector<int64_t>& in_dims, const std::vector<int64_t>& s,
+                 const std::vector<int64_t>& e, const std::vector<int64_t>& st) {
+  at::Tensor dx = at::zeros(in_dims, g->data().options());
+  slice_nd(dx, s, e, st).copy_(g->data());
+  return W(dx);
+}
+TP StackForward(const std::vector<TP>& xs, int64_t dim) {
+  std::vector<at::Tensor> parts;
+  for (auto& x : xs) parts.push_back(x->data());
+  return W(at::stack(parts, dim));
+}
+std::vector<TP> StackBackward(const std::vector<int64_t>&, int64_t dim, const TP& g) {
+  std::vector<TP> out;
+  for (auto& t : g->data().unbind(dim)) out.push_back(W(t));
+  return out;
+}
+
+// ---- registration ----------------------------------------------------------------------------------------------------------------
+#define REG_BOTH(Name)                                  \
+  REGISTER_KERNEL(DeviceType::kCPU, Name, &Name);       \
+  REGISTER_KERNEL(DeviceType::kCUDA, Name, &Name)
+
+REG_BOTH(AccumulateGrad); REG_BOTH(AdamAccumulateGrad); REG_BOTH(Fill);
+REG_BOTH(NegForward); REG_BOTH(NegBackward); REG_BOTH(ReciprocalForward); REG_BOTH(ReciprocalBackward);
+REG_BOTH(SinForward); REG_BOTH(SinBackward); REG_BOTH(CosForward); REG_BOTH(CosBackward);
+REG_BOTH(TanhForward); REG_BOTH(TanhBackward); REG_BOTH(RsqrtForward); REG_BOTH(RsqrtBackward);
+REG_BOTH(SigmoidForward); REG_BOTH(SigmoidBackward); REG_BOTH(PowForward); REG_BOTH(PowBackward);
+REG_BOTH(EqualsScalarForward); REG_BOTH(AddScalarForward); REG_BOTH(AddScalarBackward);
+REG_BOTH(MulScalarForward); REG_BOTH(MulScalarBackward);
+REG_BOTH(AddForward); REG_BOTH(AddBackward); REG_BOTH(SubForward); REG_BOTH(SubBackward);
+REG_BOTH(MulForward); REG_BOTH(MulBackward); REG_BOTH(DivForward); REG_BOTH(DivBackward);
+REG_BOTH(MatmulForward); REG_BOTH(MatmulBackward); REG_BOTH(LinearForward); REG_BOTH(LinearBackward);
+REG_BOTH(OuterForward); REG_BOTH(OuterBackward); REG_BOTH(LayerNormForward); REG_BOTH(LayerNormBackward);
+REG_BOTH(SoftmaxForward); REG_BOTH(SoftmaxBackward); REG_BOTH(CrossEntropyForward); REG_BOTH(CrossEntropyBackward);
+REG_BOTH(EmbeddingForward); REG_BOTH(EmbeddingBackward);
+REG_BOTH(MeanForward); REG_BOTH(MeanBackward); REG_BOTH(SumForward); REG_BOTH(SumBackward);
+REG_BOTH(MaxForward); REG_BOTH(MaxBackward); REG_BOTH(MinForward); REG_BOTH(MinBackward);
+REG_BOTH(TrilForward); REG_BOTH(TrilBackward); REG_BOTH(TriuForward); REG_BOTH(TriuBackward);
+REG_BOTH(TransposeForward); REG_BOTH(TransposeBackward); REG_BOTH(MaskForward); REG_BOTH(MaskBackward);
+REG_BOTH(RepeatInterleaveForward); REG_BOTH(RepeatInterleaveBackward);
+REG_BOTH(SplitForward); REG_BOTH(SplitBackward); REG_BOTH(NoOpForward); REG_BOTH(NoOpBackward);
+REG_BOTH(SliceForward); REG_BOTH(SliceBackward); REG_BOTH(StackForward); REG_BOTH(StackBackward);
+
+}  // namespace infini_train::kernels

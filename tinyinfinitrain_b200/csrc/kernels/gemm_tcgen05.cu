@@ -607,6 +607,14 @@ bool make_tmap_bf16_2d(CUtensorMap* m, const void* base, uint64_t inner, uint64_
                        uint32_t box_inner, uint32_t box_outer) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return false;
+  // The encoder is a driver-API entry point and needs a current context.  A thread that has made
+  // no runtime call yet (e.g. a fresh autograd worker thread) has none bound: bind the device's
+  // primary context once per thread through the runtime.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(nullptr);
+    ctx_bound = true;
+  }
   cuuint64_t dims[2] = {inner, outer};
   cuuint64_t strides[1] = {ld * 2};
   cuuint32_t box[2] = {box_inner, box_outer};
@@ -614,6 +622,13 @@ bool make_tmap_bf16_2d(CUtensorMap* m, const void* base, uint64_t inner, uint64_
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    static int reported = 0;
+    if (reported++ < 4)
+      fprintf(stderr, "titb200: cuTensorMapEncodeTiled failed (CUresult %d): base=%p inner=%llu outer=%llu ld=%llu box=%ux%u\n",
+              static_cast<int>(r), base, static_cast<unsigned long long>(inner), static_cast<unsigned long long>(outer),
+              static_cast<unsigned long long>(ld), box_inner, box_outer);
+  }
   return r == CUDA_SUCCESS;
 }
 
