@@ -1,0 +1,208 @@
+"""Training entry point shared by ``examples/gpt2/main.py`` and ``examples/llama3/main.py``.
+
+Flag names follow the fixture fields of the reference's end-to-end test
+(test/example/test_gpt2.cc:106-119) and the flag names its sources hint at
+(``FLAGS_batch_size, FLAGS_sequence_length``, example/common/tokenizer.cc:95), extended with the
+parallelism and precision switches of this framework.  Run under ``torchrun`` for more than one
+GPU; ranks are laid out as dp x pp x tp (``parallel/mesh.py``).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+import torch
+
+
+def build_parser(family: str) -> argparse.ArgumentParser:
+    p = argparse.ArgumentParser(description=f"Train {family} with tinyinfinitrain_b200")
+    p.add_argument("--llmc_filepath", default="", help="llm.c checkpoint to start from (random init if empty)")
+    p.add_argument("--input_bin", default="", help="llm.c token file (.bin); synthetic tokens if empty")
+    p.add_argument("--tokenizer_bin", default="", help="llm.c tokenizer file, enables text generation")
+    p.add_argument("--device", default="cuda", choices=["cuda", "cpu"])
+    p.add_argument("--model", default="gpt2" if family == "gpt2" else "llama3-1b")
+    p.add_argument("--batch_size", type=int, default=4, help="micro-batch per data-parallel rank")
+    p.add_argument("--sequence_length", type=int, default=64)
+    p.add_argument("--total_batch_size", type=int, default=0, help="tokens per optimizer step (0 = one micro-batch)")
+    p.add_argument("--num_iteration", type=int, default=10)
+    p.add_argument("--text_length", type=int, default=64)
+    p.add_argument("--freq_generate_txt", type=int, default=0)
+    p.add_argument("--learning_rate", type=float, default=1e-4)
+    p.add_argument("--weight_decay", type=float, default=0.0)
+    p.add_argument("--optimizer", default="adam", choices=["adam", "sgd"])
+    p.add_argument("--dtype", default="bfloat16", choices=["float32", "bfloat16"])
+    p.add_argument("--tensor_parallel", type=int, default=1)
+    p.add_argument("--sequence_parallel", type=int, default=1, help="kept for flag parity: TP always runs sequence parallel")
+    p.add_argument("--pipeline_parallel", type=int, default=1)
+    p.add_argument("--num_microbatches", type=int, default=1)
+    p.add_argument("--zero_stage", type=int, default=1, choices=[0, 1])
+    p.add_argument("--comm", default="fused", choices=["fused", "nccl"])
+    p.add_argument("--seed", type=int, default=42)
+    p.add_argument("--synthetic", action="store_true")
+    p.add_argument("--n_layer", type=int, default=0, help="override the preset depth (smoke tests)")
+    p.add_argument("--save", default="", help="checkpoint directory to write at the end")
+    p.add_argument("--resume", default="", help="checkpoint directory to resume from")
+    p.add_argument("--log_jsonl", default="")
+    p.add_argument("--cuda_graph", action="store_true", help="capture the single-GPU training step in a CUDA graph")
+    return p
+
+
+def _config(family: str, args):
+    import dataclasses
+
+    from .models import GPT2_PRESETS, LLAMA3_PRESETS
+
+    cfg = (GPT2_PRESETS if family == "gpt2" else LLAMA3_PRESETS)[args.model]
+    cfg = dataclasses.replace(cfg)
+    if args.n_layer:
+        cfg.n_layer = args.n_layer
+    cfg.block_size = max(args.sequence_length, min(cfg.block_size, 8192))
+    return cfg
+
+
+def _data(args, cfg, rank_dp: int, world_dp: int, pin: bool):
+    from . import data
+
+    if args.input_bin and not args.synthetic:
+        ds = data.TinyShakespeareDataset(args.input_bin, args.sequence_length)
+    else:
+        n = max(64, args.batch_size * world_dp * 8)
+        ds = data.SyntheticDataset(args.seed, cfg.vocab_size, args.sequence_length, n)
+    return data.DataLoader(ds, args.batch_size, pin_memory=pin, rank=rank_dp, world=world_dp)
+
+
+def train_main(family: str, argv=None) -> int:
+    args = build_parser(family).parse_args(argv)
+    import torch.distributed as dist
+
+    import tinyinfinitrain_b200 as tit
+    from .models import GPT2, LLaMA3
+    from .utils import CudaTimer, JsonlLogger, ThroughputMeter, load_checkpoint, save_checkpoint
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    cuda = args.device == "cuda"
+    dev = torch.device("cuda", local) if cuda else torch.device("cpu")
+    if cuda:
+        torch.cuda.set_device(local)
+    dtype = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
+    distributed = world > 1
+    if distributed:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl" if cuda else "gloo", **({"device_id": dev} if cuda else {}))
+    cfg = _config(family, args)
+    tp, pp = args.tensor_parallel, args.pipeline_parallel
+    log = JsonlLogger(args.log_jsonl if rank == 0 else None)
+    B, T = args.batch_size, args.sequence_length
+
+    if not distributed:
+        # ------------------------------------------------------------------ one process
+        cls = GPT2 if family == "gpt2" else LLaMA3
+        model = cls.FromLLMC(args.llmc_filepath, device=dev, dtype=dtype) if args.llmc_filepath else \
+            cls(cfg, device=dev, dtype=dtype, seed=args.seed)
+        if args.optimizer == "sgd":
+            opt = tit.optim.SGD(model.parameters(), args.learning_rate)
+        else:
+            opt = tit.optim.MixedPrecisionAdam(model.parameters(), lr=args.learning_rate, weight_decay=args.weight_decay)
+        start = load_checkpoint(args.resume, model, opt) if args.resume else 0
+        loader = _data(args, cfg, 0, 1, cuda)
+        accum = max(1, args.total_batch_size // (B * T)) if args.total_batch_size else 1
+        meter = ThroughputMeter(B * T * accum, model.flops_per_token(T), 1398.5 if cuda else 0.0)
+        tok = tit.data.Tokenizer(args.tokenizer_bin) if args.tokenizer_bin else None
+        it = 0
+        for step in range(start, args.num_iteration):
+            with CudaTimer() as tm:
+                opt.zero_grad()
+                lossf = 0.0
+                for _ in range(accum):
+                    x, y = loader.batch(it % len(loader))
+                    it += 1
+                    x, y = x.to(dev, non_blocking=True), y.to(dev, non_blocking=True)
+                    fused = cuda and dtype == torch.bfloat16
+                    _, loss = model(x, y, return_logits=not fused)
+                    (loss / accum).backward()
+                    lossf += float(loss) / accum
+                opt.step()
+            rep = meter.report(tm.ms)
+            if rank == 0:
+                print(f"step {step + 1}/{args.num_iteration} | loss {lossf:.6f} | lr {args.learning_rate:.2e} | "
+                      f"{tm.ms:.2f} ms | {rep['tokens_per_s']:.0f} tok/s" + (f" | mfu {rep['mfu']:.3f}" if 'mfu' in rep else ""),
+                      flush=True)
+            log.log(step=step + 1, loss=lossf, **rep)
+            if tok is not None and args.freq_generate_txt and (step + 1) % args.freq_generate_txt == 0:
+                tok.GenerateText(model, B, T, args.text_length, dev, stream=sys.stdout)
+        if args.save:
+            save_checkpoint(args.save, model, opt, args.num_iteration)
+        log.close()
+        return 0
+
+    # ---------------------------------------------------------------------- dp x pp x tp
+    from .models.tp_models import TPTransformer
+    from .parallel import DistributedOptimizer, PipelineStage, TPComm, init_mesh, partition_layers, \
+        sync_sequence_parallel_grads
+
+    mesh = init_mesh(tp=tp, pp=pp)
+    comm = TPComm(mesh.tp_group, args.comm if cuda else "nccl")
+    layers = partition_layers(cfg.n_layer, pp)[mesh.pp_rank]
+    model = TPTransformer(cfg, comm, device=dev, dtype=dtype, seed=args.seed, layers=layers, first=mesh.is_first_stage,
+                          last=mesh.is_last_stage)
+    if args.llmc_filepath:
+        from ._lib import C
+
+        _, sd = (C.llmc_read_gpt2(args.llmc_filepath, True) if family == "gpt2" else C.llmc_read_llama3(args.llmc_filepath))
+        model.load_full_state_dict(sd)
+    params = list(model.parameters())
+    if mesh.dp > 1 and args.zero_stage == 1:
+        opt = DistributedOptimizer(params, lr=args.learning_rate, weight_decay=args.weight_decay, group=mesh.dp_group,
+                                   comm=args.comm if cuda else "nccl")
+    else:
+        opt = tit.optim.MixedPrecisionAdam(params, lr=args.learning_rate, weight_decay=args.weight_decay)
+    loader = _data(args, cfg, mesh.dp_rank, mesh.dp, cuda)
+    nm = max(1, args.num_microbatches)
+    assert (B * T) % tp == 0
+    batches = []
+
+    def stage_fn(x_in, i):
+        x, y = batches[i]
+        if mesh.is_first_stage:
+            return model(x, y if mesh.is_last_stage else None)
+        return model(x_in, y if mesh.is_last_stage else None, B=B, T=T)
+
+    stage = PipelineStage(stage_fn, mesh.pp_rank, pp, None if mesh.is_first_stage else mesh.prev_stage_rank(),
+                          None if mesh.is_last_stage else mesh.next_stage_rank(), (B * T // tp, cfg.n_embd), dtype, dev)
+    meter = ThroughputMeter(B * T * nm * mesh.dp, 0.0, 0.0)
+    it = 0
+    for step in range(args.num_iteration):
+        t0 = time.perf_counter()
+        batches = []
+        for _ in range(nm):
+            x, y = loader.batch(it % len(loader))
+            it += 1
+            batches.append((x.to(dev, non_blocking=True), y.to(dev, non_blocking=True)))
+        opt.zero_grad()
+        loss = stage.run(nm)
+        sync_sequence_parallel_grads(params, comm)
+        opt.step()
+        if cuda:
+            torch.cuda.synchronize()
+        ms = torch.tensor([(time.perf_counter() - t0) * 1e3], device=dev)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        lossv = torch.tensor([float(loss) if loss is not None else 0.0], device=dev)
+        dist.all_reduce(lossv)
+        lossv = lossv.item() / (mesh.dp * tp)          # the last stage of every replica (and each tp rank) reports it
+        rep = meter.report(ms.item())
+        if rank == 0:
+            print(f"step {step + 1}/{args.num_iteration} | loss {lossv:.6f} | {ms.item():.2f} ms | "
+                  f"{rep['tokens_per_s']:.0f} tok/s | tp{tp} pp{pp} dp{mesh.dp}", flush=True)
+        log.log(step=step + 1, loss=lossv, **rep)
+    if cuda:
+        status = tit._lib.C.status_read(True)
+        if status:
+            print(f"rank {rank}: kernel status word {status} (a bounded device-side wait gave up)", file=sys.stderr)
+    log.close()
+    dist.destroy_process_group()
+    return 0

@@ -155,9 +155,17 @@ class FlatParams:
             p._fresh_grad = True
 
     def finish_unwritten(self) -> None:
-        """Parameters whose gradient was not produced this step must read as zero."""
+        """Folds gradients that arrived through plain autograd (``p.grad``: CPU tensors, fp32 ops,
+        user-defined ops) into the main-gradient buffer, and zeroes parameters that got none."""
         for p in self.params:
-            if p._fresh_grad:
+            if p.grad is not None:
+                if p._fresh_grad:
+                    p.main_grad.copy_(p.grad)
+                else:
+                    p.main_grad.add_(p.grad)
+                p._fresh_grad = False
+                p.grad = None
+            elif p._fresh_grad:
                 p.main_grad.zero_()
                 p._fresh_grad = False
 
@@ -230,3 +238,8 @@ class MixedPrecisionAdam:
         self.v.copy_(sd["v"])
         if self.mixed:
             self.flat.param.copy_(self.master.to(self.flat.dtype))
+        if self.dev_state is not None:
+            b1, b2 = self.betas
+            self.dev_state[0] = float(self.t)
+            self.dev_state[1] = 1.0 - b1 ** self.t if self.t else 0.0
+            self.dev_state[2] = 1.0 - b2 ** self.t if self.t else 0.0

@@ -1,2 +1,5 @@
-"""Utilities: training-step driver, llm.c file formats, tokenizer, checkpoints, timers."""
+"""Utilities: training-step driver, llm.c file formats, checkpoints, timers and metrics."""
+from . import llmc  # noqa: F401
+from .checkpoint import load_checkpoint, save_checkpoint  # noqa: F401
+from .profiling import CudaTimer, JsonlLogger, ThroughputMeter, nvtx_range  # noqa: F401
 from .train import TrainStep  # noqa: F401

@@ -1,0 +1,45 @@
+"""Checkpoint save / resume.
+
+The reference can only load model weights (``GPT2::FromLLMC``, example/gpt2/net.cc:246-377); it
+has no save, no optimizer state and no step counter.  Here a checkpoint is a directory:
+
+* ``model.bin``      -- llm.c layout (GPT-2 or LLaMA-3, fp32 or bf16), written by rank 0 of each
+  model-parallel layout; readable by llm.c and by the reference's loader (GPT-2 version 3),
+* ``optim_rankN.pt`` -- this data-parallel rank's optimizer shard (fp32 master weights, Adam
+  moments, step count): with ZeRO-1 every rank owns a different slice,
+* ``meta.json``      -- step, world layout, model name.
+
+Resuming restores master weights, moments and the step counter exactly, so the next step after a
+resume is bit-identical to the step an uninterrupted run would have taken (on one GPU).
+"""
+from __future__ import annotations
+
+import json
+import os
+from typing import Optional
+
+import torch
+
+
+def save_checkpoint(path: str, model, optimizer, step: int, rank: int = 0, world: int = 1, extra: Optional[dict] = None,
+                    bf16_weights: bool = False) -> None:
+    os.makedirs(path, exist_ok=True)
+    if rank == 0 and hasattr(model, "SaveLLMC"):
+        model.SaveLLMC(os.path.join(path, "model.bin"), bf16=bf16_weights)
+    sd = optimizer.state_dict()
+    torch.save({k: (v.detach().cpu() if torch.is_tensor(v) else v) for k, v in sd.items()},
+               os.path.join(path, f"optim_rank{rank}.pt"))
+    if rank == 0:
+        meta = {"step": int(step), "world": int(world), "model": type(model).__name__}
+        meta.update(extra or {})
+        with open(os.path.join(path, "meta.json"), "w") as f:
+            json.dump(meta, f)
+
+
+def load_checkpoint(path: str, model, optimizer, rank: int = 0) -> int:
+    """Restores optimizer state (and through the fp32 master weights, the parameters). Returns the step."""
+    with open(os.path.join(path, "meta.json")) as f:
+        meta = json.load(f)
+    sd = torch.load(os.path.join(path, f"optim_rank{rank}.pt"), map_location="cpu")
+    optimizer.load_state_dict(sd)
+    return int(meta["step"])
