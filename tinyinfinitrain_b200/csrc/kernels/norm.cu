@@ -286,7 +286,7 @@ __global__ void norm_bwd_dw_generic(const T* dy, const T* x, const float* mean_i
   if (!RMS && db) db[c] = accumulate ? db[c] + sb : sb;
 }
 
-constexpr int kNormBwdBlocks = 148 * 4;  // CTAs of the warp-per-row backward kernel
+constexpr int kNormBwdBlocks = 148 * 2;  // CTAs of the warp-per-row backward kernel
 constexpr int kNormBwdParts = 148 * 4;   // partial rows per gradient in the scratch buffer (upper bound)
 
 struct NormPlan {

@@ -422,7 +422,7 @@ TITB_API int titb_colsum(const void* x, float* out, long long rows, int C, int d
   if (C <= 0) return 0;
   const int vn = dtype == 1 ? 8 : 4;
   if (scratch && (C % vn) == 0 && !((uintptr_t)x & 15) && rows > 0) {
-    int parts = (int)((rows + 127) / 128);
+    int parts = (int)((rows + 31) / 32);
     if (parts > kColsumParts) parts = kColsumParts;
     dim3 grid((C / vn + 31) / 32, parts);
     if (dtype == 1) colsum_stage1<bf16><<<grid, 256, 0, st>>>((const bf16*)x, scratch, rows, C);

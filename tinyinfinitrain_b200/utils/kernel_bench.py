@@ -1,0 +1,141 @@
+"""Single-kernel benchmark driver: times one kernel of the library on one shape with CUDA events
+and reports achieved throughput against the measured peaks (``MEASURED_PEAKS.json`` at the
+repository root when present, otherwise the documented fallback).  The same command line is what
+the ncu captures summarised under ``profiles/`` run.
+
+    python -m tinyinfinitrain_b200.utils.kernel_bench gemm --m 8192 --n 3072 --k 768
+    python -m tinyinfinitrain_b200.utils.kernel_bench attn_bwd --b 8 --t 1024 --h 12 --hd 64
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+
+def peaks():
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    p = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def timeit(fn, iters, warmup=3, flush=None):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    tot = 0.0
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()          # > L2 so the timed launch starts cold
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        tot += e0.elapsed_time(e1)
+    return tot / iters
+
+
+def main():
+    from .._lib import C
+    from .. import ops
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["gemm", "gemm_nt", "gemm_wgrad", "attn_fwd", "attn_bwd", "layernorm_fwd", "layernorm_bwd",
+                                       "xent", "adam", "gelu_gemm"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=3072)
+    ap.add_argument("--k", type=int, default=768)
+    ap.add_argument("--b", type=int, default=8)
+    ap.add_argument("--t", type=int, default=1024)
+    ap.add_argument("--h", type=int, default=12)
+    ap.add_argument("--hkv", type=int, default=0)
+    ap.add_argument("--hd", type=int, default=64)
+    ap.add_argument("--tile_n", type=int, default=0)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--no_flush", action="store_true")
+    a = ap.parse_args()
+    dev = "cuda"
+    hbm, tflops, src = peaks()
+    flush = None if a.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    bf = torch.bfloat16
+    flops = bytes_ = 0.0
+    if a.kernel in ("gemm", "gemm_nt", "gemm_wgrad", "gelu_gemm"):
+        M, N, K = a.m, a.n, a.k
+        flops = 2.0 * M * N * K
+        bytes_ = 2.0 * (M * K + N * K + M * N)
+        if a.kernel == "gemm":
+            A, B = torch.randn(M, K, device=dev).to(bf), torch.randn(N, K, device=dev).to(bf)
+            fn = lambda: C.gemm(A, B, tile_n=a.tile_n)
+        elif a.kernel == "gelu_gemm":
+            A, B = torch.randn(M, K, device=dev).to(bf), torch.randn(N, K, device=dev).to(bf)
+            bias = torch.randn(N, device=dev).to(bf)
+            fn = lambda: C.gemm(A, B, epilogue=2, bias=bias, want_aux_out=True, tile_n=a.tile_n)
+        elif a.kernel == "gemm_nt":   # dgrad: dY [M, K] . W [K, N]
+            A, B = torch.randn(M, K, device=dev).to(bf), torch.randn(K, N, device=dev).to(bf)
+            fn = lambda: C.gemm(A, B, False, True, tile_n=a.tile_n)
+        else:                          # wgrad: dY^T [M=out, K=tokens] X [tokens, N]
+            A, B = torch.randn(K, M, device=dev).to(bf), torch.randn(K, N, device=dev).to(bf)
+            out = torch.zeros(M, N, device=dev)
+            fn = lambda: C.gemm(A, B, True, True, out=out, accumulate=True, tile_n=a.tile_n)
+    elif a.kernel in ("attn_fwd", "attn_bwd"):
+        Hkv = a.hkv or a.h
+        W = (a.h + 2 * Hkv) * a.hd
+        qkv = (torch.randn(a.b, a.t, W, device=dev) * 0.5).to(bf)
+        q = qkv[..., :a.h * a.hd].view(a.b, a.t, a.h, a.hd)
+        k = qkv[..., a.h * a.hd:(a.h + Hkv) * a.hd].view(a.b, a.t, Hkv, a.hd)
+        v = qkv[..., (a.h + Hkv) * a.hd:].view(a.b, a.t, Hkv, a.hd)
+        scale = a.hd ** -0.5
+        fwd_flops = 4.0 * a.b * a.h * a.t * a.t * a.hd / 2
+        if a.kernel == "attn_fwd":
+            flops = fwd_flops
+            fn = lambda: C.attn_fwd(q, k, v, scale)
+        else:
+            o, lse = C.attn_fwd(q, k, v, scale)
+            do = torch.randn_like(o)
+            flops = 2.5 * fwd_flops
+            fn = lambda: C.attn_bwd(do, q, k, v, o, lse, scale)
+        bytes_ = 2.0 * qkv.numel() * 2
+    elif a.kernel in ("layernorm_fwd", "layernorm_bwd"):
+        x = torch.randn(a.m, a.k, device=dev).to(bf)
+        w, b = torch.ones(a.k, device=dev).to(bf), torch.zeros(a.k, device=dev).to(bf)
+        if a.kernel == "layernorm_fwd":
+            bytes_ = 2.0 * x.numel() * 2
+            fn = lambda: C.layernorm_fwd(x, w, b, 1e-5)
+        else:
+            y, mean, rstd = C.layernorm_fwd(x, w, b, 1e-5)
+            dy = torch.randn_like(x)
+            bytes_ = 3.0 * x.numel() * 2
+            fn = lambda: C.layernorm_bwd(dy, x, w, mean, rstd)
+    elif a.kernel == "xent":
+        logits = torch.randn(a.m, a.n, device=dev).to(bf)
+        tgt = torch.randint(0, a.n - 47, (a.m,), device=dev)
+        bytes_ = 2.0 * logits.numel() * 2
+        fn = lambda: C.xent_fused(logits, tgt, a.n - 47, 1.0 / a.m, True, 1.0 / a.m)
+    else:
+        n = a.m * a.n
+        w, g = torch.randn(n, device=dev), torch.randn(n, device=dev)
+        m, v = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+        lp = torch.empty(n, device=dev, dtype=bf)
+        bytes_ = n * (4 * 4 + 3 * 4 + 2)
+        fn = lambda: C.adam_flat(w, lp, g, m, v, 1e-3, 0.9, 0.999, 1e-8, 0.0, 1, 1.0)
+    ms = timeit(fn, a.iters, flush=flush)
+    torch.cuda.synchronize()
+    out = {"kernel": a.kernel, "ms": ms, "status": int(C.status_read(True)), "peaks": src}
+    if flops:
+        out["tflops"] = flops / ms / 1e9
+        out["frac_of_bf16_peak"] = out["tflops"] / tflops
+    if bytes_:
+        out["gbs"] = bytes_ / ms / 1e6
+        out["frac_of_hbm_peak"] = out["gbs"] / hbm
+    out["args"] = {k: v for k, v in vars(a).items() if k != "kernel"}
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()
