@@ -60,6 +60,8 @@ struct GemmArgs {
   int splits;       // split-K factor; partial tiles go to `out` = workspace [splits, M, N] fp32
   int kb_per_split;
   int vec_ok;       // all row strides / base pointers allow 16-byte accesses
+  int tma_store;    // bf16 outputs leave through shared-memory staging + TMA stores
+  int aux_tma_load; // residual / pre-activation tiles arrive through TMA loads into the aux staging tile
   const float* alpha;  // optional device scalar multiplied into the accumulator
   uint32_t a_lbo, a_sbo, a_kstep, b_lbo, b_sbo, b_kstep;
   int* status;
@@ -71,7 +73,8 @@ struct GemmCfg {
   static constexpr int kStages = (BN == 256) ? 4 : 6;
   static constexpr int kTmemCols = 2 * BN;
   static constexpr int kRing = kStages * (kABytes + kBBytes);
-  static constexpr int kSmem = kRing + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kStage = 2 * kBM * 128;  // two [128 rows x 64 bf16] swizzled staging tiles for TMA stores
+  static constexpr int kSmem = kRing + kStage + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
 __device__ __forceinline__ float tanh_fast(float x) {
@@ -93,6 +96,7 @@ __device__ __forceinline__ float gelu_grad_fast(float x) {
 // Epilogue for one thread: 32 consecutive columns [col0, col0+32) of one output row.
 __device__ __forceinline__ void epilogue_row32(const GemmArgs& p, float (&v)[32], long long row, int col0,
                                                 int split) {
+  if (p.epi == 100) return;  // timing probe: accumulator read, nothing stored
   const int ncols = min(32, p.N - col0);
   const bool full = (ncols == 32) && p.vec_ok;
 
@@ -344,6 +348,7 @@ __device__ void rs_reduce_role(const GemmArgs& p, int tiles_n) {
 template <int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                         const __grid_constant__ CUtensorMap tma_out, const __grid_constant__ CUtensorMap tma_aux,
                          const GemmArgs p) {
   using Cfg = GemmCfg<BN>;
   constexpr int kStages = Cfg::kStages;
@@ -363,17 +368,21 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sa = smem;
   uint8_t* sb = smem + kStages * kABytes;
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + Cfg::kRing);
+  uint8_t* stage_out = smem + Cfg::kRing;
+  uint8_t* stage_aux = stage_out + kBM * 128;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + Cfg::kRing + Cfg::kStage);
   uint64_t* empty = full + kStages;
   uint64_t* acc_full = empty + kStages;
   uint64_t* acc_empty = acc_full + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* aux_bar = acc_empty + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux_bar + 1);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
+    ptx::mbar_init(aux_bar, 1);
     for (int s = 0; s < kStages; ++s) {
       ptx::mbar_init(&full[s], 1);
       ptx::mbar_init(&empty[s], 1);
@@ -495,6 +504,160 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     // ---------------------------------------------------------------- epilogue
     const int quad = warp & 3;  // TMEM lane quarter this warp may read
     int it = 0;
+    if (p.tma_store) {
+      // bf16 outputs: 64 columns at a time -> registers -> swizzled shared-memory tile -> one TMA
+      // store per tile chunk (full 128-byte lines instead of one 16-byte piece per thread and row).
+      const int trow = quad * 32 + lane;
+      const bool elected = (warp == 2 && lane == 0);
+      // Residual / pre-activation tiles are fetched one chunk ahead by TMA into the aux staging tile.
+      constexpr int kChunksPerTile = BN / 64;
+      const int my_tiles = cta < num_tiles ? (num_tiles - cta + ncta - 1) / ncta : 0;
+      const int total_chunks = my_tiles * kChunksPerTile;
+      auto issue_aux_load = [&](int g) {  // g: running chunk index over this CTA's tiles
+        const int t_local = g / kChunksPerTile;
+        const TileCoord t2 = tile_coord(p, cta + t_local * ncta, tiles_m, tiles_n, BN);
+        ptx::mbar_expect_tx(aux_bar, kBM * 128);
+        ptx::tma_load_2d(stage_aux, &tma_aux, aux_bar, t2.n0 + (g % kChunksPerTile) * 64, t2.m0);
+      };
+      int gchunk = 0;
+      if (p.aux_tma_load && elected && total_chunks > 0) issue_aux_load(0);
+      for (int tile = cta; tile < num_tiles; tile += ncta, ++it) {
+        const TileCoord tc = tile_coord(p, tile, tiles_m, tiles_n, BN);
+        const int m0 = tc.m0, n0 = tc.n0;
+        const int buf = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!ptx::mbar_wait(&acc_full[buf], acc_phase, abort_flag)) break;
+        ptx::tc_fence_after_sync();
+        const long long row = m0 + trow;
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          const int col0 = n0 + c * 64;
+          uint4 aux_row[8];
+          if (p.aux_tma_load) {
+            // chunk `gchunk` of the aux operand has landed; copy this thread's row out and prefetch the next
+            const bool got = ptx::mbar_wait(aux_bar, gchunk & 1, abort_flag);
+            if (got) {
+#pragma unroll
+              for (int u = 0; u < 8; ++u)
+                aux_row[u] = *reinterpret_cast<const uint4*>(stage_aux + trow * 128 + ((u ^ (trow & 7)) << 4));
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            ++gchunk;
+            if (elected && gchunk < total_chunks) issue_aux_load(gchunk);
+          }
+          if (col0 >= p.N) {  // whole chunk is padding: nothing to read or store, but keep the barriers in step
+            if (c == BN / 64 - 1) {
+              ptx::tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
+            }
+            continue;
+          }
+          uint32_t r0[32], r1[32];
+          ptx::tmem_ld32(t_row + c * 64, r0);
+          ptx::tmem_ld32(t_row + c * 64 + 32, r1);
+          ptx::tmem_ld_wait();
+          if (c == BN / 64 - 1) {  // accumulator fully read: the MMA warp may reuse this TMEM buffer
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
+          }
+          float v[64];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) { v[j] = __uint_as_float(r0[j]); v[32 + j] = __uint_as_float(r1[j]); }
+          if (p.alpha != nullptr) {
+            const float al = *p.alpha;
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] *= al;
+          }
+          const bool full_cols = (col0 + 64 <= p.N);
+          if (p.bias != nullptr && (p.epi == TITB_EPI_BIAS || p.epi == TITB_EPI_BIAS_GELU || p.epi == TITB_EPI_BIAS_RESIDUAL)) {
+            if (full_cols) {
+#pragma unroll
+              for (int j = 0; j < 64; j += 8) {
+                const uint4 u = *reinterpret_cast<const uint4*>(p.bias + col0 + j);
+                const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
+                v[j] += f0.x; v[j + 1] += f0.y; v[j + 2] += f1.x; v[j + 3] += f1.y;
+                v[j + 4] += f2.x; v[j + 5] += f2.y; v[j + 6] += f3.x; v[j + 7] += f3.y;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 64; ++j) if (col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
+            }
+          }
+          uint32_t aux_pk[32];
+          if (p.epi == TITB_EPI_BIAS_GELU) {
+#pragma unroll
+            for (int j = 0; j < 64; j += 2) {
+              aux_pk[j >> 1] = pack_bf16x2(v[j], v[j + 1]);
+              const float2 pr = unpack_bf16x2(aux_pk[j >> 1]);  // activation of the stored (rounded) pre-activation
+              v[j] = gelu_fast(pr.x);
+              v[j + 1] = gelu_fast(pr.y);
+            }
+          } else if (p.aux_tma_load) {
+            // out-of-range rows / columns of the aux tile were zero-filled by the TMA load
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const float2 f0 = unpack_bf16x2(aux_row[u].x), f1 = unpack_bf16x2(aux_row[u].y), f2 = unpack_bf16x2(aux_row[u].z),
+                           f3 = unpack_bf16x2(aux_row[u].w);
+              const float a8[8] = {f0.x, f0.y, f1.x, f1.y, f2.x, f2.y, f3.x, f3.y};
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                v[u * 8 + e] = (p.epi == TITB_EPI_DGELU) ? v[u * 8 + e] * gelu_grad_fast(a8[e]) : v[u * 8 + e] + a8[e];
+            }
+          } else if ((p.epi == TITB_EPI_DGELU || p.epi == TITB_EPI_BIAS_RESIDUAL) && p.aux_in != nullptr && row < p.M) {
+            const bf16* ai = p.aux_in + row * p.ld_aux_in + col0;
+            if (full_cols) {
+#pragma unroll
+              for (int j = 0; j < 64; j += 8) {
+                const uint4 u = *reinterpret_cast<const uint4*>(ai + j);
+                const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
+                const float a8[8] = {f0.x, f0.y, f1.x, f1.y, f2.x, f2.y, f3.x, f3.y};
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[j + e] = (p.epi == TITB_EPI_DGELU) ? v[j + e] * gelu_grad_fast(a8[e]) : v[j + e] + a8[e];
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 64; ++j) {
+                if (col0 + j < p.N) {
+                  const float a1 = __bfloat162float(ai[j]);
+                  v[j] = (p.epi == TITB_EPI_DGELU) ? v[j] * gelu_grad_fast(a1) : v[j] + a1;
+                }
+              }
+            }
+          }
+          // the previous chunk's TMA store must have finished reading the staging tiles
+          if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const uint32_t off = static_cast<uint32_t>(trow * 128 + ((u ^ (trow & 7)) << 4));
+            *reinterpret_cast<uint4*>(stage_out + off) =
+                make_uint4(pack_bf16x2(v[u * 8], v[u * 8 + 1]), pack_bf16x2(v[u * 8 + 2], v[u * 8 + 3]),
+                           pack_bf16x2(v[u * 8 + 4], v[u * 8 + 5]), pack_bf16x2(v[u * 8 + 6], v[u * 8 + 7]));
+            if (p.epi == TITB_EPI_BIAS_GELU && p.aux_out != nullptr)
+              *reinterpret_cast<uint4*>(stage_aux + off) =
+                  make_uint4(aux_pk[u * 4], aux_pk[u * 4 + 1], aux_pk[u * 4 + 2], aux_pk[u * 4 + 3]);
+          }
+          ptx::fence_proxy_async_smem();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (elected) {
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                             reinterpret_cast<uint64_t>(&tma_out)),
+                         "r"(ptx::smem_u32(stage_out)), "r"(col0), "r"(m0)
+                         : "memory");
+            if (p.epi == TITB_EPI_BIAS_GELU && p.aux_out != nullptr)
+              asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                               reinterpret_cast<uint64_t>(&tma_aux)),
+                           "r"(ptx::smem_u32(stage_aux)), "r"(col0), "r"(m0)
+                           : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+        }
+      }
+      if (elected) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // all stores done before the CTA exits
+    } else
     for (int tile = cta; tile < num_tiles; tile += ncta, ++it) {
       const TileCoord tc = tile_coord(p, tile, tiles_m, tiles_n, BN);
       const int split = tc.split, m0 = tc.m0, n0 = tc.n0;
@@ -505,7 +668,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       const long long row = m0 + quad * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = 0; c < (p.epi == 101 ? 0 : BN / 32); ++c) {  // 101: timing probe without any epilogue work
         uint32_t r[32];
         ptx::tmem_ld32(t_row + c * 32, r);
         ptx::tmem_ld_wait();
@@ -642,6 +805,7 @@ int device_sm_count() {
 }
 
 static unsigned g_dbg_lbo = 0, g_dbg_sbo = 0, g_dbg_kstep = 0;
+static int g_dbg_no_tma_store = 0;
 
 static int pick_tile_n(int M, int N, int splits) {
   // 128 x 256 tiles move fewer operand bytes per FLOP; 128 x 128 only wins when it removes
@@ -654,7 +818,7 @@ static int pick_tile_n(int M, int N, int splits) {
     return waves * bn;
   };
   if (N <= 128) return 128;
-  return (cost(128) * 5 < cost(256) * 4) ? 128 : 256;
+  return (cost(128) * 2 < cost(256)) ? 128 : 256;
 }
 
 }  // namespace titb
@@ -687,6 +851,7 @@ TITB_API int titb_status_read(int clear, cudaStream_t stream) {
 TITB_API void titb_gemm_debug_override(unsigned lbo, unsigned sbo, unsigned kstep) {
   g_dbg_lbo = lbo; g_dbg_sbo = sbo; g_dbg_kstep = kstep;
 }
+TITB_API void titb_gemm_set_tma_store(int enabled) { g_dbg_no_tma_store = enabled ? 0 : 1; }
 
 TITB_API int titb_gemm_pick_splits(int M, int N, int K) {
   // Split the reduction only when the output has too few tiles to fill the GPU and the
@@ -702,7 +867,8 @@ TITB_API int titb_gemm_pick_splits(int M, int N, int K) {
 }
 
 template <int BN>
-static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args, cudaStream_t stream) {
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tout, const CUtensorMap& taux,
+                       const GemmArgs& args, cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
   static bool attr_set[64] = {false};
   int dev = 0;
@@ -718,7 +884,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmA
   const int helpers = args.coll.mode ? args.coll.helper_ctas : 0;
   int grid = tiles + helpers < device_sm_count() ? tiles + helpers : device_sm_count();
   if (grid <= helpers) return TITB_ERR_SHAPE;
-  gemm_bf16_tcgen05_kernel<BN><<<grid, kGemmThreads, Cfg::kSmem, stream>>>(ta, tb, args);
+  gemm_bf16_tcgen05_kernel<BN><<<grid, kGemmThreads, Cfg::kSmem, stream>>>(ta, tb, tout, taux, args);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -795,7 +961,21 @@ TITB_API int titb_gemm_bf16(const TitbGemmDesc* d, cudaStream_t stream) {
     }
   }
 
-  int rc = (bn == 256) ? launch_gemm<256>(ta, tb, a, stream) : launch_gemm<128>(ta, tb, a, stream);
+  // bf16 results (and the GELU pre-activation) leave through TMA stores when their layout allows it
+  CUtensorMap tout = ta, taux = ta;  // placeholders when unused
+  const bool out_tma_ok = !d->out_fp32 && !d->accumulate && splits == 1 && a.coll.mode != 2 &&
+                          !(reinterpret_cast<uintptr_t>(d->out) & 15) && !(d->ldo & 7) && (d->epilogue != 100 && d->epilogue != 101) &&
+                          (!d->aux_out || (!(reinterpret_cast<uintptr_t>(d->aux_out) & 15) && !(d->ld_aux_out & 7))) &&
+                          (!d->aux_in || a.vec_ok) && (!d->bias || a.vec_ok) && g_dbg_no_tma_store == 0;
+  if (out_tma_ok) {
+    bool okm = make_tmap_bf16_2d(&tout, d->out, d->N, d->M, d->ldo, 64, kBM);
+    if (okm && d->aux_out) okm = make_tmap_bf16_2d(&taux, d->aux_out, d->N, d->M, d->ld_aux_out, 64, kBM);
+    a.tma_store = okm ? 1 : 0;
+    if (okm && !d->aux_out && d->aux_in && (d->epilogue == TITB_EPI_DGELU || d->epilogue == TITB_EPI_BIAS_RESIDUAL) &&
+        !(reinterpret_cast<uintptr_t>(d->aux_in) & 15) && !(d->ld_aux_in & 7))
+      a.aux_tma_load = make_tmap_bf16_2d(&taux, d->aux_in, d->N, d->M, d->ld_aux_in, 64, kBM) ? 1 : 0;
+  }
+  int rc = (bn == 256) ? launch_gemm<256>(ta, tb, tout, taux, a, stream) : launch_gemm<128>(ta, tb, tout, taux, a, stream);
   if (rc != 0) return rc;
   if (splits > 1) {
     const long long total = static_cast<long long>(d->M) * d->N;
