@@ -59,10 +59,11 @@ def main():
     ok = ok and status == 0
 
     # model level
-    for cfg in (LLaMA3Config(block_size=256, vocab_size=1000, n_layer=2, n_head=4, n_kv_head=2, n_embd=256, ffn_dim=512),
-                GPT2Config(block_size=256, vocab_size=1000, n_layer=2, n_head=4, n_embd=256)):
+    for cfg in (LLaMA3Config(block_size=256, vocab_size=1000, n_layer=2, n_head=8, n_kv_head=8 if world > 2 else 2,
+                             n_embd=512, ffn_dim=1024),
+                GPT2Config(block_size=256, vocab_size=1000, n_layer=2, n_head=8, n_embd=512)):
         gi = torch.Generator().manual_seed(5)
-        idx = torch.randint(0, 1000, (2, 256), generator=gi).to(dev)
+        idx = torch.randint(0, 1000, (4, 256), generator=gi).to(dev)
         tgt = torch.roll(idx, -1, 1)
         res = {}
         for name, comm in (("nccl", nccl), ("fused", fused)):

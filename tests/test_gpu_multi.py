@@ -31,5 +31,5 @@ def test_zero1_fused_matches_nccl():
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 def test_tp_fused_collectives_match_nccl():
     n = 2 if _ngpu() < 4 else 4 if _ngpu() < 8 else 8
-    r = _torchrun("dist_tp_check.py", 2)
+    r = _torchrun("dist_tp_check.py", n)
     assert r.returncode == 0, r.stdout[-4000:] + r.stderr[-3000:]

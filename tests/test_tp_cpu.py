@@ -25,6 +25,8 @@ def _worker(rank, world, port, q, which):
         comm = TPComm(m.tp_group)
         if which == "gpt2":
             cfg, cls = GPT2Config(block_size=32, vocab_size=250, n_layer=2, n_head=4, n_embd=32), GPT2
+        elif which == "gpt2_uneven_heads":   # 3 heads over 2 ranks: 2 + 1 (GPT-2 XL splits 25 heads 13 + 12)
+            cfg, cls = GPT2Config(block_size=32, vocab_size=250, n_layer=2, n_head=3, n_embd=48), GPT2
         else:
             cfg, cls = LLaMA3Config(block_size=32, vocab_size=256, n_layer=2, n_head=4, n_kv_head=2, n_embd=64,
                                     ffn_dim=96), LLaMA3
@@ -51,7 +53,7 @@ def _worker(rank, world, port, q, which):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("which", ["gpt2", "llama3"])
+@pytest.mark.parametrize("which", ["gpt2", "gpt2_uneven_heads", "llama3"])
 def test_tp2_matches_single_process(which):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()

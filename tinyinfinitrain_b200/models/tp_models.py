@@ -20,12 +20,21 @@ from .gpt2 import GPT2Config
 from .llama3 import LLaMA3Config
 
 
+def head_range(n: int, tp: int, rank: int):
+    """[first, last) of the heads rank ``rank`` owns; the first ``n % tp`` ranks take one extra head
+    (GPT-2 XL has 25 heads, which two ranks split 13 / 12)."""
+    base, rem = divmod(n, tp)
+    first = rank * base + min(rank, rem)
+    return first, first + base + (1 if rank < rem else 0)
+
+
 def _qkv_rows(n_head: int, n_kv_head: int, hd: int, tp: int, rank: int):
     """Row indices of a fused [q | k | v] projection that belong to one tensor-parallel rank."""
-    hq, hk = n_head // tp, n_kv_head // tp
-    q = torch.arange(rank * hq * hd, (rank + 1) * hq * hd)
-    k = n_head * hd + torch.arange(rank * hk * hd, (rank + 1) * hk * hd)
-    v = (n_head + n_kv_head) * hd + torch.arange(rank * hk * hd, (rank + 1) * hk * hd)
+    q0, q1 = head_range(n_head, tp, rank)
+    k0, k1 = head_range(n_kv_head, tp, rank)
+    q = torch.arange(q0 * hd, q1 * hd)
+    k = n_head * hd + torch.arange(k0 * hd, k1 * hd)
+    v = (n_head + n_kv_head) * hd + torch.arange(k0 * hd, k1 * hd)
     return torch.cat([q, k, v])
 
 
@@ -46,6 +55,9 @@ def shard_state_dict(sd: Dict[str, torch.Tensor], cfg, tp: int, rank: int) -> Di
             else:
                 n = t.shape[0] // tp
                 out[name] = t[rank * n:(rank + 1) * n]
+        elif name.endswith("attn.c_proj.weight"):
+            q0, q1 = head_range(cfg.n_head, tp, rank)
+            out[name] = t[:, q0 * hd:q1 * hd]
         elif name.endswith("c_proj.weight"):
             n = t.shape[1] // tp
             out[name] = t[:, rank * n:(rank + 1) * n]
@@ -62,12 +74,15 @@ class TPAttention(nn.Module):
 
     def __init__(self, n_embd, n_head, n_kv_head, comm, bias, rope_theta=None, device=None, dtype=torch.float32):
         super().__init__()
-        assert n_head % comm.world == 0 and n_kv_head % comm.world == 0
         self.hd = n_embd // n_head
-        self.hq, self.hk = n_head // comm.world, n_kv_head // comm.world
+        q0, q1 = head_range(n_head, comm.world, comm.rank)
+        k0, k1 = head_range(n_kv_head, comm.world, comm.rank)
+        self.hq, self.hk = q1 - q0, k1 - k0
+        assert self.hk > 0 and self.hq % self.hk == 0, "every rank needs whole groups of query heads per kv head"
         self.rope_theta = rope_theta
-        self.c_attn = tpl.ColumnParallelLinear(n_embd, (n_head + 2 * n_kv_head) * self.hd, comm, bias, device, dtype)
-        self.c_proj = tpl.RowParallelLinear(n_embd, n_embd, comm, bias, device, dtype)
+        self.c_attn = tpl.ColumnParallelLinear(n_embd, (n_head + 2 * n_kv_head) * self.hd, comm, bias, device, dtype,
+                                               out_local=(self.hq + 2 * self.hk) * self.hd)
+        self.c_proj = tpl.RowParallelLinear(n_embd, n_embd, comm, bias, device, dtype, in_local=self.hq * self.hd)
 
     def forward(self, x_s, B: int, T: int, residual_s=None):
         qkv = self.c_attn(x_s).view(B, T, -1)

@@ -237,11 +237,11 @@ class ColumnParallelLinear(nn.Module):
     kType = "ColumnParallelLinear"
 
     def __init__(self, in_features: int, out_features: int, comm: TPComm, bias: bool = True, device=None,
-                 dtype=torch.float32):
+                 dtype=torch.float32, out_local: Optional[int] = None):
         super().__init__()
-        assert out_features % comm.world == 0
+        assert out_local is not None or out_features % comm.world == 0
         self.comm, self.in_features, self.out_features = comm, in_features, out_features
-        self.out_local = out_features // comm.world
+        self.out_local = out_local if out_local is not None else out_features // comm.world  # uneven splits pass it
         self.weight = torch.nn.Parameter(torch.empty(self.out_local, in_features, device=device, dtype=dtype))
         self.bias = torch.nn.Parameter(torch.zeros(self.out_local, device=device, dtype=dtype)) if bias else None
         init.KaimingUniform(self.weight, a=math.sqrt(5.0))
@@ -259,11 +259,11 @@ class RowParallelLinear(nn.Module):
     kType = "RowParallelLinear"
 
     def __init__(self, in_features: int, out_features: int, comm: TPComm, bias: bool = True, device=None,
-                 dtype=torch.float32):
+                 dtype=torch.float32, in_local: Optional[int] = None):
         super().__init__()
-        assert in_features % comm.world == 0
+        assert in_local is not None or in_features % comm.world == 0
         self.comm, self.in_features, self.out_features = comm, in_features, out_features
-        self.in_local = in_features // comm.world
+        self.in_local = in_local if in_local is not None else in_features // comm.world
         self.weight = torch.nn.Parameter(torch.empty(out_features, self.in_local, device=device, dtype=dtype))
         self.bias = _mark_sp(torch.nn.Parameter(torch.zeros(out_features, device=device, dtype=dtype))) if bias else None
         init.KaimingUniform(self.weight, a=math.sqrt(5.0))
