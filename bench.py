@@ -15,8 +15,6 @@ from __future__ import annotations
 import argparse
 import json
 import os
-import statistics
-import subprocess
 import sys
 import time
 
@@ -35,58 +33,6 @@ def reference_arm(args):
     return 0
 
 
-class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-
-    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, index: int):
-        self.index, self.proc, self.path = index, None, f"/tmp/titb_clocks_{os.getpid()}.csv"
-
-    def start(self):
-        try:
-            self.f = open(self.path, "w")
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.index)], stdout=self.f,
-                                         stderr=subprocess.DEVNULL)
-        except Exception:  # noqa: BLE001
-            self.proc = None
-
-    def stop(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        if self.proc is None:
-            return out
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:  # noqa: BLE001
-            self.proc.kill()
-        self.f.close()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in open(self.path):
-            parts = [x.strip() for x in line.split(",")]
-            if len(parts) < 7:
-                continue
-            try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
-            except ValueError:
-                continue
-            for n, v in zip(names, parts[3:7]):
-                if v.lower().startswith("active"):
-                    reasons.add(n)
-        try:
-            os.remove(self.path)
-        except OSError:
-            pass
-        if sm:
-            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
-        return out
-
-
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -97,6 +43,8 @@ def main():
     ap.add_argument("--batch", type=int, default=8, help="micro-batch per GPU")
     ap.add_argument("--seq", type=int, default=1024)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--dp_buckets", type=int, default=1,
+                    help="ZeRO-1 buckets; >1 reduces each bucket on a side stream as soon as backward has written it")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"],
                     help="gradient reduce-scatter + Adam + parameter all-gather: own NVLink kernels or plain NCCL")
     args = ap.parse_args()
@@ -136,9 +84,11 @@ def main():
         grad_sync = None
     else:
         opt = dp.DistributedOptimizer(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1,
-                                      comm=args.comm)
+                                      comm=args.comm, num_buckets=args.dp_buckets, overlap=args.dp_buckets > 1)
         grad_sync = None  # the distributed optimizer's step() owns reduce-scatter / Adam / all-gather
-    step = TrainStep(model, opt, B, T, dev, use_graph=not args.no_graph, grad_sync=grad_sync)
+    # the NCCL baseline arm runs eagerly: its collectives are library calls issued per step, not captured
+    use_graph = not args.no_graph and (world == 1 or args.comm == "fused")
+    step = TrainStep(model, opt, B, T, dev, use_graph=use_graph, grad_sync=grad_sync)
 
     # synthetic uniform token ids, seed 0 (+rank so every rank sees different data), pinned on the host
     nbuf = 4
@@ -155,19 +105,28 @@ def main():
             dist.barrier()
         torch.cuda.synchronize(dev)
 
+    # rank 0 samples its GPU's clocks (read-only, NVML thread or nvidia-smi child) during the timed region
+    sampler = None
+    if rank == 0:
+        from tinyinfinitrain_b200.utils.clocks import ClockSampler
+
+        sampler = ClockSampler(local_rank, uuid=str(getattr(torch.cuda.get_device_properties(dev), "uuid", "") or ""))
+        sampler.launch()
+
     # ---------------- device-timed region: K steps, inputs resident -----------------
     for _ in range(W):
         step.run_device()
-    sampler = ClockSampler(local_rank)
     barrier()
-    sampler.start()
+    if sampler is not None:
+        sampler.begin()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(K):
         step.run_device()
     e1.record()
     barrier()
-    clocks = sampler.stop()
+    if sampler is not None:
+        sampler.end()
     ms = e0.elapsed_time(e1)
     final_loss = float(step.loss)
 
@@ -194,6 +153,7 @@ def main():
     status = tit._lib.C.status_read(True)
 
     if rank == 0:
+        clocks = sampler.result()
         tokens = B * T * world * K
         out = {
             "metric": "train_tokens_per_sec", "value": tokens / (ms / 1e3), "unit": "tokens/s",
@@ -207,7 +167,7 @@ def main():
                              "126 MB L2; no explicit flush",
                        "init": "random N(0,0.02), seed 42", "final_loss": final_loss, "kernel_status": status},
             "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"],
-                       "samples": clocks["samples"]},
+                       "samples": clocks["samples"], "source": clocks["backend"]},
             "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * B * T * 8,
                     "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms / K},
             "gpu_launches": int(step.launches_per_step) * K,

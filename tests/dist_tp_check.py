@@ -46,13 +46,15 @@ def main():
             res = torch.randn(Ms, N, device=dev, generator=g).bfloat16()
             z0 = nccl.gemm_rs(yin, w, False, b, res)
             z1 = fused.gemm_rs(yin, w, False, b, res)
-            e_rs = (z0.float() - z1.float()).abs().max().item()
+            # partial sums grow with the group size, and so does one bf16 ulp of the result: compare relative to the
+            # largest element
+            e_rs = ((z0.float() - z1.float()).abs().max() / z0.float().abs().max()).item()
             wt = w.t().contiguous()  # MN-major weight path (dgrad form)
             z2 = fused.gemm_rs(yin, wt, True)
             z3 = nccl.gemm_rs(yin, wt, True)
-            e_rs2 = (z2.float() - z3.float()).abs().max().item()
+            e_rs2 = ((z2.float() - z3.float()).abs().max() / z3.float().abs().max()).item()
             torch.cuda.synchronize()
-            good = e_ag < 5e-2 and e_x == 0.0 and e_ref < 0.15 and e_rs < 0.2 and e_rs2 < 0.2
+            good = e_ag < 5e-2 and e_x == 0.0 and e_ref < 0.15 and e_rs < 2e-2 and e_rs2 < 2e-2
             ok = ok and good
             msgs.append(f"[{Ms},{K},{N}] ag {e_ag:.3g} X {e_x:.3g} ref {e_ref:.3g} rs {e_rs:.3g} rs_mn {e_rs2:.3g}")
     status = tit._lib.C.status_read(True)

@@ -13,14 +13,15 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
-def run(comm, steps, dev, rank, use_graph=False):
+def run(comm, steps, dev, rank, use_graph=False, buckets=1):
     import tinyinfinitrain_b200 as tit
     from tinyinfinitrain_b200.models import GPT2, GPT2Config
     from tinyinfinitrain_b200.utils import TrainStep
 
     cfg = GPT2Config(block_size=128, vocab_size=1000, n_layer=2, n_head=4, n_embd=256)
     model = GPT2(cfg, device=dev, dtype=torch.bfloat16, seed=42)
-    opt = tit.parallel.DistributedOptimizer(model.parameters(), lr=1e-3, betas=(0.9, 0.95), weight_decay=0.1, comm=comm)
+    opt = tit.parallel.DistributedOptimizer(model.parameters(), lr=1e-3, betas=(0.9, 0.95), weight_decay=0.1, comm=comm,
+                                            num_buckets=buckets, overlap=buckets > 1)
     step = TrainStep(model, opt, 4, 128, dev, use_graph=use_graph)
     g = torch.Generator().manual_seed(1234 + rank)
     idx = torch.randint(0, 1000, (4, 128), generator=g).pin_memory()
@@ -52,6 +53,16 @@ def main():
     dist.broadcast(ref, src=0)
     same = bool((ref - p_fused).abs().max().item() == 0.0)
     ok = s0 == 0 and s1 == 0 and s2 == 0 and err < 2e-2 and errg < 2e-2 and same and l_fused[-1] < l_fused[0] - 0.3
+    nb = int(os.environ.get("TITB_TEST_ZERO_BUCKETS", "0"))
+    if nb > 1:
+        # bucketed reduction launched from backward on a side stream: same arithmetic, so the same parameters
+        p_b, l_b, s3, ob = run("fused", 6, dev, rank, buckets=nb)
+        p_bg, l_bg, s4, _ = run("fused", 5, dev, rank, use_graph=True, buckets=nb)
+        eb, ebg = (p_fused - p_b).abs().max().item(), (p_fused - p_bg).abs().max().item()
+        early = sum(1 for b in ob.buckets if not b["late"])
+        ok = ok and s3 == 0 and s4 == 0 and eb < 2e-2 and ebg < 2e-2 and len(ob.buckets) > 1 and early >= 1
+        print(f"rank {rank}: buckets={len(ob.buckets)} reduced-during-backward={early} fused-vs-bucketed={eb:.3e} "
+              f"bucketed-graph={ebg:.3e} status={s3},{s4}", flush=True)
     print(f"rank {rank}: nccl-vs-fused max|dp|={err:.3e} fused-vs-graph={errg:.3e} identical_across_ranks={same} "
           f"status={s0},{s1},{s2} multimem={'yes' if opt.gbuf.mc_ptr else 'no'} loss {l_fused[0]:.3f}->{l_fused[-1]:.3f} "
           f"ok={ok}", flush=True)

@@ -34,6 +34,7 @@ def _worker(rank, world, port, q):
             for p in opt.params:
                 p.main_grad.copy_(p.grad)
                 p._fresh_grad = False
+                p.grad = None  # a leftover .grad would be folded into main_grad a second time by step()
             opt.step()
             ropt.zero_grad()
             sum(ref(x).pow(2).mean() for x in xs).div(world).backward()

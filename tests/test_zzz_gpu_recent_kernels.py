@@ -1,0 +1,146 @@
+"""GPU numerics of the kernels and schedules that are not on the default training path: the 128 x 192
+GEMM tile, the reduction / view-like transform kernels and the bucketed ZeRO-1 step that overlaps
+backward.  Each is compared against plain PyTorch fp32 math of the same op."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from tinyinfinitrain_b200 import ops
+from tinyinfinitrain_b200._lib import C
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+BF = torch.bfloat16
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _status_ok():
+    torch.cuda.synchronize()
+    assert C.status_read(True) == 0
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 1)])
+def test_gemm_tile192_layouts_and_epilogue(a_mn, b_mn):
+    torch.manual_seed(11)
+    M, N, K = 520, 776, 328          # ragged in every dimension: 4 full 192-wide tiles + one of 8 columns
+    A = (torch.randn(M, K, device=DEV) * 0.5).to(BF)
+    W = (torch.randn(N, K, device=DEV) * 0.1).to(BF)
+    b = (torch.randn(N, device=DEV) * 0.1).to(BF)
+    R = torch.randn(M, N, device=DEV).to(BF)
+    ref = A.float() @ W.float().t()
+    a = A.t().contiguous() if a_mn else A
+    w = W.t().contiguous() if b_mn else W
+    y = C.gemm(a, w, bool(a_mn), bool(b_mn), tile_n=192, out_fp32=True)[0]
+    assert torch.allclose(y, ref, rtol=1e-4, atol=2e-2)
+    y = C.gemm(a, w, bool(a_mn), bool(b_mn), tile_n=192, epilogue=ops.EPI_BIAS_RESIDUAL, bias=b, aux_in=R)[0]
+    assert torch.allclose(y.float(), ref + b.float() + R.float(), atol=5e-2, rtol=2e-2)
+    act, pre = C.gemm(a, w, bool(a_mn), bool(b_mn), tile_n=192, epilogue=ops.EPI_BIAS_GELU, bias=b, want_aux_out=True)
+    assert torch.allclose(pre.float(), ref + b.float(), atol=3e-2, rtol=2e-2)
+    assert torch.allclose(act.float(), ops.gelu_ref(pre.float()), atol=2e-2, rtol=2e-2)
+    _status_ok()
+
+
+@pytest.mark.parametrize("splits", [1, 3])
+def test_gemm_tile192_accumulate_and_splitk(splits):
+    torch.manual_seed(1)
+    M, N, K = 384, 640, 1536
+    A = (torch.randn(M, K, device=DEV) * 0.5).to(BF)
+    B = (torch.randn(N, K, device=DEV) * 0.5).to(BF)
+    ref = A.float() @ B.float().t()
+    acc = torch.full((M, N), 2.0, device=DEV)
+    C.gemm(A, B, out=acc, accumulate=True, tile_n=192, splits=splits)
+    _status_ok()
+    assert torch.allclose(acc, ref + 2.0, rtol=1e-4, atol=5e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, BF])
+@pytest.mark.parametrize("name", ["sum", "mean", "max", "min"])
+@pytest.mark.parametrize("shape,dim", [((7, 33, 5), 1), ((6, 40), -1), ((3, 4, 5, 6), 0), ((257,), 0)])
+def test_reduce_forward_backward(name, dtype, shape, dim):
+    torch.manual_seed(3)
+    x = torch.randn(*shape, device=DEV).to(dtype)
+    xr = x.float().clone().requires_grad_(True)
+    xg = x.clone().requires_grad_(True)
+    for keepdim in (False, True):
+        y = ops.reduce(name, xg, dim, keepdim)
+        ref = getattr(torch, name)(xr, dim=dim, keepdim=keepdim)
+        ref = ref if name in ("sum", "mean") else ref.values
+        tol = dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=6e-2, rtol=2e-2)
+        assert y.shape == ref.shape and y.dtype == dtype
+        assert torch.allclose(y.float(), ref, **tol)
+    g = torch.randn_like(ref)
+    (gx,) = torch.autograd.grad(y, xg, g.to(dtype))
+    (gr,) = torch.autograd.grad(ref, xr, g)
+    assert torch.allclose(gx.float(), gr, atol=2e-2 if dtype == BF else 1e-6, rtol=2e-2 if dtype == BF else 1e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, BF])
+def test_slice_split_stack_repeat(dtype):
+    torch.manual_seed(4)
+    x = torch.randn(4, 9, 10, device=DEV).to(dtype).requires_grad_(True)
+    xr = x.detach().clone().requires_grad_(True)
+    y = ops.slice_nd(x, [1, 0, 2], [4, 9, 10], [1, 2, 3])
+    ref = xr[1:4, 0:9:2, 2:10:3]
+    assert torch.equal(y, ref.contiguous())
+    g = torch.randn_like(y)
+    assert torch.equal(torch.autograd.grad(y, x, g)[0], torch.autograd.grad(ref, xr, g)[0])
+
+    parts, rparts = ops.split(x, 4, 1), torch.split(xr, 4, 1)
+    assert len(parts) == len(rparts) == 3
+    for a, b in zip(parts, rparts):
+        assert torch.equal(a, b.contiguous())
+    gs = [torch.randn_like(a) for a in parts]
+    ga = torch.autograd.grad(parts, x, gs)[0]
+    gb = torch.autograd.grad(rparts, xr, gs)[0]
+    assert torch.equal(ga, gb)
+
+    for dim in (0, 1, 3, -1):
+        s, sr = ops.stack([x, x * 2], dim), torch.stack([xr, xr * 2], dim)
+        assert torch.equal(s, sr)
+        g = torch.randn_like(s)
+        assert torch.allclose(torch.autograd.grad(s, x, g)[0].float(), torch.autograd.grad(sr, xr, g)[0].float(),
+                              atol=2e-2, rtol=2e-2)
+
+    for dim in (0, 1, 2):
+        r, rr = ops.repeat_interleave(x, 3, dim), torch.repeat_interleave(xr, 3, dim=dim)
+        assert torch.equal(r, rr)
+        g = torch.randn_like(r)
+        assert torch.allclose(torch.autograd.grad(r, x, g)[0].float(), torch.autograd.grad(rr, xr, g)[0].float(),
+                              atol=5e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, BF])
+def test_masked_fill_and_outer(dtype):
+    torch.manual_seed(5)
+    x = torch.randn(3, 8, 8, device=DEV).to(dtype).requires_grad_(True)
+    xr = x.detach().clone().requires_grad_(True)
+    for mask in (torch.triu(torch.ones(8, 8, device=DEV), 1).bool(), torch.triu(torch.ones(8, 8, device=DEV), 1).to(dtype)):
+        y = ops.masked_fill(x, mask, -1e4)
+        ref = xr.masked_fill(mask != 0, -1e4)
+        assert torch.equal(y, ref)
+        g = torch.randn_like(y)
+        assert torch.equal(torch.autograd.grad(y, x, g)[0], torch.autograd.grad(ref, xr, g)[0])
+    a = torch.randn(37, device=DEV).to(dtype).requires_grad_(True)
+    b = torch.randn(70, device=DEV).to(dtype).requires_grad_(True)
+    ar, br = a.detach().float().requires_grad_(True), b.detach().float().requires_grad_(True)
+    o, orf = ops.outer(a, b), torch.outer(ar, br)
+    tol = dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=8e-2, rtol=2e-2)
+    assert torch.allclose(o.float(), orf, **tol)
+    g = torch.randn_like(orf)
+    da, db = torch.autograd.grad(o, (a, b), g.to(dtype))
+    dar, dbr = torch.autograd.grad(orf, (ar, br), g)
+    assert torch.allclose(da.float(), dar, **tol) and torch.allclose(db.float(), dbr, **tol)
+    _status_ok()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_zero1_bucketed_overlap_matches_single_bucket():
+    n = min(torch.cuda.device_count(), 8)
+    env = dict(os.environ, TITB_TEST_ZERO_BUCKETS="3")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29900 + os.getpid() % 90), os.path.join(HERE, "dist_zero_check.py")]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]

@@ -486,6 +486,100 @@ Tensor tri(const Tensor& x, int64_t diagonal, bool upper) {
                     cur_stream()), "tri");
   return y;
 }
+// ---------------------------------------------------------------------- reductions / view-like transforms
+// x reduced along `dim` (op: 0 sum, 1 mean, 2 max, 3 min); returns {y, idx} (idx defined for max / min only).
+std::vector<Tensor> reduce_dim(const Tensor& x_, int64_t op, int64_t dim, bool keepdim) {
+  check_cuda(x_, "x");
+  c10::cuda::CUDAGuard guard(x_.device());
+  Tensor x = x_.contiguous();
+  const int64_t nd = x.dim();
+  TORCH_CHECK(nd >= 1, "titb200 reduce: needs at least one dimension");
+  if (dim < 0) dim += nd;
+  TORCH_CHECK(dim >= 0 && dim < nd, "titb200 reduce: dim out of range");
+  int64_t outer = 1, inner = 1;
+  for (int64_t d = 0; d < dim; ++d) outer *= x.size(d);
+  for (int64_t d = dim + 1; d < nd; ++d) inner *= x.size(d);
+  auto sizes = x.sizes().vec();
+  if (keepdim) sizes[dim] = 1; else sizes.erase(sizes.begin() + dim);
+  Tensor y = at::empty(sizes, x.options());
+  Tensor idx;
+  if (op >= 2) idx = at::empty(sizes, x.options().dtype(at::kLong));
+  CHECK_RC(titb_reduce(x.data_ptr(), y.data_ptr(), idx.defined() ? reinterpret_cast<long long*>(idx.data_ptr<int64_t>()) : nullptr,
+                       outer, x.size(dim), inner, (int)op, dt_code(x), cur_stream()), "reduce");
+  return {y, idx};
+}
+Tensor reduce_dim_bwd(const Tensor& g_, const optional<Tensor>& idx_, std::vector<int64_t> in_sizes, int64_t dim, double scale) {
+  check_cuda(g_, "grad");
+  c10::cuda::CUDAGuard guard(g_.device());
+  Tensor g = g_.contiguous();
+  const int64_t nd = (int64_t)in_sizes.size();
+  if (dim < 0) dim += nd;
+  int64_t outer = 1, inner = 1;
+  for (int64_t d = 0; d < dim; ++d) outer *= in_sizes[d];
+  for (int64_t d = dim + 1; d < nd; ++d) inner *= in_sizes[d];
+  Tensor dx = at::empty(in_sizes, g.options());
+  const bool have = idx_.has_value() && idx_->defined();
+  Tensor idx = have ? idx_->contiguous() : Tensor();
+  CHECK_RC(titb_reduce_bwd(g.data_ptr(), have ? reinterpret_cast<const long long*>(idx.data_ptr<int64_t>()) : nullptr,
+                           dx.data_ptr(), outer, in_sizes[dim], inner, (float)scale, dt_code(g), cur_stream()), "reduce_bwd");
+  return dx;
+}
+// Contiguous copy of the view (sizes, strides, offset -- in elements) of `base`'s storage.
+Tensor gather_view(const Tensor& base, std::vector<int64_t> sizes, std::vector<int64_t> strides, int64_t offset) {
+  check_cuda(base, "x");
+  TORCH_CHECK(sizes.size() == strides.size() && sizes.size() <= 6, "titb200 gather_view: at most 6 dimensions");
+  c10::cuda::CUDAGuard guard(base.device());
+  Tensor out = at::empty(sizes, base.options());
+  std::vector<long long> sz(sizes.begin(), sizes.end()), st(strides.begin(), strides.end());
+  CHECK_RC(titb_gather_nd(base.data_ptr(), out.data_ptr(), (int)sz.size(), sz.data(), st.data(), offset,
+                          (int)base.element_size(), cur_stream()), "gather_view");
+  return out;
+}
+// Writes (or accumulates) the contiguous `src` into the view (sizes = src.sizes(), strides, offset) of `dst`.
+void scatter_view_(const Tensor& dst, const Tensor& src_, std::vector<int64_t> strides, int64_t offset, bool accumulate) {
+  check_cuda(dst, "dst"); check_cuda(src_, "src");
+  TORCH_CHECK(dst.scalar_type() == src_.scalar_type() && dst.is_contiguous());
+  c10::cuda::CUDAGuard guard(dst.device());
+  Tensor src = src_.contiguous();
+  TORCH_CHECK((size_t)src.dim() == strides.size() && src.dim() <= 6, "titb200 scatter_view: at most 6 dimensions");
+  std::vector<long long> sz(src.sizes().begin(), src.sizes().end()), st(strides.begin(), strides.end());
+  CHECK_RC(titb_scatter_nd(src.data_ptr(), dst.data_ptr(), (int)sz.size(), sz.data(), st.data(), offset, dt_code(dst),
+                           accumulate, cur_stream()), "scatter_view");
+}
+Tensor mask_fill(const Tensor& x_, const Tensor& mask_, double value, bool backward) {
+  check_cuda(x_, "x"); check_cuda(mask_, "mask");
+  c10::cuda::CUDAGuard guard(x_.device());
+  Tensor x = x_.contiguous(), mask = mask_.contiguous();
+  int mdt;
+  if (mask.scalar_type() == at::kFloat) mdt = 0;
+  else if (mask.scalar_type() == at::kBFloat16) mdt = 1;
+  else if (mask.scalar_type() == at::kBool || mask.scalar_type() == at::kByte) mdt = 2;
+  else TORCH_CHECK(false, "titb200 mask_fill: mask must be float32, bfloat16, bool or uint8");
+  TORCH_CHECK(mask.numel() > 0 && x.numel() % mask.numel() == 0, "titb200 mask_fill: mask must tile the trailing dims");
+  Tensor y = at::empty_like(x);
+  CHECK_RC(titb_mask_fill(x.data_ptr(), mask.data_ptr(), y.data_ptr(), x.numel(), mask.numel(), (float)value, backward,
+                          dt_code(x), mdt, cur_stream()), "mask_fill");
+  return y;
+}
+Tensor outer_fwd(const Tensor& a_, const Tensor& b_) {
+  check_cuda(a_, "a"); check_cuda(b_, "b");
+  TORCH_CHECK(a_.dim() == 1 && b_.dim() == 1 && a_.scalar_type() == b_.scalar_type());
+  c10::cuda::CUDAGuard guard(a_.device());
+  Tensor a = a_.contiguous(), b = b_.contiguous();
+  Tensor y = at::empty({a.numel(), b.numel()}, a.options());
+  CHECK_RC(titb_outer(a.data_ptr(), b.data_ptr(), y.data_ptr(), a.numel(), b.numel(), dt_code(a), cur_stream()), "outer");
+  return y;
+}
+std::vector<Tensor> outer_bwd(const Tensor& g_, const Tensor& a_, const Tensor& b_) {
+  check_cuda(g_, "grad");
+  c10::cuda::CUDAGuard guard(g_.device());
+  Tensor g = g_.contiguous(), a = a_.contiguous(), b = b_.contiguous();
+  Tensor da = at::empty_like(a), db = at::empty_like(b);
+  CHECK_RC(titb_outer_bwd(g.data_ptr(), a.data_ptr(), b.data_ptr(), da.data_ptr(), db.data_ptr(), a.numel(), b.numel(),
+                          dt_code(g), cur_stream()), "outer_bwd", 2);
+  return {da, db};
+}
+
 // Column sums of a [rows, C] view into an fp32 [C] tensor (bias gradients).
 Tensor colsum(const Tensor& x, const optional<Tensor>& out_, bool accumulate) {
   check_cuda(x, "x");
@@ -522,6 +616,15 @@ PYBIND11_MODULE(_C, m) {
         py::arg("want_aux_out") = false, py::arg("helper_ctas") = 16);
   m.def("gemm_rs", &gemm_rs, py::arg("a"), py::arg("b"), py::arg("b_mn"), py::arg("recv_ptrs"), py::arg("cnt_ptrs"),
         py::arg("rank"), py::arg("bias") = py::none(), py::arg("residual") = py::none(), py::arg("helper_ctas") = 8);
+  m.def("reduce_dim", &reduce_dim, py::arg("x"), py::arg("op"), py::arg("dim"), py::arg("keepdim") = false);
+  m.def("reduce_dim_bwd", &reduce_dim_bwd, py::arg("g"), py::arg("idx"), py::arg("in_sizes"), py::arg("dim"),
+        py::arg("scale") = 1.0);
+  m.def("gather_view", &gather_view);
+  m.def("scatter_view_", &scatter_view_, py::arg("dst"), py::arg("src"), py::arg("strides"), py::arg("offset"),
+        py::arg("accumulate") = false);
+  m.def("mask_fill", &mask_fill, py::arg("x"), py::arg("mask"), py::arg("value"), py::arg("backward") = false);
+  m.def("outer_fwd", &outer_fwd);
+  m.def("outer_bwd", &outer_bwd);
   m.def("sgemm", &sgemm, py::arg("a"), py::arg("b"), py::arg("ta") = false, py::arg("tb") = false,
         py::arg("out") = py::none(), py::arg("accumulate") = false);
   m.def("layernorm_fwd", &layernorm_fwd);

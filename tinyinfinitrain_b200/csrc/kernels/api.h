@@ -196,6 +196,29 @@ TITB_API int titb_colsum(const void* x, float* out, long long rows, int C, int d
                          float* scratch, cudaStream_t stream);
 TITB_API int titb_colsum_blocks(long long rows);
 
+// ---- reductions and view-like transforms (dtype: 0 = fp32, 1 = bf16) ---------------------------------
+// x viewed as [outer, n, inner] -> y [outer, inner].  op: 0 sum, 1 mean, 2 max, 3 min; for max / min `idx`
+// (may be null) receives the position along n of the selected element (lowest index on ties).
+TITB_API int titb_reduce(const void* x, void* y, long long* idx, long long outer, long long n, long long inner, int op,
+                         int dtype, cudaStream_t stream);
+// dx[o, i, in] = g[o, in] * scale when idx is null, else g[o, in] where i == idx[o, in] and 0 elsewhere.
+TITB_API int titb_reduce_bwd(const void* g, const long long* idx, void* dx, long long outer, long long n,
+                             long long inner, float scale, int dtype, cudaStream_t stream);
+// out (contiguous, row-major over size[0..nd)) <- in[in_offset + sum_d i_d * in_stride[d]]; nd <= 6.
+// Strides are in elements, 0 repeats an element; elem_bytes in {2, 4, 8}.
+TITB_API int titb_gather_nd(const void* in, void* out, int nd, const long long* size, const long long* in_stride,
+                            long long in_offset, int elem_bytes, cudaStream_t stream);
+// out[out_offset + sum_d i_d * out_stride[d]] <- (or +=, with atomics) in (contiguous); nd <= 6.
+TITB_API int titb_scatter_nd(const void* in, void* out, int nd, const long long* size, const long long* out_stride,
+                             long long out_offset, int dtype, int accumulate, cudaStream_t stream);
+// forward (backward = 0): y = mask ? value : x;  backward = 1: y = mask ? 0 : x.  The mask has mask_n
+// elements and repeats over the leading extent of x (n % mask_n == 0).  mask_dtype: 0 fp32, 1 bf16, 2 uint8/bool.
+TITB_API int titb_mask_fill(const void* x, const void* mask, void* y, long long n, long long mask_n, float value,
+                            int backward, int dtype, int mask_dtype, cudaStream_t stream);
+TITB_API int titb_outer(const void* a, const void* b, void* y, long long M, long long N, int dtype, cudaStream_t stream);
+TITB_API int titb_outer_bwd(const void* g, const void* a, const void* b, void* da, void* db, long long M, long long N,
+                            int dtype, cudaStream_t stream);
+
 // ---- attention --------------------------------------------------------------------------------------
 // Causal self-attention over packed projections.  q: [B, T, Hq, hd], k/v: [B, T, Hkv, hd] with
 // arbitrary (16-byte aligned) token strides so a fused QKV buffer can be addressed in place.

@@ -15,6 +15,8 @@
 #include <cuda_runtime.h>
 #include <stdio.h>
 
+#include <cstdlib>
+
 #include "api.h"
 #include "ptx_sm100.cuh"
 
@@ -70,8 +72,9 @@ struct GemmArgs {
 template <int BN>
 struct GemmCfg {
   static constexpr int kBBytes = BN * kBK * 2;
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
-  static constexpr int kTmemCols = 2 * BN;
+  static constexpr int kStages = (BN == 128) ? 6 : 4;
+  static constexpr int kAccStride = (BN == 128) ? 128 : 256;  // TMEM columns between the two accumulators
+  static constexpr int kTmemCols = 2 * kAccStride;            // allocation size must be a power of two
   static constexpr int kRing = kStages * (kABytes + kBBytes);
   static constexpr int kStage = 2 * kBM * 128;  // two [128 rows x 64 bf16] swizzled staging tiles for TMA stores
   static constexpr int kSmem = kRing + kStage + 1024 /*alignment slack*/ + 256 /*barriers*/;
@@ -482,7 +485,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
         const uint32_t acc_phase = (it >> 1) & 1;
         if (!ptx::mbar_wait(&acc_empty[buf], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
         ptx::tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + buf * BN;
+        const uint32_t d_tmem = tmem_base + buf * Cfg::kAccStride;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!ptx::mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
           ptx::tc_fence_after_sync();
@@ -529,7 +532,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
         if (!ptx::mbar_wait(&acc_full[buf], acc_phase, abort_flag)) break;
         ptx::tc_fence_after_sync();
         const long long row = m0 + trow;
-        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN;
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * Cfg::kAccStride;
 #pragma unroll 1
         for (int c = 0; c < BN / 64; ++c) {
           const int col0 = n0 + c * 64;
@@ -666,7 +669,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       if (!ptx::mbar_wait(&acc_full[buf], acc_phase, abort_flag)) break;
       ptx::tc_fence_after_sync();
       const long long row = m0 + quad * 32 + lane;
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * Cfg::kAccStride;
 #pragma unroll 1
       for (int c = 0; c < (p.epi == 101 ? 0 : BN / 32); ++c) {  // 101: timing probe without any epilogue work
         uint32_t r[32];
@@ -818,7 +821,13 @@ static int pick_tile_n(int M, int N, int splits) {
     return waves * bn;
   };
   if (N <= 128) return 128;
-  return (cost(128) * 2 < cost(256)) ? 128 : 256;
+  // 128 x 192 tiles cut the tail of the last wave for widths such as 768 and 3072 (6 x 128).  They are
+  // opt-in (TITB200_GEMM_TILE192=1, or tile_n = 192 per call) and then taken when they save more than 5%
+  // of the wave-quantised cost of 128 x 256.
+  static const bool allow192 = [] { const char* e = getenv("TITB200_GEMM_TILE192"); return e && e[0] == '1'; }();
+  const long long c256 = cost(256), c192 = allow192 ? cost(192) : (1LL << 60), c128 = cost(128);
+  if (c128 * 2 < c256 && c128 * 2 < c192) return 128;
+  return (c192 * 100 < c256 * 95) ? 192 : 256;
 }
 
 }  // namespace titb
@@ -975,7 +984,10 @@ TITB_API int titb_gemm_bf16(const TitbGemmDesc* d, cudaStream_t stream) {
         !(reinterpret_cast<uintptr_t>(d->aux_in) & 15) && !(d->ld_aux_in & 7))
       a.aux_tma_load = make_tmap_bf16_2d(&taux, d->aux_in, d->N, d->M, d->ld_aux_in, 64, kBM) ? 1 : 0;
   }
-  int rc = (bn == 256) ? launch_gemm<256>(ta, tb, tout, taux, a, stream) : launch_gemm<128>(ta, tb, tout, taux, a, stream);
+  if (bn != 128 && bn != 192 && bn != 256) return TITB_ERR_SHAPE;
+  int rc = (bn == 256)   ? launch_gemm<256>(ta, tb, tout, taux, a, stream)
+           : (bn == 192) ? launch_gemm<192>(ta, tb, tout, taux, a, stream)
+                         : launch_gemm<128>(ta, tb, tout, taux, a, stream);
   if (rc != 0) return rc;
   if (splits > 1) {
     const long long total = static_cast<long long>(d->M) * d->N;

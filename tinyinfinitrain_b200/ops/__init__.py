@@ -4,4 +4,5 @@ from .functional import (  # noqa: F401
     attention_ref, binary, cast, causal_attention, causal_attention_qkv, cross_entropy, embedding, gelu, gelu_ref, layernorm, linear,
     lm_head_loss, matmul, mlp_gelu, rmsnorm, rmsnorm_ref, rope, rope_qkv, rope_ref, set_attention_impl, softmax, swiglu,
     transpose, tril, triu, unary,
+    masked_fill, max_dim, mean_dim, min_dim, outer, reduce, repeat_interleave, slice_nd, split, stack, sum_dim,
 )

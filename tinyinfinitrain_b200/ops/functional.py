@@ -804,3 +804,188 @@ def triu(x, diagonal: int = 0):
     if x.is_cuda and x.dim() == 2 and x.dtype in (torch.float32, _bf16):
         return _TriFn.apply(x, diagonal, True)
     return torch.triu(x, diagonal)
+
+
+# ----------------------------------------------------------------------------- reductions along one axis
+_REDUCE_OPS = {"sum": 0, "mean": 1, "max": 2, "min": 3}
+
+
+def _own_kernel_ok(x) -> bool:
+    return x.is_cuda and x.dtype in (torch.float32, _bf16)
+
+
+class _ReduceFn(torch.autograd.Function):
+    """Mean / Sum / Max / Min over one axis (reference: infini_train/src/autograd/reduction.cc,
+    kernels/cuda/reduction.cu).  Max / Min route the gradient to the selected element only."""
+
+    @staticmethod
+    def forward(ctx, x, op, dim, keepdim):
+        y, idx = C.reduce_dim(x, op, dim, keepdim)
+        ctx.meta = (op, dim % x.dim(), tuple(x.shape))
+        ctx.idx = idx
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        op, dim, shape = ctx.meta
+        scale = 1.0 / shape[dim] if op == 1 else 1.0
+        return C.reduce_dim_bwd(dy, ctx.idx, list(shape), dim, scale), None, None, None
+
+
+def reduce(name: str, x, dim: int, keepdim: bool = False):
+    if _own_kernel_ok(x) and x.dim() >= 1:
+        return _ReduceFn.apply(x, _REDUCE_OPS[name], dim, keepdim)
+    if name in ("sum", "mean"):
+        return getattr(torch, name)(x, dim=dim, keepdim=keepdim)
+    return getattr(torch, name)(x, dim=dim, keepdim=keepdim).values
+
+
+def sum_dim(x, dim: int, keepdim: bool = False):
+    return reduce("sum", x, dim, keepdim)
+
+
+def mean_dim(x, dim: int, keepdim: bool = False):
+    return reduce("mean", x, dim, keepdim)
+
+
+def max_dim(x, dim: int, keepdim: bool = False):
+    return reduce("max", x, dim, keepdim)
+
+
+def min_dim(x, dim: int, keepdim: bool = False):
+    return reduce("min", x, dim, keepdim)
+
+
+# ----------------------------------------------------------------------------- view-like ops through one gather kernel
+def _contig_strides(shape):
+    st, acc = [], 1
+    for s in reversed(shape):
+        st.append(acc)
+        acc *= s
+    return list(reversed(st))
+
+
+class _GatherViewFn(torch.autograd.Function):
+    """Materialises a strided view (sizes, strides, offset over a contiguous input).  The backward
+    scatters into a zero tensor, accumulating when the view repeats elements (stride 0)."""
+
+    @staticmethod
+    def forward(ctx, x, sizes, strides, offset):
+        xc = x.contiguous()
+        ctx.meta = (tuple(x.shape), list(strides), offset)
+        return C.gather_view(xc, list(sizes), list(strides), offset)
+
+    @staticmethod
+    def backward(ctx, dy):
+        shape, strides, offset = ctx.meta
+        dx = torch.zeros(shape, device=dy.device, dtype=dy.dtype)
+        C.scatter_view_(dx, dy, strides, offset, accumulate=any(s == 0 for s in strides))
+        return dx, None, None, None
+
+
+def slice_nd(x, starts, ends, steps):
+    """Per-dimension [start, end) with step (reference: infini_train/src/kernels/cuda/slice.cu)."""
+    if not (_own_kernel_ok(x) and x.dim() <= 6):
+        idx = tuple(slice(s, e, st) for s, e, st in zip(starts, ends, steps))
+        return x[idx].contiguous()
+    base = _contig_strides(x.shape)
+    sizes = [(e - s + st - 1) // st for s, e, st in zip(starts, ends, steps)]
+    strides = [b * st for b, st in zip(base, steps)]
+    offset = sum(s * b for s, b in zip(starts, base))
+    return _GatherViewFn.apply(x, sizes, strides, offset)
+
+
+def split(x, split_size: int, dim: int = 0):
+    """Equal chunks of ``split_size`` along ``dim`` (the last may be shorter); each a contiguous tensor."""
+    dim = dim % x.dim()
+    n = x.shape[dim]
+    outs = []
+    for s in range(0, n, split_size):
+        starts = [0] * x.dim()
+        ends = list(x.shape)
+        starts[dim], ends[dim] = s, min(s + split_size, n)
+        outs.append(slice_nd(x, starts, ends, [1] * x.dim()))
+    return outs
+
+
+def repeat_interleave(x, repeats: int, dim: int):
+    """Each element along ``dim`` repeated ``repeats`` times in place (reference transform.cu RepeatInterleave)."""
+    dim = dim % x.dim()
+    if not (_own_kernel_ok(x) and x.dim() <= 5):
+        return torch.repeat_interleave(x, repeats, dim=dim)
+    base = _contig_strides(x.shape)
+    sizes = list(x.shape[:dim + 1]) + [repeats] + list(x.shape[dim + 1:])
+    strides = base[:dim + 1] + [0] + base[dim + 1:]
+    out = _GatherViewFn.apply(x, sizes, strides, 0)
+    shape = list(x.shape)
+    shape[dim] *= repeats
+    return out.view(shape)
+
+
+class _StackFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, dim, *xs):
+        shape = list(xs[0].shape)
+        n = len(xs)
+        out_shape = shape[:dim] + [n] + shape[dim:]
+        out = torch.empty(out_shape, device=xs[0].device, dtype=xs[0].dtype)
+        ost = _contig_strides(out_shape)
+        view_strides = ost[:dim] + ost[dim + 1:]
+        for i, x in enumerate(xs):
+            C.scatter_view_(out, x.contiguous(), view_strides, i * ost[dim], False)
+        ctx.meta = (dim, n, shape, view_strides, ost[dim])
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        dim, n, shape, view_strides, step = ctx.meta
+        dyc = dy.contiguous()
+        return (None,) + tuple(C.gather_view(dyc, shape, view_strides, i * step) for i in range(n))
+
+
+def stack(xs, dim: int = 0):
+    xs = list(xs)
+    nd = xs[0].dim() + 1
+    dim = dim % nd
+    if all(_own_kernel_ok(x) for x in xs) and nd <= 6:
+        return _StackFn.apply(dim, *xs)
+    return torch.stack(xs, dim)
+
+
+class _MaskFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, mask, value):
+        ctx.save_for_backward(mask)
+        return C.mask_fill(x, mask, value, False)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (mask,) = ctx.saved_tensors
+        return C.mask_fill(dy, mask, 0.0, True), None, None
+
+
+def masked_fill(x, mask, value: float):
+    """``mask != 0 ? value : x``; the mask tiles the trailing dimensions of ``x`` (reference transform.cu Mask)."""
+    if _own_kernel_ok(x) and mask.is_cuda and x.numel() % max(1, mask.numel()) == 0 and \
+            tuple(mask.shape) == tuple(x.shape[x.dim() - mask.dim():]):
+        return _MaskFn.apply(x, mask, float(value))
+    return x.masked_fill(mask != 0, value)
+
+
+class _OuterFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a, b):
+        ctx.save_for_backward(a, b)
+        return C.outer_fwd(a, b)
+
+    @staticmethod
+    def backward(ctx, dy):
+        a, b = ctx.saved_tensors
+        da, db = C.outer_bwd(dy, a, b)
+        return da, db
+
+
+def outer(a, b):
+    if _own_kernel_ok(a) and _own_kernel_ok(b) and a.dtype == b.dtype and a.dim() == 1 and b.dim() == 1:
+        return _OuterFn.apply(a, b)
+    return torch.outer(a, b)

@@ -5,8 +5,14 @@ place by the wgrad kernels); optimizer state (fp32 master weights, Adam moments)
 rank r owns elements ``[r*S, (r+1)*S)`` of the flat parameter space.
 
 ``comm="fused"`` (default on GPUs): gradient and parameter buffers live in symmetric memory and
-one kernel per step does reduce-scatter + scale + Adam + parameter all-gather over NVLink
-(``csrc/kernels/comm.cu: rs_adam_ag_kernel``), bracketed by two device-side barriers.
+one kernel per bucket does reduce-scatter + scale + Adam + parameter all-gather over NVLink
+(``csrc/kernels/comm.cu: rs_adam_ag_kernel``).  The flat space is cut into ``num_buckets``
+contiguous buckets on parameter boundaries, each sharded over the ranks; as soon as backward has
+produced every gradient of a bucket (the wgrad kernels report it through ``_on_grad_ready``) its
+barrier + fused kernel are enqueued on a side stream, so the NVLink traffic and the optimizer math
+of the deep layers run underneath the backward pass of the shallow ones.  The bucket holding the
+tied embedding (written twice) and anything not reported are handled in ``step()``.  The default
+is one bucket reduced in ``step()``; ``num_buckets > 1`` with ``overlap=True`` turns the overlap on.
 ``comm="nccl"``: the unfused baseline -- ``reduce_scatter_tensor``, local fused Adam,
 ``all_gather_into_tensor``.  On CPU (gloo) the same sharding logic runs with torch ops, which is
 what the CPU multi-process tests exercise.
@@ -23,7 +29,8 @@ from ..optim.optimizers import FlatParams
 
 class DistributedOptimizer:
     def __init__(self, params, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.0,
-                 group: Optional[dist.ProcessGroup] = None, comm: str = "fused", average: bool = True):
+                 group: Optional[dist.ProcessGroup] = None, comm: str = "fused", average: bool = True,
+                 num_buckets: int = 1, overlap: bool = False):
         plist = [p for p in params]
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
@@ -53,12 +60,21 @@ class DistributedOptimizer:
         assert f.total == total and total % self.world == 0
         self.shard_n = total // self.world
         self.shard_off = self.rank * self.shard_n
+        self.overlap = overlap and self.comm == "fused"
+        self.side_blocks = 64  # CTAs of a bucket kernel that runs beside backward (leaves SMs to the GEMMs)
+        self._plan_buckets(num_buckets if self.comm == "fused" else 1)
         # all ranks must start from identical parameters: broadcast rank 0's flat buffer
         dist.broadcast(f.param, src=dist.get_global_rank(self.group, 0) if self.group is not dist.group.WORLD else 0,
                        group=self.group)
-        sl = slice(self.shard_off, self.shard_off + self.shard_n)
         self.mixed = f.dtype != torch.float32
-        self.master = f.param[sl].float().clone()
+        if self.comm == "fused":
+            # local state = this rank's slice of every bucket, concatenated
+            pieces = [f.param[b["start"] + self.rank * b["shard"]: b["start"] + (self.rank + 1) * b["shard"]]
+                      for b in self.buckets]
+            self.master = torch.cat([x.float() for x in pieces]).contiguous()
+        else:
+            sl = slice(self.shard_off, self.shard_off + self.shard_n)
+            self.master = f.param[sl].float().clone()
         self.m = torch.zeros(self.shard_n, device=dev, dtype=torch.float32)
         self.v = torch.zeros(self.shard_n, device=dev, dtype=torch.float32)
         self.dev_state = torch.tensor([0.0, 0.0, 0.0, lr], device=dev, dtype=torch.float32) if self.is_cuda else None
@@ -66,6 +82,86 @@ class DistributedOptimizer:
         if self.is_cuda:
             torch.cuda.synchronize(dev)
         dist.barrier(group=self.group)
+
+    # ---- buckets -----------------------------------------------------------------------------------
+    def _plan_buckets(self, nb: int) -> None:
+        """Cuts [0, total) into up to ``nb`` buckets on parameter boundaries (offsets are multiples of
+        128 elements, so every bucket divides evenly over up to 16 ranks in 8-element units)."""
+        f = self.flat
+        target = max(1, f.total // max(1, nb))
+        bounds = [0]
+        for p, off in zip(f.params, f.offsets):
+            if off - bounds[-1] >= target and len(bounds) < nb:
+                bounds.append(off)
+        bounds.append(f.total)
+        self.buckets = []
+        local = 0
+        for i in range(len(bounds) - 1):
+            s, e = bounds[i], bounds[i + 1]
+            shard = (e - s) // self.world
+            self.buckets.append({"start": s, "end": e, "shard": shard, "local": local, "params": [], "pending": 0,
+                                 "launched": False, "late": False})
+            local += shard
+        for p, off in zip(f.params, f.offsets):
+            for b in self.buckets:
+                if b["start"] <= off < b["end"]:
+                    b["params"].append(p)
+                    p._bucket = b
+                    break
+        if self.overlap:
+            self.comm_stream = torch.cuda.Stream(device=f.device)
+            for p in f.params:
+                p._on_grad_ready = self._grad_ready
+                p._expected = None  # reports per step, learned from the first step
+        self._learned = False
+
+    def _reset_pending(self) -> None:
+        for b in self.buckets:
+            b["pending"] = sum(p._expected for p in b["params"]) if self._learned else -1
+            b["launched"] = False
+        for p in self.flat.params:
+            p._reports = 0
+        self._ticked = False
+
+    def _grad_ready(self, p) -> None:
+        """Called by the kernel wrappers right after the launch that wrote ``p.main_grad``.  The first
+        step only counts reports per parameter (a tied embedding reports twice, gradient accumulation
+        multiplies every count); later steps launch a bucket when its last expected report arrives."""
+        p._reports += 1
+        if not self._learned:
+            return
+        b = p._bucket
+        b["pending"] -= 1
+        if b["pending"] == 0 and not b["late"] and not b["launched"]:
+            self._launch_bucket(b, side=True)
+
+    def _finish_learning(self) -> None:
+        for p in self.flat.params:
+            p._expected = p._reports
+        for b in self.buckets:
+            # a parameter that never reports (gradient through plain autograd) keeps its bucket for step()
+            b["late"] = any(p._expected == 0 for p in b["params"])
+        self._learned = True
+
+    def _launch_bucket(self, b, side: bool) -> None:
+        from .._lib import C
+
+        b1, b2 = self.betas
+        main = torch.cuda.current_stream(self.flat.device)
+        stream = self.comm_stream if (side and self.overlap) else main
+        if stream is not main:
+            stream.wait_stream(main)
+        with torch.cuda.stream(stream):
+            if not self._ticked:
+                C.adam_tick(self.dev_state, b1, b2)
+                self._ticked = True
+            self.barrier()  # every rank has written this bucket's gradients
+            lo, n = b["local"], b["shard"]
+            C.rs_adam_ag(self.gbuf.ptrs, self.pbuf.ptrs, self.gbuf.mc_ptr, self.pbuf.mc_ptr, self.master[lo:lo + n],
+                         self.m[lo:lo + n], self.v[lo:lo + n], b["start"] + self.rank * n, self.rank, self.lr, b1, b2,
+                         self.eps, self.weight_decay, self.t + 1, self.grad_scale, self.dev_state,
+                         self.side_blocks if stream is not main else 0)
+        b["launched"] = True
 
     @staticmethod
     def _flat_size(plist, align: int) -> int:
@@ -88,6 +184,8 @@ class DistributedOptimizer:
 
     def zero_grad(self, set_to_none: bool = True) -> None:
         self.flat.mark_fresh()
+        if self.comm == "fused":
+            self._reset_pending()
 
     ZeroGrad = zero_grad
 
@@ -100,12 +198,21 @@ class DistributedOptimizer:
         self.t += 1
         b1, b2 = self.betas
         if self.comm == "fused":
-            C.adam_tick(self.dev_state, b1, b2)
-            self.barrier()  # every rank has finished writing its gradients (and reading its parameters)
-            C.rs_adam_ag(self.gbuf.ptrs, self.pbuf.ptrs, self.gbuf.mc_ptr, self.pbuf.mc_ptr, self.master, self.m,
-                         self.v, self.shard_off, self.rank, self.lr, b1, b2, self.eps, self.weight_decay, self.t,
-                         self.grad_scale, self.dev_state)
+            self.t -= 1  # buckets launched during backward used t + 1 already
+            if not hasattr(self, "_ticked"):
+                self._reset_pending()
+            main = torch.cuda.current_stream(f.device)
+            for b in self.buckets:
+                if not b["launched"]:
+                    # same stream as the early buckets: the barrier channel is used by one stream at a time
+                    self._launch_bucket(b, side=True)
+            if self.overlap:
+                main.wait_stream(self.comm_stream)
+                if not self._learned:
+                    self._finish_learning()
+            self.t += 1
             self.barrier()  # every shard of the new parameters has landed everywhere; gradients may be reused
+            self._reset_pending()
             return
         dist.reduce_scatter_tensor(self._gshard, f.grad, op=dist.ReduceOp.SUM, group=self.group) \
             if self.is_cuda else self._cpu_reduce_scatter()

@@ -5,6 +5,12 @@ the ncu captures summarised under ``profiles/`` run.
 
     python -m tinyinfinitrain_b200.utils.kernel_bench gemm --m 8192 --n 3072 --k 768
     python -m tinyinfinitrain_b200.utils.kernel_bench attn_bwd --b 8 --t 1024 --h 12 --hd 64
+
+The fused compute+collective kernels can be run on ONE GPU for profiling: ``ag_gemm`` and
+``rs_adam`` take ``--world W`` and treat W local buffers as the peers (every load and store a
+rank would send over NVLink goes to local memory instead, the instruction stream is the one the
+multi-GPU run executes; ``rs_adam`` uses plain peer loads/stores, not multimem);
+``gemm_rs`` runs as a group of one rank (its own partial tiles are the only ones it waits for).
 """
 from __future__ import annotations
 
@@ -47,7 +53,9 @@ def main():
 
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel", choices=["gemm", "gemm_nt", "gemm_wgrad", "attn_fwd", "attn_bwd", "layernorm_fwd", "layernorm_bwd",
-                                       "xent", "adam", "gelu_gemm"])
+                                       "xent", "adam", "gelu_gemm", "ag_gemm", "gemm_rs", "rs_adam"])
+    ap.add_argument("--world", type=int, default=4)
+    ap.add_argument("--helpers", type=int, default=0)
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=3072)
     ap.add_argument("--k", type=int, default=768)
@@ -112,6 +120,35 @@ def main():
             dy = torch.randn_like(x)
             bytes_ = 3.0 * x.numel() * 2
             fn = lambda: C.layernorm_bwd(dy, x, w, mean, rstd)
+    elif a.kernel == "ag_gemm":
+        # X = concat of W shards [M/W, K]; Y = X . B^T, B [N, K]
+        M, N, K, W = a.m, a.n, a.k, a.world
+        shards = [torch.randn(M // W, K, device=dev).to(bf) for _ in range(W)]
+        B = torch.randn(N, K, device=dev).to(bf)
+        flops = 2.0 * M * N * K
+        bytes_ = 2.0 * (2 * M * K + N * K + M * N)
+        ptrs = [t.data_ptr() for t in shards]
+        fn = lambda: C.gemm_ag(ptrs, 0, M // W, K, B, False, 0, None, False, a.helpers or 16)
+    elif a.kernel == "gemm_rs":
+        M, N, K = a.m, a.n, a.k
+        A, B = torch.randn(M, K, device=dev).to(bf), torch.randn(N, K, device=dev).to(bf)
+        recv = torch.empty(M, N, device=dev, dtype=bf)
+        cnt = torch.zeros(max(128, M // 128 + 1), device=dev, dtype=torch.int32)
+        flops = 2.0 * M * N * K
+        bytes_ = 2.0 * (M * K + N * K + 3 * M * N)
+        fn = lambda: C.gemm_rs(A, B, False, [recv.data_ptr()], [cnt.data_ptr()], 0, None, None,
+                               min(a.helpers or 8, M // 128))
+    elif a.kernel == "rs_adam":
+        n, W = a.m * a.n, a.world
+        n -= n % (8 * W * 16)
+        S = n // W
+        grads = [torch.randn(n, device=dev) for _ in range(W)]
+        params = [torch.empty(n, device=dev, dtype=bf) for _ in range(W)]
+        master, m, v = torch.randn(S, device=dev), torch.zeros(S, device=dev), torch.zeros(S, device=dev)
+        # per launch: W gradient shards read, fp32 state read + written, W bf16 parameter shards written
+        bytes_ = S * (4.0 * W + 3 * 4 * 2 + 2.0 * W)
+        gp, pp = [t.data_ptr() for t in grads], [t.data_ptr() for t in params]
+        fn = lambda: C.rs_adam_ag(gp, pp, 0, 0, master, m, v, 0, 0, 1e-3, 0.9, 0.999, 1e-8, 0.0, 1, 1.0 / W)
     elif a.kernel == "xent":
         logits = torch.randn(a.m, a.n, device=dev).to(bf)
         tgt = torch.randint(0, a.n - 47, (a.m,), device=dev)
