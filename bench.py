@@ -26,6 +26,8 @@ def reference_arm(args):
     # The reference tree has no setup.py/pyproject.toml, its four submodules (glog, gflags, eigen,
     # googletest) are empty directories, and 13 of its functions are unimplemented stubs, so it can
     # neither be installed nor built offline.
+    if int(os.environ.get("RANK", "0")) != 0:  # under torchrun only rank 0 reports
+        return 0
     print(json.dumps({"impl": "reference",
                       "unavailable": "reference is not installable (no setup.py/pyproject.toml; pip: 'Neither setup.py "
                                      "nor pyproject.toml found'), its third_party submodules are empty and its kernel "
@@ -38,13 +40,18 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "library"],
+                    help="ours: this framework; reference: the unmodified reference (unavailable, see above); "
+                         "library: stock PyTorch modules (cuBLAS, SDPA, fused AdamW, DDP/NCCL) on the same config")
     ap.add_argument("--model", default="gpt2")
     ap.add_argument("--batch", type=int, default=8, help="micro-batch per GPU")
     ap.add_argument("--seq", type=int, default=1024)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--dp_buckets", type=int, default=1,
                     help="ZeRO-1 buckets; >1 reduces each bucket on a side stream as soon as backward has written it")
+    ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"],
+                    help="cpu = dry run of this script's control flow (gloo ranks, fp32, wall-clock timing); not a benchmark")
+    ap.add_argument("--tiny", action="store_true", help="2-layer 64-wide model for dry runs (reported as such)")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"],
                     help="gradient reduce-scatter + Adam + parameter all-gather: own NVLink kernels or plain NCCL")
     args = ap.parse_args()
@@ -61,8 +68,11 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     assert world == args.gpus or world == 1 and args.gpus == 1, f"--gpus {args.gpus} but WORLD_SIZE={world}"
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
+    on_gpu = args.device == "cuda"
+    if on_gpu:
+        torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank) if on_gpu else torch.device("cpu")
+    dtype = torch.bfloat16 if on_gpu else torch.float32
     W = max(3, args.warmup)
     K = args.steps
 
@@ -71,46 +81,74 @@ def main():
         import torch.distributed as dist
 
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        if on_gpu:
+            dist.init_process_group("nccl", device_id=dev)
+        else:
+            dist.init_process_group("gloo")
         from tinyinfinitrain_b200 import parallel
 
         dp = parallel
 
     cfg = GPT2_PRESETS[args.model]
-    model = GPT2(cfg, device=dev, dtype=torch.bfloat16, seed=42)
+    if args.tiny:
+        from tinyinfinitrain_b200.models import GPT2Config
+
+        cfg = GPT2Config(block_size=args.seq, vocab_size=1000, n_layer=2, n_head=2, n_embd=64)
     B, T = args.batch, args.seq
-    if dp is None:
-        opt = tit.optim.MixedPrecisionAdam(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1)
-        grad_sync = None
+    library = args.impl == "library"
+    if library:
+        from baseline.library_gpt2 import LibraryGPT2, LibraryTrainStep
+
+        model = LibraryGPT2(cfg.vocab_size, cfg.padded_vocab_size, cfg.block_size, cfg.n_layer, cfg.n_head,
+                            cfg.n_embd).to(dev)
+        step = LibraryTrainStep(model, B, T, dev, world)
     else:
-        opt = dp.DistributedOptimizer(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1,
-                                      comm=args.comm, num_buckets=args.dp_buckets, overlap=args.dp_buckets > 1)
-        grad_sync = None  # the distributed optimizer's step() owns reduce-scatter / Adam / all-gather
-    # the NCCL baseline arm runs eagerly: its collectives are library calls issued per step, not captured
-    use_graph = not args.no_graph and (world == 1 or args.comm == "fused")
-    step = TrainStep(model, opt, B, T, dev, use_graph=use_graph, grad_sync=grad_sync)
+        model = GPT2(cfg, device=dev, dtype=dtype, seed=42)
+        if dp is None:
+            opt = tit.optim.MixedPrecisionAdam(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1)
+        else:
+            # the distributed optimizer's step() owns reduce-scatter / Adam / all-gather
+            opt = dp.DistributedOptimizer(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1,
+                                          comm=args.comm, num_buckets=args.dp_buckets, overlap=args.dp_buckets > 1)
+        # the NCCL baseline arm runs eagerly: its collectives are library calls issued per step, not captured
+        use_graph = not args.no_graph and (world == 1 or args.comm == "fused")
+        step = TrainStep(model, opt, B, T, dev, use_graph=use_graph)
 
     # synthetic uniform token ids, seed 0 (+rank so every rank sees different data), pinned on the host
     nbuf = 4
     gen = torch.Generator().manual_seed(0 + rank)
-    host_idx = [torch.randint(0, cfg.vocab_size, (B, T), generator=gen).pin_memory() for _ in range(nbuf)]
-    host_tgt = [torch.roll(x, -1, dims=1).pin_memory() for x in host_idx]
+    pin = (lambda t: t.pin_memory()) if on_gpu else (lambda t: t)
+    host_idx = [pin(torch.randint(0, cfg.vocab_size, (B, T), generator=gen)) for _ in range(nbuf)]
+    host_tgt = [pin(torch.roll(x, -1, dims=1)) for x in host_idx]
     step.idx.copy_(host_idx[0]); step.tgt.copy_(host_tgt[0])
-    step.prepare()
+    if not library:
+        step.prepare()
 
     def barrier():
         if world > 1:
             import torch.distributed as dist
 
             dist.barrier()
-        torch.cuda.synchronize(dev)
+        if on_gpu:
+            torch.cuda.synchronize(dev)
+
+    class WallEvent:  # stands in for a CUDA event on the CPU dry run
+        def record(self):
+            self.t = time.perf_counter()
+
+        def elapsed_time(self, other):
+            return (other.t - self.t) * 1e3
+
+    def new_event():
+        return torch.cuda.Event(enable_timing=True) if on_gpu else WallEvent()
 
     # rank 0 samples its GPU's clocks (read-only, NVML thread or nvidia-smi child) during the timed region
     sampler = None
     if rank == 0:
         from tinyinfinitrain_b200.utils.clocks import ClockSampler
 
-        sampler = ClockSampler(local_rank, uuid=str(getattr(torch.cuda.get_device_properties(dev), "uuid", "") or ""))
+        uuid = str(getattr(torch.cuda.get_device_properties(dev), "uuid", "") or "") if on_gpu else ""
+        sampler = ClockSampler(local_rank, uuid=uuid)
         sampler.launch()
 
     # ---------------- device-timed region: K steps, inputs resident -----------------
@@ -119,7 +157,7 @@ def main():
     barrier()
     if sampler is not None:
         sampler.begin()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0, e1 = new_event(), new_event()
     e0.record()
     for _ in range(K):
         step.run_device()
@@ -137,7 +175,8 @@ def main():
     t0 = time.perf_counter()
     for i in range(K):
         hl = step(host_idx[i % nbuf], host_tgt[i % nbuf])
-        torch.cuda.current_stream().synchronize()
+        if on_gpu:
+            torch.cuda.current_stream().synchronize()
         _ = float(hl)
     barrier()
     e2e_s = time.perf_counter() - t0
@@ -150,7 +189,7 @@ def main():
         ms, e2e_ms = t.tolist()
     else:
         e2e_ms = e2e_s * 1e3
-    status = tit._lib.C.status_read(True)
+    status = tit._lib.C.status_read(True) if (on_gpu and not library) else 0
 
     if rank == 0:
         clocks = sampler.result()
@@ -158,11 +197,11 @@ def main():
         out = {
             "metric": "train_tokens_per_sec", "value": tokens / (ms / 1e3), "unit": "tokens/s",
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"model": "gpt2-124M", "global_batch": B * world, "seq_len": T,
-                       "parallelism": f"dp{world}" + ("+zero1" if world > 1 else ""), "micro_batch_per_gpu": B,
-                       "optimizer": "AdamW(fp32 master, bf16 params)", "cuda_graph": step.graph is not None,
-                       "comm": args.comm if world > 1 else "none",
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if on_gpu else "fp32 (cpu dry run)", "data": "synthetic",
+            "config": {"model": "gpt2-tiny (dry run)" if args.tiny else "gpt2-124M", "global_batch": B * world, "seq_len": T,
+                       "parallelism": f"dp{world}" + ("+zero1" if world > 1 and not library else ""), "micro_batch_per_gpu": B,
+                       "optimizer": "AdamW(fp32 params, bf16 autocast)" if library else "AdamW(fp32 master, bf16 params)", "cuda_graph": getattr(step, "graph", None) is not None,
+                       "comm": ("nccl-ddp" if library else args.comm) if world > 1 else "none",
                        "l2": "per-step working set (activations + weights + optimizer state, >10 GB) exceeds the "
                              "126 MB L2; no explicit flush",
                        "init": "random N(0,0.02), seed 42", "final_loss": final_loss, "kernel_status": status},
@@ -170,8 +209,9 @@ def main():
                        "samples": clocks["samples"], "source": clocks["backend"]},
             "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * B * T * 8,
                     "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms / K},
-            "gpu_launches": int(step.launches_per_step) * K,
-            "impl": "ours",
+            # launches of this repository's own kernels inside the timed region (none on the library arm)
+            "gpu_launches": 0 if library else int(step.launches_per_step) * K,
+            "impl": args.impl,
         }
         print(json.dumps(out))
     if world > 1:

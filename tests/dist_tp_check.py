@@ -54,7 +54,7 @@ def main():
             z3 = nccl.gemm_rs(yin, wt, True)
             e_rs2 = ((z2.float() - z3.float()).abs().max() / z3.float().abs().max()).item()
             torch.cuda.synchronize()
-            good = e_ag < 5e-2 and e_x == 0.0 and e_ref < 0.15 and e_rs < 2e-2 and e_rs2 < 2e-2
+            good = e_ag < 5e-2 and e_x == 0.0 and e_ref < 0.15 and e_rs < 4e-2 and e_rs2 < 4e-2
             ok = ok and good
             msgs.append(f"[{Ms},{K},{N}] ag {e_ag:.3g} X {e_x:.3g} ref {e_ref:.3g} rs {e_rs:.3g} rs_mn {e_rs2:.3g}")
     status = tit._lib.C.status_read(True)

@@ -1,0 +1,48 @@
+"""bench.py's control flow and output contract, dry-run on CPU (tiny model, gloo ranks, wall-clock timing)."""
+import json
+import os
+import subprocess
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REQUIRED = {"metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",
+            "vs_baseline", "dtype", "data", "config", "clocks", "e2e", "gpu_launches", "impl"}
+
+
+def _run(cmd, timeout=600):
+    r = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=timeout)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    lines = [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
+    assert len(lines) == 1, r.stdout[-2000:]
+    return json.loads(lines[0])
+
+
+def _check(out, n, impl):
+    assert REQUIRED <= set(out), REQUIRED - set(out)
+    assert out["n_gpus"] == n and out["steps"] == 2 and out["warmup"] >= 3 and out["impl"] == impl
+    assert out["value"] > 0 and out["higher_is_better"] is True and out["scaling"] == "weak"
+    assert out["config"]["global_batch"] == 2 * n and out["config"]["seq_len"] == 32
+    e = out["e2e"]
+    assert e["value"] > 0 and e["h2d_bytes_per_step"] == 2 * 2 * 32 * 8 and e["d2h_bytes_per_step"] == 4
+    assert set(out["clocks"]) >= {"sm_mhz", "sm_max_mhz", "reasons"}
+
+
+def test_bench_single_rank_dry_run():
+    args = ["--device", "cpu", "--tiny", "--steps", "2", "--warmup", "1", "--batch", "2", "--seq", "32"]
+    _check(_run([sys.executable, "bench.py"] + args), 1, "ours")
+    _check(_run([sys.executable, "bench.py", "--impl", "library"] + args), 1, "library")
+
+
+def test_bench_two_ranks_dry_run():
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", str(29800 + os.getpid() % 100), "bench.py", "--gpus", "2", "--device", "cpu",
+           "--tiny", "--steps", "2", "--warmup", "3", "--batch", "2", "--seq", "32"]
+    _check(_run(cmd), 2, "ours")
+
+
+def test_reference_arm_reports_unavailable():
+    r = subprocess.run([sys.executable, "bench.py", "--impl", "reference", "--gpus", "1", "--steps", "2", "--warmup", "1"],
+                       cwd=ROOT, capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0
+    out = json.loads(r.stdout.strip().splitlines()[-1])
+    assert out["impl"] == "reference" and "unavailable" in out and "\n" not in out["unavailable"]
