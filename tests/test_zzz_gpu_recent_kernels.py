@@ -144,3 +144,30 @@ def test_zero1_bucketed_overlap_matches_single_bucket():
            "127.0.0.1", "--master-port", str(29900 + os.getpid() % 90), os.path.join(HERE, "dist_zero_check.py")]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, BF])
+@pytest.mark.parametrize("V,vocab,shards", [(512, 500, 2), (1024, 1000, 4), (96, 50, 3)])
+def test_vocab_parallel_xent_kernels_match_full_softmax(dtype, V, vocab, shards):
+    """The slices of one [M, V] logits tensor are processed as the ranks of a group would process them (same
+    kernels, one table in local memory); loss rows and gradient must equal cross entropy over the full row."""
+    torch.manual_seed(6)
+    M, Vl = 37, V // shards
+    full = (torch.randn(M, V, device=DEV) * 3).to(dtype)
+    tgt = torch.randint(0, vocab, (M,), device=DEV)
+    ref_in = full.float()[:, :vocab].clone().requires_grad_(True)
+    ref_rows = torch.nn.functional.cross_entropy(ref_in, tgt, reduction="none")
+    ref_rows.mean().backward()
+    table = torch.zeros(shards, M, 3, device=DEV)
+    slices = [full[:, r * Vl:(r + 1) * Vl].contiguous() for r in range(shards)]
+    for r, sl in enumerate(slices):
+        C.xent_vp_stats(sl, tgt, [table.data_ptr()], r, r * Vl, vocab)
+    for r, sl in enumerate(slices):
+        rows = C.xent_vp_grad(sl, tgt, table, r * Vl, vocab, 1.0 / M)
+        tol = dict(atol=1e-4, rtol=1e-4) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+        assert torch.allclose(rows, ref_rows, **tol)
+    grad = torch.cat(slices, 1).float()
+    assert torch.all(grad[:, vocab:] == 0)
+    gtol = dict(atol=1e-6, rtol=1e-4) if dtype == torch.float32 else dict(atol=2e-3, rtol=3e-2)
+    assert torch.allclose(grad[:, :vocab], ref_in.grad, **gtol)
+    _status_ok()

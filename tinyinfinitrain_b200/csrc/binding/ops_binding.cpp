@@ -372,6 +372,36 @@ Tensor xent_bwd(const Tensor& logits, const Tensor& targets, const Tensor& upstr
   return d;
 }
 
+// Vocabulary-parallel cross entropy, pass 1: (max, sum-exp, target logit) of every row of this rank's logits slice,
+// written to slot `rank` of the [world, rows, 3] fp32 table behind every address in dst_ptrs.
+void xent_vp_stats(const Tensor& logits, const Tensor& targets, const std::vector<int64_t>& dst_ptrs, int64_t rank,
+                   int64_t vocab_lo, int64_t vocab_size) {
+  check_cuda(logits, "logits"); check_cuda(targets, "targets");
+  TORCH_CHECK(targets.scalar_type() == at::kLong && targets.is_contiguous() && logits.is_contiguous());
+  c10::cuda::CUDAGuard guard(logits.device());
+  const int64_t ld = logits.size(-1), rows = logits.numel() / ld;
+  TORCH_CHECK(targets.numel() == rows, "titb200 cross entropy: one target per row");
+  std::vector<unsigned long long> d(dst_ptrs.begin(), dst_ptrs.end());
+  CHECK_RC(titb_xent_vp_stats(logits.data_ptr(), (const long long*)targets.data_ptr<int64_t>(), d.data(), (int)d.size(),
+                              (int)rank, rows, ld, ld, vocab_lo, vocab_size, dt_code(logits), cur_stream()),
+           "xent_vp_stats");
+}
+// Pass 2: per-row losses from the complete table; the slice is overwritten with grad_scale * (softmax - onehot).
+Tensor xent_vp_grad(const Tensor& logits, const Tensor& targets, const Tensor& stats, int64_t vocab_lo,
+                    int64_t vocab_size, double grad_scale) {
+  check_cuda(logits, "logits"); check_cuda(stats, "stats");
+  TORCH_CHECK(stats.scalar_type() == at::kFloat && stats.is_contiguous() && stats.dim() == 3 && stats.size(2) == 3);
+  TORCH_CHECK(targets.scalar_type() == at::kLong && targets.is_contiguous() && logits.is_contiguous());
+  c10::cuda::CUDAGuard guard(logits.device());
+  const int64_t ld = logits.size(-1), rows = logits.numel() / ld;
+  TORCH_CHECK(stats.size(1) == rows, "titb200 cross entropy: statistics table has the wrong number of rows");
+  Tensor losses = at::empty({rows}, logits.options().dtype(at::kFloat));
+  CHECK_RC(titb_xent_vp_grad(logits.data_ptr(), (const long long*)targets.data_ptr<int64_t>(), stats.data_ptr<float>(),
+                             (int)stats.size(0), losses.data_ptr<float>(), rows, ld, ld, vocab_lo, vocab_size,
+                             (float)grad_scale, dt_code(logits), cur_stream()), "xent_vp_grad");
+  return losses;
+}
+
 // ------------------------------------------------------------------ optimizers
 void adam_flat(const Tensor& master, const optional<Tensor>& lp, const Tensor& grad, const Tensor& m, const Tensor& v,
                double lr, double b1, double b2, double eps, double wd, int64_t step, double grad_scale,
@@ -649,6 +679,8 @@ PYBIND11_MODULE(_C, m) {
   m.def("xent_fused", &xent_fused, py::arg("logits"), py::arg("targets"), py::arg("V"), py::arg("grad_scale"),
         py::arg("write_grad"), py::arg("mean_scale"));
   m.def("xent_bwd", &xent_bwd);
+  m.def("xent_vp_stats", &xent_vp_stats);
+  m.def("xent_vp_grad", &xent_vp_grad);
   m.def("adam_flat", &adam_flat, py::arg("master"), py::arg("lp"), py::arg("grad"), py::arg("m"), py::arg("v"),
         py::arg("lr"), py::arg("b1"), py::arg("b2"), py::arg("eps"), py::arg("wd"), py::arg("step"),
         py::arg("grad_scale"), py::arg("dev_state") = py::none());

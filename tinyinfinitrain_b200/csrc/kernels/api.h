@@ -152,6 +152,18 @@ TITB_API int titb_xent_fwd_bwd(const void* logits, const long long* targets, flo
 TITB_API int titb_xent_bwd(const void* logits, const long long* targets, void* dlogits, const float* upstream,
                            long long rows, int V, long long ld, float grad_scale, int dtype, cudaStream_t stream);
 TITB_API int titb_mean(const float* x, float* out, long long n, float scale, cudaStream_t stream);
+// Vocabulary-parallel cross entropy.  logits [rows, ld] is this rank's slice: column c is global column
+// vocab_lo + c; columns >= V_local or with a global index >= vocab_size are padding.
+// Pass 1 writes (row max, sum exp(x - max), target logit or 0) to slot `rank` of a [world, rows, 3] fp32 table at
+// each of the n_dst (<= 16) destination addresses (the local table and/or peers' tables in peer-mapped memory).
+TITB_API int titb_xent_vp_stats(const void* logits, const long long* targets, const unsigned long long* dst_ptrs,
+                                int n_dst, int rank, long long rows, long long V_local, long long ld,
+                                long long vocab_lo, long long vocab_size, int dtype, cudaStream_t stream);
+// Pass 2 reads the complete table (all `world` slots), writes losses[row] = logsumexp - target logit (0 for rows
+// whose target is outside [0, vocab_size)) and overwrites the slice with grad_scale * (softmax - onehot).
+TITB_API int titb_xent_vp_grad(void* logits, const long long* targets, const float* stats, int world, float* losses,
+                               long long rows, long long V_local, long long ld, long long vocab_lo,
+                               long long vocab_size, float grad_scale, int dtype, cudaStream_t stream);
 
 // ---- optimizers ----------------------------------------------------------------------------
 // One launch over a flat range.  master/m/v fp32; grad fp32; param_bf16 (optional) gets the

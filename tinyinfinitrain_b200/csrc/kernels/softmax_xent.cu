@@ -93,6 +93,94 @@ xent_kernel(const T* logits, const long long* __restrict__ targets, float* __res
   }
 }
 
+// ---- vocabulary-parallel cross entropy -------------------------------------------------------------------
+// The vocabulary is split over the ranks of a tensor-parallel group: this rank's logits [rows, ld] hold global
+// columns [vocab_lo, vocab_lo + V_valid) (anything beyond is padding).  Pass 1 reduces each row of the slice to
+// (max, sum exp(x - max), logit of the target if it falls in the slice) and stores the triple at slot `rank` of
+// a [world, rows, 3] table on every destination pointer (peer stores into symmetric memory, or one local
+// table that the host all-gathers).  Pass 2 reads the complete table, forms the global log-sum-exp and writes
+// loss rows and, in place, grad_scale * (softmax - onehot) for the slice.  The full [rows, V] logits never
+// exist on one GPU.
+struct VpDst {
+  float* p[16];
+  int n;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(512)
+xent_vp_stats_kernel(const T* __restrict__ logits, const long long* __restrict__ targets, const VpDst dst, int rank,
+                     long long rows, int V_valid, long long ld, long long vocab_lo, int vec_ok) {
+  constexpr int VN = VecN<T>::n;
+  __shared__ float red[64];
+  const long long row = blockIdx.x;
+  const T* x = logits + row * ld;
+  const int nvec = vec_ok ? V_valid / VN : 0;
+  MaxSum acc{-INFINITY, 0.f};
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    Pack<T, VN> p = ld128(x + i * VN);
+    float mx = to_f32(p.v[0]);
+#pragma unroll
+    for (int e = 1; e < VN; ++e) mx = fmaxf(mx, to_f32(p.v[e]));
+    const float m = fmaxf(acc.m, mx);
+    float s = acc.s * __expf(acc.m - m);
+#pragma unroll
+    for (int e = 0; e < VN; ++e) s += __expf(to_f32(p.v[e]) - m);
+    acc = {m, s};
+  }
+  for (int i = nvec * VN + threadIdx.x; i < V_valid; i += blockDim.x) acc = ms_combine(acc, MaxSum{to_f32(x[i]), 1.f});
+  acc = ms_block(acc, red);
+  if (threadIdx.x == 0) {
+    const long long t = targets[row] - vocab_lo;
+    const float x_tgt = (t >= 0 && t < V_valid) ? to_f32(x[t]) : 0.f;
+    const long long slot = (static_cast<long long>(rank) * rows + row) * 3;
+    for (int d = 0; d < dst.n; ++d) {
+      float* o = dst.p[d] + slot;
+      o[0] = acc.m; o[1] = acc.s; o[2] = x_tgt;
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(512)
+xent_vp_grad_kernel(T* logits, const long long* __restrict__ targets, const float* __restrict__ stats, int world,
+                    float* __restrict__ losses, long long rows, int V_valid, long long ld, long long vocab_lo,
+                    long long vocab_size, float grad_scale, int vec_ok) {
+  constexpr int VN = VecN<T>::n;
+  const long long row = blockIdx.x;
+  // every thread folds the (at most 16) per-rank triples itself: cheaper than a block broadcast
+  MaxSum g{-INFINITY, 0.f};
+  float x_tgt = 0.f;
+  for (int r = 0; r < world; ++r) {
+    const float* s = stats + (static_cast<long long>(r) * rows + row) * 3;
+    g = ms_combine(g, MaxSum{s[0], s[1]});
+    x_tgt += s[2];
+  }
+  const float lse = g.m + logf(g.s);
+  const long long tgt = targets[row];
+  const bool valid = tgt >= 0 && tgt < vocab_size;
+  if (threadIdx.x == 0 && losses != nullptr) losses[row] = valid ? lse - x_tgt : 0.f;
+  const float gs = valid ? grad_scale : 0.f;
+  const long long t_local = tgt - vocab_lo;
+  T* x = logits + row * ld;
+  const int ldv = vec_ok ? (int)(ld / VN) : 0;
+  for (int i = threadIdx.x; i < ldv; i += blockDim.x) {
+    Pack<T, VN> p = ld128(x + i * VN), o;
+#pragma unroll
+    for (int e = 0; e < VN; ++e) {
+      const int c = i * VN + e;
+      float pr = (c < V_valid) ? __expf(to_f32(p.v[e]) - lse) : 0.f;
+      if (c == t_local) pr -= 1.f;
+      o.v[e] = from_f32<T>(gs * pr);
+    }
+    st128(x + i * VN, o);
+  }
+  for (long long c = (long long)ldv * VN + threadIdx.x; c < ld; c += blockDim.x) {
+    float pr = (c < V_valid) ? __expf(to_f32(x[c]) - lse) : 0.f;
+    if (c == t_local) pr -= 1.f;
+    x[c] = from_f32<T>(gs * pr);
+  }
+}
+
 // out[0] = scale * sum(x), fixed summation order.
 __global__ void mean_kernel(const float* __restrict__ x, float* __restrict__ out, long long n, float scale) {
   __shared__ float red[32];
@@ -190,5 +278,46 @@ TITB_API int titb_softmax_bwd(const void* dy, const void* y, void* dx, long long
   const unsigned blocks = (unsigned)((lines + 3) / 4);
   if (dtype == 1) softmax_bwd_kernel<bf16><<<blocks, 128, 0, st>>>((const bf16*)dy, (const bf16*)y, (bf16*)dx, outer, axis, inner);
   else softmax_bwd_kernel<float><<<blocks, 128, 0, st>>>((const float*)dy, (const float*)y, (float*)dx, outer, axis, inner);
+  return (int)cudaGetLastError();
+}
+
+static inline int vp_valid_cols(long long V_local, long long vocab_lo, long long vocab_size) {
+  long long v = vocab_size - vocab_lo;
+  if (v > V_local) v = V_local;
+  return (int)(v < 0 ? 0 : v);
+}
+
+TITB_API int titb_xent_vp_stats(const void* logits, const long long* targets, const unsigned long long* dst_ptrs,
+                                int n_dst, int rank, long long rows, long long V_local, long long ld,
+                                long long vocab_lo, long long vocab_size, int dtype, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (n_dst < 1 || n_dst > 16 || V_local > ld) return TITB_ERR_SHAPE;
+  VpDst dst{};
+  dst.n = n_dst;
+  for (int i = 0; i < n_dst; ++i) dst.p[i] = reinterpret_cast<float*>(dst_ptrs[i]);
+  const int Vv = vp_valid_cols(V_local, vocab_lo, vocab_size);
+  const int vn = dtype == 1 ? 8 : 4;
+  const int vec_ok = !((uintptr_t)logits & 15) && (ld % vn == 0);
+  const int threads = Vv >= 8192 ? 512 : 256;
+  if (dtype == 1)
+    xent_vp_stats_kernel<bf16><<<(unsigned)rows, threads, 0, st>>>((const bf16*)logits, targets, dst, rank, rows, Vv, ld, vocab_lo, vec_ok);
+  else
+    xent_vp_stats_kernel<float><<<(unsigned)rows, threads, 0, st>>>((const float*)logits, targets, dst, rank, rows, Vv, ld, vocab_lo, vec_ok);
+  return (int)cudaGetLastError();
+}
+
+TITB_API int titb_xent_vp_grad(void* logits, const long long* targets, const float* stats, int world, float* losses,
+                               long long rows, long long V_local, long long ld, long long vocab_lo,
+                               long long vocab_size, float grad_scale, int dtype, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (world < 1 || world > 16 || V_local > ld) return TITB_ERR_SHAPE;
+  const int Vv = vp_valid_cols(V_local, vocab_lo, vocab_size);
+  const int vn = dtype == 1 ? 8 : 4;
+  const int vec_ok = !((uintptr_t)logits & 15) && (ld % vn == 0);
+  const int threads = ld >= 8192 ? 512 : 256;
+  if (dtype == 1)
+    xent_vp_grad_kernel<bf16><<<(unsigned)rows, threads, 0, st>>>((bf16*)logits, targets, stats, world, losses, rows, Vv, ld, vocab_lo, vocab_size, grad_scale, vec_ok);
+  else
+    xent_vp_grad_kernel<float><<<(unsigned)rows, threads, 0, st>>>((float*)logits, targets, stats, world, losses, rows, Vv, ld, vocab_lo, vocab_size, grad_scale, vec_ok);
   return (int)cudaGetLastError();
 }

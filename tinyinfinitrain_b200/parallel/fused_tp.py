@@ -24,7 +24,7 @@ class FusedTP:
     def __init__(self, comm):
         self.comm = comm
         self.world, self.rank, self.group = comm.world, comm.rank, comm.group
-        self._ag: Dict[int, SymmetricBuffer] = {}
+        self._ag: Dict[object, SymmetricBuffer] = {}
         self._rs: Dict[Tuple[int, int], Tuple[SymmetricBuffer, SymmetricBuffer]] = {}
         self._barrier = None
         self._nbar = 0
@@ -99,3 +99,19 @@ class FusedTP:
         self._bar(dev)                           # every rank has consumed the previous contents of its receive buffer
         res = residual_s.contiguous() if residual_s is not None else None
         return C.gemm_rs(y, w, b_mn, recv.ptrs, cnt.ptrs, self.rank, bias, res, min(self.RS_HELPERS, Ms // 128))
+
+    # ---- per-row statistics table of the vocabulary-parallel loss ----------------------------------
+    def stats_table(self, rows: int, dev):
+        """A [world, rows, 3] fp32 table in symmetric memory and the addresses of every rank's copy; rank r's
+        kernel stores its triples into slot r of all of them.  Call :meth:`stats_publish` after that kernel."""
+        key = ("vp", rows)
+        buf = self._ag.get(key)
+        if buf is None:
+            buf = self._ag[key] = SymmetricBuffer(self.world * rows * 3, torch.float32, dev, self.group)
+        if self._last_read.get(key, 1 << 60) >= self._nbar:
+            self._bar(dev)                       # peers may still be reading the previous contents
+        return buf.tensor.view(self.world, rows, 3), list(buf.ptrs)
+
+    def stats_publish(self, rows: int, dev) -> None:
+        self._bar(dev)                           # every rank's slot has landed everywhere
+        self._last_read[("vp", rows)] = self._nbar

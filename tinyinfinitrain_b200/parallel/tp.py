@@ -20,6 +20,7 @@ infini_train/include/nn/modules/linear.h:11-24).
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional
 
 import torch
@@ -31,6 +32,9 @@ from ..ops import functional as F_
 from .._lib import C
 
 _bf16 = torch.bfloat16
+# The two-pass vocabulary-parallel cross-entropy kernels replace the torch-op formulation of the loss when set
+# (TITB200_VP_XENT=1); the torch-op path is the default.
+USE_VP_XENT_KERNELS = os.environ.get("TITB200_VP_XENT", "0") == "1"
 
 
 class TPComm:
@@ -79,6 +83,27 @@ class TPComm:
         if self.world > 1:
             dist.all_reduce(t, op=op, group=self.group)
         return t
+
+    # ---- statistics exchange of the vocabulary-parallel loss -------------------------------------
+    def vp_stats_table(self, rows: int, dev):
+        """Returns (table, destination addresses, slot) for the pass-1 kernel of the vocabulary-parallel cross
+        entropy.  Fused mode: the table lives in symmetric memory and the kernel stores straight into every
+        peer's copy.  NCCL mode: a one-slot local table that :meth:`vp_stats_publish` all-gathers."""
+        if self._fused is not None:
+            table, ptrs = self._fused.stats_table(rows, dev)
+            return table, ptrs, self.rank
+        table = torch.empty(1, rows, 3, device=dev, dtype=torch.float32)
+        return table, [table.data_ptr()], 0
+
+    def vp_stats_publish(self, table: torch.Tensor, rows: int) -> torch.Tensor:
+        if self._fused is not None:
+            self._fused.stats_publish(rows, table.device)
+            return table
+        if self.world == 1:
+            return table
+        full = torch.empty(self.world, rows, 3, device=table.device, dtype=torch.float32)
+        dist.all_gather_into_tensor(full, table, group=self.group)
+        return full
 
     # ---- the two fused pairs ---------------------------------------------------------------------
     def ag_gemm(self, x_s, w, bias=None, gelu=False, b_mn=False):
@@ -336,6 +361,16 @@ class _VocabParallelLossFn(torch.autograd.Function):
         logits, X = comm.ag_gemm(x_s, w)
         M, Vl = logits.shape
         lo = comm.rank * Vl
+        if USE_VP_XENT_KERNELS and logits.is_cuda and logits.dtype in (torch.float32, _bf16) and comm.world <= 16:
+            # own kernels: one pass for the slice statistics, exchange of [M, 3] triples, one in-place gradient pass
+            tgt = targets.reshape(-1).contiguous()
+            table, dst, slot = comm.vp_stats_table(M, logits.device)
+            C.xent_vp_stats(logits, tgt, dst, slot, lo, vocab_size)
+            table = comm.vp_stats_publish(table, M)
+            losses = C.xent_vp_grad(logits, tgt, table, lo, vocab_size, 1.0 / M)
+            ctx.save_for_backward(X, w, logits)
+            ctx.comm = comm
+            return losses.mean()
         lf = logits.float()
         col = torch.arange(Vl, device=logits.device) + lo
         lf = lf.masked_fill((col >= vocab_size).unsqueeze(0), float("-inf"))
