@@ -171,3 +171,52 @@ def test_vocab_parallel_xent_kernels_match_full_softmax(dtype, V, vocab, shards)
     gtol = dict(atol=1e-6, rtol=1e-4) if dtype == torch.float32 else dict(atol=2e-3, rtol=3e-2)
     assert torch.allclose(grad[:, :vocab], ref_in.grad, **gtol)
     _status_ok()
+
+
+def _fw(t, dev, requires_grad=False):
+    ft = C.FwTensor(t.clone(), requires_grad)
+    return ft.To(dev) if dev != "cpu" else ft
+
+
+def _facade_run(dev):
+    """A tour through the C++ facade's view-like, reduction and mask Functions; returns every result as CPU tensors."""
+    torch.manual_seed(8)
+    out = {}
+    x0 = torch.randn(3, 4, 6)
+    x = _fw(x0, dev, True)
+    parts = x.Split(2, 2)                                            # Split (multi-output) -> gather kernel
+    y = parts[0].Mul(parts[1]).Add(parts[2])
+    y = y.Transpose(0, 1)                                            # Transpose -> gather kernel
+    y = y.RepeatInterleave(2, 2)                                     # stride-0 gather / sum backward
+    y = y.Slice([0, 1, 0], [4, 3, 4], [1, 1, 2])                     # Slice -> gather fwd, scatter bwd
+    s = C.fw_function("Stack", [1]).Apply([y, y.MulScalar(2.0)])[0]  # Stack -> scatter fwd, gather bwd
+    sm = C.fw_function("Softmax", [2]).Apply([s])[0]
+    red = C.fw_function("Sum", [3, 0]).Apply([sm.Mul(s)])[0]
+    red = C.fw_function("Max", [0, 1]).Apply([red])[0]
+    red = C.fw_function("Mean", [2, 0]).Apply([red])[0]
+    red = C.fw_function("Min", [1, 0]).Apply([red])[0]
+    out["y"], out["stack"], out["softmax"], out["red"] = y.torch(), s.torch(), sm.torch(), red.torch()
+    red.Backward(_fw(torch.ones(1), dev))
+    out["dx"] = x.grad().torch()
+    m0 = torch.tril(torch.ones(6, 6))
+    a = _fw(torch.randn(2, 6, 6), dev, True)
+    tri = C.fw_function("Tril", [0]).Apply([_fw(torch.ones(6, 6), dev)])[0]
+    masked = a.MaskedFill(tri.Equals(0.0), -1e4)
+    out["tril"], out["masked"] = tri.torch(), masked.torch()
+    C.fw_function("Sum", [0, 0]).Apply([C.fw_function("Sum", [2, 0]).Apply([masked])[0]])[0].Backward(_fw(torch.ones(6), dev))
+    out["da"] = a.grad().torch()
+    u, v = _fw(torch.randn(5), dev, True), _fw(torch.randn(7), dev, True)
+    o = u.Outer(v)
+    out["outer"] = o.torch()
+    C.fw_function("Sum", [0, 0]).Apply([C.fw_function("Sum", [1, 0]).Apply([o.Mul(o)])[0]])[0].Backward()
+    out["du"], out["dv"] = u.grad().torch(), v.grad().torch()
+    assert torch.equal(m0, out["tril"].cpu())
+    return {k: t.detach().float().cpu() for k, t in out.items()}
+
+
+def test_cpp_facade_cuda_ops_match_cpu_oracle():
+    cpu, gpu = _facade_run("cpu"), _facade_run("cuda:0")
+    for k in cpu:
+        assert cpu[k].shape == gpu[k].shape, k
+        assert torch.allclose(cpu[k], gpu[k], atol=1e-5, rtol=1e-5), k
+    _status_ok()

@@ -4,7 +4,8 @@
 // CPU tensors: ATen fp32 math restating infini_train/src/kernels/cpu/*.cc (the numerical oracle).
 // CUDA float32/bfloat16 tensors: the sm_100a kernel library (tcgen05 GEMM for bf16 Linear/Matmul,
 // the SIMT SGEMM for fp32, fused LayerNorm / softmax / cross-entropy / embedding / Adam kernels);
-// the remaining layout ops are views or ATen copies.
+// reductions, outer product, mask, tril/triu and every materialised view (transpose, slice, split, stack,
+// repeat-interleave) go through the library's reduce / gather / scatter kernels as well.
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 
@@ -17,13 +18,48 @@
 namespace infini_train::kernels {
 
 using TP = std::shared_ptr<Tensor>;
-static TP W(at::Tensor t) { return std::make_shared<Tensor>(t.contiguous()); }
 static bool native(const at::Tensor& t) {
   return t.is_cuda() && (t.scalar_type() == at::kFloat || t.scalar_type() == at::kBFloat16);
 }
 static int dt(const at::Tensor& t) { return t.scalar_type() == at::kBFloat16 ? 1 : 0; }
 static cudaStream_t stream() { return at::cuda::getCurrentCUDAStream().stream(); }
 static void ok(int rc, const char* what) { TORCH_CHECK(rc == 0, "kernel ", what, " failed with code ", rc); }
+
+// Contiguous copy of a (possibly strided, possibly stride-0 expanded) view.  CUDA views of up to six dimensions
+// are materialised by the library's gather kernel; everything else by ATen.
+static at::Tensor materialize(const at::Tensor& t) {
+  if (t.is_contiguous()) return t;
+  const int64_t es = t.element_size();
+  if (!t.is_cuda() || t.dim() > 6 || !(es == 2 || es == 4 || es == 8) || t.numel() == 0) return t.contiguous();
+  c10::cuda::CUDAGuard guard(t.device());
+  at::Tensor out = at::empty(t.sizes(), t.options());
+  std::vector<long long> sz(t.sizes().begin(), t.sizes().end()), st(t.strides().begin(), t.strides().end());
+  ok(titb_gather_nd(t.storage().data(), out.data_ptr(), (int)sz.size(), sz.data(), st.data(), t.storage_offset(), (int)es,
+                    stream()), "gather_nd");
+  return out;
+}
+// Writes the contiguous `src` into `view`, a view of the contiguous tensor `dst` (same dtype, <= 6 dimensions).
+static void scatter_into(at::Tensor& dst, const at::Tensor& view, const at::Tensor& src_) {
+  if (!native(dst) || view.dim() > 6 || src_.scalar_type() != dst.scalar_type()) {
+    const_cast<at::Tensor&>(view).copy_(src_);
+    return;
+  }
+  c10::cuda::CUDAGuard guard(dst.device());
+  at::Tensor src = materialize(src_);
+  std::vector<long long> sz(view.sizes().begin(), view.sizes().end()), st(view.strides().begin(), view.strides().end());
+  ok(titb_scatter_nd(src.data_ptr(), dst.data_ptr(), (int)sz.size(), sz.data(), st.data(),
+                     view.storage_offset() - dst.storage_offset(), dt(dst), 0, stream()), "scatter_nd");
+}
+static TP W(at::Tensor t) { return std::make_shared<Tensor>(materialize(t)); }
+// [outer, n, inner] factorisation of a reduction over `dim`.
+struct Axis3 { int64_t outer = 1, n = 1, inner = 1; };
+static Axis3 axis3(c10::IntArrayRef dims, int64_t dim) {
+  Axis3 a;
+  for (int64_t d = 0; d < dim; ++d) a.outer *= dims[d];
+  a.n = dims[dim];
+  for (int64_t d = dim + 1; d < (int64_t)dims.size(); ++d) a.inner *= dims[d];
+  return a;
+}
 
 // ---- accumulate / optimizers ------------------------------------------------------------------------
 void AccumulateGrad(const TP& gradient, float rate, const TP& tensor) {
@@ -56,7 +92,16 @@ void AdamAccumulateGrad(const TP& grad, const TP& param, const TP& m, const TP& 
   p.sub_((mh / (vh.sqrt() + eps)).mul_(learning_rate).to(p.scalar_type()));
 }
 
-void Fill(const TP& tensor, void* value_ptr) { tensor->data().fill_(*static_cast<float*>(value_ptr)); }
+void Fill(const TP& tensor, void* value_ptr) {
+  at::Tensor& t = tensor->data();
+  const float v = *static_cast<float*>(value_ptr);
+  if (native(t) && t.is_contiguous()) {
+    c10::cuda::CUDAGuard guard(t.device());
+    ok(titb_fill(t.data_ptr(), t.numel(), v, dt(t), stream()), "Fill");
+    return;
+  }
+  t.fill_(v);
+}
 
 // ---- unary elementwise ------------------------------------------------------------------------------------
 static TP unary(int op, const TP& x, float s, at::Tensor (*ref)(const at::Tensor&, float)) {
@@ -225,9 +270,27 @@ std::tuple<TP, TP, TP> LinearBackward(const TP& input, const TP& weight, bool tr
   return {W(dx), W(dw), db};
 }
 
-TP OuterForward(const TP& a, const TP& b) { return W(at::outer(a->data(), b->data())); }
+TP OuterForward(const TP& a, const TP& b) {
+  const at::Tensor &x = a->data(), &y = b->data();
+  if (native(x) && native(y) && x.scalar_type() == y.scalar_type() && x.dim() == 1 && y.dim() == 1) {
+    c10::cuda::CUDAGuard guard(x.device());
+    at::Tensor xc = materialize(x), yc = materialize(y), out = at::empty({x.numel(), y.numel()}, x.options());
+    ok(titb_outer(xc.data_ptr(), yc.data_ptr(), out.data_ptr(), x.numel(), y.numel(), dt(x), stream()), "Outer");
+    return W(out);
+  }
+  return W(at::outer(x, y));
+}
 std::pair<TP, TP> OuterBackward(const TP& a, const TP& b, const TP& g) {
-  return {W(at::mv(g->data(), b->data())), W(at::mv(g->data().t(), a->data()))};
+  const at::Tensor &x = a->data(), &y = b->data(), &go = g->data();
+  if (native(x) && native(y) && native(go) && x.scalar_type() == y.scalar_type() && go.scalar_type() == x.scalar_type()) {
+    c10::cuda::CUDAGuard guard(x.device());
+    at::Tensor xc = materialize(x), yc = materialize(y), gc = materialize(go);
+    at::Tensor da = at::empty_like(xc), db = at::empty_like(yc);
+    ok(titb_outer_bwd(gc.data_ptr(), xc.data_ptr(), yc.data_ptr(), da.data_ptr(), db.data_ptr(), xc.numel(), yc.numel(),
+                      dt(x), stream()), "OuterBackward");
+    return {W(da), W(db)};
+  }
+  return {W(at::mv(go, y)), W(at::mv(go.t(), x))};
 }
 
 // ---- normalisation ------------------------------------------------------------------------------------------------------
@@ -261,9 +324,27 @@ std::tuple<TP, TP, TP> LayerNormBackward(const TP& input, const TP& weight, cons
 }
 
 // ---- softmax / cross entropy / embedding -------------------------------------------------------------------------------
-TP SoftmaxForward(const TP& input, int64_t dim) { return W(at::softmax(input->data(), dim)); }
+TP SoftmaxForward(const TP& input, int64_t dim) {
+  const at::Tensor& x = input->data();
+  if (native(x) && x.dim() >= 1) {
+    c10::cuda::CUDAGuard guard(x.device());
+    at::Tensor xc = materialize(x), y = at::empty_like(xc);
+    const Axis3 a = axis3(xc.sizes(), dim < 0 ? dim + xc.dim() : dim);
+    ok(titb_softmax_fwd(xc.data_ptr(), y.data_ptr(), a.outer, (int)a.n, a.inner, dt(xc), stream()), "Softmax");
+    return W(y);
+  }
+  return W(at::softmax(x, dim));
+}
 TP SoftmaxBackward(const TP& grad_output, const TP& output, int64_t dim) {
   const at::Tensor &g = grad_output->data(), &y = output->data();
+  if (native(g) && native(y) && g.scalar_type() == y.scalar_type() && y.dim() >= 1) {
+    c10::cuda::CUDAGuard guard(y.device());
+    at::Tensor gc = materialize(g), yc = materialize(y), dx = at::empty_like(yc);
+    const Axis3 a = axis3(yc.sizes(), dim < 0 ? dim + yc.dim() : dim);
+    ok(titb_softmax_bwd(gc.data_ptr(), yc.data_ptr(), dx.data_ptr(), a.outer, (int)a.n, a.inner, dt(yc), stream()),
+       "SoftmaxBackward");
+    return W(dx);
+  }
   return W(y * (g - (g * y).sum(dim, true)));
 }
 TP CrossEntropyForward(const TP& input, const TP& target) {
@@ -306,17 +387,50 @@ static at::Tensor expand_back(const at::Tensor& g, const std::vector<int64_t>& i
   at::Tensor gg = keep_dim ? g : g.unsqueeze(dim);
   return gg.expand(in_dims).contiguous();
 }
-TP MeanForward(const TP& x, int64_t dim, bool keep) { return W(x->data().mean(dim, keep)); }
-TP SumForward(const TP& x, int64_t dim, bool keep) { return W(x->data().sum(dim, keep)); }
-TP MaxForward(const TP& x, int64_t dim, bool keep) { return W(x->data().amax(dim, keep)); }
-TP MinForward(const TP& x, int64_t dim, bool keep) { return W(x->data().amin(dim, keep)); }
+// op: 0 sum, 1 mean, 2 max, 3 min
+static TP reduce_forward(const TP& x, int64_t dim, bool keep, int op) {
+  const at::Tensor& t = x->data();
+  const int64_t d = dim < 0 ? dim + t.dim() : dim;
+  if (native(t) && t.dim() >= 1 && t.numel() > 0) {
+    c10::cuda::CUDAGuard guard(t.device());
+    at::Tensor tc = materialize(t);
+    auto sizes = tc.sizes().vec();
+    if (keep) sizes[d] = 1; else sizes.erase(sizes.begin() + d);
+    at::Tensor y = at::empty(sizes, tc.options());
+    const Axis3 a = axis3(tc.sizes(), d);
+    ok(titb_reduce(tc.data_ptr(), y.data_ptr(), nullptr, a.outer, a.n, a.inner, op, dt(tc), stream()), "reduce");
+    return W(y);
+  }
+  switch (op) {
+    case 0: return W(t.sum(d, keep));
+    case 1: return W(t.mean(d, keep));
+    case 2: return W(t.amax(d, keep));
+    default: return W(t.amin(d, keep));
+  }
+}
+static TP reduce_broadcast_backward(const TP& g, const std::vector<int64_t>& in_dims, int64_t dim, bool keep, float scale) {
+  const at::Tensor& go = g->data();
+  const int64_t d = dim < 0 ? dim + (int64_t)in_dims.size() : dim;
+  if (native(go)) {
+    c10::cuda::CUDAGuard guard(go.device());
+    at::Tensor gc = materialize(go), dx = at::empty(in_dims, go.options());
+    const Axis3 a = axis3(in_dims, d);
+    ok(titb_reduce_bwd(gc.data_ptr(), nullptr, dx.data_ptr(), a.outer, a.n, a.inner, scale, dt(gc), stream()), "reduce_bwd");
+    return W(dx);
+  }
+  at::Tensor e = expand_back(go, in_dims, d, keep);
+  return W(scale == 1.f ? e : e * static_cast<double>(scale));
+}
+TP MeanForward(const TP& x, int64_t dim, bool keep) { return reduce_forward(x, dim, keep, 1); }
+TP SumForward(const TP& x, int64_t dim, bool keep) { return reduce_forward(x, dim, keep, 0); }
+TP MaxForward(const TP& x, int64_t dim, bool keep) { return reduce_forward(x, dim, keep, 2); }
+TP MinForward(const TP& x, int64_t dim, bool keep) { return reduce_forward(x, dim, keep, 3); }
 TP MeanBackward(const TP& g, const std::vector<int64_t>& in_dims, int64_t dim, bool keep) {
   const int64_t d = dim < 0 ? dim + (int64_t)in_dims.size() : dim;
-  return W(expand_back(g->data(), in_dims, d, keep) / static_cast<double>(in_dims[d]));
+  return reduce_broadcast_backward(g, in_dims, dim, keep, 1.f / static_cast<float>(in_dims[d]));
 }
 TP SumBackward(const TP& g, const std::vector<int64_t>& in_dims, int64_t dim, bool keep) {
-  const int64_t d = dim < 0 ? dim + (int64_t)in_dims.size() : dim;
-  return W(expand_back(g->data(), in_dims, d, keep));
+  return reduce_broadcast_backward(g, in_dims, dim, keep, 1.f);
 }
 // Max/Min route the gradient to every element equal to the extremum (reference reduction.cc:13-167).
 TP MaxBackward(const TP& g, const TP& input, const TP& output, int64_t dim, bool keep) {
@@ -330,10 +444,20 @@ TP MinBackward(const TP& g, const TP& input, const TP& output, int64_t dim, bool
 }
 
 // ---- transforms -------------------------------------------------------------------------------------------------------------
-TP TrilForward(const TP& x, int64_t diag) { return W(at::tril(x->data(), diag)); }
-TP TrilBackward(const TP& g, int64_t diag) { return W(at::tril(g->data(), diag)); }
-TP TriuForward(const TP& x, int64_t diag) { return W(at::triu(x->data(), diag)); }
-TP TriuBackward(const TP& g, int64_t diag) { return W(at::triu(g->data(), diag)); }
+static TP tri(const TP& x, int64_t diag, bool upper) {
+  const at::Tensor& t = x->data();
+  if (native(t) && t.dim() == 2) {
+    c10::cuda::CUDAGuard guard(t.device());
+    at::Tensor tc = materialize(t), y = at::empty_like(tc);
+    ok(titb_tri(tc.data_ptr(), y.data_ptr(), (int)tc.size(0), (int)tc.size(1), (int)diag, upper, dt(tc), stream()), "tri");
+    return W(y);
+  }
+  return W(upper ? at::triu(t, diag) : at::tril(t, diag));
+}
+TP TrilForward(const TP& x, int64_t diag) { return tri(x, diag, false); }
+TP TrilBackward(const TP& g, int64_t diag) { return tri(g, diag, false); }
+TP TriuForward(const TP& x, int64_t diag) { return tri(x, diag, true); }
+TP TriuBackward(const TP& g, int64_t diag) { return tri(g, diag, true); }
 TP TransposeForward(const TP& x, int64_t d0, int64_t d1) { return W(x->data().transpose(d0, d1)); }
 TP TransposeBackward(const TP& g, int64_t d0, int64_t d1) { return W(g->data().transpose(d0, d1)); }
 // mask is broadcast by modulo over the flattened input (reference transform.cc:121-152).
@@ -343,18 +467,41 @@ static at::Tensor mask_like(const at::Tensor& x, const at::Tensor& mask) {
   if (m != n) flat = flat.repeat({(n + m - 1) / m}).narrow(0, 0, n);
   return (flat == 1).reshape(x.sizes());
 }
-TP MaskForward(const TP& x, const TP& mask, float value) {
-  return W(x->data().masked_fill(mask_like(x->data(), mask->data()), value));
+// flags: bit 0 = backward (masked positions become 0), bit 1 = an element is masked when its entry equals 1
+static TP mask_apply(const at::Tensor& x, const at::Tensor& mask, float value, int backward) {
+  int mdt = -1;
+  if (mask.scalar_type() == at::kFloat) mdt = 0;
+  else if (mask.scalar_type() == at::kBFloat16) mdt = 1;
+  else if (mask.scalar_type() == at::kBool || mask.scalar_type() == at::kByte) mdt = 2;
+  if (native(x) && mask.is_cuda() && mdt >= 0 && mask.numel() > 0) {
+    c10::cuda::CUDAGuard guard(x.device());
+    at::Tensor xc = materialize(x), mc = materialize(mask), y = at::empty_like(xc);
+    ok(titb_mask_fill(xc.data_ptr(), mc.data_ptr(), y.data_ptr(), xc.numel(), mc.numel(), value, backward | 2, dt(xc), mdt,
+                      stream()), "Mask");
+    return W(y);
+  }
+  return W(x.masked_fill(mask_like(x, mask), backward ? 0.0 : static_cast<double>(value)));
 }
-TP MaskBackward(const TP& g, const TP& mask) { return W(g->data().masked_fill(mask_like(g->data(), mask->data()), 0)); }
+TP MaskForward(const TP& x, const TP& mask, float value) { return mask_apply(x->data(), mask->data(), value, 0); }
+TP MaskBackward(const TP& g, const TP& mask) { return mask_apply(g->data(), mask->data(), 0.f, 1); }
 TP RepeatInterleaveForward(const TP& x, int64_t repeat, int64_t dim) {
-  return W(x->data().repeat_interleave(repeat, dim));
+  const at::Tensor& t = x->data();
+  const int64_t d = dim < 0 ? dim + t.dim() : dim;
+  if (native(t) && t.dim() <= 5) {
+    // [.., n, ..] -> stride-0 view [.., n, repeat, ..] materialised by the gather kernel -> [.., n * repeat, ..]
+    std::vector<int64_t> ex = t.sizes().vec(), out = t.sizes().vec();
+    ex.insert(ex.begin() + d + 1, repeat);
+    out[d] *= repeat;
+    return W(materialize(materialize(t).unsqueeze(d + 1).expand(ex)).reshape(out));
+  }
+  return W(t.repeat_interleave(repeat, d));
 }
 TP RepeatInterleaveBackward(const TP& g, const std::vector<int64_t>& in_dims, int64_t dim) {
   std::vector<int64_t> shape = in_dims;
-  const int64_t repeat = g->data().size(dim) / in_dims[dim];
-  shape.insert(shape.begin() + dim + 1, repeat);
-  return W(g->data().reshape(shape).sum(dim + 1));
+  const int64_t d = dim < 0 ? dim + (int64_t)in_dims.size() : dim;
+  const int64_t repeat = g->data().size(d) / in_dims[d];
+  shape.insert(shape.begin() + d + 1, repeat);
+  return reduce_forward(std::make_shared<Tensor>(materialize(g->data()).reshape(shape)), d + 1, false, 0);
 }
 
 // ---- misc ---------------------------------------------------------------------------------------------------------------------
@@ -364,9 +511,16 @@ std::vector<TP> SplitForward(const TP& x, int64_t split_size, int dim) {
   return out;
 }
 TP SplitBackward(const std::vector<int64_t>& in_dims, int64_t split_size, int dim, const std::vector<TP>& grads) {
-  std::vector<at::Tensor> parts;
-  for (auto& g : grads) parts.push_back(g->data());
-  return W(at::cat(parts, dim));
+  TORCH_CHECK(!grads.empty(), "SplitBackward: no gradients");
+  at::Tensor dx = at::empty(in_dims, grads[0]->data().options());
+  int64_t pos = 0;
+  for (auto& g : grads) {
+    const int64_t len = g->data().size(dim);
+    scatter_into(dx, dx.narrow(dim, pos, len), g->data());
+    pos += len;
+  }
+  TORCH_CHECK(pos == in_dims[dim], "SplitBackward: gradients do not cover the split dimension");
+  return W(dx);
 }
 TP NoOpForward(const TP& x, const std::vector<int64_t>& dims) { return std::make_shared<Tensor>(x->data().reshape(dims)); }
 TP NoOpBackward(const std::vector<int64_t>& dims, const TP& g) { return std::make_shared<Tensor>(g->data().reshape(dims)); }
@@ -381,13 +535,17 @@ TP SliceForward(const TP& x, const std::vector<int64_t>& s, const std::vector<in
 TP SliceBackward(const TP& g, const std::vector<int64_t>& in_dims, const std::vector<int64_t>& s,
                  const std::vector<int64_t>& e, const std::vector<int64_t>& st) {
   at::Tensor dx = at::zeros(in_dims, g->data().options());
-  slice_nd(dx, s, e, st).copy_(g->data());
+  scatter_into(dx, slice_nd(dx, s, e, st), g->data());
   return W(dx);
 }
 TP StackForward(const std::vector<TP>& xs, int64_t dim) {
-  std::vector<at::Tensor> parts;
-  for (auto& x : xs) parts.push_back(x->data());
-  return W(at::stack(parts, dim));
+  TORCH_CHECK(!xs.empty(), "StackForward: no inputs");
+  std::vector<int64_t> shape = xs[0]->data().sizes().vec();
+  const int64_t d = dim < 0 ? dim + (int64_t)shape.size() + 1 : dim;
+  shape.insert(shape.begin() + d, (int64_t)xs.size());
+  at::Tensor out = at::empty(shape, xs[0]->data().options());
+  for (size_t i = 0; i < xs.size(); ++i) scatter_into(out, out.select(d, (int64_t)i), xs[i]->data());
+  return W(out);
 }
 std::vector<TP> StackBackward(const std::vector<int64_t>&, int64_t dim, const TP& g) {
   std::vector<TP> out;

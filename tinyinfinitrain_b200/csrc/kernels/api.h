@@ -223,8 +223,10 @@ TITB_API int titb_gather_nd(const void* in, void* out, int nd, const long long* 
 // out[out_offset + sum_d i_d * out_stride[d]] <- (or +=, with atomics) in (contiguous); nd <= 6.
 TITB_API int titb_scatter_nd(const void* in, void* out, int nd, const long long* size, const long long* out_stride,
                              long long out_offset, int dtype, int accumulate, cudaStream_t stream);
-// forward (backward = 0): y = mask ? value : x;  backward = 1: y = mask ? 0 : x.  The mask has mask_n
-// elements and repeats over the leading extent of x (n % mask_n == 0).  mask_dtype: 0 fp32, 1 bf16, 2 uint8/bool.
+// y = masked ? value : x, or with bit 0 of `backward` set y = masked ? 0 : x (gradient of the former).  An
+// element is masked when its mask entry is non-zero, or, with bit 1 of `backward` set, when it equals 1 (the
+// reference's rule).  The mask has mask_n elements and repeats by modulo over the flattened x.
+// mask_dtype: 0 fp32, 1 bf16, 2 uint8/bool.
 TITB_API int titb_mask_fill(const void* x, const void* mask, void* y, long long n, long long mask_n, float value,
                             int backward, int dtype, int mask_dtype, cudaStream_t stream);
 TITB_API int titb_outer(const void* a, const void* b, void* y, long long M, long long N, int dtype, cudaStream_t stream);

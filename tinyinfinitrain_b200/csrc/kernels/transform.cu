@@ -149,20 +149,21 @@ __global__ void scatter_kernel(const T* __restrict__ in, T* __restrict__ out, lo
 }
 
 // ------------------------------------------------------------------------------ mask / outer
-// y = mask != 0 ? value : x   (mask broadcast over the leading dims: mask has `mask_n` elements)
-__device__ __forceinline__ bool mask_on(float m) { return m != 0.f; }
-__device__ __forceinline__ bool mask_on(bf16 m) { return __bfloat162float(m) != 0.f; }
-__device__ __forceinline__ bool mask_on(unsigned char m) { return m != 0; }
+// y = mask ? value : x, the mask repeating by modulo over the flattened input (mask_n elements)
+__device__ __forceinline__ float mask_value(float m) { return m; }
+__device__ __forceinline__ float mask_value(bf16 m) { return __bfloat162float(m); }
+__device__ __forceinline__ float mask_value(unsigned char m) { return static_cast<float>(m); }
 
 template <typename T, typename M>
 __global__ void mask_fill_kernel(const T* __restrict__ x, const M* __restrict__ mask, T* __restrict__ y, long long n,
-                                 long long mask_n, float value, int keep_unmasked_only) {
+                                 long long mask_n, float value, int flags) {
   const long long stride = (long long)gridDim.x * blockDim.x;
   const T fill = from_f32<T>(value);
   for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < n; t += stride) {
-    const bool m = mask_on(mask[t % mask_n]);
-    // forward: masked positions take `value`; backward: masked positions pass no gradient
-    y[t] = m ? (keep_unmasked_only ? from_f32<T>(0.f) : fill) : x[t];
+    const float mv = mask_value(mask[t % mask_n]);
+    const bool m = (flags & 2) ? (mv == 1.f) : (mv != 0.f);
+    // forward: masked positions take `value`; backward (flag bit 0): masked positions pass no gradient
+    y[t] = m ? ((flags & 1) ? from_f32<T>(0.f) : fill) : x[t];
   }
 }
 
