@@ -202,6 +202,7 @@ def main():
                        "parallelism": f"dp{world}" + ("+zero1" if world > 1 and not library else ""), "micro_batch_per_gpu": B,
                        "optimizer": "AdamW(fp32 params, bf16 autocast)" if library else "AdamW(fp32 master, bf16 params)", "cuda_graph": getattr(step, "graph", None) is not None,
                        "comm": ("nccl-ddp" if library else args.comm) if world > 1 else "none",
+                       "nvls_multimem": bool(getattr(getattr(opt, "gbuf", None), "mc_ptr", 0)) if not library else False,
                        "l2": "per-step working set (activations + weights + optimizer state, >10 GB) exceeds the "
                              "126 MB L2; no explicit flush",
                        "init": "random N(0,0.02), seed 42", "final_loss": final_loss, "kernel_status": status},
