@@ -220,3 +220,15 @@ def test_cpp_facade_cuda_ops_match_cpu_oracle():
         assert cpu[k].shape == gpu[k].shape, k
         assert torch.allclose(cpu[k], gpu[k], atol=1e-5, rtol=1e-5), k
     _status_ok()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_zero1_on_the_native_symmetric_heap():
+    """The ZeRO-1 worker with buffers from this package's own heap (cuMem VMM + descriptor passing) instead of
+    PyTorch's symmetric-memory allocator."""
+    n = min(torch.cuda.device_count(), 8)
+    env = dict(os.environ, TITB200_SYMM_HEAP="native")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29990 - os.getpid() % 90), os.path.join(HERE, "dist_zero_check.py")]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]

@@ -634,6 +634,7 @@ void gemm_debug_override(int64_t lbo, int64_t sbo, int64_t kstep) {
 void bind_attention(pybind11::module_& m);
 void bind_comm(pybind11::module_& m);
 void bind_core(pybind11::module_& m);
+void bind_symm(pybind11::module_& m);
 
 PYBIND11_MODULE(_C, m) {
   m.doc() = "tinyinfinitrain_b200 native ops (sm_100a)";
@@ -702,4 +703,5 @@ PYBIND11_MODULE(_C, m) {
   bind_attention(m);
   bind_comm(m);
   bind_core(m);
+  bind_symm(m);
 }
