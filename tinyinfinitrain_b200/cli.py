@@ -40,6 +40,8 @@ def build_parser(family: str) -> argparse.ArgumentParser:
     p.add_argument("--num_microbatches", type=int, default=1)
     p.add_argument("--zero_stage", type=int, default=1, choices=[0, 1])
     p.add_argument("--comm", default="fused", choices=["fused", "nccl"])
+    p.add_argument("--dp_buckets", type=int, default=1,
+                   help="ZeRO-1 buckets; >1 reduces each bucket beside backward as soon as its gradients are written")
     p.add_argument("--seed", type=int, default=42)
     p.add_argument("--synthetic", action="store_true")
     p.add_argument("--n_layer", type=int, default=0, help="override the preset depth (smoke tests)")
@@ -158,7 +160,8 @@ def train_main(family: str, argv=None) -> int:
     params = list(model.parameters())
     if mesh.dp > 1 and args.zero_stage == 1:
         opt = DistributedOptimizer(params, lr=args.learning_rate, weight_decay=args.weight_decay, group=mesh.dp_group,
-                                   comm=args.comm if cuda else "nccl")
+                                   comm=args.comm if cuda else "nccl", num_buckets=args.dp_buckets,
+                                   overlap=args.dp_buckets > 1)
     else:
         opt = tit.optim.MixedPrecisionAdam(params, lr=args.learning_rate, weight_decay=args.weight_decay)
     loader = _data(args, cfg, mesh.dp_rank, mesh.dp, cuda)

@@ -99,6 +99,7 @@ UNARY_IMPL(Cos, false)
 UNARY_IMPL(Tanh, true)
 UNARY_IMPL(Rsqrt, false)
 UNARY_IMPL(Sigmoid, true)
+UNARY_IMPL(Gelu, false)
 
 TensorList Pow::Forward(const TensorList& in) {
   return {K(in[0], "PowForward").Call<TP, const TP&, float, bool>(in[0], exponent_, scalar_is_base_)};

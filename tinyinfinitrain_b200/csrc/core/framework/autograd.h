@@ -69,6 +69,9 @@ TITB_DECLARE_UNARY(Cos)
 TITB_DECLARE_UNARY(Tanh)
 TITB_DECLARE_UNARY(Rsqrt)
 TITB_DECLARE_UNARY(Sigmoid)
+// tanh-form GELU in one kernel (not in the reference, whose NewGELU module composes eight element-wise ops:
+// example/gpt2/net.cc:46-51); saves the input
+TITB_DECLARE_UNARY(Gelu)
 
 class Pow : public Function {
  public:

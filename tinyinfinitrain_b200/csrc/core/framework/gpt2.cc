@@ -15,6 +15,9 @@ using nn::TensorList;
 
 TensorList NewGELU::Forward(const TensorList& in) {
   const TP& x = in[0];
+  // On the GPU the activation is one kernel; on the CPU it stays the reference's chain of element-wise
+  // Functions so that CPU results match the reference operation for operation.
+  if (x->GetDevice().IsCUDA()) return std::make_shared<autograd::Gelu>()->Apply({x});
   // 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)))
   TP inner = (x + x->Pow(3.0f) * 0.044715f) * std::sqrt(2.0f / static_cast<float>(M_PI));
   return {(x * 0.5f) * (inner->Tanh() + 1.0f)};

@@ -138,6 +138,31 @@ UNARY_KERNEL(Tanh, TITB_TANH, a.tanh(), g * (1 - a * a))          // saved = out
 UNARY_KERNEL(Rsqrt, TITB_RSQRT, a.rsqrt(), g * (-0.5 / (a * a.sqrt())))
 UNARY_KERNEL(Sigmoid, TITB_SIGMOID, a.sigmoid(), g * a * (1 - a))  // saved = output
 
+// GELU, tanh form: 0.5 x (1 + tanh(k (x + 0.044715 x^3))), k = sqrt(2 / pi); saved = input
+static at::Tensor gelu_inner(const at::Tensor& x) { return (x + x.pow(3) * 0.044715) * 0.7978845608028654; }
+TP GeluForward(const TP& x) {
+  const at::Tensor& a = x->data();
+  if (native(a) && a.is_contiguous()) {
+    c10::cuda::CUDAGuard guard(a.device());
+    at::Tensor y = at::empty_like(a);
+    ok(titb_gelu_fwd(a.data_ptr(), y.data_ptr(), a.numel(), dt(a), stream()), "Gelu");
+    return W(y);
+  }
+  return W(a * 0.5 * (gelu_inner(a).tanh() + 1));
+}
+TP GeluBackward(const TP& dy, const TP& saved) {
+  const at::Tensor &g = dy->data(), &a = saved->data();
+  if (native(g) && g.is_contiguous() && a.is_contiguous() && a.scalar_type() == g.scalar_type()) {
+    c10::cuda::CUDAGuard guard(g.device());
+    at::Tensor dx = at::empty_like(g);
+    ok(titb_gelu_bwd(g.data_ptr(), a.data_ptr(), dx.data_ptr(), g.numel(), dt(g), stream()), "GeluBackward");
+    return W(dx);
+  }
+  at::Tensor t = gelu_inner(a).tanh();
+  at::Tensor dinner = (a.pow(2) * (3 * 0.044715) + 1) * 0.7978845608028654;
+  return W(g * (0.5 * (t + 1) + 0.5 * a * (1 - t * t) * dinner));
+}
+
 TP PowForward(const TP& x, float e, bool scalar_is_base) {
   return unary(scalar_is_base ? TITB_POW_SCALAR_BASE : TITB_POW_SCALAR_EXP, x, e,
                scalar_is_base ? +[](const at::Tensor& a, float s) -> at::Tensor { return at::pow(s, a); }
@@ -562,7 +587,7 @@ REG_BOTH(AccumulateGrad); REG_BOTH(AdamAccumulateGrad); REG_BOTH(Fill);
 REG_BOTH(NegForward); REG_BOTH(NegBackward); REG_BOTH(ReciprocalForward); REG_BOTH(ReciprocalBackward);
 REG_BOTH(SinForward); REG_BOTH(SinBackward); REG_BOTH(CosForward); REG_BOTH(CosBackward);
 REG_BOTH(TanhForward); REG_BOTH(TanhBackward); REG_BOTH(RsqrtForward); REG_BOTH(RsqrtBackward);
-REG_BOTH(SigmoidForward); REG_BOTH(SigmoidBackward); REG_BOTH(PowForward); REG_BOTH(PowBackward);
+REG_BOTH(SigmoidForward); REG_BOTH(SigmoidBackward); REG_BOTH(GeluForward); REG_BOTH(GeluBackward); REG_BOTH(PowForward); REG_BOTH(PowBackward);
 REG_BOTH(EqualsScalarForward); REG_BOTH(AddScalarForward); REG_BOTH(AddScalarBackward);
 REG_BOTH(MulScalarForward); REG_BOTH(MulScalarBackward);
 REG_BOTH(AddForward); REG_BOTH(AddBackward); REG_BOTH(SubForward); REG_BOTH(SubBackward);

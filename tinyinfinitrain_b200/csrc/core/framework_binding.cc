@@ -36,6 +36,7 @@ std::shared_ptr<fw::autograd::Function> make_function(const std::string& name, c
   if (name == "Tanh") return std::make_shared<Tanh>();
   if (name == "Rsqrt") return std::make_shared<Rsqrt>();
   if (name == "Sigmoid") return std::make_shared<Sigmoid>();
+  if (name == "Gelu") return std::make_shared<Gelu>();
   if (name == "Pow") return std::make_shared<Pow>((float)f(0, 2), f(1, 0) != 0);
   if (name == "EqualsScalar") return std::make_shared<EqualsScalar>((float)f(0, 0));
   if (name == "AddScalar") return std::make_shared<AddScalar>((float)f(0, 0));
