@@ -153,9 +153,11 @@ def train_main(family: str, argv=None) -> int:
     model = TPTransformer(cfg, comm, device=dev, dtype=dtype, seed=args.seed, layers=layers, first=mesh.is_first_stage,
                           last=mesh.is_last_stage)
     if args.llmc_filepath:
-        from ._lib import C
+        from .utils.llmc import map_checkpoint
 
-        _, sd = (C.llmc_read_gpt2(args.llmc_filepath, True) if family == "gpt2" else C.llmc_read_llama3(args.llmc_filepath))
+        # memory-mapped views: every rank touches only the rows / columns of its own shard
+        fam, _, sd = map_checkpoint(args.llmc_filepath)
+        assert fam == family, f"{args.llmc_filepath} is a {fam} checkpoint"
         model.load_full_state_dict(sd)
     params = list(model.parameters())
     if mesh.dp > 1 and args.zero_stage == 1:

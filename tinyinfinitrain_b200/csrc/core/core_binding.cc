@@ -76,6 +76,16 @@ void bind_core(pybind11::module_& m) {
     auto sd = titb::llmc::read_gpt2(path, &h, keep_padding);
     return py::make_tuple(gpt2_header_dict(h), sd);
   }, py::arg("path"), py::arg("keep_padding") = false);
+  m.def("llmc_map_gpt2", [](const std::string& path) {
+    titb::llmc::Gpt2Header h;
+    auto sd = titb::llmc::map_gpt2(path, &h);
+    return py::make_tuple(gpt2_header_dict(h), sd);
+  });
+  m.def("llmc_map_llama3", [](const std::string& path) {
+    titb::llmc::Llama3Header h;
+    auto sd = titb::llmc::map_llama3(path, &h);
+    return py::make_tuple(llama3_header_dict(h), sd);
+  });
   m.def("llmc_write_gpt2", [](const std::string& path, const py::dict& header, const titb::llmc::StateDict& sd) {
     titb::llmc::write_gpt2(path, gpt2_header_from(header), sd);
   });

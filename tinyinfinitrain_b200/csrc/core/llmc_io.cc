@@ -1,5 +1,10 @@
 #include "core/llmc_io.h"
 
+#include <fcntl.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
 #include <c10/util/Exception.h>
 
 #include <cstdio>
@@ -166,6 +171,76 @@ void write_llama3(const std::string& path, const Llama3Header& h, const StateDic
     for (int l = 0; l < h.n_layer; ++l) write_block(out, get(sd, layer_key(l, k.name)), h.version);
   write_block(out, get(sd, "transformer.ln_f.weight"), h.version);
   write_block(out, get(sd, "lm_head.weight").narrow(0, 0, h.vocab_size), h.version);
+}
+
+
+// ---------------------------------------------------------------------------- memory-mapped views
+namespace {
+struct Mapping {
+  void* base = MAP_FAILED;
+  size_t bytes = 0;
+  ~Mapping() { if (base != MAP_FAILED) munmap(base, bytes); }
+};
+std::shared_ptr<Mapping> map_file(const std::string& path) {
+  const int fd = open(path.c_str(), O_RDONLY | O_CLOEXEC);
+  TORCH_CHECK(fd >= 0, "cannot open ", path);
+  struct stat st;
+  if (fstat(fd, &st) != 0) { close(fd); TORCH_CHECK(false, "cannot stat ", path); }
+  auto m = std::make_shared<Mapping>();
+  m->bytes = static_cast<size_t>(st.st_size);
+  m->base = mmap(nullptr, m->bytes, PROT_READ | PROT_WRITE, MAP_PRIVATE, fd, 0);
+  close(fd);
+  TORCH_CHECK(m->base != MAP_FAILED, "cannot map ", path);
+  return m;
+}
+// Hands out consecutive blocks of the payload as tensors that keep the mapping alive.
+struct BlockCursor {
+  std::shared_ptr<Mapping> map;
+  size_t pos;
+  int version;
+  at::Tensor next(std::vector<int64_t> shape) {
+    int64_t n = 1;
+    for (int64_t d : shape) n *= d;
+    const size_t esz = version == kVersionFp32 ? 4 : 2;
+    TORCH_CHECK(pos + n * esz <= map->bytes, "checkpoint file is shorter than its header implies");
+    auto keep = map;
+    at::Tensor t = at::from_blob(static_cast<char*>(map->base) + pos, shape, [keep](void*) mutable { keep.reset(); },
+                                 at::TensorOptions().dtype(version == kVersionFp32 ? at::kFloat : at::kBFloat16));
+    pos += n * esz;
+    return t;
+  }
+};
+}  // namespace
+
+StateDict map_gpt2(const std::string& path, Gpt2Header* header_out) {
+  const Gpt2Header h = read_gpt2_header(path);
+  if (header_out) *header_out = h;
+  BlockCursor cur{map_file(path), 256 * sizeof(int32_t), h.version};
+  const int64_t C = h.n_embd;
+  StateDict sd;
+  sd["transformer.wte.weight"] = cur.next({h.padded_vocab_size, C});
+  sd["transformer.wpe.weight"] = cur.next({h.block_size, C});
+  for (const Kind& k : gpt2_kinds(C))
+    for (int l = 0; l < h.n_layer; ++l)
+      sd[layer_key(l, k.name)] = k.cols ? cur.next({k.rows, k.cols}) : cur.next({k.rows});
+  sd["transformer.ln_f.weight"] = cur.next({C});
+  sd["transformer.ln_f.bias"] = cur.next({C});
+  sd["lm_head.weight"] = sd["transformer.wte.weight"];  // tied
+  return sd;
+}
+
+StateDict map_llama3(const std::string& path, Llama3Header* header_out) {
+  const Llama3Header h = read_llama3_header(path);
+  if (header_out) *header_out = h;
+  BlockCursor cur{map_file(path), 256 * sizeof(int32_t), h.version};
+  StateDict sd;
+  sd["transformer.wte.weight"] = cur.next({h.vocab_size, h.n_embd});
+  for (const Kind& k : llama3_kinds(h))
+    for (int l = 0; l < h.n_layer; ++l)
+      sd[layer_key(l, k.name)] = k.cols ? cur.next({k.rows, k.cols}) : cur.next({k.rows});
+  sd["transformer.ln_f.weight"] = cur.next({h.n_embd});
+  sd["lm_head.weight"] = cur.next({h.vocab_size, h.n_embd});
+  return sd;
 }
 
 // ----------------------------------------------------------------------------- tokens

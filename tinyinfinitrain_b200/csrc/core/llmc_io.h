@@ -47,6 +47,13 @@ Gpt2Header read_gpt2_header(const std::string& path);
 StateDict read_gpt2(const std::string& path, Gpt2Header* header_out, bool keep_padding);
 void write_gpt2(const std::string& path, const Gpt2Header& header, const StateDict& sd);
 
+// Memory-mapped views of the same tensors (no copy, pages are read when touched): fp32 payloads map to float
+// tensors, bf16 payloads to bfloat16 tensors; GPT-2's wte keeps all padded rows.  A tensor-parallel rank slices
+// its rows / columns out of these views, so it only ever reads its own part of a large file.  The mapping is
+// private (copy-on-write) and lives as long as any returned tensor.
+StateDict map_gpt2(const std::string& path, Gpt2Header* header_out);
+StateDict map_llama3(const std::string& path, Llama3Header* header_out);
+
 Llama3Header read_llama3_header(const std::string& path);
 StateDict read_llama3(const std::string& path, Llama3Header* header_out);
 void write_llama3(const std::string& path, const Llama3Header& header, const StateDict& sd);

@@ -38,8 +38,9 @@ def _qkv_rows(n_head: int, n_kv_head: int, hd: int, tp: int, rank: int):
     return torch.cat([q, k, v])
 
 
-def shard_state_dict(sd: Dict[str, torch.Tensor], cfg, tp: int, rank: int) -> Dict[str, torch.Tensor]:
-    """Slices a full GPT-2 / LLaMA-3 state dict for tensor-parallel rank ``rank`` of ``tp``."""
+def shard_state_dict(sd: Dict[str, torch.Tensor], cfg, tp: int, rank: int, vocab_padded: int = 0) -> Dict[str, torch.Tensor]:
+    """Slices a full GPT-2 / LLaMA-3 state dict for tensor-parallel rank ``rank`` of ``tp``.  ``vocab_padded`` is
+    the row count the vocabulary-sharded tensors are padded to (zero rows) before they are split."""
     is_llama = isinstance(cfg, LLaMA3Config)
     n_kv = cfg.n_kv_head if is_llama else cfg.n_head
     hd = cfg.n_embd // cfg.n_head
@@ -62,8 +63,13 @@ def shard_state_dict(sd: Dict[str, torch.Tensor], cfg, tp: int, rank: int) -> Di
             n = t.shape[1] // tp
             out[name] = t[:, rank * n:(rank + 1) * n]
         elif name in ("transformer.wte.weight", "lm_head.weight"):
-            n = t.shape[0] // tp
-            out[name] = t[rank * n:(rank + 1) * n]
+            rows = max(vocab_padded, t.shape[0]) if vocab_padded else t.shape[0]
+            n = rows // tp
+            lo, hi = rank * n, (rank + 1) * n
+            part = t[min(lo, t.shape[0]):min(hi, t.shape[0])]
+            if part.shape[0] < n:  # this rank's range reaches into the zero padding
+                part = torch.cat([part, torch.zeros(n - part.shape[0], t.shape[1], dtype=t.dtype)])
+            out[name] = part
         else:
             out[name] = t
     return {k: v.contiguous() for k, v in out.items()}
@@ -201,13 +207,10 @@ class TPTransformer(nn.Module):
                 init.Normal(p, 0.0, 0.02, generator=seed)
 
     def load_full_state_dict(self, sd: Dict[str, torch.Tensor]) -> None:
-        """Loads this rank's slices from a full (unsharded) state dict of the single-GPU model."""
-        sd = dict(sd)
-        for k in ("transformer.wte.weight", "lm_head.weight"):
-            if k in sd and sd[k].shape[0] < self.vocab_padded:
-                pad = torch.zeros(self.vocab_padded - sd[k].shape[0], sd[k].shape[1], dtype=sd[k].dtype)
-                sd[k] = torch.cat([sd[k].cpu(), pad])
-        mine = shard_state_dict(sd, self.config, self.comm.world, self.comm.rank)
+        """Loads this rank's slices from a full (unsharded) state dict of the single-GPU model.  The tensors may
+        be memory-mapped views of a checkpoint file (``utils.llmc.map_checkpoint``): slicing happens before any
+        copy, so a rank only reads its own rows and columns of the file."""
+        mine = shard_state_dict(sd, self.config, self.comm.world, self.comm.rank, vocab_padded=self.vocab_padded)
         own = dict(self.named_parameters(remove_duplicate=False))
         with torch.no_grad():
             for name, p in own.items():

@@ -61,3 +61,20 @@ def save_llama3(model, path: str, bf16: bool = False) -> None:
            "ffn_dim": cfg.ffn_dim, "rope_theta": cfg.rope_theta, "norm_eps": cfg.norm_eps}
     sd = {k: v.detach().float().cpu() for k, v in model.StateDict().items()}
     C.llmc_write_llama3(path, hdr, sd)
+
+
+def map_checkpoint(path: str):
+    """Memory-maps an llm.c GPT-2 or LLaMA-3 checkpoint: returns ``(family, header, state_dict)`` whose tensors are
+    views into the file (fp32 or bf16, as stored; no copy, pages load when touched).  Used for tensor-parallel
+    loading, where each rank slices out its own rows and columns."""
+    import struct
+
+    with open(path, "rb") as f:
+        magic = struct.unpack("<i", f.read(4))[0]
+    if magic == 20240326:
+        hdr, sd = C.llmc_map_gpt2(path)
+        return "gpt2", hdr, sd
+    if magic == 20240803:
+        hdr, sd = C.llmc_map_llama3(path)
+        return "llama3", hdr, sd
+    raise ValueError(f"{path}: unknown checkpoint magic {magic}")
