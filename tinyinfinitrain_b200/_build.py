@@ -127,6 +127,10 @@ def build(verbose: bool = False, force: bool = False) -> None:
     ]
     for i in inc:
         cflags += ["-isystem", i]
+    # TITB200_SANITIZE=1: AddressSanitizer + UBSan build of the host-side C++ (run the CPU tests with
+    # LD_PRELOAD=$(g++ -print-file-name=libasan.so) and ASAN_OPTIONS=detect_leaks=0); rebuild without it afterwards.
+    sanitize = ["-fsanitize=address,undefined", "-fno-omit-frame-pointer", "-g"] if os.environ.get("TITB200_SANITIZE") else []
+    cflags += sanitize
     cjobs, cobjs = [], []
     for s in cc_srcs:
         tag = hashlib.sha1(str(s.relative_to(CSRC)).encode()).hexdigest()[:6]
@@ -136,8 +140,8 @@ def build(verbose: bool = False, force: bool = False) -> None:
         cobjs.append(o)
         cjobs.append(([CXX, *cflags, "-c", s, "-o", o], o))
     changed2 = _compile_all(cjobs, verbose)
-    if changed or changed2 or not CORE_LIB.exists():
-        link = [CXX, "-shared", "-o", CORE_LIB, *cobjs,
+    if changed or changed2 or not CORE_LIB.exists() or sanitize:
+        link = [CXX, "-shared", *sanitize, "-o", CORE_LIB, *cobjs,
                 f"-L{PKG}", "-ltitb200_kernels", "-Wl,-rpath,$ORIGIN"]
         for l in lib:
             link += [f"-L{l}", f"-Wl,-rpath,{l}"]
