@@ -108,8 +108,8 @@ class DistributedOptimizer:
                     b["params"].append(p)
                     p._bucket = b
                     break
+        self.comm_stream = None  # created at the first side-stream launch
         if self.overlap:
-            self.comm_stream = torch.cuda.Stream(device=f.device)
             for p in f.params:
                 p._on_grad_ready = self._grad_ready
                 p._expected = None  # reports per step, learned from the first step
@@ -148,6 +148,8 @@ class DistributedOptimizer:
 
         b1, b2 = self.betas
         main = torch.cuda.current_stream(self.flat.device)
+        if side and self.overlap and self.comm_stream is None:
+            self.comm_stream = torch.cuda.Stream(device=self.flat.device)
         stream = self.comm_stream if (side and self.overlap) else main
         if stream is not main:
             stream.wait_stream(main)
@@ -207,7 +209,8 @@ class DistributedOptimizer:
                     # same stream as the early buckets: the barrier channel is used by one stream at a time
                     self._launch_bucket(b, side=True)
             if self.overlap:
-                main.wait_stream(self.comm_stream)
+                if self.comm_stream is not None:
+                    main.wait_stream(self.comm_stream)
                 if not self._learned:
                     self._finish_learning()
             self.t += 1
