@@ -12,7 +12,6 @@ import argparse
 import json
 import os
 import sys
-import time
 
 import torch
 
@@ -182,27 +181,27 @@ def train_main(family: str, argv=None) -> int:
     meter = ThroughputMeter(B * T * nm * mesh.dp, 0.0, 0.0)
     it = 0
     for step in range(args.num_iteration):
-        t0 = time.perf_counter()
-        batches = []
-        for _ in range(nm):
-            x, y = loader.batch(it % len(loader))
-            it += 1
-            batches.append((x.to(dev, non_blocking=True), y.to(dev, non_blocking=True)))
-        opt.zero_grad()
-        loss = stage.run(nm)
-        sync_sequence_parallel_grads(params, comm)
-        opt.step()
-        if cuda:
-            torch.cuda.synchronize()
-        ms = torch.tensor([(time.perf_counter() - t0) * 1e3], device=dev)
+        # device-timed (CUDA events on the launching stream; wall clock only on the CPU path), max over ranks
+        with CudaTimer() as tm:
+            batches = []
+            for _ in range(nm):
+                x, y = loader.batch(it % len(loader))
+                it += 1
+                batches.append((x.to(dev, non_blocking=True), y.to(dev, non_blocking=True)))
+            opt.zero_grad()
+            loss = stage.run(nm)
+            sync_sequence_parallel_grads(params, comm)
+            opt.step()
+        ms = torch.tensor([tm.ms], device=dev)
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         lossv = torch.tensor([float(loss) if loss is not None else 0.0], device=dev)
         dist.all_reduce(lossv)
         lossv = lossv.item() / (mesh.dp * tp)          # the last stage of every replica (and each tp rank) reports it
         rep = meter.report(ms.item())
         if rank == 0:
-            print(f"step {step + 1}/{args.num_iteration} | loss {lossv:.6f} | {ms.item():.2f} ms | "
-                  f"{rep['tokens_per_s']:.0f} tok/s | tp{tp} pp{pp} dp{mesh.dp}", flush=True)
+            mem = f" | peak mem {torch.cuda.max_memory_allocated(dev) / 2**30:.1f} GiB" if cuda else ""
+            print(f"step {step + 1}/{args.num_iteration} | loss {lossv:.6f} | lr {args.learning_rate:.2e} | "
+                  f"{ms.item():.2f} ms | {rep['tokens_per_s']:.0f} tok/s | tp{tp} pp{pp} dp{mesh.dp}{mem}", flush=True)
         log.log(step=step + 1, loss=lossv, **rep)
     if cuda:
         status = tit._lib.C.status_read(True)
