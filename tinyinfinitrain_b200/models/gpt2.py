@@ -193,5 +193,11 @@ class GPT2(nn.Module):
         llmc.save_gpt2(self, path, bf16=bf16)
 
     @classmethod
-    def FromPretrained(cls, model_type: str):
-        raise NotImplementedError("FromPretrained needs network access; use FromLLMC with an llm.c .bin file")
+    def FromPretrained(cls, path_or_name: str, device=None, dtype=torch.float32) -> "GPT2":
+        """A Hugging Face GPT-2 checkpoint directory or cached model name, opened with ``transformers`` without
+        network access (the reference's FromPretrained aborts: example/gpt2/net.cc:223-226)."""
+        from ..utils import hf
+
+        model = hf.from_pretrained(path_or_name, device=device, dtype=dtype)
+        assert isinstance(model, cls), f"{path_or_name} is not a GPT-2 checkpoint"
+        return model

@@ -151,3 +151,12 @@ class LLaMA3(nn.Module):
         from ..utils import llmc
 
         llmc.save_llama3(self, path, bf16=bf16)
+
+    @classmethod
+    def FromPretrained(cls, path_or_name: str, device=None, dtype=torch.float32) -> "LLaMA3":
+        """A Hugging Face LLaMA checkpoint directory (opened with ``transformers``, local files only)."""
+        from ..utils import hf
+
+        model = hf.from_pretrained(path_or_name, device=device, dtype=dtype)
+        assert isinstance(model, cls), f"{path_or_name} is not a LLaMA checkpoint"
+        return model
