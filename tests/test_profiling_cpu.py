@@ -40,3 +40,26 @@ def test_jsonl_logger_and_trace(tmp_path):
     with torch_profile(str(tmp_path / "trace.json")):
         lin(torch.randn(2, 4)).sum().backward()
     assert "traceEvents" in json.load(open(tmp_path / "trace.json"))
+
+
+def test_warmup_cosine_schedule_and_scheduler():
+    import math
+
+    from tinyinfinitrain_b200.optim import LRScheduler, warmup_cosine
+
+    f = lambda s: warmup_cosine(s, 1.0, 4, 20, 0.1)  # noqa: E731
+    assert [round(f(s), 4) for s in range(4)] == [0.25, 0.5, 0.75, 1.0]
+    assert f(4) == 1.0 and abs(f(12) - (0.1 + 0.9 * 0.5)) < 1e-12 and abs(f(20) - 0.1) < 1e-12 and f(1000) == 0.1
+    assert all(f(s) >= f(s + 1) for s in range(4, 25))
+    assert abs(warmup_cosine(8, 2.0, 0, 16, 0.0) - 2.0 * 0.5 * (1 + math.cos(math.pi / 2))) < 1e-12
+
+    class Opt:
+        lr = 0.0
+
+        def set_lr(self, lr):
+            self.lr = lr
+
+    o = Opt()
+    sched = LRScheduler(o, f)
+    assert o.lr == 0.25
+    assert [sched.step() for _ in range(3)] == [0.5, 0.75, 1.0] and o.lr == 1.0

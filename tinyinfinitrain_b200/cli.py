@@ -31,6 +31,9 @@ def build_parser(family: str) -> argparse.ArgumentParser:
     p.add_argument("--freq_generate_txt", type=int, default=0)
     p.add_argument("--learning_rate", type=float, default=1e-4)
     p.add_argument("--weight_decay", type=float, default=0.0)
+    p.add_argument("--warmup_steps", type=int, default=0, help="linear learning-rate warm-up steps")
+    p.add_argument("--lr_decay_steps", type=int, default=0, help="cosine decay horizon in steps (0 = constant rate)")
+    p.add_argument("--min_lr_ratio", type=float, default=0.1, help="final rate of the cosine decay / peak rate")
     p.add_argument("--optimizer", default="adam", choices=["adam", "sgd"])
     p.add_argument("--dtype", default="bfloat16", choices=["float32", "bfloat16"])
     p.add_argument("--tensor_parallel", type=int, default=1)
@@ -100,6 +103,22 @@ def train_main(family: str, argv=None) -> int:
     log = JsonlLogger(args.log_jsonl if rank == 0 else None)
     B, T = args.batch_size, args.sequence_length
 
+    def lr_at(step: int) -> float:
+        from .optim.schedule import warmup_cosine
+
+        if not args.lr_decay_steps and not args.warmup_steps:
+            return args.learning_rate
+        return warmup_cosine(step, args.learning_rate, args.warmup_steps, args.lr_decay_steps or (1 << 62),
+                             args.min_lr_ratio if args.lr_decay_steps else 1.0)
+
+    def apply_lr(opt, step: int) -> float:
+        lr = lr_at(step)
+        if hasattr(opt, "set_lr"):
+            opt.set_lr(lr)
+        else:
+            opt.lr = lr
+        return lr
+
     if not distributed:
         # ------------------------------------------------------------------ one process
         cls = GPT2 if family == "gpt2" else LLaMA3
@@ -116,6 +135,7 @@ def train_main(family: str, argv=None) -> int:
         tok = tit.data.Tokenizer(args.tokenizer_bin) if args.tokenizer_bin else None
         it = 0
         for step in range(start, args.num_iteration):
+            lr = apply_lr(opt, step)
             with CudaTimer() as tm:
                 opt.zero_grad()
                 lossf = 0.0
@@ -130,10 +150,10 @@ def train_main(family: str, argv=None) -> int:
                 opt.step()
             rep = meter.report(tm.ms)
             if rank == 0:
-                print(f"step {step + 1}/{args.num_iteration} | loss {lossf:.6f} | lr {args.learning_rate:.2e} | "
+                print(f"step {step + 1}/{args.num_iteration} | loss {lossf:.6f} | lr {lr:.2e} | "
                       f"{tm.ms:.2f} ms | {rep['tokens_per_s']:.0f} tok/s" + (f" | mfu {rep['mfu']:.3f}" if 'mfu' in rep else ""),
                       flush=True)
-            log.log(step=step + 1, loss=lossf, **rep)
+            log.log(step=step + 1, loss=lossf, lr=lr, **rep)
             if tok is not None and args.freq_generate_txt and (step + 1) % args.freq_generate_txt == 0:
                 tok.GenerateText(model, B, T, args.text_length, dev, stream=sys.stdout)
         if args.save:
@@ -181,6 +201,7 @@ def train_main(family: str, argv=None) -> int:
     meter = ThroughputMeter(B * T * nm * mesh.dp, 0.0, 0.0)
     it = 0
     for step in range(args.num_iteration):
+        lr = apply_lr(opt, step)
         # device-timed (CUDA events on the launching stream; wall clock only on the CPU path), max over ranks
         with CudaTimer() as tm:
             batches = []
@@ -200,9 +221,9 @@ def train_main(family: str, argv=None) -> int:
         rep = meter.report(ms.item())
         if rank == 0:
             mem = f" | peak mem {torch.cuda.max_memory_allocated(dev) / 2**30:.1f} GiB" if cuda else ""
-            print(f"step {step + 1}/{args.num_iteration} | loss {lossv:.6f} | lr {args.learning_rate:.2e} | "
+            print(f"step {step + 1}/{args.num_iteration} | loss {lossv:.6f} | lr {lr:.2e} | "
                   f"{ms.item():.2f} ms | {rep['tokens_per_s']:.0f} tok/s | tp{tp} pp{pp} dp{mesh.dp}{mem}", flush=True)
-        log.log(step=step + 1, loss=lossv, **rep)
+        log.log(step=step + 1, loss=lossv, lr=lr, **rep)
     if cuda:
         status = tit._lib.C.status_read(True)
         if status:
