@@ -28,6 +28,20 @@ def main():
     ok = True
     msgs = []
     for rep in range(2):
+        if rep == 1:
+            # poison, then verify: every staging / receive buffer of the fused kernels is filled with NaN (the arrival
+            # counters are left alone), so a tile that a kernel reads before its producer has written it cannot
+            # pass unnoticed in the second round
+            ft = fused._fused
+            torch.cuda.synchronize()
+            dist.barrier()
+            for buf in ft._ag.values():
+                buf.tensor.fill_(float("nan"))
+            for recv, _cnt in ft._rs.values():
+                recv.tensor.fill_(float("nan"))
+            torch.cuda.synchronize()
+            dist.barrier()
+            ft.new_step()
         for (Ms, K, N) in [(128, 256, 512), (256, 2048, 384), (1024, 512, 1024)]:
             g = torch.Generator(device=dev).manual_seed(100 + rank + rep)
             x_s = (torch.randn(Ms, K, device=dev, generator=g) * 0.5).bfloat16()
