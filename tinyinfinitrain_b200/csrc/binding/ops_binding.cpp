@@ -625,9 +625,6 @@ Tensor colsum(const Tensor& x, const optional<Tensor>& out_, bool accumulate) {
 }
 
 int64_t status_read(bool clear) { return titb_status_read(clear, cur_stream()); }
-void gemm_debug_override(int64_t lbo, int64_t sbo, int64_t kstep) {
-  titb_gemm_debug_override((unsigned)lbo, (unsigned)sbo, (unsigned)kstep);
-}
 
 }  // namespace
 
@@ -698,7 +695,6 @@ PYBIND11_MODULE(_C, m) {
   m.def("tri", &tri);
   m.def("colsum", &colsum, py::arg("x"), py::arg("out") = py::none(), py::arg("accumulate") = false);
   m.def("status_read", &status_read, py::arg("clear") = true);
-  m.def("gemm_debug_override", &gemm_debug_override);
   m.def("gemm_set_tma_store", [](bool on) { titb_gemm_set_tma_store(on ? 1 : 0); });
   bind_attention(m);
   bind_comm(m);

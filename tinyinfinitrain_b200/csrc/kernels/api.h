@@ -88,8 +88,6 @@ struct TitbGemmDesc {
 TITB_API int titb_gemm_bf16(const TitbGemmDesc* d, cudaStream_t stream);
 // Picks the split-K factor the heuristic would use (so callers can size the workspace).
 TITB_API int titb_gemm_pick_splits(int M, int N, int K);
-// Debug hook: override descriptor strides for MN-major operands (0 = default).
-TITB_API void titb_gemm_debug_override(unsigned lbo, unsigned sbo, unsigned kstep);
 // Switches the shared-memory-staged TMA store epilogue of bf16 outputs on (default) or off (A/B timing).
 TITB_API void titb_gemm_set_tma_store(int enabled);
 // fp32 SIMT GEMM for API parity with fp32 tensors: C[M,N] (+)= op(A) op(B), row-major.

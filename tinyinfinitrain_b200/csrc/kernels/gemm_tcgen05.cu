@@ -807,8 +807,7 @@ int device_sm_count() {
   return sms[dev] > 0 ? sms[dev] : 148;
 }
 
-static unsigned g_dbg_lbo = 0, g_dbg_sbo = 0, g_dbg_kstep = 0;
-static int g_dbg_no_tma_store = 0;
+static int g_no_tma_store = 0;  // set by titb_gemm_set_tma_store(0): A/B switch for the epilogue store path
 
 static int pick_tile_n(int M, int N, int splits) {
   // 128 x 256 tiles move fewer operand bytes per FLOP; 128 x 128 only wins when it removes
@@ -859,10 +858,7 @@ TITB_API int titb_status_read(int clear, cudaStream_t stream) {
   return h;
 }
 
-TITB_API void titb_gemm_debug_override(unsigned lbo, unsigned sbo, unsigned kstep) {
-  g_dbg_lbo = lbo; g_dbg_sbo = sbo; g_dbg_kstep = kstep;
-}
-TITB_API void titb_gemm_set_tma_store(int enabled) { g_dbg_no_tma_store = enabled ? 0 : 1; }
+TITB_API void titb_gemm_set_tma_store(int enabled) { g_no_tma_store = enabled ? 0 : 1; }
 
 TITB_API int titb_gemm_pick_splits(int M, int N, int K) {
   // Split the reduction only when the output has too few tiles to fill the GPU and the
@@ -940,9 +936,7 @@ TITB_API int titb_gemm_bf16(const TitbGemmDesc* d, cudaStream_t stream) {
                (d->aux_out && ((reinterpret_cast<uintptr_t>(d->aux_out) & 15) || (d->ld_aux_out & 7))));
   // K-major: 32 bytes per 16-wide k step inside the 128-byte row, 8-row groups 1024 bytes apart.
   // MN-major: 16 k-rows of 128 bytes per step, 64-wide chunks one TMA box (64 x kBK) apart.
-  const uint32_t mn_lbo = g_dbg_lbo ? g_dbg_lbo : 64 * kBK * 2;
-  const uint32_t mn_sbo = g_dbg_sbo ? g_dbg_sbo : 1024;
-  const uint32_t mn_kstep = g_dbg_kstep ? g_dbg_kstep : 16 * 128;
+  const uint32_t mn_lbo = 64 * kBK * 2, mn_sbo = 1024, mn_kstep = 16 * 128;
   a.a_lbo = a.a_mn ? mn_lbo : 16; a.a_sbo = a.a_mn ? mn_sbo : 1024; a.a_kstep = a.a_mn ? mn_kstep : 32;
   a.b_lbo = a.b_mn ? mn_lbo : 16; a.b_sbo = a.b_mn ? mn_sbo : 1024; a.b_kstep = a.b_mn ? mn_kstep : 32;
   a.alpha = static_cast<const float*>(d->alpha);
@@ -977,7 +971,7 @@ TITB_API int titb_gemm_bf16(const TitbGemmDesc* d, cudaStream_t stream) {
   const bool out_tma_ok = !d->out_fp32 && !d->accumulate && splits == 1 && a.coll.mode != 2 &&
                           !(reinterpret_cast<uintptr_t>(d->out) & 15) && !(d->ldo & 7) && (d->epilogue != 100 && d->epilogue != 101) &&
                           (!d->aux_out || (!(reinterpret_cast<uintptr_t>(d->aux_out) & 15) && !(d->ld_aux_out & 7))) &&
-                          (!d->aux_in || a.vec_ok) && (!d->bias || a.vec_ok) && g_dbg_no_tma_store == 0;
+                          (!d->aux_in || a.vec_ok) && (!d->bias || a.vec_ok) && g_no_tma_store == 0;
   if (out_tma_ok) {
     bool okm = make_tmap_bf16_2d(&tout, d->out, d->N, d->M, d->ldo, 64, kBM);
     if (okm && d->aux_out) okm = make_tmap_bf16_2d(&taux, d->aux_out, d->N, d->M, d->ld_aux_out, 64, kBM);
