@@ -46,19 +46,19 @@ def Rsqrt(x):
 
 
 def Mean(x, dim: int, keep_dim: bool = False):
-    return x.mean(dim, keepdim=keep_dim)
+    return ops.mean_dim(x, dim, keep_dim)
 
 
 def Sum(x, dim: int, keep_dim: bool = False):
-    return x.sum(dim, keepdim=keep_dim)
+    return ops.sum_dim(x, dim, keep_dim)
 
 
 def Max(x, dim: int, keep_dim: bool = False):
-    return x.amax(dim, keepdim=keep_dim)
+    return ops.max_dim(x, dim, keep_dim)
 
 
 def Min(x, dim: int, keep_dim: bool = False):
-    return x.amin(dim, keepdim=keep_dim)
+    return ops.min_dim(x, dim, keep_dim)
 
 
 def Sigmoid(x):
@@ -70,9 +70,8 @@ def Softmax(x, dim: int = -1):
 
 
 def Slice(x, starts, ends, steps):
-    idx = tuple(slice(s, e, st) for s, e, st in zip(starts, ends, steps))
-    return x[idx].contiguous()
+    return ops.slice_nd(x, list(starts), list(ends), list(steps))
 
 
 def Stack(tensors, dim: int = 0):
-    return torch.stack(list(tensors), dim)
+    return ops.stack(list(tensors), dim)
