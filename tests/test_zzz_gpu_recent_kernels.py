@@ -237,3 +237,12 @@ def test_zero1_on_the_native_symmetric_heap():
            "127.0.0.1", "--master-port", str(29990 - os.getpid() % 90), os.path.join(HERE, "dist_zero_check.py")]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_cpp_api_program_passes_on_cuda(tmp_path):
+    """The stand-alone C++ test program (reference gtest cases + data layer + a short GPT-2 run) on cuda:0."""
+    from tinyinfinitrain_b200 import _build
+
+    built = _build.build_cpp()
+    r = subprocess.run([str(built["facade_api_test"]), "cuda", str(tmp_path)], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "all checks passed" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]

@@ -156,10 +156,59 @@ def build(verbose: bool = False, force: bool = False) -> None:
             p.unlink()
 
 
+def build_cpp(verbose: bool = False) -> dict:
+    """The C++ API as a stand-alone library plus its test program and the C++ training example (no Python involved at
+    run time): ``libtitb200_framework.so`` from ``csrc/core`` without the binding files, ``facade_api_test`` from
+    ``tests/cpp`` and ``train_gpt2`` from ``examples/cpp``.  Returns the paths."""
+    if not is_built():                        # the kernel library the framework links against; never rebuilt here when
+        build(verbose=verbose)                # present, because a running process may have it loaded
+    inc, lib = _torch_paths()
+    root = PKG.parent
+    srcs = [s for s in sorted((CSRC / "core").rglob("*.cc")) if not s.name.endswith("_binding.cc")]
+    cflags = ["-O2", "-std=c++17", "-fPIC", "-DNDEBUG", "-D_GLIBCXX_USE_CXX11_ABI=1", "-Wno-deprecated-declarations",
+              "-I", str(CSRC), "-I", str(CSRC / "kernels"), "-I", str(CUDA_HOME / "include")]
+    for i in inc:
+        cflags += ["-isystem", i]
+    out_dir = BUILD / "cpp"
+    out_dir.mkdir(parents=True, exist_ok=True)
+    stamp = _hdr_stamp([CSRC])
+    jobs, objs = [], []
+    for s in srcs:
+        tag = hashlib.sha1(str(s.relative_to(CSRC)).encode()).hexdigest()[:6]
+        o = out_dir / f"{s.stem}.{tag}.{_obj_key(s, cflags, stamp)}.o"
+        objs.append(o)
+        jobs.append(([CXX, *cflags, "-c", s, "-o", o], o))
+    changed = _compile_all(jobs, verbose)
+    libs = []
+    for l in lib:
+        libs += [f"-L{l}", f"-Wl,-rpath,{l}"]
+    libs += ["-lc10", "-ltorch_cpu", "-ltorch", f"-L{CUDA_HOME}/lib64", f"-Wl,-rpath,{CUDA_HOME}/lib64", "-lcudart",
+             "-lc10_cuda", "-ltorch_cuda"]
+    fw = PKG / "libtitb200_framework.so"
+    if changed or not fw.exists():
+        _run([CXX, "-shared", "-o", fw, *objs, f"-L{PKG}", "-ltitb200_kernels", "-Wl,-rpath,$ORIGIN", *libs], verbose)
+    live = {o.name for o in objs}
+    for p in out_dir.glob("*.o"):
+        if p.name not in live:
+            p.unlink()
+    exes = {}
+    for name, src in (("facade_api_test", root / "tests" / "cpp" / "facade_api_test.cc"),
+                      ("train_gpt2", root / "examples" / "cpp" / "train_gpt2.cc")):
+        exe = out_dir / name
+        if changed or not exe.exists() or exe.stat().st_mtime < src.stat().st_mtime:
+            _run([CXX, *cflags, src, "-o", exe, f"-L{PKG}", "-ltitb200_framework", "-ltitb200_kernels",
+                  f"-Wl,-rpath,{PKG}", "-Wl,--no-as-needed", *libs], verbose)
+        exes[name] = exe
+    return {"library": fw, **exes}
+
+
 def is_built() -> bool:
     return KERNEL_LIB.exists() and CORE_LIB.exists()
 
 
 if __name__ == "__main__":
     build(verbose="-v" in sys.argv, force="-f" in sys.argv)
+    if "--cpp" in sys.argv:
+        for k, v in build_cpp(verbose="-v" in sys.argv).items():
+            print(f"{k}: {v}")
     print("built:", KERNEL_LIB.name, CORE_LIB.name)
