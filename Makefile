@@ -8,6 +8,9 @@ clean:
 	rm -rf build/titb200
 	rm -f tinyinfinitrain_b200/_C.so tinyinfinitrain_b200/libtitb200_kernels.so
 
+cpp:
+	$(PYTHON) -m tinyinfinitrain_b200._build --cpp
+
 test-cpu: build
 	$(PYTHON) -m pytest tests -q -m "not gpu"
 
@@ -17,4 +20,4 @@ test-gpu: build
 bench: build
 	$(PYTHON) bench.py --gpus 1 --steps 20 --warmup 5
 
-.PHONY: build clean test-cpu test-gpu bench
+.PHONY: build cpp clean test-cpu test-gpu bench
