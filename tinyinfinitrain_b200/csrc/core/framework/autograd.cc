@@ -200,19 +200,28 @@ TensorList LayerNorm::Backward(const TensorList& g) {
   return {dx, dw, db};
 }
 TensorList RMSNorm::Forward(const TensorList& in) {
-  const at::Tensor xf = in[0]->data().to(at::kFloat);
-  at::Tensor rstd = (xf.pow(2).mean(-1, true) + eps_).rsqrt();
-  rstd_ = MakeTensor(rstd);
-  return {MakeTensor((xf * rstd * in[1]->data().to(at::kFloat)).to(in[0]->data().scalar_type()))};
+  auto [y, rstd] = K(in[0], "RMSNormForward").Call<std::pair<TP, TP>, const TP&, const TP&, float>(in[0], in[1], eps_);
+  rstd_ = rstd;
+  return {y};
 }
 void RMSNorm::SetupContext(const TensorList& in, const TensorList&) { saved_tensors_ = {in[0], in[1], rstd_}; }
 TensorList RMSNorm::Backward(const TensorList& g) {
-  const at::Tensor x = saved_tensors_[0]->data().to(at::kFloat), w = saved_tensors_[1]->data().to(at::kFloat);
-  const at::Tensor rstd = saved_tensors_[2]->data(), dy = g[0]->data().to(at::kFloat);
-  at::Tensor n = x * rstd, dn = dy * w;
-  at::Tensor dx = (dn - n * (dn * n).mean(-1, true)) * rstd;
-  at::Tensor dw = (dy * n).reshape({-1, x.size(-1)}).sum(0);
-  return {MakeTensor(dx.to(saved_tensors_[0]->data().scalar_type())), MakeTensor(dw.to(saved_tensors_[1]->data().scalar_type()))};
+  auto [dx, dw] = K(g[0], "RMSNormBackward").Call<std::pair<TP, TP>, const TP&, const TP&, const TP&, const TP&>(
+      saved_tensors_[0], saved_tensors_[1], saved_tensors_[2], g[0]);
+  return {dx, dw};
+}
+TensorList Rope::Forward(const TensorList& in) {
+  return {K(in[0], "RopeForward").Call<TP, const TP&, float, int64_t, bool>(in[0], theta_, pos_offset_, false)};
+}
+void Rope::SetupContext(const TensorList&, const TensorList&) {}
+TensorList Rope::Backward(const TensorList& g) {
+  // the rotation is orthogonal: its transpose is the rotation by the negative angle
+  return {K(g[0], "RopeForward").Call<TP, const TP&, float, int64_t, bool>(g[0], theta_, pos_offset_, true)};
+}
+TensorList SwiGLU::Forward(const TensorList& in) { return {K(in[0], "SwiGLUForward").Call<TP, const TP&>(in[0])}; }
+void SwiGLU::SetupContext(const TensorList& in, const TensorList&) { saved_tensors_ = {in[0]}; }
+TensorList SwiGLU::Backward(const TensorList& g) {
+  return {K(g[0], "SwiGLUBackward").Call<TP, const TP&, const TP&>(g[0], saved_tensors_[0])};
 }
 TensorList Softmax::Forward(const TensorList& in) {
   return {K(in[0], "SoftmaxForward").Call<TP, const TP&, int64_t>(in[0], dim_)};

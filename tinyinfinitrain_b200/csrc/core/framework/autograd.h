@@ -150,6 +150,21 @@ class RMSNorm : public Function {  // not in the reference
   float eps_;
   std::shared_ptr<Tensor> rstd_;
 };
+// Rotary position embedding on [B, T, H, hd]: element i is paired with i + hd/2, angle (t + pos_offset) * theta^(-2i/hd)
+// (not in the reference)
+class Rope : public Function {
+ public:
+  explicit Rope(float theta = 500000.f, int64_t pos_offset = 0) : theta_(theta), pos_offset_(pos_offset) {}
+  TITB_DECLARE_FUNCTION_BODY
+ private:
+  float theta_;
+  int64_t pos_offset_;
+};
+// silu(x[..., :F]) * x[..., F:] on a fused gate | up projection of width 2F (not in the reference); saves the input
+class SwiGLU : public Function {
+ public:
+  TITB_DECLARE_FUNCTION_BODY
+};
 class Softmax : public Function {
  public:
   explicit Softmax(int64_t dim = -1) : dim_(dim) {}

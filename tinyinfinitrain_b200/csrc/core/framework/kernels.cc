@@ -348,6 +348,90 @@ std::tuple<TP, TP, TP> LayerNormBackward(const TP& input, const TP& weight, cons
           W(g.sum(0).to(weight->data().scalar_type()))};
 }
 
+// ---- RMSNorm / RoPE / SwiGLU (LLaMA-3 building blocks; not in the reference) ---------------------------------------------
+std::pair<TP, TP> RMSNormForward(const TP& input, const TP& weight, float eps) {
+  const at::Tensor& x = input->data();
+  const int64_t C = x.size(-1), rows = x.numel() / C;
+  if (native(x) && x.is_contiguous() && weight->data().scalar_type() == x.scalar_type()) {
+    c10::cuda::CUDAGuard guard(x.device());
+    at::Tensor y = at::empty_like(x), rstd = at::empty({rows}, x.options().dtype(at::kFloat));
+    ok(titb_rmsnorm_fwd(x.data_ptr(), weight->data().data_ptr(), y.data_ptr(), rstd.data_ptr<float>(), rows, (int)C, eps,
+                        dt(x), stream()), "RMSNormForward");
+    return {W(y), W(rstd)};
+  }
+  at::Tensor xf = x.to(at::kFloat).reshape({rows, C});
+  at::Tensor rstd = (xf.pow(2).mean(1) + eps).rsqrt();
+  at::Tensor y = xf * rstd.unsqueeze(1) * weight->data().to(at::kFloat);
+  return {W(y.reshape(x.sizes()).to(x.scalar_type())), W(rstd)};
+}
+std::pair<TP, TP> RMSNormBackward(const TP& input, const TP& weight, const TP& rstd, const TP& grad_output) {
+  const at::Tensor& x = input->data();
+  const at::Tensor& g = grad_output->data();
+  const int64_t C = x.size(-1), rows = x.numel() / C;
+  if (native(x) && x.is_contiguous() && g.is_contiguous() && g.scalar_type() == x.scalar_type() &&
+      weight->data().scalar_type() == x.scalar_type()) {
+    c10::cuda::CUDAGuard guard(x.device());
+    auto fopt = x.options().dtype(at::kFloat);
+    at::Tensor dx = at::empty_like(x), dw = at::empty({C}, fopt);
+    at::Tensor scratch = at::empty({2, titb_layernorm_bwd_blocks(rows), C}, fopt);
+    ok(titb_rmsnorm_bwd(g.data_ptr(), x.data_ptr(), weight->data().data_ptr(), rstd->data().data_ptr<float>(), dx.data_ptr(),
+                        dw.data_ptr<float>(), scratch.data_ptr<float>(), rows, (int)C, dt(x), 0, stream()), "RMSNormBackward");
+    return {W(dx), W(dw.to(weight->data().scalar_type()))};
+  }
+  at::Tensor xf = x.to(at::kFloat).reshape({rows, C}), gf = g.to(at::kFloat).reshape({rows, C});
+  at::Tensor w = weight->data().to(at::kFloat), r = rstd->data().to(at::kFloat).unsqueeze(1);
+  at::Tensor n = xf * r, dn = gf * w;
+  at::Tensor dx = (dn - n * (dn * n).mean(1, true)) * r;
+  return {W(dx.reshape(x.sizes()).to(x.scalar_type())), W((gf * n).sum(0).to(weight->data().scalar_type()))};
+}
+TP RopeForward(const TP& input, float theta, int64_t pos_offset, bool inverse) {
+  const at::Tensor& x = input->data();
+  TORCH_CHECK(x.dim() == 4 && x.size(3) % 2 == 0, "Rope expects [B, T, H, hd] with an even head size");
+  const int64_t B = x.size(0), T = x.size(1), H = x.size(2), hd = x.size(3), half = hd / 2;
+  if (native(x)) {
+    c10::cuda::CUDAGuard guard(x.device());
+    at::Tensor xc = materialize(x), y = at::empty_like(xc);
+    ok(titb_rope(xc.data_ptr(), y.data_ptr(), (int)B, (int)T, (int)H, (int)hd, (int)pos_offset, theta, inverse, dt(xc),
+                 stream()), "Rope");
+    return W(y);
+  }
+  at::Tensor inv = at::pow(theta, -at::arange(0, half, at::kFloat) * 2.0 / static_cast<double>(hd));
+  at::Tensor ang = (at::arange(T, at::kFloat) + static_cast<double>(pos_offset)).unsqueeze(1) * inv.unsqueeze(0);   // [T, half]
+  at::Tensor cos = ang.cos().reshape({1, T, 1, half}), sin = ang.sin().reshape({1, T, 1, half});
+  if (inverse) sin = -sin;
+  at::Tensor a = x.narrow(3, 0, half).to(at::kFloat), b = x.narrow(3, half, half).to(at::kFloat);
+  return W(at::cat({a * cos - b * sin, b * cos + a * sin}, 3).to(x.scalar_type()));
+}
+TP SwiGLUForward(const TP& input) {
+  const at::Tensor& x = input->data();
+  const int64_t F = x.size(-1) / 2, rows = x.numel() / (2 * F);
+  auto sizes = x.sizes().vec();
+  sizes.back() = F;
+  if (native(x) && x.is_contiguous()) {
+    c10::cuda::CUDAGuard guard(x.device());
+    at::Tensor y = at::empty(sizes, x.options());
+    ok(titb_swiglu_fwd(x.data_ptr(), y.data_ptr(), rows, (int)F, dt(x), stream()), "SwiGLU");
+    return W(y);
+  }
+  at::Tensor gate = x.narrow(-1, 0, F).to(at::kFloat), up = x.narrow(-1, F, F).to(at::kFloat);
+  return W((at::silu(gate) * up).to(x.scalar_type()));
+}
+TP SwiGLUBackward(const TP& grad_output, const TP& input) {
+  const at::Tensor &g = grad_output->data(), &x = input->data();
+  const int64_t F = x.size(-1) / 2, rows = x.numel() / (2 * F);
+  if (native(x) && x.is_contiguous() && g.is_contiguous() && g.scalar_type() == x.scalar_type()) {
+    c10::cuda::CUDAGuard guard(x.device());
+    at::Tensor dx = at::empty_like(x);
+    ok(titb_swiglu_bwd(g.data_ptr(), x.data_ptr(), dx.data_ptr(), rows, (int)F, dt(x), stream()), "SwiGLUBackward");
+    return W(dx);
+  }
+  at::Tensor gate = x.narrow(-1, 0, F).to(at::kFloat), up = x.narrow(-1, F, F).to(at::kFloat), gf = g.to(at::kFloat);
+  at::Tensor sg = gate.sigmoid();
+  at::Tensor dgate = gf * up * (sg * (1 + gate * (1 - sg)));        // d silu(z) / dz = s (1 + z (1 - s))
+  at::Tensor dup = gf * gate * sg;
+  return W(at::cat({dgate, dup}, -1).to(x.scalar_type()));
+}
+
 // ---- softmax / cross entropy / embedding -------------------------------------------------------------------------------
 TP SoftmaxForward(const TP& input, int64_t dim) {
   const at::Tensor& x = input->data();
@@ -594,6 +678,7 @@ REG_BOTH(AddForward); REG_BOTH(AddBackward); REG_BOTH(SubForward); REG_BOTH(SubB
 REG_BOTH(MulForward); REG_BOTH(MulBackward); REG_BOTH(DivForward); REG_BOTH(DivBackward);
 REG_BOTH(MatmulForward); REG_BOTH(MatmulBackward); REG_BOTH(LinearForward); REG_BOTH(LinearBackward);
 REG_BOTH(OuterForward); REG_BOTH(OuterBackward); REG_BOTH(LayerNormForward); REG_BOTH(LayerNormBackward);
+REG_BOTH(RMSNormForward); REG_BOTH(RMSNormBackward); REG_BOTH(RopeForward); REG_BOTH(SwiGLUForward); REG_BOTH(SwiGLUBackward);
 REG_BOTH(SoftmaxForward); REG_BOTH(SoftmaxBackward); REG_BOTH(CrossEntropyForward); REG_BOTH(CrossEntropyBackward);
 REG_BOTH(EmbeddingForward); REG_BOTH(EmbeddingBackward);
 REG_BOTH(MeanForward); REG_BOTH(MeanBackward); REG_BOTH(SumForward); REG_BOTH(SumBackward);

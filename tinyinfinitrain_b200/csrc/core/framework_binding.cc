@@ -7,6 +7,7 @@
 #include "core/framework/autograd.h"
 #include "core/framework/dispatcher.h"
 #include "core/framework/gpt2.h"
+#include "core/framework/llama3.h"
 #include "core/framework/nn.h"
 #include "core/framework/tensor.h"
 
@@ -37,6 +38,8 @@ std::shared_ptr<fw::autograd::Function> make_function(const std::string& name, c
   if (name == "Rsqrt") return std::make_shared<Rsqrt>();
   if (name == "Sigmoid") return std::make_shared<Sigmoid>();
   if (name == "Gelu") return std::make_shared<Gelu>();
+  if (name == "SwiGLU") return std::make_shared<SwiGLU>();
+  if (name == "Rope") return std::make_shared<Rope>((float)f(0, 500000.0), (int64_t)f(1, 0));
   if (name == "Pow") return std::make_shared<Pow>((float)f(0, 2), f(1, 0) != 0);
   if (name == "EqualsScalar") return std::make_shared<EqualsScalar>((float)f(0, 0));
   if (name == "AddScalar") return std::make_shared<AddScalar>((float)f(0, 0));
@@ -189,6 +192,17 @@ void bind_framework(pybind11::module_& m) {
         return std::make_shared<fw::GPT2>(c);
       }))
       .def_static("FromLLMC", [](const std::string& p) { return std::shared_ptr<fw::GPT2>(fw::GPT2::FromLLMC(p)); });
+
+  py::class_<fw::LLaMA3, nn::Module, std::shared_ptr<fw::LLaMA3>>(m, "FwLLaMA3")
+      .def(py::init([](int64_t block, int64_t vocab, int64_t L, int64_t H, int64_t Hkv, int64_t C, int64_t F, double eps,
+                       double theta) {
+        fw::LLaMA3Config c;
+        c.block_size = block; c.vocab_size = vocab; c.n_layer = L; c.n_head = H; c.n_kv_head = Hkv; c.n_embd = C;
+        c.ffn_dim = F; c.norm_eps = (float)eps; c.rope_theta = (float)theta;
+        return std::make_shared<fw::LLaMA3>(c);
+      }), py::arg("block_size"), py::arg("vocab_size"), py::arg("n_layer"), py::arg("n_head"), py::arg("n_kv_head"),
+           py::arg("n_embd"), py::arg("ffn_dim"), py::arg("norm_eps") = 1e-5, py::arg("rope_theta") = 500000.0)
+      .def_static("FromLLMC", [](const std::string& p) { return std::shared_ptr<fw::LLaMA3>(fw::LLaMA3::FromLLMC(p)); });
 
   py::class_<fw::Optimizer, std::shared_ptr<fw::Optimizer>>(m, "FwOptimizer")
       .def("ZeroGrad", &fw::Optimizer::ZeroGrad).def("Step", &fw::Optimizer::Step);
