@@ -246,3 +246,27 @@ def test_cpp_api_program_passes_on_cuda(tmp_path):
     built = _build.build_cpp()
     r = subprocess.run([str(built["facade_api_test"]), "cuda", str(tmp_path)], capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "all checks passed" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def test_cpp_llama3_and_gpt2_on_cuda_match_the_cpu_facade():
+    """The C++ models moved to cuda:0 (kernel-backed RMSNorm / Rope / SwiGLU / Gelu / LayerNorm / softmax / SGEMM and the
+    gather kernel behind every transpose and slice) against the same models on the CPU."""
+    g = torch.Generator().manual_seed(2)
+    idx, tgt = torch.randint(0, 150, (2, 16), generator=g), torch.randint(0, 150, (2, 16), generator=g)
+    for make in (lambda: C.FwLLaMA3(32, 150, 2, 4, 2, 32, 48), lambda: C.FwGPT2(32, 150, 2, 4, 32)):
+        res = {}
+        for dev in ("cpu", "cuda:0"):
+            model = make()                       # seeded initialisation: identical weights in both runs
+            if not dev.startswith("cpu"):
+                model.To(dev)
+            put = (lambda t: C.FwTensor(t).To(dev)) if not dev.startswith("cpu") else C.FwTensor
+            logits = model.Forward([put(idx)])[0]
+            loss = C.FwCrossEntropyLoss().Forward([logits, put(tgt)])[0]
+            loss.Backward()
+            grads = {k: v.grad().torch().float().cpu() for k, v in model.StateDict().items() if v.grad() is not None}
+            res[dev] = (logits.torch().detach().float().cpu(), float(loss.torch().detach()), grads)
+        assert torch.allclose(res["cpu"][0], res["cuda:0"][0], atol=2e-3, rtol=1e-3)
+        assert abs(res["cpu"][1] - res["cuda:0"][1]) < 1e-3
+        for k, gcpu in res["cpu"][2].items():
+            assert torch.allclose(gcpu, res["cuda:0"][2][k], atol=2e-3, rtol=1e-2), k
+    _status_ok()
