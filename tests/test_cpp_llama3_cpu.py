@@ -70,3 +70,31 @@ def test_cpp_llama3_matches_python_model(tmp_path):
     for name in ("transformer.h.0.attn.c_attn.weight", "transformer.h.1.mlp.c_fc.weight", "transformer.ln_f.weight",
                  "transformer.wte.weight", "lm_head.weight"):
         assert torch.allclose(cpp.StateDict()[name].grad().torch(), py.StateDict()[name].grad, atol=1e-5), name
+
+
+def test_causal_attention_function_matches_reference_math():
+    torch.manual_seed(0)
+    B, T, Hq, Hkv, hd = 2, 9, 4, 2, 8
+    q0, k0, v0 = torch.randn(B, T, Hq, hd), torch.randn(B, T, Hkv, hd), torch.randn(B, T, Hkv, hd)
+    q, k, v = (C.FwTensor(t.clone(), True) for t in (q0, k0, v0))
+    o = C.fw_function("CausalAttention").Apply([q, k, v])[0]
+    qr, kr, vr = (t.clone().requires_grad_(True) for t in (q0, k0, v0))
+    ref = ops.attention_ref(qr, kr, vr)
+    g = torch.randn_like(ref)
+    o.Backward(C.FwTensor(g.clone()))
+    ref.backward(g)
+    assert torch.allclose(o.torch(), ref, atol=1e-6)
+    for a, b in ((q, qr), (k, kr), (v, vr)):
+        assert torch.allclose(a.grad().torch(), b.grad, atol=1e-5)
+
+
+def test_module_cast_to_bfloat16_keeps_ties_and_runs():
+    m = C.FwGPT2(16, 97, 2, 2, 32)
+    idx = torch.randint(0, 97, (2, 16), generator=torch.Generator().manual_seed(0))
+    ref = m.Forward([C.FwTensor(idx)])[0].torch()
+    m.ToDtype("bfloat16")
+    sd = m.StateDict()
+    assert all(t.Dtype() == "bfloat16" for t in sd.values())
+    assert sd["lm_head.weight"].torch().data_ptr() == sd["transformer.wte.weight"].torch().data_ptr()
+    out = m.Forward([C.FwTensor(idx)])[0].torch()
+    assert out.dtype == torch.bfloat16 and (out.float() - ref).abs().max() < 2e-2

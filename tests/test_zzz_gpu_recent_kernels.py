@@ -270,3 +270,25 @@ def test_cpp_llama3_and_gpt2_on_cuda_match_the_cpu_facade():
         for k, gcpu in res["cpu"][2].items():
             assert torch.allclose(gcpu, res["cuda:0"][2][k], atol=2e-3, rtol=1e-2), k
     _status_ok()
+
+
+def test_cpp_models_in_bf16_use_the_flash_attention_function():
+    """C++ GPT-2 (hd 64) and LLaMA-3 (hd 64, grouped-query) cast to bf16 on cuda:0: attention runs as the fused
+    CausalAttention Function (tcgen05 kernels); logits and loss stay close to the fp32 CPU model."""
+    g = torch.Generator().manual_seed(3)
+    idx, tgt = torch.randint(0, 300, (2, 128), generator=g), torch.randint(0, 300, (2, 128), generator=g)
+    for make in (lambda: C.FwGPT2(128, 300, 2, 2, 128), lambda: C.FwLLaMA3(128, 300, 2, 4, 2, 256, 512)):
+        ref_model = make()
+        ref = ref_model.Forward([C.FwTensor(idx)])[0].torch()
+        model = make()
+        model.To("cuda:0")
+        model.ToDtype("bfloat16")
+        logits = model.Forward([C.FwTensor(idx).To("cuda:0")])[0]
+        loss = C.FwCrossEntropyLoss().Forward([logits, C.FwTensor(tgt).To("cuda:0")])[0]
+        loss.Backward()
+        assert logits.torch().dtype == torch.bfloat16
+        assert (logits.torch().float().cpu() - ref).abs().max() < 0.1
+        grads = [v.grad().torch() for v in model.StateDict().values() if v.grad() is not None]
+        assert grads and all(torch.isfinite(x.float()).all() for x in grads)
+        assert any(float(x.float().abs().max()) > 0 for x in grads)
+    _status_ok()

@@ -218,6 +218,21 @@ TensorList Rope::Backward(const TensorList& g) {
   // the rotation is orthogonal: its transpose is the rotation by the negative angle
   return {K(g[0], "RopeForward").Call<TP, const TP&, float, int64_t, bool>(g[0], theta_, pos_offset_, true)};
 }
+TensorList CausalAttention::Forward(const TensorList& in) {
+  auto [o, lse] = K(in[0], "CausalAttentionForward").Call<std::pair<TP, TP>, const TP&, const TP&, const TP&, float>(
+      in[0], in[1], in[2], scale_);
+  out_ = o;
+  lse_ = lse;
+  return {o};
+}
+void CausalAttention::SetupContext(const TensorList& in, const TensorList&) { saved_tensors_ = {in[0], in[1], in[2], out_, lse_}; }
+TensorList CausalAttention::Backward(const TensorList& g) {
+  auto [dq, dk, dv] = K(g[0], "CausalAttentionBackward")
+                          .Call<TPTriple, const TP&, const TP&, const TP&, const TP&, const TP&, const TP&, float>(
+                              g[0], saved_tensors_[0], saved_tensors_[1], saved_tensors_[2], saved_tensors_[3],
+                              saved_tensors_[4], scale_);
+  return {dq, dk, dv};
+}
 TensorList SwiGLU::Forward(const TensorList& in) { return {K(in[0], "SwiGLUForward").Call<TP, const TP&>(in[0])}; }
 void SwiGLU::SetupContext(const TensorList& in, const TensorList&) { saved_tensors_ = {in[0]}; }
 TensorList SwiGLU::Backward(const TensorList& g) {

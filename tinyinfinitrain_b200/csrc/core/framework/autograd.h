@@ -165,6 +165,18 @@ class SwiGLU : public Function {
  public:
   TITB_DECLARE_FUNCTION_BODY
 };
+// Causal self-attention in one Function: inputs q [B, T, Hq, hd], k and v [B, T, Hkv, hd] (Hq % Hkv == 0), output
+// [B, T, Hq, hd].  bf16 CUDA tensors with hd 64 or 128 run the tcgen05 flash-attention kernels (the score matrix is
+// never materialised); everything else runs the same math through ATen.  The reference composes attention from
+// Matmul / MaskedFill / Softmax (example/gpt2/net.cc:91-108), which the facade models still do for fp32.
+class CausalAttention : public Function {
+ public:
+  explicit CausalAttention(float scale = 0.f) : scale_(scale) {}      // 0 = 1 / sqrt(hd)
+  TITB_DECLARE_FUNCTION_BODY
+ private:
+  float scale_;
+  std::shared_ptr<Tensor> out_, lse_;
+};
 class Softmax : public Function {
  public:
   explicit Softmax(int64_t dim = -1) : dim_(dim) {}

@@ -38,6 +38,12 @@ TensorList CausalSelfAttention::Forward(const TensorList& in) {
   const int64_t B = x->Dims()[0], T = x->Dims()[1], C = x->Dims()[2];
   const int64_t H = config_.n_head, hd = C / H;
   auto qkv = modules_[kCAttnLayerName]->Forward({x})[0]->Split(static_cast<int>(C), 2);
+  if (x->GetDevice().IsCUDA() && qkv[0]->Dtype() == DataType::kBFLOAT16 && (hd == 64 || hd == 128)) {
+    // bf16 on the GPU: one flash-attention kernel instead of the Matmul / MaskedFill / Softmax / Matmul chain
+    TP y = std::make_shared<autograd::CausalAttention>()->Apply(
+        {qkv[0]->View({B, T, H, hd}), qkv[1]->View({B, T, H, hd}), qkv[2]->View({B, T, H, hd})})[0];
+    return modules_[kCProjLayerName]->Forward({y->View({B, T, C})});
+  }
   auto heads = [&](const TP& t) { return t->View({B, T, H, hd})->Transpose(1, 2); };  // [B, H, T, hd]
   TP q = heads(qkv[0]), k = heads(qkv[1]), v = heads(qkv[2]);
   TP att = q->Matmul(k->Transpose(-2, -1)) * (1.0f / std::sqrt(static_cast<float>(hd)));

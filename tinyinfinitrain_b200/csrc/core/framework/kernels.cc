@@ -432,6 +432,82 @@ TP SwiGLUBackward(const TP& grad_output, const TP& input) {
   return W(at::cat({dgate, dup}, -1).to(x.scalar_type()));
 }
 
+// ---- fused causal attention -------------------------------------------------------------------------------------------------
+static bool attn_kernel_ok(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v) {
+  const int64_t hd = q.size(3);
+  return q.is_cuda() && q.scalar_type() == at::kBFloat16 && k.scalar_type() == at::kBFloat16 &&
+         v.scalar_type() == at::kBFloat16 && (hd == 64 || hd == 128) && q.size(2) % k.size(2) == 0;
+}
+// softmax(mask(q k^T scale)) per head as [B, Hq, T, T] fp32, plus the head-major fp32 operands
+static at::Tensor attn_probs(const at::Tensor& q, const at::Tensor& k, float scale, at::Tensor* qh, at::Tensor* kh) {
+  const int64_t T = q.size(1), group = q.size(2) / k.size(2);
+  *qh = q.to(at::kFloat).transpose(1, 2);                                            // [B, Hq, T, hd]
+  *kh = k.to(at::kFloat).transpose(1, 2).repeat_interleave(group, 1);
+  at::Tensor s = at::matmul(*qh, kh->transpose(-2, -1)) * scale;
+  at::Tensor mask = at::triu(at::ones({T, T}, s.options().dtype(at::kBool)), 1);
+  return at::softmax(s.masked_fill(mask, -INFINITY), -1);
+}
+std::pair<TP, TP> CausalAttentionForward(const TP& q_, const TP& k_, const TP& v_, float scale) {
+  const at::Tensor &q = q_->data(), &k = k_->data(), &v = v_->data();
+  TORCH_CHECK(q.dim() == 4 && k.dim() == 4 && v.sizes() == k.sizes() && q.size(3) == k.size(3), "CausalAttention: bad shapes");
+  const int64_t B = q.size(0), T = q.size(1), Hq = q.size(2), hd = q.size(3), Hkv = k.size(2);
+  if (scale == 0.f) scale = 1.f / std::sqrt(static_cast<float>(hd));
+  if (attn_kernel_ok(q, k, v)) {
+    c10::cuda::CUDAGuard guard(q.device());
+    at::Tensor qc = materialize(q), kc = materialize(k), vc = materialize(v);
+    at::Tensor o = at::empty({B, T, Hq, hd}, q.options()), lse = at::empty({B, Hq, T}, q.options().dtype(at::kFloat));
+    TitbAttnDesc d{};
+    d.q = qc.data_ptr(); d.k = kc.data_ptr(); d.v = vc.data_ptr(); d.o = o.data_ptr(); d.lse = lse.data_ptr<float>();
+    d.B = (int)B; d.T = (int)T; d.Hq = (int)Hq; d.Hkv = (int)Hkv; d.hd = (int)hd;
+    d.q_stride_t = Hq * hd; d.k_stride_t = Hkv * hd; d.v_stride_t = Hkv * hd; d.o_stride_t = Hq * hd;
+    d.scale = scale;
+    ok(titb_attn_fwd(&d, stream()), "CausalAttentionForward");
+    return {W(o), W(lse)};
+  }
+  at::Tensor qh, kh;
+  at::Tensor p = attn_probs(q, k, scale, &qh, &kh);
+  at::Tensor vh = v.to(at::kFloat).transpose(1, 2).repeat_interleave(Hq / Hkv, 1);
+  at::Tensor o = at::matmul(p, vh).transpose(1, 2).contiguous().to(q.scalar_type());
+  return {W(o), W(at::zeros({1}, o.options().dtype(at::kFloat)))};                   // no saved statistics on this path
+}
+std::tuple<TP, TP, TP> CausalAttentionBackward(const TP& go_, const TP& q_, const TP& k_, const TP& v_, const TP& o_,
+                                               const TP& lse_, float scale) {
+  const at::Tensor &go = go_->data(), &q = q_->data(), &k = k_->data(), &v = v_->data();
+  const int64_t B = q.size(0), T = q.size(1), Hq = q.size(2), hd = q.size(3), Hkv = k.size(2), group = Hq / Hkv;
+  if (scale == 0.f) scale = 1.f / std::sqrt(static_cast<float>(hd));
+  if (attn_kernel_ok(q, k, v) && go.scalar_type() == at::kBFloat16) {
+    c10::cuda::CUDAGuard guard(q.device());
+    at::Tensor qc = materialize(q), kc = materialize(k), vc = materialize(v), gc = materialize(go), oc = materialize(o_->data());
+    at::Tensor dq = at::empty_like(qc), dk = at::empty_like(kc), dv = at::empty_like(vc);
+    auto fopt = q.options().dtype(at::kFloat);
+    at::Tensor delta = at::empty({B, Hq, T}, fopt), acc = at::empty({B, T, Hq, hd}, fopt);
+    TitbAttnDesc d{};
+    d.q = qc.data_ptr(); d.k = kc.data_ptr(); d.v = vc.data_ptr(); d.o = oc.data_ptr(); d.lse = lse_->data().data_ptr<float>();
+    d.d_o = gc.data_ptr(); d.dq = dq.data_ptr(); d.dk = dk.data_ptr(); d.dv = dv.data_ptr();
+    d.delta = delta.data_ptr<float>(); d.dq_accum = acc.data_ptr<float>();
+    d.B = (int)B; d.T = (int)T; d.Hq = (int)Hq; d.Hkv = (int)Hkv; d.hd = (int)hd;
+    d.q_stride_t = d.o_stride_t = d.do_stride_t = d.dq_stride_t = Hq * hd;
+    d.k_stride_t = d.v_stride_t = d.dk_stride_t = d.dv_stride_t = Hkv * hd;
+    d.scale = scale;
+    ok(titb_attn_bwd(&d, stream()), "CausalAttentionBackward");
+    return {W(dq), W(dk), W(dv)};
+  }
+  // dV = P^T dO; dP = dO V^T; dS = P (dP - rowsum(dP P)); dQ = dS K scale; dK = dS^T Q scale; kv heads sum their group
+  at::Tensor qh, kh;
+  at::Tensor p = attn_probs(q, k, scale, &qh, &kh);
+  at::Tensor vh = v.to(at::kFloat).transpose(1, 2).repeat_interleave(group, 1);
+  at::Tensor gh = go.to(at::kFloat).transpose(1, 2);                                 // [B, Hq, T, hd]
+  at::Tensor dvh = at::matmul(p.transpose(-2, -1), gh);
+  at::Tensor dp = at::matmul(gh, vh.transpose(-2, -1));
+  at::Tensor ds = p * (dp - (dp * p).sum(-1, true));
+  at::Tensor dqh = at::matmul(ds, kh) * scale, dkh = at::matmul(ds.transpose(-2, -1), qh) * scale;
+  auto fold = [&](const at::Tensor& t) {                                             // [B, Hq, T, hd] -> [B, T, Hkv, hd]
+    return t.reshape({B, Hkv, group, T, hd}).sum(2).transpose(1, 2).contiguous();
+  };
+  return {W(dqh.transpose(1, 2).contiguous().to(q.scalar_type())), W(fold(dkh).to(k.scalar_type())),
+          W(fold(dvh).to(v.scalar_type()))};
+}
+
 // ---- softmax / cross entropy / embedding -------------------------------------------------------------------------------
 TP SoftmaxForward(const TP& input, int64_t dim) {
   const at::Tensor& x = input->data();
@@ -678,6 +754,7 @@ REG_BOTH(AddForward); REG_BOTH(AddBackward); REG_BOTH(SubForward); REG_BOTH(SubB
 REG_BOTH(MulForward); REG_BOTH(MulBackward); REG_BOTH(DivForward); REG_BOTH(DivBackward);
 REG_BOTH(MatmulForward); REG_BOTH(MatmulBackward); REG_BOTH(LinearForward); REG_BOTH(LinearBackward);
 REG_BOTH(OuterForward); REG_BOTH(OuterBackward); REG_BOTH(LayerNormForward); REG_BOTH(LayerNormBackward);
+REG_BOTH(CausalAttentionForward); REG_BOTH(CausalAttentionBackward);
 REG_BOTH(RMSNormForward); REG_BOTH(RMSNormBackward); REG_BOTH(RopeForward); REG_BOTH(SwiGLUForward); REG_BOTH(SwiGLUBackward);
 REG_BOTH(SoftmaxForward); REG_BOTH(SoftmaxBackward); REG_BOTH(CrossEntropyForward); REG_BOTH(CrossEntropyBackward);
 REG_BOTH(EmbeddingForward); REG_BOTH(EmbeddingBackward);

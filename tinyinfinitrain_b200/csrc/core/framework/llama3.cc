@@ -40,6 +40,11 @@ TensorList LLaMA3Attention::Forward(const TensorList& in) {
     return qkv->Slice(2, first_head * hd, (first_head + heads) * hd)->View({B, T, heads, hd});
   };
   auto rope = [&](const TP& t) { return std::make_shared<autograd::Rope>(config_.rope_theta, 0)->Apply({t})[0]; };
+  if (x->GetDevice().IsCUDA() && qkv->Dtype() == DataType::kBFLOAT16 && (hd == 64 || hd == 128)) {
+    // bf16 on the GPU: one flash-attention kernel; grouped-query heads are mapped inside it, nothing is repeated
+    TP y = std::make_shared<autograd::CausalAttention>()->Apply({rope(part(0, Hq)), rope(part(Hq, Hkv)), part(Hq + Hkv, Hkv)})[0];
+    return modules_[kCProjLayerName]->Forward({y->View({B, T, C})});
+  }
   TP q = rope(part(0, Hq))->Transpose(1, 2);                                              // [B, Hq, T, hd]
   TP k = rope(part(Hq, Hkv))->Transpose(1, 2);                                            // [B, Hkv, T, hd]
   TP v = part(Hq + Hkv, Hkv)->Transpose(1, 2);

@@ -80,6 +80,23 @@ void Module::To(Device device) {
   };
   rec(this);
 }
+void Module::To(DataType dtype) {
+  std::unordered_map<const Tensor*, TP> cast;
+  std::function<void(Module*)> rec = [&](Module* m) {
+    for (auto& [name, p] : m->parameters_) {
+      if (!p) continue;
+      auto it = cast.find(p.get());
+      if (it == cast.end()) {
+        TP q = std::make_shared<Tensor>(p->To(dtype));
+        if (p->requires_grad()) q->RequiresGrad();
+        it = cast.emplace(p.get(), q).first;
+      }
+      p = it->second;
+    }
+    for (auto& [name, c] : m->modules_) rec(c.get());
+  };
+  rec(this);
+}
 void Module::Apply(const std::function<void(Module*)>& fn) {
   for (const auto& name : module_order_) modules_.at(name)->Apply(fn);
   fn(this);

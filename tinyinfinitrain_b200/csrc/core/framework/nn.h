@@ -37,6 +37,9 @@ class Module : public std::enable_shared_from_this<Module> {
   std::unordered_map<std::string, std::shared_ptr<Tensor>> StateDict() const;
   virtual TensorList Forward(const TensorList& input_tensors);
   virtual void To(Device device);
+  // Casts every parameter (ties kept) to `dtype`, e.g. kBFLOAT16 for tensor-core training on the GPU (not in the
+  // reference, whose tensors are fp32 only).
+  virtual void To(DataType dtype);
   void Apply(const std::function<void(Module*)>& fn);  // post-order
 
   void AddModule(const std::string& name, std::shared_ptr<Module> m);

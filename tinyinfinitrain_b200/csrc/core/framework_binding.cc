@@ -39,6 +39,7 @@ std::shared_ptr<fw::autograd::Function> make_function(const std::string& name, c
   if (name == "Sigmoid") return std::make_shared<Sigmoid>();
   if (name == "Gelu") return std::make_shared<Gelu>();
   if (name == "SwiGLU") return std::make_shared<SwiGLU>();
+  if (name == "CausalAttention") return std::make_shared<CausalAttention>((float)f(0, 0.0));
   if (name == "Rope") return std::make_shared<Rope>((float)f(0, 500000.0), (int64_t)f(1, 0));
   if (name == "Pow") return std::make_shared<Pow>((float)f(0, 2), f(1, 0) != 0);
   if (name == "EqualsScalar") return std::make_shared<EqualsScalar>((float)f(0, 0));
@@ -170,7 +171,11 @@ void bind_framework(pybind11::module_& m) {
       .def("Forward", &nn::Module::Forward)
       .def("has_parameter", &nn::Module::has_parameter)
       .def("parameter", &nn::Module::parameter)
-      .def("To", [](nn::Module& mod, const std::string& d) { mod.To(dev_of(d)); });
+      .def("To", [](nn::Module& mod, const std::string& d) { mod.To(dev_of(d)); })
+      .def("ToDtype", [](nn::Module& mod, const std::string& dt) {
+        TORCH_CHECK(dt == "float32" || dt == "bfloat16", "ToDtype: float32 or bfloat16");
+        mod.To(dt == "bfloat16" ? fw::DataType::kBFLOAT16 : fw::DataType::kFLOAT32);
+      });
   py::class_<nn::Linear, nn::Module, std::shared_ptr<nn::Linear>>(m, "FwLinear")
       .def(py::init([](int64_t i, int64_t o, bool b) { return std::make_shared<nn::Linear>(i, o, b); }),
            py::arg("in_features"), py::arg("out_features"), py::arg("bias") = true);
