@@ -13,7 +13,7 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
-def run(comm, steps, dev, rank, use_graph=False, buckets=1):
+def run(comm, steps, dev, rank, use_graph=False, buckets=1, clip=0.0):
     import tinyinfinitrain_b200 as tit
     from tinyinfinitrain_b200.models import GPT2, GPT2Config
     from tinyinfinitrain_b200.utils import TrainStep
@@ -21,7 +21,7 @@ def run(comm, steps, dev, rank, use_graph=False, buckets=1):
     cfg = GPT2Config(block_size=128, vocab_size=1000, n_layer=2, n_head=4, n_embd=256)
     model = GPT2(cfg, device=dev, dtype=torch.bfloat16, seed=42)
     opt = tit.parallel.DistributedOptimizer(model.parameters(), lr=1e-3, betas=(0.9, 0.95), weight_decay=0.1, comm=comm,
-                                            num_buckets=buckets, overlap=buckets > 1)
+                                            num_buckets=buckets, overlap=buckets > 1, max_grad_norm=clip)
     step = TrainStep(model, opt, 4, 128, dev, use_graph=use_graph)
     g = torch.Generator().manual_seed(1234 + rank)
     idx = torch.randint(0, 1000, (4, 128), generator=g).pin_memory()
@@ -63,6 +63,18 @@ def main():
         ok = ok and s3 == 0 and s4 == 0 and eb < 2e-2 and ebg < 2e-2 and len(ob.buckets) > 1 and early >= 1
         print(f"rank {rank}: buckets={len(ob.buckets)} reduced-during-backward={early} fused-vs-bucketed={eb:.3e} "
               f"bucketed-graph={ebg:.3e} status={s3},{s4}", flush=True)
+    clip = float(os.environ.get("TITB_TEST_ZERO_CLIP", "0"))
+    if clip > 0:
+        # global-norm clipping: fused (NVLink norm pass + local scaling) against the unfused NCCL path, eager and captured
+        p_cn, _, s5, on = run("nccl", 6, dev, rank, clip=clip)
+        p_cf, _, s6, of = run("fused", 6, dev, rank, clip=clip)
+        p_cg, _, s7, _ = run("fused", 5, dev, rank, use_graph=True, clip=clip)
+        ec, ecg = (p_cn - p_cf).abs().max().item(), (p_cf - p_cg).abs().max().item()
+        nn_, nf = on.grad_norm(), of.grad_norm()
+        moved = (p_cf - p_fused).abs().max().item()          # clipping changed the trajectory
+        ok = ok and s5 == 0 and s6 == 0 and s7 == 0 and ec < 2e-2 and ecg < 2e-2 and abs(nn_ - nf) < 2e-2 * max(1.0, nn_) \
+            and moved > 0
+        print(f"rank {rank}: clip nccl-vs-fused={ec:.3e} fused-vs-graph={ecg:.3e} norms {nn_:.4f} / {nf:.4f}", flush=True)
     print(f"rank {rank}: nccl-vs-fused max|dp|={err:.3e} fused-vs-graph={errg:.3e} identical_across_ranks={same} "
           f"status={s0},{s1},{s2} multimem={'yes' if opt.gbuf.mc_ptr else 'no'} loss {l_fused[0]:.3f}->{l_fused[-1]:.3f} "
           f"ok={ok}", flush=True)

@@ -292,3 +292,29 @@ def test_cpp_models_in_bf16_use_the_flash_attention_function():
         assert grads and all(torch.isfinite(x.float()).all() for x in grads)
         assert any(float(x.float().abs().max()) > 0 for x in grads)
     _status_ok()
+
+
+def test_clip_grad_norm_kernels():
+    """sumsq -> coefficient -> in-place scaling, all on the device, against torch.nn.utils.clip_grad_norm_."""
+    torch.manual_seed(9)
+    for n, scale, max_norm in ((1_000_003, 1.0, 5.0), (4096, 1e-3, 1.0), (70_000_000, 0.5, 1.0)):
+        g = (torch.randn(n, device=DEV) * 0.01).contiguous()
+        ref = g.clone()
+        ref_norm = float(ref.double().norm()) * scale
+        coef = min(1.0, max_norm / (ref_norm + 1e-6))
+        out = torch.zeros(2, device=DEV)
+        C.clip_grad_norm_(g, max_norm, scale, out)
+        assert abs(float(out[0]) - ref_norm) < 1e-4 * max(1.0, ref_norm)
+        assert abs(float(out[1]) - coef) < 1e-5
+        assert torch.allclose(g, ref * coef, rtol=1e-5, atol=1e-9)
+    _status_ok()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_zero1_fused_gradient_clipping_matches_nccl():
+    n = min(torch.cuda.device_count(), 8)
+    env = dict(os.environ, TITB_TEST_ZERO_CLIP="0.5")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29850 + os.getpid() % 90), os.path.join(HERE, "dist_zero_check.py")]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]

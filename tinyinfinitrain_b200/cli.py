@@ -31,6 +31,7 @@ def build_parser(family: str) -> argparse.ArgumentParser:
     p.add_argument("--freq_generate_txt", type=int, default=0)
     p.add_argument("--learning_rate", type=float, default=1e-4)
     p.add_argument("--weight_decay", type=float, default=0.0)
+    p.add_argument("--max_grad_norm", type=float, default=0.0, help="clip the global gradient norm (0 = off)")
     p.add_argument("--warmup_steps", type=int, default=0, help="linear learning-rate warm-up steps")
     p.add_argument("--lr_decay_steps", type=int, default=0, help="cosine decay horizon in steps (0 = constant rate)")
     p.add_argument("--min_lr_ratio", type=float, default=0.1, help="final rate of the cosine decay / peak rate")
@@ -127,7 +128,8 @@ def train_main(family: str, argv=None) -> int:
         if args.optimizer == "sgd":
             opt = tit.optim.SGD(model.parameters(), args.learning_rate)
         else:
-            opt = tit.optim.MixedPrecisionAdam(model.parameters(), lr=args.learning_rate, weight_decay=args.weight_decay)
+            opt = tit.optim.MixedPrecisionAdam(model.parameters(), lr=args.learning_rate, weight_decay=args.weight_decay,
+                                               max_grad_norm=args.max_grad_norm)
         start = load_checkpoint(args.resume, model, opt) if args.resume else 0
         loader = _data(args, cfg, 0, 1, cuda)
         accum = max(1, args.total_batch_size // (B * T)) if args.total_batch_size else 1
@@ -182,7 +184,8 @@ def train_main(family: str, argv=None) -> int:
     if mesh.dp > 1 and args.zero_stage == 1:
         opt = DistributedOptimizer(params, lr=args.learning_rate, weight_decay=args.weight_decay, group=mesh.dp_group,
                                    comm=args.comm if cuda else "nccl", num_buckets=args.dp_buckets,
-                                   overlap=args.dp_buckets > 1)
+                                   overlap=args.dp_buckets > 1,
+                                   max_grad_norm=args.max_grad_norm if tp == 1 and pp == 1 else 0.0)
     else:
         opt = tit.optim.MixedPrecisionAdam(params, lr=args.learning_rate, weight_decay=args.weight_decay)
     loader = _data(args, cfg, mesh.dp_rank, mesh.dp, cuda)

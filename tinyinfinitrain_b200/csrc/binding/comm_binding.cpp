@@ -57,6 +57,48 @@ void allreduce_small(const std::vector<int64_t>& buf_ptrs, const Tensor& out, in
   check(titb_allreduce_small(b.data(), out.data_ptr<float>(), (int)out.numel(), (int)b.size(), (int)op,
                              at::cuda::getCurrentCUDAStream().stream()), "allreduce_small");
 }
+
+// ---- gradient-norm clipping ---------------------------------------------------------------------------------------
+// Clips a flat fp32 gradient buffer in place to `max_norm` (norm taken of pre_scale * grad); `out` is a device
+// tensor of two floats that receives {norm, coefficient}.  Everything stays on the device.
+void clip_grad_norm_(const Tensor& grad, double max_norm, double pre_scale, const Tensor& out) {
+  TORCH_CHECK(grad.is_cuda() && grad.scalar_type() == at::kFloat && grad.is_contiguous());
+  TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kFloat && out.numel() >= 2 && max_norm > 0);
+  c10::cuda::CUDAGuard guard(grad.device());
+  auto st = at::cuda::getCurrentCUDAStream().stream();
+  Tensor partials = at::empty({titb_clip_max_partials()}, grad.options());
+  int np = 0;
+  check(titb_sumsq_partials(grad.data_ptr<float>(), grad.numel(), partials.data_ptr<float>(), &np, st), "sumsq");
+  check(titb_clip_coef(partials.data_ptr<float>(), np, (float)pre_scale, (float)max_norm, out.data_ptr<float>(), st), "clip_coef");
+  check(titb_scale_by_dev(grad.data_ptr<float>(), grad.numel(), out.data_ptr<float>() + 1, st), "scale_by_dev");
+}
+// out[0] = squared norm of this rank's shard of the cross-rank gradient sum (no scaling applied).
+void rs_grad_sumsq(const std::vector<int64_t>& grad_ptrs, int64_t grad_mc, int64_t shard_off, int64_t shard_n, int64_t rank,
+                   const Tensor& out) {
+  TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kFloat && out.numel() >= 1);
+  c10::cuda::CUDAGuard guard(out.device());
+  auto st = at::cuda::getCurrentCUDAStream().stream();
+  auto g = to_u64(grad_ptrs);
+  Tensor partials = at::empty({titb_clip_max_partials()}, out.options());
+  int np = 0;
+  check(titb_rs_sumsq_partials(g.data(), reinterpret_cast<const void*>(grad_mc), shard_off, shard_n, (int)g.size(), (int)rank,
+                               partials.data_ptr<float>(), &np, st), "rs_sumsq");
+  check(titb_clip_coef(partials.data_ptr<float>(), np, 1.f, 0.f, out.data_ptr<float>(), st), "sum_partials");
+}
+// total: device tensor whose first n values are summed (e.g. the ranks' squared norms); out = {norm, coefficient}.
+void clip_coef_from_totals(const Tensor& totals, int64_t n, double pre_scale, double max_norm, const Tensor& out) {
+  TORCH_CHECK(totals.is_cuda() && totals.scalar_type() == at::kFloat && totals.numel() >= n && out.numel() >= 2 && max_norm > 0);
+  c10::cuda::CUDAGuard guard(out.device());
+  check(titb_clip_coef(totals.data_ptr<float>(), (int)n, (float)pre_scale, (float)max_norm, out.data_ptr<float>(),
+                       at::cuda::getCurrentCUDAStream().stream()), "clip_coef");
+}
+void scale_by_dev_(const Tensor& x, const Tensor& coef) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kFloat && x.is_contiguous() && coef.is_cuda() &&
+              coef.scalar_type() == at::kFloat && coef.numel() >= 1);
+  c10::cuda::CUDAGuard guard(x.device());
+  check(titb_scale_by_dev(x.data_ptr<float>(), x.numel(), coef.data_ptr<float>(), at::cuda::getCurrentCUDAStream().stream()),
+        "scale_by_dev");
+}
 }  // namespace
 
 void bind_comm(pybind11::module_& m) {
@@ -66,4 +108,8 @@ void bind_comm(pybind11::module_& m) {
         py::arg("lr"), py::arg("b1"), py::arg("b2"), py::arg("eps"), py::arg("wd"), py::arg("step"),
         py::arg("grad_scale"), py::arg("dev_state") = py::none(), py::arg("max_blocks") = 0);
   m.def("allreduce_small", &allreduce_small);
+  m.def("clip_grad_norm_", &clip_grad_norm_);
+  m.def("rs_grad_sumsq", &rs_grad_sumsq);
+  m.def("clip_coef_from_totals", &clip_coef_from_totals);
+  m.def("scale_by_dev_", &scale_by_dev_);
 }

@@ -249,6 +249,23 @@ struct TitbAttnDesc {
 TITB_API int titb_attn_fwd(const TitbAttnDesc* d, cudaStream_t stream);
 TITB_API int titb_attn_bwd(const TitbAttnDesc* d, cudaStream_t stream);
 
+// ---- gradient-norm clipping (device resident: graph-capturable) -------------------------------------------------
+// Stage 1: per-block partial sums of squares of a flat fp32 buffer (16-byte aligned).  `partials` must hold
+// titb_clip_max_partials() floats; *n_partials receives how many were written.
+TITB_API int titb_clip_max_partials(void);
+TITB_API int titb_sumsq_partials(const float* x, long long n, float* partials, int* n_partials, cudaStream_t stream);
+// Same for this rank's shard [shard_off, shard_off + shard_n) of the SUM over ranks of the peer-mapped gradient
+// buffers (multimem.ld_reduce through NVSwitch when grad_mc is given, plain peer loads otherwise).
+TITB_API int titb_rs_sumsq_partials(const unsigned long long* grad_ptrs, const void* grad_mc, long long shard_off,
+                                    long long shard_n, int world, int rank, float* partials, int* n_partials,
+                                    cudaStream_t stream);
+// Stage 2 (one block, fixed order).  max_norm > 0: out[0] = sqrt(sum) * pre_scale, out[1] = min(1, max_norm / (out[0] + 1e-6)).
+// max_norm <= 0: out[0] = sum (to be combined with other ranks' sums first).
+TITB_API int titb_clip_coef(const float* partials, int n_partials, float pre_scale, float max_norm, float* out,
+                            cudaStream_t stream);
+// x *= coef[0] with the coefficient read from device memory; returns without touching memory when it is exactly 1.
+TITB_API int titb_scale_by_dev(float* x, long long n, const float* coef, cudaStream_t stream);
+
 // ---- NVLink communication (peer-mapped symmetric memory) -------------------------------------------
 // Pointer tables are host arrays of device addresses, one per rank, valid on the calling GPU.
 // Cross-GPU barrier on signal pads: pad of rank r = uint32[8 channels][16]; `epoch` is a device

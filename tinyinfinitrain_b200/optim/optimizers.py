@@ -179,10 +179,14 @@ class MixedPrecisionAdam:
     """
 
     def __init__(self, params, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.0,
-                 grad_scale: float = 1.0):
+                 grad_scale: float = 1.0, max_grad_norm: float = 0.0):
         self.flat = params if isinstance(params, FlatParams) else FlatParams(params)
         f = self.flat
         self.lr, self.betas, self.eps, self.weight_decay, self.grad_scale = lr, betas, eps, weight_decay, grad_scale
+        # > 0: the global L2 norm of (grad_scale * gradient) is clipped to this value before the update; the norm and
+        # the coefficient live in device memory (``clip_state``: {norm, coefficient}), so a captured step stays correct
+        self.max_grad_norm = max_grad_norm
+        self.clip_state = torch.tensor([0.0, 1.0], device=f.device, dtype=torch.float32)
         self.t = 0
         self.mixed = f.dtype != torch.float32
         self.master = f.param.float().clone() if self.mixed else f.param
@@ -214,10 +218,17 @@ class MixedPrecisionAdam:
         self.t += 1
         b1, b2 = self.betas
         if f.device.type == "cuda":
+            if self.max_grad_norm > 0:
+                C.clip_grad_norm_(f.grad, self.max_grad_norm, self.grad_scale, self.clip_state)
             C.adam_tick(self.dev_state, b1, b2)
             C.adam_flat(self.master, f.param if self.mixed else None, f.grad, self.m, self.v, self.lr, b1, b2,
                         self.eps, self.weight_decay, self.t, self.grad_scale, self.dev_state)
             return
+        if self.max_grad_norm > 0:
+            norm = f.grad.norm() * self.grad_scale
+            coef = torch.clamp(self.max_grad_norm / (norm + 1e-6), max=1.0)
+            self.clip_state[0], self.clip_state[1] = norm, coef
+            f.grad.mul_(coef)
         g = f.grad * self.grad_scale
         self.m.mul_(b1).add_(g, alpha=1 - b1)
         self.v.mul_(b2).addcmul_(g, g, value=1 - b2)
@@ -227,6 +238,10 @@ class MixedPrecisionAdam:
             f.param.copy_(self.master.to(f.dtype))
 
     Step = step
+
+    def grad_norm(self) -> float:
+        """Norm of the last clipped step's gradient (before clipping); reads device memory, so it synchronises."""
+        return float(self.clip_state[0])
 
     def state_dict(self):
         return {"t": self.t, "master": self.master, "m": self.m, "v": self.v}

@@ -30,7 +30,7 @@ from ..optim.optimizers import FlatParams
 class DistributedOptimizer:
     def __init__(self, params, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.0,
                  group: Optional[dist.ProcessGroup] = None, comm: str = "fused", average: bool = True,
-                 num_buckets: int = 1, overlap: bool = False):
+                 num_buckets: int = 1, overlap: bool = False, max_grad_norm: float = 0.0):
         plist = [p for p in params]
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
@@ -41,6 +41,12 @@ class DistributedOptimizer:
         self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
         self.t = 0
         self.grad_scale = (1.0 / self.world) if average else 1.0
+        # > 0: clip the global L2 norm of the (averaged) gradient.  The norm needs the reduced gradient before the update
+        # uses it, so the fused path reads its shard of the peers' gradients once more for the norm and every rank scales
+        # its local buffer by the agreed coefficient before the fused reduce-scatter + Adam kernel runs.
+        self.max_grad_norm = max_grad_norm
+        if max_grad_norm > 0 and overlap:
+            raise ValueError("gradient clipping needs the whole gradient before any bucket is updated: use overlap=False")
         align = 8 * self.world * 16
         # size the flat space first, then allocate (symmetric) buffers and bind the parameters to them
         total = self._flat_size(plist, align)
@@ -79,6 +85,13 @@ class DistributedOptimizer:
         self.v = torch.zeros(self.shard_n, device=dev, dtype=torch.float32)
         self.dev_state = torch.tensor([0.0, 0.0, 0.0, lr], device=dev, dtype=torch.float32) if self.is_cuda else None
         self._gshard = torch.empty(self.shard_n, device=dev, dtype=torch.float32) if self.comm != "fused" else None
+        self.clip_state = torch.tensor([0.0, 1.0], device=dev, dtype=torch.float32)     # {norm, coefficient}
+        self._norm_buf = None
+        if self.comm == "fused" and max_grad_norm > 0:
+            from .symm import SymmetricBuffer
+
+            self._norm_buf = SymmetricBuffer(64, torch.float32, dev, self.group)   # slot 0: this rank's squared shard norm
+            self._norm_all = torch.zeros(1, device=dev, dtype=torch.float32)
         if self.is_cuda:
             torch.cuda.synchronize(dev)
         dist.barrier(group=self.group)
@@ -204,6 +217,8 @@ class DistributedOptimizer:
             if not hasattr(self, "_ticked"):
                 self._reset_pending()
             main = torch.cuda.current_stream(f.device)
+            if self.max_grad_norm > 0:
+                self._clip_fused()
             for b in self.buckets:
                 if not b["launched"]:
                     # same stream as the early buckets: the barrier channel is used by one stream at a time
@@ -219,6 +234,8 @@ class DistributedOptimizer:
             return
         dist.reduce_scatter_tensor(self._gshard, f.grad, op=dist.ReduceOp.SUM, group=self.group) \
             if self.is_cuda else self._cpu_reduce_scatter()
+        if self.max_grad_norm > 0:
+            self._clip_shard()
         sl = slice(self.shard_off, self.shard_off + self.shard_n)
         if self.is_cuda:
             C.adam_tick(self.dev_state, b1, b2)
@@ -238,6 +255,39 @@ class DistributedOptimizer:
             f.param.copy_(torch.cat(shards))
 
     Step = step
+
+    def _clip_fused(self) -> None:
+        """Global-norm clipping on the fused path: barrier (all gradients written) -> squared norm of this rank's shard
+        of the summed gradient (NVLink read) -> exchange of the ranks' partial results through symmetric memory ->
+        coefficient -> every rank scales its own gradient buffer.  The regular bucket launch that follows starts
+        with its own barrier, which also orders the scaling before the peers' reads."""
+        from .._lib import C
+
+        self.barrier()
+        tot = 0
+        for i, b in enumerate(self.buckets):
+            C.rs_grad_sumsq(self.gbuf.ptrs, self.gbuf.mc_ptr, b["start"] + self.rank * b["shard"], b["shard"], self.rank,
+                            self._norm_buf.tensor[i:i + 1])
+            tot += 1
+        self.barrier()
+        # sum over ranks and buckets: tot values per rank, gathered slot by slot
+        sums = torch.empty(tot, device=self.flat.device, dtype=torch.float32)
+        C.allreduce_small(self._norm_buf.ptrs, sums, 0)
+        C.clip_coef_from_totals(sums, tot, self.grad_scale, self.max_grad_norm, self.clip_state)
+        C.scale_by_dev_(self.gbuf.tensor, self.clip_state[1:2])
+
+    def _clip_shard(self) -> None:
+        """Unfused path: squared norm of the reduced shard, summed over ranks, then the shard is scaled."""
+        sq = (self._gshard.float() ** 2).sum().reshape(1)
+        dist.all_reduce(sq, group=self.group)
+        norm = sq.sqrt() * self.grad_scale
+        coef = torch.clamp(self.max_grad_norm / (norm + 1e-6), max=1.0)
+        self.clip_state[0:1].copy_(norm)
+        self.clip_state[1:2].copy_(coef)
+        self._gshard.mul_(coef)
+
+    def grad_norm(self) -> float:
+        return float(self.clip_state[0])
 
     def _cpu_reduce_scatter(self) -> None:
         # gloo has no reduce_scatter: all-reduce then slice (CPU logic tests only)
