@@ -37,17 +37,18 @@ def test_mixed_precision_adam_clips_like_torch():
         assert torch.allclose(a, b, atol=1e-5)
 
 
-def _worker(rank, world, port, q):
+def _worker(rank, world, port, q, kind):
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        from tinyinfinitrain_b200.parallel import DistributedOptimizer
+        from tinyinfinitrain_b200.parallel import AllReduceOptimizer, DistributedOptimizer
 
         torch.manual_seed(0)
         lin, ref = torch.nn.Linear(37, 19), torch.nn.Linear(37, 19)
         ref.load_state_dict(lin.state_dict())
-        opt = DistributedOptimizer(lin.parameters(), lr=1e-2, betas=(0.9, 0.95), weight_decay=0.1, max_grad_norm=0.3)
+        cls = DistributedOptimizer if kind == "zero1" else AllReduceOptimizer
+        opt = cls(lin.parameters(), lr=1e-2, betas=(0.9, 0.95), weight_decay=0.1, max_grad_norm=0.3)
         ropt = torch.optim.AdamW(ref.parameters(), lr=1e-2, betas=(0.9, 0.95), weight_decay=0.1, eps=1e-8)
         ok = True
         for step in range(3):
@@ -69,11 +70,15 @@ def _worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
-def test_zero1_clips_the_global_norm_over_two_ranks():
+import pytest  # noqa: E402
+
+
+@pytest.mark.parametrize("kind", ["zero1", "allreduce"])
+def test_data_parallel_optimizers_clip_the_global_norm_over_two_ranks(kind):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29100 + os.getpid() % 300
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    port = 29100 + os.getpid() % 300 + (7 if kind == "zero1" else 0)
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, kind)) for r in range(2)]
     for p in procs:
         p.start()
     res = sorted(q.get(timeout=120) for _ in procs)

@@ -186,6 +186,11 @@ def train_main(family: str, argv=None) -> int:
                                    comm=args.comm if cuda else "nccl", num_buckets=args.dp_buckets,
                                    overlap=args.dp_buckets > 1,
                                    max_grad_norm=args.max_grad_norm if tp == 1 and pp == 1 else 0.0)
+    elif mesh.dp > 1:
+        from .parallel import AllReduceOptimizer        # --zero_stage 0: all-reduce + full Adam on every rank
+
+        opt = AllReduceOptimizer(params, lr=args.learning_rate, weight_decay=args.weight_decay, group=mesh.dp_group,
+                                 max_grad_norm=args.max_grad_norm if tp == 1 and pp == 1 else 0.0)
     else:
         opt = tit.optim.MixedPrecisionAdam(params, lr=args.learning_rate, weight_decay=args.weight_decay)
     loader = _data(args, cfg, mesh.dp_rank, mesh.dp, cuda)

@@ -6,4 +6,4 @@ from .tp import (  # noqa: F401
     ColumnParallelLinear, RowParallelLinear, TPComm, VocabParallelEmbedding, sync_sequence_parallel_grads,
     vocab_parallel_lm_head_loss,
 )
-from .zero import DistributedOptimizer  # noqa: F401
+from .zero import AllReduceOptimizer, DistributedOptimizer  # noqa: F401

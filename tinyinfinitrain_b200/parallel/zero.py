@@ -311,3 +311,53 @@ class DistributedOptimizer:
             self.dev_state[0] = float(self.t)
             self.dev_state[1] = 1.0 - b1 ** self.t if self.t else 0.0
             self.dev_state[2] = 1.0 - b2 ** self.t if self.t else 0.0
+
+
+class AllReduceOptimizer:
+    """Plain data parallelism (``--zero_stage 0``): the flat fp32 gradient buffer is all-reduced over the group
+    (one NCCL / gloo collective on the whole buffer) and every rank runs the full Adam update on identical averaged
+    gradients.  It keeps full optimizer state on every rank and exists as the unsharded baseline next to
+    :class:`DistributedOptimizer`, whose fused kernel is the product."""
+
+    def __init__(self, params, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.0,
+                 group: Optional[dist.ProcessGroup] = None, max_grad_norm: float = 0.0):
+        from ..optim.optimizers import MixedPrecisionAdam
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.inner = MixedPrecisionAdam(params, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
+                                        grad_scale=1.0 / self.world, max_grad_norm=max_grad_norm)
+        self.flat = self.inner.flat
+        src = dist.get_global_rank(self.group, 0) if self.group is not dist.group.WORLD else 0
+        dist.broadcast(self.flat.param, src=src, group=self.group)       # all replicas start from rank 0's weights
+        if self.inner.mixed:
+            self.inner.master.copy_(self.flat.param.float())
+
+    @property
+    def params(self):
+        return self.inner.params
+
+    def set_lr(self, lr: float) -> None:
+        self.inner.set_lr(lr)
+
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        self.inner.zero_grad()
+
+    ZeroGrad = zero_grad
+
+    @torch.no_grad()
+    def step(self) -> None:
+        self.flat.finish_unwritten()
+        dist.all_reduce(self.flat.grad, group=self.group)                 # sum; the Adam kernel applies 1 / world
+        self.inner.step()
+
+    Step = step
+
+    def grad_norm(self) -> float:
+        return self.inner.grad_norm()
+
+    def state_dict(self):
+        return self.inner.state_dict()
+
+    def load_state_dict(self, sd) -> None:
+        self.inner.load_state_dict(sd)
