@@ -42,3 +42,24 @@ def test_four_ranks_layouts(layout):
            "127.0.0.1", "--master-port", str(29250 + os.getpid() % 200), "examples/gpt2/main.py"] + COMMON + layout
     out = _run(cmd)
     assert _sane(_losses(out), 50257), out[-1500:]
+
+
+def _step_losses(out: str):
+    return {int(m.group(1)): float(m.group(2)) for m in re.finditer(r"^step (\d+)/\d+ \| loss ([0-9.]+)", out, flags=re.M)}
+
+
+@pytest.mark.parametrize("ranks,layout", [(1, []), (2, []), (2, ["--zero_stage", "0"]), (4, ["--tensor_parallel", "2"])])
+def test_resume_continues_exactly_where_the_first_run_stopped(tmp_path, ranks, layout):
+    """3 steps + save, then resume to 5 == 5 uninterrupted steps (same losses at steps 4 and 5), for one process,
+    ZeRO-1 over two ranks, plain all-reduce data parallelism, and tensor x data parallel."""
+    base = [sys.executable] if ranks == 1 else \
+        [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(ranks), "--master-addr",
+         "127.0.0.1", "--master-port", str(29450 + os.getpid() % 200)]
+    common = ["examples/gpt2/main.py", "--device", "cpu", "--synthetic", "--n_layer", "1", "--batch_size", "2",
+              "--sequence_length", "16", "--dtype", "float32", "--learning_rate", "1e-3"] + layout
+    ck = str(tmp_path / "ck")
+    full = _step_losses(_run(base + common + ["--num_iteration", "5"]))
+    _run(base + common + ["--num_iteration", "3", "--save", ck])
+    resumed = _step_losses(_run(base + common + ["--num_iteration", "5", "--resume", ck]))
+    assert sorted(resumed) == [4, 5] and sorted(full) == [1, 2, 3, 4, 5]
+    assert abs(resumed[4] - full[4]) < 1e-5 and abs(resumed[5] - full[5]) < 1e-5, (full, resumed)

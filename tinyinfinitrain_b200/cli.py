@@ -135,7 +135,7 @@ def train_main(family: str, argv=None) -> int:
         accum = max(1, args.total_batch_size // (B * T)) if args.total_batch_size else 1
         meter = ThroughputMeter(B * T * accum, model.flops_per_token(T), 1398.5 if cuda else 0.0)
         tok = tit.data.Tokenizer(args.tokenizer_bin) if args.tokenizer_bin else None
-        it = 0
+        it = start * accum                       # a resumed run continues with the batches the first run had not seen
         for step in range(start, args.num_iteration):
             lr = apply_lr(opt, step)
             with CudaTimer() as tm:
@@ -193,6 +193,9 @@ def train_main(family: str, argv=None) -> int:
                                  max_grad_norm=args.max_grad_norm if tp == 1 and pp == 1 else 0.0)
     else:
         opt = tit.optim.MixedPrecisionAdam(params, lr=args.learning_rate, weight_decay=args.weight_decay)
+    # every rank keeps its own optimizer shard (fp32 master weights, moments, step); on resume the data-parallel
+    # group rebuilds the parameters from the master shards
+    start = load_checkpoint(args.resume, model, opt, rank=rank) if args.resume else 0
     loader = _data(args, cfg, mesh.dp_rank, mesh.dp, cuda)
     nm = max(1, args.num_microbatches)
     assert (B * T) % tp == 0
@@ -207,8 +210,8 @@ def train_main(family: str, argv=None) -> int:
     stage = PipelineStage(stage_fn, mesh.pp_rank, pp, None if mesh.is_first_stage else mesh.prev_stage_rank(),
                           None if mesh.is_last_stage else mesh.next_stage_rank(), (B * T // tp, cfg.n_embd), dtype, dev)
     meter = ThroughputMeter(B * T * nm * mesh.dp, 0.0, 0.0)
-    it = 0
-    for step in range(args.num_iteration):
+    it = start * nm
+    for step in range(start, args.num_iteration):
         lr = apply_lr(opt, step)
         # device-timed (CUDA events on the launching stream; wall clock only on the CPU path), max over ranks
         with CudaTimer() as tm:
@@ -232,6 +235,10 @@ def train_main(family: str, argv=None) -> int:
             print(f"step {step + 1}/{args.num_iteration} | loss {lossv:.6f} | lr {lr:.2e} | "
                   f"{ms.item():.2f} ms | {rep['tokens_per_s']:.0f} tok/s | tp{tp} pp{pp} dp{mesh.dp}{mem}", flush=True)
         log.log(step=step + 1, loss=lossv, lr=lr, **rep)
+    if args.save:
+        save_checkpoint(args.save, model, opt, args.num_iteration, rank=rank, world=world,
+                        extra={"tp": tp, "pp": pp, "dp": mesh.dp})
+        dist.barrier()
     if cuda:
         status = tit._lib.C.status_read(True)
         if status:

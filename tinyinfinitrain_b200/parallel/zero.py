@@ -311,7 +311,23 @@ class DistributedOptimizer:
             self.dev_state[0] = float(self.t)
             self.dev_state[1] = 1.0 - b1 ** self.t if self.t else 0.0
             self.dev_state[2] = 1.0 - b2 ** self.t if self.t else 0.0
+        self._gather_params_from_master()
 
+    def _gather_params_from_master(self) -> None:
+        """Rebuilds the full parameter buffer of every rank from the ranks' master-weight shards (after a resume: a
+        rank only restored its own shard).  One all-gather per bucket on the process group; not on the step path."""
+        f = self.flat
+        lo = 0
+        for b in (self.buckets if self.comm == "fused" else [{"start": 0, "shard": self.shard_n}]):
+            n = b["shard"]
+            mine = self.master[lo:lo + n].to(f.dtype).contiguous()
+            parts = [torch.empty_like(mine) for _ in range(self.world)]
+            dist.all_gather(parts, mine, group=self.group)
+            f.param[b["start"]:b["start"] + n * self.world].copy_(torch.cat(parts))
+            lo += n
+        if self.is_cuda:
+            torch.cuda.synchronize(f.device)
+        dist.barrier(group=self.group)
 
 class AllReduceOptimizer:
     """Plain data parallelism (``--zero_stage 0``): the flat fp32 gradient buffer is all-reduced over the group

@@ -10,7 +10,10 @@ has no save, no optimizer state and no step counter.  Here a checkpoint is a dir
 * ``meta.json``      -- step, world layout, model name.
 
 Resuming restores master weights, moments and the step counter exactly, so the next step after a
-resume is bit-identical to the step an uninterrupted run would have taken (on one GPU).
+resume equals the step an uninterrupted run would have taken.  In a multi-rank job every rank writes
+and reads its own ``optim_rankN.pt`` (N = global rank: its tensor / pipeline slice of the model and its
+ZeRO shard of that slice); the ZeRO optimizer then rebuilds the full parameter buffers of its
+data-parallel group from the master-weight shards.
 """
 from __future__ import annotations
 
