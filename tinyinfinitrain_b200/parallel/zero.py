@@ -298,10 +298,13 @@ class DistributedOptimizer:
     # ---- sharded checkpoint state ------------------------------------------------------------
     def state_dict(self):
         return {"t": self.t, "rank": self.rank, "world": self.world, "shard_off": self.shard_off,
+                "layout": [(b["start"], b["shard"]) for b in self.buckets] if self.comm == "fused" else [(0, self.shard_n)],
                 "master": self.master.cpu(), "m": self.m.cpu(), "v": self.v.cpu()}
 
     def load_state_dict(self, sd) -> None:
         assert sd["world"] == self.world and sd["rank"] == self.rank, "optimizer shard belongs to another layout"
+        mine = [(b["start"], b["shard"]) for b in self.buckets] if self.comm == "fused" else [(0, self.shard_n)]
+        assert [tuple(x) for x in sd.get("layout", mine)] == mine, "checkpoint was written with another bucket layout"
         self.t = int(sd["t"])
         self.master.copy_(sd["master"])
         self.m.copy_(sd["m"])
