@@ -63,3 +63,19 @@ def test_resume_continues_exactly_where_the_first_run_stopped(tmp_path, ranks, l
     resumed = _step_losses(_run(base + common + ["--num_iteration", "5", "--resume", ck]))
     assert sorted(resumed) == [4, 5] and sorted(full) == [1, 2, 3, 4, 5]
     assert abs(resumed[4] - full[4]) < 1e-5 and abs(resumed[5] - full[5]) < 1e-5, (full, resumed)
+
+
+def test_restart_after_failure_recipe(tmp_path):
+    """Periodic checkpoints + `--resume auto`: a run that stops after step 3 of 5 (here: it was only asked for 3) is
+    continued by repeating the command line, and ends where an uninterrupted run ends."""
+    ck = str(tmp_path / "ck")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", str(29050 + os.getpid() % 40), "examples/gpt2/main.py", "--device", "cpu",
+           "--synthetic", "--n_layer", "1", "--batch_size", "2", "--sequence_length", "16", "--dtype", "float32",
+           "--learning_rate", "1e-3", "--save", ck, "--save_every", "1", "--resume", "auto"]
+    first = _step_losses(_run(cmd + ["--num_iteration", "3"]))            # nothing to resume from yet
+    assert sorted(first) == [1, 2, 3] and os.path.exists(os.path.join(ck, "optim_rank1.pt"))
+    second = _step_losses(_run(cmd + ["--num_iteration", "5"]))           # same command: picks the checkpoint up
+    assert sorted(second) == [4, 5]
+    full = _step_losses(_run(cmd[:-4] + ["--num_iteration", "5"]))        # no --save / --resume: uninterrupted
+    assert abs(second[5] - full[5]) < 1e-5

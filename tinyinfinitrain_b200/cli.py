@@ -48,8 +48,10 @@ def build_parser(family: str) -> argparse.ArgumentParser:
     p.add_argument("--seed", type=int, default=42)
     p.add_argument("--synthetic", action="store_true")
     p.add_argument("--n_layer", type=int, default=0, help="override the preset depth (smoke tests)")
-    p.add_argument("--save", default="", help="checkpoint directory to write at the end")
-    p.add_argument("--resume", default="", help="checkpoint directory to resume from")
+    p.add_argument("--save", default="", help="checkpoint directory to write at the end (and every --save_every steps)")
+    p.add_argument("--save_every", type=int, default=0, help="also checkpoint every N optimizer steps (0 = only at the end)")
+    p.add_argument("--resume", default="", help="checkpoint directory to resume from; 'auto' = the --save directory if it "
+                                                "holds a checkpoint (restart-after-failure recipe: same command line again)")
     p.add_argument("--log_jsonl", default="")
     p.add_argument("--cuda_graph", action="store_true", help="capture the single-GPU training step in a CUDA graph")
     return p
@@ -103,6 +105,8 @@ def train_main(family: str, argv=None) -> int:
     tp, pp = args.tensor_parallel, args.pipeline_parallel
     log = JsonlLogger(args.log_jsonl if rank == 0 else None)
     B, T = args.batch_size, args.sequence_length
+    if args.resume == "auto":
+        args.resume = args.save if args.save and os.path.exists(os.path.join(args.save, "meta.json")) else ""
 
     def lr_at(step: int) -> float:
         from .optim.schedule import warmup_cosine
@@ -158,6 +162,8 @@ def train_main(family: str, argv=None) -> int:
             log.log(step=step + 1, loss=lossf, lr=lr, **rep)
             if tok is not None and args.freq_generate_txt and (step + 1) % args.freq_generate_txt == 0:
                 tok.GenerateText(model, B, T, args.text_length, dev, stream=sys.stdout)
+            if args.save and args.save_every and (step + 1) % args.save_every == 0 and step + 1 < args.num_iteration:
+                save_checkpoint(args.save, model, opt, step + 1)
         if args.save:
             save_checkpoint(args.save, model, opt, args.num_iteration)
         log.close()
@@ -235,6 +241,9 @@ def train_main(family: str, argv=None) -> int:
             print(f"step {step + 1}/{args.num_iteration} | loss {lossv:.6f} | lr {lr:.2e} | "
                   f"{ms.item():.2f} ms | {rep['tokens_per_s']:.0f} tok/s | tp{tp} pp{pp} dp{mesh.dp}{mem}", flush=True)
         log.log(step=step + 1, loss=lossv, lr=lr, **rep)
+        if args.save and args.save_every and (step + 1) % args.save_every == 0 and step + 1 < args.num_iteration:
+            save_checkpoint(args.save, model, opt, step + 1, rank=rank, world=world, extra={"tp": tp, "pp": pp, "dp": mesh.dp})
+            dist.barrier()
     if args.save:
         save_checkpoint(args.save, model, opt, args.num_iteration, rank=rank, world=world,
                         extra={"tp": tp, "pp": pp, "dp": mesh.dp})
