@@ -27,16 +27,28 @@ import torch
 def save_checkpoint(path: str, model, optimizer, step: int, rank: int = 0, world: int = 1, extra: Optional[dict] = None,
                     bf16_weights: bool = False) -> None:
     os.makedirs(path, exist_ok=True)
+
+    def publish(name, write):
+        # written under a temporary name and renamed: a crash in the middle of a save leaves the previous file intact
+        tmp = os.path.join(path, name + ".tmp")
+        write(tmp)
+        os.replace(tmp, os.path.join(path, name))
+
     if rank == 0 and hasattr(model, "SaveLLMC"):
-        model.SaveLLMC(os.path.join(path, "model.bin"), bf16=bf16_weights)
+        publish("model.bin", lambda p: model.SaveLLMC(p, bf16=bf16_weights))
     sd = optimizer.state_dict()
-    torch.save({k: (v.detach().cpu() if torch.is_tensor(v) else v) for k, v in sd.items()},
-               os.path.join(path, f"optim_rank{rank}.pt"))
+    sd["step"] = int(step)
+    publish(f"optim_rank{rank}.pt",
+            lambda p: torch.save({k: (v.detach().cpu() if torch.is_tensor(v) else v) for k, v in sd.items()}, p))
     if rank == 0:
         meta = {"step": int(step), "world": int(world), "model": type(model).__name__}
         meta.update(extra or {})
-        with open(os.path.join(path, "meta.json"), "w") as f:
-            json.dump(meta, f)
+
+        def write_meta(p):
+            with open(p, "w") as f:
+                json.dump(meta, f)
+
+        publish("meta.json", write_meta)
 
 
 def load_checkpoint(path: str, model, optimizer, rank: int = 0) -> int:
@@ -44,5 +56,9 @@ def load_checkpoint(path: str, model, optimizer, rank: int = 0) -> int:
     with open(os.path.join(path, "meta.json")) as f:
         meta = json.load(f)
     sd = torch.load(os.path.join(path, f"optim_rank{rank}.pt"), map_location="cpu")
+    if "step" in sd and int(sd["step"]) != int(meta["step"]):
+        raise RuntimeError(f"{path}: optimizer shard of rank {rank} is from step {sd['step']}, meta.json says {meta['step']} "
+                           "(a save was interrupted between ranks)")
+    sd.pop("step", None)
     optimizer.load_state_dict(sd)
     return int(meta["step"])
