@@ -318,3 +318,30 @@ def test_zero1_fused_gradient_clipping_matches_nccl():
            "127.0.0.1", "--master-port", str(29850 + os.getpid() % 90), os.path.join(HERE, "dist_zero_check.py")]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, BF])
+def test_deterministic_embedding_gradient(dtype):
+    """Sorted segment reduction of the token-embedding gradient: equals index_add in float64, is bit-identical across
+    runs, handles heavy repetition, a vocabulary shard, and leaves the position gradient to the regular kernel."""
+    torch.manual_seed(12)
+    B, T, Cdim, V = 4, 256, 96, 500
+    idx = torch.randint(0, V, (B, T), device=DEV)
+    idx[0, :200] = 7                                           # one token repeated 200 times
+    dout = torch.randn(B, T, Cdim, device=DEV).to(dtype)
+    ref = torch.zeros(V, Cdim, device=DEV, dtype=torch.float64)
+    ref.index_add_(0, idx.reshape(-1), dout.reshape(-1, Cdim).double())
+    runs = []
+    for _ in range(3):
+        dw = torch.zeros(V, Cdim, device=DEV)
+        dp = torch.zeros(T, Cdim, device=DEV)
+        C.embedding_bwd(idx, dout, dw, dp, 0, V, True)
+        runs.append(dw.clone())
+        assert torch.allclose(dp.double(), dout.double().sum(0), atol=1e-3)
+    assert torch.equal(runs[0], runs[1]) and torch.equal(runs[1], runs[2])
+    assert torch.allclose(runs[0].double(), ref, atol=1e-2 if dtype == BF else 1e-4, rtol=1e-3)
+    # accumulation into an existing buffer, and a vocabulary shard [100, 300)
+    dw = torch.ones(200, Cdim, device=DEV)
+    C.embedding_bwd(idx, dout, dw, None, 100, 300, True)
+    assert torch.allclose(dw.double(), 1.0 + ref[100:300], atol=1e-2 if dtype == BF else 1e-4, rtol=1e-3)
+    _status_ok()

@@ -307,14 +307,27 @@ Tensor embedding_fwd(const Tensor& idx, const Tensor& wte, const optional<Tensor
   return out;
 }
 void embedding_bwd(const Tensor& idx, const Tensor& dout, const optional<Tensor>& dwte, const optional<Tensor>& dwpe,
-                   int64_t vocab_lo, int64_t vocab_hi) {
+                   int64_t vocab_lo, int64_t vocab_hi, bool deterministic) {
   check_cuda(idx, "idx"); check_cuda(dout, "dout");
   c10::cuda::CUDAGuard guard(dout.device());
   const int64_t C = dout.size(-1), BT = idx.numel(), T = idx.size(-1);
   float* pw = dwte.has_value() && dwte->defined() ? dwte->data_ptr<float>() : nullptr;
   float* pp = dwpe.has_value() && dwpe->defined() ? dwpe->data_ptr<float>() : nullptr;
+  if (deterministic && pw != nullptr && BT <= titb_embedding_sorted_max_tokens()) {
+    // sorted segment reduce for the token rows (no atomics); the position rows are a fixed-order sum already
+    int64_t npad = 2;
+    while (npad < BT) npad <<= 1;
+    Tensor keys = at::empty({npad}, idx.options().dtype(at::kLong));
+    CHECK_RC(titb_embedding_bwd_wte_sorted((const long long*)idx.data_ptr<int64_t>(), dout.data_ptr(), pw, BT, (int)C,
+                                           (int)vocab_lo, (int)std::min<int64_t>(vocab_hi, INT32_MAX), dt_code(dout),
+                                           reinterpret_cast<unsigned long long*>(keys.data_ptr<int64_t>()), cur_stream()),
+             "embedding_bwd_wte_sorted", 2);
+    pw = nullptr;
+    if (pp == nullptr) return;
+  }
   CHECK_RC(titb_embedding_bwd((const long long*)idx.data_ptr<int64_t>(), dout.data_ptr(), pw, pp, BT, (int)T, (int)C,
-                              (int)vocab_lo, (int)vocab_hi, dt_code(dout), cur_stream()), "embedding_bwd");
+                              (int)vocab_lo, (int)std::min<int64_t>(vocab_hi, INT32_MAX), dt_code(dout), cur_stream()),
+           "embedding_bwd");
 }
 
 // ------------------------------------------------------- softmax / cross entropy
@@ -671,7 +684,8 @@ PYBIND11_MODULE(_C, m) {
   m.def("embedding_fwd", &embedding_fwd, py::arg("idx"), py::arg("wte"), py::arg("wpe") = py::none(),
         py::arg("pos_offset") = 0);
   m.def("embedding_bwd", &embedding_bwd, py::arg("idx"), py::arg("dout"), py::arg("dwte") = py::none(),
-        py::arg("dwpe") = py::none(), py::arg("vocab_lo") = 0, py::arg("vocab_hi") = (int64_t)1 << 40);
+        py::arg("dwpe") = py::none(), py::arg("vocab_lo") = 0, py::arg("vocab_hi") = (int64_t)1 << 40,
+        py::arg("deterministic") = false);
   m.def("softmax_fwd", &softmax_fwd);
   m.def("softmax_bwd", &softmax_bwd);
   m.def("xent_fused", &xent_fused, py::arg("logits"), py::arg("targets"), py::arg("V"), py::arg("grad_scale"),

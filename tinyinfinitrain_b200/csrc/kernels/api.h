@@ -136,6 +136,14 @@ TITB_API int titb_embedding_fwd(const long long* idx, const void* wte, const voi
 TITB_API int titb_embedding_bwd(const long long* idx, const void* dout, float* dwte, float* dwpe, long long BT,
                                 int T, int C, int vocab_lo, int vocab_hi, int dtype, cudaStream_t stream);
 
+// Deterministic variant of the token part (dwte only): the keys (row, position) of one step are sorted in the shared
+// memory of one block and every run of equal rows is summed in position order, no atomics.  BT must not exceed
+// titb_embedding_sorted_max_tokens(); scratch_keys: BT rounded up to a power of two, 64-bit words.
+TITB_API int titb_embedding_sorted_max_tokens(void);
+TITB_API int titb_embedding_bwd_wte_sorted(const long long* idx, const void* dout, float* dwte, long long BT, int C,
+                                           int vocab_lo, int vocab_hi, int dtype, unsigned long long* scratch_keys,
+                                           cudaStream_t stream);
+
 // ---- softmax / cross entropy -------------------------------------------------------------
 TITB_API int titb_softmax_fwd(const void* x, void* y, long long outer, int axis, long long inner, int dtype,
                               cudaStream_t stream);

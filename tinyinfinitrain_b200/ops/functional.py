@@ -28,6 +28,9 @@ import torch.nn.functional as F
 from .._lib import C
 
 EPI_NONE, EPI_BIAS, EPI_BIAS_GELU, EPI_DGELU, EPI_BIAS_RESIDUAL = 0, 1, 2, 3, 4
+# TITB200_DETERMINISTIC=1: the token-embedding gradient is built by a sorted segment reduction instead of fp32 atomics
+# (the one reduction of the training step whose summation order otherwise depends on timing)
+DETERMINISTIC_EMBEDDING_GRAD = os.environ.get("TITB200_DETERMINISTIC", "0") == "1"
 
 _bf16 = torch.bfloat16
 
@@ -440,7 +443,7 @@ class _EmbeddingFn(torch.autograd.Function):
                 if not pacc:
                     gp_buf.zero_()
         C.embedding_bwd(idx, dout, gw_buf.view(wte.shape), gp_buf.view(wpe.shape) if gp_buf is not None else None,
-                        lo, hi)
+                        lo, hi, DETERMINISTIC_EMBEDDING_GRAD)
         if wmg is None:
             gw = gw_buf.to(wte.dtype)
         else:
