@@ -67,6 +67,7 @@ def main():
     ap.add_argument("--tile_n", type=int, default=0)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no_flush", action="store_true")
+    ap.add_argument("--cached", action="store_true", help="xent: keep each row in shared memory between the two passes")
     a = ap.parse_args()
     dev = "cuda"
     hbm, tflops, src = peaks()
@@ -153,7 +154,7 @@ def main():
         logits = torch.randn(a.m, a.n, device=dev).to(bf)
         tgt = torch.randint(0, a.n - 47, (a.m,), device=dev)
         bytes_ = 2.0 * logits.numel() * 2
-        fn = lambda: C.xent_fused(logits, tgt, a.n - 47, 1.0 / a.m, True, 1.0 / a.m)
+        fn = lambda: C.xent_fused(logits, tgt, a.n - 47, 1.0 / a.m, True, 1.0 / a.m, a.cached)
     else:
         n = a.m * a.n
         w, g = torch.randn(n, device=dev), torch.randn(n, device=dev)
