@@ -53,7 +53,9 @@ def main():
 
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel", choices=["gemm", "gemm_nt", "gemm_wgrad", "attn_fwd", "attn_bwd", "layernorm_fwd", "layernorm_bwd",
-                                       "xent", "adam", "gelu_gemm", "ag_gemm", "gemm_rs", "rs_adam"])
+                                       "xent", "adam", "gelu_gemm", "ag_gemm", "gemm_rs", "rs_adam", "clip", "embedding_bwd",
+                                       "reduce", "transpose_view", "colsum"])
+    ap.add_argument("--deterministic", action="store_true", help="embedding_bwd: sorted segment reduction instead of atomics")
     ap.add_argument("--world", type=int, default=4)
     ap.add_argument("--helpers", type=int, default=0)
     ap.add_argument("--m", type=int, default=8192)
@@ -150,6 +152,32 @@ def main():
         bytes_ = S * (4.0 * W + 3 * 4 * 2 + 2.0 * W)
         gp, pp = [t.data_ptr() for t in grads], [t.data_ptr() for t in params]
         fn = lambda: C.rs_adam_ag(gp, pp, 0, 0, master, m, v, 0, 0, 1e-3, 0.9, 0.999, 1e-8, 0.0, 1, 1.0 / W)
+    elif a.kernel == "clip":
+        n = a.m * a.n
+        g = torch.randn(n, device=dev) * 0.01
+        out2 = torch.zeros(2, device=dev)
+        bytes_ = n * 4.0 * 3            # norm pass reads once; the scaling pass reads and writes (max_norm tiny: always clips)
+        fn = lambda: C.clip_grad_norm_(g, 1e-6, 1.0, out2)
+    elif a.kernel == "embedding_bwd":
+        idx = torch.randint(0, a.n, (a.b, a.t), device=dev)
+        dout = torch.randn(a.b, a.t, a.k, device=dev).to(bf)
+        dw = torch.zeros(a.n, a.k, device=dev)
+        bytes_ = a.b * a.t * a.k * (2.0 + 8.0)   # gradient rows read, fp32 table rows read-modify-written
+        fn = lambda: C.embedding_bwd(idx, dout, dw, None, 0, a.n, a.deterministic)
+    elif a.kernel == "reduce":
+        x = torch.randn(a.m, a.k, device=dev).to(bf)
+        bytes_ = x.numel() * 2.0
+        fn = lambda: C.reduce_dim(x, 0, 1, False)          # row sums
+    elif a.kernel == "transpose_view":
+        x = torch.randn(a.b, a.t, a.h, a.hd, device=dev).to(bf)
+        v = x.transpose(1, 2)                              # [B, H, T, hd] view materialised by the gather kernel
+        bytes_ = x.numel() * 4.0
+        fn = lambda: C.gather_view(x, list(v.shape), list(v.stride()), 0)
+    elif a.kernel == "colsum":
+        x = torch.randn(a.m, a.n, device=dev).to(bf)
+        outc = torch.zeros(a.n, device=dev)
+        bytes_ = x.numel() * 2.0
+        fn = lambda: C.colsum(x, outc, False)
     elif a.kernel == "xent":
         logits = torch.randn(a.m, a.n, device=dev).to(bf)
         tgt = torch.randint(0, a.n - 47, (a.m,), device=dev)
