@@ -85,3 +85,60 @@ def test_data_parallel_optimizers_clip_the_global_norm_over_two_ranks(kind):
     for p in procs:
         p.join(timeout=30)
     assert res == [(0, True), (1, True)], res
+
+
+def _mp_worker(rank, world, port, q):
+    """4 ranks = tensor parallel 2 x data parallel 2.  `w` is sharded over the tensor ranks, `r` is replicated there."""
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from tinyinfinitrain_b200.parallel import AllReduceOptimizer, DistributedOptimizer, init_mesh
+
+        mesh = init_mesh(tp=2, pp=1)                     # rank = dp_rank * 2 + tp_rank
+        t, d = mesh.tp_rank, mesh.dp_rank
+
+        def grads(step):
+            gw = torch.full((300,), 0.01 * (1 + t) * (1 + 2 * d) * (step + 1))      # differs per tensor and data rank
+            gr = torch.full((40,), 0.02 * (1 + d) * (step + 1))                      # same on both tensor ranks
+            return gw, gr
+
+        def expected_norm(step):
+            tot = 0.0
+            for tt in range(2):
+                w_avg = sum(0.01 * (1 + tt) * (1 + 2 * dd) * (step + 1) for dd in range(2)) / 2
+                tot += 300 * w_avg ** 2
+            r_avg = sum(0.02 * (1 + dd) * (step + 1) for dd in range(2)) / 2
+            return (tot + 40 * r_avg ** 2) ** 0.5
+
+        ok = True
+        for cls in (DistributedOptimizer, AllReduceOptimizer):
+            torch.manual_seed(0)
+            w, r = torch.nn.Parameter(torch.randn(300)), torch.nn.Parameter(torch.randn(40))
+            r._sp_grad_sync = True
+            opt = cls([w, r], lr=1e-2, group=mesh.dp_group, max_grad_norm=0.05, mp_group=mesh.mp_group, tp_world=2)
+            assert opt.flat.params[0] is r and opt.flat.n_replicated == 128        # replicated parameters come first
+            for step in range(2):
+                opt.zero_grad()
+                w.grad, r.grad = grads(step)
+                before = w.detach().clone()
+                opt.step()
+                n = expected_norm(step)
+                ok &= abs(opt.grad_norm() - n) < 1e-5 * max(1.0, n)
+                ok &= bool((w.detach() - before).abs().max() > 0)
+        q.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_global_norm_counts_tensor_parallel_replicas_once():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29180 + os.getpid() % 100
+    procs = [ctx.Process(target=_mp_worker, args=(r, 4, port, q)) for r in range(4)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=180) for _ in procs)
+    for p in procs:
+        p.join(timeout=30)
+    assert res == [(r, True) for r in range(4)], res

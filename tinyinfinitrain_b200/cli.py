@@ -190,15 +190,16 @@ def train_main(family: str, argv=None) -> int:
     if mesh.dp > 1 and args.zero_stage == 1:
         opt = DistributedOptimizer(params, lr=args.learning_rate, weight_decay=args.weight_decay, group=mesh.dp_group,
                                    comm=args.comm if cuda else "nccl", num_buckets=args.dp_buckets,
-                                   overlap=args.dp_buckets > 1,
-                                   max_grad_norm=args.max_grad_norm if tp == 1 and pp == 1 else 0.0)
+                                   overlap=args.dp_buckets > 1, max_grad_norm=args.max_grad_norm,
+                                   mp_group=mesh.mp_group, tp_world=tp)
     elif mesh.dp > 1:
         from .parallel import AllReduceOptimizer        # --zero_stage 0: all-reduce + full Adam on every rank
 
         opt = AllReduceOptimizer(params, lr=args.learning_rate, weight_decay=args.weight_decay, group=mesh.dp_group,
-                                 max_grad_norm=args.max_grad_norm if tp == 1 and pp == 1 else 0.0)
+                                 max_grad_norm=args.max_grad_norm, mp_group=mesh.mp_group, tp_world=tp)
     else:
-        opt = tit.optim.MixedPrecisionAdam(params, lr=args.learning_rate, weight_decay=args.weight_decay)
+        opt = tit.optim.MixedPrecisionAdam(params, lr=args.learning_rate, weight_decay=args.weight_decay,
+                                           max_grad_norm=args.max_grad_norm, mp_group=mesh.mp_group, tp_world=tp)
     # every rank keeps its own optimizer shard (fp32 master weights, moments, step); on resume the data-parallel
     # group rebuilds the parameters from the master shards
     start = load_checkpoint(args.resume, model, opt, rank=rank) if args.resume else 0

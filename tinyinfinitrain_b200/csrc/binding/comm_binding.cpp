@@ -92,6 +92,18 @@ void clip_coef_from_totals(const Tensor& totals, int64_t n, double pre_scale, do
   check(titb_clip_coef(totals.data_ptr<float>(), (int)n, (float)pre_scale, (float)max_norm, out.data_ptr<float>(),
                        at::cuda::getCurrentCUDAStream().stream()), "clip_coef");
 }
+// out[0] = sum of squares of a flat fp32 tensor (fixed summation order).
+void sumsq_(const Tensor& x, const Tensor& out) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kFloat && x.is_contiguous() && out.is_cuda() &&
+              out.scalar_type() == at::kFloat && out.numel() >= 1);
+  c10::cuda::CUDAGuard guard(x.device());
+  auto st = at::cuda::getCurrentCUDAStream().stream();
+  if (x.numel() == 0) { out.narrow(0, 0, 1).zero_(); return; }
+  Tensor partials = at::empty({titb_clip_max_partials()}, x.options());
+  int np = 0;
+  check(titb_sumsq_partials(x.data_ptr<float>(), x.numel(), partials.data_ptr<float>(), &np, st), "sumsq");
+  check(titb_clip_coef(partials.data_ptr<float>(), np, 1.f, 0.f, out.data_ptr<float>(), st), "sum_partials");
+}
 void scale_by_dev_(const Tensor& x, const Tensor& coef) {
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kFloat && x.is_contiguous() && coef.is_cuda() &&
               coef.scalar_type() == at::kFloat && coef.numel() >= 1);
@@ -112,4 +124,5 @@ void bind_comm(pybind11::module_& m) {
   m.def("rs_grad_sumsq", &rs_grad_sumsq);
   m.def("clip_coef_from_totals", &clip_coef_from_totals);
   m.def("scale_by_dev_", &scale_by_dev_);
+  m.def("sumsq_", &sumsq_);
 }

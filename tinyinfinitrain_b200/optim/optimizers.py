@@ -127,6 +127,12 @@ class FlatParams:
                 seen.add(id(p))
                 plist.append(p)
         assert plist, "no trainable parameters"
+        # parameters that are replicated over a tensor-parallel group (flagged ``_sp_grad_sync`` by parallel.tp) go first,
+        # in their original order: their gradients then form ONE contiguous region [0, n_replicated) that the group
+        # all-reduces in a single collective and that the gradient norm counts once.  Models without such
+        # parameters keep their order.
+        plist = [p for p in plist if getattr(p, "_sp_grad_sync", False)] + \
+                [p for p in plist if not getattr(p, "_sp_grad_sync", False)]
         self.params = plist
         dev, dt = plist[0].device, plist[0].dtype
         assert all(p.device == dev and p.dtype == dt for p in plist), "parameters must share device and dtype"
@@ -135,6 +141,10 @@ class FlatParams:
             self.offsets.append(off)
             off += _round_up(p.numel(), 128)
         self.total = _round_up(off, align_total)
+        self.n_replicated = 0
+        for p, o in zip(plist, self.offsets):
+            if getattr(p, "_sp_grad_sync", False):
+                self.n_replicated = o + _round_up(p.numel(), 128)
         self.device, self.dtype = dev, dt
         self.param = param_buffer if param_buffer is not None else torch.zeros(self.total, device=dev, dtype=dt)
         self.grad = grad_buffer if grad_buffer is not None else torch.zeros(self.total, device=dev,
@@ -147,6 +157,7 @@ class FlatParams:
                 p.data = self.param[o:o + n].view(p.shape)
                 p.main_grad = self.grad[o:o + n].view(p.shape)
                 p._fresh_grad = True
+                p._flat = self
                 p.grad = None
 
     def mark_fresh(self) -> None:
@@ -170,6 +181,26 @@ class FlatParams:
                 p._fresh_grad = False
 
 
+def clip_coefficient(total_sq, replicated_sq, tp_world: int, mp_group, grad_scale: float, max_norm: float, clip_state):
+    """Global gradient norm and clip coefficient from this rank's sums of squares.
+
+    ``total_sq``: all local parameters; ``replicated_sq``: the part that belongs to parameters replicated over the
+    tensor-parallel group (counted once in the global norm, so each of the ``tp_world`` copies contributes 1 / tp_world).
+    ``mp_group``: the ranks that together hold one model replica (tensor x pipeline), or None.  Writes {norm, coefficient}
+    into ``clip_state`` (device tensor of two floats) and returns the coefficient as a 1-element tensor view."""
+    import torch.distributed as dist
+
+    contrib = total_sq.reshape(1).clone()
+    if tp_world > 1 and replicated_sq is not None:
+        contrib -= (1.0 - 1.0 / tp_world) * replicated_sq.reshape(1)
+    if mp_group is not None and dist.get_world_size(mp_group) > 1:
+        dist.all_reduce(contrib, group=mp_group)
+    norm = contrib.clamp_min(0).sqrt() * grad_scale
+    clip_state[0:1].copy_(norm)
+    clip_state[1:2].copy_(torch.clamp(max_norm / (norm + 1e-6), max=1.0))
+    return clip_state[1:2]
+
+
 class MixedPrecisionAdam:
     """Adam/AdamW over :class:`FlatParams`: one fused kernel launch per step.
 
@@ -179,8 +210,11 @@ class MixedPrecisionAdam:
     """
 
     def __init__(self, params, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.0,
-                 grad_scale: float = 1.0, max_grad_norm: float = 0.0):
+                 grad_scale: float = 1.0, max_grad_norm: float = 0.0, mp_group=None, tp_world: int = 1):
         self.flat = params if isinstance(params, FlatParams) else FlatParams(params)
+        # model-parallel layout for the global gradient norm: the group holding one model replica and the size of
+        # its tensor-parallel dimension (parameters flagged as replicated there are counted once)
+        self.mp_group, self.tp_world = mp_group, tp_world
         f = self.flat
         self.lr, self.betas, self.eps, self.weight_decay, self.grad_scale = lr, betas, eps, weight_decay, grad_scale
         # > 0: the global L2 norm of (grad_scale * gradient) is clipped to this value before the update; the norm and
@@ -218,16 +252,22 @@ class MixedPrecisionAdam:
         self.t += 1
         b1, b2 = self.betas
         if f.device.type == "cuda":
-            if self.max_grad_norm > 0:
+            if self.max_grad_norm > 0 and self.mp_group is None:
                 C.clip_grad_norm_(f.grad, self.max_grad_norm, self.grad_scale, self.clip_state)
+            elif self.max_grad_norm > 0:
+                sq = torch.zeros(2, device=f.device, dtype=torch.float32)
+                C.sumsq_(f.grad, sq[0:1])
+                C.sumsq_(f.grad[:f.n_replicated], sq[1:2])
+                coef = clip_coefficient(sq[0], sq[1], self.tp_world, self.mp_group, self.grad_scale, self.max_grad_norm,
+                                        self.clip_state)
+                C.scale_by_dev_(f.grad, coef)
             C.adam_tick(self.dev_state, b1, b2)
             C.adam_flat(self.master, f.param if self.mixed else None, f.grad, self.m, self.v, self.lr, b1, b2,
                         self.eps, self.weight_decay, self.t, self.grad_scale, self.dev_state)
             return
         if self.max_grad_norm > 0:
-            norm = f.grad.norm() * self.grad_scale
-            coef = torch.clamp(self.max_grad_norm / (norm + 1e-6), max=1.0)
-            self.clip_state[0], self.clip_state[1] = norm, coef
+            coef = clip_coefficient((f.grad ** 2).sum(), (f.grad[:f.n_replicated] ** 2).sum(), self.tp_world, self.mp_group,
+                                    self.grad_scale, self.max_grad_norm, self.clip_state)
             f.grad.mul_(coef)
         g = f.grad * self.grad_scale
         self.m.mul_(b1).add_(g, alpha=1 - b1)

@@ -25,6 +25,7 @@ class ParallelMesh:
     pp_group: Optional[dist.ProcessGroup]
     dp_group: Optional[dist.ProcessGroup]
     pp_ranks: List[int]   # global ranks of this rank's pipeline, by stage
+    mp_group: Optional[dist.ProcessGroup] = None   # the tp * pp ranks that hold one model replica (None when that is 1 rank)
 
     @property
     def is_first_stage(self) -> bool:
@@ -72,4 +73,10 @@ def init_mesh(tp: int = 1, pp: int = 1, dp: Optional[int] = None) -> ParallelMes
                 if kind == "pp":
                     my_pp_ranks = ranks
     d, p, t = rank_coords(rank, tp, pp, dp)
-    return ParallelMesh(tp, pp, dp, rank, t, p, d, mine["tp"], mine["pp"], mine["dp"], my_pp_ranks)
+    mp_group = None
+    for dd in range(dp):                                   # one model-parallel group per data-parallel replica
+        ranks = list(range(dd * pp * tp, (dd + 1) * pp * tp))
+        g = dist.new_group(ranks) if len(ranks) > 1 else None
+        if rank in ranks:
+            mp_group = g
+    return ParallelMesh(tp, pp, dp, rank, t, p, d, mine["tp"], mine["pp"], mine["dp"], my_pp_ranks, mp_group)

@@ -242,15 +242,34 @@ def _mark_sp(p: torch.nn.Parameter) -> torch.nn.Parameter:
 
 
 def sync_sequence_parallel_grads(params, comm: TPComm) -> None:
+    """Sums the gradients of the parameters that are replicated over the tensor-parallel group (each rank saw only its
+    token shard).  When the parameters live in a flat buffer (``optim.FlatParams`` puts the replicated ones first) the
+    whole region is reduced by one collective; parameters outside a flat buffer are reduced one by one."""
     if comm.world == 1:
         return
+    done = set()
     for p in params:
-        if getattr(p, "_sp_grad_sync", False):
-            g = getattr(p, "main_grad", None)
-            if g is None:
-                g = p.grad
-            if g is not None:
-                comm.all_reduce(g)
+        if not getattr(p, "_sp_grad_sync", False):
+            continue
+        flat = getattr(p, "_flat", None)
+        if flat is not None and getattr(p, "main_grad", None) is not None:
+            if id(flat) not in done and flat.n_replicated > 0:
+                # a replicated parameter without a gradient this step must not contribute stale values
+                for q in flat.params:
+                    if getattr(q, "_sp_grad_sync", False) and q._fresh_grad and q.grad is None:
+                        q.main_grad.zero_()
+                        q._fresh_grad = False
+                    elif getattr(q, "_sp_grad_sync", False) and q.grad is not None:
+                        (q.main_grad.copy_ if q._fresh_grad else q.main_grad.add_)(q.grad)
+                        q._fresh_grad, q.grad = False, None
+                comm.all_reduce(flat.grad[:flat.n_replicated])
+                done.add(id(flat))
+            continue
+        g = getattr(p, "main_grad", None)
+        if g is None:
+            g = p.grad
+        if g is not None:
+            comm.all_reduce(g)
 
 
 class ColumnParallelLinear(nn.Module):

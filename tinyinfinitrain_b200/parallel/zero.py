@@ -30,7 +30,7 @@ from ..optim.optimizers import FlatParams
 class DistributedOptimizer:
     def __init__(self, params, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.0,
                  group: Optional[dist.ProcessGroup] = None, comm: str = "fused", average: bool = True,
-                 num_buckets: int = 1, overlap: bool = False, max_grad_norm: float = 0.0):
+                 num_buckets: int = 1, overlap: bool = False, max_grad_norm: float = 0.0, mp_group=None, tp_world: int = 1):
         plist = [p for p in params]
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
@@ -45,6 +45,7 @@ class DistributedOptimizer:
         # uses it, so the fused path reads its shard of the peers' gradients once more for the norm and every rank scales
         # its local buffer by the agreed coefficient before the fused reduce-scatter + Adam kernel runs.
         self.max_grad_norm = max_grad_norm
+        self.mp_group, self.tp_world = mp_group, tp_world     # model-parallel layout for the global norm (see optim.clip_coefficient)
         if max_grad_norm > 0 and overlap:
             raise ValueError("gradient clipping needs the whole gradient before any bucket is updated: use overlap=False")
         align = 8 * self.world * 16
@@ -258,32 +259,48 @@ class DistributedOptimizer:
 
     def _clip_fused(self) -> None:
         """Global-norm clipping on the fused path: barrier (all gradients written) -> squared norm of this rank's shard
-        of the summed gradient (NVLink read) -> exchange of the ranks' partial results through symmetric memory ->
-        coefficient -> every rank scales its own gradient buffer.  The regular bucket launch that follows starts
-        with its own barrier, which also orders the scaling before the peers' reads."""
+        of the summed gradient (NVLink read), separately for the region of tensor-parallel-replicated parameters ->
+        exchange of the ranks' partial results through symmetric memory -> coefficient -> every rank scales its own
+        gradient buffer.  The regular bucket launch that follows starts with its own barrier, which also orders the
+        scaling before the peers' reads."""
         from .._lib import C
+        from ..optim.optimizers import clip_coefficient
 
+        n_rep = self.flat.n_replicated
         self.barrier()
-        tot = 0
-        for i, b in enumerate(self.buckets):
-            C.rs_grad_sumsq(self.gbuf.ptrs, self.gbuf.mc_ptr, b["start"] + self.rank * b["shard"], b["shard"], self.rank,
-                            self._norm_buf.tensor[i:i + 1])
-            tot += 1
+        slots = []                                           # (slot index, belongs to the replicated region)
+        k = 0
+        self._norm_buf.tensor[:2 * len(self.buckets)].zero_()
+        for b in self.buckets:
+            lo = b["start"] + self.rank * b["shard"]
+            hi = lo + b["shard"]
+            C.rs_grad_sumsq(self.gbuf.ptrs, self.gbuf.mc_ptr, lo, b["shard"], self.rank, self._norm_buf.tensor[k:k + 1])
+            slots.append((k, False))
+            k += 1
+            rep_hi = min(hi, n_rep)
+            if rep_hi > lo:                                  # part of this shard lies in the replicated region
+                C.rs_grad_sumsq(self.gbuf.ptrs, self.gbuf.mc_ptr, lo, rep_hi - lo, self.rank, self._norm_buf.tensor[k:k + 1])
+            slots.append((k, True))
+            k += 1
         self.barrier()
-        # sum over ranks and buckets: tot values per rank, gathered slot by slot
-        sums = torch.empty(tot, device=self.flat.device, dtype=torch.float32)
-        C.allreduce_small(self._norm_buf.ptrs, sums, 0)
-        C.clip_coef_from_totals(sums, tot, self.grad_scale, self.max_grad_norm, self.clip_state)
-        C.scale_by_dev_(self.gbuf.tensor, self.clip_state[1:2])
+        sums = torch.empty(k, device=self.flat.device, dtype=torch.float32)
+        C.allreduce_small(self._norm_buf.ptrs, sums, 0)       # sum over the data-parallel ranks, slot by slot
+        total = sums[0::2].sum()
+        rep = sums[1::2].sum()
+        coef = clip_coefficient(total, rep, self.tp_world, self.mp_group, self.grad_scale, self.max_grad_norm, self.clip_state)
+        C.scale_by_dev_(self.gbuf.tensor, coef)
 
     def _clip_shard(self) -> None:
-        """Unfused path: squared norm of the reduced shard, summed over ranks, then the shard is scaled."""
-        sq = (self._gshard.float() ** 2).sum().reshape(1)
+        """Unfused path: squared norm of the reduced shard (and of its part in the replicated region), summed over the
+        data-parallel ranks, then the shard is scaled."""
+        from ..optim.optimizers import clip_coefficient
+
+        n_rep = self.flat.n_replicated
+        g = self._gshard.float()
+        rep_n = max(0, min(self.shard_off + self.shard_n, n_rep) - self.shard_off)
+        sq = torch.stack([(g ** 2).sum(), (g[:rep_n] ** 2).sum()])
         dist.all_reduce(sq, group=self.group)
-        norm = sq.sqrt() * self.grad_scale
-        coef = torch.clamp(self.max_grad_norm / (norm + 1e-6), max=1.0)
-        self.clip_state[0:1].copy_(norm)
-        self.clip_state[1:2].copy_(coef)
+        coef = clip_coefficient(sq[0], sq[1], self.tp_world, self.mp_group, self.grad_scale, self.max_grad_norm, self.clip_state)
         self._gshard.mul_(coef)
 
     def grad_norm(self) -> float:
@@ -339,13 +356,15 @@ class AllReduceOptimizer:
     :class:`DistributedOptimizer`, whose fused kernel is the product."""
 
     def __init__(self, params, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.0,
-                 group: Optional[dist.ProcessGroup] = None, max_grad_norm: float = 0.0):
+                 group: Optional[dist.ProcessGroup] = None, max_grad_norm: float = 0.0, mp_group=None, tp_world: int = 1):
         from ..optim.optimizers import MixedPrecisionAdam
 
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
         self.inner = MixedPrecisionAdam(params, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
-                                        grad_scale=1.0 / self.world, max_grad_norm=max_grad_norm)
+                                        grad_scale=1.0 / self.world, max_grad_norm=max_grad_norm,
+                                        mp_group=mp_group,
+                                        tp_world=tp_world)
         self.flat = self.inner.flat
         src = dist.get_global_rank(self.group, 0) if self.group is not dist.group.WORLD else 0
         dist.broadcast(self.flat.param, src=src, group=self.group)       # all replicas start from rank 0's weights
