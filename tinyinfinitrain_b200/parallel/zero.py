@@ -268,19 +268,16 @@ class DistributedOptimizer:
 
         n_rep = self.flat.n_replicated
         self.barrier()
-        slots = []                                           # (slot index, belongs to the replicated region)
-        k = 0
+        k = 0                                                # slots alternate: whole shard, its replicated part
         self._norm_buf.tensor[:2 * len(self.buckets)].zero_()
         for b in self.buckets:
             lo = b["start"] + self.rank * b["shard"]
             hi = lo + b["shard"]
             C.rs_grad_sumsq(self.gbuf.ptrs, self.gbuf.mc_ptr, lo, b["shard"], self.rank, self._norm_buf.tensor[k:k + 1])
-            slots.append((k, False))
             k += 1
             rep_hi = min(hi, n_rep)
             if rep_hi > lo:                                  # part of this shard lies in the replicated region
                 C.rs_grad_sumsq(self.gbuf.ptrs, self.gbuf.mc_ptr, lo, rep_hi - lo, self.rank, self._norm_buf.tensor[k:k + 1])
-            slots.append((k, True))
             k += 1
         self.barrier()
         sums = torch.empty(k, device=self.flat.device, dtype=torch.float32)
