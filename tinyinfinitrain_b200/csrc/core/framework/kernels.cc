@@ -558,12 +558,33 @@ TP CrossEntropyBackward(const TP& input, const TP& target, const TP& grad_output
 }
 TP EmbeddingForward(const TP& input, const TP& weight) {
   TORCH_CHECK(input->data().scalar_type() == at::kLong, "Embedding indices must be INT64");
-  return W(at::embedding(weight->data(), input->data()));
+  const at::Tensor &idx = input->data(), &w = weight->data();
+  const int64_t C = w.size(-1);
+  if (native(w) && idx.is_cuda() && w.is_contiguous() && C % (w.scalar_type() == at::kBFloat16 ? 8 : 4) == 0 && idx.dim() >= 1) {
+    c10::cuda::CUDAGuard guard(w.device());
+    at::Tensor ic = materialize(idx);
+    auto sizes = ic.sizes().vec();
+    sizes.push_back(C);
+    at::Tensor out = at::empty(sizes, w.options());
+    ok(titb_embedding_fwd(reinterpret_cast<const long long*>(ic.data_ptr<int64_t>()), w.data_ptr(), nullptr, out.data_ptr(),
+                          ic.numel(), (int)ic.size(-1), (int)C, 0, dt(w), stream()), "EmbeddingForward");
+    return W(out);
+  }
+  return W(at::embedding(w, idx));
 }
 TP EmbeddingBackward(const TP& input, const std::vector<int64_t>& weight_dims, const TP& grad_output) {
   const at::Tensor& g = grad_output->data();
+  const at::Tensor& idx = input->data();
   at::Tensor dw = at::zeros(weight_dims, g.options().dtype(at::kFloat));
-  dw.index_add_(0, input->data().reshape({-1}), g.reshape({-1, g.size(-1)}).to(at::kFloat));
+  const int64_t C = g.size(-1);
+  if (native(g) && idx.is_cuda() && C % (g.scalar_type() == at::kBFloat16 ? 8 : 4) == 0 && idx.dim() >= 1) {
+    c10::cuda::CUDAGuard guard(g.device());
+    at::Tensor ic = materialize(idx), gc = materialize(g);
+    ok(titb_embedding_bwd(reinterpret_cast<const long long*>(ic.data_ptr<int64_t>()), gc.data_ptr(), dw.data_ptr<float>(), nullptr,
+                          ic.numel(), (int)ic.size(-1), (int)C, 0, (int)weight_dims[0], dt(gc), stream()), "EmbeddingBackward");
+    return W(dw.to(g.scalar_type()));
+  }
+  dw.index_add_(0, idx.reshape({-1}), g.reshape({-1, C}).to(at::kFloat));
   return W(dw.to(g.scalar_type()));
 }
 
