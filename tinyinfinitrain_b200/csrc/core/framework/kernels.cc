@@ -195,9 +195,34 @@ static at::Tensor reduce_to(at::Tensor g, const std::vector<int64_t>& dims) {
     if (dims[d] == 1 && g.size(d) != 1) g = g.sum(static_cast<int64_t>(d), true);
   return g.contiguous();
 }
+// b right-aligned against a and broadcast one way (b -> a), as in the reference's elementwise.cu:23-48
+static bool broadcast_desc(const at::Tensor& a, const at::Tensor& b, TitbBroadcast* bc) {
+  if (a.dim() > 8 || b.dim() > a.dim()) return false;
+  bc->ndim = (int)a.dim();
+  const int64_t off = a.dim() - b.dim();
+  int64_t bstride = 1;
+  for (int64_t d = a.dim() - 1; d >= 0; --d) {
+    bc->a_dims[d] = a.size(d);
+    bc->b_strides[d] = 0;
+    if (d >= off) {
+      const int64_t bd = b.size(d - off);
+      if (bd != a.size(d) && bd != 1) return false;
+      bc->b_strides[d] = (bd == 1) ? 0 : bstride;
+      bstride *= bd;
+    }
+  }
+  return true;
+}
 static TP binary(int op, const TP& a, const TP& b) {
   const at::Tensor &x = a->data(), &y = b->data();
   TORCH_CHECK(x.numel() % std::max<int64_t>(1, y.numel()) == 0, "binary op: b does not broadcast to a");
+  TitbBroadcast bc{};
+  if (native(x) && native(y) && x.scalar_type() == y.scalar_type() && x.numel() > 0 && broadcast_desc(x, y, &bc)) {
+    c10::cuda::CUDAGuard guard(x.device());
+    at::Tensor xc = materialize(x), yc = materialize(y), out = at::empty_like(xc);
+    ok(titb_binary_fwd(op, xc.data_ptr(), yc.data_ptr(), out.data_ptr(), xc.numel(), bc, dt(xc), stream()), "binary");
+    return W(out);
+  }
   switch (op) {
     case 0: return W(x + y);
     case 1: return W(x - y);
@@ -291,7 +316,18 @@ std::tuple<TP, TP, TP> LinearBackward(const TP& input, const TP& weight, bool tr
   at::Tensor x2 = x.reshape({-1, x.size(-1)}), g2 = g.reshape({-1, out_features});
   at::Tensor dx = gemm2d(g2, w, false, !transpose).reshape(x.sizes());  // dY W  (or dY W^T)
   at::Tensor dw = transpose ? gemm2d(g2, x2, true, false) : gemm2d(x2, g2, true, false);
-  TP db = has_bias ? W(g2.sum(0)) : nullptr;  // column sums (the reference's CUDA path sums the wrong axis)
+  TP db = nullptr;  // column sums (the reference's CUDA path sums the wrong axis)
+  if (has_bias && native(g2)) {
+    c10::cuda::CUDAGuard guard(g2.device());
+    at::Tensor gc = materialize(g2);
+    auto fopt = gc.options().dtype(at::kFloat);
+    at::Tensor sum = at::empty({out_features}, fopt), scratch = at::empty({titb_colsum_blocks(gc.size(0)), out_features}, fopt);
+    ok(titb_colsum(gc.data_ptr(), sum.data_ptr<float>(), gc.size(0), (int)out_features, dt(gc), 0, scratch.data_ptr<float>(),
+                   stream()), "bias gradient");
+    db = W(sum.to(gc.scalar_type()));
+  } else if (has_bias) {
+    db = W(g2.sum(0));
+  }
   return {W(dx), W(dw), db};
 }
 
@@ -339,7 +375,19 @@ std::tuple<TP, TP, TP> LayerNormBackward(const TP& input, const TP& weight, cons
                                          const TP& grad_output) {
   const at::Tensor& x = input->data();
   const int64_t C = x.size(-1), rows = x.numel() / C;
-  at::Tensor xf = x.to(at::kFloat).reshape({rows, C}), g = grad_output->data().to(at::kFloat).reshape({rows, C});
+  const at::Tensor& go = grad_output->data();
+  if (native(x) && x.is_contiguous() && go.is_contiguous() && go.scalar_type() == x.scalar_type() &&
+      weight->data().scalar_type() == x.scalar_type()) {
+    c10::cuda::CUDAGuard guard(x.device());
+    auto fopt = x.options().dtype(at::kFloat);
+    at::Tensor dx = at::empty_like(x), dw = at::empty({C}, fopt), db = at::empty({C}, fopt);
+    at::Tensor scratch = at::empty({2, titb_layernorm_bwd_blocks(rows), C}, fopt);
+    ok(titb_layernorm_bwd(go.data_ptr(), x.data_ptr(), weight->data().data_ptr(), mean->data().data_ptr<float>(),
+                          rstd->data().data_ptr<float>(), dx.data_ptr(), dw.data_ptr<float>(), db.data_ptr<float>(),
+                          scratch.data_ptr<float>(), rows, (int)C, dt(x), 0, stream()), "LayerNormBackward");
+    return {W(dx), W(dw.to(weight->data().scalar_type())), W(db.to(weight->data().scalar_type()))};
+  }
+  at::Tensor xf = x.to(at::kFloat).reshape({rows, C}), g = go.to(at::kFloat).reshape({rows, C});
   at::Tensor w = weight->data().to(at::kFloat);
   at::Tensor norm = (xf - mean->data().unsqueeze(1)) * rstd->data().unsqueeze(1);
   at::Tensor dnorm = g * w;
@@ -551,6 +599,13 @@ TP CrossEntropyBackward(const TP& input, const TP& target, const TP& grad_output
   const at::Tensor& x = input->data();
   const int64_t V = x.size(-1), rows = x.numel() / V;
   at::Tensor tgt = target->data().reshape({rows}).to(at::kLong);
+  if (native(x) && x.is_contiguous() && tgt.is_cuda()) {
+    c10::cuda::CUDAGuard guard(x.device());
+    at::Tensor d = at::empty_like(x), up = grad_output->data().to(at::kFloat).reshape({-1}).contiguous(), tc = tgt.contiguous();
+    ok(titb_xent_bwd(x.data_ptr(), reinterpret_cast<const long long*>(tc.data_ptr<int64_t>()), d.data_ptr(), up.data_ptr<float>(),
+                     rows, (int)V, V, 1.f / static_cast<float>(rows), dt(x), stream()), "CrossEntropyBackward");
+    return W(d);
+  }
   at::Tensor p = at::softmax(x.to(at::kFloat).reshape({rows, V}), 1);
   p.scatter_add_(1, tgt.unsqueeze(1), at::full({rows, 1}, -1.0, p.options()));
   at::Tensor d = p * (grad_output->data().to(at::kFloat) / static_cast<double>(rows));  // honours the upstream gradient
