@@ -364,3 +364,38 @@ def test_row_cached_cross_entropy_matches_the_regular_kernel(dtype, rows, ld, V)
     assert torch.all(b[:, V:] == 0)
     assert torch.allclose(b.float()[:, :V], ref_in.grad, atol=2e-4 if dtype == BF else 1e-6, rtol=3e-2)
     _status_ok()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, BF])
+@pytest.mark.parametrize("rows,cols", [(8192, 768), (8192, 3072), (1000, 2304), (37, 264), (5, 8)])
+def test_one_launch_column_sum_matches_the_two_stage_kernel(dtype, rows, cols):
+    torch.manual_seed(17)
+    x = torch.randn(rows, cols, device=DEV).to(dtype)
+    ref = x.double().sum(0)
+    two = C.colsum(x, None, False, False)
+    runs = [C.colsum(x, None, False, True) for _ in range(3)]
+    assert torch.equal(runs[0], runs[1]) and torch.equal(runs[1], runs[2])      # fixed summation order
+    tol = 2e-3 * rows ** 0.5
+    assert torch.allclose(runs[0].double(), ref, atol=tol) and torch.allclose(two.double(), ref, atol=tol)
+    acc = torch.ones(cols, device=DEV)
+    C.colsum(x, acc, True, True)
+    assert torch.allclose(acc.double(), 1.0 + ref, atol=tol)
+    # a different shape right after: the counters of the previous launches were left at zero
+    y = torch.randn(rows + 3, cols, device=DEV).to(dtype)
+    assert torch.allclose(C.colsum(y, None, False, True).double(), y.double().sum(0), atol=tol)
+    _status_ok()
+
+
+def test_one_launch_column_sum_inside_a_cuda_graph():
+    x = torch.randn(4096, 768, device=DEV).to(BF)
+    out = torch.zeros(768, device=DEV)
+    C.colsum(x, out, False, True)                          # allocates the counters outside of the capture
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        C.colsum(x, out, False, True)
+    for _ in range(3):
+        x.normal_()
+        g.replay()
+        torch.cuda.synchronize()
+        assert torch.allclose(out.double(), x.double().sum(0), atol=0.2)

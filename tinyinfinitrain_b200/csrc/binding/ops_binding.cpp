@@ -2,8 +2,12 @@
 // Outputs are allocated with the torch caching allocator and every launch goes
 // to the current CUDA stream, so the ops can be captured in CUDA graphs.
 #include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGraphsC10Utils.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
+
+#include <map>
+#include <mutex>
 
 #include "kernels/api.h"
 
@@ -630,13 +634,43 @@ std::vector<Tensor> outer_bwd(const Tensor& g_, const Tensor& a_, const Tensor& 
 }
 
 // Column sums of a [rows, C] view into an fp32 [C] tensor (bias gradients).
-Tensor colsum(const Tensor& x, const optional<Tensor>& out_, bool accumulate) {
+// Zeroed counter words of the one-launch column sum: one array per device, cut into 64 slots of 256 words; a
+// stream always uses the same slot, so its launches (which are ordered) share self-resetting counters, and two
+// streams that run column sums at the same time interfere only if their handles hash to the same slot.
+static unsigned* colsum_counters(const Tensor& like, int words) {
+  constexpr int kSlots = 64, kSlotWords = 256;
+  TORCH_CHECK(words <= kSlotWords, "colsum: too many column strips for the one-launch kernel");
+  static std::mutex mu;
+  static std::map<int, Tensor> table;
+  std::lock_guard<std::mutex> lock(mu);
+  const int dev = (int)like.get_device();
+  auto it = table.find(dev);
+  if (it == table.end()) {
+    // a tensor created while a graph is being captured would live in the graph's private pool, and the fill
+    // that zeroes it would be replayed with the graph
+    TORCH_CHECK(c10::cuda::currentStreamCaptureStatusMayInitCtx() == c10::cuda::CaptureStatus::None,
+                "colsum: run one step outside of graph capture before capturing (counter allocation)");
+    it = table.emplace(dev, at::zeros({kSlots * kSlotWords}, like.options().dtype(at::kInt))).first;
+  }
+  const size_t slot = (std::hash<void*>()((void*)cur_stream()) >> 4) % kSlots;
+  return reinterpret_cast<unsigned*>(it->second.data_ptr<int>()) + slot * kSlotWords;
+}
+
+Tensor colsum(const Tensor& x, const optional<Tensor>& out_, bool accumulate, bool fused) {
   check_cuda(x, "x");
   c10::cuda::CUDAGuard guard(x.device());
   const int64_t C = x.size(-1), rows = x.numel() / C;
   auto fopt = x.options().dtype(at::kFloat);
   const bool have = out_.has_value() && out_->defined();
   Tensor out = have ? *out_ : at::empty({C}, fopt);
+  if (fused && titb_colsum_fused_ok(x.data_ptr(), rows, (int)C, dt_code(x)) &&
+      titb_colsum_fused_counters((int)C, dt_code(x)) <= 256) {
+    Tensor scratch = at::empty({titb_colsum_fused_scratch(rows, (int)C, dt_code(x))}, fopt);
+    unsigned* counters = colsum_counters(x, titb_colsum_fused_counters((int)C, dt_code(x)));
+    CHECK_RC(titb_colsum_fused(x.data_ptr(), out.data_ptr<float>(), rows, (int)C, dt_code(x), have && accumulate,
+                               scratch.data_ptr<float>(), counters, cur_stream()), "colsum_fused", 2);
+    return out;
+  }
   Tensor scratch = at::empty({titb_colsum_blocks(rows), C}, fopt);
   CHECK_RC(titb_colsum(x.data_ptr(), out.data_ptr<float>(), rows, (int)C, dt_code(x), have && accumulate,
                        scratch.data_ptr<float>(), cur_stream()), "colsum", 2);
@@ -713,7 +747,8 @@ PYBIND11_MODULE(_C, m) {
   m.def("fill_", &fill_);
   m.def("transpose_last2", &transpose_last2);
   m.def("tri", &tri);
-  m.def("colsum", &colsum, py::arg("x"), py::arg("out") = py::none(), py::arg("accumulate") = false);
+  m.def("colsum", &colsum, py::arg("x"), py::arg("out") = py::none(), py::arg("accumulate") = false,
+        py::arg("fused") = false);
   m.def("status_read", &status_read, py::arg("clear") = true);
   m.def("gemm_set_tma_store", [](bool on) { titb_gemm_set_tma_store(on ? 1 : 0); });
   bind_attention(m);

@@ -220,6 +220,14 @@ TITB_API int titb_tri(const void* x, void* y, int R, int C, int diagonal, int up
 TITB_API int titb_colsum(const void* x, float* out, long long rows, int C, int dtype, int accumulate,
                          float* scratch, cudaStream_t stream);
 TITB_API int titb_colsum_blocks(long long rows);
+// One-launch column sums: the last CTA of each column strip folds the partial rows.  `scratch` holds
+// titb_colsum_fused_scratch floats, `counters` titb_colsum_fused_counters unsigned words that are zero before the
+// first launch (every launch leaves them zero); launches that share counters must be ordered on one stream.
+TITB_API int titb_colsum_fused_ok(const void* x, long long rows, int C, int dtype);
+TITB_API long long titb_colsum_fused_scratch(long long rows, int C, int dtype);
+TITB_API int titb_colsum_fused_counters(int C, int dtype);
+TITB_API int titb_colsum_fused(const void* x, float* out, long long rows, int C, int dtype, int accumulate,
+                               float* scratch, unsigned* counters, cudaStream_t stream);
 
 // ---- reductions and view-like transforms (dtype: 0 = fp32, 1 = bf16) ---------------------------------
 // x viewed as [outer, n, inner] -> y [outer, inner].  op: 0 sum, 1 mean, 2 max, 3 min; for max / min `idx`

@@ -33,6 +33,8 @@ EPI_NONE, EPI_BIAS, EPI_BIAS_GELU, EPI_DGELU, EPI_BIAS_RESIDUAL = 0, 1, 2, 3, 4
 DETERMINISTIC_EMBEDDING_GRAD = os.environ.get("TITB200_DETERMINISTIC", "0") == "1"
 # TITB200_XENT_CACHED=1: the loss kernel keeps each logits row in shared memory between its two passes (rows up to 200 KB)
 XENT_ROW_CACHED = os.environ.get("TITB200_XENT_CACHED", "0") == "1"
+# bias gradients with the one-launch column sum (the last CTA of a column strip folds the partial rows)
+COLSUM_FUSED = os.environ.get("TITB200_COLSUM_FUSED", "0") == "1"
 
 _bf16 = torch.bfloat16
 
@@ -68,10 +70,10 @@ def _wgrad(dy2: torch.Tensor, x2: torch.Tensor, w: torch.Tensor, alpha=None):
 def _bgrad(dy2: torch.Tensor, b: torch.Tensor):
     mg, acc = _grad_target(b)
     if mg is not None:
-        C.colsum(dy2, out=mg, accumulate=acc)
+        C.colsum(dy2, out=mg, accumulate=acc, fused=COLSUM_FUSED)
         _grad_done(b)
         return None
-    return C.colsum(dy2).to(b.dtype)
+    return C.colsum(dy2, fused=COLSUM_FUSED).to(b.dtype)
 
 
 def gelu_ref(x: torch.Tensor) -> torch.Tensor:
@@ -138,7 +140,7 @@ class _LinearF32Fn(torch.autograd.Function):
         dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
         dx = C.sgemm(dy2, w.contiguous(), False, False).view(ctx.xshape)
         dw = C.sgemm(dy2, x2, True, False)
-        db = C.colsum(dy2) if ctx.has_b else None
+        db = C.colsum(dy2, fused=COLSUM_FUSED) if ctx.has_b else None
         return dx, dw, db
 
 

@@ -69,6 +69,7 @@ def main():
     ap.add_argument("--tile_n", type=int, default=0)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no_flush", action="store_true")
+    ap.add_argument("--fused", action="store_true", help="colsum: one launch, the last CTA of a column strip folds the partials")
     ap.add_argument("--cached", action="store_true", help="xent: keep each row in shared memory between the two passes")
     a = ap.parse_args()
     dev = "cuda"
@@ -177,7 +178,7 @@ def main():
         x = torch.randn(a.m, a.n, device=dev).to(bf)
         outc = torch.zeros(a.n, device=dev)
         bytes_ = x.numel() * 2.0
-        fn = lambda: C.colsum(x, outc, False)
+        fn = lambda: C.colsum(x, outc, False, a.fused)
     elif a.kernel == "xent":
         logits = torch.randn(a.m, a.n, device=dev).to(bf)
         tgt = torch.randint(0, a.n - 47, (a.m,), device=dev)
