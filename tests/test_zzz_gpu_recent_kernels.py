@@ -399,3 +399,71 @@ def test_one_launch_column_sum_inside_a_cuda_graph():
         g.replay()
         torch.cuda.synchronize()
         assert torch.allclose(out.double(), x.double().sum(0), atol=0.2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, BF])
+@pytest.mark.parametrize("rows,cols", [(8192, 768), (1000, 1024), (4737, 512), (37, 256), (5, 64)])
+@pytest.mark.parametrize("rms", [False, True])
+def test_one_launch_norm_backward_matches_the_two_stage_kernels(dtype, rows, cols, rms):
+    """Shapes with fewer rows than warps, a ragged last round of four rows, the widest row a warp can hold (bf16
+    1024; fp32 1024 falls back to the two-stage kernels and still has to honour `dres`)."""
+    torch.manual_seed(19)
+    x = (torch.randn(rows, cols, device=DEV) * 1.5 + 0.3).to(dtype)
+    w = (torch.rand(cols, device=DEV) + 0.5).to(dtype)
+    b = torch.randn(cols, device=DEV).to(dtype)
+    dy = torch.randn(rows, cols, device=DEV).to(dtype)
+    dres = torch.randn(rows, cols, device=DEV).to(dtype)
+    xr = x.float().requires_grad_(True)
+    wr, br = w.float().requires_grad_(True), b.float().requires_grad_(True)
+    if rms:
+        y, rstd = C.rmsnorm_fwd(x, w, 1e-5)
+        ref = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-5) * wr
+        one = lambda **kw: C.rmsnorm_bwd(dy, x, w, rstd, **kw)
+    else:
+        y, mean, rstd = C.layernorm_fwd(x, w, b, 1e-5)
+        ref = torch.nn.functional.layer_norm(xr, (cols,), wr, br, 1e-5)
+        one = lambda **kw: C.layernorm_bwd(dy, x, w, mean, rstd, **kw)
+    ref.backward(dy.float())
+    two = one()
+    runs = [one(onepass=True) for _ in range(3)]
+    for r in runs[1:]:
+        assert all(torch.equal(a, c) for a, c in zip(runs[0], r))              # fixed summation order
+    tol_x = 3e-2 if dtype == BF else 2e-5
+    tol_w = 4e-3 * rows ** 0.5 if dtype == BF else 2e-4 * rows ** 0.5
+    assert torch.allclose(runs[0][0].float(), xr.grad, atol=tol_x, rtol=2e-2)
+    assert torch.allclose(runs[0][0].float(), two[0].float(), atol=tol_x, rtol=2e-2)
+    assert torch.allclose(runs[0][1], wr.grad, atol=tol_w, rtol=1e-2)
+    if not rms:
+        assert torch.allclose(runs[0][2], br.grad, atol=tol_w, rtol=1e-2)
+    # residual gradient folded into dx; weight gradients accumulated into given buffers
+    dw_acc = torch.ones(cols, device=DEV)
+    extra = {"dw": dw_acc, "accumulate": True, "onepass": True, "dres": dres}
+    if not rms:
+        extra["db"] = torch.ones(cols, device=DEV)
+    out = one(**extra)
+    assert torch.allclose(out[0].float(), xr.grad + dres.float(), atol=2 * tol_x, rtol=2e-2)
+    assert torch.allclose(dw_acc, 1.0 + wr.grad, atol=tol_w, rtol=1e-2)
+    if not rms:
+        assert torch.allclose(extra["db"], 1.0 + br.grad, atol=tol_w, rtol=1e-2)
+    _status_ok()
+
+
+def test_norm_fork_folds_the_residual_gradient(monkeypatch):
+    """GPT-2 block gradients with the one-launch norm backward (residual gradient added inside the kernel) equal the
+    default path (separate add by autograd)."""
+    from tinyinfinitrain_b200.models import GPT2, GPT2Config
+    from tinyinfinitrain_b200.ops import functional as Fn
+    cfg = GPT2Config(block_size=64, vocab_size=300, padded_vocab_size=320, n_layer=2, n_head=2, n_embd=128)
+    idx = torch.randint(0, 300, (2, 64), device=DEV)
+    tgt = torch.randint(0, 300, (2, 64), device=DEV)
+    grads = []
+    for flag in (False, True):
+        monkeypatch.setattr(Fn, "NORM_BWD_ONEPASS", flag)
+        model = GPT2(cfg, device=DEV, dtype=BF, seed=5)
+        loss = model(idx, tgt)[1]
+        loss.backward()
+        grads.append({n: p.grad.float().clone() for n, p in model.named_parameters()})
+    for n in grads[0]:
+        scale = grads[0][n].abs().max().item() + 1e-6
+        assert (grads[0][n] - grads[1][n]).abs().max().item() < 0.05 * scale, n
+    _status_ok()

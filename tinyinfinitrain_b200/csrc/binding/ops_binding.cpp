@@ -195,10 +195,33 @@ std::vector<Tensor> layernorm_fwd(const Tensor& x, const Tensor& w, const Tensor
            "layernorm_fwd");
   return {y, mean, rstd};
 }
+// Zeroed counter words for kernels whose last CTA finishes a reduction (column sums, norm backward): one array
+// per device, cut into 64 slots of 256 words; a
+// stream always uses the same slot, so its launches (which are ordered) share self-resetting counters, and two
+// streams that run such kernels at the same time interfere only if their handles hash to the same slot.
+static unsigned* ticket_counters(const Tensor& like, int words) {
+  constexpr int kSlots = 64, kSlotWords = 256;
+  TORCH_CHECK(words <= kSlotWords, "titb200: too many ticket counters for one launch");
+  static std::mutex mu;
+  static std::map<int, Tensor> table;
+  std::lock_guard<std::mutex> lock(mu);
+  const int dev = (int)like.get_device();
+  auto it = table.find(dev);
+  if (it == table.end()) {
+    // a tensor created while a graph is being captured would live in the graph's private pool, and the fill
+    // that zeroes it would be replayed with the graph
+    TORCH_CHECK(c10::cuda::currentStreamCaptureStatusMayInitCtx() == c10::cuda::CaptureStatus::None,
+                "titb200: run one step outside of graph capture before capturing (ticket counter allocation)");
+    it = table.emplace(dev, at::zeros({kSlots * kSlotWords}, like.options().dtype(at::kInt))).first;
+  }
+  const size_t slot = (std::hash<void*>()((void*)cur_stream()) >> 4) % kSlots;
+  return reinterpret_cast<unsigned*>(it->second.data_ptr<int>()) + slot * kSlotWords;
+}
+
 // dw/db are written (or accumulated) into fp32 tensors supplied by the caller, or fresh ones.
 std::vector<Tensor> layernorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& mean,
                                   const Tensor& rstd, const optional<Tensor>& dw_, const optional<Tensor>& db_,
-                                  bool accumulate) {
+                                  bool accumulate, bool onepass, const optional<Tensor>& dres_) {
   check_cuda(dy, "dy"); check_cuda(x, "x");
   c10::cuda::CUDAGuard guard(x.device());
   const int64_t C = x.size(-1), rows = x.numel() / C;
@@ -208,11 +231,29 @@ std::vector<Tensor> layernorm_bwd(const Tensor& dy, const Tensor& x, const Tenso
   Tensor dw = have ? *dw_ : at::empty({C}, fopt);
   Tensor db = (db_.has_value() && db_->defined()) ? *db_ : at::empty({C}, fopt);
   TORCH_CHECK(dw.scalar_type() == at::kFloat && db.scalar_type() == at::kFloat, "titb200: fp32 weight grads");
+  const bool have_res = dres_.has_value() && dres_->defined();
+  Tensor dres;
+  if (have_res) {
+    dres = dres_->contiguous();
+    TORCH_CHECK(dres.sizes() == x.sizes() && dres.scalar_type() == x.scalar_type(), "titb200: dres must match x");
+  }
+  if (onepass && titb_norm_bwd_onepass_ok(rows, (int)C, dt_code(x), dy.data_ptr(), x.data_ptr(), w.data_ptr(),
+                                          have_res ? dres.data_ptr() : nullptr, dx.data_ptr())) {
+    Tensor scratch = at::empty({titb_norm_bwd_onepass_scratch((int)C)}, fopt);
+    unsigned* counters = ticket_counters(x, titb_norm_bwd_onepass_counters());
+    CHECK_RC(titb_norm_bwd_onepass(dy.data_ptr(), x.data_ptr(), w.data_ptr(), mean.data_ptr<float>(),
+                                   rstd.data_ptr<float>(), have_res ? dres.data_ptr() : nullptr, dx.data_ptr(),
+                                   dw.data_ptr<float>(), db.data_ptr<float>(), scratch.data_ptr<float>(), counters, rows,
+                                   (int)C, dt_code(x), 0, have && accumulate, cur_stream()),
+             "norm_bwd_onepass", 3);
+    return {dx, dw, db};
+  }
   Tensor scratch = at::empty({2, titb_layernorm_bwd_blocks(rows), C}, fopt);
   CHECK_RC(titb_layernorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), mean.data_ptr<float>(),
                               rstd.data_ptr<float>(), dx.data_ptr(), dw.data_ptr<float>(), db.data_ptr<float>(),
                               scratch.data_ptr<float>(), rows, (int)C, dt_code(x), have && accumulate, cur_stream()),
            "layernorm_bwd", 3);
+  if (have_res) dx.add_(dres);
   return {dx, dw, db};
 }
 std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const Tensor& w, double eps) {
@@ -226,7 +267,8 @@ std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const Tensor& w, double eps) {
   return {y, rstd};
 }
 std::vector<Tensor> rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& rstd,
-                                const optional<Tensor>& dw_, bool accumulate) {
+                                const optional<Tensor>& dw_, bool accumulate, bool onepass,
+                                const optional<Tensor>& dres_) {
   check_cuda(dy, "dy"); check_cuda(x, "x");
   c10::cuda::CUDAGuard guard(x.device());
   const int64_t C = x.size(-1), rows = x.numel() / C;
@@ -234,10 +276,28 @@ std::vector<Tensor> rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor&
   auto fopt = x.options().dtype(at::kFloat);
   const bool have = dw_.has_value() && dw_->defined();
   Tensor dw = have ? *dw_ : at::empty({C}, fopt);
+  const bool have_res = dres_.has_value() && dres_->defined();
+  Tensor dres;
+  if (have_res) {
+    dres = dres_->contiguous();
+    TORCH_CHECK(dres.sizes() == x.sizes() && dres.scalar_type() == x.scalar_type(), "titb200: dres must match x");
+  }
+  if (onepass && titb_norm_bwd_onepass_ok(rows, (int)C, dt_code(x), dy.data_ptr(), x.data_ptr(), w.data_ptr(),
+                                          have_res ? dres.data_ptr() : nullptr, dx.data_ptr())) {
+    Tensor scratch = at::empty({titb_norm_bwd_onepass_scratch((int)C)}, fopt);
+    unsigned* counters = ticket_counters(x, titb_norm_bwd_onepass_counters());
+    CHECK_RC(titb_norm_bwd_onepass(dy.data_ptr(), x.data_ptr(), w.data_ptr(), nullptr, rstd.data_ptr<float>(),
+                                   have_res ? dres.data_ptr() : nullptr, dx.data_ptr(), dw.data_ptr<float>(), nullptr,
+                                   scratch.data_ptr<float>(), counters, rows, (int)C, dt_code(x), 1,
+                                   have && accumulate, cur_stream()),
+             "norm_bwd_onepass", 2);
+    return {dx, dw};
+  }
   Tensor scratch = at::empty({2, titb_layernorm_bwd_blocks(rows), C}, fopt);
   CHECK_RC(titb_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(),
                             dw.data_ptr<float>(), scratch.data_ptr<float>(), rows, (int)C, dt_code(x),
                             have && accumulate, cur_stream()), "rmsnorm_bwd", 2);
+  if (have_res) dx.add_(dres);
   return {dx, dw};
 }
 
@@ -634,28 +694,6 @@ std::vector<Tensor> outer_bwd(const Tensor& g_, const Tensor& a_, const Tensor& 
 }
 
 // Column sums of a [rows, C] view into an fp32 [C] tensor (bias gradients).
-// Zeroed counter words of the one-launch column sum: one array per device, cut into 64 slots of 256 words; a
-// stream always uses the same slot, so its launches (which are ordered) share self-resetting counters, and two
-// streams that run column sums at the same time interfere only if their handles hash to the same slot.
-static unsigned* colsum_counters(const Tensor& like, int words) {
-  constexpr int kSlots = 64, kSlotWords = 256;
-  TORCH_CHECK(words <= kSlotWords, "colsum: too many column strips for the one-launch kernel");
-  static std::mutex mu;
-  static std::map<int, Tensor> table;
-  std::lock_guard<std::mutex> lock(mu);
-  const int dev = (int)like.get_device();
-  auto it = table.find(dev);
-  if (it == table.end()) {
-    // a tensor created while a graph is being captured would live in the graph's private pool, and the fill
-    // that zeroes it would be replayed with the graph
-    TORCH_CHECK(c10::cuda::currentStreamCaptureStatusMayInitCtx() == c10::cuda::CaptureStatus::None,
-                "colsum: run one step outside of graph capture before capturing (counter allocation)");
-    it = table.emplace(dev, at::zeros({kSlots * kSlotWords}, like.options().dtype(at::kInt))).first;
-  }
-  const size_t slot = (std::hash<void*>()((void*)cur_stream()) >> 4) % kSlots;
-  return reinterpret_cast<unsigned*>(it->second.data_ptr<int>()) + slot * kSlotWords;
-}
-
 Tensor colsum(const Tensor& x, const optional<Tensor>& out_, bool accumulate, bool fused) {
   check_cuda(x, "x");
   c10::cuda::CUDAGuard guard(x.device());
@@ -666,7 +704,7 @@ Tensor colsum(const Tensor& x, const optional<Tensor>& out_, bool accumulate, bo
   if (fused && titb_colsum_fused_ok(x.data_ptr(), rows, (int)C, dt_code(x)) &&
       titb_colsum_fused_counters((int)C, dt_code(x)) <= 256) {
     Tensor scratch = at::empty({titb_colsum_fused_scratch(rows, (int)C, dt_code(x))}, fopt);
-    unsigned* counters = colsum_counters(x, titb_colsum_fused_counters((int)C, dt_code(x)));
+    unsigned* counters = ticket_counters(x, titb_colsum_fused_counters((int)C, dt_code(x)));
     CHECK_RC(titb_colsum_fused(x.data_ptr(), out.data_ptr<float>(), rows, (int)C, dt_code(x), have && accumulate,
                                scratch.data_ptr<float>(), counters, cur_stream()), "colsum_fused", 2);
     return out;
@@ -710,10 +748,12 @@ PYBIND11_MODULE(_C, m) {
         py::arg("out") = py::none(), py::arg("accumulate") = false);
   m.def("layernorm_fwd", &layernorm_fwd);
   m.def("layernorm_bwd", &layernorm_bwd, py::arg("dy"), py::arg("x"), py::arg("w"), py::arg("mean"), py::arg("rstd"),
-        py::arg("dw") = py::none(), py::arg("db") = py::none(), py::arg("accumulate") = false);
+        py::arg("dw") = py::none(), py::arg("db") = py::none(), py::arg("accumulate") = false,
+        py::arg("onepass") = false, py::arg("dres") = py::none());
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd, py::arg("dy"), py::arg("x"), py::arg("w"), py::arg("rstd"),
-        py::arg("dw") = py::none(), py::arg("accumulate") = false);
+        py::arg("dw") = py::none(), py::arg("accumulate") = false, py::arg("onepass") = false,
+        py::arg("dres") = py::none());
   m.def("gelu_fwd", &gelu_fwd);
   m.def("gelu_bwd", &gelu_bwd);
   m.def("swiglu_fwd", &swiglu_fwd);

@@ -108,6 +108,18 @@ TITB_API int titb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd
 TITB_API int titb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw,
                               float* scratch, long long rows, int C, int dtype, int accumulate_wgrad,
                               cudaStream_t stream);
+// LayerNorm (rms == 0) or RMSNorm (rms != 0) backward in one launch, for rows of at most 128 16-byte vectors:
+// dx (+ dres when it is not null) and the finished dweight / dbias.  `scratch`: titb_norm_bwd_onepass_scratch(C)
+// floats; `counters`: titb_norm_bwd_onepass_counters() unsigned words, zero before the first launch and left zero by
+// every launch (launches that share them must be ordered on one stream).
+TITB_API int titb_norm_bwd_onepass_ok(long long rows, int C, int dtype, const void* dy, const void* x, const void* w,
+                                      const void* dres, const void* dx);
+TITB_API long long titb_norm_bwd_onepass_scratch(int C);
+TITB_API int titb_norm_bwd_onepass_counters();
+TITB_API int titb_norm_bwd_onepass(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
+                                   const void* dres, void* dx, float* dw, float* db, float* scratch,
+                                   unsigned* counters, long long rows, int C, int dtype, int rms, int accumulate_wgrad,
+                                   cudaStream_t stream);
 
 // ---- activations ----------------------------------------------------------------
 TITB_API int titb_gelu_fwd(const void* x, void* y, long long n, int dtype, cudaStream_t stream);

@@ -73,6 +73,7 @@ colsum_fused_kernel(const T* __restrict__ x, float* __restrict__ scratch, unsign
     const int cc = base + tx * 4;
     float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
     if (c0 + cc < C) {
+#pragma unroll 8
       for (int p = ty; p < parts; p += 8) {
         const float4 t = __ldcg(reinterpret_cast<const float4*>(scratch + (long long)p * C + c0 + cc));
         s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;

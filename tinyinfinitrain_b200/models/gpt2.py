@@ -98,8 +98,10 @@ class Block(nn.Module):
         self.mlp = MLP(config, device=device, dtype=dtype)
 
     def forward(self, x):
-        x = self.attn(self.ln_1(x), residual=x)
-        x = self.mlp(self.ln_2(x), residual=x)
+        h, x = self.ln_1.fork(x)
+        x = self.attn(h, residual=x)
+        h, x = self.ln_2.fork(x)
+        x = self.mlp(h, residual=x)
         return x
 
 

@@ -145,8 +145,10 @@ class TPBlock(nn.Module):
                 tpl._mark_sp(p)
 
     def forward(self, x_s, B: int, T: int):
-        x_s = self.attn(self.ln_1(x_s), B, T, residual_s=x_s)
-        x_s = self.mlp(self.ln_2(x_s), residual_s=x_s)
+        h_s, x_s = self.ln_1.fork(x_s)
+        x_s = self.attn(h_s, B, T, residual_s=x_s)
+        h_s, x_s = self.ln_2.fork(x_s)
+        x_s = self.mlp(h_s, residual_s=x_s)
         return x_s
 
 

@@ -78,6 +78,10 @@ class LayerNorm(Module):
     def forward(self, x):
         return ops.layernorm(x, self.weight, self.bias, self.eps)
 
+    def fork(self, x):
+        """(self(x), x) for a pre-norm residual block: pass the second value to the residual connection."""
+        return ops.layernorm_fork(x, self.weight, self.bias, self.eps)
+
 
 class RMSNorm(Module):
     kType = "RMSNorm"
@@ -90,6 +94,10 @@ class RMSNorm(Module):
 
     def forward(self, x):
         return ops.rmsnorm(x, self.weight, self.eps)
+
+    def fork(self, x):
+        """(self(x), x) for a pre-norm residual block: pass the second value to the residual connection."""
+        return ops.rmsnorm_fork(x, self.weight, self.eps)
 
 
 class CrossEntropyLoss(Module):

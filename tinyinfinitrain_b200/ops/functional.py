@@ -35,6 +35,8 @@ DETERMINISTIC_EMBEDDING_GRAD = os.environ.get("TITB200_DETERMINISTIC", "0") == "
 XENT_ROW_CACHED = os.environ.get("TITB200_XENT_CACHED", "0") == "1"
 # bias gradients with the one-launch column sum (the last CTA of a column strip folds the partial rows)
 COLSUM_FUSED = os.environ.get("TITB200_COLSUM_FUSED", "0") == "1"
+# LayerNorm / RMSNorm backward as one launch (dx, finished dweight / dbias, residual gradient folded in)
+NORM_BWD_ONEPASS = os.environ.get("TITB200_NORM_BWD_ONEPASS", "0") == "1"
 
 _bf16 = torch.bfloat16
 
@@ -250,27 +252,34 @@ def matmul(a, b):
 
 # ------------------------------------------------------------------------------ norms
 class _LayerNormFn(torch.autograd.Function):
+    """fork=True also returns x itself: the caller feeds that alias to the residual connection, and backward then
+    receives the residual gradient as a second argument and adds it inside the norm kernel."""
+
     @staticmethod
-    def forward(ctx, x, w, b, eps):
+    def forward(ctx, x, w, b, eps, fork=False):
         xc = x.contiguous()
         y, mean, rstd = C.layernorm_fwd(xc, w, b, eps)
         ctx.save_for_backward(xc, w, mean, rstd)
-        ctx.w, ctx.b = w, b
-        return y
+        ctx.w, ctx.b, ctx.fork = w, b, fork
+        ctx.set_materialize_grads(False)                 # an unused output arrives as None, not as a zero tensor
+        return (y, x) if fork else y
 
     @staticmethod
-    def backward(ctx, dy):
+    def backward(ctx, dy, dres=None):
         x, w, mean, rstd = ctx.saved_tensors
+        if dy is None:                                   # only the residual alias was used
+            return dres, None, None, None, None
         dy = dy.contiguous()
         wmg, wacc = _grad_target(ctx.w)
         bmg, _ = _grad_target(ctx.b)
         if wmg is not None and bmg is not None:
-            dx, _, _ = C.layernorm_bwd(dy, x, w, mean, rstd, dw=wmg, db=bmg, accumulate=wacc)
+            dx, _, _ = C.layernorm_bwd(dy, x, w, mean, rstd, dw=wmg, db=bmg, accumulate=wacc,
+                                       onepass=NORM_BWD_ONEPASS, dres=dres)
             _grad_done(ctx.w)
             _grad_done(ctx.b)
-            return dx, None, None, None
-        dx, dw, db = C.layernorm_bwd(dy, x, w, mean, rstd)
-        return dx, dw.to(w.dtype), db.to(w.dtype), None
+            return dx, None, None, None, None
+        dx, dw, db = C.layernorm_bwd(dy, x, w, mean, rstd, onepass=NORM_BWD_ONEPASS, dres=dres)
+        return dx, dw.to(w.dtype), db.to(w.dtype), None, None
 
 
 def layernorm(x, weight, bias, eps: float = 1e-5):
@@ -279,26 +288,38 @@ def layernorm(x, weight, bias, eps: float = 1e-5):
     return _LayerNormFn.apply(x, weight, bias, eps)
 
 
+def layernorm_fork(x, weight, bias, eps: float = 1e-5):
+    """(LayerNorm(x), x): use the second value for the residual connection around the normalised branch.  On CUDA with
+    the one-launch backward enabled, the gradient that comes back through the residual is added inside the norm's
+    backward kernel instead of by a separate add."""
+    if not x.is_cuda or not NORM_BWD_ONEPASS:
+        return layernorm(x, weight, bias, eps), x
+    return _LayerNormFn.apply(x, weight, bias, eps, True)
+
+
 class _RMSNormFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, eps):
+    def forward(ctx, x, w, eps, fork=False):
         xc = x.contiguous()
         y, rstd = C.rmsnorm_fwd(xc, w, eps)
         ctx.save_for_backward(xc, w, rstd)
-        ctx.w = w
-        return y
+        ctx.w, ctx.fork = w, fork
+        ctx.set_materialize_grads(False)
+        return (y, x) if fork else y
 
     @staticmethod
-    def backward(ctx, dy):
+    def backward(ctx, dy, dres=None):
         x, w, rstd = ctx.saved_tensors
+        if dy is None:
+            return dres, None, None, None
         dy = dy.contiguous()
         wmg, wacc = _grad_target(ctx.w)
         if wmg is not None:
-            dx, _ = C.rmsnorm_bwd(dy, x, w, rstd, dw=wmg, accumulate=wacc)
+            dx, _ = C.rmsnorm_bwd(dy, x, w, rstd, dw=wmg, accumulate=wacc, onepass=NORM_BWD_ONEPASS, dres=dres)
             _grad_done(ctx.w)
-            return dx, None, None
-        dx, dw = C.rmsnorm_bwd(dy, x, w, rstd)
-        return dx, dw.to(w.dtype), None
+            return dx, None, None, None
+        dx, dw = C.rmsnorm_bwd(dy, x, w, rstd, onepass=NORM_BWD_ONEPASS, dres=dres)
+        return dx, dw.to(w.dtype), None, None
 
 
 def rmsnorm_ref(x, weight, eps):
@@ -310,6 +331,13 @@ def rmsnorm(x, weight, eps: float = 1e-5):
     if not x.is_cuda:
         return rmsnorm_ref(x, weight, eps)
     return _RMSNormFn.apply(x, weight, eps)
+
+
+def rmsnorm_fork(x, weight, eps: float = 1e-5):
+    """(RMSNorm(x), x); see layernorm_fork."""
+    if not x.is_cuda or not NORM_BWD_ONEPASS:
+        return rmsnorm(x, weight, eps), x
+    return _RMSNormFn.apply(x, weight, eps, True)
 
 
 # ------------------------------------------------------------------------ activations

@@ -69,6 +69,8 @@ def main():
     ap.add_argument("--tile_n", type=int, default=0)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no_flush", action="store_true")
+    ap.add_argument("--onepass", action="store_true", help="layernorm_bwd: dx and finished dweight / dbias in one launch")
+    ap.add_argument("--residual", action="store_true", help="layernorm_bwd: add a residual gradient to dx")
     ap.add_argument("--fused", action="store_true", help="colsum: one launch, the last CTA of a column strip folds the partials")
     ap.add_argument("--cached", action="store_true", help="xent: keep each row in shared memory between the two passes")
     a = ap.parse_args()
@@ -122,8 +124,9 @@ def main():
         else:
             y, mean, rstd = C.layernorm_fwd(x, w, b, 1e-5)
             dy = torch.randn_like(x)
-            bytes_ = 3.0 * x.numel() * 2
-            fn = lambda: C.layernorm_bwd(dy, x, w, mean, rstd)
+            bytes_ = (4.0 if a.residual else 3.0) * x.numel() * 2
+            dres = torch.randn_like(x) if a.residual else None
+            fn = lambda: C.layernorm_bwd(dy, x, w, mean, rstd, onepass=a.onepass, dres=dres)
     elif a.kernel == "ag_gemm":
         # X = concat of W shards [M/W, K]; Y = X . B^T, B [N, K]
         M, N, K, W = a.m, a.n, a.k, a.world
