@@ -467,3 +467,36 @@ def test_norm_fork_folds_the_residual_gradient(monkeypatch):
         scale = grads[0][n].abs().max().item() + 1e-6
         assert (grads[0][n] - grads[1][n]).abs().max().item() < 0.05 * scale, n
     _status_ok()
+
+
+@pytest.mark.parametrize("B,T,Hq,Hkv,hd", [(2, 128, 2, 2, 64), (2, 200, 3, 3, 64), (1, 384, 4, 2, 128), (1, 1024, 2, 2, 64),
+                                           (1, 130, 8, 2, 64)])
+def test_attention_backward_with_two_warps_per_score_row(B, T, Hq, Hkv, hd):
+    """Same cases as the four-warp backward test (ragged last block, grouped-query heads, hd 128 with the aliased dQ
+    accumulator); the variant is switched back before the test returns."""
+    torch.manual_seed(13)
+    W = (Hq + 2 * Hkv) * hd
+    qkv = (torch.randn(B, T, W, device=DEV) * 0.7).to(BF)
+    do = torch.randn(B, T, Hq, hd, device=DEV).to(BF)
+    qr = qkv.float().clone().requires_grad_(True)
+    q = qr[..., :Hq * hd].reshape(B, T, Hq, hd)
+    k = qr[..., Hq * hd:(Hq + Hkv) * hd].reshape(B, T, Hkv, hd)
+    v = qr[..., (Hq + Hkv) * hd:].reshape(B, T, Hkv, hd)
+    ops.attention_ref(q, k, v).backward(do.float())
+    grads = []
+    try:
+        for warps in (4, 8):
+            C.attn_bwd_set_warps(warps)
+            qg = qkv.detach().requires_grad_(True)
+            ops.causal_attention_qkv(qg, Hq, Hkv).backward(do)
+            torch.cuda.synchronize()
+            grads.append(qg.grad.float())
+    finally:
+        C.attn_bwd_set_warps(4)
+    _status_ok()
+    scale = qr.grad.abs().max().item()
+    for g in grads:
+        assert (g - qr.grad).abs().max().item() <= 3e-2 * scale + 2e-2
+    # dK and dV do not go through atomics: the two variants must agree to the bit there
+    kv = slice(Hq * hd, W)
+    assert torch.equal(grads[0][..., kv], grads[1][..., kv])

@@ -283,6 +283,9 @@ struct TitbAttnDesc {
 };
 TITB_API int titb_attn_fwd(const TitbAttnDesc* d, cudaStream_t stream);
 TITB_API int titb_attn_bwd(const TitbAttnDesc* d, cudaStream_t stream);
+// Backward kernel variant: 8 = two warps per score row (eight element-wise warps), anything else = four warps.
+// Process-wide; the environment variable TITB200_ATTN_BWD_WARPS=8 sets the initial value.
+TITB_API void titb_attn_bwd_set_warps(int warps);
 
 // ---- gradient-norm clipping (device resident: graph-capturable) -------------------------------------------------
 // Stage 1: per-block partial sums of squares of a flat fp32 buffer (16-byte aligned).  `partials` must hold

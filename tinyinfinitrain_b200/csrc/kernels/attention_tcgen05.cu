@@ -27,6 +27,8 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+
 #include "api.h"
 #include "ptx_sm100.cuh"
 
@@ -309,8 +311,12 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
-template <int HD>
-__global__ void __launch_bounds__(kAttnThreads, 1)
+// EW = 1: four element-wise warps, one score row per thread.  EW = 2: eight element-wise warps, a score row is
+// shared by two warps (warps 2..5 take the first half of the key columns and of the head dimension, warps 6..9 the
+// second half; both sets sit on the same TMEM lane quarter `warp & 3`), which halves the thread phase between the
+// two MMA phases; the per-row statistics (lse, delta) are loaded one iteration ahead.
+template <int HD, int EW>
+__global__ void __launch_bounds__(64 + 128 * EW, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                 const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo, const AttnArgs p) {
   using Cfg = BwdCfg<HD>;
@@ -339,9 +345,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     ptx::mbar_init(kv_full, 1);
     for (int s = 0; s < 2; ++s) { ptx::mbar_init(&qdo_full[s], 1); ptx::mbar_init(&qdo_empty[s], 1); }
     ptx::mbar_init(sdp_full, 1);
-    ptx::mbar_init(pds_full, 4);
+    ptx::mbar_init(pds_full, 4 * EW);
     ptx::mbar_init(dq_full, 1);
-    ptx::mbar_init(dq_free, 4);
+    ptx::mbar_init(dq_free, 4 * EW);
     *abort_flag = (ptx::smem_u32(smem) & 1023u) ? 1u : 0u;
     ptx::mbar_fence_init();
     ptx::tma_prefetch_desc(&tq);
@@ -437,26 +443,45 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     }
   } else {
     const int quad = warp & 3;
+    const int half = (EW == 1) ? 0 : ((warp - 2) >> 2);
     const int row = quad * 32 + lane;
     const uint32_t lane_sel = static_cast<uint32_t>(quad * 32) << 16;
     const float sc = p.scale * kLog2e;
     uint8_t* p_smem = smem + Cfg::kP;
     uint8_t* ds_smem = smem + Cfg::kDS;
     bool ok = true;
+    // (lse, delta) of this thread's query row in iteration `it2`; zeros past the end of the sequence
+    auto load_stats = [&](int it2, float& l, float& d) {
+      const int g2 = it2 / nq, i2 = jb + (it2 - g2 * nq);
+      const int q2 = i2 * kBlk + row;
+      const long long stat2 = (static_cast<long long>(b) * p.Hq + (hk * G + g2)) * p.T + q2;
+      l = q2 < p.T ? p.lse[stat2] : 0.f;
+      d = q2 < p.T ? p.delta[stat2] : 0.f;
+    };
+    float pre_lse = 0.f, pre_dlt = 0.f;
+    if (EW == 2 && niter > 0) load_stats(0, pre_lse, pre_dlt);
     for (int it = 0; it < niter; ++it) {
       const int g = it / nq, i = jb + (it - g * nq);
       const int h = hk * G + g;
       const int q_idx = i * kBlk + row;
       const bool q_valid = q_idx < p.T;
-      const long long stat = (static_cast<long long>(b) * p.Hq + h) * p.T + q_idx;
-      const float lse2 = q_valid ? p.lse[stat] * kLog2e : 0.f;
-      const float dlt = q_valid ? p.delta[stat] : 0.f;
+      float lse2, dlt;
+      if constexpr (EW == 2) {
+        // statistics were requested one iteration ahead; ask for the next iteration's now
+        lse2 = pre_lse * kLog2e;
+        dlt = pre_dlt;
+        if (it + 1 < niter) load_stats(it + 1, pre_lse, pre_dlt);
+      } else {
+        const long long stat = (static_cast<long long>(b) * p.Hq + h) * p.T + q_idx;
+        lse2 = q_valid ? p.lse[stat] * kLog2e : 0.f;
+        dlt = q_valid ? p.delta[stat] : 0.f;
+      }
       if (!ptx::mbar_wait(sdp_full, it & 1, abort_flag)) { ok = false; break; }
       ptx::tc_fence_after_sync();
       const bool diag = (i == jb);
       const int kv0 = jb * kBlk;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = half * (4 / EW); c < (half + 1) * (4 / EW); ++c) {
         uint32_t rs[32], rd[32];
         ptx::tmem_ld32(tmem_base + Cfg::kColS + lane_sel + c * 32, rs);
         ptx::tmem_ld32(tmem_base + Cfg::kColDP + lane_sel + c * 32, rd);
@@ -490,7 +515,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       ptx::tc_fence_after_sync();
       float* dq_row = p.dq_accum + ((static_cast<long long>(b) * p.T + q_idx) * p.Hq + h) * HD;
 #pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int c = half * (HD / 32 / EW); c < (half + 1) * (HD / 32 / EW); ++c) {
         uint32_t r[32];
         ptx::tmem_ld32(tmem_base + Cfg::kColDQ + lane_sel + c * 32, r);
         ptx::tmem_ld_wait();
@@ -517,7 +542,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         const uint32_t col = which == 0 ? Cfg::kColDV : Cfg::kColDK;
         bf16* dst = base + (static_cast<long long>(b) * p.T + kv_idx) * stride + hk * HD;
 #pragma unroll 1
-        for (int c = 0; c < HD / 32; ++c) {
+        for (int c = half * (HD / 32 / EW); c < (half + 1) * (HD / 32 / EW); ++c) {
           uint32_t r[32];
           ptx::tmem_ld32(tmem_base + col + lane_sel + c * 32, r);
           ptx::tmem_ld_wait();
@@ -621,7 +646,13 @@ static int attn_fwd_launch(const TitbAttnDesc* d, cudaStream_t st) {
   return static_cast<int>(cudaGetLastError());
 }
 
-template <int HD>
+// 1 or 2 sets of element-wise warps in the backward kernel; process-wide, read at launch.
+static int g_attn_bwd_ew = [] {
+  const char* e = std::getenv("TITB200_ATTN_BWD_WARPS");
+  return (e && e[0] == '8') ? 2 : 1;
+}();
+
+template <int HD, int EW>
 static int attn_bwd_launch(const TitbAttnDesc* d, cudaStream_t st) {
   using Cfg = BwdCfg<HD>;
   static bool attr_set[64] = {false};
@@ -629,7 +660,7 @@ static int attn_bwd_launch(const TitbAttnDesc* d, cudaStream_t st) {
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) dev = 0;
   if (!attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem);
+    cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel<HD, EW>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem);
     if (e != cudaSuccess) return static_cast<int>(e);
     attr_set[dev] = true;
   }
@@ -655,7 +686,7 @@ static int attn_bwd_launch(const TitbAttnDesc* d, cudaStream_t st) {
   a.dk_stride_t = d->dk_stride_t; a.dv_stride_t = d->dv_stride_t;
   a.status = titb_status_ptr();
   dim3 grid((d->T + kBlk - 1) / kBlk, d->Hkv, d->B);
-  attn_bwd_kernel<HD><<<grid, kAttnThreads, Cfg::kSmem, st>>>(tq, tk, tv, tdo, a);
+  attn_bwd_kernel<HD, EW><<<grid, 64 + 128 * EW, Cfg::kSmem, st>>>(tq, tk, tv, tdo, a);
   const long long bt = static_cast<long long>(d->B) * d->T;
   const int width = d->Hq * HD;
   int cb = static_cast<int>((bt * (width / 8) + 255) / 256);
@@ -675,6 +706,9 @@ TITB_API int titb_attn_fwd(const TitbAttnDesc* d, cudaStream_t stream) {
   return d->hd == 64 ? attn_fwd_launch<64>(d, stream) : attn_fwd_launch<128>(d, stream);
 }
 
+// warps = 8: a score row is shared by two warps in the backward kernel; anything else: the four-warp version.
+TITB_API void titb_attn_bwd_set_warps(int warps) { g_attn_bwd_ew = warps == 8 ? 2 : 1; }
+
 TITB_API int titb_attn_bwd(const TitbAttnDesc* d, cudaStream_t stream) {
   (void)cudaGetLastError();
   if (d->B <= 0 || d->T <= 0) return 0;
@@ -683,5 +717,6 @@ TITB_API int titb_attn_bwd(const TitbAttnDesc* d, cudaStream_t stream) {
   if (!al(d->d_o) || !al(d->dq) || !al(d->dk) || !al(d->dv) || (d->do_stride_t & 7) || (d->dq_stride_t & 7) ||
       (d->dk_stride_t & 7) || (d->dv_stride_t & 7))
     return TITB_ERR_ALIGNMENT;
-  return d->hd == 64 ? attn_bwd_launch<64>(d, stream) : attn_bwd_launch<128>(d, stream);
+  if (g_attn_bwd_ew == 2) return d->hd == 64 ? attn_bwd_launch<64, 2>(d, stream) : attn_bwd_launch<128, 2>(d, stream);
+  return d->hd == 64 ? attn_bwd_launch<64, 1>(d, stream) : attn_bwd_launch<128, 1>(d, stream);
 }

@@ -69,6 +69,7 @@ def main():
     ap.add_argument("--tile_n", type=int, default=0)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no_flush", action="store_true")
+    ap.add_argument("--warps", type=int, default=4, help="attn_bwd: 8 = two warps per score row")
     ap.add_argument("--onepass", action="store_true", help="layernorm_bwd: dx and finished dweight / dbias in one launch")
     ap.add_argument("--residual", action="store_true", help="layernorm_bwd: add a residual gradient to dx")
     ap.add_argument("--fused", action="store_true", help="colsum: one launch, the last CTA of a column strip folds the partials")
@@ -112,6 +113,7 @@ def main():
         else:
             o, lse = C.attn_fwd(q, k, v, scale)
             do = torch.randn_like(o)
+            C.attn_bwd_set_warps(a.warps)
             flops = 2.5 * fwd_flops
             fn = lambda: C.attn_bwd(do, q, k, v, o, lse, scale)
         bytes_ = 2.0 * qkv.numel() * 2
