@@ -205,7 +205,9 @@ def main():
                        "nvls_multimem": bool(getattr(getattr(opt, "gbuf", None), "mc_ptr", 0)) if not library else False,
                        "l2": "per-step working set (activations + weights + optimizer state, >10 GB) exceeds the "
                              "126 MB L2; no explicit flush",
-                       "init": "random N(0,0.02), seed 42", "final_loss": final_loss, "kernel_status": status},
+                       "init": "random N(0,0.02), seed 42", "final_loss": final_loss, "kernel_status": status,
+                       # kernel variants switched on through the environment for this run (empty = defaults)
+                       "switches": {k: v for k, v in sorted(os.environ.items()) if k.startswith("TITB200_")}},
             "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"],
                        "samples": clocks["samples"], "source": clocks["backend"]},
             "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * B * T * 8,
