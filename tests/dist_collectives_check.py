@@ -1,0 +1,99 @@
+"""Multi-GPU check of the standalone symmetric-memory collectives (run under torch.distributed.run, one rank per GPU):
+all-reduce (fp32 and bf16, sum and mean, whole buffer and an aligned sub-range) and all-gather against NCCL, eager and
+captured in a CUDA graph, and plain data parallelism with the symmetric all-reduce against the NCCL one."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from tinyinfinitrain_b200._lib import C  # noqa: E402
+from tinyinfinitrain_b200.parallel import AllReduceOptimizer  # noqa: E402
+from tinyinfinitrain_b200.parallel.collectives import SymmCollective  # noqa: E402
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank)))
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    ok = True
+    for dtype in (torch.float32, torch.bfloat16):
+        c = SymmCollective(1 << 20, dtype, dev)
+        g = torch.Generator(device="cpu").manual_seed(7 + rank)
+        x = torch.randn(c.numel, generator=g).to(dtype).to(dev)
+        for average in (False, True):
+            c.tensor.copy_(x)
+            ref = x.float().clone()
+            dist.all_reduce(ref)
+            if average:
+                ref /= world
+            c.all_reduce_(average=average)
+            torch.cuda.synchronize()
+            tol = 1e-5 if dtype == torch.float32 else 3e-2
+            err = (c.tensor.float() - ref).abs().max().item()
+            ok = ok and err <= tol * max(1.0, ref.abs().max().item())
+        # the result is the same bits on every rank
+        chk = c.tensor.float().clone()
+        dist.broadcast(chk, src=0)
+        ok = ok and torch.equal(chk, c.tensor.float())
+        # sub-range, captured in a graph and replayed with new data
+        per = 16 * world // c.esize
+        off, n = 3 * per, 1000 * per
+        graph = torch.cuda.CUDAGraph()
+        c.tensor.copy_(x)
+        c.all_reduce_(numel=n, offset=off)                     # warm-up outside of the capture
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph):
+            c.all_reduce_(numel=n, offset=off)
+        for it in range(2):
+            y = (x * (it + 2)).to(dtype)
+            c.tensor.copy_(y)
+            graph.replay()
+            torch.cuda.synchronize()
+            ref = y.float()[off:off + n].clone()
+            dist.all_reduce(ref)
+            tol = 1e-5 if dtype == torch.float32 else 3e-2
+            ok = ok and (c.tensor.float()[off:off + n] - ref).abs().max().item() <= tol * max(1.0, ref.abs().max().item())
+            ok = ok and torch.equal(c.tensor[:off], y[:off]) and torch.equal(c.tensor[off + n:], y[off + n:])
+        # all-gather
+        c.tensor.zero_()
+        sl = c.numel // world
+        c.tensor[rank * sl:(rank + 1) * sl] = x[rank * sl:(rank + 1) * sl]
+        c.all_gather_()
+        torch.cuda.synchronize()
+        parts = [torch.empty(sl, dtype=dtype, device=dev) for _ in range(world)]
+        dist.all_gather(parts, x[rank * sl:(rank + 1) * sl].contiguous())
+        ok = ok and torch.equal(c.tensor, torch.cat(parts))
+        print(f"rank {rank}: {dtype} multimem={'yes' if c.buf.mc_ptr else 'no'} ok={ok}", flush=True)
+
+    # plain data parallelism: symmetric all-reduce against NCCL
+    finals = []
+    for comm in ("nccl", "symm"):
+        torch.manual_seed(3)
+        net = torch.nn.Sequential(torch.nn.Linear(256, 512), torch.nn.GELU(), torch.nn.Linear(512, 64)).to(dev).to(torch.bfloat16)
+        opt = AllReduceOptimizer(net.parameters(), lr=1e-2, weight_decay=0.1, comm=comm)
+        for step in range(4):
+            xb = torch.randn(32, 256, generator=torch.Generator().manual_seed(100 * step + rank)).to(dev).to(torch.bfloat16)
+            opt.zero_grad()
+            for p in opt.params:
+                p.grad = None
+            net(xb).float().pow(2).mean().backward()
+            opt.step()
+        torch.cuda.synchronize()
+        finals.append(torch.cat([p.detach().float().flatten() for p in net.parameters()]))
+    e = (finals[0] - finals[1]).abs().max().item()
+    ok = ok and e < 2e-2
+    status = C.status_read(True)
+    ok = ok and status == 0
+    print(f"rank {rank}: data-parallel nccl-vs-symm max|dp|={e:.3e} status={status} ok={ok}", flush=True)
+    t = torch.tensor([1.0 if ok else 0.0], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    dist.destroy_process_group()
+    sys.exit(0 if t.item() == 1.0 else 1)
+
+
+if __name__ == "__main__":
+    main()

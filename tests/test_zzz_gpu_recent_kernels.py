@@ -500,3 +500,44 @@ def test_attention_backward_with_two_warps_per_score_row(B, T, Hq, Hkv, hd):
     # dK and dV do not go through atomics: the two variants must agree to the bit there
     kv = slice(Hq * hd, W)
     assert torch.equal(grads[0][..., kv], grads[1][..., kv])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, BF])
+@pytest.mark.parametrize("world", [2, 8])
+def test_symmetric_collective_kernels_on_one_gpu(dtype, world):
+    """The peer-pointer branch of the all-reduce / all-gather kernels with `world` local buffers standing in for the
+    ranks' copies.  The kernels wait for nothing, so the ranks' launches simply run one after the other."""
+    torch.manual_seed(23)
+    n = 4096 * world + (16 * world // (4 if dtype == torch.float32 else 2)) * 3
+    esize = 4 if dtype == torch.float32 else 2
+    bufs = [torch.randn(n, device=DEV).to(dtype) for _ in range(world)]
+    ptrs = [b.data_ptr() for b in bufs]
+    ref = sum(b.float() for b in bufs) * 0.5
+    for r in range(world):
+        C.symm_allreduce(ptrs, 0, 0, n * esize, 1 if dtype == BF else 0, r, 0.5)
+    torch.cuda.synchronize()
+    tol = 1e-5 if dtype == torch.float32 else 3e-2
+    for b in bufs:
+        assert torch.equal(b, bufs[0])
+        assert (b.float() - ref).abs().max().item() <= tol * max(1.0, ref.abs().max().item())
+    # all-gather of a sub-range that starts 48 bytes into the buffers
+    off, per = 48 // esize, 512
+    bufs = [torch.full((n,), float(r + 1), device=DEV).to(dtype) for r in range(world)]
+    ptrs = [b.data_ptr() for b in bufs]
+    for r in range(world):
+        C.symm_allgather(ptrs, 0, off * esize, per * world * esize, r)
+    torch.cuda.synchronize()
+    want = torch.cat([torch.full((per,), float(r + 1), device=DEV) for r in range(world)]).to(dtype)
+    for r, b in enumerate(bufs):
+        assert torch.equal(b[off:off + per * world], want)
+        assert torch.all(b[:off] == r + 1) and torch.all(b[off + per * world:] == r + 1)
+    _status_ok()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_symmetric_collectives_match_nccl():
+    n = min(torch.cuda.device_count(), 8)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29750 + os.getpid() % 90), os.path.join(HERE, "dist_collectives_check.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]

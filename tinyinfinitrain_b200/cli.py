@@ -196,7 +196,8 @@ def train_main(family: str, argv=None) -> int:
         from .parallel import AllReduceOptimizer        # --zero_stage 0: all-reduce + full Adam on every rank
 
         opt = AllReduceOptimizer(params, lr=args.learning_rate, weight_decay=args.weight_decay, group=mesh.dp_group,
-                                 max_grad_norm=args.max_grad_norm, mp_group=mesh.mp_group, tp_world=tp)
+                                 max_grad_norm=args.max_grad_norm, mp_group=mesh.mp_group, tp_world=tp,
+                                 comm="symm" if os.environ.get("TITB200_SYMM_ALLREDUCE") == "1" else "nccl")
     else:
         opt = tit.optim.MixedPrecisionAdam(params, lr=args.learning_rate, weight_decay=args.weight_decay,
                                            max_grad_norm=args.max_grad_norm, mp_group=mesh.mp_group, tp_world=tp)

@@ -58,6 +58,21 @@ void allreduce_small(const std::vector<int64_t>& buf_ptrs, const Tensor& out, in
                              at::cuda::getCurrentCUDAStream().stream()), "allreduce_small");
 }
 
+// In-place sum (times scale) / gather over the ranks of a byte range of a symmetric buffer; the caller brackets the
+// call with the device barrier.
+void symm_allreduce(const std::vector<int64_t>& buf_ptrs, int64_t mc_ptr, int64_t byte_off, int64_t nbytes, int64_t dtype,
+                    int64_t rank, double scale, int64_t max_blocks) {
+  auto b = to_u64(buf_ptrs);
+  check(titb_symm_allreduce(b.data(), (unsigned long long)mc_ptr, byte_off, nbytes, (int)dtype, (int)b.size(), (int)rank,
+                            (float)scale, (int)max_blocks, at::cuda::getCurrentCUDAStream().stream()), "symm_allreduce");
+}
+void symm_allgather(const std::vector<int64_t>& buf_ptrs, int64_t mc_ptr, int64_t byte_off, int64_t nbytes, int64_t rank,
+                    int64_t max_blocks) {
+  auto b = to_u64(buf_ptrs);
+  check(titb_symm_allgather(b.data(), (unsigned long long)mc_ptr, byte_off, nbytes, (int)b.size(), (int)rank,
+                            (int)max_blocks, at::cuda::getCurrentCUDAStream().stream()), "symm_allgather");
+}
+
 // ---- gradient-norm clipping ---------------------------------------------------------------------------------------
 // Clips a flat fp32 gradient buffer in place to `max_norm` (norm taken of pre_scale * grad); `out` is a device
 // tensor of two floats that receives {norm, coefficient}.  Everything stays on the device.
@@ -120,6 +135,10 @@ void bind_comm(pybind11::module_& m) {
         py::arg("lr"), py::arg("b1"), py::arg("b2"), py::arg("eps"), py::arg("wd"), py::arg("step"),
         py::arg("grad_scale"), py::arg("dev_state") = py::none(), py::arg("max_blocks") = 0);
   m.def("allreduce_small", &allreduce_small);
+  m.def("symm_allreduce", &symm_allreduce, py::arg("buf_ptrs"), py::arg("mc_ptr"), py::arg("byte_off"), py::arg("nbytes"),
+        py::arg("dtype"), py::arg("rank"), py::arg("scale") = 1.0, py::arg("max_blocks") = 0);
+  m.def("symm_allgather", &symm_allgather, py::arg("buf_ptrs"), py::arg("mc_ptr"), py::arg("byte_off"), py::arg("nbytes"),
+        py::arg("rank"), py::arg("max_blocks") = 0);
   m.def("clip_grad_norm_", &clip_grad_norm_);
   m.def("rs_grad_sumsq", &rs_grad_sumsq);
   m.def("clip_coef_from_totals", &clip_coef_from_totals);

@@ -328,3 +328,11 @@ struct TitbRsAdamDesc {
 TITB_API int titb_rs_adam_ag(const TitbRsAdamDesc* d, cudaStream_t stream);
 TITB_API int titb_allreduce_small(const unsigned long long* buf_ptrs, float* out, int n, int world, int op,
                                   cudaStream_t stream);
+
+// Standalone in-place collectives over a symmetric buffer (collectives.cu).  dtype: 0 fp32, 1 bf16.  byte_off and
+// nbytes / world are multiples of 16.  No waits inside: the caller runs titb_comm_barrier before and after.
+TITB_API int titb_symm_allreduce(const unsigned long long* buf_ptrs, unsigned long long mc_ptr, long long byte_off,
+                                 long long nbytes, int dtype, int world, int rank, float scale, int max_blocks,
+                                 cudaStream_t stream);
+TITB_API int titb_symm_allgather(const unsigned long long* buf_ptrs, unsigned long long mc_ptr, long long byte_off,
+                                 long long nbytes, int world, int rank, int max_blocks, cudaStream_t stream);

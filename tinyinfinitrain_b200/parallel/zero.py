@@ -353,12 +353,25 @@ class AllReduceOptimizer:
     :class:`DistributedOptimizer`, whose fused kernel is the product."""
 
     def __init__(self, params, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.0,
-                 group: Optional[dist.ProcessGroup] = None, max_grad_norm: float = 0.0, mp_group=None, tp_world: int = 1):
-        from ..optim.optimizers import MixedPrecisionAdam
+                 group: Optional[dist.ProcessGroup] = None, max_grad_norm: float = 0.0, mp_group=None, tp_world: int = 1,
+                 comm: str = "nccl"):
+        """``comm="symm"``: the gradient buffer is allocated in symmetric memory and summed by this package's own
+        two-shot all-reduce kernel (multimem through NVSwitch, or peer loads) instead of NCCL."""
+        from ..optim.optimizers import FlatParams, MixedPrecisionAdam
 
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
-        self.inner = MixedPrecisionAdam(params, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
+        plist = [p for p in params]
+        self.coll = None
+        flat = plist
+        if comm == "symm" and plist and plist[0].is_cuda:
+            from .collectives import SymmCollective
+
+            align = 128 * self.world
+            total = DistributedOptimizer._flat_size(plist, align)
+            self.coll = SymmCollective(total, torch.float32, plist[0].device, self.group, channel=0)
+            flat = FlatParams(plist, align_total=align, grad_buffer=self.coll.tensor)
+        self.inner = MixedPrecisionAdam(flat, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
                                         grad_scale=1.0 / self.world, max_grad_norm=max_grad_norm,
                                         mp_group=mp_group,
                                         tp_world=tp_world)
@@ -383,7 +396,10 @@ class AllReduceOptimizer:
     @torch.no_grad()
     def step(self) -> None:
         self.flat.finish_unwritten()
-        dist.all_reduce(self.flat.grad, group=self.group)                 # sum; the Adam kernel applies 1 / world
+        if self.coll is not None:
+            self.coll.all_reduce_()                                       # own kernel, in place on the symmetric buffer
+        else:
+            dist.all_reduce(self.flat.grad, group=self.group)             # sum; the Adam kernel applies 1 / world
         self.inner.step()
 
     Step = step
