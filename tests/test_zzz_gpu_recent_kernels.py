@@ -541,3 +541,24 @@ def test_symmetric_collectives_match_nccl():
            "127.0.0.1", "--master-port", str(29750 + os.getpid() % 90), os.path.join(HERE, "dist_collectives_check.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_point_to_point_flag_signal_then_wait_and_bounded_timeout():
+    """Signal first, then wait: the two kernels run one after the other on one stream, nothing waits for a kernel
+    that has not been launched.  Then a wait for a value that nobody publishes runs out after 0.25 s, leaves the
+    peer-timeout code in the status word and the context usable."""
+    import time
+    assert C.status_read(True) == 0
+    word = torch.zeros(4, dtype=torch.int32, device=DEV)
+    C.symm_signal(word.data_ptr() + 4, 7)
+    C.symm_wait(word.data_ptr() + 4, 7, 1.0)
+    C.symm_wait(word.data_ptr() + 4, 5, 1.0)             # already passed
+    torch.cuda.synchronize()
+    assert word.tolist() == [0, 7, 0, 0] and C.status_read(True) == 0
+    t0 = time.time()
+    C.symm_wait(word.data_ptr() + 8, 1, 0.25)            # nothing sets word[2]
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 5.0
+    assert C.status_read(True) == 2                      # peer timeout, cleared by the read
+    x = torch.randn(256, 256, device=DEV).to(BF)
+    assert torch.isfinite(C.gemm(x, x)[0].float()).all() and C.status_read(True) == 0

@@ -73,6 +73,15 @@ void symm_allgather(const std::vector<int64_t>& buf_ptrs, int64_t mc_ptr, int64_
                             (int)max_blocks, at::cuda::getCurrentCUDAStream().stream()), "symm_allgather");
 }
 
+void symm_signal(int64_t remote_word, int64_t value) {
+  check(titb_symm_signal((unsigned long long)remote_word, (unsigned int)value, at::cuda::getCurrentCUDAStream().stream()),
+        "symm_signal");
+}
+void symm_wait(int64_t local_word, int64_t value, double timeout_s) {
+  check(titb_symm_wait((unsigned long long)local_word, (unsigned int)value, timeout_s,
+                       at::cuda::getCurrentCUDAStream().stream()), "symm_wait");
+}
+
 // ---- gradient-norm clipping ---------------------------------------------------------------------------------------
 // Clips a flat fp32 gradient buffer in place to `max_norm` (norm taken of pre_scale * grad); `out` is a device
 // tensor of two floats that receives {norm, coefficient}.  Everything stays on the device.
@@ -137,6 +146,8 @@ void bind_comm(pybind11::module_& m) {
   m.def("allreduce_small", &allreduce_small);
   m.def("symm_allreduce", &symm_allreduce, py::arg("buf_ptrs"), py::arg("mc_ptr"), py::arg("byte_off"), py::arg("nbytes"),
         py::arg("dtype"), py::arg("rank"), py::arg("scale") = 1.0, py::arg("max_blocks") = 0);
+  m.def("symm_signal", &symm_signal);
+  m.def("symm_wait", &symm_wait, py::arg("local_word"), py::arg("value"), py::arg("timeout_s") = 2.0);
   m.def("symm_allgather", &symm_allgather, py::arg("buf_ptrs"), py::arg("mc_ptr"), py::arg("byte_off"), py::arg("nbytes"),
         py::arg("rank"), py::arg("max_blocks") = 0);
   m.def("clip_grad_norm_", &clip_grad_norm_);

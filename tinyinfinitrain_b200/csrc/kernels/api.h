@@ -336,3 +336,8 @@ TITB_API int titb_symm_allreduce(const unsigned long long* buf_ptrs, unsigned lo
                                  cudaStream_t stream);
 TITB_API int titb_symm_allgather(const unsigned long long* buf_ptrs, unsigned long long mc_ptr, long long byte_off,
                                  long long nbytes, int world, int rank, int max_blocks, cudaStream_t stream);
+// Point-to-point flag in symmetric memory: signal stores `value` with release semantics after all earlier work of
+// the stream; wait blocks the stream until the word has reached `value` or `timeout_s` has passed (then the status
+// word reads kStatusPeerTimeout and the stream continues).
+TITB_API int titb_symm_signal(unsigned long long remote_word, unsigned int value, cudaStream_t stream);
+TITB_API int titb_symm_wait(unsigned long long local_word, unsigned int value, double timeout_s, cudaStream_t stream);

@@ -7,9 +7,10 @@
 //    otherwise a rotated loop of peer loads -- scales the sum and writes it into every rank's copy (multimem.st or
 //    peer stores).  In place is safe: slice r is read by rank r only.
 //  * all-gather: rank r writes its own slice of its local copy into every rank's copy.
+//  * signal / wait: a point-to-point flag with a bounded wait (producer / consumer hand-offs between two ranks).
 //
-// Neither kernel waits for anything: the caller brackets them with the device barrier (all inputs written before,
-// all outputs landed after), exactly as the ZeRO-1 step does.  The reference has no collectives
+// The two collective kernels wait for nothing: the caller brackets them with the device barrier (all inputs
+// written before, all outputs landed after), exactly as the ZeRO-1 step does.  The reference has no collectives
 // (infini_train/src/device.cc:11-17 enforces a single device).
 #include "api.h"
 #include "common.cuh"
@@ -127,6 +128,29 @@ __global__ void __launch_bounds__(256) allgather_kernel(const AllGatherArgs a) {
   }
 }
 
+// Point-to-point flag: the producer publishes `value` in a 32-bit word of the consumer's memory after everything it
+// wrote before; the consumer waits until the word has reached `value` (values only grow, compared as a signed
+// difference so that they may wrap).  The wait is bounded: when the budget runs out the kernel records
+// kStatusPeerTimeout and returns, and the stream carries on.
+__global__ void signal_kernel(uint32_t* remote_word, uint32_t value) {
+  __threadfence_system();
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote_word), "r"(value) : "memory");
+}
+__global__ void wait_kernel(const uint32_t* local_word, uint32_t value, long long budget_cycles, int* status) {
+  const long long t0 = clock64();
+  for (;;) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(local_word) : "memory");
+    if (static_cast<int32_t>(v - value) >= 0) break;
+    __nanosleep(64);
+    if (clock64() - t0 > budget_cycles) {
+      atomicExch(status, kStatusPeerTimeout);
+      break;
+    }
+  }
+  __threadfence_system();
+}
+
 static int coll_blocks(long long vecs, int max_blocks) {
   long long b = (vecs + 255) / 256;
   const int cap = max_blocks > 0 ? max_blocks : 148 * 2;
@@ -175,5 +199,24 @@ TITB_API int titb_symm_allgather(const unsigned long long* buf_ptrs, unsigned lo
   a.slice_off = byte_off / 16 + a.slice_vecs * rank;
   a.world = world; a.rank = rank;
   allgather_kernel<<<coll_blocks(a.slice_vecs, max_blocks), 256, 0, st>>>(a);
+  return (int)cudaGetLastError();
+}
+
+// Producer side of a flag: after all earlier work of the stream, store `value` (release, system scope) into the
+// 32-bit word at `remote_word` (an address in a peer's symmetric memory as mapped on this GPU, or local memory).
+TITB_API int titb_symm_signal(unsigned long long remote_word, unsigned int value, cudaStream_t st) {
+  (void)cudaGetLastError();
+  if (!remote_word || (remote_word & 3)) return TITB_ERR_SHAPE;
+  signal_kernel<<<1, 1, 0, st>>>(reinterpret_cast<uint32_t*>(remote_word), value);
+  return (int)cudaGetLastError();
+}
+// Consumer side: the stream waits until the word at `local_word` has reached `value`, at most `timeout_s` seconds;
+// on expiry the library status word is set to the peer-timeout code and the stream continues.
+TITB_API int titb_symm_wait(unsigned long long local_word, unsigned int value, double timeout_s, cudaStream_t st) {
+  (void)cudaGetLastError();
+  if (!local_word || (local_word & 3)) return TITB_ERR_SHAPE;
+  int* status = titb_status_ptr();
+  if (!status) return (int)cudaErrorMemoryAllocation;
+  wait_kernel<<<1, 1, 0, st>>>(reinterpret_cast<const uint32_t*>(local_word), value, (long long)(timeout_s * 1.9e9), status);
   return (int)cudaGetLastError();
 }

@@ -103,3 +103,35 @@ class SymmCollective:
         C.symm_allgather(self.buf.ptrs, self.buf.mc_ptr, offset * self.esize, n * self.esize, self.rank, max_blocks)
         self.barrier()
         return view
+
+
+class SymmFlag:
+    """Point-to-point flags in the signal pads of a symmetric buffer: ``signal(peer)`` bumps this rank's counter for
+    ``peer`` and publishes it in the peer's pad after all earlier work of the current stream; ``wait(peer)`` makes the
+    current stream wait (at most ``timeout_s``; expiry sets the library status word, the stream carries on) until
+    ``peer``'s next signal has arrived.  Slot layout: ``[channel][source rank]`` 32-bit words, the same pads the barrier
+    uses, so give flags a channel of their own (the barrier of ``SymmCollective`` uses channel 1, ZeRO-1 channel 0)."""
+
+    SLOTS_PER_CHANNEL = 16
+
+    def __init__(self, buf: SymmetricBuffer, channel: int = 2, timeout_s: float = 2.0):
+        if not 0 <= channel < 8:
+            raise ValueError("SymmFlag: channel 0..7")
+        self.buf, self.channel, self.timeout_s = buf, channel, timeout_s
+        self.sent = [0] * buf.world
+        self.seen = [0] * buf.world
+
+    def _word(self, pad_owner: int, source: int) -> int:
+        return self.buf.pad_ptrs[pad_owner] + 4 * (self.channel * self.SLOTS_PER_CHANNEL + source)
+
+    def signal(self, peer: int) -> None:
+        from .._lib import C
+
+        self.sent[peer] += 1
+        C.symm_signal(self._word(peer, self.buf.rank), self.sent[peer] & 0xFFFFFFFF)
+
+    def wait(self, peer: int) -> None:
+        from .._lib import C
+
+        self.seen[peer] += 1
+        C.symm_wait(self._word(self.buf.rank, peer), self.seen[peer] & 0xFFFFFFFF, self.timeout_s)
