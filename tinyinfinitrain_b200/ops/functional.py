@@ -285,7 +285,7 @@ class _LayerNormFn(torch.autograd.Function):
 def layernorm(x, weight, bias, eps: float = 1e-5):
     if not x.is_cuda:
         return F.layer_norm(x, (x.shape[-1],), weight, bias, eps)
-    return _LayerNormFn.apply(x, weight, bias, eps)
+    return _LayerNormFn.apply(x, weight, bias, eps, False)
 
 
 def layernorm_fork(x, weight, bias, eps: float = 1e-5):
@@ -330,7 +330,7 @@ def rmsnorm_ref(x, weight, eps):
 def rmsnorm(x, weight, eps: float = 1e-5):
     if not x.is_cuda:
         return rmsnorm_ref(x, weight, eps)
-    return _RMSNormFn.apply(x, weight, eps)
+    return _RMSNormFn.apply(x, weight, eps, False)
 
 
 def rmsnorm_fork(x, weight, eps: float = 1e-5):

@@ -107,13 +107,17 @@ class ClockSampler:
                 self._nvml = pynvml
             n = self._nvml
             n.nvmlInit()
+            self._handle = None
             if self.uuid:
                 u = self.uuid if str(self.uuid).startswith("GPU-") else f"GPU-{self.uuid}"
                 try:
-                    self._handle = n.nvmlDeviceGetHandleByUUID(u)
-                except TypeError:  # bindings that want bytes
-                    self._handle = n.nvmlDeviceGetHandleByUUID(u.encode())
-            else:
+                    try:
+                        self._handle = n.nvmlDeviceGetHandleByUUID(u)
+                    except TypeError:  # bindings that want bytes
+                        self._handle = n.nvmlDeviceGetHandleByUUID(u.encode())
+                except Exception:  # noqa: BLE001 - a UUID string NVML does not accept: fall back to the index
+                    self._handle = None
+            if self._handle is None:
                 self._handle = n.nvmlDeviceGetHandleByIndex(self.index)
             self._max = int(n.nvmlDeviceGetMaxClockInfo(self._handle, n.NVML_CLOCK_SM))
             self._read_nvml()  # fail here rather than in the thread
