@@ -4,6 +4,7 @@
     build [--cpp] [-v]       compile the CUDA / C++ extensions in-tree (and the stand-alone C++ library with --cpp)
     gpt2 | llama3 [flags]    the training entry points (same flags as examples/gpt2/main.py, examples/llama3/main.py)
     kernel-bench [args]      utils.kernel_bench        fused-bench [args]   utils.fused_bench (under torchrun)
+    plan [flags]             per-GPU memory plan of a model + parallel layout (utils.memory_plan)
 """
 from __future__ import annotations
 
@@ -72,6 +73,10 @@ def main(argv=None) -> int:
 
         sys.argv = [f"tinyinfinitrain_b200 {cmd}"] + rest
         return train_main(cmd)
+    if cmd == "plan":
+        from .utils import memory_plan
+
+        return memory_plan.main(rest)
     if cmd in ("kernel-bench", "fused-bench"):
         from .utils import fused_bench, kernel_bench
 
