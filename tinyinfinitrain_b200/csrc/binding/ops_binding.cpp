@@ -203,7 +203,8 @@ static unsigned* ticket_counters(const Tensor& like, int words) {
   constexpr int kSlots = 64, kSlotWords = 256;
   TORCH_CHECK(words <= kSlotWords, "titb200: too many ticket counters for one launch");
   static std::mutex mu;
-  static std::map<int, Tensor> table;
+  // never destroyed: a static tensor would be released after the CUDA context at process exit
+  static auto& table = *new std::map<int, Tensor>();
   std::lock_guard<std::mutex> lock(mu);
   const int dev = (int)like.get_device();
   auto it = table.find(dev);
