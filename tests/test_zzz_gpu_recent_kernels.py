@@ -562,3 +562,35 @@ def test_point_to_point_flag_signal_then_wait_and_bounded_timeout():
     assert C.status_read(True) == 2                      # peer timeout, cleared by the read
     x = torch.randn(256, 256, device=DEV).to(BF)
     assert torch.isfinite(C.gemm(x, x)[0].float()).all() and C.status_read(True) == 0
+
+
+@pytest.mark.parametrize("world,npr,M,K,bias", [(2, 128, 300, 264, False), (4, 256, 1024, 768, True), (8, 128, 520, 64, True),
+                                              (1, 384, 128, 128, False)])
+def test_parameter_gather_gemm_on_one_gpu(world, npr, M, K, bias):
+    """Collective mode 3 with `world` local buffers standing in for the ranks' copies of the weight: every launch
+    plays one rank, owns `npr` rows and has NaN everywhere else, so an output without NaN proves that every
+    chunk was fetched from its owner before the GEMM read it (helper and GEMM CTAs are in the same launch)."""
+    torch.manual_seed(29)
+    N = npr * world
+    Wt = (torch.randn(N, K, device=DEV) * 0.2).to(BF)
+    x = torch.randn(M, K, device=DEV).to(BF)
+    b = torch.randn(N, device=DEV).to(BF) if bias else None
+    ref = x.float() @ Wt.float().t() + (b.float() if bias else 0.0)
+    copies = []
+    for r in range(world):
+        c = torch.full((N, K), float("nan"), device=DEV, dtype=BF)
+        c[r * npr:(r + 1) * npr] = Wt[r * npr:(r + 1) * npr]
+        copies.append(c)
+    ptrs = [copies[r].data_ptr() + r * npr * K * 2 for r in range(world)]
+    for r in range(world):
+        y = C.gemm_param_gather(x, copies[r], ptrs, r, epilogue=ops.EPI_BIAS if bias else ops.EPI_NONE, bias=b)[0]
+        torch.cuda.synchronize()
+        assert torch.isfinite(y.float()).all(), f"rank {r}: a chunk was read before it arrived"
+        assert torch.allclose(y.float(), ref, atol=6e-2, rtol=2e-2)
+        assert torch.equal(copies[r], Wt)                  # the local copy is complete afterwards
+        # later ranks must still find NaN-free *owned* rows in the earlier ranks' copies: restore the stale state
+        if r + 1 < world:
+            keep = copies[r][r * npr:(r + 1) * npr].clone()
+            copies[r].fill_(float("nan"))
+            copies[r][r * npr:(r + 1) * npr] = keep
+    _status_ok()

@@ -138,6 +138,42 @@ std::vector<Tensor> gemm_ag(const std::vector<int64_t>& peer_ptrs, int64_t rank,
   return {out, X};
 }
 
+// Parameter all-gather -> GEMM.  `w`: this rank's full-size [N, K] copy of the weight (rows it does not own are
+// overwritten by the kernel); `peer_ptrs[r]`: address of the first row rank r owns, in r's memory.  Returns
+// {Y [M, N] (, pre-activation)}.
+std::vector<Tensor> gemm_param_gather(const Tensor& x, const Tensor& w, const std::vector<int64_t>& peer_ptrs, int64_t rank,
+                                      int64_t epilogue, const optional<Tensor>& bias, const optional<Tensor>& aux_in,
+                                      bool want_aux_out, int64_t helper_ctas, int64_t tile_n) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1);
+  TORCH_CHECK(w.is_cuda() && w.scalar_type() == at::kBFloat16 && w.dim() == 2 && w.is_contiguous());
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t world = (int64_t)peer_ptrs.size(), M = x.size(0), K = x.size(1), N = w.size(0);
+  TORCH_CHECK(w.size(1) == K, "titb200 gemm_param_gather: reduction sizes differ");
+  TORCH_CHECK(world >= 1 && N % (128 * world) == 0, "titb200 gemm_param_gather: weight rows must split into 128-row chunks per rank");
+  Tensor flags = at::empty({N / 128 + 1}, x.options().dtype(at::kInt));
+  Tensor out = at::empty({M, N}, x.options());
+  Tensor aux_out;
+  if (want_aux_out) aux_out = at::empty({M, N}, x.options());
+  std::vector<unsigned long long> pp(peer_ptrs.begin(), peer_ptrs.end());
+  TitbGemmColl c{};
+  c.mode = 3; c.world = (int)world; c.rank = (int)rank; c.helper_ctas = (int)helper_ctas;
+  c.rows_per_rank = (int)(N / world); c.peer_ptrs = pp.data(); c.gathered = w.data_ptr(); c.flags = flags.data_ptr();
+  TitbGemmDesc d{};
+  d.a = x.data_ptr(); d.b = w.data_ptr(); d.out = out.data_ptr();
+  d.M = (int)M; d.N = (int)N; d.K = (int)K; d.a_mn_major = 0; d.b_mn_major = 0;
+  d.lda = x.stride(0); d.ldb = K; d.ldo = N; d.epilogue = (int)epilogue; d.bias = opt_ptr(bias);
+  if (aux_in.has_value() && aux_in->defined()) {
+    TORCH_CHECK(aux_in->dim() == 2 && aux_in->size(0) == M && aux_in->size(1) == N && aux_in->stride(1) == 1);
+    d.aux_in = aux_in->data_ptr(); d.ld_aux_in = aux_in->stride(0);
+  }
+  if (want_aux_out) { d.aux_out = aux_out.data_ptr(); d.ld_aux_out = N; }
+  d.splits = 1; d.tile_n = (int)tile_n; d.coll = &c;
+  if (d.tile_n == 0) d.tile_n = (N / world) % 256 == 0 ? 256 : 128;   // a B tile never straddles two owners
+  CHECK_RC(titb_gemm_param_gather_bf16(&d, cur_stream()), "gemm_param_gather");
+  if (want_aux_out) return {out, aux_out};
+  return {out};
+}
+
 // GEMM -> reduce-scatter.  `recv_ptrs`: every rank's receive buffer bf16 [world][Ms][N]; `cnt_ptrs`:
 // every rank's uint32 [Ms/128] counters.  Returns this rank's [Ms, N] rows of sum_r (a_r . b_r^T).
 Tensor gemm_rs(const Tensor& a, const Tensor& b, bool b_mn, const std::vector<int64_t>& recv_ptrs,
@@ -734,6 +770,9 @@ PYBIND11_MODULE(_C, m) {
   m.def("gemm_ag", &gemm_ag, py::arg("peer_ptrs"), py::arg("rank"), py::arg("rows_per_rank"), py::arg("K"),
         py::arg("b"), py::arg("b_mn") = false, py::arg("epilogue") = 0, py::arg("bias") = py::none(),
         py::arg("want_aux_out") = false, py::arg("helper_ctas") = 16);
+  m.def("gemm_param_gather", &gemm_param_gather, py::arg("x"), py::arg("w"), py::arg("peer_ptrs"), py::arg("rank"),
+        py::arg("epilogue") = 0, py::arg("bias") = py::none(), py::arg("aux_in") = py::none(),
+        py::arg("want_aux_out") = false, py::arg("helper_ctas") = 8, py::arg("tile_n") = 0);
   m.def("gemm_rs", &gemm_rs, py::arg("a"), py::arg("b"), py::arg("b_mn"), py::arg("recv_ptrs"), py::arg("cnt_ptrs"),
         py::arg("rank"), py::arg("bias") = py::none(), py::arg("residual") = py::none(), py::arg("helper_ctas") = 8);
   m.def("reduce_dim", &reduce_dim, py::arg("x"), py::arg("op"), py::arg("dim"), py::arg("keepdim") = false);

@@ -86,6 +86,12 @@ struct TitbGemmDesc {
   const TitbGemmColl* coll;  // optional fused collective, or null
 };
 TITB_API int titb_gemm_bf16(const TitbGemmDesc* d, cudaStream_t stream);
+// Same descriptor, collective mode 3 only (gemm_param_gather.cu): the B operand is a weight [N, K] (K-major,
+// contiguous rows) whose rows are sharded over `world` ranks, rows_per_rank each (a multiple of 128).  `b` and
+// `coll->gathered` are this rank's full-size copy, `coll->peer_ptrs[r]` the first row rank r owns, in r's memory
+// as mapped on this GPU (for r == rank it may alias the local copy: then nothing is moved), `coll->flags` N / 128
+// uint32 words of scratch.  The caller orders the launch after the owners' last writes (device barrier).
+TITB_API int titb_gemm_param_gather_bf16(const TitbGemmDesc* d, cudaStream_t stream);
 // Picks the split-K factor the heuristic would use (so callers can size the workspace).
 TITB_API int titb_gemm_pick_splits(int M, int N, int K);
 // Switches the shared-memory-staged TMA store epilogue of bf16 outputs on (default) or off (A/B timing).

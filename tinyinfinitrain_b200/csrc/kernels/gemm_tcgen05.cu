@@ -20,6 +20,15 @@
 #include "api.h"
 #include "ptx_sm100.cuh"
 
+// This file is compiled twice.  On its own it is the GEMM every training step uses.  gemm_param_gather.cu defines
+// TITB_GEMM_PARAM_GATHER (and renames the namespace) before including it: that second copy adds collective mode 3,
+// the weight all-gather fused into the consuming GEMM, without changing one token of the first.
+#ifdef TITB_GEMM_PARAM_GATHER
+#define TITB_GEMM_ENTRY titb_gemm_param_gather_bf16
+#else
+#define TITB_GEMM_ENTRY titb_gemm_bf16
+#endif
+
 namespace titb {
 
 constexpr int kBM = 128;
@@ -36,6 +45,14 @@ constexpr int kGemmThreads = 192;
 //    receive buffer of the rank that owns those rows (peer stores over NVLink) and bumps a
 //    counter there; the first `helper_ctas` CTAs of the owner wait per 128-row chunk for all
 //    partial tiles, sum the `world` slots (+bias +residual) and write the output shard.
+#ifdef TITB_GEMM_PARAM_GATHER
+//  mode 3, parameter all-gather -> GEMM: the B operand (a weight [N, K], K-major) is sharded by rows over the
+//    data-parallel ranks.  `gathered` is this rank's full-size copy of the weight (the tensor map of B points at
+//    it), `peers[r]` the rows rank r owns, in r's memory.  The first `helper_ctas` CTAs pull 128-row chunks from
+//    their owners (plain loads over NVLink; the local shard is already in place when peers[rank] aliases it) and
+//    raise a flag per chunk; the GEMM CTAs visit n-blocks shard by shard, local shard first, and their TMA
+//    producer waits for the chunks under the B tile it is about to load.  rows_per_rank counts weight rows.
+#endif
 struct CollArgs {
   int mode, world, rank, helper_ctas, rows_per_rank;
   void* peers[16];      // mode 1: shard bases bf16 [Ms, K]; mode 2: receive buffers bf16 [world][Ms][N]
@@ -231,6 +248,12 @@ __device__ __forceinline__ TileCoord tile_coord(const GemmArgs& p, int tile, int
   if (p.coll.mode == 0) {
     t.mblk = mn % tiles_m;
     nblk = mn / tiles_m;
+#ifdef TITB_GEMM_PARAM_GATHER
+  } else if (p.coll.mode == 3) {
+    // n-blocks shard by shard, starting with the rows this rank owns; all m-blocks of an n-block back to back
+    t.mblk = mn % tiles_m;
+    nblk = (mn / tiles_m + (p.coll.rank * p.coll.rows_per_rank) / bn) % tiles_n;
+#endif
   } else {
     // m-blocks are visited shard by shard: all-gather starts with the local shard (already here),
     // reduce-scatter with the next rank's rows so that remote partials leave early.
@@ -298,6 +321,34 @@ __device__ void ag_copy_role(const GemmArgs& p) {
   }
 }
 
+#ifdef TITB_GEMM_PARAM_GATHER
+// mode 3 helper CTA: pull 128-row chunks of the weight from the ranks that own them into the local full copy.
+__device__ void param_gather_role(const GemmArgs& p) {
+  const CollArgs& c = p.coll;
+  const int nchunks = p.N / kBM, cpr = c.rows_per_rank / kBM;
+  const long long vec_per_chunk = static_cast<long long>(kBM) * p.K / 8;  // 16-byte units
+  for (int pos = blockIdx.x; pos < nchunks; pos += c.helper_ctas) {
+    const int chunk = (pos + c.rank * cpr) % nchunks;
+    const int src_rank = chunk / cpr;
+    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const bf16*>(c.peers[src_rank]) +
+                                                      static_cast<long long>(chunk - src_rank * cpr) * kBM * p.K);
+    uint4* dst = reinterpret_cast<uint4*>(c.gathered + static_cast<long long>(chunk) * kBM * p.K);
+    if (src != dst) {   // the owner's rows of the local copy are the authoritative ones: nothing to move
+      long long i = threadIdx.x;
+      for (; i + 3 * kGemmThreads < vec_per_chunk; i += 4 * kGemmThreads) {
+        const uint4 v0 = src[i], v1 = src[i + kGemmThreads], v2 = src[i + 2 * kGemmThreads], v3 = src[i + 3 * kGemmThreads];
+        dst[i] = v0; dst[i + kGemmThreads] = v1; dst[i + 2 * kGemmThreads] = v2; dst[i + 3 * kGemmThreads] = v3;
+      }
+      for (; i < vec_per_chunk; i += kGemmThreads) dst[i] = src[i];
+      fence_proxy_async_all();  // these generic-proxy writes are read by TMA (async proxy) below
+      __threadfence();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) st_release_gpu_u32(c.flags + chunk, 1u);
+  }
+}
+#endif
+
 // mode 2 helper CTA: sum the `world` partial slots of this rank's row chunks as they complete.
 __device__ void rs_reduce_role(const GemmArgs& p, int tiles_n) {
   const CollArgs& c = p.coll;
@@ -361,6 +412,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   const int helpers = p.coll.mode ? p.coll.helper_ctas : 0;
   if (static_cast<int>(blockIdx.x) < helpers) {
     if (p.coll.mode == 1) ag_copy_role(p);
+#ifdef TITB_GEMM_PARAM_GATHER
+    else if (p.coll.mode == 3) param_gather_role(p);
+#endif
     else rs_reduce_role(p, (p.N + BN - 1) / BN);
     return;
   }
@@ -421,6 +475,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       uint32_t phase = 0;
       bool ok = true;
       int ready_mblk = -1;
+#ifdef TITB_GEMM_PARAM_GATHER
+      int ready_n0 = -1;
+#endif
       for (int tile = cta; tile < num_tiles && ok; tile += ncta) {
         const TileCoord tc = tile_coord(p, tile, tiles_m, tiles_n, BN);
         const int split = tc.split, m0 = tc.m0, n0 = tc.n0;
@@ -437,6 +494,22 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
           fence_proxy_async_all();
           ready_mblk = tc.mblk;
         }
+#ifdef TITB_GEMM_PARAM_GATHER
+        if (p.coll.mode == 3 && n0 != ready_n0) {
+          // every 128-row chunk of the weight under this B tile must have landed in the local copy
+          const int c_lo = n0 / kBM, c_hi = (min(n0 + BN, p.N) - 1) / kBM;
+          for (int c = c_lo; c <= c_hi && ok; ++c) {
+            if (!wait_flag_ge<false>(p.coll.flags + c, 1u)) {
+              *abort_flag = 1u;
+              atomicExch(p.status, kStatusPeerTimeout);
+              ok = false;
+            }
+          }
+          if (!ok) break;
+          fence_proxy_async_all();
+          ready_n0 = n0;
+        }
+#endif
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!ptx::mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
           ptx::mbar_expect_tx(&full[stage], kABytes + kBBytes);
@@ -835,6 +908,7 @@ static int pick_tile_n(int M, int N, int splits) {
 
 using namespace titb;
 
+#ifndef TITB_GEMM_PARAM_GATHER
 static int* g_status_dev[64] = {nullptr};
 
 TITB_API int* titb_status_ptr(void) {
@@ -872,6 +946,7 @@ TITB_API int titb_gemm_pick_splits(int M, int N, int K) {
   while (s > 1 && kb / s < 8) --s;
   return s < 1 ? 1 : (s > 16 ? 16 : s);
 }
+#endif  // !TITB_GEMM_PARAM_GATHER
 
 template <int BN>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tout, const CUtensorMap& taux,
@@ -895,7 +970,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
   return static_cast<int>(cudaGetLastError());
 }
 
-TITB_API int titb_gemm_bf16(const TitbGemmDesc* d, cudaStream_t stream) {
+TITB_API int TITB_GEMM_ENTRY(const TitbGemmDesc* d, cudaStream_t stream) {
   if (d->M <= 0 || d->N <= 0 || d->K <= 0) return 0;
   (void)cudaGetLastError();  // do not report an error left behind by an earlier, unrelated call
   // TMA needs 16-byte aligned bases and row strides.
@@ -944,9 +1019,16 @@ TITB_API int titb_gemm_bf16(const TitbGemmDesc* d, cudaStream_t stream) {
   if (!a.status) return static_cast<int>(cudaErrorMemoryAllocation);
   if (d->coll != nullptr && d->coll->mode != 0) {
     const TitbGemmColl* c = d->coll;
+#ifdef TITB_GEMM_PARAM_GATHER
+    if (c->mode != 3) return TITB_ERR_SHAPE;   // this copy of the kernel serves the parameter gather only
+    if (c->world < 1 || c->world > 16 || c->rows_per_rank % kBM || d->N != c->rows_per_rank * c->world || splits != 1 ||
+        (d->K & 7) || c->helper_ctas < 1 || d->b_mn_major || d->ldb != d->K || d->b != c->gathered || (bn != 128 && bn != 256))
+      return TITB_ERR_SHAPE;
+#else
     if (c->world < 1 || c->world > 16 || c->rows_per_rank % kBM || d->M != c->rows_per_rank * c->world || splits != 1 ||
         (d->N & 7) || (d->K & 7) || c->helper_ctas < 1)
       return TITB_ERR_SHAPE;
+#endif
     if (c->mode == 2 && (d->epilogue != TITB_EPI_NONE || d->accumulate || d->alpha)) return TITB_ERR_SHAPE;
     a.coll.mode = c->mode; a.coll.world = c->world; a.coll.rank = c->rank;
     a.coll.helper_ctas = c->helper_ctas; a.coll.rows_per_rank = c->rows_per_rank;
@@ -964,6 +1046,12 @@ TITB_API int titb_gemm_bf16(const TitbGemmDesc* d, cudaStream_t stream) {
       cudaError_t e = cudaMemsetAsync(c->flags, 0, sizeof(uint32_t) * (d->M / kBM), stream);
       if (e != cudaSuccess) return static_cast<int>(e);
     }
+#ifdef TITB_GEMM_PARAM_GATHER
+    if (c->mode == 3) {
+      cudaError_t e = cudaMemsetAsync(c->flags, 0, sizeof(uint32_t) * (d->N / kBM), stream);
+      if (e != cudaSuccess) return static_cast<int>(e);
+    }
+#endif
   }
 
   // bf16 results (and the GELU pre-activation) leave through TMA stores when their layout allows it
@@ -1002,6 +1090,7 @@ TITB_API int titb_gemm_bf16(const TitbGemmDesc* d, cudaStream_t stream) {
   return rc;
 }
 
+#ifndef TITB_GEMM_PARAM_GATHER
 // ------------------------------------------------------------- fp32 SIMT GEMM
 // Kept for fp32 tensors on the GPU (API parity with the reference's fp32-only
 // Matmul/Linear); not a hot path.  64x64 tile, 16-deep k slab, 4x4 per thread.
@@ -1058,3 +1147,4 @@ TITB_API int titb_sgemm(const float* A, const float* B, float* C, int M, int N, 
   titb::sgemm_kernel<<<grid, 256, 0, stream>>>(A, B, C, M, N, K, trans_a, trans_b, accumulate);
   return static_cast<int>(cudaGetLastError());
 }
+#endif  // !TITB_GEMM_PARAM_GATHER

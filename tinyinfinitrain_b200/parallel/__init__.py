@@ -2,6 +2,7 @@
 symmetric-memory collectives (collectives)."""
 from . import mesh, pp, tp  # noqa: F401
 from .collectives import SymmCollective  # noqa: F401
+from .param_gather import GatheredWeightLinear, RowShardedAdam  # noqa: F401
 from .mesh import ParallelMesh, init_mesh  # noqa: F401
 from .pp import PipelineStage, one_f_one_b_order, partition_layers  # noqa: F401
 from .tp import (  # noqa: F401

@@ -10,7 +10,8 @@ The fused compute+collective kernels can be run on ONE GPU for profiling: ``ag_g
 ``rs_adam`` take ``--world W`` and treat W local buffers as the peers (every load and store a
 rank would send over NVLink goes to local memory instead, the instruction stream is the one the
 multi-GPU run executes; ``rs_adam`` uses plain peer loads/stores, not multimem);
-``gemm_rs`` runs as a group of one rank (its own partial tiles are the only ones it waits for).
+``gemm_rs`` runs as a group of one rank (its own partial tiles are the only ones it waits for);
+``param_gather_gemm`` pulls the weight rows of ``--world`` owners from local copies.
 """
 from __future__ import annotations
 
@@ -54,7 +55,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel", choices=["gemm", "gemm_nt", "gemm_wgrad", "attn_fwd", "attn_bwd", "layernorm_fwd", "layernorm_bwd",
                                        "xent", "adam", "gelu_gemm", "ag_gemm", "gemm_rs", "rs_adam", "clip", "embedding_bwd",
-                                       "reduce", "transpose_view", "colsum"])
+                                       "reduce", "transpose_view", "colsum", "param_gather_gemm"])
     ap.add_argument("--deterministic", action="store_true", help="embedding_bwd: sorted segment reduction instead of atomics")
     ap.add_argument("--world", type=int, default=4)
     ap.add_argument("--helpers", type=int, default=0)
@@ -138,6 +139,16 @@ def main():
         bytes_ = 2.0 * (2 * M * K + N * K + M * N)
         ptrs = [t.data_ptr() for t in shards]
         fn = lambda: C.gemm_ag(ptrs, 0, M // W, K, B, False, 0, None, False, a.helpers or 16)
+    elif a.kernel == "param_gather_gemm":
+        # Y = X . W^T with the rows of W owned by W ranks: `world` local copies stand in for the ranks' memory
+        M, N, K, W = a.m, a.n, a.k, a.world
+        X = torch.randn(M, K, device=dev).to(bf)
+        copies = [(torch.randn(N, K, device=dev) * 0.1).to(bf) for _ in range(W)]
+        npr = N // W
+        ptrs = [copies[r].data_ptr() + r * npr * K * 2 for r in range(W)]
+        flops = 2.0 * M * N * K
+        bytes_ = 2.0 * (M * K + 2 * N * K + M * N)
+        fn = lambda: C.gemm_param_gather(X, copies[0], ptrs, 0, helper_ctas=a.helpers or 8)
     elif a.kernel == "gemm_rs":
         M, N, K = a.m, a.n, a.k
         A, B = torch.randn(M, K, device=dev).to(bf), torch.randn(N, K, device=dev).to(bf)
