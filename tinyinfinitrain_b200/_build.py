@@ -15,6 +15,7 @@ from __future__ import annotations
 
 import hashlib
 import os
+import re
 import shutil
 import subprocess
 import sys
@@ -68,6 +69,13 @@ def _obj_key(src: Path, flags, stamp: str) -> str:
     h.update(str(src.stat().st_mtime_ns).encode())
     h.update(" ".join(flags).encode())
     h.update(stamp.encode())
+    # a source that includes another source file (a second compilation of the same kernel under other macros) is
+    # rebuilt when that file changes
+    if src.suffix == ".cu":
+        for line in src.read_text().splitlines():
+            m = re.match(r'\s*#include\s+"([^"]+\.cu)"', line)
+            if m and (src.parent / m.group(1)).exists():
+                h.update(str((src.parent / m.group(1)).stat().st_mtime_ns).encode())
     return h.hexdigest()[:16]
 
 
