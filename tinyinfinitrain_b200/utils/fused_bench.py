@@ -103,9 +103,40 @@ def main():
         torch.cuda.empty_cache()
     link = (world - 1) / world * n * 4 + (world - 1) / world * n * 2   # fp32 gradient shards in, bf16 parameter shards out
     report(f"rs_adam_ag_{a.params_m}M", res["fused"], res["nccl"], 0.0, link)
+    # F4: parameter all-gather -> GEMM (weight rows sharded over the ranks) against NCCL all-gather + GEMM
+    from .._lib import C
+    from ..parallel.param_gather import GatheredWeightLinear
+
+    for name, (N, K) in (("param_gather_gemm_ffn_up", (F, C)), ("param_gather_gemm_attn_out", (C, C))):
+        if N % (128 * world):
+            continue
+        layer = GatheredWeightLinear(K, N, bias=False, device=dev)
+        xin = (torch.randn(M, K, device=dev, generator=g) * 0.5).bfloat16()
+        mine = layer.weight.detach()[layer.own_rows()].clone()
+        full = torch.empty(N, K, device=dev, dtype=torch.bfloat16)
+
+        def fused_step():
+            layer.barrier()
+            C.gemm_param_gather(xin, layer.weight.detach(), layer.peer_row_ptrs, layer.rank, helper_ctas=layer.helper_ctas)
+
+        def nccl_step():
+            dist.all_gather_into_tensor(full, mine)
+            C.gemm(xin, full)
+
+        ms_f, ms_n = _time(fused_step, a.iters), _time(nccl_step, a.iters)
+        report(name, ms_f, ms_n, 2.0 * M * N * K, (world - 1) / world * N * K * 2)
+        del layer
+    # standalone all-reduce on symmetric memory against NCCL (fp32, the size of a GPT-2 124M gradient buffer)
+    from ..parallel.collectives import SymmCollective
+
+    coll = SymmCollective(n, torch.float32, dev)
+    coll.tensor.normal_()
+    plain = coll.tensor.clone()
+    ms_f = _time(lambda: coll.all_reduce_(), a.iters)
+    ms_n = _time(lambda: dist.all_reduce(plain), a.iters)
+    report(f"allreduce_fp32_{a.params_m}M", ms_f, ms_n, 0.0, 2.0 * (world - 1) / world * n * 4)
     if rank == 0 and a.json_out:
         json.dump(out, open(a.json_out, "w"), indent=1)
-    from .._lib import C
     st = C.status_read(True)
     if st:
         print(f"rank {rank}: status {st}")
