@@ -5,6 +5,7 @@
     gpt2 | llama3 [flags]    the training entry points (same flags as examples/gpt2/main.py, examples/llama3/main.py)
     kernel-bench [args]      utils.kernel_bench        fused-bench [args]   utils.fused_bench (under torchrun)
     plan [flags]             per-GPU memory plan of a model + parallel layout (utils.memory_plan)
+    ab-bench [flags]         bench.py with each kernel-variant switch, one table (utils.ab_bench)
 """
 from __future__ import annotations
 
@@ -73,6 +74,10 @@ def main(argv=None) -> int:
 
         sys.argv = [f"tinyinfinitrain_b200 {cmd}"] + rest
         return train_main(cmd)
+    if cmd == "ab-bench":
+        from .utils import ab_bench
+
+        return ab_bench.main(rest)
     if cmd == "plan":
         from .utils import memory_plan
 
