@@ -282,7 +282,7 @@ std::vector<Tensor> layernorm_bwd(const Tensor& dy, const Tensor& x, const Tenso
                                    rstd.data_ptr<float>(), have_res ? dres.data_ptr() : nullptr, dx.data_ptr(),
                                    dw.data_ptr<float>(), db.data_ptr<float>(), scratch.data_ptr<float>(), counters, rows,
                                    (int)C, dt_code(x), 0, have && accumulate, cur_stream()),
-             "norm_bwd_onepass", 3);
+             "norm_bwd_onepass", 1);
     return {dx, dw, db};
   }
   Tensor scratch = at::empty({2, titb_layernorm_bwd_blocks(rows), C}, fopt);
@@ -327,7 +327,7 @@ std::vector<Tensor> rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor&
                                    have_res ? dres.data_ptr() : nullptr, dx.data_ptr(), dw.data_ptr<float>(), nullptr,
                                    scratch.data_ptr<float>(), counters, rows, (int)C, dt_code(x), 1,
                                    have && accumulate, cur_stream()),
-             "norm_bwd_onepass", 2);
+             "norm_bwd_onepass", 1);
     return {dx, dw};
   }
   Tensor scratch = at::empty({2, titb_layernorm_bwd_blocks(rows), C}, fopt);
@@ -743,7 +743,7 @@ Tensor colsum(const Tensor& x, const optional<Tensor>& out_, bool accumulate, bo
     Tensor scratch = at::empty({titb_colsum_fused_scratch(rows, (int)C, dt_code(x))}, fopt);
     unsigned* counters = ticket_counters(x, titb_colsum_fused_counters((int)C, dt_code(x)));
     CHECK_RC(titb_colsum_fused(x.data_ptr(), out.data_ptr<float>(), rows, (int)C, dt_code(x), have && accumulate,
-                               scratch.data_ptr<float>(), counters, cur_stream()), "colsum_fused", 2);
+                               scratch.data_ptr<float>(), counters, cur_stream()), "colsum_fused", 1);
     return out;
   }
   Tensor scratch = at::empty({titb_colsum_blocks(rows), C}, fopt);
