@@ -7,8 +7,9 @@ import sys
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+SMALL = ["--n_embd", "64", "--n_head", "4", "--vocab_size", "1000"]      # keeps every child process to a few seconds
 COMMON = ["--device", "cpu", "--synthetic", "--num_iteration", "3", "--n_layer", "2", "--batch_size", "2",
-          "--sequence_length", "16", "--dtype", "float32"]
+          "--sequence_length", "16", "--dtype", "float32"] + SMALL
 
 
 def _losses(out: str):
@@ -30,9 +31,9 @@ def _run(cmd):
 
 @pytest.mark.parametrize("family", ["gpt2", "llama3"])
 def test_single_process_training_runs(family):
-    extra = [] if family == "gpt2" else ["--n_layer", "1", "--batch_size", "1", "--sequence_length", "8"]   # 1B-wide rows: keep it short
+    extra = [] if family == "gpt2" else ["--n_kv_head", "2", "--ffn_dim", "128"]
     out = _run([sys.executable, f"examples/{family}/main.py"] + COMMON + extra)
-    assert _sane(_losses(out), 50257 if family == "gpt2" else 128256), out[-1500:]
+    assert _sane(_losses(out), 1000), out[-1500:]
 
 
 @pytest.mark.parametrize("layout", [["--tensor_parallel", "2", "--pipeline_parallel", "2", "--num_microbatches", "2"],
@@ -42,7 +43,7 @@ def test_four_ranks_layouts(layout):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "4", "--master-addr",
            "127.0.0.1", "--master-port", str(29250 + os.getpid() % 200), "examples/gpt2/main.py"] + COMMON + layout
     out = _run(cmd)
-    assert _sane(_losses(out), 50257), out[-1500:]
+    assert _sane(_losses(out), 1000), out[-1500:]
 
 
 def _step_losses(out: str):
@@ -57,7 +58,7 @@ def test_resume_continues_exactly_where_the_first_run_stopped(tmp_path, ranks, l
         [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(ranks), "--master-addr",
          "127.0.0.1", "--master-port", str(29450 + os.getpid() % 200)]
     common = ["examples/gpt2/main.py", "--device", "cpu", "--synthetic", "--n_layer", "1", "--batch_size", "2",
-              "--sequence_length", "16", "--dtype", "float32", "--learning_rate", "1e-3"] + layout
+              "--sequence_length", "16", "--dtype", "float32", "--learning_rate", "1e-3"] + SMALL + layout
     ck = str(tmp_path / "ck")
     full = _step_losses(_run(base + common + ["--num_iteration", "5"]))
     _run(base + common + ["--num_iteration", "3", "--save", ck])
@@ -73,7 +74,7 @@ def test_restart_after_failure_recipe(tmp_path):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
            "127.0.0.1", "--master-port", str(29050 + os.getpid() % 40), "examples/gpt2/main.py", "--device", "cpu",
            "--synthetic", "--n_layer", "1", "--batch_size", "2", "--sequence_length", "16", "--dtype", "float32",
-           "--learning_rate", "1e-3", "--save", ck, "--save_every", "1", "--resume", "auto"]
+           "--learning_rate", "1e-3"] + SMALL + ["--save", ck, "--save_every", "1", "--resume", "auto"]
     first = _step_losses(_run(cmd + ["--num_iteration", "3"]))            # nothing to resume from yet
     assert sorted(first) == [1, 2, 3] and os.path.exists(os.path.join(ck, "optim_rank1.pt"))
     second = _step_losses(_run(cmd + ["--num_iteration", "5"]))           # same command: picks the checkpoint up

@@ -48,6 +48,11 @@ def build_parser(family: str) -> argparse.ArgumentParser:
     p.add_argument("--seed", type=int, default=42)
     p.add_argument("--synthetic", action="store_true")
     p.add_argument("--n_layer", type=int, default=0, help="override the preset depth (smoke tests)")
+    p.add_argument("--n_embd", type=int, default=0, help="override the preset width (smoke tests, small experiments)")
+    p.add_argument("--n_head", type=int, default=0, help="override the number of attention heads")
+    p.add_argument("--n_kv_head", type=int, default=0, help="override the number of key / value heads (LLaMA-3)")
+    p.add_argument("--ffn_dim", type=int, default=0, help="override the SwiGLU width (LLaMA-3)")
+    p.add_argument("--vocab_size", type=int, default=0, help="override the vocabulary size (synthetic data only)")
     p.add_argument("--save", default="", help="checkpoint directory to write at the end (and every --save_every steps)")
     p.add_argument("--save_every", type=int, default=0, help="also checkpoint every N optimizer steps (0 = only at the end)")
     p.add_argument("--resume", default="", help="checkpoint directory to resume from; 'auto' = the --save directory if it "
@@ -66,6 +71,13 @@ def _config(family: str, args):
     cfg = dataclasses.replace(cfg)
     if args.n_layer:
         cfg.n_layer = args.n_layer
+    for name in ("n_embd", "n_head", "n_kv_head", "ffn_dim"):
+        if getattr(args, name) and hasattr(cfg, name):
+            setattr(cfg, name, getattr(args, name))
+    if args.vocab_size:
+        cfg.vocab_size = args.vocab_size
+        if hasattr(cfg, "padded_vocab_size"):
+            cfg.padded_vocab_size = (args.vocab_size + 127) // 128 * 128
     cfg.block_size = max(args.sequence_length, min(cfg.block_size, 8192))
     return cfg
 
