@@ -6,6 +6,8 @@ import sys
 import pytest
 import torch
 
+from _launch import run_group
+
 pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
@@ -15,7 +17,7 @@ def _torchrun(script, nproc, extra_env=None, timeout=600):
     port = 29600 + os.getpid() % 300
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, script)]
-    return subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
+    return run_group(cmd, env=env, timeout=timeout)
 
 
 def _ngpu():

@@ -8,6 +8,7 @@ import sys
 import pytest
 import torch
 
+from _launch import run_group
 from tinyinfinitrain_b200 import ops
 from tinyinfinitrain_b200._lib import C
 
@@ -153,7 +154,7 @@ def test_zero1_bucketed_overlap_matches_single_bucket():
     env = _multi_rank_env(TITB_TEST_ZERO_BUCKETS="3")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
            "127.0.0.1", "--master-port", str(29900 + os.getpid() % 90), os.path.join(HERE, "dist_zero_check.py")]
-    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    r = run_group(cmd, env=env, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
 
 
@@ -246,7 +247,7 @@ def test_zero1_on_the_native_symmetric_heap():
     env = _multi_rank_env(TITB200_SYMM_HEAP="native")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
            "127.0.0.1", "--master-port", str(29990 - os.getpid() % 90), os.path.join(HERE, "dist_zero_check.py")]
-    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    r = run_group(cmd, env=env, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
 
 
@@ -327,7 +328,7 @@ def test_zero1_fused_gradient_clipping_matches_nccl():
     env = _multi_rank_env(TITB_TEST_ZERO_CLIP="0.5")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
            "127.0.0.1", "--master-port", str(29850 + os.getpid() % 90), os.path.join(HERE, "dist_zero_check.py")]
-    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+    r = run_group(cmd, env=env, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
 
 
@@ -550,7 +551,7 @@ def test_symmetric_collectives_match_nccl():
     n = min(torch.cuda.device_count(), 8)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
            "127.0.0.1", "--master-port", str(29750 + os.getpid() % 90), os.path.join(HERE, "dist_collectives_check.py")]
-    r = subprocess.run(cmd, env=_multi_rank_env(), capture_output=True, text=True, timeout=900)
+    r = run_group(cmd, env=_multi_rank_env(), timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
 
 
