@@ -1,10 +1,11 @@
 """The example entry points on CPU: one process, and gloo ranks for tensor / pipeline / data parallel layouts."""
 import os
 import re
-import subprocess
 import sys
 
 import pytest
+
+from _launch import run_group
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 SMALL = ["--n_embd", "64", "--n_head", "4", "--vocab_size", "1000"]      # keeps every child process to a few seconds
@@ -24,7 +25,7 @@ def _sane(ls, vocab):
 
 
 def _run(cmd):
-    r = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=600)
+    r = run_group(cmd, cwd=ROOT, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     return r.stdout
 
