@@ -1,6 +1,6 @@
-"""GPU numerics of the kernels and schedules that are not on the default training path: the 128 x 192
-GEMM tile, the reduction / view-like transform kernels and the bucketed ZeRO-1 step that overlaps
-backward.  Each is compared against plain PyTorch fp32 math of the same op."""
+"""GPU numerics of the kernels and schedules that are not on the default training path yet.  Each is compared against
+plain PyTorch fp32 math of the same op (or against the kernel it replaces).  Order: the step-level variants whose A/B
+decides the next defaults, the other single-GPU kernels, the C++ facade on CUDA, the multi-GPU jobs."""
 import os
 import subprocess
 import sys
@@ -32,385 +32,6 @@ def _multi_rank_env(**extra):
 def _status_ok():
     torch.cuda.synchronize()
     assert C.status_read(True) == 0
-
-
-@pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 1)])
-def test_gemm_tile192_layouts_and_epilogue(a_mn, b_mn):
-    torch.manual_seed(11)
-    M, N, K = 520, 776, 328          # ragged in every dimension: 4 full 192-wide tiles + one of 8 columns
-    A = (torch.randn(M, K, device=DEV) * 0.5).to(BF)
-    W = (torch.randn(N, K, device=DEV) * 0.1).to(BF)
-    b = (torch.randn(N, device=DEV) * 0.1).to(BF)
-    R = torch.randn(M, N, device=DEV).to(BF)
-    ref = A.float() @ W.float().t()
-    a = A.t().contiguous() if a_mn else A
-    w = W.t().contiguous() if b_mn else W
-    y = C.gemm(a, w, bool(a_mn), bool(b_mn), tile_n=192, out_fp32=True)[0]
-    assert torch.allclose(y, ref, rtol=1e-4, atol=2e-2)
-    y = C.gemm(a, w, bool(a_mn), bool(b_mn), tile_n=192, epilogue=ops.EPI_BIAS_RESIDUAL, bias=b, aux_in=R)[0]
-    assert torch.allclose(y.float(), ref + b.float() + R.float(), atol=5e-2, rtol=2e-2)
-    act, pre = C.gemm(a, w, bool(a_mn), bool(b_mn), tile_n=192, epilogue=ops.EPI_BIAS_GELU, bias=b, want_aux_out=True)
-    assert torch.allclose(pre.float(), ref + b.float(), atol=3e-2, rtol=2e-2)
-    assert torch.allclose(act.float(), ops.gelu_ref(pre.float()), atol=2e-2, rtol=2e-2)
-    _status_ok()
-
-
-@pytest.mark.parametrize("splits", [1, 3])
-def test_gemm_tile192_accumulate_and_splitk(splits):
-    torch.manual_seed(1)
-    M, N, K = 384, 640, 1536
-    A = (torch.randn(M, K, device=DEV) * 0.5).to(BF)
-    B = (torch.randn(N, K, device=DEV) * 0.5).to(BF)
-    ref = A.float() @ B.float().t()
-    acc = torch.full((M, N), 2.0, device=DEV)
-    C.gemm(A, B, out=acc, accumulate=True, tile_n=192, splits=splits)
-    _status_ok()
-    assert torch.allclose(acc, ref + 2.0, rtol=1e-4, atol=5e-2)
-
-
-@pytest.mark.parametrize("dtype", [torch.float32, BF])
-@pytest.mark.parametrize("name", ["sum", "mean", "max", "min"])
-@pytest.mark.parametrize("shape,dim", [((7, 33, 5), 1), ((6, 40), -1), ((3, 4, 5, 6), 0), ((257,), 0)])
-def test_reduce_forward_backward(name, dtype, shape, dim):
-    torch.manual_seed(3)
-    x = torch.randn(*shape, device=DEV).to(dtype)
-    xr = x.float().clone().requires_grad_(True)
-    xg = x.clone().requires_grad_(True)
-    for keepdim in (False, True):
-        y = ops.reduce(name, xg, dim, keepdim)
-        ref = getattr(torch, name)(xr, dim=dim, keepdim=keepdim)
-        ref = ref if name in ("sum", "mean") else ref.values
-        tol = dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=6e-2, rtol=2e-2)
-        assert y.shape == ref.shape and y.dtype == dtype
-        assert torch.allclose(y.float(), ref, **tol)
-    g = torch.randn_like(ref)
-    (gx,) = torch.autograd.grad(y, xg, g.to(dtype))
-    (gr,) = torch.autograd.grad(ref, xr, g)
-    assert torch.allclose(gx.float(), gr, atol=2e-2 if dtype == BF else 1e-6, rtol=2e-2 if dtype == BF else 1e-6)
-
-
-@pytest.mark.parametrize("dtype", [torch.float32, BF])
-def test_slice_split_stack_repeat(dtype):
-    torch.manual_seed(4)
-    x = torch.randn(4, 9, 10, device=DEV).to(dtype).requires_grad_(True)
-    xr = x.detach().clone().requires_grad_(True)
-    y = ops.slice_nd(x, [1, 0, 2], [4, 9, 10], [1, 2, 3])
-    ref = xr[1:4, 0:9:2, 2:10:3]
-    assert torch.equal(y, ref.contiguous())
-    g = torch.randn_like(y)
-    assert torch.equal(torch.autograd.grad(y, x, g)[0], torch.autograd.grad(ref, xr, g)[0])
-
-    parts, rparts = ops.split(x, 4, 1), torch.split(xr, 4, 1)
-    assert len(parts) == len(rparts) == 3
-    for a, b in zip(parts, rparts):
-        assert torch.equal(a, b.contiguous())
-    gs = [torch.randn_like(a) for a in parts]
-    ga = torch.autograd.grad(parts, x, gs)[0]
-    gb = torch.autograd.grad(rparts, xr, gs)[0]
-    assert torch.equal(ga, gb)
-
-    for dim in (0, 1, 3, -1):
-        s, sr = ops.stack([x, x * 2], dim), torch.stack([xr, xr * 2], dim)
-        assert torch.equal(s, sr)
-        g = torch.randn_like(s)
-        assert torch.allclose(torch.autograd.grad(s, x, g)[0].float(), torch.autograd.grad(sr, xr, g)[0].float(),
-                              atol=2e-2, rtol=2e-2)
-
-    for dim in (0, 1, 2):
-        r, rr = ops.repeat_interleave(x, 3, dim), torch.repeat_interleave(xr, 3, dim=dim)
-        assert torch.equal(r, rr)
-        g = torch.randn_like(r)
-        assert torch.allclose(torch.autograd.grad(r, x, g)[0].float(), torch.autograd.grad(rr, xr, g)[0].float(),
-                              atol=5e-2, rtol=2e-2)
-
-
-@pytest.mark.parametrize("dtype", [torch.float32, BF])
-def test_masked_fill_and_outer(dtype):
-    torch.manual_seed(5)
-    x = torch.randn(3, 8, 8, device=DEV).to(dtype).requires_grad_(True)
-    xr = x.detach().clone().requires_grad_(True)
-    for mask in (torch.triu(torch.ones(8, 8, device=DEV), 1).bool(), torch.triu(torch.ones(8, 8, device=DEV), 1).to(dtype)):
-        y = ops.masked_fill(x, mask, -1e4)
-        ref = xr.masked_fill(mask != 0, -1e4)
-        assert torch.equal(y, ref)
-        g = torch.randn_like(y)
-        assert torch.equal(torch.autograd.grad(y, x, g)[0], torch.autograd.grad(ref, xr, g)[0])
-    a = torch.randn(37, device=DEV).to(dtype).requires_grad_(True)
-    b = torch.randn(70, device=DEV).to(dtype).requires_grad_(True)
-    ar, br = a.detach().float().requires_grad_(True), b.detach().float().requires_grad_(True)
-    o, orf = ops.outer(a, b), torch.outer(ar, br)
-    tol = dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=8e-2, rtol=2e-2)
-    assert torch.allclose(o.float(), orf, **tol)
-    g = torch.randn_like(orf)
-    da, db = torch.autograd.grad(o, (a, b), g.to(dtype))
-    dar, dbr = torch.autograd.grad(orf, (ar, br), g)
-    assert torch.allclose(da.float(), dar, **tol) and torch.allclose(db.float(), dbr, **tol)
-    _status_ok()
-
-
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_zero1_bucketed_overlap_matches_single_bucket():
-    n = min(torch.cuda.device_count(), 8)
-    env = _multi_rank_env(TITB_TEST_ZERO_BUCKETS="3")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
-           "127.0.0.1", "--master-port", str(29900 + os.getpid() % 90), os.path.join(HERE, "dist_zero_check.py")]
-    r = run_group(cmd, env=env, timeout=600)
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
-
-
-@pytest.mark.parametrize("dtype", [torch.float32, BF])
-@pytest.mark.parametrize("V,vocab,shards", [(512, 500, 2), (1024, 1000, 4), (96, 50, 3)])
-def test_vocab_parallel_xent_kernels_match_full_softmax(dtype, V, vocab, shards):
-    """The slices of one [M, V] logits tensor are processed as the ranks of a group would process them (same
-    kernels, one table in local memory); loss rows and gradient must equal cross entropy over the full row."""
-    torch.manual_seed(6)
-    M, Vl = 37, V // shards
-    full = (torch.randn(M, V, device=DEV) * 3).to(dtype)
-    tgt = torch.randint(0, vocab, (M,), device=DEV)
-    ref_in = full.float()[:, :vocab].clone().requires_grad_(True)
-    ref_rows = torch.nn.functional.cross_entropy(ref_in, tgt, reduction="none")
-    ref_rows.mean().backward()
-    table = torch.zeros(shards, M, 3, device=DEV)
-    slices = [full[:, r * Vl:(r + 1) * Vl].contiguous() for r in range(shards)]
-    for r, sl in enumerate(slices):
-        C.xent_vp_stats(sl, tgt, [table.data_ptr()], r, r * Vl, vocab)
-    for r, sl in enumerate(slices):
-        rows = C.xent_vp_grad(sl, tgt, table, r * Vl, vocab, 1.0 / M)
-        tol = dict(atol=1e-4, rtol=1e-4) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
-        assert torch.allclose(rows, ref_rows, **tol)
-    grad = torch.cat(slices, 1).float()
-    assert torch.all(grad[:, vocab:] == 0)
-    gtol = dict(atol=1e-6, rtol=1e-4) if dtype == torch.float32 else dict(atol=2e-3, rtol=3e-2)
-    assert torch.allclose(grad[:, :vocab], ref_in.grad, **gtol)
-    _status_ok()
-
-
-def _fw(t, dev, requires_grad=False):
-    ft = C.FwTensor(t.clone(), requires_grad)
-    return ft.To(dev) if dev != "cpu" else ft
-
-
-def _facade_run(dev):
-    """A tour through the C++ facade's view-like, reduction and mask Functions; returns every result as CPU tensors."""
-    torch.manual_seed(8)
-    out = {}
-    x0 = torch.randn(3, 4, 6)
-    x = _fw(x0, dev, True)
-    parts = x.Split(2, 2)                                            # Split (multi-output) -> gather kernel
-    y = parts[0].Mul(parts[1]).Add(parts[2])
-    y = y.Transpose(0, 1)                                            # Transpose -> gather kernel
-    y = y.RepeatInterleave(2, 2)                                     # stride-0 gather / sum backward
-    y = y.Slice([0, 1, 0], [4, 3, 4], [1, 1, 2])                     # Slice -> gather fwd, scatter bwd
-    s = C.fw_function("Stack", [1]).Apply([y, y.MulScalar(2.0)])[0]  # Stack -> scatter fwd, gather bwd
-    sm = C.fw_function("Softmax", [2]).Apply([s])[0]
-    red = C.fw_function("Sum", [3, 0]).Apply([sm.Mul(s)])[0]
-    red = C.fw_function("Max", [0, 1]).Apply([red])[0]
-    red = C.fw_function("Mean", [2, 0]).Apply([red])[0]
-    red = C.fw_function("Min", [1, 0]).Apply([red])[0]
-    out["y"], out["stack"], out["softmax"], out["red"] = y.torch(), s.torch(), sm.torch(), red.torch()
-    red.Backward(_fw(torch.ones(1), dev))
-    out["dx"] = x.grad().torch()
-    m0 = torch.tril(torch.ones(6, 6))
-    a = _fw(torch.randn(2, 6, 6), dev, True)
-    tri = C.fw_function("Tril", [0]).Apply([_fw(torch.ones(6, 6), dev)])[0]
-    masked = a.MaskedFill(tri.Equals(0.0), -1e4)
-    out["tril"], out["masked"] = tri.torch(), masked.torch()
-    C.fw_function("Sum", [0, 0]).Apply([C.fw_function("Sum", [2, 0]).Apply([masked])[0]])[0].Backward(_fw(torch.ones(6), dev))
-    out["da"] = a.grad().torch()
-    ge_in = _fw(torch.randn(4, 9), dev, True)
-    ge = C.fw_function("Gelu").Apply([ge_in])[0]                     # one kernel on the GPU
-    C.fw_function("Sum", [0, 0]).Apply([C.fw_function("Sum", [1, 0]).Apply([ge])[0]])[0].Backward()
-    out["gelu"], out["dgelu"] = ge.torch(), ge_in.grad().torch()
-    u, v = _fw(torch.randn(5), dev, True), _fw(torch.randn(7), dev, True)
-    o = u.Outer(v)
-    out["outer"] = o.torch()
-    C.fw_function("Sum", [0, 0]).Apply([C.fw_function("Sum", [1, 0]).Apply([o.Mul(o)])[0]])[0].Backward()
-    out["du"], out["dv"] = u.grad().torch(), v.grad().torch()
-    assert torch.equal(m0, out["tril"].cpu())
-    return {k: t.detach().float().cpu() for k, t in out.items()}
-
-
-def test_cpp_facade_cuda_ops_match_cpu_oracle():
-    cpu, gpu = _facade_run("cpu"), _facade_run("cuda:0")
-    for k in cpu:
-        assert cpu[k].shape == gpu[k].shape, k
-        tol = 2e-3 if "gelu" in k else 1e-5   # the GPU GELU uses tanh.approx
-        assert torch.allclose(cpu[k], gpu[k], atol=tol, rtol=tol), k
-    _status_ok()
-
-
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_zero1_on_the_native_symmetric_heap():
-    """The ZeRO-1 worker with buffers from this package's own heap (cuMem VMM + descriptor passing) instead of
-    PyTorch's symmetric-memory allocator."""
-    n = min(torch.cuda.device_count(), 8)
-    env = _multi_rank_env(TITB200_SYMM_HEAP="native")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
-           "127.0.0.1", "--master-port", str(29990 - os.getpid() % 90), os.path.join(HERE, "dist_zero_check.py")]
-    r = run_group(cmd, env=env, timeout=600)
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
-
-
-def test_cpp_api_program_passes_on_cuda(tmp_path):
-    """The stand-alone C++ test program (reference gtest cases + data layer + a short GPT-2 run) on cuda:0."""
-    from tinyinfinitrain_b200 import _build
-
-    built = _build.build_cpp()
-    r = subprocess.run([str(built["facade_api_test"]), "cuda", str(tmp_path)], capture_output=True, text=True, timeout=600)
-    assert r.returncode == 0 and "all checks passed" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
-
-
-def test_cpp_llama3_and_gpt2_on_cuda_match_the_cpu_facade():
-    """The C++ models moved to cuda:0 (kernel-backed RMSNorm / Rope / SwiGLU / Gelu / LayerNorm / softmax / SGEMM and the
-    gather kernel behind every transpose and slice) against the same models on the CPU."""
-    g = torch.Generator().manual_seed(2)
-    idx, tgt = torch.randint(0, 150, (2, 16), generator=g), torch.randint(0, 150, (2, 16), generator=g)
-    for make in (lambda: C.FwLLaMA3(32, 150, 2, 4, 2, 32, 48), lambda: C.FwGPT2(32, 150, 2, 4, 32)):
-        res = {}
-        for dev in ("cpu", "cuda:0"):
-            model = make()                       # seeded initialisation: identical weights in both runs
-            if not dev.startswith("cpu"):
-                model.To(dev)
-            put = (lambda t: C.FwTensor(t).To(dev)) if not dev.startswith("cpu") else C.FwTensor
-            logits = model.Forward([put(idx)])[0]
-            loss = C.FwCrossEntropyLoss().Forward([logits, put(tgt)])[0]
-            loss.Backward()
-            grads = {k: v.grad().torch().float().cpu() for k, v in model.StateDict().items() if v.grad() is not None}
-            res[dev] = (logits.torch().detach().float().cpu(), float(loss.torch().detach()), grads)
-        assert torch.allclose(res["cpu"][0], res["cuda:0"][0], atol=2e-3, rtol=1e-3)
-        assert abs(res["cpu"][1] - res["cuda:0"][1]) < 1e-3
-        for k, gcpu in res["cpu"][2].items():
-            assert torch.allclose(gcpu, res["cuda:0"][2][k], atol=2e-3, rtol=1e-2), k
-    _status_ok()
-
-
-def test_cpp_models_in_bf16_use_the_flash_attention_function():
-    """C++ GPT-2 (hd 64) and LLaMA-3 (hd 64, grouped-query) cast to bf16 on cuda:0: attention runs as the fused
-    CausalAttention Function (tcgen05 kernels); logits and loss stay close to the fp32 CPU model."""
-    g = torch.Generator().manual_seed(3)
-    idx, tgt = torch.randint(0, 300, (2, 128), generator=g), torch.randint(0, 300, (2, 128), generator=g)
-    for make in (lambda: C.FwGPT2(128, 300, 2, 2, 128), lambda: C.FwLLaMA3(128, 300, 2, 4, 2, 256, 512)):
-        ref_model = make()
-        ref = ref_model.Forward([C.FwTensor(idx)])[0].torch()
-        model = make()
-        model.To("cuda:0")
-        model.ToDtype("bfloat16")
-        logits = model.Forward([C.FwTensor(idx).To("cuda:0")])[0]
-        loss = C.FwCrossEntropyLoss().Forward([logits, C.FwTensor(tgt).To("cuda:0")])[0]
-        loss.Backward()
-        assert logits.torch().dtype == torch.bfloat16
-        assert (logits.torch().float().cpu() - ref).abs().max() < 0.1
-        grads = [v.grad().torch() for v in model.StateDict().values() if v.grad() is not None]
-        assert grads and all(torch.isfinite(x.float()).all() for x in grads)
-        assert any(float(x.float().abs().max()) > 0 for x in grads)
-    _status_ok()
-
-
-def test_clip_grad_norm_kernels():
-    """sumsq -> coefficient -> in-place scaling, all on the device, against torch.nn.utils.clip_grad_norm_."""
-    torch.manual_seed(9)
-    for n, scale, max_norm in ((1_000_003, 1.0, 5.0), (4096, 1e-3, 1.0), (70_000_000, 0.5, 1.0)):
-        g = (torch.randn(n, device=DEV) * 0.01).contiguous()
-        ref = g.clone()
-        ref_norm = float(ref.double().norm()) * scale
-        coef = min(1.0, max_norm / (ref_norm + 1e-6))
-        out = torch.zeros(2, device=DEV)
-        C.clip_grad_norm_(g, max_norm, scale, out)
-        assert abs(float(out[0]) - ref_norm) < 1e-4 * max(1.0, ref_norm)
-        assert abs(float(out[1]) - coef) < 1e-5
-        assert torch.allclose(g, ref * coef, rtol=1e-5, atol=1e-9)
-    _status_ok()
-
-
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_zero1_fused_gradient_clipping_matches_nccl():
-    n = min(torch.cuda.device_count(), 8)
-    env = _multi_rank_env(TITB_TEST_ZERO_CLIP="0.5")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
-           "127.0.0.1", "--master-port", str(29850 + os.getpid() % 90), os.path.join(HERE, "dist_zero_check.py")]
-    r = run_group(cmd, env=env, timeout=900)
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
-
-
-@pytest.mark.parametrize("dtype", [torch.float32, BF])
-def test_deterministic_embedding_gradient(dtype):
-    """Sorted segment reduction of the token-embedding gradient: equals index_add in float64, is bit-identical across
-    runs, handles heavy repetition, a vocabulary shard, and leaves the position gradient to the regular kernel."""
-    torch.manual_seed(12)
-    B, T, Cdim, V = 4, 256, 96, 500
-    idx = torch.randint(0, V, (B, T), device=DEV)
-    idx[0, :200] = 7                                           # one token repeated 200 times
-    dout = torch.randn(B, T, Cdim, device=DEV).to(dtype)
-    ref = torch.zeros(V, Cdim, device=DEV, dtype=torch.float64)
-    ref.index_add_(0, idx.reshape(-1), dout.reshape(-1, Cdim).double())
-    runs = []
-    for _ in range(3):
-        dw = torch.zeros(V, Cdim, device=DEV)
-        dp = torch.zeros(T, Cdim, device=DEV)
-        C.embedding_bwd(idx, dout, dw, dp, 0, V, True)
-        runs.append(dw.clone())
-        assert torch.allclose(dp.double(), dout.double().sum(0), atol=1e-3)
-    assert torch.equal(runs[0], runs[1]) and torch.equal(runs[1], runs[2])
-    assert torch.allclose(runs[0].double(), ref, atol=1e-2 if dtype == BF else 1e-4, rtol=1e-3)
-    # accumulation into an existing buffer, and a vocabulary shard [100, 300)
-    dw = torch.ones(200, Cdim, device=DEV)
-    C.embedding_bwd(idx, dout, dw, None, 100, 300, True)
-    assert torch.allclose(dw.double(), 1.0 + ref[100:300], atol=1e-2 if dtype == BF else 1e-4, rtol=1e-3)
-    _status_ok()
-
-
-@pytest.mark.parametrize("dtype", [torch.float32, BF])
-@pytest.mark.parametrize("rows,ld,V", [(64, 50304, 50257), (33, 1000, 1000), (16, 512, 300)])
-def test_row_cached_cross_entropy_matches_the_regular_kernel(dtype, rows, ld, V):
-    torch.manual_seed(13)
-    logits = (torch.randn(rows, ld, device=DEV) * 2).to(dtype)
-    tgt = torch.randint(0, V, (rows,), device=DEV)
-    a, b = logits.clone(), logits.clone()
-    la = C.xent_fused(a, tgt, V, 1.0 / rows, True, 1.0 / rows, False)
-    lb = C.xent_fused(b, tgt, V, 1.0 / rows, True, 1.0 / rows, True)
-    ref_in = logits.float()[:, :V].clone().requires_grad_(True)
-    ref = torch.nn.functional.cross_entropy(ref_in, tgt)
-    ref.backward()
-    assert abs(float(la) - float(lb)) < 1e-5 and abs(float(lb) - float(ref)) < (2e-2 if dtype == BF else 1e-4)
-    assert torch.allclose(a.float(), b.float(), atol=1e-7 if dtype == torch.float32 else 1e-3, rtol=1e-3)
-    assert torch.all(b[:, V:] == 0)
-    assert torch.allclose(b.float()[:, :V], ref_in.grad, atol=2e-4 if dtype == BF else 1e-6, rtol=3e-2)
-    _status_ok()
-
-
-@pytest.mark.parametrize("dtype", [torch.float32, BF])
-@pytest.mark.parametrize("rows,cols", [(8192, 768), (8192, 3072), (1000, 2304), (37, 264), (5, 8)])
-def test_one_launch_column_sum_matches_the_two_stage_kernel(dtype, rows, cols):
-    torch.manual_seed(17)
-    x = torch.randn(rows, cols, device=DEV).to(dtype)
-    ref = x.double().sum(0)
-    two = C.colsum(x, None, False, False)
-    runs = [C.colsum(x, None, False, True) for _ in range(3)]
-    assert torch.equal(runs[0], runs[1]) and torch.equal(runs[1], runs[2])      # fixed summation order
-    tol = 2e-3 * rows ** 0.5
-    assert torch.allclose(runs[0].double(), ref, atol=tol) and torch.allclose(two.double(), ref, atol=tol)
-    acc = torch.ones(cols, device=DEV)
-    C.colsum(x, acc, True, True)
-    assert torch.allclose(acc.double(), 1.0 + ref, atol=tol)
-    # a different shape right after: the counters of the previous launches were left at zero
-    y = torch.randn(rows + 3, cols, device=DEV).to(dtype)
-    assert torch.allclose(C.colsum(y, None, False, True).double(), y.double().sum(0), atol=tol)
-    _status_ok()
-
-
-def test_one_launch_column_sum_inside_a_cuda_graph():
-    x = torch.randn(4096, 768, device=DEV).to(BF)
-    out = torch.zeros(768, device=DEV)
-    C.colsum(x, out, False, True)                          # allocates the counters outside of the capture
-    torch.cuda.synchronize()
-    g = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g):
-        C.colsum(x, out, False, True)
-    for _ in range(3):
-        x.normal_()
-        g.replay()
-        torch.cuda.synchronize()
-        assert torch.allclose(out.double(), x.double().sum(0), atol=0.2)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, BF])
@@ -515,6 +136,137 @@ def test_attention_backward_with_two_warps_per_score_row(B, T, Hq, Hkv, hd):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, BF])
+@pytest.mark.parametrize("rows,cols", [(8192, 768), (8192, 3072), (1000, 2304), (37, 264), (5, 8)])
+def test_one_launch_column_sum_matches_the_two_stage_kernel(dtype, rows, cols):
+    torch.manual_seed(17)
+    x = torch.randn(rows, cols, device=DEV).to(dtype)
+    ref = x.double().sum(0)
+    two = C.colsum(x, None, False, False)
+    runs = [C.colsum(x, None, False, True) for _ in range(3)]
+    assert torch.equal(runs[0], runs[1]) and torch.equal(runs[1], runs[2])      # fixed summation order
+    tol = 2e-3 * rows ** 0.5
+    assert torch.allclose(runs[0].double(), ref, atol=tol) and torch.allclose(two.double(), ref, atol=tol)
+    acc = torch.ones(cols, device=DEV)
+    C.colsum(x, acc, True, True)
+    assert torch.allclose(acc.double(), 1.0 + ref, atol=tol)
+    # a different shape right after: the counters of the previous launches were left at zero
+    y = torch.randn(rows + 3, cols, device=DEV).to(dtype)
+    assert torch.allclose(C.colsum(y, None, False, True).double(), y.double().sum(0), atol=tol)
+    _status_ok()
+
+
+def test_one_launch_column_sum_inside_a_cuda_graph():
+    x = torch.randn(4096, 768, device=DEV).to(BF)
+    out = torch.zeros(768, device=DEV)
+    C.colsum(x, out, False, True)                          # allocates the counters outside of the capture
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        C.colsum(x, out, False, True)
+    for _ in range(3):
+        x.normal_()
+        g.replay()
+        torch.cuda.synchronize()
+        assert torch.allclose(out.double(), x.double().sum(0), atol=0.2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, BF])
+@pytest.mark.parametrize("rows,ld,V", [(64, 50304, 50257), (33, 1000, 1000), (16, 512, 300)])
+def test_row_cached_cross_entropy_matches_the_regular_kernel(dtype, rows, ld, V):
+    torch.manual_seed(13)
+    logits = (torch.randn(rows, ld, device=DEV) * 2).to(dtype)
+    tgt = torch.randint(0, V, (rows,), device=DEV)
+    a, b = logits.clone(), logits.clone()
+    la = C.xent_fused(a, tgt, V, 1.0 / rows, True, 1.0 / rows, False)
+    lb = C.xent_fused(b, tgt, V, 1.0 / rows, True, 1.0 / rows, True)
+    ref_in = logits.float()[:, :V].clone().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(ref_in, tgt)
+    ref.backward()
+    assert abs(float(la) - float(lb)) < 1e-5 and abs(float(lb) - float(ref)) < (2e-2 if dtype == BF else 1e-4)
+    assert torch.allclose(a.float(), b.float(), atol=1e-7 if dtype == torch.float32 else 1e-3, rtol=1e-3)
+    assert torch.all(b[:, V:] == 0)
+    assert torch.allclose(b.float()[:, :V], ref_in.grad, atol=2e-4 if dtype == BF else 1e-6, rtol=3e-2)
+    _status_ok()
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 1)])
+def test_gemm_tile192_layouts_and_epilogue(a_mn, b_mn):
+    torch.manual_seed(11)
+    M, N, K = 520, 776, 328          # ragged in every dimension: 4 full 192-wide tiles + one of 8 columns
+    A = (torch.randn(M, K, device=DEV) * 0.5).to(BF)
+    W = (torch.randn(N, K, device=DEV) * 0.1).to(BF)
+    b = (torch.randn(N, device=DEV) * 0.1).to(BF)
+    R = torch.randn(M, N, device=DEV).to(BF)
+    ref = A.float() @ W.float().t()
+    a = A.t().contiguous() if a_mn else A
+    w = W.t().contiguous() if b_mn else W
+    y = C.gemm(a, w, bool(a_mn), bool(b_mn), tile_n=192, out_fp32=True)[0]
+    assert torch.allclose(y, ref, rtol=1e-4, atol=2e-2)
+    y = C.gemm(a, w, bool(a_mn), bool(b_mn), tile_n=192, epilogue=ops.EPI_BIAS_RESIDUAL, bias=b, aux_in=R)[0]
+    assert torch.allclose(y.float(), ref + b.float() + R.float(), atol=5e-2, rtol=2e-2)
+    act, pre = C.gemm(a, w, bool(a_mn), bool(b_mn), tile_n=192, epilogue=ops.EPI_BIAS_GELU, bias=b, want_aux_out=True)
+    assert torch.allclose(pre.float(), ref + b.float(), atol=3e-2, rtol=2e-2)
+    assert torch.allclose(act.float(), ops.gelu_ref(pre.float()), atol=2e-2, rtol=2e-2)
+    _status_ok()
+
+
+@pytest.mark.parametrize("splits", [1, 3])
+def test_gemm_tile192_accumulate_and_splitk(splits):
+    torch.manual_seed(1)
+    M, N, K = 384, 640, 1536
+    A = (torch.randn(M, K, device=DEV) * 0.5).to(BF)
+    B = (torch.randn(N, K, device=DEV) * 0.5).to(BF)
+    ref = A.float() @ B.float().t()
+    acc = torch.full((M, N), 2.0, device=DEV)
+    C.gemm(A, B, out=acc, accumulate=True, tile_n=192, splits=splits)
+    _status_ok()
+    assert torch.allclose(acc, ref + 2.0, rtol=1e-4, atol=5e-2)
+
+
+def test_clip_grad_norm_kernels():
+    """sumsq -> coefficient -> in-place scaling, all on the device, against torch.nn.utils.clip_grad_norm_."""
+    torch.manual_seed(9)
+    for n, scale, max_norm in ((1_000_003, 1.0, 5.0), (4096, 1e-3, 1.0), (70_000_000, 0.5, 1.0)):
+        g = (torch.randn(n, device=DEV) * 0.01).contiguous()
+        ref = g.clone()
+        ref_norm = float(ref.double().norm()) * scale
+        coef = min(1.0, max_norm / (ref_norm + 1e-6))
+        out = torch.zeros(2, device=DEV)
+        C.clip_grad_norm_(g, max_norm, scale, out)
+        assert abs(float(out[0]) - ref_norm) < 1e-4 * max(1.0, ref_norm)
+        assert abs(float(out[1]) - coef) < 1e-5
+        assert torch.allclose(g, ref * coef, rtol=1e-5, atol=1e-9)
+    _status_ok()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, BF])
+def test_deterministic_embedding_gradient(dtype):
+    """Sorted segment reduction of the token-embedding gradient: equals index_add in float64, is bit-identical across
+    runs, handles heavy repetition, a vocabulary shard, and leaves the position gradient to the regular kernel."""
+    torch.manual_seed(12)
+    B, T, Cdim, V = 4, 256, 96, 500
+    idx = torch.randint(0, V, (B, T), device=DEV)
+    idx[0, :200] = 7                                           # one token repeated 200 times
+    dout = torch.randn(B, T, Cdim, device=DEV).to(dtype)
+    ref = torch.zeros(V, Cdim, device=DEV, dtype=torch.float64)
+    ref.index_add_(0, idx.reshape(-1), dout.reshape(-1, Cdim).double())
+    runs = []
+    for _ in range(3):
+        dw = torch.zeros(V, Cdim, device=DEV)
+        dp = torch.zeros(T, Cdim, device=DEV)
+        C.embedding_bwd(idx, dout, dw, dp, 0, V, True)
+        runs.append(dw.clone())
+        assert torch.allclose(dp.double(), dout.double().sum(0), atol=1e-3)
+    assert torch.equal(runs[0], runs[1]) and torch.equal(runs[1], runs[2])
+    assert torch.allclose(runs[0].double(), ref, atol=1e-2 if dtype == BF else 1e-4, rtol=1e-3)
+    # accumulation into an existing buffer, and a vocabulary shard [100, 300)
+    dw = torch.ones(200, Cdim, device=DEV)
+    C.embedding_bwd(idx, dout, dw, None, 100, 300, True)
+    assert torch.allclose(dw.double(), 1.0 + ref[100:300], atol=1e-2 if dtype == BF else 1e-4, rtol=1e-3)
+    _status_ok()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, BF])
 @pytest.mark.parametrize("world", [2, 8])
 def test_symmetric_collective_kernels_on_one_gpu(dtype, world):
     """The peer-pointer branch of the all-reduce / all-gather kernels with `world` local buffers standing in for the
@@ -544,15 +296,6 @@ def test_symmetric_collective_kernels_on_one_gpu(dtype, world):
         assert torch.equal(b[off:off + per * world], want)
         assert torch.all(b[:off] == r + 1) and torch.all(b[off + per * world:] == r + 1)
     _status_ok()
-
-
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_symmetric_collectives_match_nccl():
-    n = min(torch.cuda.device_count(), 8)
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
-           "127.0.0.1", "--master-port", str(29750 + os.getpid() % 90), os.path.join(HERE, "dist_collectives_check.py")]
-    r = run_group(cmd, env=_multi_rank_env(), timeout=900)
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
 
 
 def test_point_to_point_flag_signal_then_wait_and_bounded_timeout():
@@ -606,3 +349,260 @@ def test_parameter_gather_gemm_on_one_gpu(world, npr, M, K, bias):
             copies[r].fill_(float("nan"))
             copies[r][r * npr:(r + 1) * npr] = keep
     _status_ok()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, BF])
+@pytest.mark.parametrize("V,vocab,shards", [(512, 500, 2), (1024, 1000, 4), (96, 50, 3)])
+def test_vocab_parallel_xent_kernels_match_full_softmax(dtype, V, vocab, shards):
+    """The slices of one [M, V] logits tensor are processed as the ranks of a group would process them (same
+    kernels, one table in local memory); loss rows and gradient must equal cross entropy over the full row."""
+    torch.manual_seed(6)
+    M, Vl = 37, V // shards
+    full = (torch.randn(M, V, device=DEV) * 3).to(dtype)
+    tgt = torch.randint(0, vocab, (M,), device=DEV)
+    ref_in = full.float()[:, :vocab].clone().requires_grad_(True)
+    ref_rows = torch.nn.functional.cross_entropy(ref_in, tgt, reduction="none")
+    ref_rows.mean().backward()
+    table = torch.zeros(shards, M, 3, device=DEV)
+    slices = [full[:, r * Vl:(r + 1) * Vl].contiguous() for r in range(shards)]
+    for r, sl in enumerate(slices):
+        C.xent_vp_stats(sl, tgt, [table.data_ptr()], r, r * Vl, vocab)
+    for r, sl in enumerate(slices):
+        rows = C.xent_vp_grad(sl, tgt, table, r * Vl, vocab, 1.0 / M)
+        tol = dict(atol=1e-4, rtol=1e-4) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+        assert torch.allclose(rows, ref_rows, **tol)
+    grad = torch.cat(slices, 1).float()
+    assert torch.all(grad[:, vocab:] == 0)
+    gtol = dict(atol=1e-6, rtol=1e-4) if dtype == torch.float32 else dict(atol=2e-3, rtol=3e-2)
+    assert torch.allclose(grad[:, :vocab], ref_in.grad, **gtol)
+    _status_ok()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, BF])
+@pytest.mark.parametrize("name", ["sum", "mean", "max", "min"])
+@pytest.mark.parametrize("shape,dim", [((7, 33, 5), 1), ((6, 40), -1), ((3, 4, 5, 6), 0), ((257,), 0)])
+def test_reduce_forward_backward(name, dtype, shape, dim):
+    torch.manual_seed(3)
+    x = torch.randn(*shape, device=DEV).to(dtype)
+    xr = x.float().clone().requires_grad_(True)
+    xg = x.clone().requires_grad_(True)
+    for keepdim in (False, True):
+        y = ops.reduce(name, xg, dim, keepdim)
+        ref = getattr(torch, name)(xr, dim=dim, keepdim=keepdim)
+        ref = ref if name in ("sum", "mean") else ref.values
+        tol = dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=6e-2, rtol=2e-2)
+        assert y.shape == ref.shape and y.dtype == dtype
+        assert torch.allclose(y.float(), ref, **tol)
+    g = torch.randn_like(ref)
+    (gx,) = torch.autograd.grad(y, xg, g.to(dtype))
+    (gr,) = torch.autograd.grad(ref, xr, g)
+    assert torch.allclose(gx.float(), gr, atol=2e-2 if dtype == BF else 1e-6, rtol=2e-2 if dtype == BF else 1e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, BF])
+def test_slice_split_stack_repeat(dtype):
+    torch.manual_seed(4)
+    x = torch.randn(4, 9, 10, device=DEV).to(dtype).requires_grad_(True)
+    xr = x.detach().clone().requires_grad_(True)
+    y = ops.slice_nd(x, [1, 0, 2], [4, 9, 10], [1, 2, 3])
+    ref = xr[1:4, 0:9:2, 2:10:3]
+    assert torch.equal(y, ref.contiguous())
+    g = torch.randn_like(y)
+    assert torch.equal(torch.autograd.grad(y, x, g)[0], torch.autograd.grad(ref, xr, g)[0])
+
+    parts, rparts = ops.split(x, 4, 1), torch.split(xr, 4, 1)
+    assert len(parts) == len(rparts) == 3
+    for a, b in zip(parts, rparts):
+        assert torch.equal(a, b.contiguous())
+    gs = [torch.randn_like(a) for a in parts]
+    ga = torch.autograd.grad(parts, x, gs)[0]
+    gb = torch.autograd.grad(rparts, xr, gs)[0]
+    assert torch.equal(ga, gb)
+
+    for dim in (0, 1, 3, -1):
+        s, sr = ops.stack([x, x * 2], dim), torch.stack([xr, xr * 2], dim)
+        assert torch.equal(s, sr)
+        g = torch.randn_like(s)
+        assert torch.allclose(torch.autograd.grad(s, x, g)[0].float(), torch.autograd.grad(sr, xr, g)[0].float(),
+                              atol=2e-2, rtol=2e-2)
+
+    for dim in (0, 1, 2):
+        r, rr = ops.repeat_interleave(x, 3, dim), torch.repeat_interleave(xr, 3, dim=dim)
+        assert torch.equal(r, rr)
+        g = torch.randn_like(r)
+        assert torch.allclose(torch.autograd.grad(r, x, g)[0].float(), torch.autograd.grad(rr, xr, g)[0].float(),
+                              atol=5e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, BF])
+def test_masked_fill_and_outer(dtype):
+    torch.manual_seed(5)
+    x = torch.randn(3, 8, 8, device=DEV).to(dtype).requires_grad_(True)
+    xr = x.detach().clone().requires_grad_(True)
+    for mask in (torch.triu(torch.ones(8, 8, device=DEV), 1).bool(), torch.triu(torch.ones(8, 8, device=DEV), 1).to(dtype)):
+        y = ops.masked_fill(x, mask, -1e4)
+        ref = xr.masked_fill(mask != 0, -1e4)
+        assert torch.equal(y, ref)
+        g = torch.randn_like(y)
+        assert torch.equal(torch.autograd.grad(y, x, g)[0], torch.autograd.grad(ref, xr, g)[0])
+    a = torch.randn(37, device=DEV).to(dtype).requires_grad_(True)
+    b = torch.randn(70, device=DEV).to(dtype).requires_grad_(True)
+    ar, br = a.detach().float().requires_grad_(True), b.detach().float().requires_grad_(True)
+    o, orf = ops.outer(a, b), torch.outer(ar, br)
+    tol = dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=8e-2, rtol=2e-2)
+    assert torch.allclose(o.float(), orf, **tol)
+    g = torch.randn_like(orf)
+    da, db = torch.autograd.grad(o, (a, b), g.to(dtype))
+    dar, dbr = torch.autograd.grad(orf, (ar, br), g)
+    assert torch.allclose(da.float(), dar, **tol) and torch.allclose(db.float(), dbr, **tol)
+    _status_ok()
+
+
+def _fw(t, dev, requires_grad=False):
+    ft = C.FwTensor(t.clone(), requires_grad)
+    return ft.To(dev) if dev != "cpu" else ft
+
+
+def _facade_run(dev):
+    """A tour through the C++ facade's view-like, reduction and mask Functions; returns every result as CPU tensors."""
+    torch.manual_seed(8)
+    out = {}
+    x0 = torch.randn(3, 4, 6)
+    x = _fw(x0, dev, True)
+    parts = x.Split(2, 2)                                            # Split (multi-output) -> gather kernel
+    y = parts[0].Mul(parts[1]).Add(parts[2])
+    y = y.Transpose(0, 1)                                            # Transpose -> gather kernel
+    y = y.RepeatInterleave(2, 2)                                     # stride-0 gather / sum backward
+    y = y.Slice([0, 1, 0], [4, 3, 4], [1, 1, 2])                     # Slice -> gather fwd, scatter bwd
+    s = C.fw_function("Stack", [1]).Apply([y, y.MulScalar(2.0)])[0]  # Stack -> scatter fwd, gather bwd
+    sm = C.fw_function("Softmax", [2]).Apply([s])[0]
+    red = C.fw_function("Sum", [3, 0]).Apply([sm.Mul(s)])[0]
+    red = C.fw_function("Max", [0, 1]).Apply([red])[0]
+    red = C.fw_function("Mean", [2, 0]).Apply([red])[0]
+    red = C.fw_function("Min", [1, 0]).Apply([red])[0]
+    out["y"], out["stack"], out["softmax"], out["red"] = y.torch(), s.torch(), sm.torch(), red.torch()
+    red.Backward(_fw(torch.ones(1), dev))
+    out["dx"] = x.grad().torch()
+    m0 = torch.tril(torch.ones(6, 6))
+    a = _fw(torch.randn(2, 6, 6), dev, True)
+    tri = C.fw_function("Tril", [0]).Apply([_fw(torch.ones(6, 6), dev)])[0]
+    masked = a.MaskedFill(tri.Equals(0.0), -1e4)
+    out["tril"], out["masked"] = tri.torch(), masked.torch()
+    C.fw_function("Sum", [0, 0]).Apply([C.fw_function("Sum", [2, 0]).Apply([masked])[0]])[0].Backward(_fw(torch.ones(6), dev))
+    out["da"] = a.grad().torch()
+    ge_in = _fw(torch.randn(4, 9), dev, True)
+    ge = C.fw_function("Gelu").Apply([ge_in])[0]                     # one kernel on the GPU
+    C.fw_function("Sum", [0, 0]).Apply([C.fw_function("Sum", [1, 0]).Apply([ge])[0]])[0].Backward()
+    out["gelu"], out["dgelu"] = ge.torch(), ge_in.grad().torch()
+    u, v = _fw(torch.randn(5), dev, True), _fw(torch.randn(7), dev, True)
+    o = u.Outer(v)
+    out["outer"] = o.torch()
+    C.fw_function("Sum", [0, 0]).Apply([C.fw_function("Sum", [1, 0]).Apply([o.Mul(o)])[0]])[0].Backward()
+    out["du"], out["dv"] = u.grad().torch(), v.grad().torch()
+    assert torch.equal(m0, out["tril"].cpu())
+    return {k: t.detach().float().cpu() for k, t in out.items()}
+
+
+def test_cpp_facade_cuda_ops_match_cpu_oracle():
+    cpu, gpu = _facade_run("cpu"), _facade_run("cuda:0")
+    for k in cpu:
+        assert cpu[k].shape == gpu[k].shape, k
+        tol = 2e-3 if "gelu" in k else 1e-5   # the GPU GELU uses tanh.approx
+        assert torch.allclose(cpu[k], gpu[k], atol=tol, rtol=tol), k
+    _status_ok()
+
+
+def test_cpp_llama3_and_gpt2_on_cuda_match_the_cpu_facade():
+    """The C++ models moved to cuda:0 (kernel-backed RMSNorm / Rope / SwiGLU / Gelu / LayerNorm / softmax / SGEMM and the
+    gather kernel behind every transpose and slice) against the same models on the CPU."""
+    g = torch.Generator().manual_seed(2)
+    idx, tgt = torch.randint(0, 150, (2, 16), generator=g), torch.randint(0, 150, (2, 16), generator=g)
+    for make in (lambda: C.FwLLaMA3(32, 150, 2, 4, 2, 32, 48), lambda: C.FwGPT2(32, 150, 2, 4, 32)):
+        res = {}
+        for dev in ("cpu", "cuda:0"):
+            model = make()                       # seeded initialisation: identical weights in both runs
+            if not dev.startswith("cpu"):
+                model.To(dev)
+            put = (lambda t: C.FwTensor(t).To(dev)) if not dev.startswith("cpu") else C.FwTensor
+            logits = model.Forward([put(idx)])[0]
+            loss = C.FwCrossEntropyLoss().Forward([logits, put(tgt)])[0]
+            loss.Backward()
+            grads = {k: v.grad().torch().float().cpu() for k, v in model.StateDict().items() if v.grad() is not None}
+            res[dev] = (logits.torch().detach().float().cpu(), float(loss.torch().detach()), grads)
+        assert torch.allclose(res["cpu"][0], res["cuda:0"][0], atol=2e-3, rtol=1e-3)
+        assert abs(res["cpu"][1] - res["cuda:0"][1]) < 1e-3
+        for k, gcpu in res["cpu"][2].items():
+            assert torch.allclose(gcpu, res["cuda:0"][2][k], atol=2e-3, rtol=1e-2), k
+    _status_ok()
+
+
+def test_cpp_models_in_bf16_use_the_flash_attention_function():
+    """C++ GPT-2 (hd 64) and LLaMA-3 (hd 64, grouped-query) cast to bf16 on cuda:0: attention runs as the fused
+    CausalAttention Function (tcgen05 kernels); logits and loss stay close to the fp32 CPU model."""
+    g = torch.Generator().manual_seed(3)
+    idx, tgt = torch.randint(0, 300, (2, 128), generator=g), torch.randint(0, 300, (2, 128), generator=g)
+    for make in (lambda: C.FwGPT2(128, 300, 2, 2, 128), lambda: C.FwLLaMA3(128, 300, 2, 4, 2, 256, 512)):
+        ref_model = make()
+        ref = ref_model.Forward([C.FwTensor(idx)])[0].torch()
+        model = make()
+        model.To("cuda:0")
+        model.ToDtype("bfloat16")
+        logits = model.Forward([C.FwTensor(idx).To("cuda:0")])[0]
+        loss = C.FwCrossEntropyLoss().Forward([logits, C.FwTensor(tgt).To("cuda:0")])[0]
+        loss.Backward()
+        assert logits.torch().dtype == torch.bfloat16
+        assert (logits.torch().float().cpu() - ref).abs().max() < 0.1
+        grads = [v.grad().torch() for v in model.StateDict().values() if v.grad() is not None]
+        assert grads and all(torch.isfinite(x.float()).all() for x in grads)
+        assert any(float(x.float().abs().max()) > 0 for x in grads)
+    _status_ok()
+
+
+def test_cpp_api_program_passes_on_cuda(tmp_path):
+    """The stand-alone C++ test program (reference gtest cases + data layer + a short GPT-2 run) on cuda:0."""
+    from tinyinfinitrain_b200 import _build
+
+    built = _build.build_cpp()
+    r = subprocess.run([str(built["facade_api_test"]), "cuda", str(tmp_path)], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "all checks passed" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_zero1_bucketed_overlap_matches_single_bucket():
+    n = min(torch.cuda.device_count(), 8)
+    env = _multi_rank_env(TITB_TEST_ZERO_BUCKETS="3")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29900 + os.getpid() % 90), os.path.join(HERE, "dist_zero_check.py")]
+    r = run_group(cmd, env=env, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_zero1_fused_gradient_clipping_matches_nccl():
+    n = min(torch.cuda.device_count(), 8)
+    env = _multi_rank_env(TITB_TEST_ZERO_CLIP="0.5")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29850 + os.getpid() % 90), os.path.join(HERE, "dist_zero_check.py")]
+    r = run_group(cmd, env=env, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_symmetric_collectives_match_nccl():
+    n = min(torch.cuda.device_count(), 8)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29750 + os.getpid() % 90), os.path.join(HERE, "dist_collectives_check.py")]
+    r = run_group(cmd, env=_multi_rank_env(), timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_zero1_on_the_native_symmetric_heap():
+    """The ZeRO-1 worker with buffers from this package's own heap (cuMem VMM + descriptor passing) instead of
+    PyTorch's symmetric-memory allocator."""
+    n = min(torch.cuda.device_count(), 8)
+    env = _multi_rank_env(TITB200_SYMM_HEAP="native")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29990 - os.getpid() % 90), os.path.join(HERE, "dist_zero_check.py")]
+    r = run_group(cmd, env=env, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
