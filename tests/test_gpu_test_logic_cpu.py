@@ -7,12 +7,77 @@ import pytest
 import torch
 
 
+def _bytes_at(ptr, nbytes):
+    """A uint8 view of `nbytes` bytes of host memory at address `ptr`, found among the live CPU tensors (the tests
+    hand raw addresses to the kernels, as they do on the GPU)."""
+    import gc
+
+    for o in gc.get_objects():
+        if isinstance(o, torch.Tensor) and o.device.type == "cpu" and o.numel() and o.is_contiguous():
+            base, size = o.data_ptr(), o.numel() * o.element_size()
+            if base <= ptr and ptr + nbytes <= base + size:
+                return o.view(-1).view(torch.uint8)[ptr - base: ptr - base + nbytes]
+    raise LookupError(hex(ptr))
+
+
 class Restated:
     """Contracts of the entry points the tests call, in plain PyTorch (fp32 math, results in the kernels' dtypes)."""
 
     @staticmethod
     def status_read(clear=True):
-        return 0
+        st = Restated._status
+        if clear:
+            Restated._status = 0
+        return st
+
+    @staticmethod
+    def symm_allreduce(ptrs, mc_ptr, byte_off, nbytes, dtype, rank, scale=1.0, max_blocks=0):
+        world, dt = len(ptrs), (torch.bfloat16 if dtype == 1 else torch.float32)
+        sl = nbytes // world                                  # this rank reduces and publishes its slice only
+        lo = byte_off + rank * sl
+        views = [_bytes_at(p + lo, sl).view(dt) for p in ptrs]
+        total = sum(v.float() for v in views) * scale
+        for v in views:
+            v.copy_(total.to(dt))
+
+    @staticmethod
+    def symm_allgather(ptrs, mc_ptr, byte_off, nbytes, rank, max_blocks=0):
+        sl = nbytes // len(ptrs)
+        lo = byte_off + rank * sl
+        mine = _bytes_at(ptrs[rank] + lo, sl).clone()
+        for p in ptrs:
+            _bytes_at(p + lo, sl).copy_(mine)
+
+    @staticmethod
+    def symm_signal(word, value):
+        _bytes_at(word, 4).view(torch.int32)[0] = value
+
+    @staticmethod
+    def symm_wait(word, value, timeout_s=2.0):
+        have = int(_bytes_at(word, 4).view(torch.int32)[0])
+        if have - value < 0:
+            Restated._status = 2                               # nothing will ever publish it here: the wait runs out
+
+    _status = 0
+
+    @staticmethod
+    def gemm_param_gather(x, w, peer_ptrs, rank, epilogue=0, bias=None, aux_in=None, want_aux_out=False, helper_ctas=8,
+                          tile_n=0):
+        world = len(peer_ptrs)
+        N, K = w.shape
+        npr, row_bytes = N // world, K * w.element_size()
+        for r in range(world):                                 # rows are fetched from the memory of the rank that owns them
+            rows = _bytes_at(peer_ptrs[r], npr * row_bytes).view(w.dtype).view(npr, K)
+            if rows.data_ptr() != w[r * npr].data_ptr():
+                w[r * npr:(r + 1) * npr] = rows
+        y = x.float() @ w.float().t()
+        if bias is not None:
+            y = y + bias.float()
+        return [y.to(x.dtype)]
+
+    @staticmethod
+    def gemm(a, b, *args, **kwargs):
+        return [(a.float() @ b.float().t()).to(a.dtype)]
 
     @staticmethod
     def attn_bwd_set_warps(warps):
@@ -140,3 +205,21 @@ def test_attention_variant_test_logic(gpu_tests, monkeypatch, B, T, Hq, Hkv, hd)
 
 def test_norm_fork_test_logic(gpu_tests, monkeypatch):
     gpu_tests.test_norm_fork_folds_the_residual_gradient(monkeypatch)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("world", [2, 8])
+def test_symmetric_collective_test_logic(gpu_tests, monkeypatch, dtype, world):
+    monkeypatch.setattr(torch.cuda, "synchronize", lambda *a, **k: None)
+    gpu_tests.test_symmetric_collective_kernels_on_one_gpu(dtype, world)
+
+
+def test_flag_test_logic(gpu_tests, monkeypatch):
+    monkeypatch.setattr(torch.cuda, "synchronize", lambda *a, **k: None)
+    gpu_tests.test_point_to_point_flag_signal_then_wait_and_bounded_timeout()
+
+
+@pytest.mark.parametrize("world,npr,M,K,bias", [(2, 128, 300, 264, False), (4, 256, 64, 96, True), (1, 384, 128, 128, False)])
+def test_parameter_gather_test_logic(gpu_tests, monkeypatch, world, npr, M, K, bias):
+    monkeypatch.setattr(torch.cuda, "synchronize", lambda *a, **k: None)
+    gpu_tests.test_parameter_gather_gemm_on_one_gpu(world, npr, M, K, bias)
