@@ -16,9 +16,17 @@ from tinyinfinitrain_b200.parallel.collectives import SymmCollective  # noqa: E4
 
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
-    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank)))
-    torch.cuda.set_device(dev)
-    dist.init_process_group("nccl", device_id=dev)
+    # TITB_TEST_DEVICE=cpu: the same script over gloo ranks and the CPU fallbacks of the same classes -- a dry run of
+    # this script's own logic (references, tolerances, call signatures) that needs no GPU
+    on_gpu = os.environ.get("TITB_TEST_DEVICE", "cuda") != "cpu"
+    if on_gpu:
+        dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank)))
+        torch.cuda.set_device(dev)
+        dist.init_process_group("nccl", device_id=dev)
+    else:
+        dev = torch.device("cpu")
+        dist.init_process_group("gloo")
+    sync = torch.cuda.synchronize if on_gpu else (lambda: None)
     ok = True
     for dtype in (torch.float32, torch.bfloat16):
         c = SymmCollective(1 << 20, dtype, dev)
@@ -31,7 +39,7 @@ def main():
             if average:
                 ref /= world
             c.all_reduce_(average=average)
-            torch.cuda.synchronize()
+            sync()
             tol = 1e-5 if dtype == torch.float32 else 3e-2
             err = (c.tensor.float() - ref).abs().max().item()
             ok = ok and err <= tol * max(1.0, ref.abs().max().item())
@@ -42,17 +50,21 @@ def main():
         # sub-range, captured in a graph and replayed with new data
         per = 16 * world // c.esize
         off, n = 3 * per, 1000 * per
-        graph = torch.cuda.CUDAGraph()
         c.tensor.copy_(x)
         c.all_reduce_(numel=n, offset=off)                     # warm-up outside of the capture
-        torch.cuda.synchronize()
-        with torch.cuda.graph(graph):
-            c.all_reduce_(numel=n, offset=off)
+        sync()
+        if on_gpu:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                c.all_reduce_(numel=n, offset=off)
+            replay = graph.replay
+        else:
+            replay = lambda: c.all_reduce_(numel=n, offset=off)
         for it in range(2):
             y = (x * (it + 2)).to(dtype)
             c.tensor.copy_(y)
-            graph.replay()
-            torch.cuda.synchronize()
+            replay()
+            sync()
             ref = y.float()[off:off + n].clone()
             dist.all_reduce(ref)
             tol = 1e-5 if dtype == torch.float32 else 3e-2
@@ -63,11 +75,11 @@ def main():
         sl = c.numel // world
         c.tensor[rank * sl:(rank + 1) * sl] = x[rank * sl:(rank + 1) * sl]
         c.all_gather_()
-        torch.cuda.synchronize()
+        sync()
         parts = [torch.empty(sl, dtype=dtype, device=dev) for _ in range(world)]
         dist.all_gather(parts, x[rank * sl:(rank + 1) * sl].contiguous())
         ok = ok and torch.equal(c.tensor, torch.cat(parts))
-        print(f"rank {rank}: {dtype} multimem={'yes' if c.buf.mc_ptr else 'no'} ok={ok}", flush=True)
+        print(f"rank {rank}: {dtype} multimem={'yes' if (c.buf is not None and c.buf.mc_ptr) else 'no'} ok={ok}", flush=True)
 
     # plain data parallelism: symmetric all-reduce against NCCL
     finals = []
@@ -82,7 +94,7 @@ def main():
                 p.grad = None
             net(xb).float().pow(2).mean().backward()
             opt.step()
-        torch.cuda.synchronize()
+        sync()
         finals.append(torch.cat([p.detach().float().flatten() for p in net.parameters()]))
     e = (finals[0] - finals[1]).abs().max().item()
     ok = ok and e < 2e-2
@@ -115,12 +127,12 @@ def main():
         ropt.zero_grad()
         (sum(ref2(torch.tanh(ref1(x))).pow(2).mean() for x in xs) / world).backward()
         ropt.step()
-    torch.cuda.synchronize()
+    sync()
     ew = max((l.weight[l.own_rows()].float() - r.weight[l.own_rows()].detach()).abs().max().item() for l, r in ((l1, ref1), (l2, ref2)))
     moved = (l1.weight[l1.own_rows()].float() - w_init).abs().max().item()
     ok = ok and ew < 8e-3 and moved > 1e-3        # near-zero gradients may flip sign in bf16: up to 2 lr per step apart
     print(f"rank {rank}: row-sharded layers vs replicated fp32 AdamW max|dw|={ew:.3e} ok={ok}", flush=True)
-    status = C.status_read(True)
+    status = C.status_read(True) if on_gpu else 0
     ok = ok and status == 0
     print(f"rank {rank}: data-parallel nccl-vs-symm max|dp|={e:.3e} status={status} ok={ok}", flush=True)
     t = torch.tensor([1.0 if ok else 0.0], device=dev)

@@ -83,3 +83,15 @@ def test_slice_arithmetic_of_the_kernels():
                 covered[so:so + sv] += 1
             assert int(covered[:byte_off // 16].sum()) == 0 and int(covered[-2:].sum()) == 0
             assert torch.all(covered[byte_off // 16:byte_off // 16 + nbytes // 16] == 1)
+
+
+def test_multi_gpu_check_script_dry_run_over_gloo():
+    """tests/dist_collectives_check.py, the job the multi-GPU test launches, with TITB_TEST_DEVICE=cpu: the script's own
+    logic (references, tolerances, call signatures) runs over two gloo ranks and the CPU fallbacks of the same classes."""
+    from _launch import run_group
+
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(29150 + os.getpid() % 40), os.path.join(ROOT, "tests", "dist_collectives_check.py")]
+    r = run_group(cmd, env=dict(os.environ, TITB_TEST_DEVICE="cpu"), timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "row-sharded layers" in r.stdout and "ok=True" in r.stdout
