@@ -184,6 +184,22 @@ def test_cpp_gpt2_matches_python_model_and_llmc_roundtrip():
                           py.StateDict()["transformer.h.0.attn.c_attn.weight"])
 
 
+def test_attention_masks_are_buffers_of_the_module_tree():
+    """The causal masks are registered buffers (the reference's "bias"), reachable from the root by dotted name, so the
+    recursive Module::To(Device) moves them together with the parameters (the move itself is checked on a GPU)."""
+    from tinyinfinitrain_b200._lib import C
+
+    for model, layers in ((C.FwGPT2(16, 50, 2, 2, 16), 2), (C.FwLLaMA3(16, 50, 3, 2, 1, 16, 24), 3)):
+        bufs = model.Buffers()
+        names = sorted(k for k in bufs if k.endswith(".attn.bias"))
+        assert len(names) == layers, names
+        for k in names:
+            m = bufs[k].torch()
+            assert m.shape == (16, 16) and torch.equal(m, torch.triu(torch.ones(16, 16), 1))
+            assert "CPU" in bufs[k].GetDevice()
+        assert not any(k.endswith(".attn.bias") for k in model.StateDict())   # buffers are not parameters
+
+
 def test_save_as_npy_and_print(tmp_path):
     import numpy as np
 

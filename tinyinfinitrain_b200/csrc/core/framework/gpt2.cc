@@ -27,11 +27,8 @@ CausalSelfAttention::CausalSelfAttention(const GPT2Config& config) : Module("Cau
   TORCH_CHECK(config.n_embd % config.n_head == 0, "n_embd must be divisible by n_head");
   AddModule(kCAttnLayerName, std::make_shared<nn::Linear>(config.n_embd, 3 * config.n_embd));
   AddModule(kCProjLayerName, std::make_shared<nn::Linear>(config.n_embd, config.n_embd));
-  mask_ = std::make_shared<Tensor>(at::triu(at::ones({config.block_size, config.block_size}, at::kFloat), 1));
-}
-void CausalSelfAttention::To(Device device) {
-  Module::To(device);
-  mask_ = std::make_shared<Tensor>(mask_->To(device));
+  // registered as a buffer (the reference's "bias"), so that a To(device) issued on any ancestor moves it too
+  buffers_[kMaskBufferName] = std::make_shared<Tensor>(at::triu(at::ones({config.block_size, config.block_size}, at::kFloat), 1));
 }
 TensorList CausalSelfAttention::Forward(const TensorList& in) {
   const TP& x = in[0];
@@ -47,7 +44,7 @@ TensorList CausalSelfAttention::Forward(const TensorList& in) {
   auto heads = [&](const TP& t) { return t->View({B, T, H, hd})->Transpose(1, 2); };  // [B, H, T, hd]
   TP q = heads(qkv[0]), k = heads(qkv[1]), v = heads(qkv[2]);
   TP att = q->Matmul(k->Transpose(-2, -1)) * (1.0f / std::sqrt(static_cast<float>(hd)));
-  TP mask = mask_->Slice({0, 0}, {T, T}, {1, 1});
+  TP mask = buffers_.at(kMaskBufferName)->Slice({0, 0}, {T, T}, {1, 1});
   att = att->MaskedFill(mask, -std::numeric_limits<float>::infinity());
   att = nn::function::Softmax(att, -1);
   TP y = att->Matmul(v)->Transpose(1, 2)->Contiguous()->View({B, T, C});

@@ -31,10 +31,9 @@ class CausalSelfAttention : public nn::Module {
   static constexpr char kCProjLayerName[] = "c_proj";
   explicit CausalSelfAttention(const GPT2Config& config);
   nn::TensorList Forward(const nn::TensorList& x) override;
-  void To(Device device) override;
+  static constexpr char kMaskBufferName[] = "bias";  // buffer: 1 where attention is NOT allowed, [block, block]
  private:
   GPT2Config config_;
-  std::shared_ptr<Tensor> mask_;  // 1 where attention is NOT allowed, [block, block]
 };
 class MLP : public nn::Module {
  public:

@@ -24,17 +24,15 @@ LLaMA3Attention::LLaMA3Attention(const LLaMA3Config& config) : Module("CausalSel
   AddModule(kCAttnLayerName, linear_no_bias(config.n_embd, (config.n_head + 2 * config.n_kv_head) * hd));
   AddModule(kCProjLayerName, linear_no_bias(config.n_embd, config.n_embd));
   const int64_t m = std::min<int64_t>(config.block_size, 4096);
-  mask_ = std::make_shared<Tensor>(at::triu(at::ones({m, m}, at::kFloat), 1));
-}
-void LLaMA3Attention::To(Device device) {
-  Module::To(device);
-  mask_ = std::make_shared<Tensor>(mask_->To(device));
+  // a buffer, so that a To(device) issued on any ancestor moves it too
+  buffers_[kMaskBufferName] = std::make_shared<Tensor>(at::triu(at::ones({m, m}, at::kFloat), 1));
 }
 TensorList LLaMA3Attention::Forward(const TensorList& in) {
   const TP& x = in[0];
   const int64_t B = x->Dims()[0], T = x->Dims()[1], C = x->Dims()[2];
   const int64_t Hq = config_.n_head, Hkv = config_.n_kv_head, hd = config_.head_dim(), group = Hq / Hkv;
-  TORCH_CHECK(T <= mask_->Dims()[0], "sequence longer than the attention mask of this facade model");
+  const TP& mask = buffers_.at(kMaskBufferName);
+  TORCH_CHECK(T <= mask->Dims()[0], "sequence longer than the attention mask of this facade model");
   TP qkv = modules_[kCAttnLayerName]->Forward({x})[0];                                  // [B, T, (Hq + 2 Hkv) hd]
   auto part = [&](int64_t first_head, int64_t heads) {
     return qkv->Slice(2, first_head * hd, (first_head + heads) * hd)->View({B, T, heads, hd});
@@ -53,7 +51,7 @@ TensorList LLaMA3Attention::Forward(const TensorList& in) {
     v = v->RepeatInterleave(group, 1);
   }
   TP att = q->Matmul(k->Transpose(-2, -1)) * (1.0f / std::sqrt(static_cast<float>(hd)));
-  att = att->MaskedFill(mask_->Slice({0, 0}, {T, T}, {1, 1}), -std::numeric_limits<float>::infinity());
+  att = att->MaskedFill(mask->Slice({0, 0}, {T, T}, {1, 1}), -std::numeric_limits<float>::infinity());
   att = nn::function::Softmax(att, -1);
   TP y = att->Matmul(v)->Transpose(1, 2)->Contiguous()->View({B, T, C});
   return modules_[kCProjLayerName]->Forward({y});

@@ -32,10 +32,9 @@ class LLaMA3Attention : public nn::Module {
   static constexpr char kCProjLayerName[] = "c_proj";
   explicit LLaMA3Attention(const LLaMA3Config& config);
   nn::TensorList Forward(const nn::TensorList& x) override;
-  void To(Device device) override;
+  static constexpr char kMaskBufferName[] = "bias";  // buffer: 1 where attention is NOT allowed (min(block, 4096) square)
  private:
   LLaMA3Config config_;
-  std::shared_ptr<Tensor> mask_;  // 1 where attention is NOT allowed, [block, block] (built for min(block, 4096))
 };
 class LLaMA3MLP : public nn::Module {
  public:

@@ -58,6 +58,13 @@ std::unordered_map<std::string, TP> Module::StateDict() const {
     for (const auto& [k, v] : m->StateDict()) out.emplace(mname + "." + k, v);
   return out;
 }
+std::unordered_map<std::string, TP> Module::Buffers() const {
+  std::unordered_map<std::string, TP> out;
+  for (const auto& [name, b] : buffers_) out.emplace(name, b);
+  for (const auto& [mname, m] : modules_)
+    for (const auto& [k, v] : m->Buffers()) out.emplace(mname + "." + k, v);
+  return out;
+}
 TensorList Module::Forward(const TensorList&) { TORCH_CHECK(false, "Forward not implemented for ", type_); }
 void Module::To(Device device) {
   if (device == device_) return;

@@ -35,6 +35,8 @@ class Module : public std::enable_shared_from_this<Module> {
   Module* mutable_module(const std::string& name);
   const Module& module(const std::string& name) const;
   std::unordered_map<std::string, std::shared_ptr<Tensor>> StateDict() const;
+  // Non-parameter tensors (e.g. the attention mask "bias"), dotted names like StateDict(); To(Device) moves them too.
+  std::unordered_map<std::string, std::shared_ptr<Tensor>> Buffers() const;
   virtual TensorList Forward(const TensorList& input_tensors);
   virtual void To(Device device);
   // Casts every parameter (ties kept) to `dtype`, e.g. kBFLOAT16 for tensor-core training on the GPU (not in the

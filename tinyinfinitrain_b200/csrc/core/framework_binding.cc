@@ -168,6 +168,7 @@ void bind_framework(pybind11::module_& m) {
       .def("type", &nn::Module::type)
       .def("Parameters", &nn::Module::Parameters)
       .def("StateDict", &nn::Module::StateDict)
+      .def("Buffers", &nn::Module::Buffers)
       .def("Forward", &nn::Module::Forward)
       .def("has_parameter", &nn::Module::has_parameter)
       .def("parameter", &nn::Module::parameter)
