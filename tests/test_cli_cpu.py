@@ -82,3 +82,24 @@ def test_restart_after_failure_recipe(tmp_path):
     assert sorted(second) == [4, 5]
     full = _step_losses(_run(cmd[:-4] + ["--num_iteration", "5"]))        # no --save / --resume: uninterrupted
     assert abs(second[5] - full[5]) < 1e-5
+
+
+def test_multi_rank_save_writes_a_full_llmc_file_and_refuses_another_layout(tmp_path):
+    """TP2 x PP2: rank 0 reassembles the full tensors from every rank's slices and writes model.bin in the llm.c layout
+    (which has ONE wte: the first stage's embedding and the last stage's output projection must still be equal after
+    training, or the save refuses).  Resuming the optimizer shards under another layout is refused with a clear message."""
+    sys.path.insert(0, ROOT)
+    ck = str(tmp_path / "ck")
+    base = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "4", "--master-addr",
+            "127.0.0.1", "--master-port", str(29650 + os.getpid() % 200), "examples/gpt2/main.py"] + COMMON
+    _run(base + ["--tensor_parallel", "2", "--pipeline_parallel", "2", "--num_microbatches", "2", "--save", ck,
+                 "--learning_rate", "1e-2"])
+    assert os.path.exists(os.path.join(ck, "model.bin")) and os.path.exists(os.path.join(ck, "optim_rank3.pt"))
+    from tinyinfinitrain_b200.utils.llmc import load_gpt2
+
+    m = load_gpt2(os.path.join(ck, "model.bin"))
+    sd = m.StateDict()
+    assert sd["transformer.wte.weight"].shape[1] == 64 and sd["transformer.h.1.mlp.c_fc.weight"].shape == (256, 64)
+    assert float(sd["transformer.h.0.attn.c_attn.weight"].abs().sum()) > 0
+    r = run_group(base + ["--tensor_parallel", "4", "--resume", ck, "--num_iteration", "4"], cwd=ROOT, timeout=600)
+    assert r.returncode != 0 and "this job runs tp=4" in (r.stdout + r.stderr)

@@ -111,3 +111,17 @@ def test_generate_text_walks_the_window(tmp_path):
 
     text = tk.GenerateText(Peaked(), 2, 16, 9, "cpu")
     assert text == "The meaning of life is" + "<319><320><321><322>"       # 4 tokens after the 5-token prompt (318 + 1 ...)
+
+
+def test_drop_last_serves_full_batches_and_equal_counts_per_rank():
+    """11 samples, batch 2, 2 ranks: 5 full batches -> 2 per rank (the 5th full batch and the short one are dropped);
+    without drop_last rank 0 gets 3 batches, rank 1 gets 3 and its last one is short."""
+    from tinyinfinitrain_b200 import data
+
+    ds = data.SyntheticDataset(1, 100, 8, 11)
+    for rank in range(2):
+        dl = data.DataLoader(ds, 2, rank=rank, world=2, drop_last=True)
+        assert len(dl) == 2
+        assert all(dl.batch(i)[0].shape == (2, 8) for i in range(len(dl)))
+    loose = [data.DataLoader(ds, 2, rank=r, world=2) for r in range(2)]
+    assert [len(d) for d in loose] == [3, 3] and loose[1].batch(2)[0].shape == (1, 8)

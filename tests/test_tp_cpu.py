@@ -32,6 +32,26 @@ def _worker(rank, world, port, q, which):
                                     ffn_dim=96), LLaMA3
         full = cls(cfg)
         tp = TPTransformer(cfg, comm)
+        # same seed => every rank's parameters are exactly its slices of the single-process model's
+        want = shard_state_dict({k: v.detach() for k, v in full.StateDict().items()}, cfg, world, rank,
+                                vocab_padded=tp.vocab_padded)
+        seeded_ok = True
+        for name, p in tp.named_parameters(remove_duplicate=False):
+            if name in want:
+                seeded_ok = seeded_ok and torch.equal(p.detach(), want[name].to(p.dtype))
+        # tensors too large to draw in full on the host: shards differ between ranks and between layers,
+        # replicated parameters stay identical across the group
+        tp.reset_parameters(42, exact_limit=0)
+        mine = {n: p.detach().clone() for n, p in tp.named_parameters()}
+        k0, k1 = "transformer.h.0.mlp.c_fc.weight", "transformer.h.1.mlp.c_fc.weight"
+        seeded_ok = seeded_ok and not torch.equal(mine[k0], mine[k1])
+        gathered = [torch.empty_like(mine[k0]) for _ in range(world)]
+        dist.all_gather(gathered, mine[k0])
+        seeded_ok = seeded_ok and not torch.equal(gathered[0], gathered[1])
+        rep = "transformer.h.0.ln_1.weight" if which == "llama3" else "transformer.wpe.weight"
+        gathered = [torch.empty_like(mine[rep]) for _ in range(world)]
+        dist.all_gather(gathered, mine[rep])
+        seeded_ok = seeded_ok and torch.equal(gathered[0], gathered[1])
         tp.load_full_state_dict(full.StateDict())
         g = torch.Generator().manual_seed(7)
         idx = torch.randint(0, cfg.vocab_size, (2, 16), generator=g)
@@ -48,7 +68,7 @@ def _worker(rank, world, port, q, which):
             if name in ref and p.grad is not None:
                 r = ref[name]
                 worst = max(worst, (p.grad[:r.shape[0]] - r).abs().max().item())
-        q.put((rank, ok and worst < 1e-4, l0.item(), l1.item(), worst))
+        q.put((rank, ok and worst < 1e-4 and seeded_ok, l0.item(), l1.item(), worst, seeded_ok))
     finally:
         dist.destroy_process_group()
 
@@ -65,3 +85,24 @@ def test_tp2_matches_single_process(which):
     for p in procs:
         p.join(timeout=30)
     assert all(r[1] for r in res), res
+
+
+@pytest.mark.parametrize("which,tp", [("gpt2", 2), ("gpt2", 3), ("llama3", 2), ("llama3", 4)])
+def test_unshard_inverts_shard(which, tp):
+    sys.path.insert(0, ROOT)
+    from tinyinfinitrain_b200.models import GPT2, GPT2Config, LLaMA3, LLaMA3Config
+    from tinyinfinitrain_b200.models.tp_models import shard_state_dict, unshard_state_dict
+
+    if which == "gpt2":
+        cfg, cls = GPT2Config(block_size=16, vocab_size=250, n_layer=1, n_head=6, n_embd=48), GPT2
+        rows = cfg.padded_vocab_size
+    else:
+        cfg, cls = LLaMA3Config(block_size=16, vocab_size=256, n_layer=1, n_head=8, n_kv_head=4, n_embd=64, ffn_dim=96), LLaMA3
+        rows = cfg.vocab_size
+    full = {k: v.detach() for k, v in cls(cfg).StateDict().items()}
+    padded = (rows + 128 * tp - 1) // (128 * tp) * (128 * tp)
+    shards = [shard_state_dict(full, cfg, tp, r, vocab_padded=padded) for r in range(tp)]
+    back = unshard_state_dict(shards, cfg, rows)
+    assert set(back) == set(full)
+    for k in full:
+        assert torch.equal(back[k], full[k]), k

@@ -82,7 +82,7 @@ def _config(family: str, args):
     return cfg
 
 
-def _data(args, cfg, rank_dp: int, world_dp: int, pin: bool):
+def _data(args, cfg, rank_dp: int, world_dp: int, pin: bool, drop_last: bool = False):
     from . import data
 
     if args.input_bin and not args.synthetic:
@@ -90,7 +90,7 @@ def _data(args, cfg, rank_dp: int, world_dp: int, pin: bool):
     else:
         n = max(64, args.batch_size * world_dp * 8)
         ds = data.SyntheticDataset(args.seed, cfg.vocab_size, args.sequence_length, n)
-    return data.DataLoader(ds, args.batch_size, pin_memory=pin, rank=rank_dp, world=world_dp)
+    return data.DataLoader(ds, args.batch_size, pin_memory=pin, rank=rank_dp, world=world_dp, drop_last=drop_last)
 
 
 def train_main(family: str, argv=None) -> int:
@@ -182,71 +182,42 @@ def train_main(family: str, argv=None) -> int:
         return 0
 
     # ---------------------------------------------------------------------- dp x pp x tp
-    from .models.tp_models import TPTransformer
-    from .parallel import DistributedOptimizer, PipelineStage, TPComm, init_mesh, partition_layers, \
-        sync_sequence_parallel_grads
+    from .utils import ParallelTrainStep
 
-    mesh = init_mesh(tp=tp, pp=pp)
-    comm = TPComm(mesh.tp_group, args.comm if cuda else "nccl")
-    layers = partition_layers(cfg.n_layer, pp)[mesh.pp_rank]
-    model = TPTransformer(cfg, comm, device=dev, dtype=dtype, seed=args.seed, layers=layers, first=mesh.is_first_stage,
-                          last=mesh.is_last_stage)
+    nm = max(1, args.num_microbatches)
+    sd = None
     if args.llmc_filepath:
         from .utils.llmc import map_checkpoint
 
         # memory-mapped views: every rank touches only the rows / columns of its own shard
         fam, _, sd = map_checkpoint(args.llmc_filepath)
         assert fam == family, f"{args.llmc_filepath} is a {fam} checkpoint"
-        model.load_full_state_dict(sd)
-    params = list(model.parameters())
-    if mesh.dp > 1 and args.zero_stage == 1:
-        opt = DistributedOptimizer(params, lr=args.learning_rate, weight_decay=args.weight_decay, group=mesh.dp_group,
-                                   comm=args.comm if cuda else "nccl", num_buckets=args.dp_buckets,
-                                   overlap=args.dp_buckets > 1, max_grad_norm=args.max_grad_norm,
-                                   mp_group=mesh.mp_group, tp_world=tp)
-    elif mesh.dp > 1:
-        from .parallel import AllReduceOptimizer        # --zero_stage 0: all-reduce + full Adam on every rank
-
-        opt = AllReduceOptimizer(params, lr=args.learning_rate, weight_decay=args.weight_decay, group=mesh.dp_group,
-                                 max_grad_norm=args.max_grad_norm, mp_group=mesh.mp_group, tp_world=tp,
-                                 comm="symm" if os.environ.get("TITB200_SYMM_ALLREDUCE") == "1" else "nccl")
-    else:
-        opt = tit.optim.MixedPrecisionAdam(params, lr=args.learning_rate, weight_decay=args.weight_decay,
-                                           max_grad_norm=args.max_grad_norm, mp_group=mesh.mp_group, tp_world=tp)
+    pstep = ParallelTrainStep(cfg, B, T, dev, dtype, tp=tp, pp=pp, num_microbatches=nm, zero_stage=args.zero_stage,
+                              comm=args.comm, dp_buckets=args.dp_buckets, lr=args.learning_rate,
+                              weight_decay=args.weight_decay, max_grad_norm=args.max_grad_norm, seed=args.seed,
+                              full_state_dict=sd)
+    mesh, model, opt = pstep.mesh, pstep.model, pstep.opt
     # every rank keeps its own optimizer shard (fp32 master weights, moments, step); on resume the data-parallel
     # group rebuilds the parameters from the master shards
-    start = load_checkpoint(args.resume, model, opt, rank=rank) if args.resume else 0
-    loader = _data(args, cfg, mesh.dp_rank, mesh.dp, cuda)
-    nm = max(1, args.num_microbatches)
-    assert (B * T) % tp == 0
-    batches = []
-
-    def stage_fn(x_in, i):
-        x, y = batches[i]
-        if mesh.is_first_stage:
-            return model(x, y if mesh.is_last_stage else None)
-        return model(x_in, y if mesh.is_last_stage else None, B=B, T=T)
-
-    stage = PipelineStage(stage_fn, mesh.pp_rank, pp, None if mesh.is_first_stage else mesh.prev_stage_rank(),
-                          None if mesh.is_last_stage else mesh.next_stage_rank(), (B * T // tp, cfg.n_embd), dtype, dev)
-    meter = ThroughputMeter(B * T * nm * mesh.dp, 0.0, 0.0)
+    layout = {"tp": tp, "pp": pp, "dp": mesh.dp}
+    start = load_checkpoint(args.resume, model, opt, rank=rank, world=world, layout=layout) if args.resume else 0
+    # static shapes (pipeline receive buffers, token shards): the incomplete last batch is dropped, and every
+    # data-parallel rank sees the same number of batches
+    loader = _data(args, cfg, mesh.dp_rank, mesh.dp, cuda, drop_last=True)
+    meter = ThroughputMeter(pstep.tokens_per_step, 0.0, 0.0)
     it = start * nm
     for step in range(start, args.num_iteration):
         lr = apply_lr(opt, step)
         # device-timed (CUDA events on the launching stream; wall clock only on the CPU path), max over ranks
         with CudaTimer() as tm:
-            batches = []
+            host = []
             for _ in range(nm):
-                x, y = loader.batch(it % len(loader))
+                host.append(loader.batch(it % len(loader)))
                 it += 1
-                batches.append((x.to(dev, non_blocking=True), y.to(dev, non_blocking=True)))
-            opt.zero_grad()
-            loss = stage.run(nm)
-            sync_sequence_parallel_grads(params, comm)
-            opt.step()
+            hl = pstep(host)
         ms = torch.tensor([tm.ms], device=dev)
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        lossv = torch.tensor([float(loss) if loss is not None else 0.0], device=dev)
+        lossv = pstep.loss.detach().reshape(1).clone()
         dist.all_reduce(lossv)
         lossv = lossv.item() / (mesh.dp * tp)          # the last stage of every replica (and each tp rank) reports it
         rep = meter.report(ms.item())
@@ -256,11 +227,10 @@ def train_main(family: str, argv=None) -> int:
                   f"{ms.item():.2f} ms | {rep['tokens_per_s']:.0f} tok/s | tp{tp} pp{pp} dp{mesh.dp}{mem}", flush=True)
         log.log(step=step + 1, loss=lossv, lr=lr, **rep)
         if args.save and args.save_every and (step + 1) % args.save_every == 0 and step + 1 < args.num_iteration:
-            save_checkpoint(args.save, model, opt, step + 1, rank=rank, world=world, extra={"tp": tp, "pp": pp, "dp": mesh.dp})
+            save_checkpoint(args.save, model, opt, step + 1, rank=rank, world=world, extra=layout, mesh=mesh)
             dist.barrier()
     if args.save:
-        save_checkpoint(args.save, model, opt, args.num_iteration, rank=rank, world=world,
-                        extra={"tp": tp, "pp": pp, "dp": mesh.dp})
+        save_checkpoint(args.save, model, opt, args.num_iteration, rank=rank, world=world, extra=layout, mesh=mesh)
         dist.barrier()
     if cuda:
         status = tit._lib.C.status_read(True)

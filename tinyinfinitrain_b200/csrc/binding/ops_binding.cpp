@@ -459,22 +459,16 @@ Tensor softmax_bwd(const Tensor& dy, const Tensor& y, int64_t dim) {
 // logits: [rows, ld] (last dim may be padded beyond V).  Returns the mean loss (0-d fp32);
 // when write_grad the gradient scaled by grad_scale overwrites `logits`.
 Tensor xent_fused(const Tensor& logits, const Tensor& targets, int64_t V, double grad_scale, bool write_grad,
-                  double mean_scale, bool row_cached) {
+                  double mean_scale) {
   check_cuda(logits, "logits"); check_cuda(targets, "targets");
   TORCH_CHECK(targets.scalar_type() == at::kLong, "titb200 cross entropy: targets must be int64");
   c10::cuda::CUDAGuard guard(logits.device());
   const int64_t ld = logits.size(-1), rows = logits.numel() / ld;
   TORCH_CHECK(targets.numel() == rows, "titb200 cross entropy: one target per row");
   Tensor losses = at::empty({rows}, logits.options().dtype(at::kFloat));
-  if (row_cached && titb_xent_cached_ok(logits.data_ptr(), ld, dt_code(logits))) {
-    CHECK_RC(titb_xent_fwd_bwd_cached(logits.data_ptr(), (const long long*)targets.data_ptr<int64_t>(),
-                                      losses.data_ptr<float>(), write_grad ? logits.data_ptr() : nullptr, rows, (int)V, ld,
-                                      (float)grad_scale, nullptr, dt_code(logits), cur_stream()), "xent_fwd_bwd_cached");
-  } else {
-    CHECK_RC(titb_xent_fwd_bwd(logits.data_ptr(), (const long long*)targets.data_ptr<int64_t>(),
-                               losses.data_ptr<float>(), write_grad ? logits.data_ptr() : nullptr, rows, (int)V, ld,
-                               (float)grad_scale, dt_code(logits), cur_stream()), "xent_fwd_bwd");
-  }
+  CHECK_RC(titb_xent_fwd_bwd(logits.data_ptr(), (const long long*)targets.data_ptr<int64_t>(),
+                             losses.data_ptr<float>(), write_grad ? logits.data_ptr() : nullptr, rows, (int)V, ld,
+                             (float)grad_scale, dt_code(logits), cur_stream()), "xent_fwd_bwd");
   Tensor loss = at::empty({}, losses.options());
   CHECK_RC(titb_mean(losses.data_ptr<float>(), loss.data_ptr<float>(), rows, (float)mean_scale, cur_stream()), "mean");
   return loss;
@@ -809,7 +803,7 @@ PYBIND11_MODULE(_C, m) {
   m.def("softmax_fwd", &softmax_fwd);
   m.def("softmax_bwd", &softmax_bwd);
   m.def("xent_fused", &xent_fused, py::arg("logits"), py::arg("targets"), py::arg("V"), py::arg("grad_scale"),
-        py::arg("write_grad"), py::arg("mean_scale"), py::arg("row_cached") = false);
+        py::arg("write_grad"), py::arg("mean_scale"));
   m.def("xent_bwd", &xent_bwd);
   m.def("xent_vp_stats", &xent_vp_stats);
   m.def("xent_vp_grad", &xent_vp_grad);

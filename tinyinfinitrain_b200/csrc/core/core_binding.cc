@@ -123,8 +123,9 @@ void bind_core(pybind11::module_& m) {
       .def(py::init<uint32_t, int64_t, size_t, size_t>(), py::arg("seed"), py::arg("vocab_size"),
            py::arg("sequence_length"), py::arg("num_samples"));
   py::class_<td::DataLoader>(m, "DataLoader")
-      .def(py::init<std::shared_ptr<td::Dataset>, size_t, bool, size_t, size_t>(), py::arg("dataset"),
-           py::arg("batch_size"), py::arg("pin_memory") = false, py::arg("rank") = 0, py::arg("world") = 1)
+      .def(py::init<std::shared_ptr<td::Dataset>, size_t, bool, size_t, size_t, bool>(), py::arg("dataset"),
+           py::arg("batch_size"), py::arg("pin_memory") = false, py::arg("rank") = 0, py::arg("world") = 1,
+           py::arg("drop_last") = false)
       .def("NumBatches", &td::DataLoader::NumBatches)
       .def("__len__", &td::DataLoader::NumBatches)
       .def("Batch", &td::DataLoader::Batch)

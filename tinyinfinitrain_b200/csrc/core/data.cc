@@ -45,11 +45,16 @@ std::pair<at::Tensor, at::Tensor> SyntheticDataset::Get(size_t idx) const {
   return sample_views(tokens_, idx, sequence_length_);
 }
 
-DataLoader::DataLoader(std::shared_ptr<Dataset> dataset, size_t batch_size, bool pin_memory, size_t rank, size_t world)
+DataLoader::DataLoader(std::shared_ptr<Dataset> dataset, size_t batch_size, bool pin_memory, size_t rank, size_t world,
+                       bool drop_last)
     : dataset_(std::move(dataset)), batch_size_(batch_size), rank_(rank), world_(world), pin_(pin_memory) {
   TORCH_CHECK(batch_size_ > 0 && world_ > 0 && rank_ < world_, "bad DataLoader arguments");
-  const size_t total = (dataset_->Size() + batch_size_ - 1) / batch_size_;
-  num_batches_ = total > rank_ ? (total - rank_ + world_ - 1) / world_ : 0;
+  if (drop_last) {
+    num_batches_ = (dataset_->Size() / batch_size_) / world_;
+  } else {
+    const size_t total = (dataset_->Size() + batch_size_ - 1) / batch_size_;
+    num_batches_ = total > rank_ ? (total - rank_ + world_ - 1) / world_ : 0;
+  }
 }
 
 std::pair<at::Tensor, at::Tensor> DataLoader::Batch(size_t i) const {

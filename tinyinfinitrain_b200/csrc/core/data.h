@@ -66,8 +66,10 @@ class SyntheticDataset : public Dataset {
 class DataLoader {
  public:
   // Rank `rank` of `world` takes batches rank, rank + world, ...  (world = 1: every batch).
+  // drop_last: only full batches are served and every rank gets the same number of them (floor(full / world)),
+  // which is what a job with static shapes or collectives per batch needs.
   DataLoader(std::shared_ptr<Dataset> dataset, size_t batch_size, bool pin_memory = false, size_t rank = 0,
-             size_t world = 1);
+             size_t world = 1, bool drop_last = false);
   size_t NumBatches() const { return num_batches_; }
   // Batch `i` of this rank as two [batch, seq] int64 tensors (the last batch may be short).
   std::pair<at::Tensor, at::Tensor> Batch(size_t i) const;

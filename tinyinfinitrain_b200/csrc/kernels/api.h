@@ -176,13 +176,6 @@ TITB_API int titb_xent_fwd_bwd(const void* logits, const long long* targets, flo
 TITB_API int titb_xent_bwd(const void* logits, const long long* targets, void* dlogits, const float* upstream,
                            long long rows, int V, long long ld, float grad_scale, int dtype, cudaStream_t stream);
 TITB_API int titb_mean(const float* x, float* out, long long n, float scale, cudaStream_t stream);
-// Same contract as titb_xent_fwd_bwd (+ optional device `upstream` scalar), but the row stays in shared memory between
-// the statistics pass and the gradient pass: one global read instead of two.  titb_xent_cached_ok tells whether the
-// row fits (<= 200 KB, 16-byte aligned rows); otherwise use the regular kernel.
-TITB_API int titb_xent_cached_ok(const void* logits, long long ld, int dtype);
-TITB_API int titb_xent_fwd_bwd_cached(const void* logits, const long long* targets, float* losses, void* dlogits,
-                                      long long rows, int V, long long ld, float grad_scale, const float* upstream,
-                                      int dtype, cudaStream_t stream);
 // Vocabulary-parallel cross entropy.  logits [rows, ld] is this rank's slice: column c is global column
 // vocab_lo + c; columns >= V_local or with a global index >= vocab_size are padding.
 // Pass 1 writes (row max, sum exp(x - max), target logit or 0) to slot `rank` of a [world, rows, 3] fp32 table at
@@ -290,7 +283,7 @@ struct TitbAttnDesc {
 TITB_API int titb_attn_fwd(const TitbAttnDesc* d, cudaStream_t stream);
 TITB_API int titb_attn_bwd(const TitbAttnDesc* d, cudaStream_t stream);
 // Backward kernel variant: 8 = two warps per score row (eight element-wise warps), anything else = four warps.
-// Process-wide; the environment variable TITB200_ATTN_BWD_WARPS=8 sets the initial value.
+// Process-wide; 8 is the initial value.
 TITB_API void titb_attn_bwd_set_warps(int warps);
 
 // ---- gradient-norm clipping (device resident: graph-capturable) -------------------------------------------------

@@ -893,13 +893,9 @@ static int pick_tile_n(int M, int N, int splits) {
     return waves * bn;
   };
   if (N <= 128) return 128;
-  // 128 x 192 tiles cut the tail of the last wave for widths such as 768 and 3072 (6 x 128).  They are
-  // opt-in (TITB200_GEMM_TILE192=1, or tile_n = 192 per call) and then taken when they save more than 5%
-  // of the wave-quantised cost of 128 x 256.
-  static const bool allow192 = [] { const char* e = getenv("TITB200_GEMM_TILE192"); return e && e[0] == '1'; }();
-  const long long c256 = cost(256), c128 = cost(128);
-  if (!allow192) return (c128 * 2 < c256) ? 128 : 256;
-  const long long c192 = cost(192);
+  // 128 x 192 tiles cut the tail of the last wave for widths such as 768 and 3072 (6 x 128); they are taken when
+  // they save more than 5% of the wave-quantised cost of 128 x 256.
+  const long long c256 = cost(256), c128 = cost(128), c192 = cost(192);
   if (c128 * 2 < c256 && c128 * 2 < c192) return 128;
   return (c192 * 100 < c256 * 95) ? 192 : 256;
 }

@@ -44,15 +44,21 @@ class DataLoader:
     Python ``Dataset`` subclasses are batched with ``torch.stack`` instead.
     """
 
-    def __init__(self, dataset, batch_size: int, pin_memory: bool = False, rank: int = 0, world: int = 1):
+    def __init__(self, dataset, batch_size: int, pin_memory: bool = False, rank: int = 0, world: int = 1,
+                 drop_last: bool = False):
+        """``drop_last``: only full batches, and the same number of them on every rank (what a multi-rank job with
+        static shapes needs; without it the last batch may be short and ranks may differ by one batch)."""
         self.dataset, self.batch_size, self.rank, self.world = dataset, batch_size, rank, world
-        self._native = C.DataLoader(dataset, batch_size, pin_memory, rank, world) \
+        self.drop_last = drop_last
+        self._native = C.DataLoader(dataset, batch_size, pin_memory, rank, world, drop_last) \
             if isinstance(dataset, C.Dataset) else None
         self.pin_memory = pin_memory
 
     def __len__(self) -> int:
         if self._native is not None:
             return len(self._native)
+        if self.drop_last:
+            return (len(self.dataset) // self.batch_size) // self.world
         total = (len(self.dataset) + self.batch_size - 1) // self.batch_size
         return max(0, (total - self.rank + self.world - 1) // self.world)
 

@@ -75,6 +75,40 @@ def shard_state_dict(sd: Dict[str, torch.Tensor], cfg, tp: int, rank: int, vocab
     return {k: v.contiguous() for k, v in out.items()}
 
 
+def unshard_state_dict(shards, cfg, vocab_rows: int) -> Dict[str, torch.Tensor]:
+    """Inverse of ``shard_state_dict``: ``shards[r]`` holds tensor-parallel rank r's tensors (same names on every
+    rank); returns the unsharded tensors.  ``vocab_rows`` is the row count the vocabulary tensors are cut back to
+    (the padding rows that were added for an even split carry no information)."""
+    tp = len(shards)
+    is_llama = isinstance(cfg, LLaMA3Config)
+    n_kv = cfg.n_kv_head if is_llama else cfg.n_head
+    hd = cfg.n_embd // cfg.n_head
+    out = {}
+    for name in shards[0]:
+        parts = [sh[name] for sh in shards]
+        if name.endswith("attn.c_attn.weight") or name.endswith("attn.c_attn.bias"):
+            q, k, v = [], [], []
+            for r, t in enumerate(parts):
+                q0, q1 = head_range(cfg.n_head, tp, r)
+                k0, k1 = head_range(n_kv, tp, r)
+                nq, nk = (q1 - q0) * hd, (k1 - k0) * hd
+                q.append(t[:nq]); k.append(t[nq:nq + nk]); v.append(t[nq + nk:nq + 2 * nk])
+            out[name] = torch.cat(q + k + v)
+        elif name.endswith("mlp.c_fc.weight") or name.endswith("mlp.c_fc.bias"):
+            if is_llama:
+                f = parts[0].shape[0] // 2
+                out[name] = torch.cat([t[:f] for t in parts] + [t[f:] for t in parts])
+            else:
+                out[name] = torch.cat(parts)
+        elif name.endswith("c_proj.weight"):
+            out[name] = torch.cat(parts, dim=1)
+        elif name in ("transformer.wte.weight", "lm_head.weight"):
+            out[name] = torch.cat(parts)[:vocab_rows]
+        else:
+            out[name] = parts[0]
+    return {k: v.contiguous() for k, v in out.items()}
+
+
 class TPAttention(nn.Module):
     kType = "CausalSelfAttention"
 
@@ -162,7 +196,7 @@ class TPTransformer(nn.Module):
     kType = "TPTransformer"
 
     def __init__(self, cfg, comm: tpl.TPComm, device=None, dtype=torch.float32, seed: Optional[int] = 42,
-                 layers: Optional[range] = None, first: bool = True, last: bool = True):
+                 layers: Optional[range] = None, first: bool = True, last: bool = True, exact_init_limit: int = 1 << 26):
         super().__init__()
         self.config, self.comm = cfg, comm
         self.is_llama = isinstance(cfg, LLaMA3Config)
@@ -193,20 +227,61 @@ class TPTransformer(nn.Module):
             else:
                 self.lm_head = nn.Module()
                 self.lm_head.weight = self.transformer["wte"].weight  # tied (GPT-2, single stage)
-        self.reset_parameters(seed)
+        self.reset_parameters(seed, exact_init_limit)
 
-    def reset_parameters(self, seed: Optional[int]) -> None:
+    def full_shape(self, name: str, p: torch.Tensor):
+        """Shape of the unsharded tensor that parameter ``name`` is a slice of."""
         cfg = self.config
+        hd = cfg.n_embd // cfg.n_head
+        n_kv = cfg.n_kv_head if self.is_llama else cfg.n_head
+        if name.endswith("attn.c_attn.weight"):
+            return ((cfg.n_head + 2 * n_kv) * hd, cfg.n_embd)
+        if name.endswith("mlp.c_fc.weight"):
+            return ((2 * cfg.ffn_dim if self.is_llama else 4 * cfg.n_embd), cfg.n_embd)
+        if name.endswith("attn.c_proj.weight"):
+            return (cfg.n_embd, cfg.n_embd)
+        if name.endswith("mlp.c_proj.weight"):
+            return (cfg.n_embd, cfg.ffn_dim if self.is_llama else 4 * cfg.n_embd)
+        if name in ("transformer.wte.weight", "lm_head.weight"):
+            return (cfg.vocab_size if self.is_llama else cfg.padded_vocab_size, cfg.n_embd)
+        return tuple(p.shape)
+
+    def reset_parameters(self, seed: Optional[int], exact_limit: int = 1 << 26) -> None:
+        """Same distributions as the single-GPU models.  A sharded parameter whose unsharded tensor has at most
+        ``exact_limit`` elements is drawn in full on the host from the start of the ``seed`` stream and this rank's
+        slice is copied, which reproduces the single-GPU model of the same seed exactly.  Larger tensors (the big
+        LLaMA matrices) are drawn on the device from a generator seeded with (seed, tensor-parallel rank, parameter
+        index), so that no two shards and no two layers repeat each other.  Replicated parameters are identical on
+        every rank of the group in both cases."""
+        cfg, comm = self.config, self.comm
         resid_std = 0.02 / math.sqrt(2 * cfg.n_layer)
-        for name, p in self.named_parameters():
+        own = {}
+        for name, p in self.named_parameters(remove_duplicate=False):
+            if id(p) not in {id(q) for q in own.values()}:
+                own[name] = p
+        for index, (name, p) in enumerate(own.items()):
             if "ln_" in name and name.endswith("weight"):
                 init.Ones(p)
-            elif name.endswith(".bias"):
+                continue
+            if name.endswith(".bias"):
                 init.Zeros(p)
-            elif name.endswith("c_proj.weight"):
-                init.Normal(p, 0.0, resid_std, generator=seed)
+                continue
+            std = resid_std if name.endswith("c_proj.weight") else 0.02
+            full = self.full_shape(name, p)
+            if full == tuple(p.shape):                 # replicated (or a group of one rank)
+                init.Normal(p, 0.0, std, generator=seed)
+            elif math.prod(full) <= exact_limit:
+                t = init.Normal(torch.empty(full, dtype=torch.float32), 0.0, std, generator=seed)
+                if not self.is_llama and name in ("transformer.wte.weight", "lm_head.weight"):
+                    t[cfg.vocab_size:].zero_()         # padding rows of the GPT-2 vocabulary
+                mine = shard_state_dict({name: t}, cfg, comm.world, comm.rank, vocab_padded=self.vocab_padded)[name]
+                with torch.no_grad():
+                    p.copy_(mine.to(device=p.device, dtype=p.dtype))
             else:
-                init.Normal(p, 0.0, 0.02, generator=seed)
+                g = torch.Generator(device=p.device)
+                g.manual_seed(((0 if seed is None else int(seed)) * 1000003 + comm.rank) * 1000003 + index)
+                with torch.no_grad():
+                    p.copy_((torch.randn(p.shape, generator=g, device=p.device, dtype=torch.float32) * std).to(p.dtype))
 
     def load_full_state_dict(self, sd: Dict[str, torch.Tensor]) -> None:
         """Loads this rank's slices from a full (unsharded) state dict of the single-GPU model.  The tensors may

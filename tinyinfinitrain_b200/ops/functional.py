@@ -31,8 +31,6 @@ EPI_NONE, EPI_BIAS, EPI_BIAS_GELU, EPI_DGELU, EPI_BIAS_RESIDUAL = 0, 1, 2, 3, 4
 # TITB200_DETERMINISTIC=1: the token-embedding gradient is built by a sorted segment reduction instead of fp32 atomics
 # (the one reduction of the training step whose summation order otherwise depends on timing)
 DETERMINISTIC_EMBEDDING_GRAD = os.environ.get("TITB200_DETERMINISTIC", "0") == "1"
-# TITB200_XENT_CACHED=1: the loss kernel keeps each logits row in shared memory between its two passes (rows up to 200 KB)
-XENT_ROW_CACHED = os.environ.get("TITB200_XENT_CACHED", "0") == "1"
 # bias gradients with the one-launch column sum (the last CTA of a column strip folds the partial rows)
 COLSUM_FUSED = os.environ.get("TITB200_COLSUM_FUSED", "0") == "1"
 # LayerNorm / RMSNorm backward as one launch (dx, finished dweight / dbias, residual gradient folded in)
@@ -528,7 +526,7 @@ class _CrossEntropyFn(torch.autograd.Function):
         tc = targets.contiguous().view(-1)
         if tc.dtype != torch.int64:
             tc = tc.to(torch.int64)
-        loss = C.xent_fused(lc, tc, V, 0.0, False, 1.0 / rows, XENT_ROW_CACHED)
+        loss = C.xent_fused(lc, tc, V, 0.0, False, 1.0 / rows)
         ctx.save_for_backward(lc, tc)
         ctx.V, ctx.rows = V, rows
         return loss
@@ -565,7 +563,7 @@ class _LMHeadLossFn(torch.autograd.Function):
         rows = x2.shape[0]
         logits = C.gemm(x2, w)[0]
         tc = targets.contiguous().view(-1)
-        loss = C.xent_fused(logits, tc, V, 1.0 / rows, True, 1.0 / rows, XENT_ROW_CACHED)
+        loss = C.xent_fused(logits, tc, V, 1.0 / rows, True, 1.0 / rows)
         ctx.save_for_backward(x2, w, logits)
         ctx.xshape = x.shape
         return loss

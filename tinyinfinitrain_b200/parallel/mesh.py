@@ -26,6 +26,9 @@ class ParallelMesh:
     dp_group: Optional[dist.ProcessGroup]
     pp_ranks: List[int]   # global ranks of this rank's pipeline, by stage
     mp_group: Optional[dist.ProcessGroup] = None   # the tp * pp ranks that hold one model replica (None when that is 1 rank)
+    # first and last pipeline stage of this rank's pipeline (same tp rank): the two holders of a tied embedding /
+    # output projection.  None when pp == 1 or on middle stages.
+    embed_group: Optional[dist.ProcessGroup] = None
 
     @property
     def is_first_stage(self) -> bool:
@@ -79,4 +82,11 @@ def init_mesh(tp: int = 1, pp: int = 1, dp: Optional[int] = None) -> ParallelMes
         g = dist.new_group(ranks) if len(ranks) > 1 else None
         if rank in ranks:
             mp_group = g
-    return ParallelMesh(tp, pp, dp, rank, t, p, d, mine["tp"], mine["pp"], mine["dp"], my_pp_ranks, mp_group)
+    embed_group = None
+    if pp > 1:
+        for ranks in ppg:                                  # one group per pipeline: its first and last stage
+            pair = [ranks[0], ranks[-1]]
+            g = dist.new_group(pair)
+            if rank in pair:
+                embed_group = g
+    return ParallelMesh(tp, pp, dp, rank, t, p, d, mine["tp"], mine["pp"], mine["dp"], my_pp_ranks, mp_group, embed_group)

@@ -1,7 +1,7 @@
 """A/B driver for the kernel variants that are selected through environment switches.
 
     python -m tinyinfinitrain_b200.utils.ab_bench --steps 20 --warmup 5 --json_out ab.json
-    python -m tinyinfinitrain_b200.utils.ab_bench --gpus 8 --only TITB200_NORM_BWD_ONEPASS=1 "--dp_buckets 4"
+    python -m tinyinfinitrain_b200.utils.ab_bench --gpus 8 --only TITB200_NO_MULTIMEM=1 "--dp_buckets 4"
 
 Runs ``bench.py`` once with the defaults and once per candidate (one switch at a time, then all of them together),
 each as its own process with a time limit, and prints one table: tokens/s, ms per step, ratio to the default run,
@@ -20,12 +20,9 @@ from typing import Dict, List, Optional
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
+# Candidates when --only is not given: the switches / flags that still select a non-default variant.
 DEFAULT_CANDIDATES = [
-    "TITB200_NORM_BWD_ONEPASS=1",
-    "TITB200_ATTN_BWD_WARPS=8",
-    "TITB200_COLSUM_FUSED=1",
-    "TITB200_XENT_CACHED=1",
-    "TITB200_GEMM_TILE192=1",
+    "TITB200_DETERMINISTIC=1",
 ]
 
 

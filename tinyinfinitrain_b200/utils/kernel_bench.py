@@ -48,6 +48,58 @@ def timeit(fn, iters, warmup=3, flush=None):
     return tot / iters
 
 
+def gemm_sweep(C, model: str, iters: int):
+    """Every GEMM of one transformer layer (forward, dgrad, wgrad) plus the vocabulary projection, this library against
+    torch.matmul (cuBLAS) on the same tensors: `iters` launches back to back between two CUDA events, no L2 flush
+    (inside a training step the operands of a GEMM were just written by the kernel before it)."""
+    dev, bf = "cuda", torch.bfloat16
+    hbm, tflops, src = peaks()
+    if model == "gpt2":
+        M, shapes = 8192, [("c_attn", 2304, 768), ("attn.c_proj", 768, 768), ("c_fc", 3072, 768), ("mlp.c_proj", 768, 3072),
+                           ("lm_head", 50304, 768)]
+    elif model == "gpt2xl":
+        M, shapes = 4096, [("c_attn", 4800, 1600), ("attn.c_proj", 1600, 1600), ("c_fc", 6400, 1600), ("mlp.c_proj", 1600, 6400)]
+    else:  # llama-1B
+        M, shapes = 8192, [("c_attn", 3072, 2048), ("attn.c_proj", 2048, 2048), ("c_fc", 16384, 2048), ("mlp.c_proj", 2048, 8192)]
+
+    def run(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        e1.synchronize()
+        return e0.elapsed_time(e1) / iters * 1e3   # us
+
+    rows = []
+    for name, N, K in shapes:
+        X = torch.randn(M, K, device=dev).to(bf)          # activations
+        W = (torch.randn(N, K, device=dev) * 0.02).to(bf)  # weight [out, in]
+        dY = torch.randn(M, N, device=dev).to(bf)
+        dWf = torch.zeros(N, K, device=dev)
+        Wt = W.t().contiguous()
+        cases = [
+            ("fwd   Y=X.W^T", lambda: C.gemm(X, W), lambda: torch.matmul(X, W.t())),
+            ("dgrad dX=dY.W", lambda: C.gemm(dY, W, False, True), lambda: torch.matmul(dY, W)),
+            ("wgrad dW+=dY^T.X (fp32 out)", lambda: C.gemm(dY, X, True, True, out=dWf, accumulate=True),
+             lambda: torch.matmul(dY.t(), X)),
+        ]
+        for label, ours, lib in cases:
+            t_o, t_l = run(ours), run(lib)
+            fl = 2.0 * M * N * K
+            rows.append({"layer": name, "case": label, "M": M, "N": N, "K": K, "ours_us": t_o, "torch_us": t_l,
+                         "ours_frac_of_bf16_peak": fl / t_o / 1e6 / tflops, "ours_over_torch": t_l / t_o})
+        del X, W, dY, dWf, Wt
+    print(f"{'layer':<12} {'case':<30} {'N':>6} {'K':>6} {'ours us':>9} {'torch us':>9} {'frac peak':>9} {'speedup':>8}")
+    for r in rows:
+        print(f"{r['layer']:<12} {r['case']:<30} {r['N']:>6} {r['K']:>6} {r['ours_us']:>9.1f} {r['torch_us']:>9.1f} "
+              f"{r['ours_frac_of_bf16_peak']:>9.3f} {r['ours_over_torch']:>8.2f}")
+    print(json.dumps({"kernel": "gemm_sweep", "model": model, "peaks": src, "status": int(C.status_read(True)), "rows": rows}))
+
+
 def main():
     from .._lib import C
     from .. import ops
@@ -55,7 +107,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel", choices=["gemm", "gemm_nt", "gemm_wgrad", "attn_fwd", "attn_bwd", "layernorm_fwd", "layernorm_bwd",
                                        "xent", "adam", "gelu_gemm", "ag_gemm", "gemm_rs", "rs_adam", "clip", "embedding_bwd",
-                                       "reduce", "transpose_view", "colsum", "param_gather_gemm"])
+                                       "reduce", "transpose_view", "colsum", "param_gather_gemm", "gemm_sweep"])
+    ap.add_argument("--model", default="gpt2", choices=["gpt2", "gpt2xl", "llama1b"], help="gemm_sweep: whose layer shapes")
     ap.add_argument("--deterministic", action="store_true", help="embedding_bwd: sorted segment reduction instead of atomics")
     ap.add_argument("--world", type=int, default=4)
     ap.add_argument("--helpers", type=int, default=0)
@@ -74,8 +127,9 @@ def main():
     ap.add_argument("--onepass", action="store_true", help="layernorm_bwd: dx and finished dweight / dbias in one launch")
     ap.add_argument("--residual", action="store_true", help="layernorm_bwd: add a residual gradient to dx")
     ap.add_argument("--fused", action="store_true", help="colsum: one launch, the last CTA of a column strip folds the partials")
-    ap.add_argument("--cached", action="store_true", help="xent: keep each row in shared memory between the two passes")
     a = ap.parse_args()
+    if a.kernel == "gemm_sweep":
+        return gemm_sweep(C, a.model, a.iters)
     dev = "cuda"
     hbm, tflops, src = peaks()
     flush = None if a.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device=dev)
@@ -199,7 +253,7 @@ def main():
         logits = torch.randn(a.m, a.n, device=dev).to(bf)
         tgt = torch.randint(0, a.n - 47, (a.m,), device=dev)
         bytes_ = 2.0 * logits.numel() * 2
-        fn = lambda: C.xent_fused(logits, tgt, a.n - 47, 1.0 / a.m, True, 1.0 / a.m, a.cached)
+        fn = lambda: C.xent_fused(logits, tgt, a.n - 47, 1.0 / a.m, True, 1.0 / a.m)
     else:
         n = a.m * a.n
         w, g = torch.randn(n, device=dev), torch.randn(n, device=dev)
