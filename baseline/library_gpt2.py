@@ -46,6 +46,21 @@ class LibraryGPT2(nn.Module):
                 std = 0.02 / math.sqrt(2 * n_layer) if name.endswith("c_proj.weight") or name.endswith("mlp_proj.weight") else 0.02
                 nn.init.normal_(p, 0.0, std)
 
+    @torch.no_grad()
+    def load_named(self, sd) -> None:
+        """Copies weights given under the GPT-2 state-dict names of the reference (``transformer.h.0.attn.c_attn.weight``
+        ...), so that this model and the hand-written one can start a comparison from identical parameters."""
+        def name_of(k: str) -> str:
+            k = k.replace("transformer.", "")
+            k = k.replace("attn.c_attn", "c_attn").replace("attn.c_proj", "c_proj")
+            return k.replace("mlp.c_fc", "c_fc").replace("mlp.c_proj", "mlp_proj")
+
+        own = dict(self.named_parameters())
+        for k, v in sd.items():
+            if k == "lm_head.weight":
+                continue
+            own[name_of(k)].copy_(v.to(own[name_of(k)].dtype))
+
     def forward(self, idx, targets):
         T = idx.shape[1]
         x = self.wte(idx) + self.wpe(torch.arange(T, device=idx.device))
@@ -65,7 +80,7 @@ class LibraryTrainStep:
         if world > 1:
             from torch.nn.parallel import DistributedDataParallel as DDP
 
-            self.model = DDP(model, device_ids=[dev.index], gradient_as_bucket_view=True)
+            self.model = DDP(model, device_ids=[dev.index] if dev.type == "cuda" else None, gradient_as_bucket_view=True)
         self.opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1,
                                      fused=dev.type == "cuda")
         self.idx = torch.zeros(B, T, dtype=torch.long, device=dev)

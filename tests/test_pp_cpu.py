@@ -55,7 +55,9 @@ def _worker(rank, world, port, q):
 
         ps = PipelineStage(fwd, m.pp_rank, world, None if m.is_first_stage else m.prev_stage_rank(),
                            None if m.is_last_stage else m.next_stage_rank(), (B * T, cfg.n_embd), torch.float32, "cpu")
+        ps.trace = []
         loss = ps.run(nm)
+        trace = list(ps.trace)
         ref_loss = sum(full(idx[i], tgt[i])[1] for i in range(nm)) / nm
         ref_loss.backward()
         ref = {k: v.grad for k, v in full.StateDict().items() if v.grad is not None}
@@ -68,7 +70,7 @@ def _worker(rank, world, port, q):
             r = ref[name]
             worst = max(worst, (p.grad[:r.shape[0]] - r).abs().max().item())
         ok = worst < 1e-4 and (loss is None or abs(loss.item() - ref_loss.item()) < 1e-4)
-        q.put((rank, ok, worst, None if loss is None else loss.item(), ref_loss.item()))
+        q.put((rank, ok, worst, None if loss is None else loss.item(), ref_loss.item(), trace))
     finally:
         dist.destroy_process_group()
 
@@ -84,3 +86,43 @@ def test_1f1b_two_stages_match_single_process():
     for p in procs:
         p.join(timeout=30)
     assert all(r[1] for r in res), res
+
+
+def _check_trace(trace, stage, P, nm):
+    """What the overlap needs from the schedule: the compute order is 1F1B, a batch that only sends is never waited
+    for before the last forward / backward has been launched, and in the warm-up and cool-down phases the receive of
+    the next micro-batch is posted before the current one is computed."""
+    from tinyinfinitrain_b200.parallel.pp import one_f_one_b_order
+
+    compute = [e for e in trace if e[0] in ("F", "B")]
+    assert compute == one_f_one_b_order(stage, P, nm), compute
+    last_compute = max(i for i, e in enumerate(trace) if e[0] in ("F", "B"))
+    send_waits = [i for i, e in enumerate(trace) if e == ("wait", "s")]
+    assert all(i > last_compute for i in send_waits), trace
+    n_send_only = sum(1 for e in trace if e == ("issue", "s"))
+    assert len(send_waits) == n_send_only                                  # every deferred handle is drained once
+    warm = min(P - stage - 1, nm)
+    if stage > 0 and warm >= 1:
+        # two receives are in flight before the first forward starts: its own input and the next one
+        first_f = trace.index(("F", 0))
+        assert sum(1 for e in trace[:first_f] if e == ("issue", "r")) == 2, trace[:first_f]
+    if stage < P - 1 and warm >= 2:
+        first_cooldown_b = trace.index(("B", nm - warm))
+        tail = trace[first_cooldown_b - 3:first_cooldown_b]
+        assert tail.count(("issue", "r")) >= 1, trace
+
+
+def test_schedule_defers_send_waits_and_prefetches_receives():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29700 + os.getpid() % 90
+    P, nm = 4, 4           # the worker runs 4 micro-batches
+    procs = [ctx.Process(target=_worker, args=(r, P, port, q)) for r in range(P)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=240) for _ in procs]
+    for p in procs:
+        p.join(timeout=30)
+    assert all(r[1] for r in res), [r[:5] for r in res]
+    for r in res:
+        _check_trace(r[5], r[0], P, nm)

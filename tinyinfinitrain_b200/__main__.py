@@ -18,9 +18,7 @@ SWITCHES = {
     "TITB200_NO_MULTIMEM": "1: NVLink kernels use peer loads / stores instead of NVLS multimem",
     "TITB200_SYMM_HEAP": "native: symmetric buffers from this package's own cuMem heap instead of PyTorch's",
     "TITB200_VP_XENT": "1: vocabulary-parallel cross entropy through the two-pass kernels",
-    "TITB200_COLSUM_FUSED": "1: bias gradients with the one-launch column sum",
     "TITB200_SYMM_ALLREDUCE": "1: --zero_stage 0 sums gradients with the own all-reduce kernel instead of NCCL",
-    "TITB200_NORM_BWD_ONEPASS": "1: LayerNorm / RMSNorm backward in one launch, residual gradient folded in",
     "TITB200_DETERMINISTIC": "1: sorted, atomics-free token-embedding gradient",
     "TITB200_NVTX": "1: the C++ API drops an NVTX marker per kernel dispatch (op names on an Nsight timeline)",
     "TITB200_SANITIZE": "1 (build time): ASan + UBSan build of the host C++",

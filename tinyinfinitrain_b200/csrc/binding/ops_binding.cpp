@@ -231,34 +231,11 @@ std::vector<Tensor> layernorm_fwd(const Tensor& x, const Tensor& w, const Tensor
            "layernorm_fwd");
   return {y, mean, rstd};
 }
-// Zeroed counter words for kernels whose last CTA finishes a reduction (column sums, norm backward): one array
-// per device, cut into 64 slots of 256 words; a
-// stream always uses the same slot, so its launches (which are ordered) share self-resetting counters, and two
-// streams that run such kernels at the same time interfere only if their handles hash to the same slot.
-static unsigned* ticket_counters(const Tensor& like, int words) {
-  constexpr int kSlots = 64, kSlotWords = 256;
-  TORCH_CHECK(words <= kSlotWords, "titb200: too many ticket counters for one launch");
-  static std::mutex mu;
-  // never destroyed: a static tensor would be released after the CUDA context at process exit
-  static auto& table = *new std::map<int, Tensor>();
-  std::lock_guard<std::mutex> lock(mu);
-  const int dev = (int)like.get_device();
-  auto it = table.find(dev);
-  if (it == table.end()) {
-    // a tensor created while a graph is being captured would live in the graph's private pool, and the fill
-    // that zeroes it would be replayed with the graph
-    TORCH_CHECK(c10::cuda::currentStreamCaptureStatusMayInitCtx() == c10::cuda::CaptureStatus::None,
-                "titb200: run one step outside of graph capture before capturing (ticket counter allocation)");
-    it = table.emplace(dev, at::zeros({kSlots * kSlotWords}, like.options().dtype(at::kInt))).first;
-  }
-  const size_t slot = (std::hash<void*>()((void*)cur_stream()) >> 4) % kSlots;
-  return reinterpret_cast<unsigned*>(it->second.data_ptr<int>()) + slot * kSlotWords;
-}
-
 // dw/db are written (or accumulated) into fp32 tensors supplied by the caller, or fresh ones.
+// `dres`: gradient arriving through a residual connection around the norm, added to dx inside the kernel.
 std::vector<Tensor> layernorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& mean,
                                   const Tensor& rstd, const optional<Tensor>& dw_, const optional<Tensor>& db_,
-                                  bool accumulate, bool onepass, const optional<Tensor>& dres_) {
+                                  bool accumulate, const optional<Tensor>& dres_) {
   check_cuda(dy, "dy"); check_cuda(x, "x");
   c10::cuda::CUDAGuard guard(x.device());
   const int64_t C = x.size(-1), rows = x.numel() / C;
@@ -274,23 +251,12 @@ std::vector<Tensor> layernorm_bwd(const Tensor& dy, const Tensor& x, const Tenso
     dres = dres_->contiguous();
     TORCH_CHECK(dres.sizes() == x.sizes() && dres.scalar_type() == x.scalar_type(), "titb200: dres must match x");
   }
-  if (onepass && titb_norm_bwd_onepass_ok(rows, (int)C, dt_code(x), dy.data_ptr(), x.data_ptr(), w.data_ptr(),
-                                          have_res ? dres.data_ptr() : nullptr, dx.data_ptr())) {
-    Tensor scratch = at::empty({titb_norm_bwd_onepass_scratch((int)C)}, fopt);
-    unsigned* counters = ticket_counters(x, titb_norm_bwd_onepass_counters());
-    CHECK_RC(titb_norm_bwd_onepass(dy.data_ptr(), x.data_ptr(), w.data_ptr(), mean.data_ptr<float>(),
-                                   rstd.data_ptr<float>(), have_res ? dres.data_ptr() : nullptr, dx.data_ptr(),
-                                   dw.data_ptr<float>(), db.data_ptr<float>(), scratch.data_ptr<float>(), counters, rows,
-                                   (int)C, dt_code(x), 0, have && accumulate, cur_stream()),
-             "norm_bwd_onepass", 1);
-    return {dx, dw, db};
-  }
   Tensor scratch = at::empty({2, titb_layernorm_bwd_blocks(rows), C}, fopt);
   CHECK_RC(titb_layernorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), mean.data_ptr<float>(),
                               rstd.data_ptr<float>(), dx.data_ptr(), dw.data_ptr<float>(), db.data_ptr<float>(),
-                              scratch.data_ptr<float>(), rows, (int)C, dt_code(x), have && accumulate, cur_stream()),
-           "layernorm_bwd", 3);
-  if (have_res) dx.add_(dres);
+                              scratch.data_ptr<float>(), rows, (int)C, dt_code(x), have && accumulate,
+                              have_res ? dres.data_ptr() : nullptr, cur_stream()),
+           "layernorm_bwd", 2);
   return {dx, dw, db};
 }
 std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const Tensor& w, double eps) {
@@ -304,8 +270,7 @@ std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const Tensor& w, double eps) {
   return {y, rstd};
 }
 std::vector<Tensor> rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& rstd,
-                                const optional<Tensor>& dw_, bool accumulate, bool onepass,
-                                const optional<Tensor>& dres_) {
+                                const optional<Tensor>& dw_, bool accumulate, const optional<Tensor>& dres_) {
   check_cuda(dy, "dy"); check_cuda(x, "x");
   c10::cuda::CUDAGuard guard(x.device());
   const int64_t C = x.size(-1), rows = x.numel() / C;
@@ -319,22 +284,10 @@ std::vector<Tensor> rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor&
     dres = dres_->contiguous();
     TORCH_CHECK(dres.sizes() == x.sizes() && dres.scalar_type() == x.scalar_type(), "titb200: dres must match x");
   }
-  if (onepass && titb_norm_bwd_onepass_ok(rows, (int)C, dt_code(x), dy.data_ptr(), x.data_ptr(), w.data_ptr(),
-                                          have_res ? dres.data_ptr() : nullptr, dx.data_ptr())) {
-    Tensor scratch = at::empty({titb_norm_bwd_onepass_scratch((int)C)}, fopt);
-    unsigned* counters = ticket_counters(x, titb_norm_bwd_onepass_counters());
-    CHECK_RC(titb_norm_bwd_onepass(dy.data_ptr(), x.data_ptr(), w.data_ptr(), nullptr, rstd.data_ptr<float>(),
-                                   have_res ? dres.data_ptr() : nullptr, dx.data_ptr(), dw.data_ptr<float>(), nullptr,
-                                   scratch.data_ptr<float>(), counters, rows, (int)C, dt_code(x), 1,
-                                   have && accumulate, cur_stream()),
-             "norm_bwd_onepass", 1);
-    return {dx, dw};
-  }
   Tensor scratch = at::empty({2, titb_layernorm_bwd_blocks(rows), C}, fopt);
   CHECK_RC(titb_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(),
                             dw.data_ptr<float>(), scratch.data_ptr<float>(), rows, (int)C, dt_code(x),
-                            have && accumulate, cur_stream()), "rmsnorm_bwd", 2);
-  if (have_res) dx.add_(dres);
+                            have && accumulate, have_res ? dres.data_ptr() : nullptr, cur_stream()), "rmsnorm_bwd", 2);
   return {dx, dw};
 }
 
@@ -725,21 +678,13 @@ std::vector<Tensor> outer_bwd(const Tensor& g_, const Tensor& a_, const Tensor& 
 }
 
 // Column sums of a [rows, C] view into an fp32 [C] tensor (bias gradients).
-Tensor colsum(const Tensor& x, const optional<Tensor>& out_, bool accumulate, bool fused) {
+Tensor colsum(const Tensor& x, const optional<Tensor>& out_, bool accumulate) {
   check_cuda(x, "x");
   c10::cuda::CUDAGuard guard(x.device());
   const int64_t C = x.size(-1), rows = x.numel() / C;
   auto fopt = x.options().dtype(at::kFloat);
   const bool have = out_.has_value() && out_->defined();
   Tensor out = have ? *out_ : at::empty({C}, fopt);
-  if (fused && titb_colsum_fused_ok(x.data_ptr(), rows, (int)C, dt_code(x)) &&
-      titb_colsum_fused_counters((int)C, dt_code(x)) <= 256) {
-    Tensor scratch = at::empty({titb_colsum_fused_scratch(rows, (int)C, dt_code(x))}, fopt);
-    unsigned* counters = ticket_counters(x, titb_colsum_fused_counters((int)C, dt_code(x)));
-    CHECK_RC(titb_colsum_fused(x.data_ptr(), out.data_ptr<float>(), rows, (int)C, dt_code(x), have && accumulate,
-                               scratch.data_ptr<float>(), counters, cur_stream()), "colsum_fused", 1);
-    return out;
-  }
   Tensor scratch = at::empty({titb_colsum_blocks(rows), C}, fopt);
   CHECK_RC(titb_colsum(x.data_ptr(), out.data_ptr<float>(), rows, (int)C, dt_code(x), have && accumulate,
                        scratch.data_ptr<float>(), cur_stream()), "colsum", 2);
@@ -783,10 +728,10 @@ PYBIND11_MODULE(_C, m) {
   m.def("layernorm_fwd", &layernorm_fwd);
   m.def("layernorm_bwd", &layernorm_bwd, py::arg("dy"), py::arg("x"), py::arg("w"), py::arg("mean"), py::arg("rstd"),
         py::arg("dw") = py::none(), py::arg("db") = py::none(), py::arg("accumulate") = false,
-        py::arg("onepass") = false, py::arg("dres") = py::none());
+        py::arg("dres") = py::none());
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd, py::arg("dy"), py::arg("x"), py::arg("w"), py::arg("rstd"),
-        py::arg("dw") = py::none(), py::arg("accumulate") = false, py::arg("onepass") = false,
+        py::arg("dw") = py::none(), py::arg("accumulate") = false,
         py::arg("dres") = py::none());
   m.def("gelu_fwd", &gelu_fwd);
   m.def("gelu_bwd", &gelu_bwd);
@@ -821,8 +766,7 @@ PYBIND11_MODULE(_C, m) {
   m.def("fill_", &fill_);
   m.def("transpose_last2", &transpose_last2);
   m.def("tri", &tri);
-  m.def("colsum", &colsum, py::arg("x"), py::arg("out") = py::none(), py::arg("accumulate") = false,
-        py::arg("fused") = false);
+  m.def("colsum", &colsum, py::arg("x"), py::arg("out") = py::none(), py::arg("accumulate") = false);
   m.def("status_read", &status_read, py::arg("clear") = true);
   m.def("gemm_set_tma_store", [](bool on) { titb_gemm_set_tma_store(on ? 1 : 0); });
   m.def("attn_bwd_set_warps", [](int warps) { titb_attn_bwd_set_warps(warps); });

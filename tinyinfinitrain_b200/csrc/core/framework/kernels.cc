@@ -384,7 +384,7 @@ std::tuple<TP, TP, TP> LayerNormBackward(const TP& input, const TP& weight, cons
     at::Tensor scratch = at::empty({2, titb_layernorm_bwd_blocks(rows), C}, fopt);
     ok(titb_layernorm_bwd(go.data_ptr(), x.data_ptr(), weight->data().data_ptr(), mean->data().data_ptr<float>(),
                           rstd->data().data_ptr<float>(), dx.data_ptr(), dw.data_ptr<float>(), db.data_ptr<float>(),
-                          scratch.data_ptr<float>(), rows, (int)C, dt(x), 0, stream()), "LayerNormBackward");
+                          scratch.data_ptr<float>(), rows, (int)C, dt(x), 0, nullptr, stream()), "LayerNormBackward");
     return {W(dx), W(dw.to(weight->data().scalar_type())), W(db.to(weight->data().scalar_type()))};
   }
   at::Tensor xf = x.to(at::kFloat).reshape({rows, C}), g = go.to(at::kFloat).reshape({rows, C});
@@ -423,7 +423,7 @@ std::pair<TP, TP> RMSNormBackward(const TP& input, const TP& weight, const TP& r
     at::Tensor dx = at::empty_like(x), dw = at::empty({C}, fopt);
     at::Tensor scratch = at::empty({2, titb_layernorm_bwd_blocks(rows), C}, fopt);
     ok(titb_rmsnorm_bwd(g.data_ptr(), x.data_ptr(), weight->data().data_ptr(), rstd->data().data_ptr<float>(), dx.data_ptr(),
-                        dw.data_ptr<float>(), scratch.data_ptr<float>(), rows, (int)C, dt(x), 0, stream()), "RMSNormBackward");
+                        dw.data_ptr<float>(), scratch.data_ptr<float>(), rows, (int)C, dt(x), 0, nullptr, stream()), "RMSNormBackward");
     return {W(dx), W(dw.to(weight->data().scalar_type()))};
   }
   at::Tensor xf = x.to(at::kFloat).reshape({rows, C}), gf = g.to(at::kFloat).reshape({rows, C});

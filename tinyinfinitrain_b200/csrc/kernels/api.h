@@ -105,28 +105,17 @@ TITB_API int titb_sgemm(const float* A, const float* B, float* C, int M, int N, 
 TITB_API int titb_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
                                 long long rows, int C, float eps, int dtype, cudaStream_t stream);
 // dw/db partial sums use `scratch` (fp32 [2, nblocks, C]); nblocks = titb_layernorm_bwd_blocks(rows).
+// `dres` (optional, same shape and dtype as x): a gradient arriving through a residual connection around the norm;
+// dx = norm backward + dres, added inside the kernel.
 TITB_API int titb_layernorm_bwd_blocks(long long rows);
 TITB_API int titb_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
                                 void* dx, float* dw, float* db, float* scratch, long long rows, int C, int dtype,
-                                int accumulate_wgrad, cudaStream_t stream);
+                                int accumulate_wgrad, const void* dres, cudaStream_t stream);
 TITB_API int titb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long long rows, int C, float eps,
                               int dtype, cudaStream_t stream);
 TITB_API int titb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw,
-                              float* scratch, long long rows, int C, int dtype, int accumulate_wgrad,
+                              float* scratch, long long rows, int C, int dtype, int accumulate_wgrad, const void* dres,
                               cudaStream_t stream);
-// LayerNorm (rms == 0) or RMSNorm (rms != 0) backward in one launch, for rows of at most 128 16-byte vectors:
-// dx (+ dres when it is not null) and the finished dweight / dbias.  `scratch`: titb_norm_bwd_onepass_scratch(C)
-// floats; `counters`: titb_norm_bwd_onepass_counters() unsigned words, zero before the first launch and left zero by
-// every launch (launches that share them must be ordered on one stream).
-TITB_API int titb_norm_bwd_onepass_ok(long long rows, int C, int dtype, const void* dy, const void* x, const void* w,
-                                      const void* dres, const void* dx);
-TITB_API long long titb_norm_bwd_onepass_scratch(int C);
-TITB_API int titb_norm_bwd_onepass_counters();
-TITB_API int titb_norm_bwd_onepass(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
-                                   const void* dres, void* dx, float* dw, float* db, float* scratch,
-                                   unsigned* counters, long long rows, int C, int dtype, int rms, int accumulate_wgrad,
-                                   cudaStream_t stream);
-
 // ---- activations ----------------------------------------------------------------
 TITB_API int titb_gelu_fwd(const void* x, void* y, long long n, int dtype, cudaStream_t stream);
 TITB_API int titb_gelu_bwd(const void* dy, const void* x, void* dx, long long n, int dtype, cudaStream_t stream);
@@ -231,15 +220,6 @@ TITB_API int titb_tri(const void* x, void* y, int R, int C, int diagonal, int up
 TITB_API int titb_colsum(const void* x, float* out, long long rows, int C, int dtype, int accumulate,
                          float* scratch, cudaStream_t stream);
 TITB_API int titb_colsum_blocks(long long rows);
-// One-launch column sums: the last CTA of each column strip folds the partial rows.  `scratch` holds
-// titb_colsum_fused_scratch floats, `counters` titb_colsum_fused_counters unsigned words that are zero before the
-// first launch (every launch leaves them zero); launches that share counters must be ordered on one stream.
-TITB_API int titb_colsum_fused_ok(const void* x, long long rows, int C, int dtype);
-TITB_API long long titb_colsum_fused_scratch(long long rows, int C, int dtype);
-TITB_API int titb_colsum_fused_counters(int C, int dtype);
-TITB_API int titb_colsum_fused(const void* x, float* out, long long rows, int C, int dtype, int accumulate,
-                               float* scratch, unsigned* counters, cudaStream_t stream);
-
 // ---- reductions and view-like transforms (dtype: 0 = fp32, 1 = bf16) ---------------------------------
 // x viewed as [outer, n, inner] -> y [outer, inner].  op: 0 sum, 1 mean, 2 max, 3 min; for max / min `idx`
 // (may be null) receives the position along n of the selected element (lowest index on ties).

@@ -21,7 +21,7 @@ TITB_API int titb_layernorm_bwd_noalloc(const void* dy, const void* x, const voi
                                         int dtype, int accumulate_wgrad, cudaStream_t stream) {
   if (C <= 0 || rows < 0) return TITB_ERR_SHAPE;
   if (C > TITB_NOALLOC_LAYERNORM_MAX_C) return TITB_ERR_NOALLOC_TOO_LARGE;
-  if (titb_layernorm_bwd_blocks(rows) != kParts) return TITB_ERR_NOALLOC_SYMBOL;
+  if (titb_layernorm_bwd_blocks(rows) != kParts) return TITB_ERR_NOALLOC_LAYOUT;
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return static_cast<int>(e);
@@ -36,7 +36,7 @@ TITB_API int titb_layernorm_bwd_noalloc(const void* dy, const void* x, const voi
     g_scratch_addr[dev] = static_cast<float*>(p);
   }
   return titb_layernorm_bwd(dy, x, w, mean, rstd, dx, dw, db, g_scratch_addr[dev], rows, C, dtype, accumulate_wgrad,
-                            stream);
+                            nullptr, stream);
 }
 
 TITB_API const char* titb_strerror(int code) {
@@ -48,6 +48,8 @@ TITB_API const char* titb_strerror(int code) {
     case TITB_ERR_NOALLOC_TOO_LARGE:
       return "row width exceeds TITB_NOALLOC_LAYERNORM_MAX_C, the largest the built-in scratch array can serve";
     case TITB_ERR_NOALLOC_SYMBOL: return "the built-in scratch array could not be located on this device";
+    case TITB_ERR_NOALLOC_LAYOUT:
+      return "the built-in scratch array was sized for another partial-row count than the LayerNorm backward kernel uses";
     default: return cudaGetErrorString(static_cast<cudaError_t>(code));
   }
 }

@@ -43,6 +43,7 @@ TITB_API int titb_layernorm_bwd_noalloc(const void* dy, const void* x, const voi
 
 #define TITB_ERR_NOALLOC_TOO_LARGE 20010
 #define TITB_ERR_NOALLOC_SYMBOL 20011
+#define TITB_ERR_NOALLOC_LAYOUT 20012  /* library built inconsistently: scratch sized for another kernel layout */
 
 // Text for the library's own error codes (>= 20000); cudaGetErrorString for anything else.
 TITB_API const char* titb_strerror(int code);

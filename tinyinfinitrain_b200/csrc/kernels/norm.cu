@@ -99,9 +99,9 @@ __global__ void norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w
 // for the columns it owns in registers; the partials go to scratch[2][nparts][C].
 template <typename T, int MAXV, int G, bool RMS>
 __global__ void norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
-                                const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
-                                T* __restrict__ dx, float* __restrict__ scratch, long long rows, int C,
-                                int nparts) {
+                                const T* __restrict__ dres, const float* __restrict__ mean_in,
+                                const float* __restrict__ rstd_in, T* __restrict__ dx, float* __restrict__ scratch,
+                                long long rows, int C, int nparts) {
   constexpr int VN = VecN<T>::n;
   __shared__ float red[2 * (G > 32 ? G / 32 : 1)];
   const int tig = (G == 32) ? (threadIdx.x & 31) : threadIdx.x;
@@ -153,12 +153,15 @@ __global__ void norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ 
     for (int k = 0; k < MAXV; ++k) {
       const int i = tig + k * G;
       if (i < nvec) {
-        Pack<T, VN> ov;
+        Pack<T, VN> ov, rv;
+        if (dres != nullptr) rv = ld128(dres + row * C + i * VN);
 #pragma unroll
         for (int e = 0; e < VN; ++e) {
           float n = (to_f32(xv[k].v[e]) - mean) * rstd;
           float dn = to_f32(dv[k].v[e]) * to_f32(wv[k].v[e]);
-          ov.v[e] = from_f32<T>((dn - m1 - n * m2) * rstd);
+          float o = (dn - m1 - n * m2) * rstd;
+          if (dres != nullptr) o += to_f32(rv.v[e]);
+          ov.v[e] = from_f32<T>(o);
         }
         st128(dxr + i * VN, ov);
       }
@@ -207,6 +210,195 @@ __global__ void norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ 
   }
 }
 
+template <typename P>
+__device__ __forceinline__ void opaque128(P& p) {
+  static_assert(sizeof(P) == 16, "128-bit pack expected");
+  uint32_t* u = reinterpret_cast<uint32_t*>(&p);
+  asm volatile("" : "+r"(u[0]), "+r"(u[1]), "+r"(u[2]), "+r"(u[3]));
+}
+
+// Four independent warp sums with interleaved shuffles (one exposed shuffle latency instead of four).
+__device__ __forceinline__ void warp_sum4(float& a, float& b, float& c, float& d) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ta = __shfl_xor_sync(0xffffffffu, a, o), tb = __shfl_xor_sync(0xffffffffu, b, o);
+    const float tc = __shfl_xor_sync(0xffffffffu, c, o), td = __shfl_xor_sync(0xffffffffu, d, o);
+    a += ta; b += tb; c += tc; d += td;
+  }
+}
+
+// Backward for rows that fit one warp (C <= 32 * NV * VN): 8 warps per CTA, 2 CTAs per SM, every warp keeps
+// two rows in flight (all loads of both rows are issued before the first use), which puts about 100 KB of
+// loads in flight per SM.  `dres` (optional) is a gradient that arrives through a residual connection around
+// the norm: it is added to dx here instead of by a separate kernel.  The dweight / dbias partial sums of a warp
+// live in its private slice of shared memory (registers are needed for the two rows), laid out so that every
+// access is a conflict-free float4 per lane; at the end they are folded over the CTA's warps in warp order and
+// leave as one partial row per CTA: scratch[0][cta][C] (dweight), scratch[1][cta][C] (dbias).
+template <typename T, int NV, bool RMS>
+__global__ void __launch_bounds__(256, 2)
+norm_bwd_rows2_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
+                      const T* __restrict__ dres, const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
+                      T* __restrict__ dx, float* __restrict__ scratch, long long rows, int C, int nparts) {
+  constexpr int VN = VecN<T>::n;
+  constexpr int Q = VN / 4;                       // float4 groups per 128-bit vector
+  constexpr int kPerWarp = NV * Q * 32 * 4;       // floats of one gradient held by one warp
+  constexpr int kGrads = RMS ? 1 : 2;
+  extern __shared__ float4 acc4[];                // [8 warps][kGrads][NV][Q][32 lanes] float4
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long gw = blockIdx.x * 8LL + warp, nw = gridDim.x * 8LL;
+  const int nvec = C / VN;
+  const float invC = 1.f / C;
+  float4* my_dw = acc4 + (warp * kGrads) * (kPerWarp / 4);
+  float4* my_db = my_dw + kPerWarp / 4;
+
+  Pack<T, VN> wv[NV];
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int i = lane + k * 32;
+    if (i < nvec) wv[k] = ld128(w + i * VN);
+#pragma unroll
+    for (int q = 0; q < Q; ++q) {
+      my_dw[(k * Q + q) * 32 + lane] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (!RMS) my_db[(k * Q + q) * 32 + lane] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
+
+  for (long long r0 = gw; r0 < rows; r0 += 2 * nw) {
+    const long long r1 = r0 + nw;
+    const bool has1 = r1 < rows;
+    Pack<T, VN> xa[NV], da[NV], xb[NV], db_[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int i = lane + k * 32;
+      if (i < nvec) {
+        xa[k] = ld128(x + r0 * C + i * VN);
+        da[k] = ld128(dy + r0 * C + i * VN);
+        if (has1) {
+          xb[k] = ld128(x + r1 * C + i * VN);
+          db_[k] = ld128(dy + r1 * C + i * VN);
+        }
+      }
+    }
+    const float mean0 = RMS ? 0.f : mean_in[r0], rstd0 = rstd_in[r0];
+    const float mean1 = (RMS || !has1) ? 0.f : mean_in[r1], rstd1 = has1 ? rstd_in[r1] : 0.f;
+    float s1a = 0.f, s2a = 0.f, s1b = 0.f, s2b = 0.f;  // sum(dnorm), sum(dnorm * norm) of the two rows
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int i = lane + k * 32;
+      if (i < nvec) {
+#pragma unroll
+        for (int q = 0; q < Q; ++q) {
+          float gw4[4], gb4[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int e = q * 4 + j;
+            const float wf = to_f32(wv[k].v[e]);
+            const float n0 = (to_f32(xa[k].v[e]) - mean0) * rstd0;
+            const float g0 = to_f32(da[k].v[e]);
+            s1a += g0 * wf;
+            s2a += g0 * wf * n0;
+            gw4[j] = g0 * n0;
+            gb4[j] = g0;
+            if (has1) {
+              const float n1 = (to_f32(xb[k].v[e]) - mean1) * rstd1;
+              const float g1 = to_f32(db_[k].v[e]);
+              s1b += g1 * wf;
+              s2b += g1 * wf * n1;
+              gw4[j] += g1 * n1;
+              gb4[j] += g1;
+            }
+          }
+          float4 a = my_dw[(k * Q + q) * 32 + lane];
+          a.x += gw4[0]; a.y += gw4[1]; a.z += gw4[2]; a.w += gw4[3];
+          my_dw[(k * Q + q) * 32 + lane] = a;
+          if (!RMS) {
+            float4 b = my_db[(k * Q + q) * 32 + lane];
+            b.x += gb4[0]; b.y += gb4[1]; b.z += gb4[2]; b.w += gb4[3];
+            my_db[(k * Q + q) * 32 + lane] = b;
+          }
+        }
+      }
+    }
+    warp_sum4(s1a, s2a, s1b, s2b);
+    // The packed rows pass through an opaque no-op: the compiler then unpacks them again below instead of keeping
+    // every converted element of both rows alive across the reduction (which spilled).
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      opaque128(xa[k]); opaque128(da[k]); opaque128(xb[k]); opaque128(db_[k]);
+    }
+    const float m1a = RMS ? 0.f : s1a * invC, m2a = s2a * invC;
+    const float m1b = RMS ? 0.f : s1b * invC, m2b = s2b * invC;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int i = lane + k * 32;
+      if (i < nvec) {
+        Pack<T, VN> oa, ob, ra, rb;
+        if (dres != nullptr) {
+          ra = ld128(dres + r0 * C + i * VN);
+          if (has1) rb = ld128(dres + r1 * C + i * VN);
+        }
+#pragma unroll
+        for (int e = 0; e < VN; ++e) {
+          const float wf = to_f32(wv[k].v[e]);
+          const float n0 = (to_f32(xa[k].v[e]) - mean0) * rstd0;
+          float o0 = (to_f32(da[k].v[e]) * wf - m1a - n0 * m2a) * rstd0;
+          if (dres != nullptr) o0 += to_f32(ra.v[e]);
+          oa.v[e] = from_f32<T>(o0);
+          if (has1) {
+            const float n1 = (to_f32(xb[k].v[e]) - mean1) * rstd1;
+            float o1 = (to_f32(db_[k].v[e]) * wf - m1b - n1 * m2b) * rstd1;
+            if (dres != nullptr) o1 += to_f32(rb.v[e]);
+            ob.v[e] = from_f32<T>(o1);
+          }
+        }
+        st128(dx + r0 * C + i * VN, oa);
+        if (has1) st128(dx + r1 * C + i * VN, ob);
+      }
+    }
+  }
+
+  // fold the 8 warps' sums in warp order; one partial row per CTA.  Column c = vec * VN + q * 4 + j lives at
+  // float index ((k * Q + q) * 32 + lane) * 4 + j of a warp's slice, with vec = lane + 32 k.
+  __syncthreads();
+  const float* accf = reinterpret_cast<const float*>(acc4);
+  float* dwp = scratch + (long long)blockIdx.x * C;
+  float* dbp = scratch + ((long long)nparts + blockIdx.x) * C;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const int vec = c / VN, e = c - vec * VN;
+    const int k = vec >> 5, ln = vec & 31, q = e >> 2, j = e & 3;
+    const int idx = ((k * Q + q) * 32 + ln) * 4 + j;
+    float tw = 0.f, tb = 0.f;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      tw += accf[(g * kGrads) * kPerWarp + idx];
+      if (!RMS) tb += accf[(g * kGrads + 1) * kPerWarp + idx];
+    }
+    dwp[c] = tw;
+    if (!RMS) dbp[c] = tb;
+  }
+}
+
+// Stage 2 for both gradients in one launch: blockIdx.y = 0 folds the dweight partial rows, 1 the dbias rows.
+__global__ void partial_colsum2_kernel(const float* __restrict__ scratch, float* __restrict__ dw, float* __restrict__ db,
+                                       int used, int nparts, int C, int accumulate) {
+  __shared__ float sm[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + tx;
+  const float* src = scratch + (long long)blockIdx.y * nparts * C;
+  float* out = blockIdx.y == 0 ? dw : db;
+  float s = 0.f;
+  if (c < C)
+    for (int p = ty; p < used; p += 8) s += src[(long long)p * C + c];
+  sm[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && c < C) {
+    float t = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) t += sm[j][tx];
+    out[c] = accumulate ? out[c] + t : t;
+  }
+}
+
 // Stage 2: out[c] (+)= sum_p scratch[p][c], in a fixed order.  32 columns per CTA,
 // 8 threads per column each summing every 8th partial row.
 __global__ void partial_colsum_kernel(const float* __restrict__ scratch, float* __restrict__ out, int nparts, int C,
@@ -251,8 +443,8 @@ __global__ void norm_fwd_generic(const T* x, const T* w, const T* b, T* y, float
   }
 }
 template <typename T, bool RMS>
-__global__ void norm_bwd_dx_generic(const T* dy, const T* x, const T* w, const float* mean_in, const float* rstd_in,
-                                    T* dx, long long rows, int C) {
+__global__ void norm_bwd_dx_generic(const T* dy, const T* x, const T* w, const T* dres, const float* mean_in,
+                                    const float* rstd_in, T* dx, long long rows, int C) {
   __shared__ float red[32];
   const long long row = blockIdx.x;
   const float mean = RMS ? 0.f : mean_in[row], rstd = rstd_in[row];
@@ -268,7 +460,9 @@ __global__ void norm_bwd_dx_generic(const T* dy, const T* x, const T* w, const f
   for (int i = threadIdx.x; i < C; i += blockDim.x) {
     float n = (to_f32(x[row * C + i]) - mean) * rstd;
     float dn = to_f32(dy[row * C + i]) * to_f32(w[i]);
-    dx[row * C + i] = from_f32<T>((dn - m1 - n * m2) * rstd);
+    float o = (dn - m1 - n * m2) * rstd;
+    if (dres != nullptr) o += to_f32(dres[row * C + i]);
+    dx[row * C + i] = from_f32<T>(o);
   }
 }
 template <typename T, bool RMS>
@@ -327,33 +521,47 @@ static int norm_fwd_launch(const void* x, const void* w, const void* b, void* y,
   return (int)cudaGetLastError();
 }
 
+int device_sm_count();
+
 template <typename T, bool RMS>
-static int norm_bwd_launch(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
-                           void* dx, float* dw, float* db, float* scratch, long long rows, int C, int accumulate,
-                           cudaStream_t st) {
+static int norm_bwd_launch(const void* dy, const void* x, const void* w, const void* dres, const float* mean,
+                           const float* rstd, void* dx, float* dw, float* db, float* scratch, long long rows, int C,
+                           int accumulate, cudaStream_t st) {
   if (rows <= 0) return 0;
+  constexpr int VN = VecN<T>::n;
   const T* DY = static_cast<const T*>(dy); const T* X = static_cast<const T*>(x); const T* W = static_cast<const T*>(w);
+  const T* R = static_cast<const T*>(dres);
   T* DX = static_cast<T*>(dx);
   NormPlan p = plan_norm<T>(C);
-  const bool aligned = !((uintptr_t)x & 15) && !((uintptr_t)dy & 15) && !((uintptr_t)w & 15) && !((uintptr_t)dx & 15);
+  const bool aligned = !((uintptr_t)x & 15) && !((uintptr_t)dy & 15) && !((uintptr_t)w & 15) && !((uintptr_t)dx & 15) &&
+                       !((uintptr_t)dres & 15);
   if (p.G != 0 && aligned && scratch != nullptr) {
     const int nparts = kNormBwdParts;  // scratch is [2][kNormBwdParts][C]; the first `used` rows are written
     int used;
     if (p.G == 32) {
-      used = kNormBwdBlocks;
-      const size_t sm = 2 * (size_t)C * sizeof(float);
-      if (p.maxv == 4) norm_bwd_kernel<T, 4, 32, RMS><<<used, 128, sm, st>>>(DY, X, W, mean, rstd, DX, scratch, rows, C, nparts);
-      else norm_bwd_kernel<T, 8, 32, RMS><<<used, 128, sm, st>>>(DY, X, W, mean, rstd, DX, scratch, rows, C, nparts);
+      used = 2 * device_sm_count();
+      if (used > kNormBwdBlocks) used = kNormBwdBlocks;
+      const int nv = (C / VN + 31) / 32;  // 128-bit vectors per lane
+      auto launch = [&](auto kern, int NVc) {
+        // per warp and gradient: NVc vectors * VN floats * 32 lanes
+        const size_t sm = 8 * (size_t)(RMS ? 1 : 2) * NVc * VN * 32 * sizeof(float);
+        if (sm > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+        kern<<<used, 256, sm, st>>>(DY, X, W, R, mean, rstd, DX, scratch, rows, C, nparts);
+      };
+      if (nv <= 3) launch(norm_bwd_rows2_kernel<T, 3, RMS>, 3);
+      else if (nv <= 4) launch(norm_bwd_rows2_kernel<T, 4, RMS>, 4);
+      else {  // up to 8 vectors per lane: one row at a time per warp, sums in registers
+        used = kNormBwdBlocks;
+        norm_bwd_kernel<T, 8, 32, RMS><<<used, 128, 2 * (size_t)C * sizeof(float), st>>>(DY, X, W, R, mean, rstd, DX, scratch, rows, C, nparts);
+      }
     } else {
       used = kNormBwdParts;
-      if (p.maxv == 2) norm_bwd_kernel<T, 2, 256, RMS><<<used, 256, 0, st>>>(DY, X, W, mean, rstd, DX, scratch, rows, C, nparts);
-      else norm_bwd_kernel<T, 8, 256, RMS><<<used, 256, 0, st>>>(DY, X, W, mean, rstd, DX, scratch, rows, C, nparts);
+      if (p.maxv == 2) norm_bwd_kernel<T, 2, 256, RMS><<<used, 256, 0, st>>>(DY, X, W, R, mean, rstd, DX, scratch, rows, C, nparts);
+      else norm_bwd_kernel<T, 8, 256, RMS><<<used, 256, 0, st>>>(DY, X, W, R, mean, rstd, DX, scratch, rows, C, nparts);
     }
-    partial_colsum_kernel<<<(C + 31) / 32, 256, 0, st>>>(scratch, dw, used, C, accumulate);
-    if (!RMS && db)
-      partial_colsum_kernel<<<(C + 31) / 32, 256, 0, st>>>(scratch + (long long)nparts * C, db, used, C, accumulate);
+    partial_colsum2_kernel<<<dim3((C + 31) / 32, (!RMS && db) ? 2 : 1), 256, 0, st>>>(scratch, dw, db, used, nparts, C, accumulate);
   } else {
-    norm_bwd_dx_generic<T, RMS><<<(unsigned)rows, 256, 0, st>>>(DY, X, W, mean, rstd, DX, rows, C);
+    norm_bwd_dx_generic<T, RMS><<<(unsigned)rows, 256, 0, st>>>(DY, X, W, R, mean, rstd, DX, rows, C);
     norm_bwd_dw_generic<T, RMS><<<(C + 127) / 128, 128, 0, st>>>(DY, X, mean, rstd, dw, db, rows, C, accumulate);
   }
   return (int)cudaGetLastError();
@@ -371,10 +579,10 @@ TITB_API int titb_layernorm_fwd(const void* x, const void* w, const void* b, voi
 TITB_API int titb_layernorm_bwd_blocks(long long) { return kNormBwdParts; }
 TITB_API int titb_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
                                 void* dx, float* dw, float* db, float* scratch, long long rows, int C, int dtype,
-                                int accumulate_wgrad, cudaStream_t stream) {
+                                int accumulate_wgrad, const void* dres, cudaStream_t stream) {
   return dtype == 1
-             ? norm_bwd_launch<bf16, false>(dy, x, w, mean, rstd, dx, dw, db, scratch, rows, C, accumulate_wgrad, stream)
-             : norm_bwd_launch<float, false>(dy, x, w, mean, rstd, dx, dw, db, scratch, rows, C, accumulate_wgrad, stream);
+             ? norm_bwd_launch<bf16, false>(dy, x, w, dres, mean, rstd, dx, dw, db, scratch, rows, C, accumulate_wgrad, stream)
+             : norm_bwd_launch<float, false>(dy, x, w, dres, mean, rstd, dx, dw, db, scratch, rows, C, accumulate_wgrad, stream);
 }
 TITB_API int titb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long long rows, int C, float eps,
                               int dtype, cudaStream_t stream) {
@@ -382,9 +590,9 @@ TITB_API int titb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd
                     : norm_fwd_launch<float, true>(x, w, w, y, nullptr, rstd, rows, C, eps, stream);
 }
 TITB_API int titb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw,
-                              float* scratch, long long rows, int C, int dtype, int accumulate_wgrad,
+                              float* scratch, long long rows, int C, int dtype, int accumulate_wgrad, const void* dres,
                               cudaStream_t stream) {
   return dtype == 1
-             ? norm_bwd_launch<bf16, true>(dy, x, w, nullptr, rstd, dx, dw, nullptr, scratch, rows, C, accumulate_wgrad, stream)
-             : norm_bwd_launch<float, true>(dy, x, w, nullptr, rstd, dx, dw, nullptr, scratch, rows, C, accumulate_wgrad, stream);
+             ? norm_bwd_launch<bf16, true>(dy, x, w, dres, nullptr, rstd, dx, dw, nullptr, scratch, rows, C, accumulate_wgrad, stream)
+             : norm_bwd_launch<float, true>(dy, x, w, dres, nullptr, rstd, dx, dw, nullptr, scratch, rows, C, accumulate_wgrad, stream);
 }

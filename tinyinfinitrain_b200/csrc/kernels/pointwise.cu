@@ -12,6 +12,7 @@
 namespace titb {
 
 constexpr int kEwThreads = 256;
+int device_sm_count();
 
 static inline int ew_blocks(long long nvec) {
   long long b = (nvec + kEwThreads - 1) / kEwThreads;
@@ -217,35 +218,61 @@ __global__ void tri_kernel(const T* __restrict__ x, T* __restrict__ y, int R, in
 
 // Column sums of a [rows, C] matrix in two deterministic stages (bias gradients).
 constexpr int kColsumParts = 148 * 2;
-template <typename T>
-__global__ void colsum_stage1(const T* __restrict__ x, float* __restrict__ scratch, long long rows, int C) {
-  // CTA = 32 x 8 threads over a 32*VN-column strip; blockIdx.y walks row chunks.
+// Stage 1: a warp reads whole row segments (coalesced), four rows in flight, and keeps the sums of its NV * VN
+// columns per lane in registers; the 8 warps of a CTA fold their sums in warp order through shared memory and the
+// CTA writes one partial row.  blockIdx.y selects a strip of 32 * NV * VN columns.
+template <typename T, int NV>
+__global__ void __launch_bounds__(256) colsum_rows_kernel(const T* __restrict__ x, float* __restrict__ scratch,
+                                                          long long rows, int C) {
   constexpr int VN = VecN<T>::n;
-  __shared__ float sm[8][32 * VN + 1];
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-  const int c = (blockIdx.x * 32 + tx) * VN;
-  float acc[VN];
+  constexpr int kStrip = 32 * NV * VN;
+  __shared__ float sm[kStrip];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c0 = blockIdx.y * kStrip;
+  const long long gw = blockIdx.x * 8LL + warp, nw = gridDim.x * 8LL;
+  float acc[NV][VN];
 #pragma unroll
-  for (int e = 0; e < VN; ++e) acc[e] = 0.f;
-  if (c < C) {
-    for (long long r = (long long)blockIdx.y * 8 + ty; r < rows; r += (long long)gridDim.y * 8) {
-      Pack<T, VN> v = ld128(x + r * C + c);
+  for (int k = 0; k < NV; ++k)
 #pragma unroll
-      for (int e = 0; e < VN; ++e) acc[e] += to_f32(v.v[e]);
+    for (int e = 0; e < VN; ++e) acc[k][e] = 0.f;
+  for (long long r = gw; r < rows; r += 4 * nw) {
+    Pack<T, VN> v[4][NV];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const long long rr = r + q * nw;
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        const int c = c0 + (lane + k * 32) * VN;
+        if (rr < rows && c < C) v[q][k] = ld128(x + rr * C + c);
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const long long rr = r + q * nw;
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        const int c = c0 + (lane + k * 32) * VN;
+        if (rr < rows && c < C) {
+#pragma unroll
+          for (int e = 0; e < VN; ++e) acc[k][e] += to_f32(v[q][k].v[e]);
+        }
+      }
     }
   }
+  for (int g = 0; g < 8; ++g) {
+    if (warp == g) {
 #pragma unroll
-  for (int e = 0; e < VN; ++e) sm[ty][tx * VN + e] = acc[e];
-  __syncthreads();
-  for (int i = threadIdx.x; i < 32 * VN; i += blockDim.x) {
-    const int cc = blockIdx.x * 32 * VN + i;
-    if (cc < C) {
-      float t = 0.f;
+      for (int k = 0; k < NV; ++k)
 #pragma unroll
-      for (int j = 0; j < 8; ++j) t += sm[j][i];
-      scratch[(long long)blockIdx.y * C + cc] = t;
+        for (int e = 0; e < VN; ++e) {
+          const int i = (lane + k * 32) * VN + e;
+          sm[i] = (g == 0 ? 0.f : sm[i]) + acc[k][e];
+        }
     }
+    __syncthreads();
   }
+  for (int i = threadIdx.x; i < kStrip; i += blockDim.x)
+    if (c0 + i < C) scratch[(long long)blockIdx.x * C + c0 + i] = sm[i];
 }
 __global__ void colsum_stage2(const float* __restrict__ scratch, float* __restrict__ out, int nparts, int C,
                               int accumulate) {
@@ -422,11 +449,21 @@ TITB_API int titb_colsum(const void* x, float* out, long long rows, int C, int d
   if (C <= 0) return 0;
   const int vn = dtype == 1 ? 8 : 4;
   if (scratch && (C % vn) == 0 && !((uintptr_t)x & 15) && rows > 0) {
-    int parts = (int)((rows + 31) / 32);
+    // strips of 32 * NV vectors; NV = 3 fits widths that are multiples of 768 (bf16) exactly, NV = 4 otherwise
+    const int nvec = C / vn;
+    const int nv = (nvec % 96 == 0 || nvec <= 96) ? 3 : 4;
+    const int strips = (nvec + 32 * nv - 1) / (32 * nv);
+    int parts = (2 * device_sm_count() + strips - 1) / strips;
     if (parts > kColsumParts) parts = kColsumParts;
-    dim3 grid((C / vn + 31) / 32, parts);
-    if (dtype == 1) colsum_stage1<bf16><<<grid, 256, 0, st>>>((const bf16*)x, scratch, rows, C);
-    else colsum_stage1<float><<<grid, 256, 0, st>>>((const float*)x, scratch, rows, C);
+    if (parts > (rows + 7) / 8) parts = (int)((rows + 7) / 8);
+    dim3 grid(parts, strips);
+    if (dtype == 1) {
+      if (nv == 3) colsum_rows_kernel<bf16, 3><<<grid, 256, 0, st>>>((const bf16*)x, scratch, rows, C);
+      else colsum_rows_kernel<bf16, 4><<<grid, 256, 0, st>>>((const bf16*)x, scratch, rows, C);
+    } else {
+      if (nv == 3) colsum_rows_kernel<float, 3><<<grid, 256, 0, st>>>((const float*)x, scratch, rows, C);
+      else colsum_rows_kernel<float, 4><<<grid, 256, 0, st>>>((const float*)x, scratch, rows, C);
+    }
     colsum_stage2<<<(C + 31) / 32, 256, 0, st>>>(scratch, out, parts, C, accumulate);
   } else {
     if (dtype == 1) colsum_generic<bf16><<<(C + 127) / 128, 128, 0, st>>>((const bf16*)x, out, rows, C, accumulate);

@@ -31,10 +31,6 @@ EPI_NONE, EPI_BIAS, EPI_BIAS_GELU, EPI_DGELU, EPI_BIAS_RESIDUAL = 0, 1, 2, 3, 4
 # TITB200_DETERMINISTIC=1: the token-embedding gradient is built by a sorted segment reduction instead of fp32 atomics
 # (the one reduction of the training step whose summation order otherwise depends on timing)
 DETERMINISTIC_EMBEDDING_GRAD = os.environ.get("TITB200_DETERMINISTIC", "0") == "1"
-# bias gradients with the one-launch column sum (the last CTA of a column strip folds the partial rows)
-COLSUM_FUSED = os.environ.get("TITB200_COLSUM_FUSED", "0") == "1"
-# LayerNorm / RMSNorm backward as one launch (dx, finished dweight / dbias, residual gradient folded in)
-NORM_BWD_ONEPASS = os.environ.get("TITB200_NORM_BWD_ONEPASS", "0") == "1"
 
 _bf16 = torch.bfloat16
 
@@ -70,10 +66,10 @@ def _wgrad(dy2: torch.Tensor, x2: torch.Tensor, w: torch.Tensor, alpha=None):
 def _bgrad(dy2: torch.Tensor, b: torch.Tensor):
     mg, acc = _grad_target(b)
     if mg is not None:
-        C.colsum(dy2, out=mg, accumulate=acc, fused=COLSUM_FUSED)
+        C.colsum(dy2, out=mg, accumulate=acc)
         _grad_done(b)
         return None
-    return C.colsum(dy2, fused=COLSUM_FUSED).to(b.dtype)
+    return C.colsum(dy2).to(b.dtype)
 
 
 def gelu_ref(x: torch.Tensor) -> torch.Tensor:
@@ -140,7 +136,7 @@ class _LinearF32Fn(torch.autograd.Function):
         dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
         dx = C.sgemm(dy2, w.contiguous(), False, False).view(ctx.xshape)
         dw = C.sgemm(dy2, x2, True, False)
-        db = C.colsum(dy2, fused=COLSUM_FUSED) if ctx.has_b else None
+        db = C.colsum(dy2) if ctx.has_b else None
         return dx, dw, db
 
 
@@ -272,11 +268,11 @@ class _LayerNormFn(torch.autograd.Function):
         bmg, _ = _grad_target(ctx.b)
         if wmg is not None and bmg is not None:
             dx, _, _ = C.layernorm_bwd(dy, x, w, mean, rstd, dw=wmg, db=bmg, accumulate=wacc,
-                                       onepass=NORM_BWD_ONEPASS, dres=dres)
+                                       dres=dres)
             _grad_done(ctx.w)
             _grad_done(ctx.b)
             return dx, None, None, None, None
-        dx, dw, db = C.layernorm_bwd(dy, x, w, mean, rstd, onepass=NORM_BWD_ONEPASS, dres=dres)
+        dx, dw, db = C.layernorm_bwd(dy, x, w, mean, rstd, dres=dres)
         return dx, dw.to(w.dtype), db.to(w.dtype), None, None
 
 
@@ -287,10 +283,10 @@ def layernorm(x, weight, bias, eps: float = 1e-5):
 
 
 def layernorm_fork(x, weight, bias, eps: float = 1e-5):
-    """(LayerNorm(x), x): use the second value for the residual connection around the normalised branch.  On CUDA with
-    the one-launch backward enabled, the gradient that comes back through the residual is added inside the norm's
-    backward kernel instead of by a separate add."""
-    if not x.is_cuda or not NORM_BWD_ONEPASS:
+    """(LayerNorm(x), x): use the second value for the residual connection around the normalised branch.  On CUDA the
+    gradient that comes back through the residual is added inside the norm's backward kernel instead of by a
+    separate add."""
+    if not x.is_cuda:
         return layernorm(x, weight, bias, eps), x
     return _LayerNormFn.apply(x, weight, bias, eps, True)
 
@@ -313,10 +309,10 @@ class _RMSNormFn(torch.autograd.Function):
         dy = dy.contiguous()
         wmg, wacc = _grad_target(ctx.w)
         if wmg is not None:
-            dx, _ = C.rmsnorm_bwd(dy, x, w, rstd, dw=wmg, accumulate=wacc, onepass=NORM_BWD_ONEPASS, dres=dres)
+            dx, _ = C.rmsnorm_bwd(dy, x, w, rstd, dw=wmg, accumulate=wacc, dres=dres)
             _grad_done(ctx.w)
             return dx, None, None, None
-        dx, dw = C.rmsnorm_bwd(dy, x, w, rstd, onepass=NORM_BWD_ONEPASS, dres=dres)
+        dx, dw = C.rmsnorm_bwd(dy, x, w, rstd, dres=dres)
         return dx, dw.to(w.dtype), None, None
 
 
@@ -333,7 +329,7 @@ def rmsnorm(x, weight, eps: float = 1e-5):
 
 def rmsnorm_fork(x, weight, eps: float = 1e-5):
     """(RMSNorm(x), x); see layernorm_fork."""
-    if not x.is_cuda or not NORM_BWD_ONEPASS:
+    if not x.is_cuda:
         return rmsnorm(x, weight, eps), x
     return _RMSNormFn.apply(x, weight, eps, True)
 

@@ -124,9 +124,7 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no_flush", action="store_true")
     ap.add_argument("--warps", type=int, default=4, help="attn_bwd: 8 = two warps per score row")
-    ap.add_argument("--onepass", action="store_true", help="layernorm_bwd: dx and finished dweight / dbias in one launch")
     ap.add_argument("--residual", action="store_true", help="layernorm_bwd: add a residual gradient to dx")
-    ap.add_argument("--fused", action="store_true", help="colsum: one launch, the last CTA of a column strip folds the partials")
     a = ap.parse_args()
     if a.kernel == "gemm_sweep":
         return gemm_sweep(C, a.model, a.iters)
@@ -183,7 +181,7 @@ def main():
             dy = torch.randn_like(x)
             bytes_ = (4.0 if a.residual else 3.0) * x.numel() * 2
             dres = torch.randn_like(x) if a.residual else None
-            fn = lambda: C.layernorm_bwd(dy, x, w, mean, rstd, onepass=a.onepass, dres=dres)
+            fn = lambda: C.layernorm_bwd(dy, x, w, mean, rstd, dres=dres)
     elif a.kernel == "ag_gemm":
         # X = concat of W shards [M/W, K]; Y = X . B^T, B [N, K]
         M, N, K, W = a.m, a.n, a.k, a.world
@@ -248,7 +246,7 @@ def main():
         x = torch.randn(a.m, a.n, device=dev).to(bf)
         outc = torch.zeros(a.n, device=dev)
         bytes_ = x.numel() * 2.0
-        fn = lambda: C.colsum(x, outc, False, a.fused)
+        fn = lambda: C.colsum(x, outc, False)
     elif a.kernel == "xent":
         logits = torch.randn(a.m, a.n, device=dev).to(bf)
         tgt = torch.randint(0, a.n - 47, (a.m,), device=dev)
