@@ -19,7 +19,7 @@ def main():
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     import tinyinfinitrain_b200 as tit
-    from tinyinfinitrain_b200.models import GPT2Config, LLaMA3Config
+    from tinyinfinitrain_b200.models import GPT2, GPT2Config, LLaMA3, LLaMA3Config
     from tinyinfinitrain_b200.models.tp_models import TPTransformer
     from tinyinfinitrain_b200.parallel.tp import TPComm, sync_sequence_parallel_grads
 
@@ -93,9 +93,13 @@ def main():
         for n, gn in res["nccl"][1].items():
             gf = res["fused"][1][n]
             worst = max(worst, ((gn - gf).abs().max() / (gn.abs().max() + 1e-6)).item())
-        good = dl < 2e-2 and worst < 8e-2
+        # the same seed gives every rank exactly its slices of the single-GPU model: the losses must agree
+        single = (LLaMA3 if isinstance(cfg, LLaMA3Config) else GPT2)(cfg, device=dev, dtype=torch.bfloat16, seed=42)
+        l1 = single(idx, tgt, return_logits=False)[1].item()
+        good = dl < 2e-2 and worst < 8e-2 and abs(l1 - res["fused"][0]) < 3e-2
         ok = ok and good
-        msgs.append(f"{type(cfg).__name__}: loss nccl {res['nccl'][0]:.4f} fused {res['fused'][0]:.4f} worst rel grad diff {worst:.3g}")
+        msgs.append(f"{type(cfg).__name__}: loss nccl {res['nccl'][0]:.4f} fused {res['fused'][0]:.4f} single-GPU {l1:.4f} "
+                    f"worst rel grad diff {worst:.3g}")
     status = tit._lib.C.status_read(True)
     ok = ok and status == 0
     print(f"rank {rank}: ok={ok} status={status}\n  " + "\n  ".join(msgs), flush=True)

@@ -26,7 +26,7 @@ def _lib():
     vp, ll, ci = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int
     lib.titb_layernorm_bwd_noalloc.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, ll, ci, ci, ci, vp]
     lib.titb_layernorm_bwd_noalloc.restype = ci
-    lib.titb_layernorm_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, ll, ci, ci, ci, vp]
+    lib.titb_layernorm_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, ll, ci, ci, ci, vp, vp]   # ..., dres, stream
     lib.titb_layernorm_bwd.restype = ci
     lib.titb_layernorm_bwd_blocks.argtypes = [ll]
     lib.titb_layernorm_bwd_blocks.restype = ci
@@ -61,7 +61,7 @@ def test_noalloc_layernorm_bwd_matches_regular_entry_point(dtype, code):
                                             code, 0, stream)
         assert rc == 0, lib.titb_strerror(rc)
         rc = lib.titb_layernorm_bwd(p(dy), p(x), p(w), p(mean), p(rstd), p(dx_b), p(dw_b), p(db_b), p(scratch), rows,
-                                    C, code, 0, stream)
+                                    C, code, 0, None, stream)
         assert rc == 0, lib.titb_strerror(rc)
         torch.cuda.synchronize()
         tol = dict(atol=1e-4, rtol=1e-4) if dtype == torch.float32 else dict(atol=6e-2, rtol=3e-2)

@@ -17,7 +17,6 @@ SWITCHES = {
     "TITB200_ATTN": "native | sdpa: attention implementation of ops.causal_attention (sdpa = library baseline arm)",
     "TITB200_NO_MULTIMEM": "1: NVLink kernels use peer loads / stores instead of NVLS multimem",
     "TITB200_SYMM_HEAP": "native: symmetric buffers from this package's own cuMem heap instead of PyTorch's",
-    "TITB200_VP_XENT": "1: vocabulary-parallel cross entropy through the two-pass kernels",
     "TITB200_SYMM_ALLREDUCE": "1: --zero_stage 0 sums gradients with the own all-reduce kernel instead of NCCL",
     "TITB200_DETERMINISTIC": "1: sorted, atomics-free token-embedding gradient",
     "TITB200_NVTX": "1: the C++ API drops an NVTX marker per kernel dispatch (op names on an Nsight timeline)",

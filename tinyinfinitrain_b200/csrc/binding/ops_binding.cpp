@@ -769,7 +769,6 @@ PYBIND11_MODULE(_C, m) {
   m.def("colsum", &colsum, py::arg("x"), py::arg("out") = py::none(), py::arg("accumulate") = false);
   m.def("status_read", &status_read, py::arg("clear") = true);
   m.def("gemm_set_tma_store", [](bool on) { titb_gemm_set_tma_store(on ? 1 : 0); });
-  m.def("attn_bwd_set_warps", [](int warps) { titb_attn_bwd_set_warps(warps); });
   bind_attention(m);
   bind_comm(m);
   bind_core(m);

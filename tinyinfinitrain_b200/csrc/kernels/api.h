@@ -94,6 +94,8 @@ TITB_API int titb_gemm_bf16(const TitbGemmDesc* d, cudaStream_t stream);
 TITB_API int titb_gemm_param_gather_bf16(const TitbGemmDesc* d, cudaStream_t stream);
 // Picks the split-K factor the heuristic would use (so callers can size the workspace).
 TITB_API int titb_gemm_pick_splits(int M, int N, int K);
+// Tile width (128, 192 or 256) the GEMM takes for this shape and split-K factor when the descriptor leaves tile_n 0.
+TITB_API int titb_gemm_pick_tile(int M, int N, int K, int splits);
 // Switches the shared-memory-staged TMA store epilogue of bf16 outputs on (default) or off (A/B timing).
 TITB_API void titb_gemm_set_tma_store(int enabled);
 // fp32 SIMT GEMM for API parity with fp32 tensors: C[M,N] (+)= op(A) op(B), row-major.
@@ -262,9 +264,6 @@ struct TitbAttnDesc {
 };
 TITB_API int titb_attn_fwd(const TitbAttnDesc* d, cudaStream_t stream);
 TITB_API int titb_attn_bwd(const TitbAttnDesc* d, cudaStream_t stream);
-// Backward kernel variant: 8 = two warps per score row (eight element-wise warps), anything else = four warps.
-// Process-wide; 8 is the initial value.
-TITB_API void titb_attn_bwd_set_warps(int warps);
 
 // ---- gradient-norm clipping (device resident: graph-capturable) -------------------------------------------------
 // Stage 1: per-block partial sums of squares of a flat fp32 buffer (16-byte aligned).  `partials` must hold

@@ -83,6 +83,16 @@ struct FwdCfg {
   static constexpr int kTmemCols = 256;  // S: [0,128)  O_blk: [128, 128+HD)
 };
 
+// Forward pipeline.  Per key block j the CTA runs
+//   MMA warp:      S(j+1) = Q K(j+1)^T is issued as soon as the softmax warps have copied S(j) out of tensor
+//                  memory (s_free), i.e. it runs underneath the exponentials of block j; O += P(j) V(j) is issued
+//                  when P(j) has been written (p_full) and accumulates in tensor memory over the whole loop.
+//   softmax warps: one score row per thread, read from tensor memory ONCE (128 registers), row maximum, then the
+//                  exponentials straight from registers.  The running maximum `m_ref` that the exponentials refer
+//                  to is only advanced when a block's maximum exceeds it by more than 2^8 (P stays within bf16
+//                  range, the row sum is fp32); only then is the O accumulator rescaled, in place in tensor
+//                  memory, after the previous P V product has finished.  P(j) is stored to shared memory after
+//                  P(j-1) V(j-1) has finished reading the buffer.
 template <int HD>
 __global__ void __launch_bounds__(kAttnThreads, (HD == 64) ? 2 : 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
@@ -96,7 +106,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   uint64_t* s_full = bars + 5;
   uint64_t* p_full = bars + 6;
   uint64_t* o_full = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* s_free = bars + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -113,6 +124,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     ptx::mbar_init(s_full, 1);
     ptx::mbar_init(p_full, 4);
     ptx::mbar_init(o_full, 1);
+    ptx::mbar_init(s_free, 4);
     *abort_flag = (ptx::smem_u32(smem) & 1023u) ? 1u : 0u;  // swizzled tiles need a 1024-byte aligned base
     ptx::mbar_fence_init();
     ptx::tma_prefetch_desc(&tq);
@@ -173,6 +185,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         issue_s(0);
       }
       for (int j = 0; j < nblk && ok; ++j) {
+        if (j + 1 < nblk) {
+          // S(j+1) goes into the score columns as soon as S(j) has been copied to registers
+          if (!ptx::mbar_wait(&kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag)) break;
+          if (!ptx::mbar_wait(s_free, j & 1, abort_flag)) break;
+          ptx::tc_fence_after_sync();
+          issue_s(j + 1);
+        }
         if (!ptx::mbar_wait(p_full, j & 1, abort_flag)) break;
         ptx::tc_fence_after_sync();
         const uint32_t v_base = ptx::smem_u32(smem + Cfg::kV + (j & 1) * Cfg::kTileBytes);
@@ -180,15 +199,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         for (int k = 0; k < kBlk / 16; ++k) {
           const uint32_t a_off = (k >> 2) * kChunkBytes + (k & 3) * 32;
           ptx::mma_f16_ss(tO, ptx::make_smem_desc(p_base + a_off, 16, 1024),
-                          ptx::make_smem_desc(v_base + k * 2048, kChunkBytes, 1024), idesc_o, k > 0);
+                          ptx::make_smem_desc(v_base + k * 2048, kChunkBytes, 1024), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
         }
         ptx::tc_commit(o_full);
         ptx::tc_commit(&kv_empty[j & 1]);
-        if (j + 1 < nblk) {
-          if (!ptx::mbar_wait(&kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag)) break;
-          ptx::tc_fence_after_sync();
-          issue_s(j + 1);
-        }
       }
     }
   } else {
@@ -197,85 +211,123 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     const int q_idx = q0 + row;
     const uint32_t lane_sel = static_cast<uint32_t>(quad * 32) << 16;
     const float sc = p.scale * kLog2e;
-    float m = -INFINITY, l = 0.f;
-    float o[HD];
-#pragma unroll
-    for (int d = 0; d < HD; ++d) o[d] = 0.f;
+    constexpr float kLazy = 8.f;   // log2 of the largest P value tolerated before the reference maximum moves
+    float m_ref = -INFINITY, l = 0.f;
     uint8_t* p_smem = smem + Cfg::kP;
     bool ok = true;
     for (int j = 0; j < nblk; ++j) {
       if (!ptx::mbar_wait(s_full, j & 1, abort_flag)) { ok = false; break; }
       ptx::tc_fence_after_sync();
-      const bool diag = (j == qb);
+      uint32_t r0[32], r1[32], r2[32], r3[32];
+      ptx::tmem_ld32(tS + lane_sel + 0, r0);
+      ptx::tmem_ld32(tS + lane_sel + 32, r1);
+      ptx::tmem_ld32(tS + lane_sel + 64, r2);
+      ptx::tmem_ld32(tS + lane_sel + 96, r3);
+      ptx::tmem_ld_wait();
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(s_free);   // the score columns may be overwritten by S(j+1)
       const int kv0 = j * kBlk;
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        ptx::tmem_ld32(tS + lane_sel + c * 32, r);
-        ptx::tmem_ld_wait();
+      if (j == qb) {  // diagonal block: keys after the query are masked
+        const uint32_t ninf = __float_as_uint(-INFINITY);
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
-          float x = __uint_as_float(r[e]) * sc;
-          if (diag && (kv0 + c * 32 + e > q_idx)) x = -INFINITY;
-          mx = fmaxf(mx, x);
+          if (kv0 + e > q_idx) r0[e] = ninf;
+          if (kv0 + 32 + e > q_idx) r1[e] = ninf;
+          if (kv0 + 64 + e > q_idx) r2[e] = ninf;
+          if (kv0 + 96 + e > q_idx) r3[e] = ninf;
         }
       }
-      const float m_new = fmaxf(m, mx);
-      const float alpha = ex2(m - m_new);
-      float rs = 0.f;
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        mx0 = fmaxf(mx0, __uint_as_float(r0[e]));
+        mx1 = fmaxf(mx1, __uint_as_float(r1[e]));
+        mx2 = fmaxf(mx2, __uint_as_float(r2[e]));
+        mx3 = fmaxf(mx3, __uint_as_float(r3[e]));
+      }
+      const float m_blk = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sc;
+      bool waited_o = (j == 0);
+      if (j == 0) {
+        m_ref = m_blk;
+      } else {
+        const bool need = m_blk > m_ref + kLazy;
+        if (__any_sync(0xffffffffu, need)) {
+          // the previous P V product must have landed before O is rescaled in place
+          if (!ptx::mbar_wait(o_full, (j - 1) & 1, abort_flag)) { ok = false; break; }
+          ptx::tc_fence_after_sync();
+          waited_o = true;
+          const float alpha = need ? ex2(m_ref - m_blk) : 1.f;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        ptx::tmem_ld32(tS + lane_sel + c * 32, r);
-        ptx::tmem_ld_wait();
+          for (int c = 0; c < HD / 16; ++c) {
+            uint32_t t[16];
+            ptx::tmem_ld16(tO + lane_sel + c * 16, t);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 16; ++e) t[e] = __float_as_uint(__uint_as_float(t[e]) * alpha);
+            ptx::tmem_st16(tO + lane_sel + c * 16, t);
+          }
+          ptx::tmem_st_wait();
+          l *= alpha;
+          if (need) m_ref = m_blk;
+        }
+      }
+      const float neg = -m_ref;
+      float rs0 = 0.f, rs1 = 0.f;
+      auto exp_chunk = [&](uint32_t (&r)[32], int c) {
         uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
-          float x0 = __uint_as_float(r[e]) * sc, x1 = __uint_as_float(r[e + 1]) * sc;
-          if (diag) {
-            if (kv0 + c * 32 + e > q_idx) x0 = -INFINITY;
-            if (kv0 + c * 32 + e + 1 > q_idx) x1 = -INFINITY;
-          }
-          const float p0 = ex2(x0 - m_new), p1 = ex2(x1 - m_new);
-          rs += p0 + p1;
+          const float p0 = ex2(fmaf(__uint_as_float(r[e]), sc, neg));
+          const float p1 = ex2(fmaf(__uint_as_float(r[e + 1]), sc, neg));
+          rs0 += p0;
+          rs1 += p1;
           pk[e >> 1] = pack_bf16x2(p0, p1);
+        }
+        if (c == 0 && !waited_o) {
+          // P(j-1) V(j-1) must have finished reading the P buffer before it is overwritten
+          if (!ptx::mbar_wait(o_full, (j - 1) & 1, abort_flag)) ok = false;
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u)
           *reinterpret_cast<uint4*>(p_smem + swz_off(row, c * 4 + u)) =
               make_uint4(pk[u * 4], pk[u * 4 + 1], pk[u * 4 + 2], pk[u * 4 + 3]);
-      }
-      l = l * alpha + rs;
-      m = m_new;
+      };
+      exp_chunk(r0, 0);
+      if (!ok) break;
+      exp_chunk(r1, 1);
+      exp_chunk(r2, 2);
+      exp_chunk(r3, 3);
+      l += rs0 + rs1;
       ptx::fence_proxy_async_smem();
       ptx::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(p_full);
-      if (!ptx::mbar_wait(o_full, j & 1, abort_flag)) { ok = false; break; }
+    }
+    if (ok) ok = ptx::mbar_wait(o_full, (nblk - 1) & 1, abort_flag);
+    if (ok) {
       ptx::tc_fence_after_sync();
-#pragma unroll
+      const float inv = 1.f / l;
+      bf16* dst = p.o + (static_cast<long long>(b) * p.T + q_idx) * p.o_stride_t + h * HD;
+#pragma unroll 1
       for (int c = 0; c < HD / 32; ++c) {
         uint32_t r[32];
         ptx::tmem_ld32(tO + lane_sel + c * 32, r);
         ptx::tmem_ld_wait();
+        if (q_idx < p.T) {
 #pragma unroll
-        for (int e = 0; e < 32; ++e) o[c * 32 + e] = o[c * 32 + e] * alpha + __uint_as_float(r[e]);
+          for (int d = 0; d < 32; d += 8) {
+            uint4 u;
+            u.x = pack_bf16x2(__uint_as_float(r[d]) * inv, __uint_as_float(r[d + 1]) * inv);
+            u.y = pack_bf16x2(__uint_as_float(r[d + 2]) * inv, __uint_as_float(r[d + 3]) * inv);
+            u.z = pack_bf16x2(__uint_as_float(r[d + 4]) * inv, __uint_as_float(r[d + 5]) * inv);
+            u.w = pack_bf16x2(__uint_as_float(r[d + 6]) * inv, __uint_as_float(r[d + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + d) = u;
+          }
+        }
       }
-    }
-    if (ok && q_idx < p.T) {
-      const float inv = 1.f / l;
-      bf16* dst = p.o + (static_cast<long long>(b) * p.T + q_idx) * p.o_stride_t + h * HD;
-#pragma unroll
-      for (int d = 0; d < HD; d += 8) {
-        uint4 u;
-        u.x = pack_bf16x2(o[d] * inv, o[d + 1] * inv);
-        u.y = pack_bf16x2(o[d + 2] * inv, o[d + 3] * inv);
-        u.z = pack_bf16x2(o[d + 4] * inv, o[d + 5] * inv);
-        u.w = pack_bf16x2(o[d + 6] * inv, o[d + 7] * inv);
-        *reinterpret_cast<uint4*>(dst + d) = u;
-      }
-      p.lse[(static_cast<long long>(b) * p.Hq + h) * p.T + q_idx] = (m + log2f(l)) * 0.6931471805599453f;
+      if (q_idx < p.T)
+        p.lse[(static_cast<long long>(b) * p.Hq + h) * p.T + q_idx] = (m_ref + log2f(l)) * 0.6931471805599453f;
     }
   }
 
@@ -311,16 +363,24 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
-// EW = 1: four element-wise warps, one score row per thread.  EW = 2: eight element-wise warps, a score row is
-// shared by two warps (warps 2..5 take the first half of the key columns and of the head dimension, warps 6..9 the
-// second half; both sets sit on the same TMEM lane quarter `warp & 3`), which halves the thread phase between the
-// two MMA phases; the per-row statistics (lse, delta) are loaded one iteration ahead.
-template <int HD, int EW>
-__global__ void __launch_bounds__(64 + 128 * EW, 1)
+// Backward pipeline.  Warps 2..9 are the element-wise warps: a score row is shared by two warps (warps 2..5 take
+// key columns 0..63 and the first half of the head dimension, warps 6..9 the second halves; both sets sit on the
+// TMEM lane quarter `warp & 3`).  Per (query head, query block) iteration `it`:
+//   MMA warp:  S(it+1), dP(it+1) are issued as soon as the element-wise warps have copied S(it), dP(it) out of
+//              tensor memory (sdp_free), so they run underneath the exponentials of iteration it; dV, dK
+//              accumulate over the whole loop; dQ(it) is issued when the element-wise warps have flushed dQ(it-1).
+//   EW warps:  S and dP of their 64 columns are read from tensor memory once (128 registers), P and dS are
+//              computed from registers, stored to shared memory once MMA group 2 of iteration it-1 has finished
+//              reading the buffers, and only then is dQ(it-1) flushed to HBM -- underneath dV(it), dK(it).
+// With hd = 128 tensor memory is full and dQ shares the S columns, so S(it+1) has to wait for the dQ(it) flush:
+// that instantiation keeps the order S, dP -> P, dS -> dV, dK, dQ -> flush.
+template <int HD>
+__global__ void __launch_bounds__(320, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                 const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo, const AttnArgs p) {
   using Cfg = BwdCfg<HD>;
   constexpr int S = Cfg::kStages;
+  constexpr bool kPipe = !Cfg::kAliasDq;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kBar);
   uint64_t* kv_full = bars;            // 1
@@ -330,7 +390,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   uint64_t* pds_full = bars + 6;
   uint64_t* dq_full = bars + 7;
   uint64_t* dq_free = bars + 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  uint64_t* sdp_free = bars + 9;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -345,9 +406,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     ptx::mbar_init(kv_full, 1);
     for (int s = 0; s < 2; ++s) { ptx::mbar_init(&qdo_full[s], 1); ptx::mbar_init(&qdo_empty[s], 1); }
     ptx::mbar_init(sdp_full, 1);
-    ptx::mbar_init(pds_full, 4 * EW);
+    ptx::mbar_init(pds_full, 8);
     ptx::mbar_init(dq_full, 1);
-    ptx::mbar_init(dq_free, 4 * EW);
+    ptx::mbar_init(dq_free, 8);
+    ptx::mbar_init(sdp_free, 8);
     *abort_flag = (ptx::smem_u32(smem) & 1023u) ? 1u : 0u;
     ptx::mbar_fence_init();
     ptx::tma_prefetch_desc(&tq);
@@ -396,16 +458,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       const uint32_t idesc_q = ptx::make_idesc_bf16(128, HD, 0, 1);    // dQ    : K-major x MN-major
       const uint32_t k_base = ptx::smem_u32(smem + Cfg::kK), v_base = ptx::smem_u32(smem + Cfg::kV);
       const uint32_t p_base = ptx::smem_u32(smem + Cfg::kP), ds_base = ptx::smem_u32(smem + Cfg::kDS);
-      bool ok = ptx::mbar_wait(kv_full, 0, abort_flag);
-      for (int it = 0; it < niter && ok; ++it) {
+      auto issue_sdp = [&](int it) {
         const int st = it % S;
         const uint32_t q_base = ptx::smem_u32(smem + Cfg::kQ + st * Cfg::kTileBytes);
         const uint32_t do_base = ptx::smem_u32(smem + Cfg::kDO + st * Cfg::kTileBytes);
-        if (!ptx::mbar_wait(&qdo_full[st], (it / S) & 1, abort_flag)) break;
-        if (Cfg::kAliasDq && it > 0) {
-          if (!ptx::mbar_wait(dq_free, (it - 1) & 1, abort_flag)) break;
-        }
-        ptx::tc_fence_after_sync();
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
           const uint32_t off = (k >> 2) * kChunkBytes + (k & 3) * 32;
@@ -419,6 +475,26 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
                           ptx::make_smem_desc(v_base + off, 16, 1024), idesc_s, k > 0);
         }
         ptx::tc_commit(sdp_full);
+      };
+      bool ok = ptx::mbar_wait(kv_full, 0, abort_flag);
+      if (ok && niter > 0) {
+        ok = ptx::mbar_wait(&qdo_full[0], 0, abort_flag);
+        if (ok) {
+          ptx::tc_fence_after_sync();
+          issue_sdp(0);
+        }
+      }
+      for (int it = 0; it < niter && ok; ++it) {
+        const int st = it % S;
+        const uint32_t q_base = ptx::smem_u32(smem + Cfg::kQ + st * Cfg::kTileBytes);
+        const uint32_t do_base = ptx::smem_u32(smem + Cfg::kDO + st * Cfg::kTileBytes);
+        if (kPipe && it + 1 < niter) {
+          // next S / dP: operands loaded, and the score columns copied out by the element-wise warps
+          if (!ptx::mbar_wait(&qdo_full[(it + 1) % S], ((it + 1) / S) & 1, abort_flag)) break;
+          if (!ptx::mbar_wait(sdp_free, it & 1, abort_flag)) break;
+          ptx::tc_fence_after_sync();
+          issue_sdp(it + 1);
+        }
         if (!ptx::mbar_wait(pds_full, it & 1, abort_flag)) break;
         ptx::tc_fence_after_sync();
 #pragma unroll
@@ -431,6 +507,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
           ptx::mma_f16_ss(tmem_base + Cfg::kColDK, ptx::make_smem_desc(ds_base + k * 2048, kChunkBytes, 1024),
                           ptx::make_smem_desc(q_base + k * 2048, kChunkBytes, 1024), idesc_t, (it > 0 || k > 0));
         }
+        if (kPipe && it > 0) {
+          // dQ(it-1) has left tensor memory
+          if (!ptx::mbar_wait(dq_free, (it - 1) & 1, abort_flag)) break;
+          ptx::tc_fence_after_sync();
+        }
 #pragma unroll
         for (int k = 0; k < kBlk / 16; ++k) {  // reduction over the 128 keys
           const uint32_t a_off = (k >> 2) * kChunkBytes + (k & 3) * 32;
@@ -439,97 +520,126 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         }
         ptx::tc_commit(dq_full);
         ptx::tc_commit(&qdo_empty[st]);
+        if (!kPipe && it + 1 < niter) {
+          // dQ shares the S columns: the next S / dP wait for the flush of dQ(it)
+          if (!ptx::mbar_wait(&qdo_full[(it + 1) % S], ((it + 1) / S) & 1, abort_flag)) break;
+          if (!ptx::mbar_wait(dq_free, it & 1, abort_flag)) break;
+          ptx::tc_fence_after_sync();
+          issue_sdp(it + 1);
+        }
       }
     }
   } else {
     const int quad = warp & 3;
-    const int half = (EW == 1) ? 0 : ((warp - 2) >> 2);
+    const int half = (warp - 2) >> 2;
     const int row = quad * 32 + lane;
     const uint32_t lane_sel = static_cast<uint32_t>(quad * 32) << 16;
     const float sc = p.scale * kLog2e;
     uint8_t* p_smem = smem + Cfg::kP;
     uint8_t* ds_smem = smem + Cfg::kDS;
     bool ok = true;
-    // (lse, delta) of this thread's query row in iteration `it2`; zeros past the end of the sequence
+    // (lse, delta) of this thread's query row in iteration `it2`; rows past the end of the sequence get lse = +inf,
+    // which turns their probabilities into exact zeros
     auto load_stats = [&](int it2, float& l, float& d) {
       const int g2 = it2 / nq, i2 = jb + (it2 - g2 * nq);
       const int q2 = i2 * kBlk + row;
       const long long stat2 = (static_cast<long long>(b) * p.Hq + (hk * G + g2)) * p.T + q2;
-      l = q2 < p.T ? p.lse[stat2] : 0.f;
+      l = q2 < p.T ? p.lse[stat2] * kLog2e : INFINITY;
       d = q2 < p.T ? p.delta[stat2] : 0.f;
     };
-    float pre_lse = 0.f, pre_dlt = 0.f;
-    if (EW == 2 && niter > 0) load_stats(0, pre_lse, pre_dlt);
-    for (int it = 0; it < niter; ++it) {
-      const int g = it / nq, i = jb + (it - g * nq);
-      const int h = hk * G + g;
-      const int q_idx = i * kBlk + row;
-      const bool q_valid = q_idx < p.T;
-      float lse2, dlt;
-      if constexpr (EW == 2) {
-        // statistics were requested one iteration ahead; ask for the next iteration's now
-        lse2 = pre_lse * kLog2e;
-        dlt = pre_dlt;
-        if (it + 1 < niter) load_stats(it + 1, pre_lse, pre_dlt);
-      } else {
-        const long long stat = (static_cast<long long>(b) * p.Hq + h) * p.T + q_idx;
-        lse2 = q_valid ? p.lse[stat] * kLog2e : 0.f;
-        dlt = q_valid ? p.delta[stat] : 0.f;
-      }
-      if (!ptx::mbar_wait(sdp_full, it & 1, abort_flag)) { ok = false; break; }
-      ptx::tc_fence_after_sync();
-      const bool diag = (i == jb);
-      const int kv0 = jb * kBlk;
+    // dQ of iteration `it2`, this warp's half of the head dimension: tensor memory -> fp32 reductions in HBM
+    auto flush_dq = [&](int it2) {
+      const int g2 = it2 / nq, i2 = jb + (it2 - g2 * nq);
+      const int q2 = i2 * kBlk + row;
+      float* dq_row = p.dq_accum + ((static_cast<long long>(b) * p.T + q2) * p.Hq + (hk * G + g2)) * HD;
 #pragma unroll 1
-      for (int c = half * (4 / EW); c < (half + 1) * (4 / EW); ++c) {
-        uint32_t rs[32], rd[32];
-        ptx::tmem_ld32(tmem_base + Cfg::kColS + lane_sel + c * 32, rs);
-        ptx::tmem_ld32(tmem_base + Cfg::kColDP + lane_sel + c * 32, rd);
-        ptx::tmem_ld_wait();
-        uint32_t pk[16], dk_[16];
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float pv[2], dv_[2];
-#pragma unroll
-          for (int t = 0; t < 2; ++t) {
-            const bool keep = q_valid && !(diag && (kv0 + c * 32 + e + t > q_idx));
-            const float pr = keep ? ex2(__uint_as_float(rs[e + t]) * sc - lse2) : 0.f;
-            pv[t] = pr;
-            dv_[t] = pr * (__uint_as_float(rd[e + t]) - dlt) * p.scale;
-          }
-          pk[e >> 1] = pack_bf16x2(pv[0], pv[1]);
-          dk_[e >> 1] = pack_bf16x2(dv_[0], dv_[1]);
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const uint32_t off = swz_off(row, c * 4 + u);
-          *reinterpret_cast<uint4*>(p_smem + off) = make_uint4(pk[u * 4], pk[u * 4 + 1], pk[u * 4 + 2], pk[u * 4 + 3]);
-          *reinterpret_cast<uint4*>(ds_smem + off) = make_uint4(dk_[u * 4], dk_[u * 4 + 1], dk_[u * 4 + 2], dk_[u * 4 + 3]);
-        }
-      }
-      ptx::fence_proxy_async_smem();
-      ptx::tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(pds_full);
-      if (!ptx::mbar_wait(dq_full, it & 1, abort_flag)) { ok = false; break; }
-      ptx::tc_fence_after_sync();
-      float* dq_row = p.dq_accum + ((static_cast<long long>(b) * p.T + q_idx) * p.Hq + h) * HD;
-#pragma unroll 1
-      for (int c = half * (HD / 32 / EW); c < (half + 1) * (HD / 32 / EW); ++c) {
+      for (int c = half * (HD / 64); c < (half + 1) * (HD / 64); ++c) {
         uint32_t r[32];
         ptx::tmem_ld32(tmem_base + Cfg::kColDQ + lane_sel + c * 32, r);
         ptx::tmem_ld_wait();
-        if (q_valid) {
+        if (q2 < p.T) {
 #pragma unroll
           for (int e = 0; e < 32; e += 4)
             red_add_v4(dq_row + c * 32 + e, __uint_as_float(r[e]), __uint_as_float(r[e + 1]), __uint_as_float(r[e + 2]),
                        __uint_as_float(r[e + 3]));
         }
       }
-      if (Cfg::kAliasDq) {
-        ptx::tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(dq_free);
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(dq_free);
+    };
+    float pre_lse = 0.f, pre_dlt = 0.f;
+    if (niter > 0) load_stats(0, pre_lse, pre_dlt);
+    for (int it = 0; it < niter; ++it) {
+      const int i = jb + (it % nq);
+      const int q_idx = i * kBlk + row;
+      const float lse2 = pre_lse, dlt = pre_dlt;       // requested one iteration ahead
+      if (it + 1 < niter) load_stats(it + 1, pre_lse, pre_dlt);
+      if (!ptx::mbar_wait(sdp_full, it & 1, abort_flag)) { ok = false; break; }
+      ptx::tc_fence_after_sync();
+      uint32_t s0[32], s1[32], d0[32], d1[32];
+      ptx::tmem_ld32(tmem_base + Cfg::kColS + lane_sel + half * 64, s0);
+      ptx::tmem_ld32(tmem_base + Cfg::kColS + lane_sel + half * 64 + 32, s1);
+      ptx::tmem_ld32(tmem_base + Cfg::kColDP + lane_sel + half * 64, d0);
+      ptx::tmem_ld32(tmem_base + Cfg::kColDP + lane_sel + half * 64 + 32, d1);
+      ptx::tmem_ld_wait();
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(sdp_free);       // S / dP columns may be overwritten
+      if (i == jb) {  // diagonal block: keys after the query get probability zero
+        const uint32_t ninf = __float_as_uint(-INFINITY);
+        const int kv0 = jb * kBlk + half * 64;
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          if (kv0 + e > q_idx) s0[e] = ninf;
+          if (kv0 + 32 + e > q_idx) s1[e] = ninf;
+        }
+      }
+      const float neg = -lse2;
+      auto ew_chunk = [&](uint32_t (&rs)[32], uint32_t (&rd)[32], int c) {
+        uint32_t pk[16], dk_[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          const float p0 = ex2(fmaf(__uint_as_float(rs[e]), sc, neg));
+          const float p1 = ex2(fmaf(__uint_as_float(rs[e + 1]), sc, neg));
+          const float g0 = p0 * (__uint_as_float(rd[e]) - dlt) * p.scale;
+          const float g1 = p1 * (__uint_as_float(rd[e + 1]) - dlt) * p.scale;
+          pk[e >> 1] = pack_bf16x2(p0, p1);
+          dk_[e >> 1] = pack_bf16x2(g0, g1);
+        }
+        if (kPipe && c == 0 && it > 0) {
+          // MMA group 2 of the previous iteration must have finished reading P / dS (and produced dQ(it-1))
+          if (!ptx::mbar_wait(dq_full, (it - 1) & 1, abort_flag)) ok = false;
+          ptx::tc_fence_after_sync();
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const uint32_t off = swz_off(row, half * 8 + c * 4 + u);
+          *reinterpret_cast<uint4*>(p_smem + off) = make_uint4(pk[u * 4], pk[u * 4 + 1], pk[u * 4 + 2], pk[u * 4 + 3]);
+          *reinterpret_cast<uint4*>(ds_smem + off) = make_uint4(dk_[u * 4], dk_[u * 4 + 1], dk_[u * 4 + 2], dk_[u * 4 + 3]);
+        }
+      };
+      ew_chunk(s0, d0, 0);
+      if (!ok) break;
+      ew_chunk(s1, d1, 1);
+      ptx::fence_proxy_async_smem();
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(pds_full);
+      if (kPipe) {
+        if (it > 0) flush_dq(it - 1);                   // underneath dV(it), dK(it)
+      } else {
+        // dQ shares the S columns: flush dQ(it) before the next S / dP may be issued
+        if (!ptx::mbar_wait(dq_full, it & 1, abort_flag)) { ok = false; break; }
+        ptx::tc_fence_after_sync();
+        flush_dq(it);
+      }
+    }
+    if (kPipe && ok && niter > 0) {
+      ok = ptx::mbar_wait(dq_full, (niter - 1) & 1, abort_flag);
+      if (ok) {
+        ptx::tc_fence_after_sync();
+        flush_dq(niter - 1);
       }
     }
     // The last dq_full arrival also covers every dV/dK accumulation issued before it.
@@ -542,7 +652,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         const uint32_t col = which == 0 ? Cfg::kColDV : Cfg::kColDK;
         bf16* dst = base + (static_cast<long long>(b) * p.T + kv_idx) * stride + hk * HD;
 #pragma unroll 1
-        for (int c = half * (HD / 32 / EW); c < (half + 1) * (HD / 32 / EW); ++c) {
+        for (int c = half * (HD / 64); c < (half + 1) * (HD / 64); ++c) {
           uint32_t r[32];
           ptx::tmem_ld32(tmem_base + col + lane_sel + c * 32, r);
           ptx::tmem_ld_wait();
@@ -646,11 +756,7 @@ static int attn_fwd_launch(const TitbAttnDesc* d, cudaStream_t st) {
   return static_cast<int>(cudaGetLastError());
 }
 
-// 1 or 2 sets of element-wise warps in the backward kernel; process-wide, read at launch.  Two sets (a score row
-// shared by two warps) measured 1.28x faster at B8 T1024 H12 hd64 and are the default.
-static int g_attn_bwd_ew = 2;
-
-template <int HD, int EW>
+template <int HD>
 static int attn_bwd_launch(const TitbAttnDesc* d, cudaStream_t st) {
   using Cfg = BwdCfg<HD>;
   static bool attr_set[64] = {false};
@@ -658,7 +764,7 @@ static int attn_bwd_launch(const TitbAttnDesc* d, cudaStream_t st) {
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) dev = 0;
   if (!attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel<HD, EW>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem);
+    cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem);
     if (e != cudaSuccess) return static_cast<int>(e);
     attr_set[dev] = true;
   }
@@ -684,7 +790,7 @@ static int attn_bwd_launch(const TitbAttnDesc* d, cudaStream_t st) {
   a.dk_stride_t = d->dk_stride_t; a.dv_stride_t = d->dv_stride_t;
   a.status = titb_status_ptr();
   dim3 grid((d->T + kBlk - 1) / kBlk, d->Hkv, d->B);
-  attn_bwd_kernel<HD, EW><<<grid, 64 + 128 * EW, Cfg::kSmem, st>>>(tq, tk, tv, tdo, a);
+  attn_bwd_kernel<HD><<<grid, 320, Cfg::kSmem, st>>>(tq, tk, tv, tdo, a);
   const long long bt = static_cast<long long>(d->B) * d->T;
   const int width = d->Hq * HD;
   int cb = static_cast<int>((bt * (width / 8) + 255) / 256);
@@ -704,9 +810,6 @@ TITB_API int titb_attn_fwd(const TitbAttnDesc* d, cudaStream_t stream) {
   return d->hd == 64 ? attn_fwd_launch<64>(d, stream) : attn_fwd_launch<128>(d, stream);
 }
 
-// warps = 8: a score row is shared by two warps in the backward kernel; anything else: the four-warp version.
-TITB_API void titb_attn_bwd_set_warps(int warps) { g_attn_bwd_ew = warps == 8 ? 2 : 1; }
-
 TITB_API int titb_attn_bwd(const TitbAttnDesc* d, cudaStream_t stream) {
   (void)cudaGetLastError();
   if (d->B <= 0 || d->T <= 0) return 0;
@@ -715,6 +818,5 @@ TITB_API int titb_attn_bwd(const TitbAttnDesc* d, cudaStream_t stream) {
   if (!al(d->d_o) || !al(d->dq) || !al(d->dk) || !al(d->dv) || (d->do_stride_t & 7) || (d->dq_stride_t & 7) ||
       (d->dk_stride_t & 7) || (d->dv_stride_t & 7))
     return TITB_ERR_ALIGNMENT;
-  if (g_attn_bwd_ew == 2) return d->hd == 64 ? attn_bwd_launch<64, 2>(d, stream) : attn_bwd_launch<128, 2>(d, stream);
-  return d->hd == 64 ? attn_bwd_launch<64, 1>(d, stream) : attn_bwd_launch<128, 1>(d, stream);
+  return d->hd == 64 ? attn_bwd_launch<64>(d, stream) : attn_bwd_launch<128>(d, stream);
 }

@@ -882,22 +882,36 @@ int device_sm_count() {
 
 static int g_no_tma_store = 0;  // set by titb_gemm_set_tma_store(0): A/B switch for the epilogue store path
 
-static int pick_tile_n(int M, int N, int splits) {
-  // 128 x 256 tiles move fewer operand bytes per FLOP; 128 x 128 only wins when it removes
-  // a clearly larger share of the last, partially filled wave.
-  const int sms = device_sm_count();
-  const long long tm = (M + kBM - 1) / kBM;
-  auto cost = [&](int bn) {
-    const long long tiles = tm * ((N + bn - 1) / bn) * splits;
-    const long long waves = (tiles + sms - 1) / sms;
-    return waves * bn;
-  };
+// Estimated duration of a GEMM for a tile width and a split-K factor, in units of one 128 x 256 x 64 k-block
+// (about 0.37 us of tensor-core time on one SM).  Main loop: the last CTA runs `waves` tiles of kb_per k-blocks,
+// a k-block of a narrower tile is proportionally cheaper; the epilogue of the last tile is exposed (those of the
+// earlier tiles overlap the next main loop through the second TMEM accumulator); split-K adds the fp32 partial
+// tiles' trip through memory and a second launch.
+static double plan_cost(int M, int N, int K, int bn, int splits, int sms) {
+  const long long tm = (M + kBM - 1) / kBM, tn = (N + bn - 1) / bn;
+  const int kb = (K + kBK - 1) / kBK;
+  const int kb_per = (kb + splits - 1) / splits;
+  const int s = (kb + kb_per - 1) / kb_per;
+  const long long tiles = tm * tn * s;
+  const long long waves = (tiles + sms - 1) / sms;
+  const double w = bn / 256.0;
+  double cost = waves * (double)(kb_per > 3 ? kb_per : 3) * w + 3.0 * w;
+  if (s > 1) cost += 5.0 + ((double)M * N * 4.0 * (s + 1)) / 6.5e6 / 0.37;   // us -> units
+  return cost;
+}
+
+static int pick_tile_n(int M, int N, int K, int splits) {
+  // 128 x 256 tiles move the fewest operand bytes per FLOP; 192 and 128 win when they fill the last wave better
+  // (widths such as 768 and 3072 = 6 x 128).  A narrower tile must save more than 5% to be taken.
   if (N <= 128) return 128;
-  // 128 x 192 tiles cut the tail of the last wave for widths such as 768 and 3072 (6 x 128); they are taken when
-  // they save more than 5% of the wave-quantised cost of 128 x 256.
-  const long long c256 = cost(256), c128 = cost(128), c192 = cost(192);
-  if (c128 * 2 < c256 && c128 * 2 < c192) return 128;
-  return (c192 * 100 < c256 * 95) ? 192 : 256;
+  const int sms = device_sm_count();
+  const double c256 = plan_cost(M, N, K, 256, splits, sms), c192 = plan_cost(M, N, K, 192, splits, sms),
+               c128 = plan_cost(M, N, K, 128, splits, sms);
+  int bn = 256;
+  double best = c256;
+  if (c192 < best * 0.95) { bn = 192; best = c192; }
+  if (c128 < best * 0.95 && c128 < c256 * 0.95) { bn = 128; best = c128; }
+  return bn;
 }
 
 }  // namespace titb
@@ -930,17 +944,25 @@ TITB_API int titb_status_read(int clear, cudaStream_t stream) {
 
 TITB_API void titb_gemm_set_tma_store(int enabled) { g_no_tma_store = enabled ? 0 : 1; }
 
+TITB_API int titb_gemm_pick_tile(int M, int N, int K, int splits) { return pick_tile_n(M, N, K, splits < 1 ? 1 : splits); }
+
 TITB_API int titb_gemm_pick_splits(int M, int N, int K) {
-  // Split the reduction only when the output has too few tiles to fill the GPU and the
-  // reduction is long enough that each split still runs a deep pipeline.
+  // Joint choice of split-K factor and tile width by estimated duration (plan_cost): the reduction is split when the
+  // output has too few tiles to fill the GPU -- weight gradients: small outputs, K = the token count -- and each
+  // split still runs a pipeline of at least 8 k-blocks.
   const int sms = device_sm_count();
-  const long long tm = (M + kBM - 1) / kBM;
-  const long long tiles = tm * ((N + 127) / 128);
   const int kb = (K + kBK - 1) / kBK;
-  if (tiles * 2 > sms || kb < 32) return 1;
-  int s = static_cast<int>(sms / tiles);
-  while (s > 1 && kb / s < 8) --s;
-  return s < 1 ? 1 : (s > 16 ? 16 : s);
+  int best_s = 1;
+  double best = 1e30;
+  for (int s = 1; s <= 16; ++s) {
+    if (s > 1 && kb / s < 8) break;
+    for (int bn : {256, 192, 128}) {
+      if (bn > 128 && N <= 128) continue;
+      const double c = plan_cost(M, N, K, bn, s, sms);
+      if (c < best * (s > best_s ? 0.97 : 1.0)) { best = c; best_s = s; }   // a deeper split must pay for itself
+    }
+  }
+  return best_s;
 }
 #endif  // !TITB_GEMM_PARAM_GATHER
 
@@ -977,7 +999,7 @@ TITB_API int TITB_GEMM_ENTRY(const TitbGemmDesc* d, cudaStream_t stream) {
   const int num_kb = (d->K + kBK - 1) / kBK;
   if (splits > num_kb) splits = num_kb;
   if (splits > 1 && (d->workspace == nullptr || (d->N & 3))) splits = 1;
-  const int bn = d->tile_n ? d->tile_n : pick_tile_n(d->M, d->N, splits);
+  const int bn = d->tile_n ? d->tile_n : pick_tile_n(d->M, d->N, d->K, splits);
 
   CUtensorMap ta, tb;
   bool ok;

@@ -20,7 +20,6 @@ infini_train/include/nn/modules/linear.h:11-24).
 from __future__ import annotations
 
 import math
-import os
 from typing import Optional
 
 import torch
@@ -32,9 +31,6 @@ from ..ops import functional as F_
 from .._lib import C
 
 _bf16 = torch.bfloat16
-# The two-pass vocabulary-parallel cross-entropy kernels replace the torch-op formulation of the loss when set
-# (TITB200_VP_XENT=1); the torch-op path is the default.
-USE_VP_XENT_KERNELS = os.environ.get("TITB200_VP_XENT", "0") == "1"
 
 
 class TPComm:
@@ -380,7 +376,7 @@ class _VocabParallelLossFn(torch.autograd.Function):
         logits, X = comm.ag_gemm(x_s, w)
         M, Vl = logits.shape
         lo = comm.rank * Vl
-        if USE_VP_XENT_KERNELS and logits.is_cuda and logits.dtype in (torch.float32, _bf16) and comm.world <= 16:
+        if logits.is_cuda and logits.dtype in (torch.float32, _bf16) and comm.world <= 16:
             # own kernels: one pass for the slice statistics, exchange of [M, 3] triples, one in-place gradient pass
             tgt = targets.reshape(-1).contiguous()
             table, dst, slot = comm.vp_stats_table(M, logits.device)
@@ -390,6 +386,7 @@ class _VocabParallelLossFn(torch.autograd.Function):
             ctx.save_for_backward(X, w, logits)
             ctx.comm = comm
             return losses.mean()
+        # CPU ranks (and groups beyond 16 ranks): the same exchange written with torch ops and three all-reduces
         lf = logits.float()
         col = torch.arange(Vl, device=logits.device) + lo
         lf = lf.masked_fill((col >= vocab_size).unsqueeze(0), float("-inf"))

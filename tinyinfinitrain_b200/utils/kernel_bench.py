@@ -123,7 +123,6 @@ def main():
     ap.add_argument("--tile_n", type=int, default=0)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no_flush", action="store_true")
-    ap.add_argument("--warps", type=int, default=4, help="attn_bwd: 8 = two warps per score row")
     ap.add_argument("--residual", action="store_true", help="layernorm_bwd: add a residual gradient to dx")
     a = ap.parse_args()
     if a.kernel == "gemm_sweep":
@@ -166,7 +165,6 @@ def main():
         else:
             o, lse = C.attn_fwd(q, k, v, scale)
             do = torch.randn_like(o)
-            C.attn_bwd_set_warps(a.warps)
             flops = 2.5 * fwd_flops
             fn = lambda: C.attn_bwd(do, q, k, v, o, lse, scale)
         bytes_ = 2.0 * qkv.numel() * 2
