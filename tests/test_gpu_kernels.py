@@ -50,6 +50,29 @@ def test_gemm_tiles_and_splitk(tile_n, splits):
     assert torch.allclose(acc, ref + 2.0, rtol=1e-4, atol=5e-2)
 
 
+@pytest.mark.parametrize("tile_n", [128, 192, 256])
+@pytest.mark.parametrize("splits,accumulate", [(1, False), (1, True), (4, False), (4, True), (0, False)])
+def test_gemm_weight_gradient_form_fp32_out(tile_n, splits, accumulate):
+    """dW = dY^T X (both operands MN-major, long reduction, fp32 result): stored, accumulated, and split over K with the
+    partial tiles added in the output (zero-filled first when it does not accumulate); splits = 0 lets the planner
+    choose.  Ragged in both output dimensions."""
+    torch.manual_seed(6)
+    tokens, n_out, k_in = 4096, 328, 776
+    dY = (torch.randn(tokens, n_out, device=DEV) * 0.5).to(BF)
+    X = (torch.randn(tokens, k_in, device=DEV) * 0.5).to(BF)
+    ref = dY.float().t() @ X.float()
+    out = torch.full((n_out, k_in), 3.0, device=DEV)
+    C.gemm(dY, X, True, True, out=out, accumulate=accumulate, tile_n=tile_n, splits=splits)
+    _status_ok()
+    want = ref + 3.0 if accumulate else ref
+    assert torch.allclose(out, want, rtol=1e-4, atol=5e-2)
+    al = torch.tensor([0.5], device=DEV)
+    out.fill_(1.0)
+    C.gemm(dY, X, True, True, out=out, accumulate=True, tile_n=tile_n, splits=splits, alpha=al)
+    assert torch.allclose(out, 0.5 * ref + 1.0, rtol=1e-4, atol=5e-2)
+    _status_ok()
+
+
 def test_gemm_epilogues():
     torch.manual_seed(2)
     M, N, K = 520, 776, 264

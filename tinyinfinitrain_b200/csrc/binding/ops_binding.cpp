@@ -97,13 +97,16 @@ std::vector<Tensor> gemm(const Tensor& a, const Tensor& b, bool a_mn, bool b_mn,
   }
   int s = splits > 0 ? (int)splits : titb_gemm_pick_splits((int)M, (int)N, (int)K);
   if (epilogue != TITB_EPI_NONE || (N & 3)) s = 1;
+  // bf16 outputs go through an fp32 workspace and a reduction kernel: worth it only for very long reductions
+  // (the vocabulary projection's input gradient, K = 50304)
+  if (s > 1 && splits <= 0 && !out_fp32 && K < 16384) s = 1;
   Tensor ws;
-  if (s > 1) {
+  if (s > 1 && !titb_gemm_split_in_place(&d)) {
     ws = at::empty({s, M, N}, a.options().dtype(at::kFloat));
     d.workspace = ws.data_ptr();
   }
   d.splits = s;
-  CHECK_RC(titb_gemm_bf16(&d, cur_stream()), "gemm_bf16", s > 1 ? 2 : 1);
+  CHECK_RC(titb_gemm_bf16(&d, cur_stream()), "gemm_bf16", (s > 1 && ws.defined()) ? 2 : 1);
   if (want_aux_out) return {out, aux_out};
   return {out};
 }

@@ -96,6 +96,9 @@ TITB_API int titb_gemm_param_gather_bf16(const TitbGemmDesc* d, cudaStream_t str
 TITB_API int titb_gemm_pick_splits(int M, int N, int K);
 // Tile width (128, 192 or 256) the GEMM takes for this shape and split-K factor when the descriptor leaves tile_n 0.
 TITB_API int titb_gemm_pick_tile(int M, int N, int K, int splits);
+// 1 when a split-K call with this descriptor sums its partial tiles in the output itself (fp32 output, no fused
+// epilogue, TMA reduce-add) and needs no workspace; 0 when it needs workspace [splits, M, N] fp32.
+TITB_API int titb_gemm_split_in_place(const TitbGemmDesc* d);
 // Switches the shared-memory-staged TMA store epilogue of bf16 outputs on (default) or off (A/B timing).
 TITB_API void titb_gemm_set_tma_store(int enabled);
 // fp32 SIMT GEMM for API parity with fp32 tensors: C[M,N] (+)= op(A) op(B), row-major.

@@ -79,17 +79,23 @@ struct GemmArgs {
   int splits;       // split-K factor; partial tiles go to `out` = workspace [splits, M, N] fp32
   int kb_per_split;
   int vec_ok;       // all row strides / base pointers allow 16-byte accesses
-  int tma_store;    // bf16 outputs leave through shared-memory staging + TMA stores
+  int tma_store;    // 1: bf16 outputs leave through shared-memory staging + TMA stores; 2: fp32 outputs do
+  int f32_red;      // tma_store == 2: tiles are added to the output (TMA reduce-add) instead of stored
   int aux_tma_load; // residual / pre-activation tiles arrive through TMA loads into the aux staging tile
   const float* alpha;  // optional device scalar multiplied into the accumulator
   uint32_t a_lbo, a_sbo, a_kstep, b_lbo, b_sbo, b_kstep;
   int* status;
 };
 
-template <int BN>
+// PAIR: two CTAs of a cluster share one 256 x BN tile (tcgen05 cta_group::2).  Each stages its own 128 rows of A and
+// its own half of the B tile, so a k-block costs every SM (128 + BN / 2) x 64 x 2 bytes of operand traffic instead
+// of (128 + BN) x 64 x 2: two thirds at BN = 256.  No multicast: every CTA fetches its own tiles.
+template <int BN, bool PAIR = false>
 struct GemmCfg {
-  static constexpr int kBBytes = BN * kBK * 2;
-  static constexpr int kStages = (BN == 128) ? 6 : 4;
+  static constexpr int kBRows = PAIR ? BN / 2 : BN;   // rows of B (output columns) this CTA stages per k-block
+  static constexpr int kBBytes = kBRows * kBK * 2;
+  static constexpr int kStages = PAIR ? 6 : ((BN == 128) ? 6 : 4);
+  static constexpr int kTileM = PAIR ? 2 * kBM : kBM;
   static constexpr int kAccStride = (BN == 128) ? 128 : 256;  // TMEM columns between the two accumulators
   static constexpr int kTmemCols = 2 * kAccStride;            // allocation size must be a power of two
   static constexpr int kRing = kStages * (kABytes + kBBytes);
@@ -239,7 +245,8 @@ __device__ __forceinline__ void epilogue_row32(const GemmArgs& p, float (&v)[32]
 
 struct TileCoord { int m0, n0, split, mblk; };
 
-__device__ __forceinline__ TileCoord tile_coord(const GemmArgs& p, int tile, int tiles_m, int tiles_n, int bn) {
+__device__ __forceinline__ TileCoord tile_coord(const GemmArgs& p, int tile, int tiles_m, int tiles_n, int bn,
+                                                int tile_m = kBM, int row_off = 0) {
   const int tiles_mn = tiles_m * tiles_n;
   TileCoord t;
   t.split = tile / tiles_mn;
@@ -262,7 +269,7 @@ __device__ __forceinline__ TileCoord tile_coord(const GemmArgs& p, int tile, int
     t.mblk = (mn / tiles_n + start) % tiles_m;
     nblk = mn % tiles_n;
   }
-  t.m0 = t.mblk * kBM;
+  t.m0 = t.mblk * tile_m + row_off;   // row_off: second CTA of a pair owns the lower 128 rows of the tile
   t.n0 = nblk * bn;
   return t;
 }
@@ -399,18 +406,21 @@ __device__ void rs_reduce_role(const GemmArgs& p, int tiles_n) {
   }
 }
 
-template <int BN>
+template <int BN, bool PAIR>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                          const __grid_constant__ CUtensorMap tma_out, const __grid_constant__ CUtensorMap tma_aux,
                          const GemmArgs p) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, PAIR>;
   constexpr int kStages = Cfg::kStages;
   constexpr int kBBytes = Cfg::kBBytes;
+  constexpr int kTileM = Cfg::kTileM;
+  const uint32_t pair_rank = PAIR ? ptx::cluster_ctarank() : 0u;   // 0 issues the MMAs of the pair
+  const int row_off = static_cast<int>(pair_rank) * kBM;
 
   // Leading CTAs of a fused-collective launch do the copy / reduction instead of GEMM tiles.
-  const int helpers = p.coll.mode ? p.coll.helper_ctas : 0;
-  if (static_cast<int>(blockIdx.x) < helpers) {
+  const int helpers = (!PAIR && p.coll.mode) ? p.coll.helper_ctas : 0;
+  if (!PAIR && static_cast<int>(blockIdx.x) < helpers) {
     if (p.coll.mode == 1) ag_copy_role(p);
 #ifdef TITB_GEMM_PARAM_GATHER
     else if (p.coll.mode == 3) param_gather_role(p);
@@ -418,8 +428,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     else rs_reduce_role(p, (p.N + BN - 1) / BN);
     return;
   }
-  const int cta = static_cast<int>(blockIdx.x) - helpers;
-  const int ncta = static_cast<int>(gridDim.x) - helpers;
+  // a pair walks the tile list as one unit
+  const int cta = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x) - helpers;
+  const int ncta = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x) - helpers;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -446,7 +457,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(&acc_full[b], 1);
-      ptx::mbar_init(&acc_empty[b], 4);
+      ptx::mbar_init(&acc_empty[b], PAIR ? 8 : 4);   // pair: the epilogue warps of both CTAs arrive on rank 0's copy
     }
     *abort_flag = 0;
     ptx::mbar_fence_init();
@@ -454,15 +465,21 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     ptx::tma_prefetch_desc(&tma_b);
   }
   if (warp == 1) {
-    ptx::tmem_alloc(tmem_slot, Cfg::kTmemCols);
-    ptx::tmem_relinquish();
+    if (PAIR) {
+      ptx::tmem_alloc_pair(tmem_slot, Cfg::kTmemCols);
+      ptx::tmem_relinquish_pair();
+    } else {
+      ptx::tmem_alloc(tmem_slot, Cfg::kTmemCols);
+      ptx::tmem_relinquish();
+    }
   }
   ptx::tc_fence_before_sync();
   __syncthreads();
+  if (PAIR) ptx::cluster_sync_all();   // the peer's barriers are initialised before anything signals them
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int tiles_m = (p.M + kBM - 1) / kBM;
+  const int tiles_m = (p.M + kTileM - 1) / kTileM;
   const int tiles_n = (p.N + BN - 1) / BN;
   const int tiles_mn = tiles_m * tiles_n;
   const int num_tiles = tiles_mn * p.splits;
@@ -479,8 +496,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       int ready_n0 = -1;
 #endif
       for (int tile = cta; tile < num_tiles && ok; tile += ncta) {
-        const TileCoord tc = tile_coord(p, tile, tiles_m, tiles_n, BN);
+        const TileCoord tc = tile_coord(p, tile, tiles_m, tiles_n, BN, kTileM, row_off);
         const int split = tc.split, m0 = tc.m0, n0 = tc.n0;
+        const int nb0 = n0 + static_cast<int>(pair_rank) * Cfg::kBRows;   // first B row (output column) this CTA stages
         const int kb0 = split * p.kb_per_split;
         const int kb1 = min(num_kb_total, kb0 + p.kb_per_split);
         if (p.coll.mode == 1 && tc.mblk != ready_mblk) {
@@ -512,22 +530,26 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
 #endif
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!ptx::mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
-          ptx::mbar_expect_tx(&full[stage], kABytes + kBBytes);
           uint8_t* a_dst = sa + stage * kABytes;
           uint8_t* b_dst = sb + stage * kBBytes;
+          // pair: both CTAs' bytes are counted on rank 0's barrier, which rank 0 arms for the sum
+          auto load = [&](void* dst, const CUtensorMap* m, int x, int y) {
+            if (PAIR) ptx::tma_load_2d_pair(dst, m, &full[stage], x, y);
+            else ptx::tma_load_2d(dst, m, &full[stage], x, y);
+          };
+          if (!PAIR) ptx::mbar_expect_tx(&full[stage], kABytes + kBBytes);
+          else if (pair_rank == 0) ptx::mbar_expect_tx(&full[stage], 2 * (kABytes + kBBytes));
           if (!p.a_mn) {
-            ptx::tma_load_2d(a_dst, &tma_a, &full[stage], kb * kBK, m0);
+            load(a_dst, &tma_a, kb * kBK, m0);
           } else {
 #pragma unroll
-            for (int j = 0; j < kBM / 64; ++j)
-              ptx::tma_load_2d(a_dst + j * (64 * kBK * 2), &tma_a, &full[stage], m0 + j * 64, kb * kBK);
+            for (int j = 0; j < kBM / 64; ++j) load(a_dst + j * (64 * kBK * 2), &tma_a, m0 + j * 64, kb * kBK);
           }
           if (!p.b_mn) {
-            ptx::tma_load_2d(b_dst, &tma_b, &full[stage], kb * kBK, n0);
+            load(b_dst, &tma_b, kb * kBK, nb0);
           } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
-              ptx::tma_load_2d(b_dst + j * (64 * kBK * 2), &tma_b, &full[stage], n0 + j * 64, kb * kBK);
+            for (int j = 0; j < Cfg::kBRows / 64; ++j) load(b_dst + j * (64 * kBK * 2), &tma_b, nb0 + j * 64, kb * kBK);
           }
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
@@ -544,8 +566,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
-      const uint32_t idesc = ptx::make_idesc_bf16(kBM, BN, p.a_mn, p.b_mn);
+    if (lane == 0 && pair_rank == 0) {
+      const uint32_t idesc = ptx::make_idesc_bf16(kTileM, BN, p.a_mn, p.b_mn);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
@@ -568,19 +590,97 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
           for (int k = 0; k < kBK / 16; ++k) {
             const uint64_t adesc = ptx::make_smem_desc(a_base + k * p.a_kstep, p.a_lbo, p.a_sbo);
             const uint64_t bdesc = ptx::make_smem_desc(b_base + k * p.b_kstep, p.b_lbo, p.b_sbo);
-            ptx::mma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            if (PAIR) ptx::mma_f16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            else ptx::mma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
-          ptx::tc_commit(&empty[stage]);  // frees the smem stage once these MMAs retire
+          // frees the smem stage (of both CTAs of a pair) once these MMAs retire
+          if (PAIR) ptx::tc_commit_pair(&empty[stage], 3);
+          else ptx::tc_commit(&empty[stage]);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
-        if (ok) ptx::tc_commit(&acc_full[buf]);
+        if (ok) {
+          if (PAIR) ptx::tc_commit_pair(&acc_full[buf], 3);
+          else ptx::tc_commit(&acc_full[buf]);
+        }
       }
     }
   } else {
     // ---------------------------------------------------------------- epilogue
     const int quad = warp & 3;  // TMEM lane quarter this warp may read
     int it = 0;
-    if (p.tma_store) {
+    // the accumulator buffer has been read: the MMA warp (of rank 0 in a pair) may reuse it
+    auto release_acc = [&](int b) {
+      if (PAIR) ptx::mbar_arrive_cluster(&acc_empty[b], 0);
+      else ptx::mbar_arrive(&acc_empty[b]);
+    };
+    if (p.tma_store == 2) {
+      // fp32 outputs (weight gradients): 32 columns at a time -> registers -> swizzled shared-memory tile -> one TMA
+      // store, or one TMA reduce-add when the tile is a split-K partial or accumulates into the output.  The two
+      // staging tiles alternate, so the copy of chunk c overlaps the staging of chunk c + 1.
+      const int trow = quad * 32 + lane;
+      const bool elected = (warp == 2 && lane == 0);
+      int gchunk = 0;
+      for (int tile = cta; tile < num_tiles; tile += ncta, ++it) {
+        const TileCoord tc = tile_coord(p, tile, tiles_m, tiles_n, BN, kTileM, row_off);
+        const int m0 = tc.m0, n0 = tc.n0;
+        const int buf = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!ptx::mbar_wait(&acc_full[buf], acc_phase, abort_flag)) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * Cfg::kAccStride;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col0 = n0 + c * 32;
+          const bool last = (c == BN / 32 - 1);
+          if (col0 >= p.N) {  // whole chunk is padding
+            if (last) {
+              ptx::tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) release_acc(buf);
+            }
+            continue;
+          }
+          uint32_t r[32];
+          ptx::tmem_ld32(t_row + c * 32, r);
+          ptx::tmem_ld_wait();
+          if (last) {  // accumulator fully read: the MMA warp may reuse this TMEM buffer
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) release_acc(buf);
+          }
+          if (p.alpha != nullptr) {
+            const float al = *p.alpha;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * al);
+          }
+          uint8_t* stg = (gchunk & 1) ? stage_aux : stage_out;
+          // the copy issued two chunks ago has finished reading this staging tile
+          if (elected) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            *reinterpret_cast<uint4*>(stg + trow * 128 + ((u ^ (trow & 7)) << 4)) =
+                make_uint4(r[u * 4], r[u * 4 + 1], r[u * 4 + 2], r[u * 4 + 3]);
+          ptx::fence_proxy_async_smem();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (elected) {
+            if (p.f32_red)
+              asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                               reinterpret_cast<uint64_t>(&tma_out)),
+                           "r"(ptx::smem_u32(stg)), "r"(col0), "r"(m0)
+                           : "memory");
+            else
+              asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                               reinterpret_cast<uint64_t>(&tma_out)),
+                           "r"(ptx::smem_u32(stg)), "r"(col0), "r"(m0)
+                           : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+          ++gchunk;
+        }
+      }
+      if (elected) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // all copies done before the CTA exits
+    } else if (p.tma_store) {
       // bf16 outputs: 64 columns at a time -> registers -> swizzled shared-memory tile -> one TMA
       // store per tile chunk (full 128-byte lines instead of one 16-byte piece per thread and row).
       const int trow = quad * 32 + lane;
@@ -591,14 +691,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       const int total_chunks = my_tiles * kChunksPerTile;
       auto issue_aux_load = [&](int g) {  // g: running chunk index over this CTA's tiles
         const int t_local = g / kChunksPerTile;
-        const TileCoord t2 = tile_coord(p, cta + t_local * ncta, tiles_m, tiles_n, BN);
+        const TileCoord t2 = tile_coord(p, cta + t_local * ncta, tiles_m, tiles_n, BN, kTileM, row_off);
         ptx::mbar_expect_tx(aux_bar, kBM * 128);
         ptx::tma_load_2d(stage_aux, &tma_aux, aux_bar, t2.n0 + (g % kChunksPerTile) * 64, t2.m0);
       };
       int gchunk = 0;
       if (p.aux_tma_load && elected && total_chunks > 0) issue_aux_load(0);
       for (int tile = cta; tile < num_tiles; tile += ncta, ++it) {
-        const TileCoord tc = tile_coord(p, tile, tiles_m, tiles_n, BN);
+        const TileCoord tc = tile_coord(p, tile, tiles_m, tiles_n, BN, kTileM, row_off);
         const int m0 = tc.m0, n0 = tc.n0;
         const int buf = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
@@ -626,7 +726,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
             if (c == BN / 64 - 1) {
               ptx::tc_fence_before_sync();
               __syncwarp();
-              if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
+              if (lane == 0) release_acc(buf);
             }
             continue;
           }
@@ -637,7 +737,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
           if (c == BN / 64 - 1) {  // accumulator fully read: the MMA warp may reuse this TMEM buffer
             ptx::tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
+            if (lane == 0) release_acc(buf);
           }
           float v[64];
 #pragma unroll
@@ -735,7 +835,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       if (elected) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // all stores done before the CTA exits
     } else
     for (int tile = cta; tile < num_tiles; tile += ncta, ++it) {
-      const TileCoord tc = tile_coord(p, tile, tiles_m, tiles_n, BN);
+      const TileCoord tc = tile_coord(p, tile, tiles_m, tiles_n, BN, kTileM, row_off);
       const int split = tc.split, m0 = tc.m0, n0 = tc.n0;
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
@@ -774,7 +874,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       }
       ptx::tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
+      if (lane == 0) release_acc(buf);
       if (p.coll.mode == 2) {
         // this warp's 32 rows of the tile are on their way: publish them to the owner (the owner
         // expects four such arrivals per tile, one per epilogue warp)
@@ -791,9 +891,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
 
   ptx::tc_fence_before_sync();
   __syncthreads();
+  if (PAIR) ptx::cluster_sync_all();   // neither CTA leaves while the other may still signal its barriers
   if (warp == 1) {
     __syncwarp();
-    ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    if (PAIR) ptx::tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+    else ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
   if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, kStatusMbarTimeout);
 }
@@ -871,6 +973,20 @@ bool make_tmap_bf16_2d(CUtensorMap* m, const void* base, uint64_t inner, uint64_
   return r == CUDA_SUCCESS;
 }
 
+// fp32 matrix stored [outer, inner] with `ld` elements between rows; box = box_inner x box_outer (128-byte rows).
+static bool make_tmap_f32_2d(CUtensorMap* m, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
+                             uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {ld * 4};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 int device_sm_count() {
   static int sms[64] = {0};
   int dev = 0;
@@ -882,11 +998,12 @@ int device_sm_count() {
 
 static int g_no_tma_store = 0;  // set by titb_gemm_set_tma_store(0): A/B switch for the epilogue store path
 
-// Estimated duration of a GEMM for a tile width and a split-K factor, in units of one 128 x 256 x 64 k-block
-// (about 0.37 us of tensor-core time on one SM).  Main loop: the last CTA runs `waves` tiles of kb_per k-blocks,
-// a k-block of a narrower tile is proportionally cheaper; the epilogue of the last tile is exposed (those of the
-// earlier tiles overlap the next main loop through the second TMEM accumulator); split-K adds the fp32 partial
-// tiles' trip through memory and a second launch.
+// Estimated duration of a GEMM for a tile width and a split-K factor, in units of one k-block (64 deep) of a
+// lightly loaded SM (about 0.4 us, measured: the same for 128-, 192- and 256-wide tiles when few CTAs run).  When
+// most SMs are busy the operand traffic out of L2 sets the pace and a k-block costs more, in proportion to the
+// bytes it loads ((128 + BN) x 64 x 2): about 1.7 units for a 128 x 256 tile on a full machine.  The epilogue of
+// the last tile of a CTA is exposed (earlier ones overlap the next main loop); a split adds the zero fill of the
+// output and the contention of the partial tiles' reduce-adds.
 static double plan_cost(int M, int N, int K, int bn, int splits, int sms) {
   const long long tm = (M + kBM - 1) / kBM, tn = (N + bn - 1) / bn;
   const int kb = (K + kBK - 1) / kBK;
@@ -894,9 +1011,10 @@ static double plan_cost(int M, int N, int K, int bn, int splits, int sms) {
   const int s = (kb + kb_per - 1) / kb_per;
   const long long tiles = tm * tn * s;
   const long long waves = (tiles + sms - 1) / sms;
-  const double w = bn / 256.0;
-  double cost = waves * (double)(kb_per > 3 ? kb_per : 3) * w + 3.0 * w;
-  if (s > 1) cost += 5.0 + ((double)M * N * 4.0 * (s + 1)) / 6.5e6 / 0.37;   // us -> units
+  const double load = tiles >= sms ? 1.0 : (double)tiles / sms;
+  const double c_kb = 1.0 + 0.7 * load * (128.0 + bn) / 384.0;
+  double cost = waves * (double)(kb_per > 3 ? kb_per : 3) * c_kb + 3.0 * bn / 256.0;
+  if (s > 1) cost += 4.0 + 0.5 * s;
   return cost;
 }
 
@@ -949,7 +1067,8 @@ TITB_API int titb_gemm_pick_tile(int M, int N, int K, int splits) { return pick_
 TITB_API int titb_gemm_pick_splits(int M, int N, int K) {
   // Joint choice of split-K factor and tile width by estimated duration (plan_cost): the reduction is split when the
   // output has too few tiles to fill the GPU -- weight gradients: small outputs, K = the token count -- and each
-  // split still runs a pipeline of at least 8 k-blocks.
+  // split still runs a pipeline of at least 8 k-blocks.  (Callers use the result only where the partial tiles can
+  // be summed: fp32 outputs without a fused epilogue.)
   const int sms = device_sm_count();
   const int kb = (K + kBK - 1) / kBK;
   int best_s = 1;
@@ -965,6 +1084,15 @@ TITB_API int titb_gemm_pick_splits(int M, int N, int K) {
   return best_s;
 }
 #endif  // !TITB_GEMM_PARAM_GATHER
+
+static bool deterministic_reductions() {
+  static const bool det = [] { const char* e = getenv("TITB200_DETERMINISTIC"); return e && e[0] == '1'; }();
+  return det;
+}
+static bool f32_tma_eligible(const TitbGemmDesc* d) {
+  return d->out_fp32 && d->epilogue == TITB_EPI_NONE && (d->coll == nullptr || d->coll->mode == 0) &&
+         !(reinterpret_cast<uintptr_t>(d->out) & 15) && !(d->ldo & 3) && g_no_tma_store == 0;
+}
 
 template <int BN>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tout, const CUtensorMap& taux,
@@ -988,6 +1116,10 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
   return static_cast<int>(cudaGetLastError());
 }
 
+#ifndef TITB_GEMM_PARAM_GATHER
+TITB_API int titb_gemm_split_in_place(const TitbGemmDesc* d) { return (f32_tma_eligible(d) && !deterministic_reductions()) ? 1 : 0; }
+#endif
+
 TITB_API int TITB_GEMM_ENTRY(const TitbGemmDesc* d, cudaStream_t stream) {
   if (d->M <= 0 || d->N <= 0 || d->K <= 0) return 0;
   (void)cudaGetLastError();  // do not report an error left behind by an earlier, unrelated call
@@ -998,7 +1130,14 @@ TITB_API int TITB_GEMM_ENTRY(const TitbGemmDesc* d, cudaStream_t stream) {
   int splits = d->splits < 1 ? 1 : d->splits;
   const int num_kb = (d->K + kBK - 1) / kBK;
   if (splits > num_kb) splits = num_kb;
-  if (splits > 1 && (d->workspace == nullptr || (d->N & 3))) splits = 1;
+  // fp32 results without a fused epilogue (weight gradients) leave through shared-memory staging and TMA: a plain
+  // store, or a reduce-add when the tile accumulates into the output or is one of several split-K partials -- the
+  // partial tiles then meet in the output itself (added in L2), with no workspace and no second kernel.  The order
+  // of those additions is not fixed for three or more partials; TITB200_DETERMINISTIC=1 keeps the fixed-order
+  // workspace + reduction kernel instead.
+  const bool f32_tma_ok = f32_tma_eligible(d);
+  const bool red_split = f32_tma_ok && !deterministic_reductions();
+  if (splits > 1 && !red_split && (d->workspace == nullptr || (d->N & 3))) splits = 1;
   const int bn = d->tile_n ? d->tile_n : pick_tile_n(d->M, d->N, d->K, splits);
 
   CUtensorMap ta, tb;
@@ -1013,7 +1152,7 @@ TITB_API int TITB_GEMM_ENTRY(const TitbGemmDesc* d, cudaStream_t stream) {
   a.M = d->M; a.N = d->N; a.K = d->K;
   a.a_mn = d->a_mn_major ? 1 : 0;
   a.b_mn = d->b_mn_major ? 1 : 0;
-  a.out = splits > 1 ? d->workspace : d->out;
+  a.out = (splits > 1 && !red_split) ? d->workspace : d->out;
   a.ldo = d->ldo;
   a.out_fp32 = d->out_fp32; a.accumulate = d->accumulate; a.epi = d->epilogue;
   a.bias = static_cast<const bf16*>(d->bias);
@@ -1086,12 +1225,24 @@ TITB_API int TITB_GEMM_ENTRY(const TitbGemmDesc* d, cudaStream_t stream) {
         !(reinterpret_cast<uintptr_t>(d->aux_in) & 15) && !(d->ld_aux_in & 7))
       a.aux_tma_load = make_tmap_bf16_2d(&taux, d->aux_in, d->N, d->M, d->ld_aux_in, 64, kBM) ? 1 : 0;
   }
+  if (f32_tma_ok && (splits == 1 || red_split)) {
+    if (make_tmap_f32_2d(&tout, d->out, d->N, d->M, d->ldo, 32, kBM)) {
+      a.tma_store = 2;
+      a.f32_red = (splits > 1 || d->accumulate) ? 1 : 0;
+      if (splits > 1 && !d->accumulate) {   // the partial tiles are added to zeros
+        cudaError_t e = cudaMemset2DAsync(d->out, static_cast<size_t>(d->ldo) * 4, 0, static_cast<size_t>(d->N) * 4, d->M, stream);
+        if (e != cudaSuccess) return static_cast<int>(e);
+      }
+    } else if (splits > 1 && red_split) {
+      return TITB_ERR_TENSOR_MAP;
+    }
+  }
   if (bn != 128 && bn != 192 && bn != 256) return TITB_ERR_SHAPE;
   int rc = (bn == 256)   ? launch_gemm<256>(ta, tb, tout, taux, a, stream)
            : (bn == 192) ? launch_gemm<192>(ta, tb, tout, taux, a, stream)
                          : launch_gemm<128>(ta, tb, tout, taux, a, stream);
   if (rc != 0) return rc;
-  if (splits > 1) {
+  if (splits > 1 && a.tma_store != 2) {
     const long long total = static_cast<long long>(d->M) * d->N;
     int blocks = static_cast<int>((total / 4 + 255) / 256);
     if (blocks > 148 * 8) blocks = 148 * 8;
