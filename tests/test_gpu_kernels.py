@@ -73,6 +73,55 @@ def test_gemm_weight_gradient_form_fp32_out(tile_n, splits, accumulate):
     _status_ok()
 
 
+@pytest.mark.parametrize("M,N,K,a_mn,b_mn", [
+    (256, 256, 64, 0, 0), (512, 768, 512, 0, 0), (1000, 776, 520, 0, 0), (1024, 768, 2048, 0, 1),
+    (768, 1024, 1024, 1, 1), (136, 264, 40, 1, 0), (2048, 2304, 768, 0, 0), (8192, 768, 768, 0, 1),
+])
+def test_gemm_cta_pairs(M, N, K, a_mn, b_mn):
+    """tile_n = 512: two CTAs of a cluster share each 256 x 256 tile (tcgen05 cta_group::2), each staging its own
+    half of the operands.  Row counts that leave the second CTA of the last pair partly or wholly outside the matrix,
+    ragged widths, all operand layouts, many tiles per pair (both accumulator buffers and every ring stage reused)."""
+    torch.manual_seed(8)
+    A = (torch.randn(M, K, device=DEV) * 0.5).to(BF)
+    B = (torch.randn(N, K, device=DEV) * 0.5).to(BF)
+    ref = A.float() @ B.float().t()
+    a = A.t().contiguous() if a_mn else A
+    b = B.t().contiguous() if b_mn else B
+    out = C.gemm(a, b, bool(a_mn), bool(b_mn), out_fp32=True, tile_n=512)[0]
+    _status_ok()
+    assert torch.allclose(out, ref, rtol=1e-4, atol=1e-3 * math.sqrt(K))
+    out16 = C.gemm(a, b, bool(a_mn), bool(b_mn), tile_n=512)[0]
+    _status_ok()
+    assert torch.allclose(out16.float(), ref, rtol=2e-2, atol=2e-2 * math.sqrt(K))
+
+
+def test_gemm_cta_pairs_epilogues_and_splits():
+    torch.manual_seed(9)
+    M, N, K = 1160, 776, 328
+    A = (torch.randn(M, K, device=DEV) * 0.5).to(BF)
+    W = (torch.randn(N, K, device=DEV) * 0.1).to(BF)
+    b = (torch.randn(N, device=DEV) * 0.1).to(BF)
+    R = torch.randn(M, N, device=DEV).to(BF)
+    ref = A.float() @ W.float().t()
+    y = C.gemm(A, W, epilogue=ops.EPI_BIAS_RESIDUAL, bias=b, aux_in=R, tile_n=512)[0]
+    assert torch.allclose(y.float(), ref + b.float() + R.float(), atol=5e-2, rtol=2e-2)
+    act, pre = C.gemm(A, W, epilogue=ops.EPI_BIAS_GELU, bias=b, want_aux_out=True, tile_n=512)
+    assert torch.allclose(pre.float(), ref + b.float(), atol=3e-2, rtol=2e-2)
+    assert torch.allclose(act.float(), ops.gelu_ref(pre.float()), atol=2e-2, rtol=2e-2)
+    y = C.gemm(A, W, epilogue=ops.EPI_DGELU, aux_in=pre, tile_n=512)[0]
+    x = pre.float().requires_grad_(True)
+    ops.gelu_ref(x).sum().backward()
+    assert torch.allclose(y.float(), ref * x.grad, atol=5e-2, rtol=3e-2)
+    # weight-gradient form, fp32 accumulate, split over K
+    tokens = 4096
+    dY = (torch.randn(tokens, 520, device=DEV) * 0.5).to(BF)
+    X = (torch.randn(tokens, 776, device=DEV) * 0.5).to(BF)
+    acc = torch.full((520, 776), 2.0, device=DEV)
+    C.gemm(dY, X, True, True, out=acc, accumulate=True, tile_n=512, splits=4)
+    assert torch.allclose(acc, dY.float().t() @ X.float() + 2.0, rtol=1e-4, atol=5e-2)
+    _status_ok()
+
+
 def test_gemm_epilogues():
     torch.manual_seed(2)
     M, N, K = 520, 776, 264

@@ -36,6 +36,8 @@ namespace titb {
 
 bool make_tmap_bf16_2d(CUtensorMap* m, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
                        uint32_t box_inner, uint32_t box_outer);
+bool make_tmap_f32_2d(CUtensorMap* m, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
+                      uint32_t box_inner, uint32_t box_outer);
 
 constexpr int kAttnThreads = 192;
 constexpr int kBlk = 128;             // query rows per CTA tile and keys per step
@@ -53,6 +55,10 @@ __device__ __forceinline__ float ex2(float x) {
 __device__ __forceinline__ uint32_t swz_off(int row, int u) {
   return static_cast<uint32_t>((u >> 3) * kChunkBytes + row * 128 + (((u & 7) ^ (row & 7)) << 4));
 }
+
+// A shared-memory descriptor whose start address is moved by `bytes` (a multiple of 16 that stays inside the CTA's
+// shared memory): only the 14-bit address field changes, so one add replaces rebuilding the descriptor.
+__device__ __forceinline__ uint64_t desc_add(uint64_t desc, uint32_t bytes) { return desc + (bytes >> 4); }
 
 struct AttnArgs {
   int B, T, Hq, Hkv, hd;
@@ -101,13 +107,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kBar);
   uint64_t* q_full = bars;          // 1
-  uint64_t* kv_full = bars + 1;     // [2]
-  uint64_t* kv_empty = bars + 3;    // [2]
-  uint64_t* s_full = bars + 5;
-  uint64_t* p_full = bars + 6;
-  uint64_t* o_full = bars + 7;
-  uint64_t* s_free = bars + 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  uint64_t* k_full = bars + 1;      // [2]
+  uint64_t* k_empty = bars + 3;     // [2]  a K tile is free as soon as its S product has finished ...
+  uint64_t* v_full = bars + 5;      // [2]
+  uint64_t* v_empty = bars + 7;     // [2]  ... a V tile only after its P V product: K runs a block further ahead
+  uint64_t* s_full = bars + 9;
+  uint64_t* p_full = bars + 10;
+  uint64_t* o_full = bars + 11;
+  uint64_t* s_free = bars + 12;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -120,7 +128,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     ptx::mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) { ptx::mbar_init(&kv_full[s], 1); ptx::mbar_init(&kv_empty[s], 1); }
+    for (int s = 0; s < 2; ++s) {
+      ptx::mbar_init(&k_full[s], 1); ptx::mbar_init(&k_empty[s], 1);
+      ptx::mbar_init(&v_full[s], 1); ptx::mbar_init(&v_empty[s], 1);
+    }
     ptx::mbar_init(s_full, 1);
     ptx::mbar_init(p_full, 4);
     ptx::mbar_init(o_full, 1);
@@ -152,15 +163,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         ptx::tma_load_2d(smem + Cfg::kQ + c * kChunkBytes, &tq, q_full, h * HD + c * 64, b * p.T + q0);
       for (int j = 0; j < nblk; ++j) {
         const int st = j & 1;
-        if (!ptx::mbar_wait(&kv_empty[st], ((j >> 1) & 1) ^ 1u, abort_flag)) break;
-        ptx::mbar_expect_tx(&kv_full[st], 2 * Cfg::kTileBytes);
+        if (!ptx::mbar_wait(&k_empty[st], ((j >> 1) & 1) ^ 1u, abort_flag)) break;
+        ptx::mbar_expect_tx(&k_full[st], Cfg::kTileBytes);
 #pragma unroll
-        for (int c = 0; c < HD / 64; ++c) {
-          ptx::tma_load_2d(smem + Cfg::kK + st * Cfg::kTileBytes + c * kChunkBytes, &tk, &kv_full[st],
+        for (int c = 0; c < HD / 64; ++c)
+          ptx::tma_load_2d(smem + Cfg::kK + st * Cfg::kTileBytes + c * kChunkBytes, &tk, &k_full[st],
                            hk * HD + c * 64, b * p.T + j * kBlk);
-          ptx::tma_load_2d(smem + Cfg::kV + st * Cfg::kTileBytes + c * kChunkBytes, &tv, &kv_full[st],
+        if (!ptx::mbar_wait(&v_empty[st], ((j >> 1) & 1) ^ 1u, abort_flag)) break;
+        ptx::mbar_expect_tx(&v_full[st], Cfg::kTileBytes);
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c)
+          ptx::tma_load_2d(smem + Cfg::kV + st * Cfg::kTileBytes + c * kChunkBytes, &tv, &v_full[st],
                            hk * HD + c * 64, b * p.T + j * kBlk);
-        }
       }
     }
   } else if (warp == 1) {
@@ -169,17 +183,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       const uint32_t idesc_o = ptx::make_idesc_bf16(128, HD, 0, 1);
       const uint32_t q_base = ptx::smem_u32(smem + Cfg::kQ);
       const uint32_t p_base = ptx::smem_u32(smem + Cfg::kP);
+      const uint64_t q_desc = ptx::make_smem_desc(q_base, 16, 1024);
+      const uint64_t k_desc0 = ptx::make_smem_desc(ptx::smem_u32(smem + Cfg::kK), 16, 1024);
+      const uint64_t p_desc = ptx::make_smem_desc(p_base, 16, 1024);
+      const uint64_t v_desc0 = ptx::make_smem_desc(ptx::smem_u32(smem + Cfg::kV), kChunkBytes, 1024);
       auto issue_s = [&](int j) {
-        const uint32_t k_base = ptx::smem_u32(smem + Cfg::kK + (j & 1) * Cfg::kTileBytes);
+        const uint64_t k_desc = desc_add(k_desc0, (j & 1) * Cfg::kTileBytes);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
           const uint32_t off = (k >> 2) * kChunkBytes + (k & 3) * 32;
-          ptx::mma_f16_ss(tS, ptx::make_smem_desc(q_base + off, 16, 1024), ptx::make_smem_desc(k_base + off, 16, 1024),
-                          idesc_s, k > 0);
+          ptx::mma_f16_ss(tS, desc_add(q_desc, off), desc_add(k_desc, off), idesc_s, k > 0);
         }
         ptx::tc_commit(s_full);
+        ptx::tc_commit(&k_empty[j & 1]);   // the K tile may be refilled once this product has finished
       };
-      bool ok = ptx::mbar_wait(q_full, 0, abort_flag) && ptx::mbar_wait(&kv_full[0], 0, abort_flag);
+      bool ok = ptx::mbar_wait(q_full, 0, abort_flag) && ptx::mbar_wait(&k_full[0], 0, abort_flag);
       if (ok) {
         ptx::tc_fence_after_sync();
         issue_s(0);
@@ -187,22 +205,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       for (int j = 0; j < nblk && ok; ++j) {
         if (j + 1 < nblk) {
           // S(j+1) goes into the score columns as soon as S(j) has been copied to registers
-          if (!ptx::mbar_wait(&kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag)) break;
+          if (!ptx::mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag)) break;
           if (!ptx::mbar_wait(s_free, j & 1, abort_flag)) break;
           ptx::tc_fence_after_sync();
           issue_s(j + 1);
         }
+        if (!ptx::mbar_wait(&v_full[j & 1], (j >> 1) & 1, abort_flag)) break;
         if (!ptx::mbar_wait(p_full, j & 1, abort_flag)) break;
         ptx::tc_fence_after_sync();
-        const uint32_t v_base = ptx::smem_u32(smem + Cfg::kV + (j & 1) * Cfg::kTileBytes);
+        const uint64_t v_desc = desc_add(v_desc0, (j & 1) * Cfg::kTileBytes);
 #pragma unroll
         for (int k = 0; k < kBlk / 16; ++k) {
           const uint32_t a_off = (k >> 2) * kChunkBytes + (k & 3) * 32;
-          ptx::mma_f16_ss(tO, ptx::make_smem_desc(p_base + a_off, 16, 1024),
-                          ptx::make_smem_desc(v_base + k * 2048, kChunkBytes, 1024), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+          ptx::mma_f16_ss(tO, desc_add(p_desc, a_off), desc_add(v_desc, k * 2048), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
         }
         ptx::tc_commit(o_full);
-        ptx::tc_commit(&kv_empty[j & 1]);
+        ptx::tc_commit(&v_empty[j & 1]);
       }
     }
   } else {
@@ -344,7 +362,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 template <int HD>
 struct BwdCfg {
   static constexpr int kTileBytes = kBlk * HD * 2;
-  static constexpr int kStages = (HD == 64) ? 2 : 1;
+  // Q / dO tiles of the coming iterations: with three stages a load is issued a whole iteration before its tile is
+  // needed (two stages left no lead at all: the slot of iteration it+1 is only released by iteration it-1)
+  static constexpr int kStages = (HD == 64) ? 3 : 1;
   static constexpr bool kAliasDq = (HD > 64);  // dQ partial reuses the S columns when TMEM is full
   static constexpr int kK = 0;
   static constexpr int kV = kK + kTileBytes;
@@ -352,7 +372,11 @@ struct BwdCfg {
   static constexpr int kDO = kQ + kStages * kTileBytes;
   static constexpr int kP = kDO + kStages * kTileBytes;
   static constexpr int kDS = kP + kBlk * kBlk * 2;
-  static constexpr int kBar = kDS + kBlk * kBlk * 2;
+  // hd 64: two [128 rows x 32 fp32] staging tiles from which dQ leaves by TMA reduce-add (hd 128 has no room and
+  // flushes dQ with vector reductions from registers)
+  static constexpr int kDQ = kDS + kBlk * kBlk * 2;
+  static constexpr int kDQBytes = kAliasDq ? 0 : 2 * kBlk * 128;
+  static constexpr int kBar = kDQ + kDQBytes;
   static constexpr int kSmem = kBar + 128;
   static constexpr int kTmemCols = 512;
   static constexpr int kColS = 0, kColDP = 128, kColDV = 256, kColDK = 256 + HD;
@@ -377,21 +401,22 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 template <int HD>
 __global__ void __launch_bounds__(320, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
-                const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo, const AttnArgs p) {
+                const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
+                const __grid_constant__ CUtensorMap tdq, const AttnArgs p) {
   using Cfg = BwdCfg<HD>;
   constexpr int S = Cfg::kStages;
   constexpr bool kPipe = !Cfg::kAliasDq;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kBar);
   uint64_t* kv_full = bars;            // 1
-  uint64_t* qdo_full = bars + 1;       // [2]
-  uint64_t* qdo_empty = bars + 3;      // [2]
-  uint64_t* sdp_full = bars + 5;
-  uint64_t* pds_full = bars + 6;
-  uint64_t* dq_full = bars + 7;
-  uint64_t* dq_free = bars + 8;
-  uint64_t* sdp_free = bars + 9;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* qdo_full = bars + 1;       // [3]
+  uint64_t* qdo_empty = bars + 4;      // [3]
+  uint64_t* sdp_full = bars + 7;
+  uint64_t* pds_full = bars + 8;
+  uint64_t* dq_full = bars + 9;
+  uint64_t* dq_free = bars + 10;
+  uint64_t* sdp_free = bars + 11;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -404,7 +429,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     ptx::mbar_init(kv_full, 1);
-    for (int s = 0; s < 2; ++s) { ptx::mbar_init(&qdo_full[s], 1); ptx::mbar_init(&qdo_empty[s], 1); }
+    for (int s = 0; s < 3; ++s) { ptx::mbar_init(&qdo_full[s], 1); ptx::mbar_init(&qdo_empty[s], 1); }
     ptx::mbar_init(sdp_full, 1);
     ptx::mbar_init(pds_full, 8);
     ptx::mbar_init(dq_full, 1);
@@ -458,21 +483,26 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       const uint32_t idesc_q = ptx::make_idesc_bf16(128, HD, 0, 1);    // dQ    : K-major x MN-major
       const uint32_t k_base = ptx::smem_u32(smem + Cfg::kK), v_base = ptx::smem_u32(smem + Cfg::kV);
       const uint32_t p_base = ptx::smem_u32(smem + Cfg::kP), ds_base = ptx::smem_u32(smem + Cfg::kDS);
+      // descriptors of the fixed tiles, and of stage 0 of the Q / dO ring, in both operand layouts
+      const uint64_t k_kmaj = ptx::make_smem_desc(k_base, 16, 1024), v_kmaj = ptx::make_smem_desc(v_base, 16, 1024);
+      const uint64_t k_mn = ptx::make_smem_desc(k_base, kChunkBytes, 1024);
+      const uint64_t p_mn = ptx::make_smem_desc(p_base, kChunkBytes, 1024), ds_mn = ptx::make_smem_desc(ds_base, kChunkBytes, 1024);
+      const uint64_t ds_kmaj = ptx::make_smem_desc(ds_base, 16, 1024);
+      const uint32_t q_base0 = ptx::smem_u32(smem + Cfg::kQ), do_base0 = ptx::smem_u32(smem + Cfg::kDO);
+      const uint64_t q_kmaj0 = ptx::make_smem_desc(q_base0, 16, 1024), do_kmaj0 = ptx::make_smem_desc(do_base0, 16, 1024);
+      const uint64_t q_mn0 = ptx::make_smem_desc(q_base0, kChunkBytes, 1024), do_mn0 = ptx::make_smem_desc(do_base0, kChunkBytes, 1024);
       auto issue_sdp = [&](int it) {
-        const int st = it % S;
-        const uint32_t q_base = ptx::smem_u32(smem + Cfg::kQ + st * Cfg::kTileBytes);
-        const uint32_t do_base = ptx::smem_u32(smem + Cfg::kDO + st * Cfg::kTileBytes);
+        const uint32_t st_off = (it % S) * Cfg::kTileBytes;
+        const uint64_t q_d = desc_add(q_kmaj0, st_off), do_d = desc_add(do_kmaj0, st_off);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
           const uint32_t off = (k >> 2) * kChunkBytes + (k & 3) * 32;
-          ptx::mma_f16_ss(tmem_base + Cfg::kColS, ptx::make_smem_desc(q_base + off, 16, 1024),
-                          ptx::make_smem_desc(k_base + off, 16, 1024), idesc_s, k > 0);
+          ptx::mma_f16_ss(tmem_base + Cfg::kColS, desc_add(q_d, off), desc_add(k_kmaj, off), idesc_s, k > 0);
         }
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
           const uint32_t off = (k >> 2) * kChunkBytes + (k & 3) * 32;
-          ptx::mma_f16_ss(tmem_base + Cfg::kColDP, ptx::make_smem_desc(do_base + off, 16, 1024),
-                          ptx::make_smem_desc(v_base + off, 16, 1024), idesc_s, k > 0);
+          ptx::mma_f16_ss(tmem_base + Cfg::kColDP, desc_add(do_d, off), desc_add(v_kmaj, off), idesc_s, k > 0);
         }
         ptx::tc_commit(sdp_full);
       };
@@ -486,8 +516,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       }
       for (int it = 0; it < niter && ok; ++it) {
         const int st = it % S;
-        const uint32_t q_base = ptx::smem_u32(smem + Cfg::kQ + st * Cfg::kTileBytes);
-        const uint32_t do_base = ptx::smem_u32(smem + Cfg::kDO + st * Cfg::kTileBytes);
+        const uint64_t q_m = desc_add(q_mn0, st * Cfg::kTileBytes), do_m = desc_add(do_mn0, st * Cfg::kTileBytes);
         if (kPipe && it + 1 < niter) {
           // next S / dP: operands loaded, and the score columns copied out by the element-wise warps
           if (!ptx::mbar_wait(&qdo_full[(it + 1) % S], ((it + 1) / S) & 1, abort_flag)) break;
@@ -499,13 +528,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         ptx::tc_fence_after_sync();
 #pragma unroll
         for (int k = 0; k < kBlk / 16; ++k) {  // reduction over the 128 query rows
-          ptx::mma_f16_ss(tmem_base + Cfg::kColDV, ptx::make_smem_desc(p_base + k * 2048, kChunkBytes, 1024),
-                          ptx::make_smem_desc(do_base + k * 2048, kChunkBytes, 1024), idesc_t, (it > 0 || k > 0));
+          ptx::mma_f16_ss(tmem_base + Cfg::kColDV, desc_add(p_mn, k * 2048), desc_add(do_m, k * 2048), idesc_t, (it > 0 || k > 0));
         }
 #pragma unroll
         for (int k = 0; k < kBlk / 16; ++k) {
-          ptx::mma_f16_ss(tmem_base + Cfg::kColDK, ptx::make_smem_desc(ds_base + k * 2048, kChunkBytes, 1024),
-                          ptx::make_smem_desc(q_base + k * 2048, kChunkBytes, 1024), idesc_t, (it > 0 || k > 0));
+          ptx::mma_f16_ss(tmem_base + Cfg::kColDK, desc_add(ds_mn, k * 2048), desc_add(q_m, k * 2048), idesc_t, (it > 0 || k > 0));
         }
         if (kPipe && it > 0) {
           // dQ(it-1) has left tensor memory
@@ -515,8 +542,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 #pragma unroll
         for (int k = 0; k < kBlk / 16; ++k) {  // reduction over the 128 keys
           const uint32_t a_off = (k >> 2) * kChunkBytes + (k & 3) * 32;
-          ptx::mma_f16_ss(tmem_base + Cfg::kColDQ, ptx::make_smem_desc(ds_base + a_off, 16, 1024),
-                          ptx::make_smem_desc(k_base + k * 2048, kChunkBytes, 1024), idesc_q, k > 0);
+          ptx::mma_f16_ss(tmem_base + Cfg::kColDQ, desc_add(ds_kmaj, a_off), desc_add(k_mn, k * 2048), idesc_q, k > 0);
         }
         ptx::tc_commit(dq_full);
         ptx::tc_commit(&qdo_empty[st]);
@@ -544,29 +570,62 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       const int g2 = it2 / nq, i2 = jb + (it2 - g2 * nq);
       const int q2 = i2 * kBlk + row;
       const long long stat2 = (static_cast<long long>(b) * p.Hq + (hk * G + g2)) * p.T + q2;
-      l = q2 < p.T ? p.lse[stat2] * kLog2e : INFINITY;
+      // raw values: the conversion to base 2 happens where lse is used, so that nothing here waits for the loads
+      l = q2 < p.T ? p.lse[stat2] : INFINITY;
       d = q2 < p.T ? p.delta[stat2] : 0.f;
     };
-    // dQ of iteration `it2`, this warp's half of the head dimension: tensor memory -> fp32 reductions in HBM
+    // dQ of iteration `it2`, this warp's half of the head dimension, leaves tensor memory and is added to the fp32
+    // accumulator in HBM.  hd 64: through a swizzled shared-memory tile and one TMA reduce-add per half (rows past the
+    // end of the sequence are exact zeros, so adding them is harmless); hd 128: vector reductions from registers.
     auto flush_dq = [&](int it2) {
       const int g2 = it2 / nq, i2 = jb + (it2 - g2 * nq);
       const int q2 = i2 * kBlk + row;
-      float* dq_row = p.dq_accum + ((static_cast<long long>(b) * p.T + q2) * p.Hq + (hk * G + g2)) * HD;
-#pragma unroll 1
-      for (int c = half * (HD / 64); c < (half + 1) * (HD / 64); ++c) {
+      if constexpr (kPipe) {
+        uint8_t* stg = smem + Cfg::kDQ + half * (kBlk * 128);
+        const bool elected = (warp == 2 && lane == 0);
+        // the reduce-adds of the previous flush have finished reading the staging tiles
+        if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        asm volatile("bar.sync 2, 256;" ::: "memory");
         uint32_t r[32];
-        ptx::tmem_ld32(tmem_base + Cfg::kColDQ + lane_sel + c * 32, r);
+        ptx::tmem_ld32(tmem_base + Cfg::kColDQ + lane_sel + half * 32, r);
         ptx::tmem_ld_wait();
-        if (q2 < p.T) {
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(dq_free);       // the dQ columns may be overwritten
 #pragma unroll
-          for (int e = 0; e < 32; e += 4)
-            red_add_v4(dq_row + c * 32 + e, __uint_as_float(r[e]), __uint_as_float(r[e + 1]), __uint_as_float(r[e + 2]),
-                       __uint_as_float(r[e + 3]));
+        for (int u = 0; u < 8; ++u)
+          *reinterpret_cast<uint4*>(stg + row * 128 + ((u ^ (row & 7)) << 4)) =
+              make_uint4(r[u * 4], r[u * 4 + 1], r[u * 4 + 2], r[u * 4 + 3]);
+        ptx::fence_proxy_async_smem();
+        asm volatile("bar.sync 2, 256;" ::: "memory");
+        if (elected) {
+          const int x = (hk * G + g2) * HD, y = b * p.T + i2 * kBlk;
+#pragma unroll
+          for (int h2 = 0; h2 < 2; ++h2)
+            asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                             reinterpret_cast<uint64_t>(&tdq)),
+                         "r"(ptx::smem_u32(smem + Cfg::kDQ + h2 * (kBlk * 128))), "r"(x + h2 * 32), "r"(y)
+                         : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
+      } else {
+        float* dq_row = p.dq_accum + ((static_cast<long long>(b) * p.T + q2) * p.Hq + (hk * G + g2)) * HD;
+#pragma unroll 1
+        for (int c = half * (HD / 64); c < (half + 1) * (HD / 64); ++c) {
+          uint32_t r[32];
+          ptx::tmem_ld32(tmem_base + Cfg::kColDQ + lane_sel + c * 32, r);
+          ptx::tmem_ld_wait();
+          if (q2 < p.T) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 4)
+              red_add_v4(dq_row + c * 32 + e, __uint_as_float(r[e]), __uint_as_float(r[e + 1]), __uint_as_float(r[e + 2]),
+                         __uint_as_float(r[e + 3]));
+          }
+        }
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(dq_free);
       }
-      ptx::tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(dq_free);
     };
     float pre_lse = 0.f, pre_dlt = 0.f;
     if (niter > 0) load_stats(0, pre_lse, pre_dlt);
@@ -595,7 +654,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
           if (kv0 + 32 + e > q_idx) s1[e] = ninf;
         }
       }
-      const float neg = -lse2;
+      const float neg = -lse2 * kLog2e;
       auto ew_chunk = [&](uint32_t (&rs)[32], uint32_t (&rd)[32], int c) {
         uint32_t pk[16], dk_[16];
 #pragma unroll
@@ -642,6 +701,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         flush_dq(niter - 1);
       }
     }
+    if (kPipe && warp == 2 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // all reduce-adds done
     // The last dq_full arrival also covers every dV/dK accumulation issued before it.
     const int kv_idx = jb * kBlk + row;
     if (ok && niter > 0) {
@@ -769,11 +829,15 @@ static int attn_bwd_launch(const TitbAttnDesc* d, cudaStream_t st) {
     attr_set[dev] = true;
   }
   const uint64_t rows = static_cast<uint64_t>(d->B) * d->T;
-  CUtensorMap tq, tk, tv, tdo;
+  CUtensorMap tq, tk, tv, tdo, tdq;
   if (!make_tmap_bf16_2d(&tq, d->q, static_cast<uint64_t>(d->Hq) * HD, rows, d->q_stride_t, 64, kBlk) ||
       !make_tmap_bf16_2d(&tk, d->k, static_cast<uint64_t>(d->Hkv) * HD, rows, d->k_stride_t, 64, kBlk) ||
       !make_tmap_bf16_2d(&tv, d->v, static_cast<uint64_t>(d->Hkv) * HD, rows, d->v_stride_t, 64, kBlk) ||
       !make_tmap_bf16_2d(&tdo, d->d_o, static_cast<uint64_t>(d->Hq) * HD, rows, d->do_stride_t, 64, kBlk))
+    return TITB_ERR_TENSOR_MAP;
+  tdq = tq;  // placeholder where the kernel does not use it (hd 128)
+  if (!Cfg::kAliasDq && !make_tmap_f32_2d(&tdq, d->dq_accum, static_cast<uint64_t>(d->Hq) * HD, rows,
+                                          static_cast<uint64_t>(d->Hq) * HD, 32, kBlk))
     return TITB_ERR_TENSOR_MAP;
   const long long nrows = static_cast<long long>(d->B) * d->T * d->Hq;
   int blocks = static_cast<int>((nrows + 255) / 256);
@@ -790,7 +854,7 @@ static int attn_bwd_launch(const TitbAttnDesc* d, cudaStream_t st) {
   a.dk_stride_t = d->dk_stride_t; a.dv_stride_t = d->dv_stride_t;
   a.status = titb_status_ptr();
   dim3 grid((d->T + kBlk - 1) / kBlk, d->Hkv, d->B);
-  attn_bwd_kernel<HD><<<grid, 320, Cfg::kSmem, st>>>(tq, tk, tv, tdo, a);
+  attn_bwd_kernel<HD><<<grid, 320, Cfg::kSmem, st>>>(tq, tk, tv, tdo, tdq, a);
   const long long bt = static_cast<long long>(d->B) * d->T;
   const int width = d->Hq * HD;
   int cb = static_cast<int>((bt * (width / 8) + 255) / 256);

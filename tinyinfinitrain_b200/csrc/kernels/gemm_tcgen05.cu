@@ -974,10 +974,15 @@ bool make_tmap_bf16_2d(CUtensorMap* m, const void* base, uint64_t inner, uint64_
 }
 
 // fp32 matrix stored [outer, inner] with `ld` elements between rows; box = box_inner x box_outer (128-byte rows).
-static bool make_tmap_f32_2d(CUtensorMap* m, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
-                             uint32_t box_inner, uint32_t box_outer) {
+bool make_tmap_f32_2d(CUtensorMap* m, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
+                      uint32_t box_inner, uint32_t box_outer) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return false;
+  static thread_local bool ctx_bound = false;   // see make_tmap_bf16_2d
+  if (!ctx_bound) {
+    cudaFree(nullptr);
+    ctx_bound = true;
+  }
   cuuint64_t dims[2] = {inner, outer};
   cuuint64_t strides[1] = {ld * 4};
   cuuint32_t box[2] = {box_inner, box_outer};
@@ -1094,25 +1099,45 @@ static bool f32_tma_eligible(const TitbGemmDesc* d) {
          !(reinterpret_cast<uintptr_t>(d->out) & 15) && !(d->ldo & 3) && g_no_tma_store == 0;
 }
 
-template <int BN>
+template <int BN, bool PAIR>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tout, const CUtensorMap& taux,
                        const GemmArgs& args, cudaStream_t stream) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, PAIR>;
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) dev = 0;
   if (!attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::kSmem);
     if (e != cudaSuccess) return static_cast<int>(e);
     attr_set[dev] = true;
   }
-  const int tiles = ((args.M + kBM - 1) / kBM) * ((args.N + BN - 1) / BN) * args.splits;
+  const int tiles = ((args.M + Cfg::kTileM - 1) / Cfg::kTileM) * ((args.N + BN - 1) / BN) * args.splits;
+  if (PAIR) {
+    // clusters of two CTAs, one pair per tile in flight; the pair count is capped at half the SMs
+    if (args.coll.mode) return TITB_ERR_SHAPE;
+    int pairs = device_sm_count() / 2;
+    if (tiles < pairs) pairs = tiles;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = Cfg::kSmem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_bf16_tcgen05_kernel<BN, PAIR>, ta, tb, tout, taux, args);
+    return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
+  }
   const int helpers = args.coll.mode ? args.coll.helper_ctas : 0;
   int grid = tiles + helpers < device_sm_count() ? tiles + helpers : device_sm_count();
   if (grid <= helpers) return TITB_ERR_SHAPE;
-  gemm_bf16_tcgen05_kernel<BN><<<grid, kGemmThreads, Cfg::kSmem, stream>>>(ta, tb, tout, taux, args);
+  gemm_bf16_tcgen05_kernel<BN, PAIR><<<grid, kGemmThreads, Cfg::kSmem, stream>>>(ta, tb, tout, taux, args);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -1138,13 +1163,19 @@ TITB_API int TITB_GEMM_ENTRY(const TitbGemmDesc* d, cudaStream_t stream) {
   const bool f32_tma_ok = f32_tma_eligible(d);
   const bool red_split = f32_tma_ok && !deterministic_reductions();
   if (splits > 1 && !red_split && (d->workspace == nullptr || (d->N & 3))) splits = 1;
-  const int bn = d->tile_n ? d->tile_n : pick_tile_n(d->M, d->N, d->K, splits);
+  // tile_n = 512 asks for CTA pairs on 256 x 256 tiles (cta_group::2); 128 / 192 / 256 are single-CTA 128 x tile_n
+  int bn = d->tile_n ? d->tile_n : pick_tile_n(d->M, d->N, d->K, splits);
+  bool pair = false;
+  if (bn == 512) {
+    pair = (d->coll == nullptr || d->coll->mode == 0) && d->M > kBM && d->N > 128;
+    bn = 256;
+  }
 
   CUtensorMap ta, tb;
   bool ok;
   if (!d->a_mn_major) ok = make_tmap_bf16_2d(&ta, d->a, d->K, d->M, d->lda, kBK, kBM);
   else ok = make_tmap_bf16_2d(&ta, d->a, d->M, d->K, d->lda, 64, kBK);
-  if (!d->b_mn_major) ok = ok && make_tmap_bf16_2d(&tb, d->b, d->K, d->N, d->ldb, kBK, bn);
+  if (!d->b_mn_major) ok = ok && make_tmap_bf16_2d(&tb, d->b, d->K, d->N, d->ldb, kBK, pair ? bn / 2 : bn);
   else ok = ok && make_tmap_bf16_2d(&tb, d->b, d->N, d->K, d->ldb, 64, kBK);
   if (!ok) return TITB_ERR_TENSOR_MAP;
 
@@ -1238,9 +1269,10 @@ TITB_API int TITB_GEMM_ENTRY(const TitbGemmDesc* d, cudaStream_t stream) {
     }
   }
   if (bn != 128 && bn != 192 && bn != 256) return TITB_ERR_SHAPE;
-  int rc = (bn == 256)   ? launch_gemm<256>(ta, tb, tout, taux, a, stream)
-           : (bn == 192) ? launch_gemm<192>(ta, tb, tout, taux, a, stream)
-                         : launch_gemm<128>(ta, tb, tout, taux, a, stream);
+  int rc = pair          ? launch_gemm<256, true>(ta, tb, tout, taux, a, stream)
+           : (bn == 256) ? launch_gemm<256, false>(ta, tb, tout, taux, a, stream)
+           : (bn == 192) ? launch_gemm<192, false>(ta, tb, tout, taux, a, stream)
+                         : launch_gemm<128, false>(ta, tb, tout, taux, a, stream);
   if (rc != 0) return rc;
   if (splits > 1 && a.tma_store != 2) {
     const long long total = static_cast<long long>(d->M) * d->N;

@@ -87,16 +87,19 @@ def gemm_sweep(C, model: str, iters: int):
             ("wgrad dW+=dY^T.X (fp32 out)", lambda: C.gemm(dY, X, True, True, out=dWf, accumulate=True),
              lambda: torch.matmul(dY.t(), X)),
         ]
-        for label, ours, lib in cases:
-            t_o, t_l = run(ours), run(lib)
+        pair_cases = [lambda: C.gemm(X, W, tile_n=512), lambda: C.gemm(dY, W, False, True, tile_n=512),
+                      lambda: C.gemm(dY, X, True, True, out=dWf, accumulate=True, tile_n=512)]
+        for (label, ours, lib), pair in zip(cases, pair_cases):
+            t_o, t_l, t_p = run(ours), run(lib), run(pair)
             fl = 2.0 * M * N * K
             rows.append({"layer": name, "case": label, "M": M, "N": N, "K": K, "ours_us": t_o, "torch_us": t_l,
+                         "pair_us": t_p,   # forced CTA pairs (256 x 256 tiles), whatever the planner would pick
                          "ours_frac_of_bf16_peak": fl / t_o / 1e6 / tflops, "ours_over_torch": t_l / t_o})
         del X, W, dY, dWf, Wt
-    print(f"{'layer':<12} {'case':<30} {'N':>6} {'K':>6} {'ours us':>9} {'torch us':>9} {'frac peak':>9} {'speedup':>8}")
+    print(f"{'layer':<12} {'case':<30} {'N':>6} {'K':>6} {'ours us':>9} {'torch us':>9} {'frac peak':>9} {'speedup':>8} {'pairs us':>9}")
     for r in rows:
         print(f"{r['layer']:<12} {r['case']:<30} {r['N']:>6} {r['K']:>6} {r['ours_us']:>9.1f} {r['torch_us']:>9.1f} "
-              f"{r['ours_frac_of_bf16_peak']:>9.3f} {r['ours_over_torch']:>8.2f}")
+              f"{r['ours_frac_of_bf16_peak']:>9.3f} {r['ours_over_torch']:>8.2f} {r['pair_us']:>9.1f}")
     print(json.dumps({"kernel": "gemm_sweep", "model": model, "peaks": src, "status": int(C.status_read(True)), "rows": rows}))
 
 
