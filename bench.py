@@ -221,9 +221,10 @@ def main():
     if library and parallel_path:
         raise SystemExit("--impl library exists for the gpt2_dp config only; the comparison arm of the other configs is --comm nccl")
 
-    # synthetic uniform token ids, seed 0 (+rank so every rank sees different data), pinned on the host
+    # synthetic uniform token ids, pinned on the host: seed 0 + data-parallel rank, so that replicas see different data
+    # and the tensor / pipeline ranks of one replica see the same batch
     nbuf = 4
-    gen = torch.Generator().manual_seed(0 + rank)
+    gen = torch.Generator().manual_seed(0 + rank // (tp * pp))
     pin = (lambda t: t.pin_memory()) if on_gpu else (lambda t: t)
 
     def host_pair():

@@ -95,57 +95,95 @@ struct RsAdamArgs {
   const float* dev_state;  // optional {t, bc1, bc2, lr}
 };
 
+// One 8-element group of the shard: reduced gradient in `g`, Adam on the fp32 state, bf16 result to every rank.
+__device__ __forceinline__ void rs_adam_update8(const RsAdamArgs& a, long long loc, long long glob, const float (&g)[8], float lr,
+                                                float bc1, float bc2) {
+  float4 m0 = *reinterpret_cast<const float4*>(a.m + loc), m1 = *reinterpret_cast<const float4*>(a.m + loc + 4);
+  float4 v0 = *reinterpret_cast<const float4*>(a.v + loc), v1 = *reinterpret_cast<const float4*>(a.v + loc + 4);
+  float4 w0 = *reinterpret_cast<const float4*>(a.master + loc), w1 = *reinterpret_cast<const float4*>(a.master + loc + 4);
+  float mm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+  float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+  float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float ge = g[e] * a.gscale;
+    mm[e] = a.b1 * mm[e] + (1.f - a.b1) * ge;
+    vv[e] = a.b2 * vv[e] + (1.f - a.b2) * ge * ge;
+    ww[e] -= lr * ((mm[e] / bc1) / (sqrtf(vv[e] / bc2) + a.eps) + a.wd * ww[e]);
+  }
+  *reinterpret_cast<float4*>(a.m + loc) = make_float4(mm[0], mm[1], mm[2], mm[3]);
+  *reinterpret_cast<float4*>(a.m + loc + 4) = make_float4(mm[4], mm[5], mm[6], mm[7]);
+  *reinterpret_cast<float4*>(a.v + loc) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+  *reinterpret_cast<float4*>(a.v + loc + 4) = make_float4(vv[4], vv[5], vv[6], vv[7]);
+  *reinterpret_cast<float4*>(a.master + loc) = make_float4(ww[0], ww[1], ww[2], ww[3]);
+  *reinterpret_cast<float4*>(a.master + loc + 4) = make_float4(ww[4], ww[5], ww[6], ww[7]);
+  const uint4 packed = make_uint4(pack_bf16x2(ww[0], ww[1]), pack_bf16x2(ww[2], ww[3]), pack_bf16x2(ww[4], ww[5]),
+                                  pack_bf16x2(ww[6], ww[7]));
+  if (a.param_mc != nullptr) {
+    multimem_st_b32x4(static_cast<bf16*>(a.param_mc) + glob, packed);
+  } else {
+    for (int q = 0; q < a.world; ++q) {
+      const int pr = (a.rank + q) % a.world;
+      *reinterpret_cast<uint4*>(static_cast<bf16*>(a.params.p[pr]) + glob) = packed;
+    }
+  }
+}
+
+// Every thread handles kGroups 8-element groups per trip and issues all of their remote gradient loads before it
+// uses the first: a load that crosses NVLink (or is reduced in the switch) takes microseconds, and the link is only
+// busy when megabytes are outstanding.
 __global__ void __launch_bounds__(256) rs_adam_ag_kernel(const RsAdamArgs a) {
   float lr = a.lr, bc1 = a.bc1, bc2 = a.bc2;
   if (a.dev_state != nullptr) { bc1 = a.dev_state[1]; bc2 = a.dev_state[2]; lr = a.dev_state[3]; }
+  constexpr int kGroups = 4;
   const long long nvec = a.shard_n / 8;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
-    const long long loc = i * 8, glob = a.shard_off + loc;
-    float g[8];
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < nvec; i0 += kGroups * stride) {
+    float g[kGroups][8];
     if (a.grad_mc != nullptr) {
-      const float4 g0 = multimem_ld_reduce_f32x4(a.grad_mc + glob);
-      const float4 g1 = multimem_ld_reduce_f32x4(a.grad_mc + glob + 4);
-      g[0] = g0.x; g[1] = g0.y; g[2] = g0.z; g[3] = g0.w; g[4] = g1.x; g[5] = g1.y; g[6] = g1.z; g[7] = g1.w;
+#pragma unroll
+      for (int u = 0; u < kGroups; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < nvec) {
+          const long long glob = a.shard_off + i * 8;
+          const float4 g0 = multimem_ld_reduce_f32x4(a.grad_mc + glob);
+          const float4 g1 = multimem_ld_reduce_f32x4(a.grad_mc + glob + 4);
+          g[u][0] = g0.x; g[u][1] = g0.y; g[u][2] = g0.z; g[u][3] = g0.w;
+          g[u][4] = g1.x; g[u][5] = g1.y; g[u][6] = g1.z; g[u][7] = g1.w;
+        }
+      }
     } else {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) g[e] = 0.f;
-      // start at this rank and wrap, so the eight ranks do not all read the same peer at once
-      for (int q = 0; q < a.world; ++q) {
-        const int pr = (a.rank + q) % a.world;
-        const float* src = static_cast<const float*>(a.grads.p[pr]) + glob;
-        const float4 g0 = *reinterpret_cast<const float4*>(src);
-        const float4 g1 = *reinterpret_cast<const float4*>(src + 4);
-        g[0] += g0.x; g[1] += g0.y; g[2] += g0.z; g[3] += g0.w; g[4] += g1.x; g[5] += g1.y; g[6] += g1.z; g[7] += g1.w;
-      }
-    }
-    float4 m0 = *reinterpret_cast<const float4*>(a.m + loc), m1 = *reinterpret_cast<const float4*>(a.m + loc + 4);
-    float4 v0 = *reinterpret_cast<const float4*>(a.v + loc), v1 = *reinterpret_cast<const float4*>(a.v + loc + 4);
-    float4 w0 = *reinterpret_cast<const float4*>(a.master + loc), w1 = *reinterpret_cast<const float4*>(a.master + loc + 4);
-    float mm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
-    float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-    float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+      for (int u = 0; u < kGroups; ++u)
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const float ge = g[e] * a.gscale;
-      mm[e] = a.b1 * mm[e] + (1.f - a.b1) * ge;
-      vv[e] = a.b2 * vv[e] + (1.f - a.b2) * ge * ge;
-      ww[e] -= lr * ((mm[e] / bc1) / (sqrtf(vv[e] / bc2) + a.eps) + a.wd * ww[e]);
-    }
-    *reinterpret_cast<float4*>(a.m + loc) = make_float4(mm[0], mm[1], mm[2], mm[3]);
-    *reinterpret_cast<float4*>(a.m + loc + 4) = make_float4(mm[4], mm[5], mm[6], mm[7]);
-    *reinterpret_cast<float4*>(a.v + loc) = make_float4(vv[0], vv[1], vv[2], vv[3]);
-    *reinterpret_cast<float4*>(a.v + loc + 4) = make_float4(vv[4], vv[5], vv[6], vv[7]);
-    *reinterpret_cast<float4*>(a.master + loc) = make_float4(ww[0], ww[1], ww[2], ww[3]);
-    *reinterpret_cast<float4*>(a.master + loc + 4) = make_float4(ww[4], ww[5], ww[6], ww[7]);
-    const uint4 packed = make_uint4(pack_bf16x2(ww[0], ww[1]), pack_bf16x2(ww[2], ww[3]), pack_bf16x2(ww[4], ww[5]),
-                                    pack_bf16x2(ww[6], ww[7]));
-    if (a.param_mc != nullptr) {
-      multimem_st_b32x4(static_cast<bf16*>(a.param_mc) + glob, packed);
-    } else {
+        for (int e = 0; e < 8; ++e) g[u][e] = 0.f;
+      // start at this rank and wrap, so the ranks do not all read the same peer at once
       for (int q = 0; q < a.world; ++q) {
         const int pr = (a.rank + q) % a.world;
-        *reinterpret_cast<uint4*>(static_cast<bf16*>(a.params.p[pr]) + glob) = packed;
+        float4 t0[kGroups], t1[kGroups];
+#pragma unroll
+        for (int u = 0; u < kGroups; ++u) {
+          const long long i = i0 + u * stride;
+          if (i < nvec) {
+            const float* src = static_cast<const float*>(a.grads.p[pr]) + a.shard_off + i * 8;
+            t0[u] = *reinterpret_cast<const float4*>(src);
+            t1[u] = *reinterpret_cast<const float4*>(src + 4);
+          } else {
+            t0[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            t1[u] = t0[u];
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < kGroups; ++u) {
+          g[u][0] += t0[u].x; g[u][1] += t0[u].y; g[u][2] += t0[u].z; g[u][3] += t0[u].w;
+          g[u][4] += t1[u].x; g[u][5] += t1[u].y; g[u][6] += t1[u].z; g[u][7] += t1[u].w;
+        }
       }
+    }
+#pragma unroll
+    for (int u = 0; u < kGroups; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < nvec) rs_adam_update8(a, i * 8, a.shard_off + i * 8, g[u], lr, bc1, bc2);
     }
   }
 }

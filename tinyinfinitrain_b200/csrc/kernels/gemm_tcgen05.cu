@@ -122,7 +122,6 @@ __device__ __forceinline__ float gelu_grad_fast(float x) {
 // Epilogue for one thread: 32 consecutive columns [col0, col0+32) of one output row.
 __device__ __forceinline__ void epilogue_row32(const GemmArgs& p, float (&v)[32], long long row, int col0,
                                                 int split) {
-  if (p.epi == 100) return;  // timing probe: accumulator read, nothing stored
   const int ncols = min(32, p.N - col0);
   const bool full = (ncols == 32) && p.vec_ok;
 
@@ -315,10 +314,16 @@ __device__ void ag_copy_role(const GemmArgs& p) {
     const uint4* src = reinterpret_cast<const uint4*>(static_cast<const bf16*>(c.peers[src_rank]) +
                                                       static_cast<long long>(mblk - src_rank * cpr) * kBM * p.K);
     uint4* dst = reinterpret_cast<uint4*>(c.gathered + static_cast<long long>(mblk) * kBM * p.K);
+    // sixteen 16-byte loads per thread in flight: a load from a peer takes a few microseconds over NVLink, and the
+    // link is only busy when a couple of megabytes are outstanding on the whole GPU
     long long i = threadIdx.x;
-    for (; i + 3 * kGemmThreads < vec_per_chunk; i += 4 * kGemmThreads) {
-      const uint4 v0 = src[i], v1 = src[i + kGemmThreads], v2 = src[i + 2 * kGemmThreads], v3 = src[i + 3 * kGemmThreads];
-      dst[i] = v0; dst[i + kGemmThreads] = v1; dst[i + 2 * kGemmThreads] = v2; dst[i + 3 * kGemmThreads] = v3;
+    constexpr int kInFlight = 16;
+    for (; i + (kInFlight - 1) * kGemmThreads < vec_per_chunk; i += kInFlight * kGemmThreads) {
+      uint4 v[kInFlight];
+#pragma unroll
+      for (int u = 0; u < kInFlight; ++u) v[u] = src[i + u * kGemmThreads];
+#pragma unroll
+      for (int u = 0; u < kInFlight; ++u) dst[i + u * kGemmThreads] = v[u];
     }
     for (; i < vec_per_chunk; i += kGemmThreads) dst[i] = src[i];
     fence_proxy_async_all();  // these generic-proxy writes are read by TMA (async proxy) below
@@ -356,53 +361,67 @@ __device__ void param_gather_role(const GemmArgs& p) {
 }
 #endif
 
-// mode 2 helper CTA: sum the `world` partial slots of this rank's row chunks as they complete.
-__device__ void rs_reduce_role(const GemmArgs& p, int tiles_n) {
+// mode 2, second phase: when a CTA has pushed all its partial tiles, its four epilogue warps (128 threads, named
+// barrier 1) help to sum the `world` partial slots of this rank's rows.  A work unit is a 128-row chunk x a strip of
+// columns; units are dealt round-robin over all CTAs, so the whole GPU streams the reduction (a handful of helper
+// CTAs cannot pull more than a fraction of the memory bandwidth).  A unit waits -- bounded -- until every rank's
+// partial tiles of its chunk have arrived; remote ranks send this rank's rows first, so they usually have.
+__device__ void rs_reduce_phase(const GemmArgs& p, int tiles_n, int worker, int nworkers, int tid) {
   const CollArgs& c = p.coll;
   __shared__ int ok_sh;
   const int cpr = c.rows_per_rank / kBM;
-  const uint32_t expected = static_cast<uint32_t>(c.world * tiles_n * 4);  // 4 epilogue warps per tile
+  const uint32_t expected = static_cast<uint32_t>(c.world * tiles_n);  // one arrival per partial tile
   const bf16* recv = static_cast<const bf16*>(c.peers[c.rank]);
   const long long slot = static_cast<long long>(c.rows_per_rank) * p.N;
+  // strips of 64 columns (8 vectors): a thread sums one vector of one row per step, `world` loads in flight each
   const int nv = p.N / 8;
-  for (int ch = blockIdx.x; ch < cpr; ch += c.helper_ctas) {
-    if (threadIdx.x == 0) {
+  const int strips = (nv + 7) / 8;
+  const int units = cpr * strips;
+  for (int u = worker; u < units; u += nworkers) {
+    const int ch = u / strips, st = u - ch * strips;
+    if (tid == 0) {
       ok_sh = wait_flag_ge<true>(c.flags + ch, expected) ? 1 : 0;
       if (!ok_sh) atomicExch(p.status, kStatusPeerTimeout);
     }
-    __syncthreads();
-    if (ok_sh) {
-      for (int i = threadIdx.x; i < kBM * nv; i += kGemmThreads) {
-        const int r = ch * kBM + i / nv, col = (i % nv) * 8;
-        const long long off = static_cast<long long>(r) * p.N + col;
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int s = 0; s < c.world; ++s) {
-          const uint4 u = *reinterpret_cast<const uint4*>(recv + s * slot + off);
-          const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    const bool ok = ok_sh != 0;
+    asm volatile("bar.sync 1, 128;" ::: "memory");   // ok_sh may be rewritten for the next unit
+    if (!ok) continue;
+    const int v0 = st * 8, vn = min(8, nv - v0);
+    // 128 rows x vn vectors; consecutive threads take consecutive vectors of a row
+    for (int i = tid; i < kBM * vn; i += 128) {
+      const int r = ch * kBM + i / vn, col = (v0 + i % vn) * 8;
+      const long long off = static_cast<long long>(r) * p.N + col;
+      uint4 part[16];
+#pragma unroll
+      for (int s = 0; s < 16; ++s)
+        if (s < c.world) part[s] = *reinterpret_cast<const uint4*>(recv + s * slot + off);
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int s = 0; s < 16; ++s) {
+        if (s < c.world) {
+          const float2 f0 = unpack_bf16x2(part[s].x), f1 = unpack_bf16x2(part[s].y), f2 = unpack_bf16x2(part[s].z),
+                       f3 = unpack_bf16x2(part[s].w);
           acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
           acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
         }
-        if (c.rs_bias != nullptr) {
-          const uint4 u = *reinterpret_cast<const uint4*>(c.rs_bias + col);
-          const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
-          acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
-          acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
-        }
-        if (c.rs_residual != nullptr) {
-          const uint4 u = *reinterpret_cast<const uint4*>(c.rs_residual + off);
-          const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
-          acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
-          acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
-        }
-        *reinterpret_cast<uint4*>(c.rs_out + off) =
-            make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
-                       pack_bf16x2(acc[6], acc[7]));
       }
+      if (c.rs_bias != nullptr) {
+        const uint4 b = *reinterpret_cast<const uint4*>(c.rs_bias + col);
+        const float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z), f3 = unpack_bf16x2(b.w);
+        acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
+        acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+      }
+      if (c.rs_residual != nullptr) {
+        const uint4 b = *reinterpret_cast<const uint4*>(c.rs_residual + off);
+        const float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z), f3 = unpack_bf16x2(b.w);
+        acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
+        acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+      }
+      *reinterpret_cast<uint4*>(c.rs_out + off) =
+          make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
+                     pack_bf16x2(acc[6], acc[7]));
     }
-    __syncthreads();
-    // Every partial of this chunk has arrived, so the counter can be cleared for the next call:
-    // peers only start the next call's stores after a cross-GPU barrier that follows this kernel.
-    if (threadIdx.x == 0) { c.flags[ch] = 0u; __threadfence_system(); }
   }
 }
 
@@ -419,13 +438,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   const int row_off = static_cast<int>(pair_rank) * kBM;
 
   // Leading CTAs of a fused-collective launch do the copy / reduction instead of GEMM tiles.
-  const int helpers = (!PAIR && p.coll.mode) ? p.coll.helper_ctas : 0;
+  const int helpers = (!PAIR && (p.coll.mode == 1 || p.coll.mode == 3)) ? p.coll.helper_ctas : 0;
   if (!PAIR && static_cast<int>(blockIdx.x) < helpers) {
     if (p.coll.mode == 1) ag_copy_role(p);
 #ifdef TITB_GEMM_PARAM_GATHER
     else if (p.coll.mode == 3) param_gather_role(p);
 #endif
-    else rs_reduce_role(p, (p.N + BN - 1) / BN);
     return;
   }
   // a pair walks the tile list as one unit
@@ -613,7 +631,74 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       if (PAIR) ptx::mbar_arrive_cluster(&acc_empty[b], 0);
       else ptx::mbar_arrive(&acc_empty[b]);
     };
-    if (p.tma_store == 2) {
+    if (p.coll.mode == 2) {
+      // GEMM -> reduce-scatter: the bf16 partial tile goes to slot [this rank] of the receive buffer of the rank that
+      // owns its rows.  64 columns at a time are staged in shared memory (two tiles, alternating) and copied out so
+      // that eight neighbouring lanes write one whole 128-byte row segment -- full NVLink write packets instead of one
+      // 16-byte piece per thread and row.  One release per tile tells the owner that the partial has been written.
+      const int trow = quad * 32 + lane;
+      const int tid = threadIdx.x - 64;                 // 0 .. 127 among the epilogue threads
+      const int crow = tid >> 3, cunit = tid & 7;       // copy-out: row within a group of 16, 16-byte unit of the row
+      for (int tile = cta; tile < num_tiles; tile += ncta, ++it) {
+        const TileCoord tc = tile_coord(p, tile, tiles_m, tiles_n, BN, kTileM, row_off);
+        const int m0 = tc.m0, n0 = tc.n0;
+        const int buf = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!ptx::mbar_wait(&acc_full[buf], acc_phase, abort_flag)) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * Cfg::kAccStride;
+        const int owner = m0 / p.coll.rows_per_rank;
+        const long long lrow0 = m0 - static_cast<long long>(owner) * p.coll.rows_per_rank;
+        bf16* slot = static_cast<bf16*>(p.coll.peers[owner]) +
+                     (static_cast<long long>(p.coll.rank) * p.coll.rows_per_rank + lrow0) * p.N;
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          const int col0 = n0 + c * 64;
+          const bool last = (c == BN / 64 - 1);
+          if (col0 < p.N) {
+            uint32_t r0[32], r1[32];
+            ptx::tmem_ld32(t_row + c * 64, r0);
+            ptx::tmem_ld32(t_row + c * 64 + 32, r1);
+            ptx::tmem_ld_wait();
+            uint8_t* stg = (c & 1) ? stage_aux : stage_out;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const uint32_t* r = u < 4 ? r0 : r1;
+              const int o = (u & 3) * 8;
+              *reinterpret_cast<uint4*>(stg + trow * 128 + ((u ^ (trow & 7)) << 4)) = make_uint4(
+                  pack_bf16x2(__uint_as_float(r[o]), __uint_as_float(r[o + 1])),
+                  pack_bf16x2(__uint_as_float(r[o + 2]), __uint_as_float(r[o + 3])),
+                  pack_bf16x2(__uint_as_float(r[o + 4]), __uint_as_float(r[o + 5])),
+                  pack_bf16x2(__uint_as_float(r[o + 6]), __uint_as_float(r[o + 7])));
+            }
+          }
+          if (last) {  // accumulator fully read: the MMA warp may reuse this TMEM buffer
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) release_acc(buf);
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (col0 < p.N && col0 + cunit * 8 < p.N) {
+            const uint8_t* stg = (c & 1) ? stage_aux : stage_out;
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              const int row = g * 16 + crow;
+              if (m0 + row < p.M)
+                *reinterpret_cast<uint4*>(slot + static_cast<long long>(row) * p.N + col0 + cunit * 8) =
+                    *reinterpret_cast<const uint4*>(stg + row * 128 + ((cunit ^ (row & 7)) << 4));
+            }
+          }
+        }
+        // every thread's stores of this tile are ordered before the one arrival that publishes it to the owner
+        __threadfence_system();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (tid == 0) {
+          const int chunk = static_cast<int>(lrow0 / kBM);
+          red_release_sys_add_u32(static_cast<uint32_t*>(p.coll.cnt_peers[owner]) + chunk, 1u);
+        }
+      }
+      rs_reduce_phase(p, tiles_n, cta, ncta, tid);
+    } else if (p.tma_store == 2) {
       // fp32 outputs (weight gradients): 32 columns at a time -> registers -> swizzled shared-memory tile -> one TMA
       // store, or one TMA reduce-add when the tile is a split-K partial or accumulates into the output.  The two
       // staging tiles alternate, so the copy of chunk c overlaps the staging of chunk c + 1.
@@ -844,7 +929,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       const long long row = m0 + quad * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * Cfg::kAccStride;
 #pragma unroll 1
-      for (int c = 0; c < (p.epi == 101 ? 0 : BN / 32); ++c) {  // 101: timing probe without any epilogue work
+      for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
         ptx::tmem_ld32(t_row + c * 32, r);
         ptx::tmem_ld_wait();
@@ -853,39 +938,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
           float v[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-          if (p.coll.mode == 2) {
-            // partial tile -> slot [this rank] of the owning rank's receive buffer (peer store)
-            const int owner = static_cast<int>(row / p.coll.rows_per_rank);
-            const long long lrow = row - static_cast<long long>(owner) * p.coll.rows_per_rank;
-            bf16* dst = static_cast<bf16*>(p.coll.peers[owner]) +
-                        (static_cast<long long>(p.coll.rank) * p.coll.rows_per_rank + lrow) * p.N + col0;
-            const int ncols = min(32, p.N - col0);
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              if (j < ncols)
-                *reinterpret_cast<uint4*>(dst + j) =
-                    make_uint4(pack_bf16x2(v[j], v[j + 1]), pack_bf16x2(v[j + 2], v[j + 3]),
-                               pack_bf16x2(v[j + 4], v[j + 5]), pack_bf16x2(v[j + 6], v[j + 7]));
-            }
-          } else {
-            epilogue_row32(p, v, row, col0, split);
-          }
+          epilogue_row32(p, v, row, col0, split);
         }
       }
       ptx::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) release_acc(buf);
-      if (p.coll.mode == 2) {
-        // this warp's 32 rows of the tile are on their way: publish them to the owner (the owner
-        // expects four such arrivals per tile, one per epilogue warp)
-        __threadfence_system();
-        __syncwarp();
-        if (lane == 0) {
-          const int owner = m0 / p.coll.rows_per_rank;
-          const int chunk = (m0 - owner * p.coll.rows_per_rank) / kBM;
-          red_release_sys_add_u32(static_cast<uint32_t*>(p.coll.cnt_peers[owner]) + chunk, 1u);
-        }
-      }
     }
   }
 
@@ -1134,7 +1192,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_bf16_tcgen05_kernel<BN, PAIR>, ta, tb, tout, taux, args);
     return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
   }
-  const int helpers = args.coll.mode ? args.coll.helper_ctas : 0;
+  const int helpers = (args.coll.mode == 1 || args.coll.mode == 3) ? args.coll.helper_ctas : 0;
   int grid = tiles + helpers < device_sm_count() ? tiles + helpers : device_sm_count();
   if (grid <= helpers) return TITB_ERR_SHAPE;
   gemm_bf16_tcgen05_kernel<BN, PAIR><<<grid, kGemmThreads, Cfg::kSmem, stream>>>(ta, tb, tout, taux, args);
@@ -1245,7 +1303,7 @@ TITB_API int TITB_GEMM_ENTRY(const TitbGemmDesc* d, cudaStream_t stream) {
   // bf16 results (and the GELU pre-activation) leave through TMA stores when their layout allows it
   CUtensorMap tout = ta, taux = ta;  // placeholders when unused
   const bool out_tma_ok = !d->out_fp32 && !d->accumulate && splits == 1 && a.coll.mode != 2 &&
-                          !(reinterpret_cast<uintptr_t>(d->out) & 15) && !(d->ldo & 7) && (d->epilogue != 100 && d->epilogue != 101) &&
+                          !(reinterpret_cast<uintptr_t>(d->out) & 15) && !(d->ldo & 7) &&
                           (!d->aux_out || (!(reinterpret_cast<uintptr_t>(d->aux_out) & 15) && !(d->ld_aux_out & 7))) &&
                           (!d->aux_in || a.vec_ok) && (!d->bias || a.vec_ok) && g_no_tma_store == 0;
   if (out_tma_ok) {
@@ -1274,6 +1332,12 @@ TITB_API int TITB_GEMM_ENTRY(const TitbGemmDesc* d, cudaStream_t stream) {
            : (bn == 192) ? launch_gemm<192, false>(ta, tb, tout, taux, a, stream)
                          : launch_gemm<128, false>(ta, tb, tout, taux, a, stream);
   if (rc != 0) return rc;
+  if (a.coll.mode == 2) {
+    // every partial of this call has been counted when the kernel ends; the counters start the next call at zero
+    // (peers send that call's tiles only after a cross-GPU barrier that follows this memset in stream order)
+    cudaError_t e = cudaMemsetAsync(a.coll.flags, 0, sizeof(uint32_t) * (a.coll.rows_per_rank / kBM), stream);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
   if (splits > 1 && a.tma_store != 2) {
     const long long total = static_cast<long long>(d->M) * d->N;
     int blocks = static_cast<int>((total / 4 + 255) / 256);

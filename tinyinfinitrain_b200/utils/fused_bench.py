@@ -55,7 +55,7 @@ def main():
     dist.init_process_group("nccl", device_id=dev)
     _, tflops, src = peaks()
     nccl, fused = TPComm(dist.group.WORLD, "nccl"), TPComm(dist.group.WORLD, "fused")
-    M, C, F = a.tokens, a.d_model, a.ffn
+    M, Cd, F = a.tokens, a.d_model, a.ffn
     Ms = M // world
     out = []
 
@@ -72,19 +72,19 @@ def main():
 
     g = torch.Generator(device=dev).manual_seed(rank)
     # F1: all-gather -> GEMM (column parallel: QKV-like [C -> 3C/world... use FFN up 2F/world])
-    x_s = (torch.randn(Ms, C, device=dev, generator=g) * 0.5).bfloat16()
-    for name, N in (("ag_gemm_ffn_up", 2 * F // world), ("ag_gemm_qkv", 3 * C // world)):
-        w = (torch.randn(N, C, device=dev, generator=g) * 0.05).bfloat16()
+    x_s = (torch.randn(Ms, Cd, device=dev, generator=g) * 0.5).bfloat16()
+    for name, N in (("ag_gemm_ffn_up", 2 * F // world), ("ag_gemm_qkv", 3 * Cd // world)):
+        w = (torch.randn(N, Cd, device=dev, generator=g) * 0.05).bfloat16()
         ms_f = _time(lambda: fused.ag_gemm(x_s, w), a.iters)
         ms_n = _time(lambda: nccl.ag_gemm(x_s, w), a.iters)
-        report(name, ms_f, ms_n, 2.0 * M * N * C, (world - 1) * Ms * C * 2)
+        report(name, ms_f, ms_n, 2.0 * M * N * Cd, (world - 1) * Ms * Cd * 2)
     # F2: GEMM -> reduce-scatter (row parallel: FFN down [F/world -> C], attention out [C/world -> C])
-    for name, K in (("gemm_rs_ffn_down", F // world), ("gemm_rs_attn_out", C // world)):
+    for name, K in (("gemm_rs_ffn_down", F // world), ("gemm_rs_attn_out", Cd // world)):
         y = (torch.randn(M, K, device=dev, generator=g) * 0.5).bfloat16()
-        w = (torch.randn(C, K, device=dev, generator=g) * 0.05).bfloat16()
+        w = (torch.randn(Cd, K, device=dev, generator=g) * 0.05).bfloat16()
         ms_f = _time(lambda: fused.gemm_rs(y, w), a.iters)
         ms_n = _time(lambda: nccl.gemm_rs(y, w), a.iters)
-        report(name, ms_f, ms_n, 2.0 * M * C * K, (world - 1) * Ms * C * 2)
+        report(name, ms_f, ms_n, 2.0 * M * Cd * K, (world - 1) * Ms * Cd * 2)
     # F3: gradient reduce-scatter + Adam + parameter all-gather
     n = a.params_m * 1000 * 1000
     res = {}
@@ -107,7 +107,7 @@ def main():
     from .._lib import C
     from ..parallel.param_gather import GatheredWeightLinear
 
-    for name, (N, K) in (("param_gather_gemm_ffn_up", (F, C)), ("param_gather_gemm_attn_out", (C, C))):
+    for name, (N, K) in (("param_gather_gemm_ffn_up", (F, Cd)), ("param_gather_gemm_attn_out", (Cd, Cd))):
         if N % (128 * world):
             continue
         layer = GatheredWeightLinear(K, N, bias=False, device=dev)
