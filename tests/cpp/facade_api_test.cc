@@ -113,6 +113,31 @@ static void TestTensorAutograd() {
   EXPECT(near(V(1.f / T({2.f, 4.f}, {2})), {0.5f, 0.25f}, 0.f));
 }
 
+// Tensor::Uniform(from, to, generator) and the static Tensor::SetPrintOptions of the reference's tensor.h:124,151.
+static void TestUniformAndPrintOptions() {
+  auto a = std::make_shared<Tensor>(std::vector<int64_t>{4, 5}, DataType::kFLOAT32, g_dev);
+  auto b = std::make_shared<Tensor>(std::vector<int64_t>{4, 5}, DataType::kFLOAT32, g_dev);
+  std::mt19937 gen(7);
+  auto ra = a->Uniform(-2.f, 3.f, gen);
+  b->Uniform(-2.f, 3.f, gen);                     // the generator is copied: same seed, same values
+  EXPECT(ra.get() == a.get());
+  const auto va = V(a), vb = V(b);
+  EXPECT(near(va, vb, 0.f));
+  bool in_range = true, varied = false;
+  for (float x : va) {
+    in_range = in_range && x >= -2.f && x < 3.f;
+    varied = varied || x != va[0];
+  }
+  EXPECT(in_range && varied);
+  std::mt19937 expect(7);
+  std::uniform_real_distribution<float> dist(-2.f, 3.f);
+  EXPECT(std::fabs(va[0] - dist(expect)) == 0.f);  // libstdc++ stream, element order = memory order
+  Tensor::SetPrintOptions(2, std::nullopt, std::nullopt, 120);
+  EXPECT(PrintOptions::Get().precision == 2 && PrintOptions::Get().linewidth == 120);
+  Tensor::SetPrintOptions(std::nullopt, std::nullopt, std::nullopt, std::nullopt, std::string("default"));
+  EXPECT(PrintOptions::Get().precision == 4 && PrintOptions::Get().linewidth == 80);
+}
+
 static void CounterKernel(int* c) { ++*c; }
 static int AddKernel(int a, int b) { return a + b; }
 static void TestDispatcher() {
@@ -201,6 +226,7 @@ int main(int argc, char** argv) {
     TestAdam();
     TestTensorAutograd();
     TestDispatcher();
+    TestUniformAndPrintOptions();
     TestDataAndTraining(dir);
   } catch (const std::exception& e) {
     std::printf("EXCEPTION: %s\n", e.what());

@@ -95,6 +95,66 @@ def test_norm_fork_folds_the_residual_gradient(monkeypatch):
     _status_ok()
 
 
+@pytest.mark.parametrize("dtype", [BF, torch.float32])
+def test_vocab_parallel_embedding_push_and_pull(dtype):
+    """The push / pull kernels of the row-split embedding table, with four local buffers standing in for the four
+    ranks' token shards: every row arrives exactly once (stale rows are NaN, so a row nobody wrote cannot pass), ids
+    outside the vocabulary give zero rows, and the pulled gradient equals the dense scatter-add."""
+    torch.manual_seed(8)
+    world, Ms, Cd, Vl = 4, 96, 256, 50
+    M, V = world * Ms, world * Vl
+    table = torch.randn(V, Cd, device=DEV).to(dtype)
+    idx = torch.randint(0, V, (M,), device=DEV)
+    idx[5], idx[M - 1] = V + 3, -1                                  # strays
+    shards = [torch.full((Ms, Cd), float("nan"), device=DEV, dtype=dtype) for _ in range(world)]
+    ptrs = [t.data_ptr() for t in shards]
+    for r in range(world):
+        C.embedding_vp_push(idx, table[r * Vl:(r + 1) * Vl].contiguous(), ptrs, Ms, r * Vl, V, r == 0)
+    got = torch.cat(shards, 0)
+    ok = (idx >= 0) & (idx < V)
+    ref = torch.where(ok.unsqueeze(1), table[idx.clamp(0, V - 1)], torch.zeros((), device=DEV, dtype=dtype))
+    assert torch.equal(got, ref)
+    dx = [torch.randn(Ms, Cd, device=DEV).to(dtype) for _ in range(world)]
+    dref = torch.zeros(V, Cd, device=DEV)
+    dref.index_add_(0, idx[ok], torch.cat(dx, 0).float()[ok])
+    for r in range(world):
+        dw = torch.zeros(Vl, Cd, device=DEV)
+        C.embedding_vp_pull_bwd(idx, [t.data_ptr() for t in dx], dw, Ms, r * Vl, dx[0])
+        assert (dw - dref[r * Vl:(r + 1) * Vl]).abs().max().item() < 1e-4
+    _status_ok()
+
+
+@pytest.mark.parametrize("rms", [False, True])
+def test_norm_fork_writes_into_a_caller_buffer(rms):
+    """`fork(x, out=buf)`: the normalised rows land in `buf` (the input slot of a collective in the tensor-parallel
+    blocks), values and gradients equal those of the call that allocates its own output, and `buf` itself gains no
+    autograd history."""
+    torch.manual_seed(4)
+    M, Cd = 384, 768
+    x = torch.randn(M, Cd, device=DEV).to(BF)
+    w = (1 + 0.1 * torch.randn(Cd, device=DEV)).to(BF)
+    b = (0.1 * torch.randn(Cd, device=DEV)).to(BF)
+    dy = torch.randn(M, Cd, device=DEV).to(BF)
+    res = []
+    buf = torch.full((M, Cd), float("nan"), device=DEV, dtype=BF)
+    for out in (None, buf):
+        xr = x.clone().requires_grad_(True)
+        wr = w.clone().requires_grad_(True)
+        if rms:
+            y, alias = ops.rmsnorm_fork(xr, wr, 1e-5, out=out)
+        else:
+            y, alias = ops.layernorm_fork(xr, wr, b, 1e-5, out=out)
+        (y.float() * dy.float()).sum().add(alias.float().sum()).backward()
+        res.append((y.detach().clone(), xr.grad.clone(), wr.grad.clone()))
+        if out is not None:
+            assert y.data_ptr() == buf.data_ptr()
+    assert buf.grad_fn is None and not buf.requires_grad
+    assert torch.equal(buf, res[0][0])
+    for a, c in zip(res[0], res[1]):
+        assert torch.equal(a, c)
+    _status_ok()
+
+
 @pytest.mark.parametrize("B,T,Hq,Hkv,hd", [(2, 128, 2, 2, 64), (2, 200, 3, 3, 64), (1, 384, 4, 2, 128), (1, 1024, 2, 2, 64),
                                            (1, 130, 8, 2, 64), (1, 4096, 8, 2, 128), (1, 4096, 4, 4, 64), (2, 2048, 4, 1, 64)])
 def test_attention_pipelines_forward_and_backward(B, T, Hq, Hkv, hd):

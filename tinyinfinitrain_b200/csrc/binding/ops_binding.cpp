@@ -223,11 +223,20 @@ Tensor sgemm(const Tensor& a, const Tensor& b, bool ta, bool tb, const optional<
 }
 
 // ---------------------------------------------------------------------- norms
-std::vector<Tensor> layernorm_fwd(const Tensor& x, const Tensor& w, const Tensor& b, double eps) {
+// `out`: where the normalised rows go (same shape and dtype as x, contiguous); a caller that feeds the result to a
+// collective passes a view of its symmetric buffer here, which saves the staging copy.
+static Tensor norm_out(const Tensor& x, const c10::optional<Tensor>& out) {
+  if (!out.has_value()) return at::empty_like(x);
+  TORCH_CHECK(out->is_cuda() && out->is_contiguous() && out->scalar_type() == x.scalar_type() &&
+              out->numel() == x.numel(), "norm: out must be a contiguous CUDA tensor of x's size and dtype");
+  return out->detach();   // a fresh handle on the same memory, so autograd metadata never lands on the caller's tensor
+}
+std::vector<Tensor> layernorm_fwd(const Tensor& x, const Tensor& w, const Tensor& b, double eps,
+                                  const c10::optional<Tensor>& out) {
   check_cuda(x, "x"); check_cuda(w, "weight"); check_cuda(b, "bias");
   c10::cuda::CUDAGuard guard(x.device());
   const int64_t C = x.size(-1), rows = x.numel() / C;
-  Tensor y = at::empty_like(x);
+  Tensor y = norm_out(x, out);
   Tensor mean = at::empty({rows}, x.options().dtype(at::kFloat)), rstd = at::empty_like(mean);
   CHECK_RC(titb_layernorm_fwd(x.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(), mean.data_ptr<float>(),
                               rstd.data_ptr<float>(), rows, (int)C, (float)eps, dt_code(x), cur_stream()),
@@ -262,11 +271,11 @@ std::vector<Tensor> layernorm_bwd(const Tensor& dy, const Tensor& x, const Tenso
            "layernorm_bwd", 2);
   return {dx, dw, db};
 }
-std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const Tensor& w, double eps) {
+std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const Tensor& w, double eps, const c10::optional<Tensor>& out) {
   check_cuda(x, "x"); check_cuda(w, "weight");
   c10::cuda::CUDAGuard guard(x.device());
   const int64_t C = x.size(-1), rows = x.numel() / C;
-  Tensor y = at::empty_like(x);
+  Tensor y = norm_out(x, out);
   Tensor rstd = at::empty({rows}, x.options().dtype(at::kFloat));
   CHECK_RC(titb_rmsnorm_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr<float>(), rows, (int)C,
                             (float)eps, dt_code(x), cur_stream()), "rmsnorm_fwd");
@@ -385,6 +394,31 @@ void embedding_bwd(const Tensor& idx, const Tensor& dout, const optional<Tensor>
   CHECK_RC(titb_embedding_bwd((const long long*)idx.data_ptr<int64_t>(), dout.data_ptr(), pw, pp, BT, (int)T, (int)C,
                               (int)vocab_lo, (int)std::min<int64_t>(vocab_hi, INT32_MAX), dt_code(dout), cur_stream()),
            "embedding_bwd");
+}
+// Vocabulary-parallel table, forward: rows of `w` (this rank's slice [vocab_lo, vocab_lo + w.size(0))) go to the
+// [Ms, C] token-shard buffers behind dst_ptrs (one address per rank).  Barriers are the caller's.
+void embedding_vp_push(const Tensor& idx, const Tensor& w, const std::vector<int64_t>& dst_ptrs, int64_t rows_per_rank,
+                       int64_t vocab_lo, int64_t vocab_total, bool zero_strays) {
+  check_cuda(idx, "idx"); check_cuda(w, "weight");
+  TORCH_CHECK(idx.scalar_type() == at::kLong && idx.is_contiguous() && w.is_contiguous() && w.dim() == 2);
+  c10::cuda::CUDAGuard guard(w.device());
+  std::vector<unsigned long long> d(dst_ptrs.begin(), dst_ptrs.end());
+  CHECK_RC(titb_embedding_vp_push((const long long*)idx.data_ptr<int64_t>(), w.data_ptr(), d.data(), (int)d.size(),
+                                  idx.numel(), rows_per_rank, (int)w.size(1), vocab_lo, vocab_lo + w.size(0),
+                                  vocab_total, zero_strays ? 1 : 0, dt_code(w), cur_stream()), "embedding_vp_push");
+}
+// Backward: gradient rows of the ids in this rank's slice, pulled from the token owners' [Ms, C] buffers (dtype of
+// `like`) and added to dw (fp32 [rows of the slice, C]).
+void embedding_vp_pull_bwd(const Tensor& idx, const std::vector<int64_t>& src_ptrs, const Tensor& dw,
+                           int64_t rows_per_rank, int64_t vocab_lo, const Tensor& like) {
+  check_cuda(idx, "idx"); check_cuda(dw, "dw");
+  TORCH_CHECK(idx.scalar_type() == at::kLong && idx.is_contiguous() && dw.scalar_type() == at::kFloat &&
+              dw.is_contiguous() && dw.dim() == 2);
+  c10::cuda::CUDAGuard guard(dw.device());
+  std::vector<unsigned long long> s(src_ptrs.begin(), src_ptrs.end());
+  CHECK_RC(titb_embedding_vp_pull_bwd((const long long*)idx.data_ptr<int64_t>(), s.data(), (int)s.size(),
+                                      dw.data_ptr<float>(), idx.numel(), rows_per_rank, (int)dw.size(1), vocab_lo,
+                                      vocab_lo + dw.size(0), dt_code(like), cur_stream()), "embedding_vp_pull_bwd");
 }
 
 // ------------------------------------------------------- softmax / cross entropy
@@ -728,11 +762,12 @@ PYBIND11_MODULE(_C, m) {
   m.def("outer_bwd", &outer_bwd);
   m.def("sgemm", &sgemm, py::arg("a"), py::arg("b"), py::arg("ta") = false, py::arg("tb") = false,
         py::arg("out") = py::none(), py::arg("accumulate") = false);
-  m.def("layernorm_fwd", &layernorm_fwd);
+  m.def("layernorm_fwd", &layernorm_fwd, py::arg("x"), py::arg("weight"), py::arg("bias"), py::arg("eps"),
+        py::arg("out") = py::none());
   m.def("layernorm_bwd", &layernorm_bwd, py::arg("dy"), py::arg("x"), py::arg("w"), py::arg("mean"), py::arg("rstd"),
         py::arg("dw") = py::none(), py::arg("db") = py::none(), py::arg("accumulate") = false,
         py::arg("dres") = py::none());
-  m.def("rmsnorm_fwd", &rmsnorm_fwd);
+  m.def("rmsnorm_fwd", &rmsnorm_fwd, py::arg("x"), py::arg("weight"), py::arg("eps"), py::arg("out") = py::none());
   m.def("rmsnorm_bwd", &rmsnorm_bwd, py::arg("dy"), py::arg("x"), py::arg("w"), py::arg("rstd"),
         py::arg("dw") = py::none(), py::arg("accumulate") = false,
         py::arg("dres") = py::none());
@@ -748,6 +783,8 @@ PYBIND11_MODULE(_C, m) {
   m.def("embedding_bwd", &embedding_bwd, py::arg("idx"), py::arg("dout"), py::arg("dwte") = py::none(),
         py::arg("dwpe") = py::none(), py::arg("vocab_lo") = 0, py::arg("vocab_hi") = (int64_t)1 << 40,
         py::arg("deterministic") = false);
+  m.def("embedding_vp_push", &embedding_vp_push);
+  m.def("embedding_vp_pull_bwd", &embedding_vp_pull_bwd);
   m.def("softmax_fwd", &softmax_fwd);
   m.def("softmax_bwd", &softmax_bwd);
   m.def("xent_fused", &xent_fused, py::arg("logits"), py::arg("targets"), py::arg("V"), py::arg("grad_scale"),

@@ -121,10 +121,25 @@ std::vector<float> Tensor::ToFloatVector() const {
   return std::vector<float>(c.data_ptr<float>(), c.data_ptr<float>() + c.numel());
 }
 
-void Tensor::Uniform(float lo, float hi) {
+std::shared_ptr<Tensor> Tensor::Uniform(float from, float to, std::optional<std::mt19937> generator) {
   at::Tensor h = at::empty(dims_, at::kFloat);
-  titb::rng::fill_uniform(h.data_ptr<float>(), h.numel(), lo, hi, std::nullopt);
+  float* p = h.data_ptr<float>();
+  const int64_t n = h.numel();
+  if (generator.has_value()) {
+    std::mt19937 g = *generator;                       // a copy: the caller's generator does not advance
+    std::uniform_real_distribution<float> dist(from, to);
+    for (int64_t i = 0; i < n; ++i) p[i] = dist(g);
+  } else {
+    titb::rng::fill_uniform(p, n, from, to, std::nullopt);
+  }
   data_.copy_(h);
+  return shared_from_this();
+}
+void Tensor::SetPrintOptions(std::optional<int64_t> precision, std::optional<int64_t> threshold, std::optional<int64_t> edge_items,
+                             std::optional<int64_t> linewidth, std::optional<std::string> profile, std::optional<bool> sci_mode) {
+  infini_train::SetPrintOptions(precision ? static_cast<int>(*precision) : -1, threshold ? static_cast<int>(*threshold) : -1,
+                                edge_items ? static_cast<int>(*edge_items) : -1, linewidth ? static_cast<int>(*linewidth) : -1,
+                                profile ? *profile : std::string(), sci_mode ? (*sci_mode ? 1 : 0) : -1);
 }
 
 // ---------------------------------------------------------------------------------- autograd fields

@@ -14,6 +14,8 @@
 #include <cstdint>
 #include <iostream>
 #include <memory>
+#include <optional>
+#include <random>
 #include <string>
 #include <vector>
 
@@ -113,7 +115,14 @@ class Tensor : public std::enable_shared_from_this<Tensor> {
   std::shared_ptr<Tensor> Matmul(const std::shared_ptr<Tensor>& other);
   std::shared_ptr<Tensor> Outer(const std::shared_ptr<Tensor>& other);
   std::shared_ptr<Tensor> MaskedFill(const std::shared_ptr<Tensor>& mask, float value);
-  void Uniform(float lo = 0.f, float hi = 1.f);
+  // Fills the tensor with U[from, to) drawn on the host (libstdc++ uniform_real_distribution over std::mt19937) and
+  // returns it; `generator` is copied, as in the reference (infini_train/include/tensor.h:124), so the same seeded
+  // generator gives the same values on every call.  Without one a process-wide generator advances.
+  std::shared_ptr<Tensor> Uniform(float from = 0.f, float to = 1.f, std::optional<std::mt19937> generator = std::nullopt);
+  // Same options as torch.set_printoptions; unset arguments keep their value (reference tensor.h:151-153).
+  static void SetPrintOptions(std::optional<int64_t> precision = std::nullopt, std::optional<int64_t> threshold = std::nullopt,
+                              std::optional<int64_t> edge_items = std::nullopt, std::optional<int64_t> linewidth = std::nullopt,
+                              std::optional<std::string> profile = std::nullopt, std::optional<bool> sci_mode = std::nullopt);
 
   // ---- autograd ---------------------------------------------------------------------------------
   std::shared_ptr<Tensor> RequiresGrad();

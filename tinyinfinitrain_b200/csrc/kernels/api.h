@@ -147,6 +147,19 @@ TITB_API int titb_embedding_fwd(const long long* idx, const void* wte, const voi
 // dwte[idx[b,t],:] += dout[b,t,:] ; dwpe[t,:] += sum_b dout[b,t,:].  fp32 gradient buffers.
 TITB_API int titb_embedding_bwd(const long long* idx, const void* dout, float* dwte, float* dwpe, long long BT,
                                 int T, int C, int vocab_lo, int vocab_hi, int dtype, cudaStream_t stream);
+// Vocabulary-parallel table: this rank holds rows [vocab_lo, vocab_hi) of the table; the M = world * Ms tokens are
+// split by position, rank r owning tokens [r * Ms, (r + 1) * Ms).  `push` stores the rows this rank holds into the
+// [Ms, C] buffer of each token's owner (dst_ptrs[r], 16-byte aligned, local or peer-mapped memory; world <= 16); with
+// zero_strays != 0 it also writes zero rows for ids outside [0, vocab_total).  Across the ranks every destination row
+// is written exactly once, so no reduction follows; the caller puts a cross-rank barrier before (destinations free)
+// and after (all rows landed) the launch.  `pull_bwd` is the transpose: gradient rows of the ids this rank holds are
+// read from the token owners' [Ms, C] buffers (src_ptrs) and added to dw [vocab_hi - vocab_lo, C] fp32 with atomics.
+TITB_API int titb_embedding_vp_push(const long long* idx, const void* w, const unsigned long long* dst_ptrs, int world,
+                                    long long M, long long Ms, int C, long long vocab_lo, long long vocab_hi,
+                                    long long vocab_total, int zero_strays, int dtype, cudaStream_t stream);
+TITB_API int titb_embedding_vp_pull_bwd(const long long* idx, const unsigned long long* src_ptrs, int world, float* dw,
+                                        long long M, long long Ms, int C, long long vocab_lo, long long vocab_hi,
+                                        int dtype, cudaStream_t stream);
 
 // Deterministic variant of the token part (dwte only): the keys (row, position) of one step are sorted in the shared
 // memory of one block and every run of equal rows is summed in position order, no atomics.  BT must not exceed

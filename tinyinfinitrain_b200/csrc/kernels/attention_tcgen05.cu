@@ -841,7 +841,7 @@ static int attn_bwd_launch(const TitbAttnDesc* d, cudaStream_t st) {
     return TITB_ERR_TENSOR_MAP;
   const long long nrows = static_cast<long long>(d->B) * d->T * d->Hq;
   int blocks = static_cast<int>((nrows + 255) / 256);
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks > device_sm_count() * 8) blocks = device_sm_count() * 8;
   attn_delta_kernel<<<blocks, 256, 0, st>>>(static_cast<const bf16*>(d->d_o), static_cast<const bf16*>(d->o), d->delta,
                                             d->B, d->T, d->Hq, HD, d->do_stride_t, d->o_stride_t);
   cudaError_t e = cudaMemsetAsync(d->dq_accum, 0, sizeof(float) * nrows * HD, st);
@@ -858,7 +858,7 @@ static int attn_bwd_launch(const TitbAttnDesc* d, cudaStream_t st) {
   const long long bt = static_cast<long long>(d->B) * d->T;
   const int width = d->Hq * HD;
   int cb = static_cast<int>((bt * (width / 8) + 255) / 256);
-  if (cb > 148 * 8) cb = 148 * 8;
+  if (cb > device_sm_count() * 8) cb = device_sm_count() * 8;
   attn_dq_convert_kernel<<<cb, 256, 0, st>>>(d->dq_accum, static_cast<bf16*>(d->dq), bt, width, d->dq_stride_t);
   return static_cast<int>(cudaGetLastError());
 }

@@ -153,7 +153,7 @@ __global__ void wait_kernel(const uint32_t* local_word, uint32_t value, long lon
 
 static int coll_blocks(long long vecs, int max_blocks) {
   long long b = (vecs + 255) / 256;
-  const int cap = max_blocks > 0 ? max_blocks : 148 * 2;
+  const int cap = max_blocks > 0 ? max_blocks : device_sm_count() * 2;
   if (b > cap) b = cap;
   return b < 1 ? 1 : (int)b;
 }

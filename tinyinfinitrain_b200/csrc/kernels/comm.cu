@@ -235,7 +235,7 @@ TITB_API int titb_rs_adam_ag(const TitbRsAdamDesc* d, cudaStream_t st) {
   a.bc1 = d->bc1; a.bc2 = d->bc2; a.gscale = d->grad_scale; a.dev_state = d->dev_state;
   long long nvec = d->shard_n / 8;
   int blocks = (int)((nvec + 255) / 256);
-  const int cap = d->max_blocks > 0 ? d->max_blocks : 148 * 4;
+  const int cap = d->max_blocks > 0 ? d->max_blocks : device_sm_count() * 4;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   rs_adam_ag_kernel<<<blocks, 256, 0, st>>>(a);

@@ -18,6 +18,16 @@ enum StatusCode : int {
   kStatusBadShape = 3,
 };
 
+// Number of SMs of the current device (cached per device); grid sizes and per-SM partial buffers derive from it.
+inline int device_sm_count() {
+  static int sms[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (sms[dev] == 0) cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
+  return sms[dev] > 0 ? sms[dev] : 148;
+}
+
 template <typename T>
 struct alignas(16) Vec8 {  // eight 16-bit values = one 128-bit transaction
   T v[8];

@@ -1050,15 +1050,6 @@ bool make_tmap_f32_2d(CUtensorMap* m, const void* base, uint64_t inner, uint64_t
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-int device_sm_count() {
-  static int sms[64] = {0};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) dev = 0;
-  if (sms[dev] == 0) cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
-  return sms[dev] > 0 ? sms[dev] : 148;
-}
-
 static int g_no_tma_store = 0;  // set by titb_gemm_set_tma_store(0): A/B switch for the epilogue store path
 
 // Estimated duration of a GEMM for a tile width and a split-K factor, in units of one k-block (64 deep) of a
@@ -1341,7 +1332,7 @@ TITB_API int TITB_GEMM_ENTRY(const TitbGemmDesc* d, cudaStream_t stream) {
   if (splits > 1 && a.tma_store != 2) {
     const long long total = static_cast<long long>(d->M) * d->N;
     int blocks = static_cast<int>((total / 4 + 255) / 256);
-    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks > device_sm_count() * 8) blocks = device_sm_count() * 8;
     if (d->out_fp32)
       splitk_reduce_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<const float*>(d->workspace),
                                                                static_cast<float*>(d->out), d->M, d->N, d->ldo,

@@ -480,8 +480,10 @@ __global__ void norm_bwd_dw_generic(const T* dy, const T* x, const float* mean_i
   if (!RMS && db) db[c] = accumulate ? db[c] + sb : sb;
 }
 
-constexpr int kNormBwdBlocks = 148 * 2;  // CTAs of the warp-per-row backward kernel
-constexpr int kNormBwdParts = 148 * 4;   // partial rows per gradient in the scratch buffer (upper bound)
+// Sizes of the caller-provided scratch, fixed so that callers (and the allocation-free entry point) can size it without
+// a device query; grids are derived from the SM count of the device and clamped to these.
+constexpr int kNormBwdBlocks = 296;  // most CTAs the warp-per-row backward kernels launch
+constexpr int kNormBwdParts = 592;   // partial rows per gradient in the scratch buffer
 
 struct NormPlan {
   int G;      // 32 or 256; 0 = generic fallback
@@ -521,7 +523,6 @@ static int norm_fwd_launch(const void* x, const void* w, const void* b, void* y,
   return (int)cudaGetLastError();
 }
 
-int device_sm_count();
 
 template <typename T, bool RMS>
 static int norm_bwd_launch(const void* dy, const void* x, const void* w, const void* dres, const float* mean,

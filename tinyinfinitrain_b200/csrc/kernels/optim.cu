@@ -89,7 +89,8 @@ __global__ void axpy_kernel(float* __restrict__ y, const X* __restrict__ x, floa
 
 static inline int blocks_for(long long n) {
   long long b = (n + 255) / 256;
-  return (int)(b < 1 ? 1 : (b > 148 * 8 ? 148 * 8 : b));
+  const long long cap = device_sm_count() * 8;
+  return (int)(b < 1 ? 1 : (b > cap ? cap : b));
 }
 
 }  // namespace titb

@@ -12,7 +12,6 @@
 namespace titb {
 
 constexpr int kEwThreads = 256;
-int device_sm_count();
 
 static inline int ew_blocks(long long nvec) {
   long long b = (nvec + kEwThreads - 1) / kEwThreads;
@@ -217,7 +216,7 @@ __global__ void tri_kernel(const T* __restrict__ x, T* __restrict__ y, int R, in
 }
 
 // Column sums of a [rows, C] matrix in two deterministic stages (bias gradients).
-constexpr int kColsumParts = 148 * 2;
+constexpr int kColsumParts = 296;  // partial rows in the caller-provided scratch; the grid is sized from the SM count and clamped to it
 // Stage 1: a warp reads whole row segments (coalesced), four rows in flight, and keeps the sums of its NV * VN
 // columns per lane in registers; the 8 warps of a CTA fold their sums in warp order through shared memory and the
 // CTA writes one partial row.  blockIdx.y selects a strip of 32 * NV * VN columns.

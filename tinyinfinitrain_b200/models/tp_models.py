@@ -163,6 +163,7 @@ class TPBlock(nn.Module):
 
     def __init__(self, cfg, comm, device=None, dtype=torch.float32):
         super().__init__()
+        self.comm = comm
         llama = isinstance(cfg, LLaMA3Config)
         if llama:
             self.ln_1 = nn.RMSNorm(cfg.n_embd, cfg.norm_eps, device=device, dtype=dtype)
@@ -179,9 +180,10 @@ class TPBlock(nn.Module):
                 tpl._mark_sp(p)
 
     def forward(self, x_s, B: int, T: int):
-        h_s, x_s = self.ln_1.fork(x_s)
+        # the norms write straight into the input slot of the all-gather -> GEMM kernel that consumes them
+        h_s, x_s = self.ln_1.fork(x_s, out=self.comm.ag_input(x_s))
         x_s = self.attn(h_s, B, T, residual_s=x_s)
-        h_s, x_s = self.ln_2.fork(x_s)
+        h_s, x_s = self.ln_2.fork(x_s, out=self.comm.ag_input(x_s))
         x_s = self.mlp(h_s, residual_s=x_s)
         return x_s
 

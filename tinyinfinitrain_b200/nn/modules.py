@@ -78,9 +78,10 @@ class LayerNorm(Module):
     def forward(self, x):
         return ops.layernorm(x, self.weight, self.bias, self.eps)
 
-    def fork(self, x):
-        """(self(x), x) for a pre-norm residual block: pass the second value to the residual connection."""
-        return ops.layernorm_fork(x, self.weight, self.bias, self.eps)
+    def fork(self, x, out=None):
+        """(self(x), x) for a pre-norm residual block: pass the second value to the residual connection.  ``out``
+        (optional) receives the normalised rows, see ``ops.layernorm_fork``."""
+        return ops.layernorm_fork(x, self.weight, self.bias, self.eps, out=out)
 
 
 class RMSNorm(Module):
@@ -95,9 +96,10 @@ class RMSNorm(Module):
     def forward(self, x):
         return ops.rmsnorm(x, self.weight, self.eps)
 
-    def fork(self, x):
-        """(self(x), x) for a pre-norm residual block: pass the second value to the residual connection."""
-        return ops.rmsnorm_fork(x, self.weight, self.eps)
+    def fork(self, x, out=None):
+        """(self(x), x) for a pre-norm residual block: pass the second value to the residual connection.  ``out``
+        (optional) receives the normalised rows, see ``ops.layernorm_fork``."""
+        return ops.rmsnorm_fork(x, self.weight, self.eps, out=out)
 
 
 class CrossEntropyLoss(Module):

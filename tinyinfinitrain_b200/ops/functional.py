@@ -250,9 +250,9 @@ class _LayerNormFn(torch.autograd.Function):
     receives the residual gradient as a second argument and adds it inside the norm kernel."""
 
     @staticmethod
-    def forward(ctx, x, w, b, eps, fork=False):
+    def forward(ctx, x, w, b, eps, fork=False, out=None):
         xc = x.contiguous()
-        y, mean, rstd = C.layernorm_fwd(xc, w, b, eps)
+        y, mean, rstd = C.layernorm_fwd(xc, w, b, eps, out=out[0] if out else None)
         ctx.save_for_backward(xc, w, mean, rstd)
         ctx.w, ctx.b, ctx.fork = w, b, fork
         ctx.set_materialize_grads(False)                 # an unused output arrives as None, not as a zero tensor
@@ -262,7 +262,7 @@ class _LayerNormFn(torch.autograd.Function):
     def backward(ctx, dy, dres=None):
         x, w, mean, rstd = ctx.saved_tensors
         if dy is None:                                   # only the residual alias was used
-            return dres, None, None, None, None
+            return dres, None, None, None, None, None
         dy = dy.contiguous()
         wmg, wacc = _grad_target(ctx.w)
         bmg, _ = _grad_target(ctx.b)
@@ -271,9 +271,9 @@ class _LayerNormFn(torch.autograd.Function):
                                        dres=dres)
             _grad_done(ctx.w)
             _grad_done(ctx.b)
-            return dx, None, None, None, None
+            return dx, None, None, None, None, None
         dx, dw, db = C.layernorm_bwd(dy, x, w, mean, rstd, dres=dres)
-        return dx, dw.to(w.dtype), db.to(w.dtype), None, None
+        return dx, dw.to(w.dtype), db.to(w.dtype), None, None, None
 
 
 def layernorm(x, weight, bias, eps: float = 1e-5):
@@ -282,20 +282,21 @@ def layernorm(x, weight, bias, eps: float = 1e-5):
     return _LayerNormFn.apply(x, weight, bias, eps, False)
 
 
-def layernorm_fork(x, weight, bias, eps: float = 1e-5):
+def layernorm_fork(x, weight, bias, eps: float = 1e-5, out=None):
     """(LayerNorm(x), x): use the second value for the residual connection around the normalised branch.  On CUDA the
     gradient that comes back through the residual is added inside the norm's backward kernel instead of by a
-    separate add."""
+    separate add.  ``out``: a contiguous CUDA tensor of x's size and dtype that receives the normalised rows (the
+    input slot of a collective, for instance); nothing may keep a reference to its previous contents."""
     if not x.is_cuda:
         return layernorm(x, weight, bias, eps), x
-    return _LayerNormFn.apply(x, weight, bias, eps, True)
+    return _LayerNormFn.apply(x, weight, bias, eps, True, (out,) if out is not None else None)
 
 
 class _RMSNormFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, eps, fork=False):
+    def forward(ctx, x, w, eps, fork=False, out=None):
         xc = x.contiguous()
-        y, rstd = C.rmsnorm_fwd(xc, w, eps)
+        y, rstd = C.rmsnorm_fwd(xc, w, eps, out=out[0] if out else None)
         ctx.save_for_backward(xc, w, rstd)
         ctx.w, ctx.fork = w, fork
         ctx.set_materialize_grads(False)
@@ -305,15 +306,15 @@ class _RMSNormFn(torch.autograd.Function):
     def backward(ctx, dy, dres=None):
         x, w, rstd = ctx.saved_tensors
         if dy is None:
-            return dres, None, None, None
+            return dres, None, None, None, None
         dy = dy.contiguous()
         wmg, wacc = _grad_target(ctx.w)
         if wmg is not None:
             dx, _ = C.rmsnorm_bwd(dy, x, w, rstd, dw=wmg, accumulate=wacc, dres=dres)
             _grad_done(ctx.w)
-            return dx, None, None, None
+            return dx, None, None, None, None
         dx, dw = C.rmsnorm_bwd(dy, x, w, rstd, dres=dres)
-        return dx, dw.to(w.dtype), None, None
+        return dx, dw.to(w.dtype), None, None, None
 
 
 def rmsnorm_ref(x, weight, eps):
@@ -327,11 +328,11 @@ def rmsnorm(x, weight, eps: float = 1e-5):
     return _RMSNormFn.apply(x, weight, eps, False)
 
 
-def rmsnorm_fork(x, weight, eps: float = 1e-5):
+def rmsnorm_fork(x, weight, eps: float = 1e-5, out=None):
     """(RMSNorm(x), x); see layernorm_fork."""
     if not x.is_cuda:
         return rmsnorm(x, weight, eps), x
-    return _RMSNormFn.apply(x, weight, eps, True)
+    return _RMSNormFn.apply(x, weight, eps, True, (out,) if out is not None else None)
 
 
 # ------------------------------------------------------------------------ activations

@@ -61,10 +61,26 @@ class FusedTP:
         return b
 
     # ---- all-gather -> GEMM ---------------------------------------------------------------------
+    def _ag_eligible(self, Ms: int, K: int) -> bool:
+        return Ms % 128 == 0 and K % 8 == 0
+
+    def ag_input(self, Ms: int, K: int, dev):
+        """A [Ms, K] bf16 view of this rank's slot of the gather buffer, safe to overwrite: the kernel that produces
+        the next :meth:`ag_gemm` operand (a norm) writes there directly, and :meth:`ag_gemm` recognises the
+        address and skips its staging copy.  ``None`` for shapes the fused kernel does not take."""
+        if not self._ag_eligible(Ms, K):
+            return None
+        buf = self._ag_buf(Ms * K, dev)
+        key = ("ag", Ms * K)
+        if self._last_read.get(key, 1 << 60) >= self._nbar:
+            self._bar(dev)                       # peers may still be reading this buffer
+            self._last_read[key] = -1            # nothing has read it since that barrier
+        return buf.tensor.view(Ms, K)
+
     def ag_gemm(self, x_s, w, bias=None, gelu=False, b_mn=False):
         Ms, K = x_s.shape
         N = w.shape[1] if b_mn else w.shape[0]
-        if Ms % 128 or K % 8 or N % 8:
+        if not self._ag_eligible(Ms, K) or N % 8:
             X = self.comm.all_gather_rows(x_s)
             from .tp import _local_gemm
 
@@ -72,9 +88,10 @@ class FusedTP:
         dev = x_s.device
         buf = self._ag_buf(Ms * K, dev)
         key = ("ag", Ms * K)
-        if self._last_read.get(key, 1 << 60) >= self._nbar:
-            self._bar(dev)                       # peers may still be reading this buffer
-        buf.tensor.view(Ms, K).copy_(x_s)
+        if x_s.data_ptr() != buf.tensor.data_ptr():          # not produced in place through ag_input()
+            if self._last_read.get(key, 1 << 60) >= self._nbar:
+                self._bar(dev)                   # peers may still be reading this buffer
+            buf.tensor.view(Ms, K).copy_(x_s)
         self._bar(dev)                           # every shard is written
         epi = F_.EPI_BIAS_GELU if gelu else (F_.EPI_BIAS if bias is not None else F_.EPI_NONE)
         out = C.gemm_ag(buf.ptrs, self.rank, Ms, K, w, b_mn, epi, bias, gelu, self.AG_HELPERS)
@@ -99,6 +116,34 @@ class FusedTP:
         self._bar(dev)                           # every rank has consumed the previous contents of its receive buffer
         res = residual_s.contiguous() if residual_s is not None else None
         return C.gemm_rs(y, w, b_mn, recv.ptrs, cnt.ptrs, self.rank, bias, res, min(self.RS_HELPERS, Ms // 128))
+
+    # ---- vocabulary-parallel embedding ------------------------------------------------------------
+    def _emb_buf(self, Ms: int, Cd: int, dtype, dev) -> SymmetricBuffer:
+        key = ("emb", Ms, Cd, dtype)
+        b = self._ag.get(key)
+        if b is None:
+            b = self._ag[key] = SymmetricBuffer(Ms * Cd, dtype, dev, self.group)
+        return b
+
+    def embedding_push(self, idx, w, vocab_total: int):
+        """Token shard [M / world, C] of the embedding of ``idx`` (M ids) from a table split by rows: every rank
+        stores the rows it holds into the shard buffer of the rank that owns the token, then the shard is copied
+        out of the shared buffer."""
+        M, Ms, Cd = idx.numel(), idx.numel() // self.world, w.shape[1]
+        buf = self._emb_buf(Ms, Cd, w.dtype, w.device)
+        self._bar(w.device)                      # every rank has consumed the previous contents of its buffer
+        C.embedding_vp_push(idx.reshape(-1), w, list(buf.ptrs), Ms, self.rank * w.shape[0], vocab_total, self.rank == 0)
+        self._bar(w.device)                      # all rows have landed
+        return buf.tensor.view(Ms, Cd).clone()
+
+    def embedding_pull_bwd(self, idx, dx_s, dw) -> None:
+        """dw (fp32, this rank's rows of the table) += gradient rows of the ids it holds, read from the token owners."""
+        Ms, Cd = dx_s.shape
+        buf = self._emb_buf(Ms, Cd, dx_s.dtype, dx_s.device)
+        self._bar(dx_s.device)                   # nobody reads or writes the buffers any more
+        buf.tensor.view(Ms, Cd).copy_(dx_s)
+        self._bar(dx_s.device)                   # every shard is written
+        C.embedding_vp_pull_bwd(idx.reshape(-1), list(buf.ptrs), dw, Ms, self.rank * dw.shape[0], dx_s)
 
     # ---- per-row statistics table of the vocabulary-parallel loss ----------------------------------
     def stats_table(self, rows: int, dev):

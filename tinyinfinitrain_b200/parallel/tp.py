@@ -102,6 +102,13 @@ class TPComm:
         return full
 
     # ---- the two fused pairs ---------------------------------------------------------------------
+    def ag_input(self, like: torch.Tensor):
+        """Where the producer of the next ``ag_gemm`` operand (same shape and dtype as ``like``) may write its result
+        so that no staging copy is needed: a view of the symmetric gather buffer in fused mode, else ``None``."""
+        if self._fused is None or not like.is_cuda or like.dtype != _bf16 or like.dim() != 2:
+            return None
+        return self._fused.ag_input(like.shape[0], like.shape[1], like.device)
+
     def ag_gemm(self, x_s, w, bias=None, gelu=False, b_mn=False):
         """X = all_gather(x_s); returns (X W^T (+bias) [, pre-activation], X).
         b_mn: ``w`` is stored [K, N] (the product is X W), used by dgrad."""
@@ -312,6 +319,34 @@ class RowParallelLinear(nn.Module):
         return _RowParallelFn.apply(y, self.weight, self.bias, residual_s, self.comm)
 
 
+class _VocabParallelEmbeddingPushFn(torch.autograd.Function):
+    """The same result from the peer-memory kernels: each row is stored once, by the rank that holds it, into the
+    token owner's shard; the backward pulls only the gradient rows a rank holds.  No reduction, 1 / world of the
+    NVLink traffic of the masked gather + reduce-scatter below."""
+
+    @staticmethod
+    def forward(ctx, idx, w, comm: TPComm):
+        idx = idx.contiguous()
+        ctx.save_for_backward(idx)
+        ctx.w, ctx.comm = w, comm
+        return comm._fused.embedding_push(idx, w, w.shape[0] * comm.world)
+
+    @staticmethod
+    def backward(ctx, dx_s):
+        (idx,) = ctx.saved_tensors
+        w, comm = ctx.w, ctx.comm
+        mg, acc = F_._grad_target(w)
+        if mg is not None:
+            if not acc:
+                mg.zero_()
+            comm._fused.embedding_pull_bwd(idx, dx_s.contiguous(), mg.view(w.shape))
+            F_._grad_done(w)
+            return None, None, None
+        g = torch.zeros(w.shape, device=w.device, dtype=torch.float32)
+        comm._fused.embedding_pull_bwd(idx, dx_s.contiguous(), g)
+        return None, g.to(w.dtype), None
+
+
 class _VocabParallelEmbeddingFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, idx, w, comm: TPComm):
@@ -360,7 +395,12 @@ class VocabParallelEmbedding(nn.Module):
         init.Normal(self.weight, 0.0, 1.0)
 
     def forward(self, idx):
-        return _VocabParallelEmbeddingFn.apply(idx, self.weight, self.comm)
+        w, comm = self.weight, self.comm
+        vn = 8 if w.dtype == _bf16 else 4
+        if (comm._fused is not None and w.is_cuda and w.dtype in (_bf16, torch.float32) and comm.world <= 16
+                and idx.numel() % comm.world == 0 and w.shape[1] % vn == 0 and not F_.DETERMINISTIC_EMBEDDING_GRAD):
+            return _VocabParallelEmbeddingPushFn.apply(idx, w, comm)
+        return _VocabParallelEmbeddingFn.apply(idx, w, comm)
 
 
 class _VocabParallelLossFn(torch.autograd.Function):
