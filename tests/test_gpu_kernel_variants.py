@@ -83,7 +83,7 @@ def test_norm_fork_folds_the_residual_gradient(monkeypatch):
     grads = []
     for folded in (True, False):
         if not folded:
-            monkeypatch.setattr(Fn, "layernorm_fork", lambda x, w, b, eps=1e-5: (Fn.layernorm(x, w, b, eps), x))
+            monkeypatch.setattr(Fn, "layernorm_fork", lambda x, w, b, eps=1e-5, out=None: (Fn.layernorm(x, w, b, eps), x))
             monkeypatch.setattr(ops, "layernorm_fork", Fn.layernorm_fork, raising=False)
         model = GPT2(cfg, device=DEV, dtype=BF, seed=5)
         loss = model(idx, tgt)[1]
@@ -92,6 +92,26 @@ def test_norm_fork_folds_the_residual_gradient(monkeypatch):
     for n in grads[0]:
         scale = grads[0][n].abs().max().item() + 1e-6
         assert (grads[0][n] - grads[1][n]).abs().max().item() < 0.05 * scale, n
+    _status_ok()
+
+
+@pytest.mark.parametrize("M,N,K,world,helpers", [(1024, 512, 256, 4, 0), (2048, 3072, 768, 2, 0), (8192, 8192, 1024, 8, 0),
+                                                  (4096, 2304, 768, 4, 8), (4096, 1024, 2048, 4, 40), (1024, 256, 320, 8, 3)])
+def test_all_gather_gemm_with_local_shards_as_peers(M, N, K, world, helpers):
+    """All-gather -> GEMM on one GPU: `world` local tensors stand in for the ranks' shards.  The copying CTAs move
+    them with bulk copies through shared memory and then join the tile list; the gathered operand must equal the
+    concatenation bit for bit and the product must match fp32."""
+    torch.manual_seed(M + N + helpers)
+    shards = [(torch.randn(M // world, K, device=DEV) * 0.5).to(BF) for _ in range(world)]
+    B = (torch.randn(N, K, device=DEV) * 0.1).to(BF)
+    bias = torch.randn(N, device=DEV).to(BF)
+    ptrs = [t.data_ptr() for t in shards]
+    X = torch.cat(shards, 0)
+    ref = X.float() @ B.float().t() + bias.float()
+    for rank in (0, world - 1):
+        out, Xg = C.gemm_ag(ptrs, rank, M // world, K, B, False, 1, bias, False, helpers)
+        assert torch.equal(Xg, X)
+        assert (out.float() - ref).abs().max().item() < 0.05 * ref.abs().max().item() + 0.05
     _status_ok()
 
 

@@ -18,13 +18,14 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 
 def _multi_rank_env(**extra):
-    """Environment of a multi-rank child job whose code paths have not all run on GPUs yet: NVLink multicast stays
-    off in NCCL and in this package's kernels (plain peer loads / stores), so that a rank that stops early -- a
-    Python error in a new branch, say -- never leaves memory bound to a multicast object behind.  TITB_TEST_MULTIMEM=1
-    keeps multicast on for a deliberate run once these paths are known to finish."""
+    """Environment of a multi-rank child job: NVLink multicast stays off in NCCL and in this package's kernels
+    (plain peer loads / stores), so that a rank that stops early -- a Python error in a new branch, say -- never
+    leaves memory bound to a multicast object behind.  TITB_TEST_MULTIMEM=1 runs the multicast branches instead."""
     env = dict(os.environ, **extra)
     if os.environ.get("TITB_TEST_MULTIMEM") != "1":
         env.update(NCCL_NVLS_ENABLE="0", TITB200_NO_MULTIMEM="1", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
+    else:
+        env.update(TITB200_MULTIMEM="1")
     return env
 
 

@@ -15,7 +15,7 @@ import sys
 
 SWITCHES = {
     "TITB200_ATTN": "native | sdpa: attention implementation of ops.causal_attention (sdpa = library baseline arm)",
-    "TITB200_NO_MULTIMEM": "1: NVLink kernels use peer loads / stores instead of NVLS multimem",
+    "TITB200_MULTIMEM": "1: NVLink kernels go through the NVSwitch multicast address (multimem) instead of peer loads / stores",
     "TITB200_SYMM_HEAP": "native: symmetric buffers from this package's own cuMem heap instead of PyTorch's",
     "TITB200_SYMM_ALLREDUCE": "1: --zero_stage 0 sums gradients with the own all-reduce kernel instead of NCCL",
     "TITB200_DETERMINISTIC": "1: sorted, atomics-free token-embedding gradient",

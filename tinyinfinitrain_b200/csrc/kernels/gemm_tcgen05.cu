@@ -38,9 +38,13 @@ constexpr int kGemmThreads = 192;
 
 // Collective fused into the GEMM (tensor parallelism with sequence-sharded activations).
 //  mode 1, all-gather -> GEMM: the first `helper_ctas` CTAs copy 128-row chunks of every rank's
-//    activation shard from peer memory (plain loads over NVLink) into the local `gathered`
-//    buffer and raise a per-chunk flag; the GEMM CTAs visit m-blocks in the same order (local
+//    activation shard from peer memory into the local `gathered` buffer (bulk copies by the TMA
+//    engine: peer memory -> shared memory -> local memory, a dozen 16 KB pieces in flight per
+//    CTA) and raise a per-chunk flag; the GEMM CTAs visit m-blocks in the same order (local
 //    shard first) and their TMA producer waits on the flag of the chunk it is about to load.
+//    When their copies are done the helper CTAs join the GEMM: they sit out the first
+//    `helper_rounds` rounds of the tile list (the other CTAs share those) and take a full
+//    share of every later round.
 //  mode 2, GEMM -> reduce-scatter: the epilogue stores each bf16 partial tile straight into the
 //    receive buffer of the rank that owns those rows (peer stores over NVLink) and bumps a
 //    counter there; the first `helper_ctas` CTAs of the owner wait per 128-row chunk for all
@@ -55,6 +59,7 @@ constexpr int kGemmThreads = 192;
 #endif
 struct CollArgs {
   int mode, world, rank, helper_ctas, rows_per_rank;
+  int helper_rounds;    // mode 1: rounds of the tile list the helper CTAs leave to the others while they copy
   void* peers[16];      // mode 1: shard bases bf16 [Ms, K]; mode 2: receive buffers bf16 [world][Ms][N]
   void* cnt_peers[16];  // mode 2: counter arrays uint32 [Ms / 128] of every rank
   bf16* gathered;       // mode 1: local [M, K] staging buffer (the GEMM's A operand)
@@ -289,6 +294,9 @@ __device__ __forceinline__ void st_release_gpu_u32(uint32_t* a, uint32_t v) {
 __device__ __forceinline__ void red_release_sys_add_u32(uint32_t* a, uint32_t v) {
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(a), "r"(v) : "memory");
 }
+__device__ __forceinline__ void red_release_gpu_add_u32(uint32_t* a, uint32_t v) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(a), "r"(v) : "memory");
+}
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
 // Bounded spin until *flag >= want (acquire at `sys` or `gpu` scope); false on timeout.
@@ -303,34 +311,135 @@ __device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t want
   }
 }
 
-// mode 1 helper CTA: pull 128-row chunks of every rank's shard into the local gathered buffer.
-__device__ void ag_copy_role(const GemmArgs& p) {
-  const CollArgs& c = p.coll;
-  const int nchunks = p.M / kBM, cpr = c.rows_per_rank / kBM;
-  const long long vec_per_chunk = static_cast<long long>(kBM) * p.K / 8;  // 16-byte units
-  for (int pos = blockIdx.x; pos < nchunks; pos += c.helper_ctas) {
-    const int mblk = (pos + c.rank * cpr) % nchunks;
-    const int src_rank = mblk / cpr;
-    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const bf16*>(c.peers[src_rank]) +
-                                                      static_cast<long long>(mblk - src_rank * cpr) * kBM * p.K);
-    uint4* dst = reinterpret_cast<uint4*>(c.gathered + static_cast<long long>(mblk) * kBM * p.K);
-    // sixteen 16-byte loads per thread in flight: a load from a peer takes a few microseconds over NVLink, and the
-    // link is only busy when a couple of megabytes are outstanding on the whole GPU
-    long long i = threadIdx.x;
-    constexpr int kInFlight = 16;
-    for (; i + (kInFlight - 1) * kGemmThreads < vec_per_chunk; i += kInFlight * kGemmThreads) {
-      uint4 v[kInFlight];
-#pragma unroll
-      for (int u = 0; u < kInFlight; ++u) v[u] = src[i + u * kGemmThreads];
-#pragma unroll
-      for (int u = 0; u < kInFlight; ++u) dst[i + u * kGemmThreads] = v[u];
-    }
-    for (; i < vec_per_chunk; i += kGemmThreads) dst[i] = src[i];
-    fence_proxy_async_all();  // these generic-proxy writes are read by TMA (async proxy) below
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) st_release_gpu_u32(c.flags + mblk, 1u);
+// Which tiles a CTA works on, round by round.  Plain launches deal the tiles round-robin over n CTAs (H = 0).  In an
+// all-gather -> GEMM launch the first H CTAs are busy copying during the first `skip` rounds, which the other n - H
+// CTAs share among themselves; from round `skip` on all n CTAs take part.
+struct TileWalk {
+  int c, n, H, skip;
+  __device__ __forceinline__ int first_round() const { return c < H ? skip : 0; }
+  __device__ __forceinline__ int tile(int round) const {
+    return round < skip ? round * (n - H) + (c - H) : skip * (n - H) + (round - skip) * n + c;
   }
+};
+
+// mode 1 helper CTA: pull 128-row chunks of every rank's shard into the local gathered buffer.  One thread drives
+// the TMA engine: 16 KB pieces travel peer (or local) memory -> shared-memory ring -> gathered buffer; of the twelve
+// stages eight hold loads in flight and four hold stores that are still being read, so neither latency is exposed
+// per piece (plain per-thread loads and stores moved 13-17 GB/s per CTA, one round trip per 48 KB batch).  Returns
+// false when a wait ran out (status word set).
+constexpr int kAgMaxStages = 12;
+constexpr int kAgPiece = 16384;
+constexpr int kAgStoresInFlight = 5;
+// A 128-row chunk of the gathered operand is copied in up to four parts by different CTAs; its flag counts parts.
+__device__ __forceinline__ int ag_pieces_per_chunk(int K) { return (kBM * K * 2 + kAgPiece - 1) / kAgPiece; }
+__device__ __forceinline__ int ag_pieces_per_part(int K) { return (ag_pieces_per_chunk(K) + 3) / 4; }
+__device__ __forceinline__ int ag_parts_per_chunk(int K) {
+  return (ag_pieces_per_chunk(K) + ag_pieces_per_part(K) - 1) / ag_pieces_per_part(K);   // no part is empty
+}
+
+__device__ __noinline__ bool ag_copy_role(const GemmArgs& p, uint8_t* ring, int kAgStages) {
+  __shared__ uint64_t ag_bar[kAgMaxStages];
+  __shared__ int ag_sig[kAgMaxStages];   // per stage: m-block to publish when that stage's store completes, or -1
+  __shared__ int ag_ok;
+  const CollArgs& c = p.coll;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kAgStages; ++s) ptx::mbar_init(&ag_bar[s], 1);
+    ptx::mbar_fence_init();
+    const int nchunks = p.M / kBM, cpr = c.rows_per_rank / kBM;
+    const int chunk_bytes = kBM * p.K * 2;
+    const int ppc = ag_pieces_per_chunk(p.K);
+    const int parts = ag_parts_per_chunk(p.K);
+    const int pp = ag_pieces_per_part(p.K);
+    const int H = c.helper_ctas;
+    volatile uint32_t no_abort = 0;
+    // The copying CTAs deal out the parts of all chunks (chunks in the order the GEMM visits them) round-robin, so
+    // the first chunks are complete after a quarter of a chunk time.  A cursor walks this CTA's pieces and keeps
+    // addresses, ring stage and barrier parity up to date with additions only: one thread issues every copy, so
+    // its instruction count per piece bounds the copy rate.
+    struct Cursor {
+      int pos, part, piece, end, stage, mblk;
+      uint32_t parity;
+      const uint8_t* src;
+      uint8_t* dst;
+    };
+    auto open_part = [&](Cursor& q) {
+      q.mblk = (q.pos + c.rank * cpr) % nchunks;
+      const int src_rank = q.mblk / cpr;
+      q.src = reinterpret_cast<const uint8_t*>(static_cast<const bf16*>(c.peers[src_rank]) +
+                                               static_cast<long long>(q.mblk - src_rank * cpr) * kBM * p.K);
+      q.dst = reinterpret_cast<uint8_t*>(c.gathered + static_cast<long long>(q.mblk) * kBM * p.K);
+      q.piece = q.part * pp;
+      q.end = min(ppc, q.piece + pp);
+    };
+    auto valid = [&](const Cursor& q) { return q.pos < nchunks; };
+    auto advance = [&](Cursor& q) {
+      if (++q.piece == q.end) {
+        q.part += H;
+        while (q.part >= parts) { q.part -= parts; ++q.pos; }
+        if (valid(q)) open_part(q);
+      }
+      if (++q.stage == kAgStages) { q.stage = 0; q.parity ^= 1u; }
+    };
+    auto piece_bytes = [&](const Cursor& q) {
+      return static_cast<uint32_t>(min(kAgPiece, chunk_bytes - q.piece * kAgPiece));
+    };
+    const int g0 = static_cast<int>(blockIdx.x);
+    Cursor ld{g0 / parts, g0 % parts, 0, 0, 0, 0, 0u, nullptr, nullptr};
+    if (valid(ld)) open_part(ld);
+    Cursor st = ld;
+    auto issue = [&]() {
+      const uint32_t bytes = piece_bytes(ld);
+      ptx::mbar_expect_tx(&ag_bar[ld.stage], bytes);
+      ptx::bulk_load(ring + ld.stage * kAgPiece, ld.src + ld.piece * kAgPiece, bytes, &ag_bar[ld.stage]);
+      advance(ld);
+    };
+    // the store issued from `stage` has completed: if it closed a part, tell the GEMM CTAs
+    auto publish = [&](int stage) {
+      if (ag_sig[stage] >= 0) {
+        fence_proxy_async_all();   // written through the async proxy, read through it again by the GEMM's TMA loads
+        red_release_gpu_add_u32(c.flags + ag_sig[stage], 1u);
+      }
+    };
+    bool ok = true;
+    // kAgStoresInFlight stages hold stores that have not completed, the others loads in flight
+    for (int n = 0; n < kAgStages - kAgStoresInFlight && valid(ld); ++n) issue();
+    int i = 0;           // pieces stored so far
+    int oldest = 0;      // stage of the oldest store not yet known to be complete
+    for (; valid(st); ++i) {
+      if (!ptx::mbar_wait(&ag_bar[st.stage], st.parity, &no_abort)) { ok = false; break; }
+      ptx::bulk_store(st.dst + st.piece * kAgPiece, ring + st.stage * kAgPiece, piece_bytes(st));
+      ptx::bulk_commit();
+      ag_sig[st.stage] = (st.piece == st.end - 1) ? st.mblk : -1;
+      advance(st);
+      // all but the newest kAgStoresInFlight - 1 stores are complete: the oldest one can be published and its stage
+      // reused (waiting for a store issued several pieces ago costs little; waiting for the newest would serialise
+      // the ring on the latency of a store)
+      ptx::bulk_wait_all<kAgStoresInFlight - 1>();
+      if (i >= kAgStoresInFlight - 1) {
+        publish(oldest);
+        if (++oldest == kAgStages) oldest = 0;
+      }
+      if (valid(ld)) issue();
+    }
+    ptx::bulk_wait_all<0>();
+    if (ok) {
+      for (int d = max(0, i - (kAgStoresInFlight - 1)); d < i; ++d) {
+        publish(oldest);
+        if (++oldest == kAgStages) oldest = 0;
+      }
+    } else {
+      atomicExch(p.status, kStatusPeerTimeout);
+      // loads already issued still write into the ring: give each a bounded wait before the CTA leaves
+      for (int s = 0; s < kAgStages; ++s) {
+        const long long t0 = clock64();
+        while (!ptx::mbar_try_wait(&ag_bar[s], 0) && !ptx::mbar_try_wait(&ag_bar[s], 1) && clock64() - t0 < 2000000LL) {
+        }
+      }
+    }
+    ag_ok = ok ? 1 : 0;
+  }
+  __syncthreads();
+  return ag_ok != 0;
 }
 
 #ifdef TITB_GEMM_PARAM_GATHER
@@ -363,65 +472,85 @@ __device__ void param_gather_role(const GemmArgs& p) {
 
 // mode 2, second phase: when a CTA has pushed all its partial tiles, its four epilogue warps (128 threads, named
 // barrier 1) help to sum the `world` partial slots of this rank's rows.  A work unit is a 128-row chunk x a strip of
-// columns; units are dealt round-robin over all CTAs, so the whole GPU streams the reduction (a handful of helper
-// CTAs cannot pull more than a fraction of the memory bandwidth).  A unit waits -- bounded -- until every rank's
-// partial tiles of its chunk have arrived; remote ranks send this rank's rows first, so they usually have.
-__device__ void rs_reduce_phase(const GemmArgs& p, int tiles_n, int worker, int nworkers, int tid) {
+// 64 columns; units are dealt round-robin over all CTAs, so the whole GPU streams the reduction.  A unit waits --
+// bounded -- until every rank's partial tiles of its chunk have arrived; remote ranks send this rank's rows first,
+// so they usually have.  The pass is pure streaming, so what matters is bytes in flight: a thread issues the loads
+// of B rows x W slots (16 vectors of 16 bytes) before it sums the first.
+__device__ __forceinline__ void rs_add8(float (&acc)[8], const uint4& v) {
+  const float2 f0 = unpack_bf16x2(v.x), f1 = unpack_bf16x2(v.y), f2 = unpack_bf16x2(v.z), f3 = unpack_bf16x2(v.w);
+  acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
+  acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+}
+
+// W: slots read per row (world rounded up to a power of two); B = 16 / W rows in flight per thread.
+template <int W>
+__device__ __forceinline__ void rs_sum_unit(const GemmArgs& p, const bf16* recv, long long slot, int ch, int v0, int vn,
+                                            int tid) {
+  constexpr int B = W >= 8 ? 1 : 8 / W;
+  const CollArgs& c = p.coll;
+  // 128 rows x vn vectors; consecutive threads take consecutive vectors of a row.  Position tid + 128 j, j < vn:
+  // every thread has the same number of positions, so the guards below are uniform.
+  for (int j0 = 0; j0 < vn; j0 += B) {
+    uint4 part[B][W];
+    long long off[B];
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      const int i = tid + (j0 + b) * 128;
+      const int r = ch * kBM + i / vn, col = (v0 + i % vn) * 8;
+      off[b] = static_cast<long long>(r) * p.N + col;
+      if (j0 + b < vn) {
+#pragma unroll
+        for (int s = 0; s < W; ++s)
+          if (s < c.world) part[b][s] = *reinterpret_cast<const uint4*>(recv + s * slot + off[b]);
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      const int i = tid + (j0 + b) * 128;
+      if (j0 + b >= vn) continue;
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int s = 0; s < W; ++s)
+        if (s < c.world) rs_add8(acc, part[b][s]);
+      if (c.rs_bias != nullptr) rs_add8(acc, *reinterpret_cast<const uint4*>(c.rs_bias + (v0 + i % vn) * 8));
+      if (c.rs_residual != nullptr) rs_add8(acc, *reinterpret_cast<const uint4*>(c.rs_residual + off[b]));
+      *reinterpret_cast<uint4*>(c.rs_out + off[b]) =
+          make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
+                     pack_bf16x2(acc[6], acc[7]));
+    }
+  }
+}
+
+__device__ __noinline__ void rs_reduce_phase(const GemmArgs& p, int tiles_n, int worker, int nworkers, int tid) {
   const CollArgs& c = p.coll;
   __shared__ int ok_sh;
   const int cpr = c.rows_per_rank / kBM;
   const uint32_t expected = static_cast<uint32_t>(c.world * tiles_n);  // one arrival per partial tile
   const bf16* recv = static_cast<const bf16*>(c.peers[c.rank]);
   const long long slot = static_cast<long long>(c.rows_per_rank) * p.N;
-  // strips of 64 columns (8 vectors): a thread sums one vector of one row per step, `world` loads in flight each
   const int nv = p.N / 8;
   const int strips = (nv + 7) / 8;
   const int units = cpr * strips;
+  int ready_ch = -1;
   for (int u = worker; u < units; u += nworkers) {
     const int ch = u / strips, st = u - ch * strips;
-    if (tid == 0) {
-      ok_sh = wait_flag_ge<true>(c.flags + ch, expected) ? 1 : 0;
-      if (!ok_sh) atomicExch(p.status, kStatusPeerTimeout);
+    if (ch != ready_ch) {
+      if (tid == 0) {
+        ok_sh = wait_flag_ge<true>(c.flags + ch, expected) ? 1 : 0;
+        if (!ok_sh) atomicExch(p.status, kStatusPeerTimeout);
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const bool ok = ok_sh != 0;
+      asm volatile("bar.sync 1, 128;" ::: "memory");   // ok_sh may be rewritten for the next unit
+      if (!ok) continue;
+      ready_ch = ch;
     }
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    const bool ok = ok_sh != 0;
-    asm volatile("bar.sync 1, 128;" ::: "memory");   // ok_sh may be rewritten for the next unit
-    if (!ok) continue;
     const int v0 = st * 8, vn = min(8, nv - v0);
-    // 128 rows x vn vectors; consecutive threads take consecutive vectors of a row
-    for (int i = tid; i < kBM * vn; i += 128) {
-      const int r = ch * kBM + i / vn, col = (v0 + i % vn) * 8;
-      const long long off = static_cast<long long>(r) * p.N + col;
-      uint4 part[16];
-#pragma unroll
-      for (int s = 0; s < 16; ++s)
-        if (s < c.world) part[s] = *reinterpret_cast<const uint4*>(recv + s * slot + off);
-      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int s = 0; s < 16; ++s) {
-        if (s < c.world) {
-          const float2 f0 = unpack_bf16x2(part[s].x), f1 = unpack_bf16x2(part[s].y), f2 = unpack_bf16x2(part[s].z),
-                       f3 = unpack_bf16x2(part[s].w);
-          acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
-          acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
-        }
-      }
-      if (c.rs_bias != nullptr) {
-        const uint4 b = *reinterpret_cast<const uint4*>(c.rs_bias + col);
-        const float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z), f3 = unpack_bf16x2(b.w);
-        acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
-        acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
-      }
-      if (c.rs_residual != nullptr) {
-        const uint4 b = *reinterpret_cast<const uint4*>(c.rs_residual + off);
-        const float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z), f3 = unpack_bf16x2(b.w);
-        acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
-        acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
-      }
-      *reinterpret_cast<uint4*>(c.rs_out + off) =
-          make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
-                     pack_bf16x2(acc[6], acc[7]));
-    }
+    if (c.world <= 1) rs_sum_unit<1>(p, recv, slot, ch, v0, vn, tid);
+    else if (c.world <= 2) rs_sum_unit<2>(p, recv, slot, ch, v0, vn, tid);
+    else if (c.world <= 4) rs_sum_unit<4>(p, recv, slot, ch, v0, vn, tid);
+    else if (c.world <= 8) rs_sum_unit<8>(p, recv, slot, ch, v0, vn, tid);
+    else rs_sum_unit<16>(p, recv, slot, ch, v0, vn, tid);
   }
 }
 
@@ -429,7 +558,7 @@ template <int BN, bool PAIR>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                          const __grid_constant__ CUtensorMap tma_out, const __grid_constant__ CUtensorMap tma_aux,
-                         const GemmArgs p) {
+                         const __grid_constant__ GemmArgs p) {
   using Cfg = GemmCfg<BN, PAIR>;
   constexpr int kStages = Cfg::kStages;
   constexpr int kBBytes = Cfg::kBBytes;
@@ -437,21 +566,28 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   const uint32_t pair_rank = PAIR ? ptx::cluster_ctarank() : 0u;   // 0 issues the MMAs of the pair
   const int row_off = static_cast<int>(pair_rank) * kBM;
 
-  // Leading CTAs of a fused-collective launch do the copy / reduction instead of GEMM tiles.
-  const int helpers = (!PAIR && (p.coll.mode == 1 || p.coll.mode == 3)) ? p.coll.helper_ctas : 0;
-  if (!PAIR && static_cast<int>(blockIdx.x) < helpers) {
-    if (p.coll.mode == 1) ag_copy_role(p);
-#ifdef TITB_GEMM_PARAM_GATHER
-    else if (p.coll.mode == 3) param_gather_role(p);
-#endif
-    return;
-  }
-  // a pair walks the tile list as one unit
-  const int cta = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x) - helpers;
-  const int ncta = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x) - helpers;
-
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  // Leading CTAs of a fused-collective launch first move the remote operand.  All-gather -> GEMM: the operand ring
+  // is their copy ring, and when the copies are done they join the tile list (TileWalk).  Parameter gather: they
+  // leave when the weight is in place.
+  const int helpers = (!PAIR && (p.coll.mode == 1 || p.coll.mode == 3)) ? p.coll.helper_ctas : 0;
+  if (!PAIR && static_cast<int>(blockIdx.x) < helpers) {
+    if (p.coll.mode == 1) {
+      constexpr int kRingPieces = Cfg::kRing / kAgPiece;   // the operand ring doubles as the copy ring
+      static_assert(kRingPieces >= 2 * kAgStoresInFlight, "the copy ring needs stages for loads and for stores in flight");
+      if (!ag_copy_role(p, smem, kRingPieces < kAgMaxStages ? kRingPieces : kAgMaxStages)) return;
+    }
+#ifdef TITB_GEMM_PARAM_GATHER
+    else if (p.coll.mode == 3) { param_gather_role(p); return; }
+#endif
+  }
+  const bool joined = !PAIR && p.coll.mode == 1;   // helper CTAs take tiles too
+  // a pair walks the tile list as one unit
+  const int cta = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x) - (joined ? 0 : helpers);
+  const int ncta = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x) - (joined ? 0 : helpers);
+  const TileWalk walk{cta, ncta, joined ? helpers : 0, joined ? p.coll.helper_rounds : 0};
   uint8_t* sa = smem;
   uint8_t* sb = smem + kStages * kABytes;
   uint8_t* stage_out = smem + Cfg::kRing;
@@ -513,7 +649,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
 #ifdef TITB_GEMM_PARAM_GATHER
       int ready_n0 = -1;
 #endif
-      for (int tile = cta; tile < num_tiles && ok; tile += ncta) {
+      for (int rnd = walk.first_round(), tile; (tile = walk.tile(rnd)) < num_tiles && ok; ++rnd) {
         const TileCoord tc = tile_coord(p, tile, tiles_m, tiles_n, BN, kTileM, row_off);
         const int split = tc.split, m0 = tc.m0, n0 = tc.n0;
         const int nb0 = n0 + static_cast<int>(pair_rank) * Cfg::kBRows;   // first B row (output column) this CTA stages
@@ -521,7 +657,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
         const int kb1 = min(num_kb_total, kb0 + p.kb_per_split);
         if (p.coll.mode == 1 && tc.mblk != ready_mblk) {
           // the rows of this m-block must have landed in the gathered buffer
-          if (!wait_flag_ge<false>(p.coll.flags + tc.mblk, 1u)) {
+          if (!wait_flag_ge<false>(p.coll.flags + tc.mblk, static_cast<uint32_t>(ag_parts_per_chunk(p.K)))) {
             *abort_flag = 1u;
             atomicExch(p.status, kStatusPeerTimeout);
             ok = false;
@@ -590,7 +726,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int tile = cta; tile < num_tiles && ok; tile += ncta, ++it) {
+      for (int rnd = walk.first_round(), tile; (tile = walk.tile(rnd)) < num_tiles && ok; ++rnd, ++it) {
         const int split = tile / tiles_mn;
         const int kb0 = split * p.kb_per_split;
         const int kb1 = min(num_kb_total, kb0 + p.kb_per_split);
@@ -639,7 +775,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       const int trow = quad * 32 + lane;
       const int tid = threadIdx.x - 64;                 // 0 .. 127 among the epilogue threads
       const int crow = tid >> 3, cunit = tid & 7;       // copy-out: row within a group of 16, 16-byte unit of the row
-      for (int tile = cta; tile < num_tiles; tile += ncta, ++it) {
+      for (int rnd = walk.first_round(), tile; (tile = walk.tile(rnd)) < num_tiles; ++rnd, ++it) {
         const TileCoord tc = tile_coord(p, tile, tiles_m, tiles_n, BN, kTileM, row_off);
         const int m0 = tc.m0, n0 = tc.n0;
         const int buf = it & 1;
@@ -689,8 +825,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
             }
           }
         }
-        // every thread's stores of this tile are ordered before the one arrival that publishes it to the owner
-        __threadfence_system();
+        // every thread's stores of this tile happen before the barrier, the barrier before the release below: one
+        // system-scope release by one thread publishes the whole tile (a fence per thread cost 128 membar.sys a tile)
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (tid == 0) {
           const int chunk = static_cast<int>(lrow0 / kBM);
@@ -705,7 +841,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       const int trow = quad * 32 + lane;
       const bool elected = (warp == 2 && lane == 0);
       int gchunk = 0;
-      for (int tile = cta; tile < num_tiles; tile += ncta, ++it) {
+      for (int rnd = walk.first_round(), tile; (tile = walk.tile(rnd)) < num_tiles; ++rnd, ++it) {
         const TileCoord tc = tile_coord(p, tile, tiles_m, tiles_n, BN, kTileM, row_off);
         const int m0 = tc.m0, n0 = tc.n0;
         const int buf = it & 1;
@@ -782,7 +918,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       };
       int gchunk = 0;
       if (p.aux_tma_load && elected && total_chunks > 0) issue_aux_load(0);
-      for (int tile = cta; tile < num_tiles; tile += ncta, ++it) {
+      for (int rnd = walk.first_round(), tile; (tile = walk.tile(rnd)) < num_tiles; ++rnd, ++it) {
         const TileCoord tc = tile_coord(p, tile, tiles_m, tiles_n, BN, kTileM, row_off);
         const int m0 = tc.m0, n0 = tc.n0;
         const int buf = it & 1;
@@ -919,7 +1055,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       }
       if (elected) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // all stores done before the CTA exits
     } else
-    for (int tile = cta; tile < num_tiles; tile += ncta, ++it) {
+    for (int rnd = walk.first_round(), tile; (tile = walk.tile(rnd)) < num_tiles; ++rnd, ++it) {
       const TileCoord tc = tile_coord(p, tile, tiles_m, tiles_n, BN, kTileM, row_off);
       const int split = tc.split, m0 = tc.m0, n0 = tc.n0;
       const int buf = it & 1;
@@ -1148,6 +1284,8 @@ static bool f32_tma_eligible(const TitbGemmDesc* d) {
          !(reinterpret_cast<uintptr_t>(d->out) & 15) && !(d->ldo & 3) && g_no_tma_store == 0;
 }
 
+constexpr double kTflopsPerSm = 10.8;   // bf16 tensor throughput of one SM at the sustained clock (1.6 PFLOP/s / 148)
+
 template <int BN, bool PAIR>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tout, const CUtensorMap& taux,
                        const GemmArgs& args, cudaStream_t stream) {
@@ -1183,8 +1321,35 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_bf16_tcgen05_kernel<BN, PAIR>, ta, tb, tout, taux, args);
     return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
   }
-  const int helpers = (args.coll.mode == 1 || args.coll.mode == 3) ? args.coll.helper_ctas : 0;
-  int grid = tiles + helpers < device_sm_count() ? tiles + helpers : device_sm_count();
+  const int sms = device_sm_count();
+  if (args.coll.mode == 1) {
+    // All-gather -> GEMM: how many CTAs copy, and for how many rounds of the tile list they are excused.  The copy
+    // has to stay ahead of the GEMM CTAs, which reach the first remote rows after 1 / world of the tiles; the model
+    // below (microseconds of one CTA) errs on the side of more helpers, which cost little because they join the
+    // GEMM afterwards.  A copying CTA moves about 35 GB/s of local memory (measured) and less from a peer.
+    GemmArgs a2 = args;
+    const double t_tile = 2.0 * kBM * BN * args.K / (kTflopsPerSm * 1e6);
+    const double remote = 2.0 * args.K * args.coll.rows_per_rank * (args.coll.world - 1), local = 2.0 * args.K * args.coll.rows_per_rank;
+    const double w_copy = remote / 20e3 + local / 35e3;                  // CTA-microseconds
+    const double t_total = (tiles * t_tile + w_copy) / sms;
+    int H = args.coll.helper_ctas;
+    if (H <= 0) {
+      const double window = t_total * (args.coll.world > 1 ? 1.0 - 1.0 / args.coll.world : 1.0);
+      H = static_cast<int>(1.5 * w_copy / (window > 1.0 ? window : 1.0)) + 1;
+      if (H < 8) H = 8;
+      if (H > 64) H = 64;                                                // the link is full long before that
+    }
+    if (H > sms / 2) H = sms / 2;
+    int grid = tiles + H < sms ? tiles + H : sms;
+    if (grid <= H) return TITB_ERR_SHAPE;
+    int rounds = static_cast<int>(w_copy / H / t_tile + 0.999);
+    a2.coll.helper_ctas = H;
+    a2.coll.helper_rounds = rounds < 1 ? 1 : rounds;
+    gemm_bf16_tcgen05_kernel<BN, PAIR><<<grid, kGemmThreads, Cfg::kSmem, stream>>>(ta, tb, tout, taux, a2);
+    return static_cast<int>(cudaGetLastError());
+  }
+  const int helpers = args.coll.mode == 3 ? args.coll.helper_ctas : 0;
+  int grid = tiles + helpers < sms ? tiles + helpers : sms;
   if (grid <= helpers) return TITB_ERR_SHAPE;
   gemm_bf16_tcgen05_kernel<BN, PAIR><<<grid, kGemmThreads, Cfg::kSmem, stream>>>(ta, tb, tout, taux, args);
   return static_cast<int>(cudaGetLastError());
@@ -1263,7 +1428,7 @@ TITB_API int TITB_GEMM_ENTRY(const TitbGemmDesc* d, cudaStream_t stream) {
       return TITB_ERR_SHAPE;
 #else
     if (c->world < 1 || c->world > 16 || c->rows_per_rank % kBM || d->M != c->rows_per_rank * c->world || splits != 1 ||
-        (d->N & 7) || (d->K & 7) || c->helper_ctas < 1)
+        (d->N & 7) || (d->K & 7) || (c->mode != 1 && c->helper_ctas < 1))   // mode 1: helper_ctas <= 0 lets the launcher choose
       return TITB_ERR_SHAPE;
 #endif
     if (c->mode == 2 && (d->epilogue != TITB_EPI_NONE || d->accumulate || d->alpha)) return TITB_ERR_SHAPE;

@@ -18,7 +18,7 @@ from .symm import DeviceBarrier, SymmetricBuffer
 
 
 class FusedTP:
-    AG_HELPERS = 24   # CTAs that pull peer shards over NVLink while the rest run GEMM tiles
+    AG_HELPERS = 0    # CTAs that pull peer shards over NVLink before they join the GEMM tiles; 0: the launcher sizes it
     RS_HELPERS = 8    # CTAs that reduce arriving partial tiles
 
     def __init__(self, comm):

@@ -114,7 +114,7 @@ def main():
     ap.add_argument("--model", default="gpt2", choices=["gpt2", "gpt2xl", "llama1b"], help="gemm_sweep: whose layer shapes")
     ap.add_argument("--deterministic", action="store_true", help="embedding_bwd: sorted segment reduction instead of atomics")
     ap.add_argument("--world", type=int, default=4)
-    ap.add_argument("--helpers", type=int, default=0)
+    ap.add_argument("--helpers", type=int, default=0, help="ag_gemm: copying CTAs (0: sized by the launcher)")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=3072)
     ap.add_argument("--k", type=int, default=768)
@@ -191,7 +191,7 @@ def main():
         flops = 2.0 * M * N * K
         bytes_ = 2.0 * (2 * M * K + N * K + M * N)
         ptrs = [t.data_ptr() for t in shards]
-        fn = lambda: C.gemm_ag(ptrs, 0, M // W, K, B, False, 0, None, False, a.helpers or 16)
+        fn = lambda: C.gemm_ag(ptrs, 0, M // W, K, B, False, 0, None, False, max(a.helpers, 0))
     elif a.kernel == "param_gather_gemm":
         # Y = X . W^T with the rows of W owned by W ranks: `world` local copies stand in for the ranks' memory
         M, N, K, W = a.m, a.n, a.k, a.world
