@@ -220,14 +220,17 @@ int main(int argc, char** argv) {
   const std::string dev = argc > 1 ? argv[1] : "cpu";
   const std::string dir = argc > 2 ? argv[2] : "/tmp";
   g_dev = dev == "cuda" ? Device(DeviceType::kCUDA, 0) : Device();
+  // optional third argument: run one case group only (the reference has one test program per group)
+  const std::string only = argc > 3 ? argv[3] : "";
+  auto want = [&](const char* name) { return only.empty() || only == name; };
   try {
-    TestNeg();
-    TestMatmul();
-    TestAdam();
-    TestTensorAutograd();
-    TestDispatcher();
-    TestUniformAndPrintOptions();
-    TestDataAndTraining(dir);
+    if (want("elementwise")) TestNeg();
+    if (want("matmul")) TestMatmul();
+    if (want("adam")) TestAdam();
+    if (want("autograd")) TestTensorAutograd();
+    if (want("dispatcher")) TestDispatcher();
+    if (want("tensor")) TestUniformAndPrintOptions();
+    if (want("gpt2")) TestDataAndTraining(dir);
   } catch (const std::exception& e) {
     std::printf("EXCEPTION: %s\n", e.what());
     return 2;

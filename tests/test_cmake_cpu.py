@@ -20,4 +20,4 @@ def test_cmake_project_configures_and_lists_its_targets(tmp_path):
     for target in ("titb200_kernels", "titb200_framework", "train_gpt2", "facade_api_test"):
         assert target in h.stdout, target
     t = subprocess.run(["ctest", "--test-dir", str(tmp_path), "-N"], capture_output=True, text=True, timeout=120)
-    assert "facade_api_cpu" in t.stdout and "facade_api_cuda" in t.stdout
+    assert "facade_api_cpu_matmul" in t.stdout and "facade_api_cuda_gpt2" in t.stdout

@@ -1330,7 +1330,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
     GemmArgs a2 = args;
     const double t_tile = 2.0 * kBM * BN * args.K / (kTflopsPerSm * 1e6);
     const double remote = 2.0 * args.K * args.coll.rows_per_rank * (args.coll.world - 1), local = 2.0 * args.K * args.coll.rows_per_rank;
-    const double w_copy = remote / 20e3 + local / 35e3;                  // CTA-microseconds
+    const double w_copy = remote / 15e3 + local / 35e3;                  // CTA-microseconds
     const double t_total = (tiles * t_tile + w_copy) / sms;
     int H = args.coll.helper_ctas;
     if (H <= 0) {
