@@ -46,3 +46,14 @@ def test_reference_arm_reports_unavailable():
     assert r.returncode == 0
     out = json.loads(r.stdout.strip().splitlines()[-1])
     assert out["impl"] == "reference" and "unavailable" in out and "\n" not in out["unavailable"]
+
+
+def test_pipeline_bubble_bench_two_stages_dry_run():
+    """utils/pp_bench.py on two gloo ranks: the record carries the measured and the ideal bubble of the 1F1B schedule."""
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", str(29700 + os.getpid() % 100), "-m", "tinyinfinitrain_b200.utils.pp_bench",
+           "--micro", "2", "--batch", "1", "--seq", "32", "--layers", "2", "--d_model", "64", "--heads", "2", "--iters", "2"]
+    out = _run(cmd)
+    assert out["stages"] == 2 and out["micro_batches"] == 2 and out["ms_2m"] > 0 and out["ms_m"] > 0
+    assert abs(out["bubble_ideal"] - 1.0 / 3.0) < 1e-9 and abs(out["bubble_ideal_2m"] - 0.2) < 1e-9
+    assert abs(out["slot_ms"] * 2 - (out["ms_2m"] - out["ms_m"])) < 1e-6

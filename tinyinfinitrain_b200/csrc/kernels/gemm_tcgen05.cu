@@ -53,13 +53,13 @@ constexpr int kGemmThreads = 192;
 //  mode 3, parameter all-gather -> GEMM: the B operand (a weight [N, K], K-major) is sharded by rows over the
 //    data-parallel ranks.  `gathered` is this rank's full-size copy of the weight (the tensor map of B points at
 //    it), `peers[r]` the rows rank r owns, in r's memory.  The first `helper_ctas` CTAs pull 128-row chunks from
-//    their owners (plain loads over NVLink; the local shard is already in place when peers[rank] aliases it) and
-//    raise a flag per chunk; the GEMM CTAs visit n-blocks shard by shard, local shard first, and their TMA
+//    their owners (the same bulk-copy role as mode 1; the local shard is already in place when peers[rank] aliases
+//    it) and raise the chunk's flag; the GEMM CTAs visit n-blocks shard by shard, local shard first, and their TMA
 //    producer waits for the chunks under the B tile it is about to load.  rows_per_rank counts weight rows.
 #endif
 struct CollArgs {
   int mode, world, rank, helper_ctas, rows_per_rank;
-  int helper_rounds;    // mode 1: rounds of the tile list the helper CTAs leave to the others while they copy
+  int helper_rounds;    // modes 1, 3: rounds of the tile list the copying CTAs leave to the others while they copy
   void* peers[16];      // mode 1: shard bases bf16 [Ms, K]; mode 2: receive buffers bf16 [world][Ms][N]
   void* cnt_peers[16];  // mode 2: counter arrays uint32 [Ms / 128] of every rank
   bf16* gathered;       // mode 1: local [M, K] staging buffer (the GEMM's A operand)
@@ -327,6 +327,12 @@ struct TileWalk {
 // stages eight hold loads in flight and four hold stores that are still being read, so neither latency is exposed
 // per piece (plain per-thread loads and stores moved 13-17 GB/s per CTA, one round trip per 48 KB batch).  Returns
 // false when a wait ran out (status word set).
+// the gather mode this compilation serves: activation rows (mode 1), or weight rows in the parameter-gather build
+#ifdef TITB_GEMM_PARAM_GATHER
+constexpr int kGatherMode = 3;
+#else
+constexpr int kGatherMode = 1;
+#endif
 constexpr int kAgMaxStages = 12;
 constexpr int kAgPiece = 16384;
 constexpr int kAgStoresInFlight = 5;
@@ -337,15 +343,19 @@ __device__ __forceinline__ int ag_parts_per_chunk(int K) {
   return (ag_pieces_per_chunk(K) + ag_pieces_per_part(K) - 1) / ag_pieces_per_part(K);   // no part is empty
 }
 
+// The gathered extent is M for the activation gather and N for the weight gather of mode 3, where a part whose source
+// already is its destination (the owner's rows of the weight) is published without a copy.
 __device__ __noinline__ bool ag_copy_role(const GemmArgs& p, uint8_t* ring, int kAgStages) {
   __shared__ uint64_t ag_bar[kAgMaxStages];
   __shared__ int ag_sig[kAgMaxStages];   // per stage: m-block to publish when that stage's store completes, or -1
   __shared__ int ag_ok;
   const CollArgs& c = p.coll;
+  const bool skip_local = c.mode == 3;        // mode 3 gathers rows of B (the weight), mode 1 rows of A
+  const int rows = skip_local ? p.N : p.M;
   if (threadIdx.x == 0) {
     for (int s = 0; s < kAgStages; ++s) ptx::mbar_init(&ag_bar[s], 1);
     ptx::mbar_fence_init();
-    const int nchunks = p.M / kBM, cpr = c.rows_per_rank / kBM;
+    const int nchunks = rows / kBM, cpr = c.rows_per_rank / kBM;
     const int chunk_bytes = kBM * p.K * 2;
     const int ppc = ag_pieces_per_chunk(p.K);
     const int parts = ag_parts_per_chunk(p.K);
@@ -372,11 +382,24 @@ __device__ __noinline__ bool ag_copy_role(const GemmArgs& p, uint8_t* ring, int 
       q.end = min(ppc, q.piece + pp);
     };
     auto valid = [&](const Cursor& q) { return q.pos < nchunks; };
-    auto advance = [&](Cursor& q) {
+    auto next_part = [&](Cursor& q) {
+      q.part += H;
+      while (q.part >= parts) { q.part -= parts; ++q.pos; }
+    };
+    // opens the part under the cursor, passing over parts that need no copy (`announce`: the cursor that issues the
+    // stores also publishes those parts; the load cursor walks the same sequence silently)
+    auto settle = [&](Cursor& q, bool announce) {
+      while (valid(q)) {
+        open_part(q);
+        if (!(skip_local && q.src == q.dst)) break;
+        if (announce) red_release_gpu_add_u32(c.flags + q.mblk, 1u);
+        next_part(q);
+      }
+    };
+    auto advance = [&](Cursor& q, bool announce) {
       if (++q.piece == q.end) {
-        q.part += H;
-        while (q.part >= parts) { q.part -= parts; ++q.pos; }
-        if (valid(q)) open_part(q);
+        next_part(q);
+        settle(q, announce);
       }
       if (++q.stage == kAgStages) { q.stage = 0; q.parity ^= 1u; }
     };
@@ -385,13 +408,14 @@ __device__ __noinline__ bool ag_copy_role(const GemmArgs& p, uint8_t* ring, int 
     };
     const int g0 = static_cast<int>(blockIdx.x);
     Cursor ld{g0 / parts, g0 % parts, 0, 0, 0, 0, 0u, nullptr, nullptr};
-    if (valid(ld)) open_part(ld);
     Cursor st = ld;
+    settle(ld, false);
+    settle(st, true);
     auto issue = [&]() {
       const uint32_t bytes = piece_bytes(ld);
       ptx::mbar_expect_tx(&ag_bar[ld.stage], bytes);
       ptx::bulk_load(ring + ld.stage * kAgPiece, ld.src + ld.piece * kAgPiece, bytes, &ag_bar[ld.stage]);
-      advance(ld);
+      advance(ld, false);
     };
     // the store issued from `stage` has completed: if it closed a part, tell the GEMM CTAs
     auto publish = [&](int stage) {
@@ -410,7 +434,7 @@ __device__ __noinline__ bool ag_copy_role(const GemmArgs& p, uint8_t* ring, int 
       ptx::bulk_store(st.dst + st.piece * kAgPiece, ring + st.stage * kAgPiece, piece_bytes(st));
       ptx::bulk_commit();
       ag_sig[st.stage] = (st.piece == st.end - 1) ? st.mblk : -1;
-      advance(st);
+      advance(st, true);
       // all but the newest kAgStoresInFlight - 1 stores are complete: the oldest one can be published and its stage
       // reused (waiting for a store issued several pieces ago costs little; waiting for the newest would serialise
       // the ring on the latency of a store)
@@ -442,33 +466,6 @@ __device__ __noinline__ bool ag_copy_role(const GemmArgs& p, uint8_t* ring, int 
   return ag_ok != 0;
 }
 
-#ifdef TITB_GEMM_PARAM_GATHER
-// mode 3 helper CTA: pull 128-row chunks of the weight from the ranks that own them into the local full copy.
-__device__ void param_gather_role(const GemmArgs& p) {
-  const CollArgs& c = p.coll;
-  const int nchunks = p.N / kBM, cpr = c.rows_per_rank / kBM;
-  const long long vec_per_chunk = static_cast<long long>(kBM) * p.K / 8;  // 16-byte units
-  for (int pos = blockIdx.x; pos < nchunks; pos += c.helper_ctas) {
-    const int chunk = (pos + c.rank * cpr) % nchunks;
-    const int src_rank = chunk / cpr;
-    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const bf16*>(c.peers[src_rank]) +
-                                                      static_cast<long long>(chunk - src_rank * cpr) * kBM * p.K);
-    uint4* dst = reinterpret_cast<uint4*>(c.gathered + static_cast<long long>(chunk) * kBM * p.K);
-    if (src != dst) {   // the owner's rows of the local copy are the authoritative ones: nothing to move
-      long long i = threadIdx.x;
-      for (; i + 3 * kGemmThreads < vec_per_chunk; i += 4 * kGemmThreads) {
-        const uint4 v0 = src[i], v1 = src[i + kGemmThreads], v2 = src[i + 2 * kGemmThreads], v3 = src[i + 3 * kGemmThreads];
-        dst[i] = v0; dst[i + kGemmThreads] = v1; dst[i + 2 * kGemmThreads] = v2; dst[i + 3 * kGemmThreads] = v3;
-      }
-      for (; i < vec_per_chunk; i += kGemmThreads) dst[i] = src[i];
-      fence_proxy_async_all();  // these generic-proxy writes are read by TMA (async proxy) below
-      __threadfence();
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) st_release_gpu_u32(c.flags + chunk, 1u);
-  }
-}
-#endif
 
 // mode 2, second phase: when a CTA has pushed all its partial tiles, its four epilogue warps (128 threads, named
 // barrier 1) help to sum the `world` partial slots of this rank's rows.  A work unit is a 128-row chunk x a strip of
@@ -569,21 +566,17 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
-  // Leading CTAs of a fused-collective launch first move the remote operand.  All-gather -> GEMM: the operand ring
-  // is their copy ring, and when the copies are done they join the tile list (TileWalk).  Parameter gather: they
-  // leave when the weight is in place.
-  const int helpers = (!PAIR && (p.coll.mode == 1 || p.coll.mode == 3)) ? p.coll.helper_ctas : 0;
+  // Leading CTAs of a fused-collective launch first move the remote operand (activation rows in mode 1, weight rows in
+  // mode 3): the operand ring is their copy ring, and when the copies are done they join the tile list (TileWalk).
+  const int helpers = (!PAIR && p.coll.mode == kGatherMode) ? p.coll.helper_ctas : 0;
   if (!PAIR && static_cast<int>(blockIdx.x) < helpers) {
-    if (p.coll.mode == 1) {
+    if (p.coll.mode == kGatherMode) {
       constexpr int kRingPieces = Cfg::kRing / kAgPiece;   // the operand ring doubles as the copy ring
       static_assert(kRingPieces >= 2 * kAgStoresInFlight, "the copy ring needs stages for loads and for stores in flight");
       if (!ag_copy_role(p, smem, kRingPieces < kAgMaxStages ? kRingPieces : kAgMaxStages)) return;
     }
-#ifdef TITB_GEMM_PARAM_GATHER
-    else if (p.coll.mode == 3) { param_gather_role(p); return; }
-#endif
   }
-  const bool joined = !PAIR && p.coll.mode == 1;   // helper CTAs take tiles too
+  const bool joined = !PAIR && p.coll.mode == kGatherMode;   // helper CTAs take tiles too
   // a pair walks the tile list as one unit
   const int cta = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x) - (joined ? 0 : helpers);
   const int ncta = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x) - (joined ? 0 : helpers);
@@ -671,7 +664,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
           // every 128-row chunk of the weight under this B tile must have landed in the local copy
           const int c_lo = n0 / kBM, c_hi = (min(n0 + BN, p.N) - 1) / kBM;
           for (int c = c_lo; c <= c_hi && ok; ++c) {
-            if (!wait_flag_ge<false>(p.coll.flags + c, 1u)) {
+            if (!wait_flag_ge<false>(p.coll.flags + c, static_cast<uint32_t>(ag_parts_per_chunk(p.K)))) {
               *abort_flag = 1u;
               atomicExch(p.status, kStatusPeerTimeout);
               ok = false;
@@ -1322,14 +1315,16 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
     return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
   }
   const int sms = device_sm_count();
-  if (args.coll.mode == 1) {
-    // All-gather -> GEMM: how many CTAs copy, and for how many rounds of the tile list they are excused.  The copy
-    // has to stay ahead of the GEMM CTAs, which reach the first remote rows after 1 / world of the tiles; the model
-    // below (microseconds of one CTA) errs on the side of more helpers, which cost little because they join the
-    // GEMM afterwards.  A copying CTA moves about 35 GB/s of local memory (measured) and less from a peer.
+  if (args.coll.mode == 1 || args.coll.mode == 3) {
+    // All-gather -> GEMM (of activation rows, or of weight rows in mode 3): how many CTAs copy, and for how many rounds
+    // of the tile list they are excused.  The copy has to stay ahead of the GEMM CTAs, which reach the first remote rows
+    // after 1 / world of the tiles; the model below (microseconds of one CTA) errs on the side of more helpers, which
+    // cost little because they join the GEMM afterwards.  A copying CTA moves about 35 GB/s of local memory (measured)
+    // and less from a peer; the owner's rows of a gathered weight are already in place.
     GemmArgs a2 = args;
     const double t_tile = 2.0 * kBM * BN * args.K / (kTflopsPerSm * 1e6);
-    const double remote = 2.0 * args.K * args.coll.rows_per_rank * (args.coll.world - 1), local = 2.0 * args.K * args.coll.rows_per_rank;
+    const double shard = 2.0 * args.K * args.coll.rows_per_rank;
+    const double remote = shard * (args.coll.world - 1), local = args.coll.mode == 1 ? shard : 0.0;
     const double w_copy = remote / 15e3 + local / 35e3;                  // CTA-microseconds
     const double t_total = (tiles * t_tile + w_copy) / sms;
     int H = args.coll.helper_ctas;
@@ -1348,9 +1343,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
     gemm_bf16_tcgen05_kernel<BN, PAIR><<<grid, kGemmThreads, Cfg::kSmem, stream>>>(ta, tb, tout, taux, a2);
     return static_cast<int>(cudaGetLastError());
   }
-  const int helpers = args.coll.mode == 3 ? args.coll.helper_ctas : 0;
-  int grid = tiles + helpers < sms ? tiles + helpers : sms;
-  if (grid <= helpers) return TITB_ERR_SHAPE;
+  int grid = tiles < sms ? tiles : sms;
   gemm_bf16_tcgen05_kernel<BN, PAIR><<<grid, kGemmThreads, Cfg::kSmem, stream>>>(ta, tb, tout, taux, args);
   return static_cast<int>(cudaGetLastError());
 }
@@ -1424,11 +1417,11 @@ TITB_API int TITB_GEMM_ENTRY(const TitbGemmDesc* d, cudaStream_t stream) {
 #ifdef TITB_GEMM_PARAM_GATHER
     if (c->mode != 3) return TITB_ERR_SHAPE;   // this copy of the kernel serves the parameter gather only
     if (c->world < 1 || c->world > 16 || c->rows_per_rank % kBM || d->N != c->rows_per_rank * c->world || splits != 1 ||
-        (d->K & 7) || c->helper_ctas < 1 || d->b_mn_major || d->ldb != d->K || d->b != c->gathered || (bn != 128 && bn != 256))
+        (d->K & 7) || d->b_mn_major || d->ldb != d->K || d->b != c->gathered || (bn != 128 && bn != 256))   // helper_ctas <= 0: the launcher chooses
       return TITB_ERR_SHAPE;
 #else
     if (c->world < 1 || c->world > 16 || c->rows_per_rank % kBM || d->M != c->rows_per_rank * c->world || splits != 1 ||
-        (d->N & 7) || (d->K & 7) || (c->mode != 1 && c->helper_ctas < 1))   // mode 1: helper_ctas <= 0 lets the launcher choose
+        (d->N & 7) || (d->K & 7))   // mode 1: helper_ctas <= 0 lets the launcher choose
       return TITB_ERR_SHAPE;
 #endif
     if (c->mode == 2 && (d->epilogue != TITB_EPI_NONE || d->accumulate || d->alpha)) return TITB_ERR_SHAPE;

@@ -77,7 +77,7 @@ class GatheredWeightLinear(tnn.Module):
     kParamBiasName = "bias"
 
     def __init__(self, in_features: int, out_features: int, bias: bool = True, group: Optional[dist.ProcessGroup] = None,
-                 device=None, dtype=torch.bfloat16, helper_ctas: int = 8, channel: int = 3):
+                 device=None, dtype=torch.bfloat16, helper_ctas: int = 0, channel: int = 3):
         super().__init__()
         self.group = group if group is not None else dist.group.WORLD
         self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)

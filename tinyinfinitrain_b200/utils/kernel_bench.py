@@ -201,7 +201,7 @@ def main():
         ptrs = [copies[r].data_ptr() + r * npr * K * 2 for r in range(W)]
         flops = 2.0 * M * N * K
         bytes_ = 2.0 * (M * K + 2 * N * K + M * N)
-        fn = lambda: C.gemm_param_gather(X, copies[0], ptrs, 0, helper_ctas=a.helpers or 8)
+        fn = lambda: C.gemm_param_gather(X, copies[0], ptrs, 0, helper_ctas=max(a.helpers, 0))
     elif a.kernel == "gemm_rs":
         M, N, K = a.m, a.n, a.k
         A, B = torch.randn(M, K, device=dev).to(bf), torch.randn(N, K, device=dev).to(bf)
