@@ -203,7 +203,7 @@ def main():
 
         cfg = GPT2Config(block_size=max(32, args.seq), vocab_size=1000, n_layer=2, n_head=4, n_embd=64) \
             if spec["family"] == "gpt2" else \
-            LLaMA3Config(block_size=max(32, args.seq), vocab_size=1024, n_layer=2, n_head=4, n_kv_head=2, n_embd=64, ffn_dim=128)
+            LLaMA3Config(block_size=max(32, args.seq), vocab_size=1024, n_layer=2, n_head=16, n_kv_head=8, n_embd=128, ffn_dim=256)
         label = f"{spec['family']}-tiny (dry run)"
     if args.layers:
         cfg.n_layer = args.layers

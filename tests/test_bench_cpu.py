@@ -57,3 +57,20 @@ def test_pipeline_bubble_bench_two_stages_dry_run():
     assert out["stages"] == 2 and out["micro_batches"] == 2 and out["ms_2m"] > 0 and out["ms_m"] > 0
     assert abs(out["bubble_ideal"] - 1.0 / 3.0) < 1e-9 and abs(out["bubble_ideal_2m"] - 0.2) < 1e-9
     assert abs(out["slot_ms"] * 2 - (out["ms_2m"] - out["ms_m"])) < 1e-6
+
+
+import pytest  # noqa: E402
+
+
+@pytest.mark.parametrize("config,parallelism", [("llama1b_tp8", "tp8+sp+dp1"), ("gpt2xl_tp2pp2dp2", "tp2+sp+pp2+dp2+zero1"),
+                                                ("llama8b_tp4dp2", "tp4+sp+dp2+zero1")])
+def test_bench_named_eight_rank_layouts_dry_run(config, parallelism):
+    """The three 8-GPU configurations of the bench with their real process layout (tensor x pipeline x data parallel
+    groups, sequence parallelism, ZeRO-1, 1F1B micro-batches) on eight gloo ranks and a tiny model of the same family."""
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "8", "--master-addr",
+           "127.0.0.1", "--master-port", str(29600 + os.getpid() % 100), "bench.py", "--gpus", "8", "--device", "cpu",
+           "--tiny", "--config", config, "--steps", "2", "--warmup", "3", "--batch", "2", "--seq", "32", "--micro", "2",
+           "--no-baseline"]
+    out = _run(cmd, timeout=900)
+    assert out["n_gpus"] == 8 and out["config"]["name"] == config and out["config"]["parallelism"] == parallelism
+    assert out["value"] > 0 and out["scaling"] == "strong" and out["config"]["final_loss"] > 0
