@@ -73,6 +73,7 @@ struct GemmArgs {
   CollArgs coll;
   int M, N, K;
   int a_mn, b_mn;
+  int a_box3, b_box3;   // MN-major operand arrives as one 3-D TMA box (64 columns x kBK rows x chunks) per k-block
   void* out;
   long long ldo;
   int out_fp32, accumulate, epi;
@@ -686,14 +687,26 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
           };
           if (!PAIR) ptx::mbar_expect_tx(&full[stage], kABytes + kBBytes);
           else if (pair_rank == 0) ptx::mbar_expect_tx(&full[stage], 2 * (kABytes + kBBytes));
+          // An MN-major tile is a row of 64-column chunks (the 128-byte swizzle limits a box to 64 columns).  Over a
+          // 3-D view of the matrix (64 columns, K rows, chunks) all chunks of the tile are ONE box, which lands in
+          // shared memory chunk after chunk exactly as the separate boxes would: one TMA instruction per operand and
+          // k-block instead of two to four (the TMA issue rate bounds the main loop of the weight-gradient form).
+          auto load3 = [&](void* dst, const CUtensorMap* m, int y, int z) {
+            if (PAIR) ptx::tma_load_3d_pair(dst, m, &full[stage], 0, y, z);
+            else ptx::tma_load_3d(dst, m, &full[stage], 0, y, z);
+          };
           if (!p.a_mn) {
             load(a_dst, &tma_a, kb * kBK, m0);
+          } else if (p.a_box3) {
+            load3(a_dst, &tma_a, kb * kBK, m0 >> 6);
           } else {
 #pragma unroll
             for (int j = 0; j < kBM / 64; ++j) load(a_dst + j * (64 * kBK * 2), &tma_a, m0 + j * 64, kb * kBK);
           }
           if (!p.b_mn) {
             load(b_dst, &tma_b, kb * kBK, nb0);
+          } else if (p.b_box3) {
+            load3(b_dst, &tma_b, kb * kBK, nb0 >> 6);
           } else {
 #pragma unroll
             for (int j = 0; j < Cfg::kBRows / 64; ++j) load(b_dst + j * (64 * kBK * 2), &tma_b, nb0 + j * 64, kb * kBK);
@@ -1272,6 +1285,26 @@ static bool deterministic_reductions() {
   static const bool det = [] { const char* e = getenv("TITB200_DETERMINISTIC"); return e && e[0] == '1'; }();
   return det;
 }
+// 3-D view of an MN-major bf16 matrix [k rows, mn columns] (mn a multiple of 64): dims (64, k, mn / 64), so that a box of
+// (64, box_k, chunks) covers `chunks` neighbouring 64-column chunks of box_k rows.
+static bool make_tmap_bf16_mn3d(CUtensorMap* m, const void* base, uint64_t mn, uint64_t k, uint64_t ld, uint32_t box_k,
+                                uint32_t chunks) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn || (mn & 63) || chunks < 1 || chunks > 256) return false;
+  static thread_local bool ctx_bound = false;   // see make_tmap_bf16_2d
+  if (!ctx_bound) {
+    cudaFree(nullptr);
+    ctx_bound = true;
+  }
+  cuuint64_t dims[3] = {64, k, mn / 64};
+  cuuint64_t strides[2] = {ld * 2, 128};
+  cuuint32_t box[3] = {64, box_k, chunks};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 static bool f32_tma_eligible(const TitbGemmDesc* d) {
   return d->out_fp32 && d->epilogue == TITB_EPI_NONE && (d->coll == nullptr || d->coll->mode == 0) &&
          !(reinterpret_cast<uintptr_t>(d->out) & 15) && !(d->ldo & 3) && g_no_tma_store == 0;
@@ -1372,6 +1405,13 @@ TITB_API int TITB_GEMM_ENTRY(const TitbGemmDesc* d, cudaStream_t stream) {
   if (splits > 1 && !red_split && (d->workspace == nullptr || (d->N & 3))) splits = 1;
   // tile_n = 512 asks for CTA pairs on 256 x 256 tiles (cta_group::2); 128 / 192 / 256 are single-CTA 128 x tile_n
   int bn = d->tile_n ? d->tile_n : pick_tile_n(d->M, d->N, d->K, splits);
+  // CTA pairs for long reductions over an MN-major B operand (weight gradients, and dgrads with a wide output): such
+  // a k-block costs a single CTA four TMA boxes for B (64-column boxes under the 128-byte swizzle) plus one or two
+  // for A, a pair stages half of B per CTA.  Measured: 5-16 % faster from 2048 reduction elements per split on,
+  // slower below that and on 768-wide dgrad outputs.
+  if (d->tile_n == 0 && d->b_mn_major && (d->coll == nullptr || d->coll->mode == 0) && d->M >= 2 * kBM && d->N >= 256 &&
+      (num_kb + splits - 1) / splits >= 32 && (d->a_mn_major || d->N >= 1024))
+    bn = 512;
   bool pair = false;
   if (bn == 512) {
     pair = (d->coll == nullptr || d->coll->mode == 0) && d->M > kBM && d->N > 128;
@@ -1380,16 +1420,28 @@ TITB_API int TITB_GEMM_ENTRY(const TitbGemmDesc* d, cudaStream_t stream) {
 
   CUtensorMap ta, tb;
   bool ok;
-  if (!d->a_mn_major) ok = make_tmap_bf16_2d(&ta, d->a, d->K, d->M, d->lda, kBK, kBM);
-  else ok = make_tmap_bf16_2d(&ta, d->a, d->M, d->K, d->lda, 64, kBK);
-  if (!d->b_mn_major) ok = ok && make_tmap_bf16_2d(&tb, d->b, d->K, d->N, d->ldb, kBK, pair ? bn / 2 : bn);
-  else ok = ok && make_tmap_bf16_2d(&tb, d->b, d->N, d->K, d->ldb, 64, kBK);
+  // MN-major operands whose extent is a multiple of 64 are fetched as one 3-D box per k-block; the 2-D map with one
+  // box per 64-column chunk covers ragged extents
+  bool a_box3 = false, b_box3 = false;
+  if (!d->a_mn_major) {
+    ok = make_tmap_bf16_2d(&ta, d->a, d->K, d->M, d->lda, kBK, kBM);
+  } else {
+    a_box3 = (d->M & 63) == 0 && make_tmap_bf16_mn3d(&ta, d->a, d->M, d->K, d->lda, kBK, kBM / 64);
+    ok = a_box3 || make_tmap_bf16_2d(&ta, d->a, d->M, d->K, d->lda, 64, kBK);
+  }
+  if (!d->b_mn_major) {
+    ok = ok && make_tmap_bf16_2d(&tb, d->b, d->K, d->N, d->ldb, kBK, pair ? bn / 2 : bn);
+  } else {
+    b_box3 = (d->N & 63) == 0 && make_tmap_bf16_mn3d(&tb, d->b, d->N, d->K, d->ldb, kBK, (pair ? bn / 2 : bn) / 64);
+    ok = ok && (b_box3 || make_tmap_bf16_2d(&tb, d->b, d->N, d->K, d->ldb, 64, kBK));
+  }
   if (!ok) return TITB_ERR_TENSOR_MAP;
 
   GemmArgs a{};
   a.M = d->M; a.N = d->N; a.K = d->K;
   a.a_mn = d->a_mn_major ? 1 : 0;
   a.b_mn = d->b_mn_major ? 1 : 0;
+  a.a_box3 = a_box3 ? 1 : 0; a.b_box3 = b_box3 ? 1 : 0;
   a.out = (splits > 1 && !red_split) ? d->workspace : d->out;
   a.ldo = d->ldo;
   a.out_fp32 = d->out_fp32; a.accumulate = d->accumulate; a.epi = d->epilogue;
