@@ -85,3 +85,17 @@ def test_single_rank_heap_needs_no_sockets():
     t = heap.tensor(i, 0, torch.int32, 250)
     t.copy_(torch.arange(250, dtype=torch.int32))
     assert int(heap.tensor(i, 0, torch.int32, 250).sum()) == 250 * 249 // 2
+
+
+def test_multicast_is_opt_in(monkeypatch):
+    """NVLink kernels use peer loads / stores unless TITB200_MULTIMEM=1 asks for the NVSwitch multicast address; the older
+    TITB200_NO_MULTIMEM=1 still forces it off."""
+    from tinyinfinitrain_b200.parallel.symm import use_multimem
+
+    monkeypatch.delenv("TITB200_MULTIMEM", raising=False)
+    monkeypatch.delenv("TITB200_NO_MULTIMEM", raising=False)
+    assert use_multimem() is False
+    monkeypatch.setenv("TITB200_MULTIMEM", "1")
+    assert use_multimem() is True
+    monkeypatch.setenv("TITB200_NO_MULTIMEM", "1")
+    assert use_multimem() is False
