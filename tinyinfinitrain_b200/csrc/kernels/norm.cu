@@ -378,45 +378,41 @@ norm_bwd_rows2_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T
   }
 }
 
-// Stage 2 for both gradients in one launch: blockIdx.y = 0 folds the dweight partial rows, 1 the dbias rows.
-__global__ void partial_colsum2_kernel(const float* __restrict__ scratch, float* __restrict__ dw, float* __restrict__ db,
-                                       int used, int nparts, int C, int accumulate) {
-  __shared__ float sm[8][33];
+// Stage 2: out[c] (+)= sum_p scratch[p][c] in a fixed order.  The partial rows are a megabyte at most, so the pass is
+// pure latency: 32 columns per CTA and kFoldTy threads per column, each summing every kFoldTy-th partial row with four
+// independent accumulators (four loads in flight), then one fixed-order fold through shared memory.
+constexpr int kFoldTy = 32;
+__device__ __forceinline__ void fold_partial_rows(const float* __restrict__ src, float* __restrict__ out, int used, int C,
+                                                  int accumulate) {
+  __shared__ float sm[kFoldTy][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + tx;
-  const float* src = scratch + (long long)blockIdx.y * nparts * C;
-  float* out = blockIdx.y == 0 ? dw : db;
-  float s = 0.f;
-  if (c < C)
-    for (int p = ty; p < used; p += 8) s += src[(long long)p * C + c];
-  sm[ty][tx] = s;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  if (c < C) {
+    int p = ty;
+    for (; p + 3 * kFoldTy < used; p += 4 * kFoldTy) {
+      s0 += src[(long long)p * C + c];
+      s1 += src[(long long)(p + kFoldTy) * C + c];
+      s2 += src[(long long)(p + 2 * kFoldTy) * C + c];
+      s3 += src[(long long)(p + 3 * kFoldTy) * C + c];
+    }
+    for (; p < used; p += kFoldTy) s0 += src[(long long)p * C + c];
+  }
+  sm[ty][tx] = (s0 + s1) + (s2 + s3);
   __syncthreads();
   if (ty == 0 && c < C) {
     float t = 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) t += sm[j][tx];
+    for (int j = 0; j < kFoldTy; ++j) t += sm[j][tx];
     out[c] = accumulate ? out[c] + t : t;
   }
 }
 
-// Stage 2: out[c] (+)= sum_p scratch[p][c], in a fixed order.  32 columns per CTA,
-// 8 threads per column each summing every 8th partial row.
-__global__ void partial_colsum_kernel(const float* __restrict__ scratch, float* __restrict__ out, int nparts, int C,
-                                      int accumulate) {
-  __shared__ float sm[8][33];
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-  const int c = blockIdx.x * 32 + tx;
-  float s = 0.f;
-  if (c < C)
-    for (int p = ty; p < nparts; p += 8) s += scratch[(long long)p * C + c];
-  sm[ty][tx] = s;
-  __syncthreads();
-  if (ty == 0 && c < C) {
-    float t = 0.f;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) t += sm[j][tx];
-    out[c] = accumulate ? out[c] + t : t;
-  }
+// Both gradients in one launch: blockIdx.y = 0 folds the dweight partial rows, 1 the dbias rows.
+__global__ void __launch_bounds__(32 * kFoldTy)
+partial_colsum2_kernel(const float* __restrict__ scratch, float* __restrict__ dw, float* __restrict__ db, int used,
+                       int nparts, int C, int accumulate) {
+  fold_partial_rows(scratch + (long long)blockIdx.y * nparts * C, blockIdx.y == 0 ? dw : db, used, C, accumulate);
 }
 
 // Scalar fallbacks (any C): CTA per row, re-reading the row from L1/L2.
@@ -560,7 +556,7 @@ static int norm_bwd_launch(const void* dy, const void* x, const void* w, const v
       if (p.maxv == 2) norm_bwd_kernel<T, 2, 256, RMS><<<used, 256, 0, st>>>(DY, X, W, R, mean, rstd, DX, scratch, rows, C, nparts);
       else norm_bwd_kernel<T, 8, 256, RMS><<<used, 256, 0, st>>>(DY, X, W, R, mean, rstd, DX, scratch, rows, C, nparts);
     }
-    partial_colsum2_kernel<<<dim3((C + 31) / 32, (!RMS && db) ? 2 : 1), 256, 0, st>>>(scratch, dw, db, used, nparts, C, accumulate);
+    partial_colsum2_kernel<<<dim3((C + 31) / 32, (!RMS && db) ? 2 : 1), 32 * kFoldTy, 0, st>>>(scratch, dw, db, used, nparts, C, accumulate);
   } else {
     norm_bwd_dx_generic<T, RMS><<<(unsigned)rows, 256, 0, st>>>(DY, X, W, R, mean, rstd, DX, rows, C);
     norm_bwd_dw_generic<T, RMS><<<(C + 127) / 128, 128, 0, st>>>(DY, X, mean, rstd, dw, db, rows, C, accumulate);

@@ -221,7 +221,7 @@ constexpr int kColsumParts = 296;  // partial rows in the caller-provided scratc
 // columns per lane in registers; the 8 warps of a CTA fold their sums in warp order through shared memory and the
 // CTA writes one partial row.  blockIdx.y selects a strip of 32 * NV * VN columns.
 template <typename T, int NV>
-__global__ void __launch_bounds__(256) colsum_rows_kernel(const T* __restrict__ x, float* __restrict__ scratch,
+__global__ void __launch_bounds__(256, 2) colsum_rows_kernel(const T* __restrict__ x, float* __restrict__ scratch,
                                                           long long rows, int C) {
   constexpr int VN = VecN<T>::n;
   constexpr int kStrip = 32 * NV * VN;
@@ -234,24 +234,28 @@ __global__ void __launch_bounds__(256) colsum_rows_kernel(const T* __restrict__ 
   for (int k = 0; k < NV; ++k)
 #pragma unroll
     for (int e = 0; e < VN; ++e) acc[k][e] = 0.f;
-  for (long long r = gw; r < rows; r += 4 * nw) {
+  // one pointer per lane walks down the rows (row stride of this warp: nw rows); which of the NV vectors of a row lie
+  // inside the matrix is the same for every row
+  const long long step = nw * static_cast<long long>(C);
+  const T* px = x + gw * static_cast<long long>(C) + c0 + lane * VN;
+  bool in[NV];
+#pragma unroll
+  for (int k = 0; k < NV; ++k) in[k] = c0 + (lane + k * 32) * VN < C;
+  for (long long r = gw; r < rows; r += 4 * nw, px += 4 * step) {
     Pack<T, VN> v[4][NV];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      const long long rr = r + q * nw;
+      const bool row_ok = r + q * nw < rows;
 #pragma unroll
-      for (int k = 0; k < NV; ++k) {
-        const int c = c0 + (lane + k * 32) * VN;
-        if (rr < rows && c < C) v[q][k] = ld128(x + rr * C + c);
-      }
+      for (int k = 0; k < NV; ++k)
+        if (row_ok && in[k]) v[q][k] = ld128(px + q * step + k * 32 * VN);
     }
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      const long long rr = r + q * nw;
+      const bool row_ok = r + q * nw < rows;
 #pragma unroll
       for (int k = 0; k < NV; ++k) {
-        const int c = c0 + (lane + k * 32) * VN;
-        if (rr < rows && c < C) {
+        if (row_ok && in[k]) {
 #pragma unroll
           for (int e = 0; e < VN; ++e) acc[k][e] += to_f32(v[q][k].v[e]);
         }
@@ -273,21 +277,31 @@ __global__ void __launch_bounds__(256) colsum_rows_kernel(const T* __restrict__ 
   for (int i = threadIdx.x; i < kStrip; i += blockDim.x)
     if (c0 + i < C) scratch[(long long)blockIdx.x * C + c0 + i] = sm[i];
 }
-__global__ void colsum_stage2(const float* __restrict__ scratch, float* __restrict__ out, int nparts, int C,
-                              int accumulate) {
-  // 32 columns per CTA, 8 threads per column each folding every 8th partial row, fixed order.
-  __shared__ float sm[8][33];
+// Stage 2: out[c] (+)= sum over the partial rows, fixed order.  A megabyte at most, so pure latency: 32 columns per CTA,
+// kFoldTy threads per column, four independent accumulators per thread (four loads in flight), one shared-memory fold.
+constexpr int kFoldTy = 32;
+__global__ void __launch_bounds__(32 * kFoldTy)
+colsum_stage2(const float* __restrict__ scratch, float* __restrict__ out, int nparts, int C, int accumulate) {
+  __shared__ float sm[kFoldTy][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + tx;
-  float s = 0.f;
-  if (c < C)
-    for (int p = ty; p < nparts; p += 8) s += scratch[(long long)p * C + c];
-  sm[ty][tx] = s;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  if (c < C) {
+    int p = ty;
+    for (; p + 3 * kFoldTy < nparts; p += 4 * kFoldTy) {
+      s0 += scratch[(long long)p * C + c];
+      s1 += scratch[(long long)(p + kFoldTy) * C + c];
+      s2 += scratch[(long long)(p + 2 * kFoldTy) * C + c];
+      s3 += scratch[(long long)(p + 3 * kFoldTy) * C + c];
+    }
+    for (; p < nparts; p += kFoldTy) s0 += scratch[(long long)p * C + c];
+  }
+  sm[ty][tx] = (s0 + s1) + (s2 + s3);
   __syncthreads();
   if (ty == 0 && c < C) {
     float t = 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) t += sm[j][tx];
+    for (int j = 0; j < kFoldTy; ++j) t += sm[j][tx];
     out[c] = accumulate ? out[c] + t : t;
   }
 }
@@ -463,7 +477,7 @@ TITB_API int titb_colsum(const void* x, float* out, long long rows, int C, int d
       if (nv == 3) colsum_rows_kernel<float, 3><<<grid, 256, 0, st>>>((const float*)x, scratch, rows, C);
       else colsum_rows_kernel<float, 4><<<grid, 256, 0, st>>>((const float*)x, scratch, rows, C);
     }
-    colsum_stage2<<<(C + 31) / 32, 256, 0, st>>>(scratch, out, parts, C, accumulate);
+    colsum_stage2<<<(C + 31) / 32, 32 * kFoldTy, 0, st>>>(scratch, out, parts, C, accumulate);
   } else {
     if (dtype == 1) colsum_generic<bf16><<<(C + 127) / 128, 128, 0, st>>>((const bf16*)x, out, rows, C, accumulate);
     else colsum_generic<float><<<(C + 127) / 128, 128, 0, st>>>((const float*)x, out, rows, C, accumulate);
